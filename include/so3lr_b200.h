@@ -1,0 +1,140 @@
+/* so3lr_b200 -- C ABI of the B200-native SO3LR energy + force library.
+ *
+ * Plain pointers and sizes only; every device pointer is a CUDA device address on the device the handle was
+ * created on, `stream` is a cudaStream_t passed as void*.  Every function returns an int status
+ * (SO3LR_B200_OK == 0).  Nothing here falls back to the CPU: without a CUDA device the calls fail.
+ *
+ * "Reference" citations name files of the so3lr package (general-molecular-simulations/so3lr) whose behaviour
+ * the entry point replaces.
+ */
+#ifndef SO3LR_B200_H_
+#define SO3LR_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define SO3LR_B200_API __attribute__((visibility("default")))
+#else
+#define SO3LR_B200_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  SO3LR_B200_OK = 0,
+  SO3LR_B200_INVALID_ARGUMENT = 1,
+  SO3LR_B200_CUDA_ERROR = 2,
+  SO3LR_B200_OVERFLOW = 3,      /* a neighbor list did not fit its fixed capacity */
+  SO3LR_B200_NOT_FINITE = 4,    /* NaN / Inf positions */
+  SO3LR_B200_TOO_LARGE = 5
+};
+
+typedef struct so3lr_b200_model so3lr_b200_model;     /* weights + derived tables on one device */
+typedef struct so3lr_b200_system so3lr_b200_system;   /* one evaluation context: atoms, lists, workspaces */
+
+/* Library / ABI version. */
+SO3LR_B200_API int so3lr_b200_version(void);
+SO3LR_B200_API const char* so3lr_b200_status_string(int status);
+
+/* Create the model from the packed float32 parameter blob (host pointer, `n_floats` = 530238 values in the order
+ * of so3lr/params/params.pkl as written by so3lr_b200/params/pack_params.py).
+ * Replaces: MLFFPotentialSparse.create_from_workdir(...) in so3lr/potential.py:17-29 and
+ *           load_model_from_workdir(...) in so3lr/base_calculator.py:24-33. */
+SO3LR_B200_API int so3lr_b200_model_create(const float* blob_host, size_t n_floats, int device, so3lr_b200_model** out);
+SO3LR_B200_API int so3lr_b200_model_destroy(so3lr_b200_model* model);
+
+/* Options of an evaluation context.
+ * cutoff_lr <= 0 : no long-range cutoff (plain erf Coulomb, unswitched dispersion; all pairs inside a graph).
+ * damping   <= 0 : dispersion is not switched off before cutoff_lr.
+ * lr_both_directions: 0 = each pair once, energy booked on the first atom (neighborlist_format_lr
+ *   'ordered_sparse', so3lr/potential.py:22); 1 = both directions at half weight ('sparse',
+ *   so3lr/base_calculator.py:31).
+ * skin: extra list radius; lists are rebuilt when an atom moved more than skin/2 since the last build
+ *   (dr_threshold of so3lr/jaxmd_utils.py:85). */
+typedef struct so3lr_b200_options {
+  float cutoff_lr;
+  float damping;
+  float skin;
+  int lr_both_directions;
+  float lr_list_cutoff;   /* radius of the long-range list when cutoff_lr <= 0; <= 0: all pairs of a graph */
+} so3lr_b200_options;
+
+/* Create a context for `n_atoms` atoms split into `n_graphs` graphs of contiguous atoms
+ * (graph g owns atoms graph_start[g] .. graph_start[g+1]-1; pass n_graphs = 1 and graph_start = NULL for one
+ * structure).  `atomic_numbers`, `graph_start`, `total_charge`, `num_unpaired` are host arrays (the last two may
+ * be NULL = all zero).  `cell` is NULL (free space) or 9 floats, rows = lattice vectors, in Angstrom.
+ * Replaces: the Graph / inputs-dict assembly of so3lr/jaxmd_utils.py:57-73 and so3lr/base_calculator.py:57-86. */
+SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms, const int32_t* atomic_numbers, int n_graphs,
+                             const int32_t* graph_start, const float* total_charge, const float* num_unpaired,
+                             const float* cell, const so3lr_b200_options* options, so3lr_b200_system** out);
+SO3LR_B200_API int so3lr_b200_system_destroy(so3lr_b200_system* sys);
+/* New cell (NPT); forces a list rebuild on the next evaluation. */
+SO3LR_B200_API int so3lr_b200_system_set_cell(so3lr_b200_system* sys, const float* cell);
+
+/* Energy + forces from positions that already live on the device (positions_dev: n_atoms x 3 float32, Cartesian,
+ * Angstrom).  Outputs are device pointers and may be NULL when not wanted:
+ *   forces_dev (n_atoms x 3), e_atom_dev (n_atoms), energy_dev (n_graphs doubles), charges_dev (n_atoms),
+ *   hirshfeld_dev (n_atoms), dipole_dev (n_graphs x 3).
+ * Work is enqueued on `stream`; the call synchronises with the stream only when a neighbor list has to be rebuilt.
+ * Replaces: energy_fn + jax_md.quantity.force of so3lr/jaxmd_utils.py:130-141 (neighbor_fn.update included) and
+ *           so3lr_fn of so3lr/base_calculator.py:95-122. */
+SO3LR_B200_API int so3lr_b200_system_compute(so3lr_b200_system* sys, void* stream, const float* positions_dev, float* forces_dev,
+                              float* e_atom_dev, double* energy_dev, float* charges_dev, float* hirshfeld_dev,
+                              float* dipole_dev);
+
+/* Same evaluation with HOST buffers: copies positions in, results out, and returns after the stream is idle.
+ * This is the call a host application (ASE calculator, so3lr/ase_utils.py:7-28) makes once per step. */
+SO3LR_B200_API int so3lr_b200_system_compute_host(so3lr_b200_system* sys, const float* positions_host, float* forces_host,
+                                   double* energy_host, float* charges_host, float* hirshfeld_host, float* dipole_host);
+
+/* Per-term energies of the last evaluation, per atom, device pointers valid until the next call (aux dictionary of
+ * potential(graph, has_aux=True), so3lr/jaxmd_utils.py:138-139). */
+SO3LR_B200_API int so3lr_b200_system_aux(so3lr_b200_system* sys, const float** zbl_dev, const float** coulomb_dev,
+                          const float** dispersion_dev);
+
+/* Counters: number of list rebuilds, current short-range edges and long-range pairs, kernels launched so far. */
+SO3LR_B200_API int so3lr_b200_system_stats(so3lr_b200_system* sys, int64_t* n_rebuilds, int64_t* n_edges, int64_t* n_pairs,
+                            int64_t* n_launches);
+
+/* Copy the current neighbor lists out in jax-md layout: idx (2, capacity) int32 on the device, padded with n_atoms
+ * (Sparse for the short-range list, OrderedSparse for the long-range one unless lr_both_directions).
+ * which = 0: short range, 1: long range.  Sets *overflow_host when the list does not fit `capacity`.
+ * Replaces: neighbor_fn.allocate / nbrs.update / nbrs.idx / nbrs.did_buffer_overflow
+ *           (so3lr/jaxmd_utils.py:96-121, so3lr/cli/so3lr_md.py:862-876). */
+SO3LR_B200_API int so3lr_b200_system_export_list(so3lr_b200_system* sys, void* stream, const float* positions_dev, int which,
+                                  int32_t* idx_dev, int64_t capacity, int64_t* count_host, int* overflow_host);
+
+/* Graph-level evaluation (the boundary at which the reference differentiates): displacements and index lists are
+ * inputs, the outputs are per-atom energies and the gradients of sum_i g_e_atom[i] * e_atom[i] with respect to the
+ * displacements.  Lists must be grouped by centre index (idx_i non-decreasing); padding entries carry index
+ * n_atoms.  All pointers are device pointers; g_e_atom may be NULL (= ones).
+ * Replaces: potential(graph) and its jax.grad w.r.t. graph.edges / graph.edges_lr
+ *           (so3lr/jaxmd_utils.py:130-141, so3lr/graph.py:3-24). */
+SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* sys, void* stream, int64_t n_edges, const int32_t* idx_i,
+                                 const int32_t* idx_j, const float* edges, int64_t n_pairs, const int32_t* idx_i_lr,
+                                 const int32_t* idx_j_lr, const float* edges_lr, const float* g_e_atom,
+                                 float* e_atom_dev, float* g_edges_dev, float* g_edges_lr_dev, float* charges_dev,
+                                 float* hirshfeld_dev);
+
+/* A velocity-Verlet (NVE) step driven by the library: positions/velocities/forces stay on the device.
+ * masses_dev in amu, dt in fs, velocities in Angstrom/fs.  Runs `n_steps` steps; forces_dev must hold the forces
+ * of positions_dev on entry (call so3lr_b200_system_compute first) and holds the final forces on return.
+ * Replaces: the step body of jax_md.simulate.nve as driven by so3lr/cli/so3lr_md.py:1115-1152. */
+SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* sys, void* stream, int n_steps, float dt_fs, const float* masses_dev,
+                          float* positions_dev, float* velocities_dev, float* forces_dev, double* energy_dev);
+
+/* Host-callable pieces of the device math, exported for the CPU tests (no GPU needed). */
+SO3LR_B200_API void so3lr_b200_host_sph_harm(float x, float y, float z, float* y24);
+SO3LR_B200_API void so3lr_b200_host_sph_harm_vjp(float x, float y, float z, const float* g24, float* g3);
+SO3LR_B200_API void so3lr_b200_host_pair_terms(float r, int zi, int zj, float qi, float qj, float hi, float hj, float cutoff_lr,
+                                float damping, float* out8);
+SO3LR_B200_API void so3lr_b200_host_zbl(const float* blob_host, float r, int zi, int zj, float* out2);
+SO3LR_B200_API void so3lr_b200_host_radial_filter(const float* blob_host, int layer, double r, double* w256, double* dw256);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SO3LR_B200_H_ */

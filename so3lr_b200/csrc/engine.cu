@@ -1,0 +1,594 @@
+// Evaluation contexts and the C ABI of libso3lr_b200 (see include/so3lr_b200.h).
+#include "../../include/so3lr_b200.h"
+
+#include <cmath>
+#include <cstring>
+#include <limits>
+#include <vector>
+
+#include "kernels.h"
+
+using namespace so3lr;
+
+struct so3lr_b200_model {
+  int device = 0;
+  ModelDev M{};
+  std::vector<void*> owned;
+};
+
+namespace {
+
+// tracked device allocation
+struct Pool {
+  std::vector<void*> ptrs;
+  int status = kOk;
+  template <typename T>
+  T* get(size_t n) {
+    void* p = nullptr;
+    if (n == 0) n = 1;
+    if (cudaMalloc(&p, n * sizeof(T)) != cudaSuccess) { status = kCudaError; return nullptr; }
+    ptrs.push_back(p);
+    return (T*)p;
+  }
+  void release() {
+    for (void* p : ptrs) cudaFree(p);
+    ptrs.clear();
+  }
+};
+
+__global__ void fill_kernel(float* p, size_t n, float v) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = v;
+}
+__global__ void combine_energy_kernel(int n, const float* e_nn, const float* e_zbl, const float* e_c, const float* e_d, float* e_atom) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) e_atom[i] = ((e_nn[i] + e_zbl[i]) + e_c[i]) + e_d[i];
+}
+__global__ void moved_kernel(int n, const float* R, const float* Rref, float thr2, int* flag) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float dx = R[3 * (size_t)i] - Rref[3 * (size_t)i], dy = R[3 * (size_t)i + 1] - Rref[3 * (size_t)i + 1],
+        dz = R[3 * (size_t)i + 2] - Rref[3 * (size_t)i + 2];
+  float d2 = dx * dx + dy * dy + dz * dz;
+  if (!(d2 <= thr2)) atomicOr(flag, (d2 != d2 || isinf(d2)) ? 2 : 1);
+}
+__global__ void row_ptr_from_sorted_kernel(int n, long long n_edges, const int* __restrict__ idx_i, int* __restrict__ row_ptr) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i > n) return;
+  // first edge whose centre index is >= i
+  long long lo = 0, hi = n_edges;
+  while (lo < hi) {
+    long long mid = (lo + hi) >> 1;
+    if (idx_i[mid] < i) lo = mid + 1; else hi = mid;
+  }
+  row_ptr[i] = (int)lo;
+}
+__global__ void export_list_kernel(int n, long long count, long long capacity, const int* __restrict__ edge_i,
+                                   const int* __restrict__ nbr_j, int* __restrict__ idx) {
+  long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= capacity) return;
+  idx[e] = e < count ? edge_i[e] : n;
+  idx[capacity + e] = e < count ? nbr_j[e] : n;
+}
+// velocity Verlet halves.  units: eV, Angstrom, amu, fs -> acceleration = F/m * 9.64853321e-3 A/fs^2
+constexpr float kAccel = 9.648533212331e-3f;
+__global__ void vv_first_kernel(int n, float dt, const float* m, float* R, float* V, const float* F) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float s = 0.5f * dt * kAccel / m[i];
+  for (int k = 0; k < 3; ++k) {
+    float v = V[3 * (size_t)i + k] + s * F[3 * (size_t)i + k];
+    V[3 * (size_t)i + k] = v;
+    R[3 * (size_t)i + k] += dt * v;
+  }
+}
+__global__ void vv_second_kernel(int n, float dt, const float* m, float* V, const float* F) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float s = 0.5f * dt * kAccel / m[i];
+  for (int k = 0; k < 3; ++k) V[3 * (size_t)i + k] += s * F[3 * (size_t)i + k];
+}
+
+int make_cell(const float* cell9, Cell* c) {
+  std::memset(c, 0, sizeof(Cell));
+  if (!cell9) { c->periodic = 0; return kOk; }
+  double h[9], inv[9];
+  for (int k = 0; k < 9; ++k) h[k] = cell9[k];
+  double det = h[0] * (h[4] * h[8] - h[5] * h[7]) - h[1] * (h[3] * h[8] - h[5] * h[6]) + h[2] * (h[3] * h[7] - h[4] * h[6]);
+  if (!(std::fabs(det) > 1e-12) || !std::isfinite(det)) return kInvalidArgument;
+  inv[0] = (h[4] * h[8] - h[5] * h[7]) / det; inv[1] = (h[2] * h[7] - h[1] * h[8]) / det; inv[2] = (h[1] * h[5] - h[2] * h[4]) / det;
+  inv[3] = (h[5] * h[6] - h[3] * h[8]) / det; inv[4] = (h[0] * h[8] - h[2] * h[6]) / det; inv[5] = (h[2] * h[3] - h[0] * h[5]) / det;
+  inv[6] = (h[3] * h[7] - h[4] * h[6]) / det; inv[7] = (h[1] * h[6] - h[0] * h[7]) / det; inv[8] = (h[0] * h[4] - h[1] * h[3]) / det;
+  for (int k = 0; k < 9; ++k) { c->h[k] = (float)h[k]; c->hinv[k] = (float)inv[k]; }
+  c->periodic = 1;
+  return kOk;
+}
+
+}  // namespace
+
+struct so3lr_b200_system {
+  so3lr_b200_model* model = nullptr;
+  int n = 0, n_graphs = 1;
+  so3lr_b200_options opt{};
+  Cell cell{};
+  LrParams lr{};
+  Pool pool;
+  // static inputs
+  int *d_Z = nullptr, *d_seg = nullptr, *d_graph_start = nullptr;
+  float* d_total_charge = nullptr;
+  // lists
+  NeighborListDev sr, lrl;
+  NlistWorkspace* nws = nullptr;
+  float* d_Rref = nullptr;
+  int* d_flag = nullptr;
+  int* h_flag = nullptr;   // pinned
+  bool have_lists = false;
+  // graph-level row pointers
+  int *d_rowptr_g = nullptr, *d_rowptr_lr_g = nullptr;
+  // activations
+  float* x[kNumLayers + 1] = {};
+  float* ev[kNumLayers + 1] = {};
+  float *qkv[kNumLayers] = {}, *xa[kNumLayers] = {}, *ev1[kNumLayers] = {}, *z1[kNumLayers] = {}, *x3[kNumLayers] = {},
+        *gate[kNumLayers] = {};
+  float *ze = nullptr, *zq = nullptr, *zh = nullptr, *e_nn = nullptr, *q_raw = nullptr, *hv = nullptr, *q = nullptr, *h = nullptr;
+  float *e_atom = nullptr, *e_zbl = nullptr, *e_coul = nullptr, *e_disp = nullptr;
+  float *gq = nullptr, *gh = nullptr, *gq_raw = nullptr, *ones = nullptr;
+  float *g4 = nullptr, *g_xa = nullptr, *gev_a = nullptr, *gev_b = nullptr, *gev1 = nullptr, *g_qkv = nullptr;
+  float *dR = nullptr, *g_dR = nullptr;
+  long long edge_cap = 0;
+  float* F_int = nullptr;
+  double* d_energy = nullptr;
+  float* d_dipole = nullptr;
+  // host staging
+  float *h_R = nullptr, *h_F = nullptr, *h_q = nullptr, *h_h = nullptr, *h_dip = nullptr;
+  double* h_E = nullptr;
+  float* d_Rstage = nullptr;
+  cudaStream_t own_stream = nullptr;
+  int64_t n_rebuilds = 0, n_launches = 0;
+};
+
+namespace {
+
+void fill(cudaStream_t s, float* p, size_t n, float v) {
+  if (n == 0) return;
+  if (v == 0.f) { cudaMemsetAsync(p, 0, n * sizeof(float), s); return; }
+  fill_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p, n, v);
+}
+
+int ensure_edge_buffers(so3lr_b200_system* S, long long n_edges) {
+  if (n_edges <= S->edge_cap) return kOk;
+  long long cap = n_edges + n_edges / 4 + 1024;
+  if (S->dR) cudaFree(S->dR);
+  if (S->g_dR) cudaFree(S->g_dR);
+  S->dR = S->g_dR = nullptr;
+  SO3LR_CUDA_CHECK(cudaMalloc((void**)&S->dR, (size_t)cap * 3 * sizeof(float)));
+  SO3LR_CUDA_CHECK(cudaMalloc((void**)&S->g_dR, (size_t)cap * 3 * sizeof(float)));
+  S->edge_cap = cap;
+  return kOk;
+}
+
+int rebuild_lists(so3lr_b200_system* S, cudaStream_t st, const float* R) {
+  const float r_sr = kCutoffSr + S->opt.skin;
+  const bool many = S->n_graphs > 1 || !S->cell.periodic;
+  const int* seg = S->n_graphs > 1 ? S->d_seg : nullptr;
+  const int* gs = (S->n_graphs > 1 && !S->cell.periodic) ? S->d_graph_start : nullptr;
+  (void)many;
+  int rc = nlist_build(S->nws, st, S->cell, S->n, R, r_sr, 0, seg, gs, &S->sr, 1, nullptr);
+  if (rc) return rc;
+  float r_lr;
+  const int* gs_lr = gs;
+  if (S->opt.cutoff_lr > 0.f) r_lr = S->opt.cutoff_lr + S->opt.skin;
+  else if (S->opt.lr_list_cutoff > 0.f) r_lr = S->opt.lr_list_cutoff + S->opt.skin;
+  else {
+    r_lr = 1e18f;
+    if (S->cell.periodic) return kInvalidArgument;   // all-pairs long range needs free space
+    gs_lr = S->d_graph_start;                        // loop over the graph's atoms, no cells
+  }
+  rc = nlist_build(S->nws, st, S->cell, S->n, R, r_lr, S->opt.lr_both_directions ? 0 : 1, seg ? seg : (gs_lr ? S->d_seg : nullptr),
+                   gs_lr, &S->lrl, 1, nullptr);
+  if (rc) return rc;
+  SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->d_Rref, R, (size_t)S->n * 3 * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  rc = ensure_edge_buffers(S, S->sr.count);
+  if (rc) return rc;
+  S->have_lists = true;
+  S->n_rebuilds++;
+  S->n_launches += 12;
+  return kOk;
+}
+
+// forward + backward over prepared lists.  graph_mode: displacements given (dR / dR_lr), gradients per edge.
+int evaluate(so3lr_b200_system* S, cudaStream_t st, const float* R, const int* row_ptr, const int* nbr_j, const int* edge_i,
+             long long n_edges, const int* row_ptr_lr, const int* nbr_j_lr, int graph_mode, const float* dR_in,
+             const float* dR_lr_in, float* g_dR_out, float* g_dR_lr_out, const float* ge, float* F) {
+  const ModelDev& M = S->model->M;
+  const int n = S->n;
+  float* dR = graph_mode ? const_cast<float*>(dR_in) : S->dR;
+  float* g_dR = graph_mode ? g_dR_out : S->g_dR;
+  fill(st, S->e_zbl, n, 0.f); fill(st, S->e_coul, n, 0.f); fill(st, S->e_disp, n, 0.f);
+  fill(st, S->gq, n, 0.f); fill(st, S->gh, n, 0.f);
+  if (F) fill(st, F, (size_t)n * 3, 0.f);
+  launch_sr_geometry_zbl(st, M, S->cell, n, n_edges, edge_i, nbr_j, S->d_Z, R, graph_mode, dR, S->e_zbl, g_dR, ge);
+  launch_embed(st, M, S->d_Z, n, S->x[0]);
+  S->n_launches += 8;
+  for (int l = 0; l < kNumLayers; ++l) {
+    const LayerDev& L = M.layer[l];
+    launch_proj_fwd(st, L, S->x[l], n, S->qkv[l]);
+    launch_attn_fwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
+    launch_atom_post_fwd(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]);
+    S->n_launches += 3;
+  }
+  launch_heads_fwd(st, M, n, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv);
+  launch_charge_conserve(st, S->n_graphs, S->d_graph_start, S->q_raw, S->d_total_charge, S->hv, S->q, S->h);
+  launch_pair_lr(st, S->lr, S->cell, n, row_ptr_lr, nbr_j_lr, S->d_Z, R, S->q, S->h, graph_mode ? 1 : 0, dR_lr_in, g_dR_lr_out,
+                 nullptr, F, S->gq, S->gh, S->e_coul, S->e_disp, ge);
+  combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom);
+  // backward
+  launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw);
+  launch_heads_bwd(st, M, n, S->d_Z, S->ze, S->zq, S->zh, S->hv, ge ? ge : S->ones, S->gq_raw, S->gh, S->g4);
+  S->n_launches += 6;
+  float* gev2 = S->gev_a;
+  float* gev_in = S->gev_b;
+  fill(st, gev2, (size_t)n * kMTot, 0.f);
+  for (int l = kNumLayers - 1; l >= 0; --l) {
+    const LayerDev& L = M.layer[l];
+    launch_atom_post_bwd(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, gev2, S->g_xa, S->gev1);
+    if (l > 0) {
+      SO3LR_CUDA_CHECK(cudaMemcpyAsync(gev_in, S->gev1, (size_t)n * kMTot * sizeof(float), cudaMemcpyDeviceToDevice, st));
+      fill(st, S->g_qkv, (size_t)n * kProj, 0.f);
+      launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, g_dR, 0);
+      // dL/dx_in = g_xa (skip connection) + projections^T
+      SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)n * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
+      launch_proj_bwd(st, L, S->g_qkv, n, S->g4, 1);
+      float* t = gev2; gev2 = gev_in; gev_in = t;
+      S->n_launches += 6;
+    } else {
+      launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, nullptr, nullptr, g_dR, 1);
+      S->n_launches += 2;
+    }
+  }
+  if (!graph_mode && F) {
+    launch_force_scatter(st, n, n_edges, edge_i, nbr_j, g_dR, F);
+    S->n_launches += 1;
+  }
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+}  // namespace
+
+extern "C" {
+
+SO3LR_B200_API int so3lr_b200_version(void) { return 100; }
+
+SO3LR_B200_API const char* so3lr_b200_status_string(int status) {
+  switch (status) {
+    case kOk: return "ok";
+    case kInvalidArgument: return "invalid argument";
+    case kCudaError: return "CUDA error";
+    case kOverflow: return "neighbor list overflow";
+    case kNotFinite: return "non-finite positions";
+    case kTooLarge: return "system too large";
+    default: return "unknown status";
+  }
+}
+
+SO3LR_B200_API int so3lr_b200_model_create(const float* blob_host, size_t n_floats, int device, so3lr_b200_model** out) {
+  if (!blob_host || !out) return kInvalidArgument;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+    std::fprintf(stderr, "so3lr_b200: no CUDA device available; this library has no CPU path\n");
+    return kCudaError;
+  }
+  if (device < 0 || device >= count) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(device));
+  so3lr_b200_model* m = new so3lr_b200_model();
+  m->device = device;
+  int rc = build_model(blob_host, n_floats, &m->M, &m->owned);
+  if (rc == kOk) rc = configure_atom_kernels();
+  if (rc == kOk) rc = configure_attention_kernels();
+  if (rc != kOk) { so3lr_b200_model_destroy(m); return rc; }
+  *out = m;
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_model_destroy(so3lr_b200_model* m) {
+  if (!m) return kOk;
+  cudaSetDevice(m->device);
+  for (void* p : m->owned) cudaFree(p);
+  delete m;
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms, const int32_t* Z, int n_graphs, const int32_t* graph_start,
+                             const float* total_charge, const float* num_unpaired, const float* cell9,
+                             const so3lr_b200_options* options, so3lr_b200_system** out) {
+  if (!model || !Z || !out || !options || n_atoms <= 0 || n_graphs <= 0) return kInvalidArgument;
+  if (n_atoms > 64 * 1000 * 1000) return kTooLarge;
+  if (n_graphs > 1 && !graph_start) return kInvalidArgument;
+  if (num_unpaired)
+    for (int g = 0; g < n_graphs; ++g)
+      if (num_unpaired[g] != 0.f) {
+        std::fprintf(stderr, "so3lr_b200: open-shell graphs (num_unpaired_electrons != 0) are not supported\n");
+        return kInvalidArgument;
+      }
+  if (total_charge)
+    for (int g = 0; g < n_graphs; ++g)
+      if (total_charge[g] != 0.f) {
+        std::fprintf(stderr, "so3lr_b200: charged graphs (total_charge != 0) are not supported by the feature embedding\n");
+        return kInvalidArgument;
+      }
+  SO3LR_CUDA_CHECK(cudaSetDevice(model->device));
+  so3lr_b200_system* S = new so3lr_b200_system();
+  S->model = model; S->n = n_atoms; S->n_graphs = n_graphs; S->opt = *options;
+  int rc = make_cell(cell9, &S->cell);
+  if (rc) { delete S; return rc; }
+  // long-range constants
+  LrParams& P = S->lr;
+  P.has_cutoff = options->cutoff_lr > 0.f;
+  P.rc = options->cutoff_lr;
+  P.cuton = kCutonFraction * options->cutoff_lr;
+  P.has_damping = options->damping > 0.f;
+  P.disp_on = options->cutoff_lr - options->damping;
+  P.pair_factor = options->lr_both_directions ? 0.5f : 1.f;
+  if (P.has_cutoff) {
+    double rcd = options->cutoff_lr, sg = kSigmaCoulomb;
+    double pot = std::erf(rcd / sg) / rcd;
+    double dpot = (2.0 / std::sqrt(M_PI) / sg * std::exp(-(rcd / sg) * (rcd / sg)) - pot) / rcd;
+    P.v_rc = (float)pot; P.dv_rc = (float)dpot;
+  }
+  const int n = n_atoms;
+  Pool& A = S->pool;
+  S->d_Z = A.get<int>(n); S->d_seg = A.get<int>(n); S->d_graph_start = A.get<int>(n_graphs + 1);
+  S->d_total_charge = A.get<float>(n_graphs);
+  std::vector<int> gs(n_graphs + 1), seg(n);
+  if (graph_start) { for (int g = 0; g <= n_graphs; ++g) gs[g] = graph_start[g]; }
+  else { gs[0] = 0; gs[1] = n; }
+  if (gs[0] != 0 || gs[n_graphs] != n) { A.release(); delete S; return kInvalidArgument; }
+  for (int g = 0; g < n_graphs; ++g) {
+    if (gs[g + 1] < gs[g]) { A.release(); delete S; return kInvalidArgument; }
+    for (int a = gs[g]; a < gs[g + 1]; ++a) seg[a] = g;
+  }
+  std::vector<float> tq(n_graphs, 0.f);
+  if (total_charge) for (int g = 0; g < n_graphs; ++g) tq[g] = total_charge[g];
+  S->d_Rref = A.get<float>((size_t)n * 3); S->d_flag = A.get<int>(1);
+  S->d_rowptr_g = A.get<int>((size_t)n + 1); S->d_rowptr_lr_g = A.get<int>((size_t)n + 1);
+  for (int l = 0; l <= kNumLayers; ++l) { S->x[l] = A.get<float>((size_t)n * kF); S->ev[l] = A.get<float>((size_t)n * kMTot); }
+  for (int l = 0; l < kNumLayers; ++l) {
+    S->qkv[l] = A.get<float>((size_t)n * kProj); S->xa[l] = A.get<float>((size_t)n * kF); S->ev1[l] = A.get<float>((size_t)n * kMTot);
+    S->z1[l] = A.get<float>((size_t)n * kF); S->x3[l] = A.get<float>((size_t)n * kF); S->gate[l] = A.get<float>((size_t)n * 4);
+  }
+  S->ze = A.get<float>((size_t)n * kF); S->zq = A.get<float>((size_t)n * kF); S->zh = A.get<float>((size_t)n * 64);
+  S->e_nn = A.get<float>(n); S->q_raw = A.get<float>(n); S->hv = A.get<float>(n); S->q = A.get<float>(n); S->h = A.get<float>(n);
+  S->e_atom = A.get<float>(n); S->e_zbl = A.get<float>(n); S->e_coul = A.get<float>(n); S->e_disp = A.get<float>(n);
+  S->gq = A.get<float>(n); S->gh = A.get<float>(n); S->gq_raw = A.get<float>(n); S->ones = A.get<float>(n);
+  S->g4 = A.get<float>((size_t)n * kF); S->g_xa = A.get<float>((size_t)n * kF);
+  S->gev_a = A.get<float>((size_t)n * kMTot); S->gev_b = A.get<float>((size_t)n * kMTot); S->gev1 = A.get<float>((size_t)n * kMTot);
+  S->g_qkv = A.get<float>((size_t)n * kProj);
+  S->F_int = A.get<float>((size_t)n * 3);
+  S->d_energy = A.get<double>(n_graphs); S->d_dipole = A.get<float>((size_t)n_graphs * 3);
+  S->d_Rstage = A.get<float>((size_t)n * 3);
+  if (A.status != kOk) { A.release(); delete S; return A.status; }
+  bool ok = cudaMemcpy(S->d_Z, Z, (size_t)n * sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess &&
+            cudaMemcpy(S->d_seg, seg.data(), (size_t)n * sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess &&
+            cudaMemcpy(S->d_graph_start, gs.data(), (size_t)(n_graphs + 1) * sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess &&
+            cudaMemcpy(S->d_total_charge, tq.data(), (size_t)n_graphs * sizeof(float), cudaMemcpyHostToDevice) == cudaSuccess &&
+            cudaMemset(S->ev[0], 0, (size_t)n * kMTot * sizeof(float)) == cudaSuccess &&
+            cudaMallocHost((void**)&S->h_flag, sizeof(int)) == cudaSuccess &&
+            cudaMallocHost((void**)&S->h_R, (size_t)n * 3 * sizeof(float)) == cudaSuccess &&
+            cudaMallocHost((void**)&S->h_F, (size_t)n * 3 * sizeof(float)) == cudaSuccess &&
+            cudaMallocHost((void**)&S->h_q, (size_t)n * sizeof(float)) == cudaSuccess &&
+            cudaMallocHost((void**)&S->h_h, (size_t)n * sizeof(float)) == cudaSuccess &&
+            cudaMallocHost((void**)&S->h_dip, (size_t)n_graphs * 3 * sizeof(float)) == cudaSuccess &&
+            cudaMallocHost((void**)&S->h_E, (size_t)n_graphs * sizeof(double)) == cudaSuccess &&
+            cudaStreamCreateWithFlags(&S->own_stream, cudaStreamNonBlocking) == cudaSuccess;
+  if (!ok) { so3lr_b200_system_destroy(S); return kCudaError; }
+  fill(nullptr, S->ones, n, 1.f);
+  cudaDeviceSynchronize();
+  S->nws = nlist_workspace_create();
+  *out = S;
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_destroy(so3lr_b200_system* S) {
+  if (!S) return kOk;
+  cudaSetDevice(S->model->device);
+  cudaDeviceSynchronize();
+  S->pool.release();
+  nlist_workspace_destroy(S->nws);
+  for (NeighborListDev* L : {&S->sr, &S->lrl}) { cudaFree(L->row_ptr); cudaFree(L->nbr_j); cudaFree(L->edge_i); }
+  cudaFree(S->dR); cudaFree(S->g_dR);
+  if (S->h_flag) cudaFreeHost(S->h_flag);
+  if (S->h_R) cudaFreeHost(S->h_R);
+  if (S->h_F) cudaFreeHost(S->h_F);
+  if (S->h_q) cudaFreeHost(S->h_q);
+  if (S->h_h) cudaFreeHost(S->h_h);
+  if (S->h_dip) cudaFreeHost(S->h_dip);
+  if (S->h_E) cudaFreeHost(S->h_E);
+  if (S->own_stream) cudaStreamDestroy(S->own_stream);
+  delete S;
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_set_cell(so3lr_b200_system* S, const float* cell9) {
+  if (!S) return kInvalidArgument;
+  int rc = make_cell(cell9, &S->cell);
+  if (rc) return rc;
+  S->have_lists = false;
+  return kOk;
+}
+
+static int prepare_lists(so3lr_b200_system* S, cudaStream_t st, const float* R) {
+  bool rebuild = !S->have_lists;
+  if (!rebuild) {
+    if (S->opt.skin <= 0.f) rebuild = true;
+    else {
+      float thr = 0.5f * S->opt.skin;
+      SO3LR_CUDA_CHECK(cudaMemsetAsync(S->d_flag, 0, sizeof(int), st));
+      moved_kernel<<<(S->n + 255) / 256, 256, 0, st>>>(S->n, R, S->d_Rref, thr * thr, S->d_flag);
+      SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_flag, S->d_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
+      SO3LR_CUDA_CHECK(cudaStreamSynchronize(st));
+      S->n_launches += 1;
+      if (*S->h_flag & 2) return kNotFinite;
+      rebuild = *S->h_flag != 0;
+    }
+  }
+  if (rebuild) return rebuild_lists(S, st, R);
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_compute(so3lr_b200_system* S, void* stream, const float* R, float* F, float* e_atom, double* energy,
+                              float* charges, float* hirshfeld, float* dipole) {
+  if (!S || !R) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = prepare_lists(S, st, R);
+  if (rc) return rc;
+  float* Fout = F ? F : S->F_int;
+  rc = evaluate(S, st, R, S->sr.row_ptr, S->sr.nbr_j, S->sr.edge_i, S->sr.count, S->lrl.row_ptr, S->lrl.nbr_j, 0, nullptr, nullptr,
+                nullptr, nullptr, nullptr, Fout);
+  if (rc) return rc;
+  const int n = S->n;
+  launch_graph_reduce(st, S->n_graphs, S->d_graph_start, S->e_atom, S->q, R, S->d_energy, S->d_dipole);
+  S->n_launches += 1;
+  if (e_atom) SO3LR_CUDA_CHECK(cudaMemcpyAsync(e_atom, S->e_atom, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  if (energy) SO3LR_CUDA_CHECK(cudaMemcpyAsync(energy, S->d_energy, (size_t)S->n_graphs * sizeof(double), cudaMemcpyDeviceToDevice, st));
+  if (charges) SO3LR_CUDA_CHECK(cudaMemcpyAsync(charges, S->q, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  if (hirshfeld) SO3LR_CUDA_CHECK(cudaMemcpyAsync(hirshfeld, S->h, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  if (dipole) SO3LR_CUDA_CHECK(cudaMemcpyAsync(dipole, S->d_dipole, (size_t)S->n_graphs * 3 * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_compute_host(so3lr_b200_system* S, const float* R_host, float* F_host, double* E_host, float* q_host,
+                                   float* h_host, float* dip_host) {
+  if (!S || !R_host) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  cudaStream_t st = S->own_stream;
+  const int n = S->n;
+  std::memcpy(S->h_R, R_host, (size_t)n * 3 * sizeof(float));
+  SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->d_Rstage, S->h_R, (size_t)n * 3 * sizeof(float), cudaMemcpyHostToDevice, st));
+  int rc = so3lr_b200_system_compute(S, st, S->d_Rstage, S->F_int, nullptr, nullptr, nullptr, nullptr, nullptr);
+  if (rc) return rc;
+  if (F_host) SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_F, S->F_int, (size_t)n * 3 * sizeof(float), cudaMemcpyDeviceToHost, st));
+  if (E_host) SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_E, S->d_energy, (size_t)S->n_graphs * sizeof(double), cudaMemcpyDeviceToHost, st));
+  if (q_host) SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_q, S->q, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost, st));
+  if (h_host) SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_h, S->h, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost, st));
+  if (dip_host) SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_dip, S->d_dipole, (size_t)S->n_graphs * 3 * sizeof(float), cudaMemcpyDeviceToHost, st));
+  SO3LR_CUDA_CHECK(cudaStreamSynchronize(st));
+  if (F_host) std::memcpy(F_host, S->h_F, (size_t)n * 3 * sizeof(float));
+  if (E_host) std::memcpy(E_host, S->h_E, (size_t)S->n_graphs * sizeof(double));
+  if (q_host) std::memcpy(q_host, S->h_q, (size_t)n * sizeof(float));
+  if (h_host) std::memcpy(h_host, S->h_h, (size_t)n * sizeof(float));
+  if (dip_host) std::memcpy(dip_host, S->h_dip, (size_t)S->n_graphs * 3 * sizeof(float));
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_aux(so3lr_b200_system* S, const float** zbl, const float** coul, const float** disp) {
+  if (!S) return kInvalidArgument;
+  if (zbl) *zbl = S->e_zbl;
+  if (coul) *coul = S->e_coul;
+  if (disp) *disp = S->e_disp;
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_stats(so3lr_b200_system* S, int64_t* n_rebuilds, int64_t* n_edges, int64_t* n_pairs, int64_t* n_launches) {
+  if (!S) return kInvalidArgument;
+  if (n_rebuilds) *n_rebuilds = S->n_rebuilds;
+  if (n_edges) *n_edges = S->sr.count;
+  if (n_pairs) *n_pairs = S->lrl.count;
+  if (n_launches) *n_launches = S->n_launches;
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_export_list(so3lr_b200_system* S, void* stream, const float* R, int which, int32_t* idx, int64_t capacity,
+                                  int64_t* count_host, int* overflow_host) {
+  if (!S || !R || !idx || capacity <= 0) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  S->have_lists = false;
+  int rc = prepare_lists(S, st, R);
+  if (rc) return rc;
+  const NeighborListDev& L = which == 0 ? S->sr : S->lrl;
+  long long cnt = L.count < capacity ? L.count : capacity;
+  export_list_kernel<<<(unsigned)((capacity + 255) / 256), 256, 0, st>>>(S->n, cnt, capacity, L.edge_i, L.nbr_j, idx);
+  SO3LR_CUDA_CHECK(cudaStreamSynchronize(st));
+  if (count_host) *count_host = L.count;
+  if (overflow_host) *overflow_host = L.count > capacity ? 1 : 0;
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* S, void* stream, int64_t n_edges, const int32_t* idx_i, const int32_t* idx_j,
+                                 const float* edges, int64_t n_pairs, const int32_t* idx_i_lr, const int32_t* idx_j_lr,
+                                 const float* edges_lr, const float* g_e_atom, float* e_atom, float* g_edges, float* g_edges_lr,
+                                 float* charges, float* hirshfeld) {
+  if (!S || !idx_i || !idx_j || !edges || !g_edges || n_edges < 0 || n_pairs < 0) return kInvalidArgument;
+  if (n_pairs > 0 && (!idx_i_lr || !idx_j_lr || !edges_lr || !g_edges_lr)) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  const int n = S->n;
+  row_ptr_from_sorted_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(n, n_edges, idx_i, S->d_rowptr_g);
+  row_ptr_from_sorted_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(n, n_pairs, idx_i_lr, S->d_rowptr_lr_g);
+  S->n_launches += 2;
+  int rc = evaluate(S, st, nullptr, S->d_rowptr_g, idx_j, idx_i, n_edges, S->d_rowptr_lr_g, idx_j_lr, 1, edges, edges_lr, g_edges,
+                    g_edges_lr, g_e_atom, nullptr);
+  if (rc) return rc;
+  if (e_atom) SO3LR_CUDA_CHECK(cudaMemcpyAsync(e_atom, S->e_atom, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  if (charges) SO3LR_CUDA_CHECK(cudaMemcpyAsync(charges, S->q, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  if (hirshfeld) SO3LR_CUDA_CHECK(cudaMemcpyAsync(hirshfeld, S->h, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* S, void* stream, int n_steps, float dt, const float* masses, float* R, float* V,
+                          float* F, double* energy) {
+  if (!S || !masses || !R || !V || !F || n_steps < 0) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  const int n = S->n, blocks = (n + 255) / 256;
+  for (int step = 0; step < n_steps; ++step) {
+    vv_first_kernel<<<blocks, 256, 0, st>>>(n, dt, masses, R, V, F);
+    int rc = so3lr_b200_system_compute(S, st, R, F, nullptr, step == n_steps - 1 ? energy : nullptr, nullptr, nullptr, nullptr);
+    if (rc) return rc;
+    vv_second_kernel<<<blocks, 256, 0, st>>>(n, dt, masses, V, F);
+    S->n_launches += 2;
+  }
+  return kOk;
+}
+
+SO3LR_B200_API void so3lr_b200_host_sph_harm(float x, float y, float z, float* y24) { sph_harm_24(x, y, z, y24); }
+SO3LR_B200_API void so3lr_b200_host_sph_harm_vjp(float x, float y, float z, const float* g24, float* g3) {
+  sph_harm_24_vjp(x, y, z, g24, g3[0], g3[1], g3[2]);
+}
+SO3LR_B200_API void so3lr_b200_host_pair_terms(float r, int zi, int zj, float qi, float qj, float hi, float hj, float cutoff_lr, float damping,
+                                float* out8) {
+  LrParams P{};
+  P.has_cutoff = cutoff_lr > 0.f; P.rc = cutoff_lr; P.cuton = kCutonFraction * cutoff_lr; P.has_damping = damping > 0.f;
+  P.disp_on = cutoff_lr - damping; P.pair_factor = 1.f;
+  if (P.has_cutoff) {
+    double rcd = cutoff_lr, sg = kSigmaCoulomb;
+    double pot = std::erf(rcd / sg) / rcd;
+    P.v_rc = (float)pot;
+    P.dv_rc = (float)((2.0 / std::sqrt(M_PI) / sg * std::exp(-(rcd / sg) * (rcd / sg)) - pot) / rcd);
+  }
+  float chi, dchi;
+  coulomb_chi(P, r, chi, dchi);
+  out8[0] = kKe * qi * qj * chi; out8[1] = kKe * qi * qj * dchi; out8[2] = kKe * qj * chi;
+  dispersion_pair(P, r, zi, zj, hi, hj, out8[3], out8[4], out8[5], out8[6]);
+  out8[7] = 0.f;
+}
+SO3LR_B200_API void so3lr_b200_host_zbl(const float* blob, float r, int zi, int zj, float* out2) {
+  BlobOffsets O = blob_offsets();
+  ZblParams z{};
+  double a[4], c[4], cs = 0.0;
+  auto sp = [](double x) { return x > 30 ? x : std::log1p(std::exp(x)); };
+  for (int k = 0; k < 4; ++k) { a[k] = sp(blob[O.zbl[k]]); c[k] = sp(blob[O.zbl[4 + k]]); cs += c[k]; }
+  for (int k = 0; k < 4; ++k) { z.a[k] = (float)a[k]; z.c[k] = (float)(c[k] / cs); }
+  z.p = (float)sp(blob[O.zbl[8]]); z.d = (float)sp(blob[O.zbl[9]]);
+  float cut, dcut;
+  phys_cutoff(r, cut, dcut);
+  if (r >= kCutoffSr) { cut = 0.f; dcut = 0.f; }
+  zbl_edge(z, r, cut, dcut, zi, zj, out2[0], out2[1]);
+}
+SO3LR_B200_API void so3lr_b200_host_radial_filter(const float* blob, int layer, double r, double* w256, double* dw256) {
+  radial_filter_reference(blob, layer, r, w256, dw256);
+}
+
+}  // extern "C"

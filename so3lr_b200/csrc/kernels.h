@@ -1,0 +1,74 @@
+// Launchers of the SO3LR CUDA kernels (one .cu file per group).
+#pragma once
+#include "model.h"
+
+namespace so3lr {
+
+// ---- atom_kernels.cu ----
+int configure_atom_kernels();
+void launch_embed(cudaStream_t s, const ModelDev& M, const int* Z, int n, float* x);
+void launch_proj_fwd(cudaStream_t s, const LayerDev& L, const float* x, int n, float* qkv);
+void launch_proj_bwd(cudaStream_t s, const LayerDev& L, const float* g_qkv, int n, float* gx, int accumulate);
+void launch_atom_post_fwd(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, float* z1,
+                          float* x3, float* gate, float* x4, float* ev2);
+void launch_atom_post_bwd(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, const float* z1,
+                          const float* x3, const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1);
+void launch_heads_fwd(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* x, float* ze, float* zq, float* zh,
+                      float* e_nn, float* q_raw, float* hv);
+void launch_heads_bwd(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* ze, const float* zq, const float* zh,
+                      const float* hv, const float* ge, const float* gq, const float* gh, float* gx);
+
+// ---- attention.cu ----
+// Short-range edges are grouped by receiver: edges row_ptr[i] .. row_ptr[i+1]-1 belong to centre i and hold the
+// neighbour index nbr_j[e] and the displacement dR[e] (3 floats).  Edges with |dR| >= 4.5, |dR| == 0 or
+// nbr_j >= n are padding.
+int configure_attention_kernels();
+void launch_attn_fwd(cudaStream_t s, const LayerDev& L, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+                     const float* qkv, const float* x_in, const float* ev_in, float* xa, float* ev1);
+// g_xa / gev1: cotangents of xa / ev1.  Adds into g_qkv (k,v parts by atomics; q parts stored), gev_in (atomics; the
+// caller pre-loads it with gev1 for the skip connection) and g_dR (+=).  `first_layer`: only g_dR is produced.
+void launch_attn_bwd(cudaStream_t s, const LayerDev& L, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+                     const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv,
+                     float* gev_in, float* g_dR, int first_layer);
+
+// ---- pair_kernels.cu ----
+// dR for every short-range edge from positions (+ minimum image), ZBL energy into e_atom[centre], ZBL gradient
+// written to g_dR (initialises it).  With `dR_given` the displacements are inputs.
+void launch_sr_geometry_zbl(cudaStream_t s, const ModelDev& M, const Cell& cell, int n, long long n_edges, const int* edge_i,
+                            const int* nbr_j, const int* Z, const float* R, int dR_given, float* dR, float* e_atom, float* g_dR,
+                            const float* ge);
+// F[i] += g, F[j] -= g for every edge
+void launch_force_scatter(cudaStream_t s, int n, long long n_edges, const int* edge_i, const int* nbr_j, const float* g_dR,
+                          float* F);
+// long-range pairs grouped by first atom (row_ptr over i).  mode 0: displacements from positions, forces accumulated;
+// mode 1: displacements given (dR_lr), gradient per pair written to g_dR_lr.
+void launch_pair_lr(cudaStream_t s, const LrParams& P, const Cell& cell, int n, const int* row_ptr, const int* nbr_j,
+                    const int* Z, const float* R, const float* q, const float* h, int mode, const float* dR_lr,
+                    float* g_dR_lr, float* e_atom, float* F, float* gq, float* gh, float* e_coul, float* e_disp,
+                    const float* ge);
+// q = q_raw + (Q_g - sum_g q_raw) / n_g ; h = |hv| ; and the transposed operation for the cotangents
+// (atoms of one graph are contiguous: graph g owns atoms graph_start[g] .. graph_start[g+1]-1)
+void launch_charge_conserve(cudaStream_t s, int n_graphs, const int* graph_start, const float* q_raw,
+                            const float* total_charge, const float* hv, float* q, float* h);
+void launch_charge_conserve_bwd(cudaStream_t s, int n_graphs, const int* graph_start, const float* gq, float* gq_raw);
+// per-graph energy (double) and dipole sums
+void launch_graph_reduce(cudaStream_t s, int n_graphs, const int* graph_start, const float* e_atom, const float* q,
+                         const float* R, double* e_graph, float* dipole);
+
+// ---- nlist.cu ----
+struct NeighborListDev {
+  int* row_ptr = nullptr;    // n + 1
+  int* nbr_j = nullptr;      // capacity
+  int* edge_i = nullptr;     // capacity
+  long long capacity = 0;
+  long long count = 0;       // valid after build
+};
+struct NlistWorkspace;       // opaque scratch (cell ids, sort buffers)
+NlistWorkspace* nlist_workspace_create();
+void nlist_workspace_destroy(NlistWorkspace*);
+// Builds rows for all i.  ordered: keep j > i only.  seg/graph_start (optional): pairs only inside one graph and the
+// candidate loop runs over the graph's atoms.  Grows `out` when `allow_grow`, otherwise sets *overflow (device int).
+int nlist_build(NlistWorkspace* ws, cudaStream_t s, const Cell& cell, int n, const float* R, float r_list, int ordered,
+                const int* seg, const int* graph_start, NeighborListDev* out, int allow_grow, int* d_overflow);
+
+}  // namespace so3lr

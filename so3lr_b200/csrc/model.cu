@@ -1,0 +1,200 @@
+// Host-side preparation of the SO3LR weights: radial-filter tables, transposed kernels, ZBL constants.
+#include "model.h"
+
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+namespace so3lr {
+
+namespace {
+
+double softplus_d(double x) { return x > 30 ? x : std::log1p(std::exp(x)); }
+double silu_d(double x) { return x / (1.0 + std::exp(-x)); }
+double dsilu_d(double x) {
+  double s = 1.0 / (1.0 + std::exp(-x));
+  return s * (1.0 + x * (1.0 - s));
+}
+
+// the reference keeps the Bernstein decay constant as a float32 number
+const double kGamma = (double)(float)0.9448630629184640;
+
+// 32 exponential Bernstein polynomials and d/dr at distance r
+void bernstein(double r, double* b, double* db) {
+  const int n = kNumRbf - 1;
+  double x = std::exp(-kGamma * r);
+  double dx = -kGamma * x;
+  double one = 1.0 - x;
+  double logc = 0.0;  // log C(n,k)
+  for (int k = 0; k <= n; ++k) {
+    if (k > 0) logc += std::log((double)(n - k + 1)) - std::log((double)k);
+    double c = std::exp(logc);
+    double xk = std::pow(x, k), ok = std::pow(one, n - k);
+    b[k] = c * xk * ok;
+    double t1 = k > 0 ? k * std::pow(x, k - 1) * ok : 0.0;
+    double t2 = (n - k) > 0 ? (n - k) * xk * std::pow(one, n - k - 1) : 0.0;
+    db[k] = c * (t1 - t2) * dx;
+  }
+}
+
+// w(r) and dw/dr of both radial filters of one layer, including the constant part of the spherical filter
+void radial_filters(const float* blob, const BlobOffsets& O, int layer, double r, double* w, double* dw) {
+  const LayerOffsets& L = O.layer[layer];
+  double b[kNumRbf], db[kNumRbf];
+  bernstein(r, b, db);
+  for (int f = 0; f < 2; ++f) {
+    const float* k1 = blob + L.rad_l1_k[f];
+    const float* b1 = blob + L.rad_l1_b[f];
+    const float* k2 = blob + L.rad_l2_k[f];
+    const float* b2 = blob + L.rad_l2_b[f];
+    double h[kF], dh[kF];
+    for (int j = 0; j < kF; ++j) {
+      double z = b1[j], dz = 0.0;
+      for (int k = 0; k < kNumRbf; ++k) { z += b[k] * k1[k * kF + j]; dz += db[k] * k1[k * kF + j]; }
+      h[j] = silu_d(z);
+      dh[j] = dsilu_d(z) * dz;
+    }
+    const float* sb2 = blob + L.sph_l2_b[f];
+    for (int j = 0; j < kF; ++j) {
+      double a = (double)b2[j] + (double)sb2[j], da = 0.0;
+      for (int k = 0; k < kF; ++k) { a += h[k] * k2[k * kF + j]; da += dh[k] * k2[k * kF + j]; }
+      w[f * kF + j] = a;
+      dw[f * kF + j] = da;
+    }
+    if (layer == 0) {
+      // ev = 0 in the first layer: spherical filter = Dense2(silu(bias1)) (its bias2 is already added above)
+      const float* sb1 = blob + L.sph_l1_b[f];
+      const float* sk2 = blob + L.sph_l2_k[f];
+      for (int j = 0; j < kF; ++j) {
+        double a = 0.0;
+        for (int c = 0; c < 32; ++c) a += silu_d(sb1[c]) * sk2[c * kF + j];
+        w[f * kF + j] += a;
+      }
+    }
+  }
+}
+
+struct Uploader {
+  std::vector<void*>* owned;
+  int status = kOk;
+  const float* up(const std::vector<float>& v) {
+    void* d = nullptr;
+    if (cudaMalloc(&d, v.size() * sizeof(float)) != cudaSuccess) { status = kCudaError; return nullptr; }
+    if (cudaMemcpy(d, v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) { status = kCudaError; }
+    owned->push_back(d);
+    return (const float*)d;
+  }
+  const float* up(const float* p, size_t n) { return up(std::vector<float>(p, p + n)); }
+  const float* upT(const float* p, int rows, int cols) {  // [rows][cols] -> [cols][rows]
+    std::vector<float> t((size_t)rows * cols);
+    for (int r = 0; r < rows; ++r)
+      for (int c = 0; c < cols; ++c) t[(size_t)c * rows + r] = p[(size_t)r * cols + c];
+    return up(t);
+  }
+};
+
+}  // namespace
+
+void radial_filter_reference(const float* blob, int layer, double r, double* w256, double* dw256) {
+  BlobOffsets O = blob_offsets();
+  radial_filters(blob, O, layer, r, w256, dw256);
+}
+
+int build_model(const float* blob, size_t n_floats, ModelDev* M, std::vector<void*>* owned) {
+  BlobOffsets O = blob_offsets();
+  if (n_floats != O.total) {
+    std::fprintf(stderr, "so3lr_b200: parameter blob has %zu floats, expected %zu\n", n_floats, O.total);
+    return kInvalidArgument;
+  }
+  Uploader U{owned};
+  {
+    std::vector<float> e(blob + O.embed_z, blob + O.embed_z + kZEmbed * kF);
+    const float s = (float)(1.0 / std::sqrt(3.0));
+    for (auto& v : e) v *= s;
+    M->embed_z = U.up(e);
+  }
+  for (int e = 0; e < 2; ++e) {
+    M->cs_embed_q[e] = U.up(blob + O.cs[e].embed_q, kZEmbed * kF);
+    M->cs_embed_k[e] = U.up(blob + O.cs[e].embed_k, 2 * kF);
+    M->cs_embed_v[e] = U.up(blob + O.cs[e].embed_v, 2 * kF);
+    M->cs_res0[e] = U.up(blob + O.cs[e].res0, kF * kF);
+    M->cs_res1[e] = U.up(blob + O.cs[e].res1, kF * kF);
+  }
+  for (int l = 0; l < kNumLayers; ++l) {
+    const LayerOffsets& L = O.layer[l];
+    LayerDev& D = M->layer[l];
+    D.has_spherical = l > 0;
+    // projections
+    std::vector<float> P(5 * 4 * 32 * 32), PT(5 * 4 * 32 * 32);
+    for (int w = 0; w < 5; ++w) {
+      const float* W = blob + L.W[w];
+      for (int h = 0; h < 4; ++h)
+        for (int i = 0; i < 32; ++i)
+          for (int j = 0; j < 32; ++j) {
+            float v = W[(h * 32 + i) * 32 + j];
+            P[((w * 4 + h) * 32 + i) * 32 + j] = v;
+            PT[((w * 4 + h) * 32 + j) * 32 + i] = v;
+          }
+    }
+    D.proj = U.up(P);
+    D.projT = U.up(PT);
+    // radial tables
+    std::vector<float> tab((size_t)kTableGrid * 2 * 256);
+    std::vector<double> w(256), dw(256);
+    for (int g = 0; g < kTableGrid; ++g) {
+      double r = (double)g * (double)kTableH;
+      radial_filters(blob, O, l, r, w.data(), dw.data());
+      for (int j = 0; j < 256; ++j) {
+        tab[((size_t)g * 2 + 0) * 256 + j] = (float)w[j];
+        tab[((size_t)g * 2 + 1) * 256 + j] = (float)(dw[j] * (double)kTableH);
+      }
+    }
+    D.table = U.up(tab);
+    std::vector<float> s1k(2 * 4 * 32), s1b(2 * 32), s2k(2 * 32 * 128);
+    for (int f = 0; f < 2; ++f) {
+      std::memcpy(&s1k[f * 128], blob + L.sph_l1_k[f], 128 * sizeof(float));
+      std::memcpy(&s1b[f * 32], blob + L.sph_l1_b[f], 32 * sizeof(float));
+      std::memcpy(&s2k[f * 4096], blob + L.sph_l2_k[f], 4096 * sizeof(float));
+    }
+    D.sph1_k = U.up(s1k); D.sph1_b = U.up(s1b); D.sph2_k = U.up(s2k);
+    D.ln1_s = U.up(blob + L.ln1_s, kF); D.ln1_b = U.up(blob + L.ln1_b, kF);
+    D.ln2_s = U.up(blob + L.ln2_s, kF); D.ln2_b = U.up(blob + L.ln2_b, kF);
+    D.res1_k = U.up(blob + L.res1_k, kF * kF); D.res1_kT = U.upT(blob + L.res1_k, kF, kF); D.res1_b = U.up(blob + L.res1_b, kF);
+    D.res2_k = U.up(blob + L.res2_k, kF * kF); D.res2_kT = U.upT(blob + L.res2_k, kF, kF); D.res2_b = U.up(blob + L.res2_b, kF);
+    const float* E = blob + L.exch_k;  // [132 in][132 out]
+    std::vector<float> xx(128 * 128), xg(128 * 4), ix(4 * 128), ig(16);
+    for (int i = 0; i < 132; ++i)
+      for (int o = 0; o < 132; ++o) {
+        float v = E[i * 132 + o];
+        if (i < 128 && o < 128) xx[i * 128 + o] = v;
+        else if (i < 128) xg[i * 4 + (o - 128)] = v;
+        else if (o < 128) ix[(i - 128) * 128 + o] = v;
+        else ig[(i - 128) * 4 + (o - 128)] = v;
+      }
+    D.ex_xx = U.up(xx); D.ex_xxT = U.upT(xx.data(), 128, 128);
+    D.ex_xg = U.up(xg); D.ex_ix = U.up(ix); D.ex_ig = U.up(ig);
+    D.ex_bx = U.up(blob + L.exch_b, 128); D.ex_bg = U.up(blob + L.exch_b + 128, 4);
+  }
+  M->e_reg_k = U.up(blob + O.e_reg_k, kF * kF); M->e_reg_kT = U.upT(blob + O.e_reg_k, kF, kF);
+  M->e_reg_b = U.up(blob + O.e_reg_b, kF); M->e_fin_k = U.up(blob + O.e_fin_k, kF);
+  M->e_fin_b = blob[O.e_fin_b];
+  M->e_scale = U.up(blob + O.e_scale, kZEmbed); M->e_offset = U.up(blob + O.e_offset, kZEmbed);
+  M->q_embed = U.up(blob + O.q_embed, kZHead);
+  M->q_reg_k = U.up(blob + O.q_reg_k, kF * kF); M->q_reg_kT = U.upT(blob + O.q_reg_k, kF, kF);
+  M->q_reg_b = U.up(blob + O.q_reg_b, kF); M->q_fin_k = U.up(blob + O.q_fin_k, kF);
+  M->q_fin_b = blob[O.q_fin_b];
+  M->h_embed0 = U.up(blob + O.h_embed0, kZHead); M->h_embed1 = U.up(blob + O.h_embed1, kZHead * 64);
+  M->h_reg_k = U.up(blob + O.h_reg_k, kF * 64); M->h_reg_kT = U.upT(blob + O.h_reg_k, kF, 64);
+  M->h_reg_b = U.up(blob + O.h_reg_b, 64);
+  M->h_fin_k = U.up(blob + O.h_fin_k, 64 * 64); M->h_fin_kT = U.upT(blob + O.h_fin_k, 64, 64);
+  M->h_fin_b = U.up(blob + O.h_fin_b, 64);
+  // ZBL constants: softplus of the raw parameters, weights normalised to one
+  double a[4], c[4], cs = 0.0;
+  for (int k = 0; k < 4; ++k) { a[k] = softplus_d(blob[O.zbl[k]]); c[k] = softplus_d(blob[O.zbl[4 + k]]); cs += c[k]; }
+  for (int k = 0; k < 4; ++k) { M->zbl.a[k] = (float)a[k]; M->zbl.c[k] = (float)(c[k] / cs); }
+  M->zbl.p = (float)softplus_d(blob[O.zbl[8]]);
+  M->zbl.d = (float)softplus_d(blob[O.zbl[9]]);
+  return U.status;
+}
+
+}  // namespace so3lr

@@ -1,0 +1,51 @@
+// Device-resident, kernel-ready form of the SO3LR weights (built once per handle from the packed blob).
+#pragma once
+#include <vector>
+
+#include "common.cuh"
+#include "pair_terms.cuh"
+
+namespace so3lr {
+
+struct LayerDev {
+  const float* projT;   // [5][4][32 j][32 i]   forward projection  (out_i = sum_j W[h][i][j] x[h][j])
+  const float* proj;    // [5][4][32 i][32 j]   as stored; used by the backward projection
+  const float* table;   // [kTableGrid][2][256] radial filters: value, h * d/dr ; (w1 | w2)
+  const float* sph1_k;  // [2][4][32]   spherical filter, first layer kernel (filter, invariant, hidden)
+  const float* sph1_b;  // [2][32]
+  const float* sph2_k;  // [2][32][128] second layer kernel (filter, hidden, feature); bias is folded into `table`
+  const float *ln1_s, *ln1_b, *ln2_s, *ln2_b;
+  const float *res1_k, *res1_kT, *res1_b, *res2_k, *res2_kT, *res2_b;   // [in][out] and transposed
+  const float *ex_xx, *ex_xxT;  // [128][128] features -> features
+  const float* ex_xg;           // [128][4]   features -> gates
+  const float* ex_ix;           // [4][128]   invariants -> features
+  const float* ex_ig;           // [4][4]     invariants -> gates
+  const float* ex_bx;           // [128]
+  const float* ex_bg;           // [4]
+  int has_spherical;            // layer 0 sees ev = 0: its spherical filter is a constant folded into `table`
+};
+
+struct ModelDev {
+  const float* embed_z;   // [119][128], already divided by sqrt(3)
+  LayerDev layer[kNumLayers];
+  // energy head
+  const float *e_reg_k, *e_reg_kT, *e_reg_b, *e_fin_k, *e_scale, *e_offset;
+  float e_fin_b;
+  // partial charge head
+  const float *q_embed, *q_reg_k, *q_reg_kT, *q_reg_b, *q_fin_k;
+  float q_fin_b;
+  // Hirshfeld head
+  const float *h_embed0, *h_embed1, *h_reg_k, *h_reg_kT, *h_reg_b, *h_fin_k, *h_fin_kT, *h_fin_b;
+  // charge / spin embeddings (only evaluated when a graph carries charge or unpaired electrons)
+  const float *cs_embed_q[2], *cs_embed_k[2], *cs_embed_v[2], *cs_res0[2], *cs_res1[2];
+  ZblParams zbl;
+};
+
+// Builds every derived array on the host (double precision where it matters) and uploads it.
+// `owned` receives the device allocations so the handle can free them.
+int build_model(const float* blob, size_t n_floats, ModelDev* out, std::vector<void*>* owned);
+
+// host helper exposed for tests: evaluate the radial-filter table entry (value, derivative) directly
+void radial_filter_reference(const float* blob, int layer, double r, double* w256, double* dw256);
+
+}  // namespace so3lr

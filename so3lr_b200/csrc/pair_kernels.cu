@@ -1,0 +1,244 @@
+// Edge geometry + ZBL repulsion on the short-range graph, the fused long-range pair kernel (damped Coulomb +
+// dispersion with analytic gradients) and the small per-graph reductions around them.
+#include "kernels.h"
+
+namespace so3lr {
+
+namespace {
+
+__global__ void sr_geometry_zbl_kernel(ZblParams zbl, Cell cell, int n, long long n_edges, const int* __restrict__ edge_i,
+                                       const int* __restrict__ nbr_j, const int* __restrict__ Z, const float* __restrict__ R,
+                                       int dR_given, float* __restrict__ dR, float* __restrict__ e_atom,
+                                       float* __restrict__ g_dR, const float* __restrict__ ge) {
+  long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n_edges) return;
+  const int i = edge_i[e], j = nbr_j[e];
+  float dx = 0.f, dy = 0.f, dz = 0.f;
+  const bool valid = i >= 0 && i < n && j >= 0 && j < n;
+  if (dR_given) {
+    dx = dR[3 * e]; dy = dR[3 * e + 1]; dz = dR[3 * e + 2];
+  } else {
+    if (valid) {
+      dx = R[3 * (size_t)j] - R[3 * (size_t)i];
+      dy = R[3 * (size_t)j + 1] - R[3 * (size_t)i + 1];
+      dz = R[3 * (size_t)j + 2] - R[3 * (size_t)i + 2];
+      min_image(cell, dx, dy, dz);
+    }
+    dR[3 * e] = dx; dR[3 * e + 1] = dy; dR[3 * e + 2] = dz;
+  }
+  float gx = 0.f, gy = 0.f, gz = 0.f;
+  const float r2 = dx * dx + dy * dy + dz * dz;
+  if (valid && r2 > 0.f && r2 < kZblSwitchOff * kZblSwitchOff) {
+    const float r = sqrtf(r2);
+    float cut, dcut, ez, dez;
+    phys_cutoff(r, cut, dcut);
+    zbl_edge(zbl, r, cut, dcut, Z[i], Z[j], ez, dez);
+    atomicAdd(e_atom + i, ez);
+    const float s = (ge ? ge[i] : 1.f) * dez / r;
+    gx = s * dx; gy = s * dy; gz = s * dz;
+  }
+  g_dR[3 * e] = gx; g_dR[3 * e + 1] = gy; g_dR[3 * e + 2] = gz;
+}
+
+__global__ void force_scatter_kernel(int n, long long n_edges, const int* __restrict__ edge_i, const int* __restrict__ nbr_j,
+                                     const float* __restrict__ g_dR, float* __restrict__ F) {
+  long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n_edges) return;
+  const float gx = g_dR[3 * e], gy = g_dR[3 * e + 1], gz = g_dR[3 * e + 2];
+  if (gx == 0.f && gy == 0.f && gz == 0.f) return;
+  const int i = edge_i[e], j = nbr_j[e];
+  if (i < 0 || i >= n || j < 0 || j >= n) return;
+  // E depends on dR = R_j - R_i:  F_i = +g, F_j = -g
+  atomicAdd(F + 3 * (size_t)i, gx); atomicAdd(F + 3 * (size_t)i + 1, gy); atomicAdd(F + 3 * (size_t)i + 2, gz);
+  atomicAdd(F + 3 * (size_t)j, -gx); atomicAdd(F + 3 * (size_t)j + 1, -gy); atomicAdd(F + 3 * (size_t)j + 2, -gz);
+}
+
+// one warp per row i; lanes stride over the row's pairs
+template <int MODE>
+__global__ void __launch_bounds__(256) pair_lr_kernel(LrParams P, Cell cell, int n, const int* __restrict__ row_ptr,
+                                                      const int* __restrict__ nbr_j, const int* __restrict__ Z,
+                                                      const float* __restrict__ R, const float* __restrict__ q,
+                                                      const float* __restrict__ h, const float* __restrict__ dR_lr,
+                                                      float* __restrict__ g_dR_lr, float* __restrict__ e_atom,
+                                                      float* __restrict__ F, float* __restrict__ gq, float* __restrict__ gh,
+                                                      float* __restrict__ e_coul, float* __restrict__ e_disp, const float* __restrict__ ge) {
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (i >= n) return;
+  const int e0 = row_ptr[i], e1 = row_ptr[i + 1];
+  if (e0 == e1) return;
+  const float qi = q[i], hi = h[i];
+  const int Zi = Z[i];
+  const float gei = ge ? ge[i] : 1.f;
+  float xi = 0.f, yi = 0.f, zi = 0.f;
+  if (MODE == 0) { xi = R[3 * (size_t)i]; yi = R[3 * (size_t)i + 1]; zi = R[3 * (size_t)i + 2]; }
+  float ec = 0.f, ed = 0.f, fx = 0.f, fy = 0.f, fz = 0.f, gqi = 0.f, ghi = 0.f;
+  for (int e = e0 + lane; e < e1; e += 32) {
+    const int j = nbr_j[e];
+    float gx = 0.f, gy = 0.f, gz = 0.f;
+    if (j >= 0 && j < n) {
+      float dx, dy, dz;
+      if (MODE == 0) {
+        dx = R[3 * (size_t)j] - xi; dy = R[3 * (size_t)j + 1] - yi; dz = R[3 * (size_t)j + 2] - zi;
+        min_image(cell, dx, dy, dz);
+      } else {
+        dx = dR_lr[3 * (size_t)e]; dy = dR_lr[3 * (size_t)e + 1]; dz = dR_lr[3 * (size_t)e + 2];
+      }
+      const float r2 = dx * dx + dy * dy + dz * dz;
+      if (r2 > 0.f && (!P.has_cutoff || r2 < P.rc * P.rc)) {
+        const float r = sqrtf(r2);
+        float chi, dchi;
+        coulomb_chi(P, r, chi, dchi);
+        const float qj = q[j], hj = h[j];
+        const float pf = P.pair_factor;
+        const float kq = pf * kKe;
+        const float e_c = kq * qi * qj * chi;
+        float e_d, dd_dr, dd_dhi, dd_dhj;
+        dispersion_pair(P, r, Zi, Z[j], hi, hj, e_d, dd_dr, dd_dhi, dd_dhj);
+        e_d *= pf; dd_dr *= pf; dd_dhi *= pf; dd_dhj *= pf;
+        ec += e_c; ed += e_d;
+        gqi = fmaf(kq * qj, chi, gqi);
+        ghi += dd_dhi;
+        atomicAdd(gq + j, gei * kq * qi * chi);
+        atomicAdd(gh + j, gei * dd_dhj);
+        const float de_dr = gei * (kq * qi * qj * dchi + dd_dr);
+        const float s = de_dr / r;
+        gx = s * dx; gy = s * dy; gz = s * dz;   // dE/d(dR), dR = R_j - R_i
+        if (MODE == 0) {
+          fx += gx; fy += gy; fz += gz;
+          atomicAdd(F + 3 * (size_t)j, -gx); atomicAdd(F + 3 * (size_t)j + 1, -gy); atomicAdd(F + 3 * (size_t)j + 2, -gz);
+        }
+      }
+    }
+    if (MODE == 1) { g_dR_lr[3 * (size_t)e] = gx; g_dR_lr[3 * (size_t)e + 1] = gy; g_dR_lr[3 * (size_t)e + 2] = gz; }
+  }
+  ec = warp_sum(ec); ed = warp_sum(ed); gqi = warp_sum(gqi); ghi = warp_sum(ghi);
+  if (MODE == 0) { fx = warp_sum(fx); fy = warp_sum(fy); fz = warp_sum(fz); }
+  if (lane == 0) {
+    if (e_atom) atomicAdd(e_atom + i, ec + ed);
+    if (e_coul) atomicAdd(e_coul + i, ec);
+    if (e_disp) atomicAdd(e_disp + i, ed);
+    atomicAdd(gq + i, gei * gqi);
+    atomicAdd(gh + i, gei * ghi);
+    if (MODE == 0) { atomicAdd(F + 3 * (size_t)i, fx); atomicAdd(F + 3 * (size_t)i + 1, fy); atomicAdd(F + 3 * (size_t)i + 2, fz); }
+  }
+}
+
+// one CTA per graph: q = q_raw + (Q - sum q_raw) / n_g ; h = |hv|
+__global__ void charge_conserve_kernel(int n_graphs, const int* __restrict__ graph_start, const float* __restrict__ q_raw,
+                                       const float* __restrict__ total_charge, const float* __restrict__ hv,
+                                       float* __restrict__ q, float* __restrict__ h) {
+  __shared__ float red[32];
+  const int g = blockIdx.x;
+  const int a0 = graph_start[g], a1 = graph_start[g + 1];
+  float s = 0.f;
+  for (int a = a0 + threadIdx.x; a < a1; a += blockDim.x) s += q_raw[a];
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) red[0] = v;
+  }
+  __syncthreads();
+  const float Q = total_charge ? total_charge[g] : 0.f;
+  const float corr = a1 > a0 ? (Q - red[0]) / (float)(a1 - a0) : 0.f;
+  for (int a = a0 + threadIdx.x; a < a1; a += blockDim.x) {
+    q[a] = q_raw[a] + corr;
+    h[a] = fabsf(hv[a]);
+  }
+}
+
+// gq_raw = gq - mean_graph(gq)
+__global__ void charge_conserve_bwd_kernel(int n_graphs, const int* __restrict__ graph_start, const float* __restrict__ gq,
+                                           float* __restrict__ gq_raw) {
+  __shared__ float red[32];
+  const int g = blockIdx.x;
+  const int a0 = graph_start[g], a1 = graph_start[g + 1];
+  float s = 0.f;
+  for (int a = a0 + threadIdx.x; a < a1; a += blockDim.x) s += gq[a];
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) red[0] = v;
+  }
+  __syncthreads();
+  const float mean = a1 > a0 ? red[0] / (float)(a1 - a0) : 0.f;
+  for (int a = a0 + threadIdx.x; a < a1; a += blockDim.x) gq_raw[a] = gq[a] - mean;
+}
+
+// per-graph energy (double accumulation) and dipole sum_i q_i R_i; one CTA per graph
+__global__ void graph_reduce_kernel(int n_graphs, const int* __restrict__ graph_start, const float* __restrict__ e_atom,
+                                    const float* __restrict__ q, const float* __restrict__ R, double* __restrict__ e_graph,
+                                    float* __restrict__ dipole) {
+  __shared__ double red[4][32];
+  const int g = blockIdx.x;
+  const int a0 = graph_start[g], a1 = graph_start[g + 1];
+  double v[4] = {0.0, 0.0, 0.0, 0.0};
+  for (int a = a0 + threadIdx.x; a < a1; a += blockDim.x) {
+    v[0] += (double)e_atom[a];
+    if (R) {
+      float qa = q[a];
+      v[1] += (double)(qa * R[3 * (size_t)a]); v[2] += (double)(qa * R[3 * (size_t)a + 1]); v[3] += (double)(qa * R[3 * (size_t)a + 2]);
+    }
+  }
+  for (int k = 0; k < 4; ++k) {
+    double s = v[k];
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) red[k][threadIdx.x >> 5] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x < 4) {
+    double s = 0.0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += red[threadIdx.x][w];
+    if (threadIdx.x == 0) e_graph[g] = s;
+    else if (dipole) dipole[3 * g + threadIdx.x - 1] = (float)s;
+  }
+}
+
+}  // namespace
+
+void launch_sr_geometry_zbl(cudaStream_t s, const ModelDev& M, const Cell& cell, int n, long long n_edges, const int* edge_i,
+                            const int* nbr_j, const int* Z, const float* R, int dR_given, float* dR, float* e_atom, float* g_dR, const float* ge) {
+  if (n_edges <= 0) return;
+  unsigned blocks = (unsigned)((n_edges + 255) / 256);
+  sr_geometry_zbl_kernel<<<blocks, 256, 0, s>>>(M.zbl, cell, n, n_edges, edge_i, nbr_j, Z, R, dR_given, dR, e_atom, g_dR, ge);
+}
+
+void launch_force_scatter(cudaStream_t s, int n, long long n_edges, const int* edge_i, const int* nbr_j, const float* g_dR, float* F) {
+  if (n_edges <= 0) return;
+  unsigned blocks = (unsigned)((n_edges + 255) / 256);
+  force_scatter_kernel<<<blocks, 256, 0, s>>>(n, n_edges, edge_i, nbr_j, g_dR, F);
+}
+
+void launch_pair_lr(cudaStream_t s, const LrParams& P, const Cell& cell, int n, const int* row_ptr, const int* nbr_j,
+                    const int* Z, const float* R, const float* q, const float* h, int mode, const float* dR_lr,
+                    float* g_dR_lr, float* e_atom, float* F, float* gq, float* gh, float* e_coul, float* e_disp, const float* ge) {
+  if (n <= 0) return;
+  int blocks = (n + 7) / 8;
+  if (mode == 0)
+    pair_lr_kernel<0><<<blocks, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, Z, R, q, h, dR_lr, g_dR_lr, e_atom, F, gq, gh, e_coul, e_disp, ge);
+  else
+    pair_lr_kernel<1><<<blocks, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, Z, R, q, h, dR_lr, g_dR_lr, e_atom, F, gq, gh, e_coul, e_disp, ge);
+}
+
+void launch_charge_conserve(cudaStream_t s, int n_graphs, const int* graph_start, const float* q_raw,
+                            const float* total_charge, const float* hv, float* q, float* h) {
+  if (n_graphs <= 0) return;
+  charge_conserve_kernel<<<n_graphs, 256, 0, s>>>(n_graphs, graph_start, q_raw, total_charge, hv, q, h);
+}
+void launch_charge_conserve_bwd(cudaStream_t s, int n_graphs, const int* graph_start, const float* gq, float* gq_raw) {
+  if (n_graphs <= 0) return;
+  charge_conserve_bwd_kernel<<<n_graphs, 256, 0, s>>>(n_graphs, graph_start, gq, gq_raw);
+}
+void launch_graph_reduce(cudaStream_t s, int n_graphs, const int* graph_start, const float* e_atom, const float* q,
+                         const float* R, double* e_graph, float* dipole) {
+  if (n_graphs <= 0) return;
+  graph_reduce_kernel<<<n_graphs, 256, 0, s>>>(n_graphs, graph_start, e_atom, q, R, e_graph, dipole);
+}
+
+}  // namespace so3lr

@@ -1,0 +1,172 @@
+"""Thin object layer over the C ABI: `Model` (weights on one device) and `System` (one evaluation context).
+
+torch is used only to own device memory and streams; every number is produced by libso3lr_b200.so.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import Options, check, lib
+
+_PARAMS = os.path.join(os.path.dirname(os.path.abspath(__file__)), "params", "so3lr_v1.npz")
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if isinstance(t, torch.Tensor):
+        return C.c_void_p(t.data_ptr())
+    return t.ctypes.data_as(C.c_void_p)
+
+
+def load_blob(path=None):
+    return np.ascontiguousarray(np.load(path or _PARAMS)["blob"], dtype=np.float32)
+
+
+class Model:
+    """Pretrained SO3LR weights uploaded to one CUDA device (handle of so3lr_b200_model_create)."""
+    _cache = {}
+
+    def __init__(self, device=0, blob=None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("so3lr_b200 needs a CUDA device (sm_100a); there is no CPU path")
+        self.device = int(device)
+        torch.cuda.init()
+        b = load_blob() if blob is None else np.ascontiguousarray(blob, dtype=np.float32)
+        h = C.c_void_p()
+        check(lib.so3lr_b200_model_create(_ptr(b), b.size, self.device, C.byref(h)), "model_create")
+        self._h = h
+
+    @classmethod
+    def default(cls, device=0):
+        if device not in cls._cache:
+            cls._cache[device] = cls(device)
+        return cls._cache[device]
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            lib.so3lr_b200_model_destroy(h)
+            self._h = None
+
+
+class System:
+    """Evaluation context: atoms (optionally several graphs), neighbor lists and workspaces.
+
+    cell: None or (3,3) with lattice vectors as rows [Angstrom].  cutoff_lr None: no long-range cutoff.
+    lr_format: 'ordered_sparse' (so3lr/potential.py:22) or 'sparse' (so3lr/base_calculator.py:31).
+    """
+
+    def __init__(self, atomic_numbers, cell=None, *, cutoff_lr=12.0, damping=2.0, skin=0.0, lr_format="ordered_sparse",
+                 graph_start=None, total_charge=None, num_unpaired=None, lr_list_cutoff=None, model=None, device=0):
+        self.model = model or Model.default(device)
+        self.device = torch.device("cuda", self.model.device)
+        Z = np.ascontiguousarray(atomic_numbers, dtype=np.int32)
+        self.n = int(Z.size)
+        gs = None if graph_start is None else np.ascontiguousarray(graph_start, dtype=np.int32)
+        self.n_graphs = 1 if gs is None else int(gs.size - 1)
+        tq = None if total_charge is None else np.ascontiguousarray(total_charge, dtype=np.float32).reshape(-1)
+        ts = None if num_unpaired is None else np.ascontiguousarray(num_unpaired, dtype=np.float32).reshape(-1)
+        c9 = None if cell is None else np.ascontiguousarray(np.asarray(cell, dtype=np.float32).reshape(9))
+        opt = Options(float(cutoff_lr) if cutoff_lr else -1.0, float(damping) if damping else -1.0, float(skin),
+                      1 if lr_format == "sparse" else 0, float(lr_list_cutoff) if lr_list_cutoff else -1.0)
+        h = C.c_void_p()
+        check(lib.so3lr_b200_system_create(self.model._h, self.n, _ptr(Z), self.n_graphs, _ptr(gs), _ptr(tq), _ptr(ts),
+                                           _ptr(c9), C.byref(opt), C.byref(h)), "system_create")
+        self._h = h
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            lib.so3lr_b200_system_destroy(h)
+            self._h = None
+
+    def set_cell(self, cell):
+        c9 = np.ascontiguousarray(np.asarray(cell, dtype=np.float32).reshape(9))
+        check(lib.so3lr_b200_system_set_cell(self._h, _ptr(c9)), "set_cell")
+
+    def compute(self, positions, stream=None):
+        """positions: float32 CUDA tensor (n,3).  Returns dict of CUDA tensors (async on the current stream)."""
+        R = positions.to(self.device, torch.float32).contiguous()
+        n, g = self.n, self.n_graphs
+        out = dict(forces=torch.empty(n, 3, device=self.device), e_atom=torch.empty(n, device=self.device),
+                   energy=torch.empty(g, dtype=torch.float64, device=self.device),
+                   partial_charges=torch.empty(n, device=self.device), hirshfeld_ratios=torch.empty(n, device=self.device),
+                   dipole_vec=torch.empty(g, 3, device=self.device))
+        s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        check(lib.so3lr_b200_system_compute(self._h, C.c_void_p(s.cuda_stream), _ptr(R), _ptr(out["forces"]), _ptr(out["e_atom"]),
+                                            _ptr(out["energy"]), _ptr(out["partial_charges"]), _ptr(out["hirshfeld_ratios"]),
+                                            _ptr(out["dipole_vec"])), "system_compute")
+        return out
+
+    def compute_host(self, positions, want_aux=True):
+        """positions: numpy float32 (n,3) on the host; results are numpy arrays (host<->device copies inside)."""
+        R = np.ascontiguousarray(positions, dtype=np.float32)
+        n, g = self.n, self.n_graphs
+        F = np.empty((n, 3), np.float32); E = np.empty(g, np.float64)
+        q = np.empty(n, np.float32) if want_aux else None
+        h = np.empty(n, np.float32) if want_aux else None
+        d = np.empty((g, 3), np.float32) if want_aux else None
+        check(lib.so3lr_b200_system_compute_host(self._h, _ptr(R), _ptr(F), _ptr(E), _ptr(q), _ptr(h), _ptr(d)), "compute_host")
+        return dict(forces=F, energy=E, partial_charges=q, hirshfeld_ratios=h, dipole_vec=d)
+
+    def aux(self):
+        """Per-atom ZBL / Coulomb / dispersion energies of the last evaluation (copies)."""
+        ps = [C.c_void_p() for _ in range(3)]
+        check(lib.so3lr_b200_system_aux(self._h, *[C.byref(p) for p in ps]), "aux")
+        out = {}
+        for name, p in zip(("zbl_repulsion", "electrostatic_energy", "dispersion_energy"), ps):
+            out[name] = _from_ptr(p.value, self.n, self.device).clone()
+        return out
+
+    def stats(self):
+        v = [C.c_int64() for _ in range(4)]
+        check(lib.so3lr_b200_system_stats(self._h, *[C.byref(x) for x in v]), "stats")
+        return dict(rebuilds=v[0].value, edges=v[1].value, pairs=v[2].value, launches=v[3].value)
+
+    def neighbor_list(self, positions, which, capacity):
+        """jax-md style (2, capacity) int32 index array padded with n, plus (count, overflow)."""
+        R = positions.to(self.device, torch.float32).contiguous()
+        idx = torch.empty(2, capacity, dtype=torch.int32, device=self.device)
+        cnt, ovf = C.c_int64(), C.c_int()
+        s = torch.cuda.current_stream(self.device)
+        check(lib.so3lr_b200_system_export_list(self._h, C.c_void_p(s.cuda_stream), _ptr(R), int(which), _ptr(idx), int(capacity),
+                                                C.byref(cnt), C.byref(ovf)), "export_list")
+        return idx, cnt.value, bool(ovf.value)
+
+    def graph_eval(self, idx_i, idx_j, edges, idx_i_lr, idx_j_lr, edges_lr, g_e_atom=None):
+        dev = self.device
+        t = lambda a, dt: a.to(dev, dt).contiguous()
+        idx_i, idx_j, idx_i_lr, idx_j_lr = (t(a, torch.int32) for a in (idx_i, idx_j, idx_i_lr, idx_j_lr))
+        edges, edges_lr = t(edges, torch.float32), t(edges_lr, torch.float32)
+        ge = None if g_e_atom is None else t(g_e_atom, torch.float32)
+        n = self.n
+        out = dict(e_atom=torch.empty(n, device=dev), g_edges=torch.zeros_like(edges), g_edges_lr=torch.zeros_like(edges_lr),
+                   partial_charges=torch.empty(n, device=dev), hirshfeld_ratios=torch.empty(n, device=dev))
+        s = torch.cuda.current_stream(dev)
+        check(lib.so3lr_b200_system_graph_eval(self._h, C.c_void_p(s.cuda_stream), edges.shape[0], _ptr(idx_i), _ptr(idx_j), _ptr(edges),
+                                               edges_lr.shape[0], _ptr(idx_i_lr), _ptr(idx_j_lr), _ptr(edges_lr), _ptr(ge),
+                                               _ptr(out["e_atom"]), _ptr(out["g_edges"]), _ptr(out["g_edges_lr"]),
+                                               _ptr(out["partial_charges"]), _ptr(out["hirshfeld_ratios"])), "graph_eval")
+        return out
+
+    def nve(self, n_steps, dt_fs, masses, positions, velocities, forces):
+        """In-place velocity-Verlet steps on device tensors; returns the per-graph energy of the last step."""
+        E = torch.empty(self.n_graphs, dtype=torch.float64, device=self.device)
+        s = torch.cuda.current_stream(self.device)
+        check(lib.so3lr_b200_system_nve(self._h, C.c_void_p(s.cuda_stream), int(n_steps), float(dt_fs), _ptr(masses), _ptr(positions),
+                                        _ptr(velocities), _ptr(forces), _ptr(E)), "nve")
+        return E
+
+
+def _from_ptr(ptr, n, device):
+    """float32 CUDA tensor viewing `n` floats at a raw device address."""
+    iface = {"shape": (n,), "typestr": "<f4", "data": (int(ptr), False), "version": 2}
+
+    class _W:
+        __cuda_array_interface__ = iface
+
+    return torch.as_tensor(_W(), device=device)
