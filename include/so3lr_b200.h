@@ -126,6 +126,14 @@ SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* sys, void* st
 SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* sys, void* stream, int n_steps, float dt_fs, const float* masses_dev,
                           float* positions_dev, float* velocities_dev, float* forces_dev, double* energy_dev);
 
+/* Optional timing of kernel groups with CUDA events recorded on the launching stream.  `profile(sys, 1)` starts a
+ * fresh recording; `profile_read` synchronises the device, returns the number of groups and fills, per group, the
+ * summed device time in ms, the number of timed launches and a static name.  No counterpart in the reference
+ * (it only measures wall-clock time per MD cycle, so3lr/cli/so3lr_md.py:1813-1839). */
+SO3LR_B200_API int so3lr_b200_system_profile(so3lr_b200_system* sys, int enable);
+SO3LR_B200_API int so3lr_b200_system_profile_read(so3lr_b200_system* sys, int max_groups, float* ms_total, int64_t* launches,
+                                                  const char** names);
+
 /* Host-callable pieces of the device math, exported for the CPU tests (no GPU needed). */
 SO3LR_B200_API void so3lr_b200_host_sph_harm(float x, float y, float z, float* y24);
 SO3LR_B200_API void so3lr_b200_host_sph_harm_vjp(float x, float y, float z, const float* g24, float* g3);

@@ -53,7 +53,20 @@ C6_FREE = (6.5, 1.46, 1387.0, 214.0, 99.5, 46.6, 24.2, 15.6, 9.52, 6.38, 1556.0,
 GAMMA_CUBIC = (-0.00433008, 0.24428889, 0.04125273, -0.00078893)   # b0..b3 of the QDO width fit
 
 _SEG = torch.tensor(sum([[i] * (2 * l + 1) for i, l in enumerate(DEGREES)], []))
-_INV_W = torch.tensor([1.0 / math.sqrt(2 * l + 1) for l in DEGREES], dtype=torch.float64)
+_DTYPE = [torch.float64]
+
+
+def set_dtype(dtype):
+    """Arithmetic type of the oracle: torch.float64 (parity checks) or torch.float32 (CPU timing baseline)."""
+    _DTYPE[0] = dtype
+
+
+def _dt():
+    return _DTYPE[0]
+
+
+def _inv_w():
+    return torch.tensor([1.0 / math.sqrt(2 * l + 1) for l in DEGREES], dtype=_dt())
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 DEFAULT_BLOB = os.path.join(_HERE, "..", "so3lr_b200", "params", "so3lr_v1.npz")
@@ -67,7 +80,7 @@ def load_params(path: str = DEFAULT_BLOB) -> Dict[str, torch.Tensor]:
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     blob = np.load(path)["blob"]
-    return {k: torch.tensor(v, dtype=torch.float64) for k, v in mod.unpack(blob).items()}
+    return {k: torch.tensor(v, dtype=_dt()) for k, v in mod.unpack(blob).items()}
 
 
 # ----------------------------------------------------------------------------------------------------------
@@ -130,8 +143,8 @@ def layer_norm(x, P, name):
 def bernstein_rbf(d):
     """32 exponential Bernstein polynomials b_k = C(31,k) x^k (1-x)^(31-k), x = exp(-gamma d)."""
     K = NUM_RBF
-    k = torch.arange(K, dtype=torch.float64)
-    logb = torch.tensor([math.lgamma(K) - math.lgamma(i + 1) - math.lgamma(K - i) for i in range(K)], dtype=torch.float64)
+    k = torch.arange(K, dtype=_dt())
+    logb = torch.tensor([math.lgamma(K) - math.lgamma(i + 1) - math.lgamma(K - i) for i in range(K)], dtype=_dt())
     ar = -RBF_GAMMA * d[:, None]
     return torch.exp(logb + k * ar + (K - 1 - k) * torch.log(-torch.expm1(ar)))
 
@@ -166,7 +179,7 @@ def real_sph_harm(u):
 def degree_invariants(ev):
     """Per-degree contraction to l=0: sum_m chi_lm^2 / sqrt(2l+1), (n, 24) -> (n, 4)."""
     out = torch.zeros(ev.shape[0], 4, dtype=ev.dtype)
-    return out.index_add(1, _SEG, ev * ev) * _INV_W
+    return out.index_add(1, _SEG, ev * ev) * _inv_w()
 
 
 def _smooth_sigma(x):
@@ -310,8 +323,8 @@ def energy_from_graph(P, Z, dR, idx_i, idx_j, dR_lr, idx_i_lr, idx_j_lr, *, lr_f
         batch_segments = torch.zeros(N, dtype=torch.int64)
     else:
         batch_segments = torch.as_tensor(np.asarray(batch_segments).astype(np.int64))
-    tq = torch.zeros(num_graphs, dtype=torch.float64) if total_charge is None else torch.as_tensor(total_charge, dtype=torch.float64).reshape(-1)
-    ts = torch.zeros(num_graphs, dtype=torch.float64) if num_unpaired is None else torch.as_tensor(num_unpaired, dtype=torch.float64).reshape(-1)
+    tq = torch.zeros(num_graphs, dtype=_dt()) if total_charge is None else torch.as_tensor(total_charge, dtype=_dt()).reshape(-1)
+    ts = torch.zeros(num_graphs, dtype=_dt()) if num_unpaired is None else torch.as_tensor(num_unpaired, dtype=_dt()).reshape(-1)
 
     # drop padding
     d_all = dR.norm(dim=-1)
@@ -327,7 +340,7 @@ def energy_from_graph(P, Z, dR, idx_i, idx_j, dR_lr, idx_i_lr, idx_j_lr, *, lr_f
     x = x + charge_spin_embed(P, "feature_embeddings_1", Z, tq, batch_segments, num_graphs)
     x = x + charge_spin_embed(P, "feature_embeddings_2", Z, ts, batch_segments, num_graphs)
     x = x / math.sqrt(3.0)
-    ev = torch.zeros(N, M_TOT, dtype=torch.float64)
+    ev = torch.zeros(N, M_TOT, dtype=_dt())
     if record is not None:
         record["x0"] = x
     for l in range(NUM_LAYERS):
@@ -339,17 +352,17 @@ def energy_from_graph(P, Z, dR, idx_i, idx_j, dR_lr, idx_i_lr, idx_j_lr, *, lr_f
 
     # ZBL repulsion on the short-range edges
     a, c, p, dd = zbl_energy(P, None, None, None, None, None)
-    zi, zj = Z[idx_i].double(), Z[idx_j].double()
+    zi, zj = Z[idx_i].to(_dt()), Z[idx_j].to(_dt())
     rzd = d * (zi ** p + zj ** p) * dd
     phi = sum(ck * torch.exp(-ak * rzd) for ak, ck in zip(a, c))
     e_zbl_edge = 0.5 * KE * cut * zi * zj / d * phi * switching_fn(d, 0.0, ZBL_SWITCH_OFF)
-    e_zbl = torch.zeros(N, dtype=torch.float64).index_add(0, idx_i, e_zbl_edge)
+    e_zbl = torch.zeros(N, dtype=_dt()).index_add(0, idx_i, e_zbl_edge)
 
     # partial charges with per-graph charge conservation
     pc = o + "electrostatic_energy/partial_charges/"
     qt = P[pc + "Embed_0/embedding"][Z][:, 0] + dense(silu(dense(x, P, pc + "charge_dense_regression_vec")), P, pc + "charge_dense_final_vec")[:, 0]
-    qsum = torch.zeros(num_graphs, dtype=torch.float64).index_add(0, batch_segments, qt)
-    cnt = torch.zeros(num_graphs, dtype=torch.float64).index_add(0, batch_segments, torch.ones(N, dtype=torch.float64))
+    qsum = torch.zeros(num_graphs, dtype=_dt()).index_add(0, batch_segments, qt)
+    cnt = torch.zeros(num_graphs, dtype=_dt()).index_add(0, batch_segments, torch.ones(N, dtype=_dt()))
     q = qt + ((tq - qsum) / cnt.clamp(min=1))[batch_segments]
 
     # Hirshfeld ratios
@@ -366,8 +379,8 @@ def energy_from_graph(P, Z, dR, idx_i, idx_j, dR_lr, idx_i_lr, idx_j_lr, *, lr_f
     e_d_pair = fac * dispersion_pair(dl, Z[il], Z[jl], hr[il], hr[jl], cutoff_lr, damping)
     if cutoff_lr is not None:
         e_d_pair = torch.where(dl < cutoff_lr, e_d_pair, torch.zeros_like(e_d_pair))
-    e_c = torch.zeros(N, dtype=torch.float64).index_add(0, il, e_c_pair)
-    e_d = torch.zeros(N, dtype=torch.float64).index_add(0, il, e_d_pair)
+    e_c = torch.zeros(N, dtype=_dt()).index_add(0, il, e_c_pair)
+    e_d = torch.zeros(N, dtype=_dt()).index_add(0, il, e_d_pair)
 
     e_atom = e_nn + e_zbl + e_c + e_d
     aux = dict(partial_charges=q, hirshfeld_ratios=hr, zbl_repulsion=e_zbl, electrostatic_energy=e_c,
@@ -398,14 +411,14 @@ def energy_forces(P, R, Z, cell=None, *, cutoff_lr: Optional[float] = 12.0, damp
             m = bs[idx_i_lr] == bs[idx_j_lr]; idx_i_lr, idx_j_lr = idx_i_lr[m], idx_j_lr[m]
     else:
         idx_i, idx_j, idx_i_lr, idx_j_lr = lists
-    Rt = torch.tensor(R, requires_grad=True)
+    Rt = torch.tensor(R, dtype=_dt(), requires_grad=True)
     ii, jj = torch.as_tensor(idx_i.astype(np.int64)), torch.as_tensor(idx_j.astype(np.int64))
     il, jl = torch.as_tensor(idx_i_lr.astype(np.int64)), torch.as_tensor(idx_j_lr.astype(np.int64))
 
     def disp(a, b):
         dR = Rt[b] - Rt[a]
         if cell is not None:
-            c = torch.tensor(np.asarray(cell, dtype=np.float64))
+            c = torch.tensor(np.asarray(cell, dtype=np.float64), dtype=_dt())
             s = dR.detach() @ torch.linalg.inv(c)
             dR = dR - torch.round(s) @ c
         return dR
@@ -418,8 +431,8 @@ def energy_forces(P, R, Z, cell=None, *, cutoff_lr: Optional[float] = 12.0, damp
     F = -torch.autograd.grad(E, Rt)[0]
     bs = aux["batch_segments"]
     q = aux["partial_charges"].detach()
-    dip = torch.zeros(num_graphs, 3, dtype=torch.float64).index_add(0, bs, q[:, None] * Rt.detach())
-    e_graph = torch.zeros(num_graphs, dtype=torch.float64).index_add(0, bs, e_atom.detach())
+    dip = torch.zeros(num_graphs, 3, dtype=_dt()).index_add(0, bs, q[:, None] * Rt.detach())
+    e_graph = torch.zeros(num_graphs, dtype=_dt()).index_add(0, bs, e_atom.detach())
     out = dict(energy=E.item(), energy_per_graph=e_graph.numpy(), forces=F.numpy(), e_atom=e_atom.detach().numpy(),
                partial_charges=q.numpy(), hirshfeld_ratios=aux["hirshfeld_ratios"].detach().numpy(),
                dipole_vec=dip.numpy(), zbl_repulsion=aux["zbl_repulsion"].detach().numpy(),

@@ -106,8 +106,41 @@ int make_cell(const float* cell9, Cell* c) {
 
 }  // namespace
 
+// Optional per-kernel-group timing with CUDA events on the launching stream.
+enum ProfGroup { kPNlist = 0, kPGeom, kPProj, kPAttnFwd, kPPostFwd, kPHeads, kPPairLr, kPPostBwd, kPAttnBwd, kPProjBwd, kPScatter,
+                 kPMisc, kPGroups };
+static const char* kProfNames[kPGroups] = {"nlist", "sr_geometry_zbl", "proj_fwd", "attn_fwd", "atom_post_fwd", "heads", "pair_lr",
+                                           "atom_post_bwd", "attn_bwd", "proj_bwd", "force_scatter", "misc"};
+struct Profiler {
+  bool on = false;
+  std::vector<cudaEvent_t> a, b;
+  std::vector<int> grp;
+  size_t used = 0;
+  void begin(int g, cudaStream_t st) {
+    if (!on) return;
+    if (used == a.size()) {
+      cudaEvent_t e0, e1;
+      cudaEventCreate(&e0); cudaEventCreate(&e1);
+      a.push_back(e0); b.push_back(e1); grp.push_back(g);
+    }
+    grp[used] = g;
+    cudaEventRecord(a[used], st);
+  }
+  void end(cudaStream_t st) {
+    if (!on) return;
+    cudaEventRecord(b[used], st);
+    ++used;
+  }
+  void destroy() {
+    for (auto e : a) cudaEventDestroy(e);
+    for (auto e : b) cudaEventDestroy(e);
+    a.clear(); b.clear(); grp.clear(); used = 0;
+  }
+};
+
 struct so3lr_b200_system {
   so3lr_b200_model* model = nullptr;
+  Profiler prof;
   int n = 0, n_graphs = 1;
   so3lr_b200_options opt{};
   Cell cell{};
@@ -207,47 +240,49 @@ int evaluate(so3lr_b200_system* S, cudaStream_t st, const float* R, const int* r
   fill(st, S->e_zbl, n, 0.f); fill(st, S->e_coul, n, 0.f); fill(st, S->e_disp, n, 0.f);
   fill(st, S->gq, n, 0.f); fill(st, S->gh, n, 0.f);
   if (F) fill(st, F, (size_t)n * 3, 0.f);
-  launch_sr_geometry_zbl(st, M, S->cell, n, n_edges, edge_i, nbr_j, S->d_Z, R, graph_mode, dR, S->e_zbl, g_dR, ge);
+  S->prof.begin(kPGeom, st); launch_sr_geometry_zbl(st, M, S->cell, n, n_edges, edge_i, nbr_j, S->d_Z, R, graph_mode, dR, S->e_zbl, g_dR, ge); S->prof.end(st);
   launch_embed(st, M, S->d_Z, n, S->x[0]);
   S->n_launches += 8;
   for (int l = 0; l < kNumLayers; ++l) {
     const LayerDev& L = M.layer[l];
-    launch_proj_fwd(st, L, S->x[l], n, S->qkv[l]);
-    launch_attn_fwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
-    launch_atom_post_fwd(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]);
+    S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], n, S->qkv[l]); S->prof.end(st);
+    S->prof.begin(kPAttnFwd, st); launch_attn_fwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]); S->prof.end(st);
+    S->prof.begin(kPPostFwd, st); launch_atom_post_fwd(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]); S->prof.end(st);
     S->n_launches += 3;
   }
-  launch_heads_fwd(st, M, n, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv);
+  S->prof.begin(kPHeads, st); launch_heads_fwd(st, M, n, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv); S->prof.end(st);
   launch_charge_conserve(st, S->n_graphs, S->d_graph_start, S->q_raw, S->d_total_charge, S->hv, S->q, S->h);
+  S->prof.begin(kPPairLr, st);
   launch_pair_lr(st, S->lr, S->cell, n, row_ptr_lr, nbr_j_lr, S->d_Z, R, S->q, S->h, graph_mode ? 1 : 0, dR_lr_in, g_dR_lr_out,
                  nullptr, F, S->gq, S->gh, S->e_coul, S->e_disp, ge);
+  S->prof.end(st);
   combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom);
   // backward
   launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw);
-  launch_heads_bwd(st, M, n, S->d_Z, S->ze, S->zq, S->zh, S->hv, ge ? ge : S->ones, S->gq_raw, S->gh, S->g4);
+  S->prof.begin(kPHeads, st); launch_heads_bwd(st, M, n, S->d_Z, S->ze, S->zq, S->zh, S->hv, ge ? ge : S->ones, S->gq_raw, S->gh, S->g4); S->prof.end(st);
   S->n_launches += 6;
   float* gev2 = S->gev_a;
   float* gev_in = S->gev_b;
   fill(st, gev2, (size_t)n * kMTot, 0.f);
   for (int l = kNumLayers - 1; l >= 0; --l) {
     const LayerDev& L = M.layer[l];
-    launch_atom_post_bwd(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, gev2, S->g_xa, S->gev1);
+    S->prof.begin(kPPostBwd, st); launch_atom_post_bwd(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, gev2, S->g_xa, S->gev1); S->prof.end(st);
     if (l > 0) {
       SO3LR_CUDA_CHECK(cudaMemcpyAsync(gev_in, S->gev1, (size_t)n * kMTot * sizeof(float), cudaMemcpyDeviceToDevice, st));
       fill(st, S->g_qkv, (size_t)n * kProj, 0.f);
-      launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, g_dR, 0);
+      S->prof.begin(kPAttnBwd, st); launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, g_dR, 0); S->prof.end(st);
       // dL/dx_in = g_xa (skip connection) + projections^T
       SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)n * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
-      launch_proj_bwd(st, L, S->g_qkv, n, S->g4, 1);
+      S->prof.begin(kPProjBwd, st); launch_proj_bwd(st, L, S->g_qkv, n, S->g4, 1); S->prof.end(st);
       float* t = gev2; gev2 = gev_in; gev_in = t;
       S->n_launches += 6;
     } else {
-      launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, nullptr, nullptr, g_dR, 1);
+      S->prof.begin(kPAttnBwd, st); launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, nullptr, nullptr, g_dR, 1); S->prof.end(st);
       S->n_launches += 2;
     }
   }
   if (!graph_mode && F) {
-    launch_force_scatter(st, n, n_edges, edge_i, nbr_j, g_dR, F);
+    S->prof.begin(kPScatter, st); launch_force_scatter(st, n, n_edges, edge_i, nbr_j, g_dR, F); S->prof.end(st);
     S->n_launches += 1;
   }
   SO3LR_CUDA_CHECK(cudaGetLastError());
@@ -394,6 +429,7 @@ SO3LR_B200_API int so3lr_b200_system_destroy(so3lr_b200_system* S) {
   cudaSetDevice(S->model->device);
   cudaDeviceSynchronize();
   S->pool.release();
+  S->prof.destroy();
   nlist_workspace_destroy(S->nws);
   for (NeighborListDev* L : {&S->sr, &S->lrl}) { cudaFree(L->row_ptr); cudaFree(L->nbr_j); cudaFree(L->edge_i); }
   cudaFree(S->dR); cudaFree(S->g_dR);
@@ -432,7 +468,12 @@ static int prepare_lists(so3lr_b200_system* S, cudaStream_t st, const float* R) 
       rebuild = *S->h_flag != 0;
     }
   }
-  if (rebuild) return rebuild_lists(S, st, R);
+  if (rebuild) {
+    S->prof.begin(kPNlist, st);
+    int rc = rebuild_lists(S, st, R);
+    S->prof.end(st);
+    return rc;
+  }
   return kOk;
 }
 
@@ -553,7 +594,31 @@ SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* S, void* stream, int
   return kOk;
 }
 
-SO3LR_B200_API void so3lr_b200_host_sph_harm(float x, float y, float z, float* y24) { sph_harm_24(x, y, z, y24); }
+SO3LR_B200_API int so3lr_b200_system_profile(so3lr_b200_system* S, int enable) {
+  if (!S) return kInvalidArgument;
+  S->prof.on = enable != 0;
+  S->prof.used = 0;
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_profile_read(so3lr_b200_system* S, int max_groups, float* ms_total, int64_t* launches, const char** names) {
+  if (!S || !ms_total || !launches) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  SO3LR_CUDA_CHECK(cudaDeviceSynchronize());
+  int ng = max_groups < (int)kPGroups ? max_groups : (int)kPGroups;
+  for (int g = 0; g < ng; ++g) { ms_total[g] = 0.f; launches[g] = 0; if (names) names[g] = kProfNames[g]; }
+  for (size_t k = 0; k < S->prof.used; ++k) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, S->prof.a[k], S->prof.b[k]) == cudaSuccess && S->prof.grp[k] < ng) {
+      ms_total[S->prof.grp[k]] += ms;
+      launches[S->prof.grp[k]] += 1;
+    }
+  }
+  S->prof.used = 0;
+  return ng;
+}
+
+void so3lr_b200_host_sph_harm(float x, float y, float z, float* y24) { sph_harm_24(x, y, z, y24); }
 SO3LR_B200_API void so3lr_b200_host_sph_harm_vjp(float x, float y, float z, const float* g24, float* g3) {
   sph_harm_24_vjp(x, y, z, g24, g3[0], g3[1], g3[2]);
 }

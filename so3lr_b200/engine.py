@@ -127,6 +127,15 @@ class System:
         check(lib.so3lr_b200_system_stats(self._h, *[C.byref(x) for x in v]), "stats")
         return dict(rebuilds=v[0].value, edges=v[1].value, pairs=v[2].value, launches=v[3].value)
 
+    def profile(self, enable=True):
+        check(lib.so3lr_b200_system_profile(self._h, 1 if enable else 0), "profile")
+
+    def profile_read(self):
+        """{group: (total_ms, launches)} since profile(True); synchronises the device."""
+        ms = (C.c_float * 16)(); cnt = (C.c_int64 * 16)(); names = (C.c_char_p * 16)()
+        ng = lib.so3lr_b200_system_profile_read(self._h, 16, ms, cnt, names)
+        return {names[g].decode(): (float(ms[g]), int(cnt[g])) for g in range(ng)}
+
     def neighbor_list(self, positions, which, capacity):
         """jax-md style (2, capacity) int32 index array padded with n, plus (count, overflow)."""
         R = positions.to(self.device, torch.float32).contiguous()
