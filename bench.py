@@ -1,0 +1,277 @@
+"""Benchmark of the SO3LR energy+force hot path: atom-steps/s on a periodic water box.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload water_1m|water_24k|...]
+
+One "step" is one molecular-dynamics step of the whole box: velocity-Verlet update, skin test (neighbor lists are
+rebuilt when an atom moved more than skin/2), and one energy+force evaluation.  Positions, velocities and forces
+stay in HBM for the device-timed `value`; `e2e` is the same metric through the host-buffer call
+(so3lr_b200_system_compute_host via System.compute_host): positions come from host memory every step and forces
+and energy go back to the host inside the timed region.
+
+Prints ONE JSON line (rank 0).  `--impl reference` times the CPU implementation of the same path (the float32
+torch restatement under oracle/, all host threads) on a bounded sample of the workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "atom-steps/s (E+F)"
+UNIT = "atom-steps/s"
+WATER_DENSITY = 333333 / 215.0 ** 3          # molecules per cubic Angstrom of the 1M-atom configuration
+
+WORKLOADS = {
+    # name: (molecules, box edge, seed)   -- seeds follow numpy.random.default_rng(1000 + config index)
+    "water_192": (64, 12.42, 1000),
+    "water_24k": (8000, 62.1, 1002),
+    "water_98k": (32768, 99.2, 1003),           # profiling-sized case: working set above the L2, a few GB on the device
+    "water_1m": (333333, 215.0, 1004),
+}
+
+
+def _peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except Exception:
+                continue
+            for k, nm in enumerate(names):
+                if len(r) > 3 + k and r[3 + k].lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# algorithmic (unique-data) bytes per launch of each kernel group: every array the kernel must read or write is
+# counted once.  N atoms, E directed short-range list entries (skin included), P long-range list entries.
+# ---------------------------------------------------------------------------------------------------------------
+def algorithmic_bytes(group, N, E, P):
+    f = 4
+    if group == "attn_fwd":      # q1,q2 (256) + ev_i (24) + sender rows k1,v,k2 (384) + ev_j (24) + x_in (128); out xa, ev1 (152)
+        return N * f * (256 + 24 + 384 + 24 + 128 + 152) + E * (4 + 12) + (N + 1) * 4
+    if group == "attn_bwd":      # q1,q2, g_xa, gev1, ev (i and j once), sender rows; out g_qkv (640), gev_in (24); per edge idx, dR, g_dR rmw
+        return N * f * (256 + 128 + 24 + 24 + 384 + 640 + 24) + E * (4 + 12 + 24) + (N + 1) * 4
+    if group == "pair_lr":       # per pair: index; per atom: R, q, h, Z in; F, gq, gh, e_coul, e_disp out
+        return P * 4 + N * (12 + 4 + 4 + 4 + 12 + 4 + 4 + 4 + 4) + (N + 1) * 4
+    if group == "atom_post_fwd":
+        return N * f * (128 + 24 + 128 + 128 + 4 + 128 + 24)
+    if group == "atom_post_bwd":
+        return N * f * (128 + 24 + 128 + 128 + 4 + 128 + 24 + 128 + 24)
+    return None
+
+
+def run_b200(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from so3lr_b200 import workloads as W
+    from so3lr_b200.engine import System
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    n_mol, box, seed = WORKLOADS[args.workload]
+    if world > 1:
+        from so3lr_b200 import domain
+        return domain.bench_entry(args, rank, world, local_rank, n_mol, box, seed)
+
+    Z, R, cell = W.water_box(n_mol, box, seed)
+    V, m = W.maxwell_boltzmann(Z, 300.0, seed + 1)
+    N = len(Z)
+    skin = args.skin
+    sysm = System(Z, cell, cutoff_lr=12.0, damping=2.0, skin=skin, device=local_rank)
+    Rd = torch.tensor(R, dtype=torch.float32, device=dev)
+    Vd = torch.tensor(V, dtype=torch.float32, device=dev)
+    md = torch.tensor(m, dtype=torch.float32, device=dev)
+    out = sysm.compute(Rd)
+    Fd = out["forces"].clone()
+    torch.cuda.synchronize()
+    dt = 0.5
+
+    for _ in range(args.warmup):
+        sysm.nve(1, dt, md, Rd, Vd, Fd)
+    torch.cuda.synchronize()
+    st0 = sysm.stats()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    torch.cuda.synchronize()
+    ev[0].record()
+    for _ in range(args.steps):
+        sysm.nve(1, dt, md, Rd, Vd, Fd)
+    ev[1].record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = ev[0].elapsed_time(ev[1])
+    st1 = sysm.stats()
+    launches = st1["launches"] - st0["launches"]
+    value = N * args.steps / (ms * 1e-3)
+
+    # per-kernel device times over another K steps of the same trajectory (CUDA events on the launching stream)
+    sysm.profile(True)
+    for _ in range(args.steps):
+        sysm.nve(1, dt, md, Rd, Vd, Fd)
+    prof = sysm.profile_read()
+    sysm.profile(False)
+    st2 = sysm.stats()
+    E_list, P_list = st2["edges"], st2["pairs"]
+    groups = {k: v for k, v in prof.items() if v[1] > 0}
+    top = max((g for g in groups if algorithmic_bytes(g, N, E_list, P_list)), key=lambda g: groups[g][0])
+    t_launch = groups[top][0] / groups[top][1]
+    ab = algorithmic_bytes(top, N, E_list, P_list)
+    peak, peak_kind = _peaks()
+    achieved = ab / (t_launch * 1e-3) / 1e9
+    roofline = {"kernel": top, "bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "peak_kind": f"of {peak_kind}",
+                "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": args.traffic,
+                "algorithmic_bytes_per_launch": ab, "ms_per_launch": round(t_launch, 4),
+                "groups_ms_per_step": {g: round(v[0] / args.steps, 4) for g, v in sorted(groups.items(), key=lambda kv: -kv[1][0])}}
+
+    # end to end through the host-buffer call: positions from host memory, forces + energy back, every step
+    Rh = Rd.cpu().numpy().copy()
+    Vh = Vd.cpu().numpy().copy()
+    Fh = Fd.cpu().numpy().copy()
+    acc = (0.5 * dt * 9.648533212331e-3 / m).astype(np.float32)[:, None]
+    for _ in range(2):
+        o = sysm.compute_host(Rh, want_aux=False)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        Vh += acc * Fh
+        Rh += dt * Vh
+        o = sysm.compute_host(Rh, want_aux=False)
+        Fh = o["forces"]
+        Vh += acc * Fh
+    torch.cuda.synchronize()
+    t_e2e = time.perf_counter() - t0
+    e2e = {"value": round(N * args.steps / t_e2e, 1), "unit": UNIT, "h2d_bytes_per_step": N * 12, "d2h_bytes_per_step": N * 12 + 8,
+           "ms_per_step": round(1e3 * t_e2e / args.steps, 3)}
+
+    cpu = cpu_baseline(args, sample_molecules=args.cpu_molecules, evals=1) if not args.no_cpu else None
+    line = {"metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {N} atoms periodic water, cutoffs 4.5/12 A, skin {skin} A, NVE dt 0.5 fs from 300 K",
+                       "atoms": N, "sr_list_edges": E_list, "lr_list_pairs": P_list,
+                       "list_rebuilds_in_timed_steps": st1["rebuilds"] - st0["rebuilds"],
+                       "l2_policy": "inputs larger than L2 (activations > 1 GB per step)" if N > 200000 else "inputs smaller than L2; no flush",
+                       "ns_per_day": round(args.steps / (ms * 1e-3) * 0.0432, 3)},
+            "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu}
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline(args, sample_molecules, evals):
+    """Times the CPU restatement (float32, all host threads) on a periodic water box of `sample_molecules` molecules at
+    the workload's density; the per-atom cost of this path is size-independent beyond the cutoffs."""
+    import torch
+    from oracle import so3lr_oracle as O
+    from so3lr_b200 import workloads as W
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    O.set_dtype(torch.float32)
+    P = O.load_params()
+    box = (sample_molecules / WATER_DENSITY) ** (1.0 / 3.0)
+    Z, R, cell = W.water_box(sample_molecules, box, 1004)
+    N = len(Z)
+    # neighbor lists are built once outside the timed region, as they are amortised over many steps on the GPU side too
+    t0 = time.perf_counter()
+    ii, jj = O.neighbor_list(R, cell, 4.5, ordered=False)
+    il, jl = O.neighbor_list(R, cell, 12.0, ordered=True)
+    t_list = time.perf_counter() - t0
+    times = []
+    for _ in range(evals):
+        t0 = time.perf_counter()
+        O.energy_forces(P, R, Z, cell, cutoff_lr=12.0, damping=2.0, lists=(ii, jj, il, jl))
+        times.append(time.perf_counter() - t0)
+    O.set_dtype(torch.float64)
+    t = float(np.median(times))
+    return {"value": round(N / t, 1), "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{N}-atom periodic water box at the workload's density, {evals} energy+force evaluation(s) of the float32 "
+                      f"CPU restatement, {t:.2f} s each (lists prebuilt in {t_list:.1f} s, not timed)"}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    n = args.cpu_molecules
+    t_all = time.perf_counter()
+    cpu = cpu_baseline(args, n, evals=max(1, args.steps))
+    n_mol, box, _ = WORKLOADS[args.workload]
+    line = {"impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(1e3 * 3 * n / cpu["value"], 3), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: bounded sample of {3 * n} atoms of the periodic water box per step"},
+            "cpu_baseline": cpu, "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0, "wall_s": round(time.perf_counter() - t_all, 1)}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="water_1m", choices=sorted(WORKLOADS))
+    ap.add_argument("--skin", type=float, default=1.0)
+    ap.add_argument("--cpu-molecules", type=int, default=1024, help="molecules in the CPU-baseline sample")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the roofline kernel (from profiles/)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    rank = int(os.environ.get("RANK", 0)); world = int(os.environ.get("WORLD_SIZE", 1)); local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_b200(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()
