@@ -134,6 +134,26 @@ SO3LR_B200_API int so3lr_b200_system_profile(so3lr_b200_system* sys, int enable)
 SO3LR_B200_API int so3lr_b200_system_profile_read(so3lr_b200_system* sys, int max_groups, float* ms_total, int64_t* launches,
                                                   const char** names);
 
+/* Pair list without any device allocation.  No counterpart in the reference: it exists for callers that cannot call
+ * cudaMalloc at all, such as an XLA custom-call handler (XLA's allocator already holds most of the GPU's memory, so an
+ * allocation made inside the handler may fail and, if it succeeds, stalls the whole device) or a host program that
+ * serves all GPU memory from its own fixed arena.  The only memory used besides the arguments is a 128 KiB scratch
+ * array that is part of the library image on every GPU that loads it; that fixes the limit of
+ * SO3LR_B200_NOALLOC_MAX_ATOMS atoms (larger systems return SO3LR_B200_TOO_LARGE; use
+ * so3lr_b200_system_export_list for them).
+ *   positions_dev: n_atoms x 3 float32 on the CURRENT device (cudaGetDevice); cell: HOST pointer to 9 floats (rows =
+ *   lattice vectors, each perpendicular width >= 2 * r_cutoff) or NULL for free space; ordered = 1 keeps i < j only.
+ *   idx_dev: (2, capacity) int32, pairs grouped by centre with ascending neighbour index, unused slots = n_atoms;
+ *   count_dev / overflow_dev: DEVICE words that receive the number of pairs found and whether it exceeds capacity.
+ * Work is only enqueued on `stream`; nothing is read back.  The first call on a device looks up the device address of
+ * the scratch array (cudaGetSymbolAddress); make that first call before any stream capture begins.  The scratch is
+ * shared by all calls on a device: calls whose kernels could overlap on the GPU (different streams or threads) race
+ * and must be serialised by the caller.  It needs no clearing between calls. */
+#define SO3LR_B200_NOALLOC_MAX_ATOMS 16384
+SO3LR_B200_API int so3lr_b200_neighbor_list_noalloc(void* stream, int n_atoms, const float* positions_dev, const float* cell,
+                                                    float r_cutoff, int ordered, int32_t* idx_dev, int64_t capacity,
+                                                    int64_t* count_dev, int* overflow_dev);
+
 /* Host-callable pieces of the device math, exported for the CPU tests (no GPU needed). */
 SO3LR_B200_API void so3lr_b200_host_sph_harm(float x, float y, float z, float* y24);
 SO3LR_B200_API void so3lr_b200_host_sph_harm_vjp(float x, float y, float z, const float* g24, float* g3);

@@ -27,7 +27,7 @@ class Options(C.Structure):
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} not found. Build it with `python -m so3lr_b200.build` (needs nvcc); "
+            f"{LIB_PATH} not found. Build it with `python so3lr_b200/build.py` (needs nvcc); "
             "so3lr_b200 has no CPU fallback.")
     lib = C.CDLL(LIB_PATH)
     p, i32, i64, f32 = C.c_void_p, C.c_int, C.c_int64, C.c_float
@@ -48,6 +48,7 @@ def _load():
         "so3lr_b200_system_nve": (i32, [p, p, i32, f32, p, p, p, p, p]),
         "so3lr_b200_system_profile": (i32, [p, i32]),
         "so3lr_b200_system_profile_read": (i32, [p, i32, p, p, p]),
+        "so3lr_b200_neighbor_list_noalloc": (i32, [p, i32, p, p, f32, i32, p, i64, p, p]),
         "so3lr_b200_host_sph_harm": (None, [f32, f32, f32, p]),
         "so3lr_b200_host_sph_harm_vjp": (None, [f32, f32, f32, p, p]),
         "so3lr_b200_host_pair_terms": (None, [f32, i32, i32, f32, f32, f32, f32, f32, f32, p]),

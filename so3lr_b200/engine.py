@@ -179,3 +179,23 @@ def _from_ptr(ptr, n, device):
         __cuda_array_interface__ = iface
 
     return torch.as_tensor(_W(), device=device)
+
+
+NOALLOC_MAX_ATOMS = 16384
+
+
+def neighbor_list_noalloc(positions, cell, r_cutoff, ordered, idx, count, overflow, stream=None):
+    """Pair list through so3lr_b200_neighbor_list_noalloc, the entry point for callers that cannot allocate GPU memory
+    (for instance a handler running inside XLA, whose allocator already owns the device's memory).  Every buffer is the
+    caller's: positions (n,3) float32 CUDA, idx (2,capacity) int32 CUDA, count (1,) int64 CUDA, overflow (1,) int32
+    CUDA; cell is None or a host (3,3) array with lattice vectors as rows.  At most NOALLOC_MAX_ATOMS atoms.  The
+    call only enqueues work; calls on one device must not overlap because they share one fixed scratch array."""
+    assert positions.is_cuda and positions.dtype == torch.float32 and positions.is_contiguous()
+    assert idx.is_cuda and idx.dtype == torch.int32 and idx.is_contiguous() and idx.shape[0] == 2
+    assert count.is_cuda and count.dtype == torch.int64 and overflow.is_cuda and overflow.dtype == torch.int32
+    c9 = None if cell is None else np.ascontiguousarray(np.asarray(cell, dtype=np.float32).reshape(9))
+    with torch.cuda.device(positions.device):
+        s = stream if stream is not None else torch.cuda.current_stream(positions.device)
+        check(lib.so3lr_b200_neighbor_list_noalloc(C.c_void_p(s.cuda_stream), int(positions.shape[0]), _ptr(positions), _ptr(c9),
+                                                   float(r_cutoff), 1 if ordered else 0, _ptr(idx), int(idx.shape[1]), _ptr(count),
+                                                   _ptr(overflow)), "neighbor_list_noalloc")

@@ -8,7 +8,7 @@ import torch
 
 from oracle import so3lr_oracle as O
 
-_lib = pytest.importorskip("so3lr_b200._lib")
+from so3lr_b200 import _lib
 lib = _lib.lib
 
 
