@@ -70,6 +70,30 @@ __global__ void export_list_kernel(int n, long long count, long long capacity, c
   idx[e] = e < count ? edge_i[e] : n;
   idx[capacity + e] = e < count ? nbr_j[e] : n;
 }
+// atoms are evaluated in a spatially sorted order: slot k holds atom perm[k]
+__global__ void gather_positions_kernel(int n, const int* __restrict__ perm, const float* __restrict__ R, float* __restrict__ Rs) {
+  int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= n) return;
+  const size_t a = (size_t)perm[k];
+  Rs[3 * (size_t)k] = R[3 * a]; Rs[3 * (size_t)k + 1] = R[3 * a + 1]; Rs[3 * (size_t)k + 2] = R[3 * a + 2];
+}
+__global__ void gather_int_kernel(int n, const int* __restrict__ perm, const int* __restrict__ src, int* __restrict__ dst) {
+  int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k < n) dst[k] = src[perm[k]];
+}
+struct UnsortArgs {
+  const float* src[7];
+  float* dst[7];
+};
+__global__ void unsort_kernel(int n, const int* __restrict__ perm, const float* __restrict__ Fs, float* __restrict__ F, UnsortArgs A) {
+  int k = blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= n) return;
+  const size_t a = (size_t)perm[k];
+  F[3 * a] = Fs[3 * (size_t)k]; F[3 * a + 1] = Fs[3 * (size_t)k + 1]; F[3 * a + 2] = Fs[3 * (size_t)k + 2];
+#pragma unroll
+  for (int q = 0; q < 7; ++q)
+    if (A.dst[q]) A.dst[q][a] = A.src[q][k];
+}
 // velocity Verlet halves.  units: eV, Angstrom, amu, fs -> acceleration = F/m * 9.64853321e-3 A/fs^2
 constexpr float kAccel = 9.648533212331e-3f;
 __global__ void vv_first_kernel(int n, float dt, const float* m, float* R, float* V, const float* F) {
@@ -146,8 +170,15 @@ struct so3lr_b200_system {
   Cell cell{};
   LrParams lr{};
   Pool pool;
-  // static inputs
-  int *d_Z = nullptr, *d_seg = nullptr, *d_graph_start = nullptr;
+  // static inputs.  d_Z is the array the kernels read: d_Z0 (caller order) or d_Zs (sorted order)
+  int *d_Z = nullptr, *d_Z0 = nullptr, *d_Zs = nullptr, *d_seg = nullptr, *d_graph_start = nullptr;
+  // spatial ordering (periodic single-graph systems): slot k of every internal per-atom array holds atom d_perm[k]
+  int* d_perm = nullptr;
+  float *d_Rs = nullptr, *F_s = nullptr;
+  bool sorted = false;
+  // per-atom results in caller order (alias the internal arrays when not sorted)
+  float *o_e_atom = nullptr, *o_q = nullptr, *o_h = nullptr, *o_zbl = nullptr, *o_coul = nullptr, *o_disp = nullptr;
+  float *u_e_atom = nullptr, *u_q = nullptr, *u_h = nullptr, *u_zbl = nullptr, *u_coul = nullptr, *u_disp = nullptr;
   float* d_total_charge = nullptr;
   // lists
   NeighborListDev sr, lrl;
@@ -167,7 +198,7 @@ struct so3lr_b200_system {
   float *e_atom = nullptr, *e_zbl = nullptr, *e_coul = nullptr, *e_disp = nullptr;
   float *gq = nullptr, *gh = nullptr, *gq_raw = nullptr, *ones = nullptr;
   float *g4 = nullptr, *g_xa = nullptr, *gev_a = nullptr, *gev_b = nullptr, *gev1 = nullptr, *g_qkv = nullptr;
-  float *dR = nullptr, *g_dR = nullptr;
+  float* dR = nullptr;
   long long edge_cap = 0;
   float* F_int = nullptr;
   double* d_energy = nullptr;
@@ -192,16 +223,31 @@ int ensure_edge_buffers(so3lr_b200_system* S, long long n_edges) {
   if (n_edges <= S->edge_cap) return kOk;
   long long cap = n_edges + n_edges / 4 + 1024;
   if (S->dR) cudaFree(S->dR);
-  if (S->g_dR) cudaFree(S->g_dR);
-  S->dR = S->g_dR = nullptr;
+  S->dR = nullptr;
   SO3LR_CUDA_CHECK(cudaMalloc((void**)&S->dR, (size_t)cap * 3 * sizeof(float)));
-  SO3LR_CUDA_CHECK(cudaMalloc((void**)&S->g_dR, (size_t)cap * 3 * sizeof(float)));
   S->edge_cap = cap;
   return kOk;
 }
 
-int rebuild_lists(so3lr_b200_system* S, cudaStream_t st, const float* R) {
+constexpr int kSortMinAtoms = 512;
+
+int rebuild_lists(so3lr_b200_system* S, cudaStream_t st, const float* R_user, bool allow_sort) {
   const float r_sr = kCutoffSr + S->opt.skin;
+  const float* R = R_user;
+  const int nb = (S->n + 255) / 256;
+  S->sorted = allow_sort && S->cell.periodic && S->n_graphs == 1 && S->n >= kSortMinAtoms;
+  if (S->sorted) {
+    int rc0 = spatial_order(S->nws, st, S->cell, S->n, R_user, r_sr, S->d_perm);
+    if (rc0) return rc0;
+    gather_positions_kernel<<<nb, 256, 0, st>>>(S->n, S->d_perm, R_user, S->d_Rs);
+    gather_int_kernel<<<nb, 256, 0, st>>>(S->n, S->d_perm, S->d_Z0, S->d_Zs);
+    R = S->d_Rs;
+    S->d_Z = S->d_Zs;
+    S->o_e_atom = S->u_e_atom; S->o_q = S->u_q; S->o_h = S->u_h; S->o_zbl = S->u_zbl; S->o_coul = S->u_coul; S->o_disp = S->u_disp;
+  } else {
+    S->d_Z = S->d_Z0;
+    S->o_e_atom = S->e_atom; S->o_q = S->q; S->o_h = S->h; S->o_zbl = S->e_zbl; S->o_coul = S->e_coul; S->o_disp = S->e_disp;
+  }
   const bool many = S->n_graphs > 1 || !S->cell.periodic;
   const int* seg = S->n_graphs > 1 ? S->d_seg : nullptr;
   const int* gs = (S->n_graphs > 1 && !S->cell.periodic) ? S->d_graph_start : nullptr;
@@ -220,7 +266,7 @@ int rebuild_lists(so3lr_b200_system* S, cudaStream_t st, const float* R) {
   rc = nlist_build(S->nws, st, S->cell, S->n, R, r_lr, S->opt.lr_both_directions ? 0 : 1, seg ? seg : (gs_lr ? S->d_seg : nullptr),
                    gs_lr, &S->lrl, 1, nullptr);
   if (rc) return rc;
-  SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->d_Rref, R, (size_t)S->n * 3 * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->d_Rref, R_user, (size_t)S->n * 3 * sizeof(float), cudaMemcpyDeviceToDevice, st));
   rc = ensure_edge_buffers(S, S->sr.count);
   if (rc) return rc;
   S->have_lists = true;
@@ -236,17 +282,21 @@ int evaluate(so3lr_b200_system* S, cudaStream_t st, const float* R, const int* r
   const ModelDev& M = S->model->M;
   const int n = S->n;
   float* dR = graph_mode ? const_cast<float*>(dR_in) : S->dR;
-  float* g_dR = graph_mode ? g_dR_out : S->g_dR;
+  float* g_dR = graph_mode ? g_dR_out : nullptr;
+  const bool fused = !graph_mode;   // positions -> forces: gather-only attention kernels on the symmetric list
   fill(st, S->e_zbl, n, 0.f); fill(st, S->e_coul, n, 0.f); fill(st, S->e_disp, n, 0.f);
   fill(st, S->gq, n, 0.f); fill(st, S->gh, n, 0.f);
   if (F) fill(st, F, (size_t)n * 3, 0.f);
-  S->prof.begin(kPGeom, st); launch_sr_geometry_zbl(st, M, S->cell, n, n_edges, edge_i, nbr_j, S->d_Z, R, graph_mode, dR, S->e_zbl, g_dR, ge); S->prof.end(st);
+  S->prof.begin(kPGeom, st); launch_sr_geometry_zbl(st, M, S->cell, n, n_edges, edge_i, nbr_j, S->d_Z, R, graph_mode, dR, S->e_zbl, g_dR, ge, fused ? F : nullptr); S->prof.end(st);
   launch_embed(st, M, S->d_Z, n, S->x[0]);
   S->n_launches += 8;
   for (int l = 0; l < kNumLayers; ++l) {
     const LayerDev& L = M.layer[l];
     S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], n, S->qkv[l]); S->prof.end(st);
-    S->prof.begin(kPAttnFwd, st); launch_attn_fwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]); S->prof.end(st);
+    S->prof.begin(kPAttnFwd, st);
+    if (fused) launch_attn_fwd_sym(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
+    else launch_attn_fwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
+    S->prof.end(st);
     S->prof.begin(kPPostFwd, st); launch_atom_post_fwd(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]); S->prof.end(st);
     S->n_launches += 3;
   }
@@ -267,7 +317,18 @@ int evaluate(so3lr_b200_system* S, cudaStream_t st, const float* R, const int* r
   for (int l = kNumLayers - 1; l >= 0; --l) {
     const LayerDev& L = M.layer[l];
     S->prof.begin(kPPostBwd, st); launch_atom_post_bwd(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, gev2, S->g_xa, S->gev1); S->prof.end(st);
-    if (l > 0) {
+    if (fused) {
+      S->prof.begin(kPAttnBwd, st);
+      launch_attn_bwd_sym(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, F, l == 0 ? 1 : 0);
+      S->prof.end(st);
+      S->n_launches += 1;
+      if (l > 0) {
+        SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)n * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
+        S->prof.begin(kPProjBwd, st); launch_proj_bwd(st, L, S->g_qkv, n, S->g4, 1); S->prof.end(st);
+        float* t = gev2; gev2 = gev_in; gev_in = t;
+        S->n_launches += 2;
+      }
+    } else if (l > 0) {
       SO3LR_CUDA_CHECK(cudaMemcpyAsync(gev_in, S->gev1, (size_t)n * kMTot * sizeof(float), cudaMemcpyDeviceToDevice, st));
       fill(st, S->g_qkv, (size_t)n * kProj, 0.f);
       S->prof.begin(kPAttnBwd, st); launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, g_dR, 0); S->prof.end(st);
@@ -280,10 +341,6 @@ int evaluate(so3lr_b200_system* S, cudaStream_t st, const float* R, const int* r
       S->prof.begin(kPAttnBwd, st); launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, nullptr, nullptr, g_dR, 1); S->prof.end(st);
       S->n_launches += 2;
     }
-  }
-  if (!graph_mode && F) {
-    S->prof.begin(kPScatter, st); launch_force_scatter(st, n, n_edges, edge_i, nbr_j, g_dR, F); S->prof.end(st);
-    S->n_launches += 1;
   }
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
@@ -321,6 +378,7 @@ SO3LR_B200_API int so3lr_b200_model_create(const float* blob_host, size_t n_floa
   int rc = build_model(blob_host, n_floats, &m->M, &m->owned);
   if (rc == kOk) rc = configure_atom_kernels();
   if (rc == kOk) rc = configure_attention_kernels();
+  if (rc == kOk) rc = configure_attention_sym_kernels();
   if (rc != kOk) { so3lr_b200_model_destroy(m); return rc; }
   *out = m;
   return kOk;
@@ -373,7 +431,11 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
   }
   const int n = n_atoms;
   Pool& A = S->pool;
-  S->d_Z = A.get<int>(n); S->d_seg = A.get<int>(n); S->d_graph_start = A.get<int>(n_graphs + 1);
+  S->d_Z0 = A.get<int>(n); S->d_Zs = A.get<int>(n); S->d_Z = S->d_Z0; S->d_perm = A.get<int>(n);
+  S->d_Rs = A.get<float>((size_t)n * 3); S->F_s = A.get<float>((size_t)n * 3);
+  S->u_e_atom = A.get<float>(n); S->u_q = A.get<float>(n); S->u_h = A.get<float>(n);
+  S->u_zbl = A.get<float>(n); S->u_coul = A.get<float>(n); S->u_disp = A.get<float>(n);
+  S->d_seg = A.get<int>(n); S->d_graph_start = A.get<int>(n_graphs + 1);
   S->d_total_charge = A.get<float>(n_graphs);
   std::vector<int> gs(n_graphs + 1), seg(n);
   if (graph_start) { for (int g = 0; g <= n_graphs; ++g) gs[g] = graph_start[g]; }
@@ -403,7 +465,7 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
   S->d_energy = A.get<double>(n_graphs); S->d_dipole = A.get<float>((size_t)n_graphs * 3);
   S->d_Rstage = A.get<float>((size_t)n * 3);
   if (A.status != kOk) { A.release(); delete S; return A.status; }
-  bool ok = cudaMemcpy(S->d_Z, Z, (size_t)n * sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess &&
+  bool ok = cudaMemcpy(S->d_Z0, Z, (size_t)n * sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess &&
             cudaMemcpy(S->d_seg, seg.data(), (size_t)n * sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess &&
             cudaMemcpy(S->d_graph_start, gs.data(), (size_t)(n_graphs + 1) * sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess &&
             cudaMemcpy(S->d_total_charge, tq.data(), (size_t)n_graphs * sizeof(float), cudaMemcpyHostToDevice) == cudaSuccess &&
@@ -432,7 +494,7 @@ SO3LR_B200_API int so3lr_b200_system_destroy(so3lr_b200_system* S) {
   S->prof.destroy();
   nlist_workspace_destroy(S->nws);
   for (NeighborListDev* L : {&S->sr, &S->lrl}) { cudaFree(L->row_ptr); cudaFree(L->nbr_j); cudaFree(L->edge_i); }
-  cudaFree(S->dR); cudaFree(S->g_dR);
+  cudaFree(S->dR);
   if (S->h_flag) cudaFreeHost(S->h_flag);
   if (S->h_R) cudaFreeHost(S->h_R);
   if (S->h_F) cudaFreeHost(S->h_F);
@@ -453,7 +515,7 @@ SO3LR_B200_API int so3lr_b200_system_set_cell(so3lr_b200_system* S, const float*
   return kOk;
 }
 
-static int prepare_lists(so3lr_b200_system* S, cudaStream_t st, const float* R) {
+static int prepare_lists(so3lr_b200_system* S, cudaStream_t st, const float* R, bool allow_sort = true) {
   bool rebuild = !S->have_lists;
   if (!rebuild) {
     if (S->opt.skin <= 0.f) rebuild = true;
@@ -470,7 +532,7 @@ static int prepare_lists(so3lr_b200_system* S, cudaStream_t st, const float* R) 
   }
   if (rebuild) {
     S->prof.begin(kPNlist, st);
-    int rc = rebuild_lists(S, st, R);
+    int rc = rebuild_lists(S, st, R, allow_sort);
     S->prof.end(st);
     return rc;
   }
@@ -485,16 +547,27 @@ SO3LR_B200_API int so3lr_b200_system_compute(so3lr_b200_system* S, void* stream,
   int rc = prepare_lists(S, st, R);
   if (rc) return rc;
   float* Fout = F ? F : S->F_int;
-  rc = evaluate(S, st, R, S->sr.row_ptr, S->sr.nbr_j, S->sr.edge_i, S->sr.count, S->lrl.row_ptr, S->lrl.nbr_j, 0, nullptr, nullptr,
-                nullptr, nullptr, nullptr, Fout);
-  if (rc) return rc;
   const int n = S->n;
-  launch_graph_reduce(st, S->n_graphs, S->d_graph_start, S->e_atom, S->q, R, S->d_energy, S->d_dipole);
+  const float* R_eval = R;
+  if (S->sorted) {
+    gather_positions_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->d_perm, R, S->d_Rs);
+    R_eval = S->d_Rs;
+  }
+  rc = evaluate(S, st, R_eval, S->sr.row_ptr, S->sr.nbr_j, S->sr.edge_i, S->sr.count, S->lrl.row_ptr, S->lrl.nbr_j, 0, nullptr, nullptr,
+                nullptr, nullptr, nullptr, S->sorted ? S->F_s : Fout);
+  if (rc) return rc;
+  launch_graph_reduce(st, S->n_graphs, S->d_graph_start, S->e_atom, S->q, R_eval, S->d_energy, S->d_dipole);
   S->n_launches += 1;
-  if (e_atom) SO3LR_CUDA_CHECK(cudaMemcpyAsync(e_atom, S->e_atom, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  if (S->sorted) {
+    UnsortArgs A{{S->e_atom, S->q, S->h, S->e_zbl, S->e_coul, S->e_disp, nullptr},
+                 {S->u_e_atom, S->u_q, S->u_h, S->u_zbl, S->u_coul, S->u_disp, nullptr}};
+    unsort_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->d_perm, S->F_s, Fout, A);
+    S->n_launches += 2;
+  }
+  if (e_atom) SO3LR_CUDA_CHECK(cudaMemcpyAsync(e_atom, S->o_e_atom, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
   if (energy) SO3LR_CUDA_CHECK(cudaMemcpyAsync(energy, S->d_energy, (size_t)S->n_graphs * sizeof(double), cudaMemcpyDeviceToDevice, st));
-  if (charges) SO3LR_CUDA_CHECK(cudaMemcpyAsync(charges, S->q, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
-  if (hirshfeld) SO3LR_CUDA_CHECK(cudaMemcpyAsync(hirshfeld, S->h, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  if (charges) SO3LR_CUDA_CHECK(cudaMemcpyAsync(charges, S->o_q, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  if (hirshfeld) SO3LR_CUDA_CHECK(cudaMemcpyAsync(hirshfeld, S->o_h, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
   if (dipole) SO3LR_CUDA_CHECK(cudaMemcpyAsync(dipole, S->d_dipole, (size_t)S->n_graphs * 3 * sizeof(float), cudaMemcpyDeviceToDevice, st));
   return kOk;
 }
@@ -511,8 +584,8 @@ SO3LR_B200_API int so3lr_b200_system_compute_host(so3lr_b200_system* S, const fl
   if (rc) return rc;
   if (F_host) SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_F, S->F_int, (size_t)n * 3 * sizeof(float), cudaMemcpyDeviceToHost, st));
   if (E_host) SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_E, S->d_energy, (size_t)S->n_graphs * sizeof(double), cudaMemcpyDeviceToHost, st));
-  if (q_host) SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_q, S->q, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost, st));
-  if (h_host) SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_h, S->h, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost, st));
+  if (q_host) SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_q, S->o_q, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost, st));
+  if (h_host) SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_h, S->o_h, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost, st));
   if (dip_host) SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_dip, S->d_dipole, (size_t)S->n_graphs * 3 * sizeof(float), cudaMemcpyDeviceToHost, st));
   SO3LR_CUDA_CHECK(cudaStreamSynchronize(st));
   if (F_host) std::memcpy(F_host, S->h_F, (size_t)n * 3 * sizeof(float));
@@ -525,9 +598,9 @@ SO3LR_B200_API int so3lr_b200_system_compute_host(so3lr_b200_system* S, const fl
 
 SO3LR_B200_API int so3lr_b200_system_aux(so3lr_b200_system* S, const float** zbl, const float** coul, const float** disp) {
   if (!S) return kInvalidArgument;
-  if (zbl) *zbl = S->e_zbl;
-  if (coul) *coul = S->e_coul;
-  if (disp) *disp = S->e_disp;
+  if (zbl) *zbl = S->o_zbl ? S->o_zbl : S->e_zbl;
+  if (coul) *coul = S->o_coul ? S->o_coul : S->e_coul;
+  if (disp) *disp = S->o_disp ? S->o_disp : S->e_disp;
   return kOk;
 }
 
@@ -546,8 +619,9 @@ SO3LR_B200_API int so3lr_b200_system_export_list(so3lr_b200_system* S, void* str
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
   cudaStream_t st = (cudaStream_t)stream;
   S->have_lists = false;
-  int rc = prepare_lists(S, st, R);
+  int rc = prepare_lists(S, st, R, false);   // lists in the caller's atom order
   if (rc) return rc;
+  S->have_lists = false;                      // the next evaluation rebuilds them in its own (sorted) order
   const NeighborListDev& L = which == 0 ? S->sr : S->lrl;
   long long cnt = L.count < capacity ? L.count : capacity;
   export_list_kernel<<<(unsigned)((capacity + 255) / 256), 256, 0, st>>>(S->n, cnt, capacity, L.edge_i, L.nbr_j, idx);
@@ -566,6 +640,9 @@ SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* S, void* stre
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
   cudaStream_t st = (cudaStream_t)stream;
   const int n = S->n;
+  // graph-level lists are in the caller's atom order
+  S->d_Z = S->d_Z0; S->sorted = false; S->have_lists = false;
+  S->o_e_atom = S->e_atom; S->o_q = S->q; S->o_h = S->h; S->o_zbl = S->e_zbl; S->o_coul = S->e_coul; S->o_disp = S->e_disp;
   row_ptr_from_sorted_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(n, n_edges, idx_i, S->d_rowptr_g);
   row_ptr_from_sorted_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(n, n_pairs, idx_i_lr, S->d_rowptr_lr_g);
   S->n_launches += 2;

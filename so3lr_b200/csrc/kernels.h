@@ -31,12 +31,24 @@ void launch_attn_bwd(cudaStream_t s, const LayerDev& L, int n, const int* row_pt
                      const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv,
                      float* gev_in, float* g_dR, int first_layer);
 
+// ---- attention_sym.cu ----
+// Gather-only kernels of the fused positions -> forces path.  They need a symmetric list (j in row i <=> i in row j with
+// dR_ji = -dR_ij), which the cell-list builder guarantees.  The backward kernel writes g_qkv / gev_in rows completely
+// (no pre-fill needed; gev_in includes the skip term gev1) and adds the attention part of the force on atom i to F[i].
+int configure_attention_sym_kernels();
+void launch_attn_fwd_sym(cudaStream_t s, const LayerDev& L, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+                         const float* qkv, const float* x_in, const float* ev_in, float* xa, float* ev1);
+void launch_attn_bwd_sym(cudaStream_t s, const LayerDev& L, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+                         const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv, float* gev_in,
+                         float* F, int first_layer);
+
 // ---- pair_kernels.cu ----
 // dR for every short-range edge from positions (+ minimum image), ZBL energy into e_atom[centre], ZBL gradient
-// written to g_dR (initialises it).  With `dR_given` the displacements are inputs.
+// written to g_dR (initialises it) when g_dR is given, and/or added straight into the forces F_direct (F_i += g,
+// F_j -= g).  With `dR_given` the displacements are inputs.
 void launch_sr_geometry_zbl(cudaStream_t s, const ModelDev& M, const Cell& cell, int n, long long n_edges, const int* edge_i,
                             const int* nbr_j, const int* Z, const float* R, int dR_given, float* dR, float* e_atom, float* g_dR,
-                            const float* ge);
+                            const float* ge, float* F_direct);
 // F[i] += g, F[j] -= g for every edge
 void launch_force_scatter(cudaStream_t s, int n, long long n_edges, const int* edge_i, const int* nbr_j, const float* g_dR,
                           float* F);
@@ -66,6 +78,9 @@ struct NeighborListDev {
 struct NlistWorkspace;       // opaque scratch (cell ids, sort buffers)
 NlistWorkspace* nlist_workspace_create();
 void nlist_workspace_destroy(NlistWorkspace*);
+// perm[k] = index of the atom that comes k-th along a Morton curve through cells of edge >= cell_size (periodic cells
+// only).  Radix sort is stable, so the order is deterministic.
+int spatial_order(NlistWorkspace* ws, cudaStream_t s, const Cell& cell, int n, const float* R, float cell_size, int* perm);
 // Builds rows for all i.  ordered: keep j > i only.  seg/graph_start (optional): pairs only inside one graph and the
 // candidate loop runs over the graph's atoms.  Grows `out` when `allow_grow`, otherwise sets *overflow (device int).
 int nlist_build(NlistWorkspace* ws, cudaStream_t s, const Cell& cell, int n, const float* R, float r_list, int ordered,

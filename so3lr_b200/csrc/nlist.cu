@@ -23,6 +23,12 @@ struct NlistWorkspace {
   long long* d_total = nullptr;
   long long* h_total = nullptr;  // pinned
   int n_cap = 0, cell_cap = 0;
+  // spatial ordering of the atoms (Morton keys of the short-range cells)
+  unsigned* key = nullptr;
+  unsigned* key_sorted = nullptr;
+  void* sort_tmp = nullptr;
+  size_t sort_bytes = 0;
+  int key_cap = 0;
 };
 
 NlistWorkspace* nlist_workspace_create() { return new NlistWorkspace(); }
@@ -30,6 +36,7 @@ void nlist_workspace_destroy(NlistWorkspace* w) {
   if (!w) return;
   cudaFree(w->cell_of); cudaFree(w->cell_sorted); cudaFree(w->atom_sorted); cudaFree(w->atom_iota);
   cudaFree(w->cell_start); cudaFree(w->row_count); cudaFree(w->cub_tmp); cudaFree(w->d_total);
+  cudaFree(w->key); cudaFree(w->key_sorted); cudaFree(w->sort_tmp);
   if (w->h_total) cudaFreeHost(w->h_total);
   delete w;
 }
@@ -178,6 +185,24 @@ __global__ void clamp_rows_kernel(int n, int* __restrict__ row_ptr, long long ca
   if (k <= n && (long long)row_ptr[k] > capacity) row_ptr[k] = (int)capacity;
 }
 
+__device__ __forceinline__ unsigned spread3(unsigned v) {   // 10 bits -> every third bit
+  v &= 0x3ffu;
+  v = (v | (v << 16)) & 0x030000ffu;
+  v = (v | (v << 8)) & 0x0300f00fu;
+  v = (v | (v << 4)) & 0x030c30c3u;
+  v = (v | (v << 2)) & 0x09249249u;
+  return v;
+}
+__global__ void morton_keys_kernel(Cell cell, Grid G, int n, const float* __restrict__ R, unsigned* __restrict__ key,
+                                   int* __restrict__ iota) {
+  int a = blockIdx.x * blockDim.x + threadIdx.x;
+  if (a >= n) return;
+  int c[3];
+  cell_coords(cell, G, R[3 * (size_t)a], R[3 * (size_t)a + 1], R[3 * (size_t)a + 2], c);
+  key[a] = spread3((unsigned)c[0]) | (spread3((unsigned)c[1]) << 1) | (spread3((unsigned)c[2]) << 2);
+  iota[a] = a;
+}
+
 template <typename T>
 int ensure(T** p, size_t n) {
   if (*p) cudaFree(*p);
@@ -187,6 +212,47 @@ int ensure(T** p, size_t n) {
 }
 
 }  // namespace
+
+int spatial_order(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, const float* R, float cell_size, int* perm) {
+  if (n <= 0 || !cell.periodic) return kInvalidArgument;
+  if (n > w->key_cap) {
+    int st;
+    if ((st = ensure(&w->key, n))) return st;
+    if ((st = ensure(&w->key_sorted, n))) return st;
+    w->key_cap = n;
+  }
+  if (n > w->n_cap) {
+    int st;
+    if ((st = ensure(&w->cell_of, n))) return st;
+    if ((st = ensure(&w->cell_sorted, n))) return st;
+    if ((st = ensure(&w->atom_sorted, n))) return st;
+    if ((st = ensure(&w->atom_iota, n))) return st;
+    if ((st = ensure(&w->row_count, (size_t)n + 1))) return st;
+    w->n_cap = n;
+  }
+  Grid G{};
+  for (int k = 0; k < 3; ++k) {
+    double nx = cell.hinv[0 + k], ny = cell.hinv[3 + k], nz = cell.hinv[6 + k];
+    double width = 1.0 / std::sqrt(nx * nx + ny * ny + nz * nz);
+    int nc = (int)std::floor(width / (double)cell_size);
+    if (nc < 1) nc = 1;
+    if (nc > 1024) nc = 1024;
+    G.nc[k] = nc; G.wrap[k] = 1;
+  }
+  morton_keys_kernel<<<(n + 255) / 256, 256, 0, s>>>(cell, G, n, R, w->key, w->atom_iota);
+  size_t need = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, need, w->key, w->key_sorted, w->atom_iota, perm, n, 0, 30, s);
+  if (need > w->sort_bytes) {
+    if (w->sort_tmp) cudaFree(w->sort_tmp);
+    w->sort_tmp = nullptr;
+    SO3LR_CUDA_CHECK(cudaMalloc(&w->sort_tmp, need));
+    w->sort_bytes = need;
+  }
+  size_t tmp = w->sort_bytes;
+  cub::DeviceRadixSort::SortPairs(w->sort_tmp, tmp, w->key, w->key_sorted, w->atom_iota, perm, n, 0, 30, s);
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
 
 int nlist_build(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, const float* R, float r_list, int ordered,
                 const int* seg, const int* graph_start, NeighborListDev* out, int allow_grow, int* d_overflow) {

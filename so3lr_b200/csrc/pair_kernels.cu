@@ -9,7 +9,7 @@ namespace {
 __global__ void sr_geometry_zbl_kernel(ZblParams zbl, Cell cell, int n, long long n_edges, const int* __restrict__ edge_i,
                                        const int* __restrict__ nbr_j, const int* __restrict__ Z, const float* __restrict__ R,
                                        int dR_given, float* __restrict__ dR, float* __restrict__ e_atom,
-                                       float* __restrict__ g_dR, const float* __restrict__ ge) {
+                                       float* __restrict__ g_dR, const float* __restrict__ ge, float* __restrict__ F_direct) {
   long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= n_edges) return;
   const int i = edge_i[e], j = nbr_j[e];
@@ -36,8 +36,12 @@ __global__ void sr_geometry_zbl_kernel(ZblParams zbl, Cell cell, int n, long lon
     atomicAdd(e_atom + i, ez);
     const float s = (ge ? ge[i] : 1.f) * dez / r;
     gx = s * dx; gy = s * dy; gz = s * dz;
+    if (F_direct) {   // only edges shorter than 1.5 A get here: a handful per atom
+      atomicAdd(F_direct + 3 * (size_t)i, gx); atomicAdd(F_direct + 3 * (size_t)i + 1, gy); atomicAdd(F_direct + 3 * (size_t)i + 2, gz);
+      atomicAdd(F_direct + 3 * (size_t)j, -gx); atomicAdd(F_direct + 3 * (size_t)j + 1, -gy); atomicAdd(F_direct + 3 * (size_t)j + 2, -gz);
+    }
   }
-  g_dR[3 * e] = gx; g_dR[3 * e + 1] = gy; g_dR[3 * e + 2] = gz;
+  if (g_dR) { g_dR[3 * e] = gx; g_dR[3 * e + 1] = gy; g_dR[3 * e + 2] = gz; }
 }
 
 __global__ void force_scatter_kernel(int n, long long n_edges, const int* __restrict__ edge_i, const int* __restrict__ nbr_j,
@@ -203,10 +207,11 @@ __global__ void graph_reduce_kernel(int n_graphs, const int* __restrict__ graph_
 }  // namespace
 
 void launch_sr_geometry_zbl(cudaStream_t s, const ModelDev& M, const Cell& cell, int n, long long n_edges, const int* edge_i,
-                            const int* nbr_j, const int* Z, const float* R, int dR_given, float* dR, float* e_atom, float* g_dR, const float* ge) {
+                            const int* nbr_j, const int* Z, const float* R, int dR_given, float* dR, float* e_atom, float* g_dR, const float* ge,
+                            float* F_direct) {
   if (n_edges <= 0) return;
   unsigned blocks = (unsigned)((n_edges + 255) / 256);
-  sr_geometry_zbl_kernel<<<blocks, 256, 0, s>>>(M.zbl, cell, n, n_edges, edge_i, nbr_j, Z, R, dR_given, dR, e_atom, g_dR, ge);
+  sr_geometry_zbl_kernel<<<blocks, 256, 0, s>>>(M.zbl, cell, n, n_edges, edge_i, nbr_j, Z, R, dR_given, dR, e_atom, g_dR, ge, F_direct);
 }
 
 void launch_force_scatter(cudaStream_t s, int n, long long n_edges, const int* edge_i, const int* nbr_j, const float* g_dR, float* F) {
