@@ -2,7 +2,9 @@
 //
 // One warp owns one receiver atom i and walks its row of the (symmetric) short-range list in chunks of 32 entries:
 //   phase A  lane = list entry: distance test, cutoff, Hermite weights of the radial table, per-degree invariants of
-//            (ev_j - ev_i), spherical harmonics; the surviving entries are compacted into per-warp shared memory.
+//            (ev_j - ev_i), spherical harmonics; the surviving entries are compacted into per-warp shared memory
+//            records.  Records that do not fill a group of 8 are carried over to the next chunk, so only the last
+//            group of a row is padded.
 //   phase B  lane = 4 features: groups of 8 compacted edges share one pass over the spherical-filter weights
 //            (register-blocked 8 edges x 8 columns per lane), then the radial table, logits and weighted sums.
 // The backward kernel uses the symmetry of the list instead of atomics: while visiting neighbour j, warp i evaluates
@@ -18,8 +20,8 @@ namespace {
 constexpr int EB = 8;                       // edges per pass over the filter weights
 constexpr int FW_WARPS = 8;
 constexpr int BW_WARPS = 12;
-constexpr int kYS = 28;                     // row stride of the spherical-harmonics buffer (floats)
-constexpr int kFwRec = 16;                  // floats per compacted edge record, forward
+constexpr int kSlots = 40;                  // record slots per warp: up to 7 carried over + 32 new, rounded up to a group
+constexpr int kFwRec = 36;                  // floats per compacted edge record, forward: header 4 | Hermite 4 | invariants 4 | Y 24
 constexpr int kBwRec = 40;                  // floats per compacted edge record, backward
 constexpr int kDwS = 132;                   // row stride of the dw staging buffer
 constexpr float kInvNbar = 1.0f / kAvgNumNeighbors;
@@ -100,7 +102,7 @@ __device__ __forceinline__ void filter_gemm(const float* __restrict__ K2f, const
 // ------------------------------------------------------------------------------------------------------------------
 // forward
 // ------------------------------------------------------------------------------------------------------------------
-constexpr int kFwWarpFloats = 32 * kFwRec + 32 * kYS + 2 * 32 * EB;   // records | Y | hidden activations (2 filters)
+constexpr int kFwWarpFloats = kSlots * kFwRec + 2 * 32 * EB;   // records | hidden activations (2 filters)
 
 template <bool SPH>
 __global__ void __launch_bounds__(FW_WARPS * 32, 2) attn_fwd_sym_kernel(LayerDev L, int n, const int* __restrict__ row_ptr,
@@ -117,8 +119,7 @@ __global__ void __launch_bounds__(FW_WARPS * 32, 2) attn_fwd_sym_kernel(LayerDev
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* rec = sm + (SPH ? 2 * 32 * kF : 0) + warp * kFwWarpFloats;
-  float* Yb = rec + 32 * kFwRec;
-  float* hsg = Yb + 32 * kYS;
+  float* hsg = rec + kSlots * kFwRec;
   const int col = 4 * lane;
   float k1w1[4] = {0.f, 0.f, 0.f, 0.f}, k1w2[4] = {0.f, 0.f, 0.f, 0.f}, b1 = 0.f, b2 = 0.f;
   if (SPH) {
@@ -135,6 +136,7 @@ __global__ void __launch_bounds__(FW_WARPS * 32, 2) attn_fwd_sym_kernel(LayerDev
     float4 accx = f4_zero();
     float accev = 0.f;
     const int e0 = row_ptr[i], e1 = row_ptr[i + 1];
+    int rem = 0;   // records carried over from the previous chunk
     for (int eb = e0; eb < e1; eb += 32) {
       // ---- phase A ----
       const int e = eb + lane;
@@ -145,10 +147,11 @@ __global__ void __launch_bounds__(FW_WARPS * 32, 2) attn_fwd_sym_kernel(LayerDev
       const float r2 = dx * dx + dy * dy + dz * dz;
       const bool valid = in && j >= 0 && j < n && r2 < kRc2 && r2 > 0.f;
       const unsigned mask = __ballot_sync(0xffffffffu, valid);
-      const int nv = __popc(mask);
-      if (nv == 0) continue;
+      const int total = rem + __popc(mask);
+      const bool last = eb + 32 >= e1;
+      const int nproc = last ? ((total + EB - 1) & ~(EB - 1)) : (total & ~(EB - 1));
       if (valid) {
-        const int p = __popc(mask & ((1u << lane) - 1u));
+        const int p = rem + __popc(mask & ((1u << lane) - 1u));
         const float r = sqrtf(r2), ir = 1.f / r;
         float cut, dcut;
         phys_cutoff(r, cut, dcut);
@@ -162,23 +165,18 @@ __global__ void __launch_bounds__(FW_WARPS * 32, 2) attn_fwd_sym_kernel(LayerDev
         st4(rp, make_float4(__int_as_float(j), cut * kInvNbar, __int_as_float(g), 0.f));
         st4(rp + 4, hv);
         st4(rp + 8, make_float4(s[0], s[1], s[2], s[3]));
-        float* yp = Yb + p * kYS;
 #pragma unroll
-        for (int c = 0; c < 6; ++c) st4(yp + 4 * c, make_float4(Y[4 * c], Y[4 * c + 1], Y[4 * c + 2], Y[4 * c + 3]));
+        for (int c = 0; c < 6; ++c) st4(rp + 12 + 4 * c, make_float4(Y[4 * c], Y[4 * c + 1], Y[4 * c + 2], Y[4 * c + 3]));
       }
-      const int nvp = (nv + EB - 1) & ~(EB - 1);
-      if (lane >= nv && lane < nvp) {   // padding slots of the last group: a harmless edge to atom i with zero weight
-        float* rp = rec + lane * kFwRec;
+      if (total + lane < nproc) {   // padding slots of the row's last group: a harmless edge to atom i with zero weight
+        float* rp = rec + (total + lane) * kFwRec;
         st4(rp, make_float4(__int_as_float(i), 0.f, __int_as_float(0), 0.f));
-        st4(rp + 4, f4_zero());
-        st4(rp + 8, f4_zero());
-        float* yp = Yb + lane * kYS;
 #pragma unroll
-        for (int c = 0; c < 6; ++c) st4(yp + 4 * c, f4_zero());
+        for (int c = 1; c < 9; ++c) st4(rp + 4 * c, f4_zero());
       }
       __syncwarp();
       // ---- phase B ----
-      for (int g0 = 0; g0 < nv; g0 += EB) {
+      for (int g0 = 0; g0 < nproc; g0 += EB) {
         float4 w1[EB], w2[EB];
 #pragma unroll
         for (int k = 0; k < EB; ++k) { w1[k] = f4_zero(); w2[k] = f4_zero(); }
@@ -210,12 +208,18 @@ __global__ void __launch_bounds__(FW_WARPS * 32, 2) attn_fwd_sym_kernel(LayerDev
           const float a1 = group8_sum(dot3(q1, w1[k], k1)) * sc;
           const float a2 = group8_sum(dot3(q2, w2[k], k2)) * sc;
           accx = f4_fma(a1, v1, accx);
-          const float ym = lane < kMTot ? Yb[(g0 + k) * kYS + lane] : 0.f;
+          const float ym = lane < kMTot ? rp[12 + lane] : 0.f;
           const float a2m = __shfl_sync(0xffffffffu, a2, 8 * deg);
           accev = fmaf(a2m, ym, accev);
         }
       }
       __syncwarp();
+      // carry the records that did not fill a group over to the next chunk
+      rem = total - nproc;
+      if (rem > 0 && nproc > 0) {
+        for (int q = lane; q < rem * (kFwRec / 4); q += 32) st4(rec + 4 * q, ld4(rec + nproc * kFwRec + 4 * q));
+        __syncwarp();
+      }
     }
     const float4 xi = ld4(x_in + (size_t)i * kF + col);
     st4(xa + (size_t)i * kF + col, make_float4(xi.x + accx.x, xi.y + accx.y, xi.z + accx.z, xi.w + accx.w));
@@ -227,9 +231,10 @@ __global__ void __launch_bounds__(FW_WARPS * 32, 2) attn_fwd_sym_kernel(LayerDev
 // backward
 // ------------------------------------------------------------------------------------------------------------------
 // record fields (floats): 0 j | 1 sc | 2 table index | 3 dcut/nbar | 4-7 Hermite value weights | 8-11 derivative weights |
-// 12-15 invariants | 16-19 da2 of edge (i<-j) | 20-23 da2 of edge (j<-i) | 24-27 a2 (i<-j) | 28-31 a2 (j<-i) |
-// 32-35 d/d invariants | 36 d/dr
-constexpr int kBwWarpFloats = 32 * kBwRec + 2 * 32 * EB + EB * kDwS;   // records | hidden (silu, silu') | dw staging
+// 12-15 invariants | 16-19 da of edge (i<-j), filter 2 | 20-23 da of edge (j<-i), filter 2 | 24-27 a2 (i<-j) | 28-31 a2 (j<-i) |
+// 32-34 unit vector | 35 1/r | 36-39: d/d invariants (written after the group's last read of everything else) ... 36 also
+// receives d/dr: the layout below keeps them apart: 36 d/dr, and d/d invariants overwrite the invariants (12-15).
+constexpr int kBwWarpFloats = kSlots * kBwRec + 2 * 32 * EB + EB * kDwS;   // records | hidden (silu, silu') | dw staging
 
 template <bool FIRST>
 __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev L, int n, const int* __restrict__ row_ptr,
@@ -253,35 +258,26 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* rec = sm + (FIRST ? 0 : 4 * 32 * kF) + warp * kBwWarpFloats;
-  float* hsg = rec + 32 * kBwRec;
+  float* hsg = rec + kSlots * kBwRec;
   float* dwb = hsg + 2 * 32 * EB;
   const int col = 4 * lane, grp = lane >> 3;
   const int cg = lane & 7, ep = lane >> 3;      // tile of the second filter GEMM: columns 4cg..4cg+3, edges 2ep, 2ep+1
   const int deg = degree_of(lane < kMTot ? lane : 0);
-  float k1w[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, k1b[2] = {0.f, 0.f};
-  if (!FIRST) {
-#pragma unroll
-    for (int f = 0; f < 2; ++f) {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) k1w[f][k] = L.sph1_k[(f * 4 + k) * 32 + lane];
-      k1b[f] = L.sph1_b[f * 32 + lane];
-    }
-  }
   for (int tile = blockIdx.x; tile * BW_WARPS < n; tile += gridDim.x) {
     const int i = tile * BW_WARPS + warp;
     if (i >= n) continue;
     const float* qi = qkv + (size_t)i * kProj;
-    float4 qf_i[2], kf_i[2];
-    qf_i[0] = ld4(qi + col); kf_i[0] = ld4(qi + kF + col);
-    qf_i[1] = ld4(qi + 3 * kF + col); kf_i[1] = ld4(qi + 4 * kF + col);
+    // "a" = the filter of the current pass, "b" = the other one; swapped after each pass
+    float4 qa = ld4(qi + col), ka = ld4(qi + kF + col), qb = ld4(qi + 3 * kF + col), kb = ld4(qi + 4 * kF + col);
     const float4 v_i = ld4(qi + 2 * kF + col);
     const float4 gx_i = ld4(g_xa + (size_t)i * kF + col);
     const float* gevi = gev1 + (size_t)i * kMTot;
     const float* evi = ev_in + (size_t)i * kMTot;
-    float4 gq[2] = {f4_zero(), f4_zero()}, gk[2] = {f4_zero(), f4_zero()}, gv = f4_zero();
+    float4 gqa = f4_zero(), gka = f4_zero(), gqb = f4_zero(), gkb = f4_zero(), gv = f4_zero();
     float gevacc = 0.f, fx = 0.f, fy = 0.f, fz = 0.f;
     const float evi_m = (!FIRST && lane < kMTot) ? evi[lane] : 0.f;
     const int e0 = row_ptr[i], e1 = row_ptr[i + 1];
+    int rem = 0;
     for (int eb = e0; eb < e1; eb += 32) {
       // ---- phase A: lane = list entry ----
       const int e = eb + lane;
@@ -292,14 +288,13 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev
       const float r2 = dx * dx + dy * dy + dz * dz;
       const bool valid = in && j >= 0 && j < n && r2 < kRc2 && r2 > 0.f;
       const unsigned mask = __ballot_sync(0xffffffffu, valid);
-      const int nv = __popc(mask);
-      if (nv == 0) continue;
-      const int p = __popc(mask & ((1u << lane) - 1u));
-      float ux = 0.f, uy = 0.f, uz = 0.f, ir = 0.f;
+      const int total = rem + __popc(mask);
+      const bool last = eb + 32 >= e1;
+      const int nproc = last ? ((total + EB - 1) & ~(EB - 1)) : (total & ~(EB - 1));
       if (valid) {
-        const float r = sqrtf(r2);
-        ir = 1.f / r;
-        ux = dx * ir; uy = dy * ir; uz = dz * ir;
+        const int p = rem + __popc(mask & ((1u << lane) - 1u));
+        const float r = sqrtf(r2), ir = 1.f / r;
+        const float ux = dx * ir, uy = dy * ir, uz = dz * ir;
         float cut, dcut;
         phys_cutoff(r, cut, dcut);
         int g; float4 hv, hd;
@@ -331,34 +326,37 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev
         st4(rp + 12, make_float4(s[0], s[1], s[2], s[3]));
         st4(rp + 16, make_float4(dA[0], dA[1], dA[2], dA[3]));
         st4(rp + 20, make_float4(dB[0], dB[1], dB[2], dB[3]));
+        st4(rp + 32, make_float4(ux, uy, uz, ir));
       }
-      const int nvp = (nv + EB - 1) & ~(EB - 1);
-      if (lane >= nv && lane < nvp) {
-        float* rp = rec + lane * kBwRec;
+      if (total + lane < nproc) {
+        float* rp = rec + (total + lane) * kBwRec;
         st4(rp, make_float4(__int_as_float(i), 0.f, __int_as_float(0), 0.f));
 #pragma unroll
-        for (int c = 1; c < 6; ++c) st4(rp + 4 * c, f4_zero());
+        for (int c = 1; c < 9; ++c) st4(rp + 4 * c, f4_zero());
       }
       __syncwarp();
       // ---- phase B: lane = 4 features ----
-      for (int g0 = 0; g0 < nv; g0 += EB) {
+      for (int g0 = 0; g0 < nproc; g0 += EB) {
         float gr[EB];
 #pragma unroll
         for (int k = 0; k < EB; ++k) gr[k] = 0.f;
         float dsp[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};   // d/d invariants, partial over this lane's 4 hidden units
-#pragma unroll
+#pragma unroll 1
         for (int f = 0; f < 2; ++f) {
           float4 w[EB];
 #pragma unroll
           for (int k = 0; k < EB; ++k) w[k] = f4_zero();
           if (!FIRST) {
-            hidden_layer<true>(rec, kBwRec, 12, g0, k1w[f], k1b[f], lane, hsg);
+            float kw[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) kw[k] = L.sph1_k[(f * 4 + k) * 32 + lane];
+            hidden_layer<true>(rec, kBwRec, 12, g0, kw, L.sph1_b[f * 32 + lane], lane, hsg);
             __syncwarp();
             filter_gemm(K2 + f * 32 * kF, hsg, col, w);
           }
 #pragma unroll
           for (int k = 0; k < EB; ++k) {
-            const float* rp = rec + (g0 + k) * kBwRec;
+            float* rp = rec + (g0 + k) * kBwRec;
             const float4 r0 = ld4(rp), hv = ld4(rp + 4), hd = ld4(rp + 8);
             const int j2 = __float_as_int(r0.x), g = __float_as_int(r0.z);
             const float sc = r0.y, dcn = r0.w;
@@ -366,36 +364,35 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev
             const float4 v0 = ld4(p0), m0 = ld4(p0 + 256), v1 = ld4(p0 + 512), m1 = ld4(p0 + 768);
             w[k] = f4_fma(hv.x, v0, f4_fma(hv.y, m0, f4_fma(hv.z, v1, f4_fma(hv.w, m1, w[k]))));
             const float4 td = f4_fma(hd.x, v0, f4_fma(hd.y, m0, f4_fma(hd.z, v1, f4_fma(hd.w, m1, f4_zero()))));
-            const float* kj = qkv + (size_t)j2 * kProj;
-            const float4 kf_j = ld4(kj + (f ? 4 * kF : kF) + col), qf_j = ld4(kj + (f ? 3 * kF : 0) + col);
+            const float* kj = qkv + (size_t)j2 * kProj + f * 3 * kF;
+            const float4 qf_j = ld4(kj + col), kf_j = ld4(kj + kF + col);
             const float4 wk = w[k];
-            const float DA = group8_sum(dot3(qf_i[f], wk, kf_j));
-            const float DB = group8_sum(dot3(qf_j, wk, kf_i[f]));
+            const float DA = group8_sum(dot3(qa, wk, kf_j));
+            const float DB = group8_sum(dot3(qf_j, wk, ka));
             float daA, daB;
-            float4 gx_j = f4_zero();
             if (f == 0) {
               const float4 v_j = ld4(kj + 2 * kF + col);
-              gx_j = ld4(g_xa + (size_t)j2 * kF + col);
+              const float4 gx_j = ld4(g_xa + (size_t)j2 * kF + col);
               daA = group8_sum(dot2(gx_i, v_j));
               daB = group8_sum(dot2(gx_j, v_i));
+              if (!FIRST) gv = f4_fma(sc * DB, gx_j, gv);
             } else {
               daA = rp[16 + grp];
               daB = rp[20 + grp];
+              if (cg == 0) { rp[24 + grp] = sc * DA; rp[28 + grp] = sc * DB; }
             }
             const float dDA = sc * daA, dDB = sc * daB;
             gr[k] = fmaf(dcn * 0.125f, fmaf(daA, DA, daB * DB), gr[k]);
             if (!FIRST) {
-              gq[f] = make_float4(fmaf(dDA * wk.x, kf_j.x, gq[f].x), fmaf(dDA * wk.y, kf_j.y, gq[f].y), fmaf(dDA * wk.z, kf_j.z, gq[f].z),
-                                  fmaf(dDA * wk.w, kf_j.w, gq[f].w));
-              gk[f] = make_float4(fmaf(dDB * wk.x, qf_j.x, gk[f].x), fmaf(dDB * wk.y, qf_j.y, gk[f].y), fmaf(dDB * wk.z, qf_j.z, gk[f].z),
-                                  fmaf(dDB * wk.w, qf_j.w, gk[f].w));
-              if (f == 0) gv = f4_fma(sc * DB, gx_j, gv);
+              gqa = make_float4(fmaf(dDA * wk.x, kf_j.x, gqa.x), fmaf(dDA * wk.y, kf_j.y, gqa.y), fmaf(dDA * wk.z, kf_j.z, gqa.z),
+                                fmaf(dDA * wk.w, kf_j.w, gqa.w));
+              gka = make_float4(fmaf(dDB * wk.x, qf_j.x, gka.x), fmaf(dDB * wk.y, qf_j.y, gka.y), fmaf(dDB * wk.z, qf_j.z, gka.z),
+                                fmaf(dDB * wk.w, qf_j.w, gka.w));
             }
-            const float4 dw = make_float4(fmaf(dDA * qf_i[f].x, kf_j.x, dDB * qf_j.x * kf_i[f].x), fmaf(dDA * qf_i[f].y, kf_j.y, dDB * qf_j.y * kf_i[f].y),
-                                          fmaf(dDA * qf_i[f].z, kf_j.z, dDB * qf_j.z * kf_i[f].z), fmaf(dDA * qf_i[f].w, kf_j.w, dDB * qf_j.w * kf_i[f].w));
+            const float4 dw = make_float4(fmaf(dDA * qa.x, kf_j.x, dDB * qf_j.x * ka.x), fmaf(dDA * qa.y, kf_j.y, dDB * qf_j.y * ka.y),
+                                          fmaf(dDA * qa.z, kf_j.z, dDB * qf_j.z * ka.z), fmaf(dDA * qa.w, kf_j.w, dDB * qf_j.w * ka.w));
             gr[k] += dot2(dw, td);
             if (!FIRST) st4(dwb + k * kDwS + col, dw);
-            if (f == 1 && cg == 0) { rec[(g0 + k) * kBwRec + 24 + grp] = sc * DA; rec[(g0 + k) * kBwRec + 28 + grp] = sc * DB; }
           }
           if (!FIRST) {
             __syncwarp();
@@ -403,7 +400,7 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev
             float4 a0 = f4_zero(), a1 = f4_zero();
             const float* kt = K2T + f * 4096 + 4 * cg;
             const float* d0 = dwb + (2 * ep) * kDwS, *d1 = dwb + (2 * ep + 1) * kDwS;
-#pragma unroll 4
+#pragma unroll 2
             for (int t4 = 0; t4 < 32; ++t4) {
               const float4 da = ld4(d0 + 4 * t4), db = ld4(d1 + 4 * t4);
               const float4 k0 = ld4(kt + (4 * t4) * 32), k1 = ld4(kt + (4 * t4 + 1) * 32), k2 = ld4(kt + (4 * t4 + 2) * 32),
@@ -424,8 +421,10 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev
                 dsp[1][l] = fmaf(dz1, kw, dsp[1][l]);
               }
             }
-            __syncwarp();
           }
+          __syncwarp();
+          // the other filter becomes the current one
+          { float4 t = qa; qa = qb; qb = t; t = ka; ka = kb; kb = t; t = gqa; gqa = gqb; gqb = t; t = gka; gka = gkb; gkb = t; }
         }
         if (!FIRST) {
 #pragma unroll
@@ -436,9 +435,9 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev
               v += __shfl_xor_sync(0xffffffffu, v, 1); v += __shfl_xor_sync(0xffffffffu, v, 2); v += __shfl_xor_sync(0xffffffffu, v, 4);
               dsp[ee][l] = v;
             }
-          if (cg == 0) {
-            st4(rec + (g0 + 2 * ep) * kBwRec + 32, make_float4(dsp[0][0], dsp[0][1], dsp[0][2], dsp[0][3]));
-            st4(rec + (g0 + 2 * ep + 1) * kBwRec + 32, make_float4(dsp[1][0], dsp[1][1], dsp[1][2], dsp[1][3]));
+          if (cg == 0) {   // all reads of the invariants of this group are done: their slots take the cotangents
+            st4(rec + (g0 + 2 * ep) * kBwRec + 12, make_float4(dsp[0][0], dsp[0][1], dsp[0][2], dsp[0][3]));
+            st4(rec + (g0 + 2 * ep + 1) * kBwRec + 12, make_float4(dsp[1][0], dsp[1][1], dsp[1][2], dsp[1][3]));
           }
         }
 #pragma unroll
@@ -448,12 +447,14 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev
         }
       }
       __syncwarp();
-      // ---- phase C: lane = list entry again: angular part and the force on atom i ----
-      if (valid) {
-        const float* rp = rec + p * kBwRec;
-        const float4 aA = ld4(rp + 24), aB = ld4(rp + 28);
+      // ---- phase C: lane = record: angular part and the force on atom i ----
+      const int ndone = nproc < total ? nproc : total;   // processed records that are real edges
+      for (int slot = lane; slot < ndone; slot += 32) {
+        const float* rp = rec + slot * kBwRec;
+        const int j2 = __float_as_int(rp[0]);
+        const float4 aA = ld4(rp + 24), aB = ld4(rp + 28), uu = ld4(rp + 32);
         const float g_r = rp[36];
-        const float* gevj = gev1 + (size_t)j * kMTot;
+        const float* gevj = gev1 + (size_t)j2 * kMTot;
         float gY[kMTot];
 #pragma unroll
         for (int c = 0; c < 6; ++c) {
@@ -467,31 +468,36 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev
           }
         }
         float gux, guy, guz;
-        sph_harm_24_vjp(ux, uy, uz, gY, gux, guy, guz);
-        const float gd = gux * ux + guy * uy + guz * uz;
-        fx += g_r * ux + (gux - gd * ux) * ir;
-        fy += g_r * uy + (guy - gd * uy) * ir;
-        fz += g_r * uz + (guz - gd * uz) * ir;
+        sph_harm_24_vjp(uu.x, uu.y, uu.z, gY, gux, guy, guz);
+        const float gd = gux * uu.x + guy * uu.y + guz * uu.z;
+        fx += g_r * uu.x + (gux - gd * uu.x) * uu.w;
+        fy += g_r * uu.y + (guy - gd * uu.y) * uu.w;
+        fz += g_r * uu.z + (guz - gd * uu.z) * uu.w;
       }
       if (!FIRST) {
         // lane = component m: d/d ev_i through the invariants, - ds_l * 2 (ev_j - ev_i)_m / sqrt(2l+1)
-        for (int pp = 0; pp < nv; ++pp) {
+        for (int pp = 0; pp < ndone; ++pp) {
           const float* rp = rec + pp * kBwRec;
           const int j2 = __float_as_int(rp[0]);
           if (lane < kMTot) {
             const float dev = ev_in[(size_t)j2 * kMTot + lane] - evi_m;
-            gevacc = fmaf(-2.f * invw(deg) * rp[32 + deg], dev, gevacc);
+            gevacc = fmaf(-2.f * invw(deg) * rp[12 + deg], dev, gevacc);
           }
         }
       }
       __syncwarp();
+      rem = total - nproc;
+      if (rem > 0 && nproc > 0) {
+        for (int q = lane; q < rem * (kBwRec / 4); q += 32) st4(rec + 4 * q, ld4(rec + nproc * kBwRec + 4 * q));
+        __syncwarp();
+      }
     }
     fx = warp_sum(fx); fy = warp_sum(fy); fz = warp_sum(fz);
     if (lane == 0) { F[3 * (size_t)i] += fx; F[3 * (size_t)i + 1] += fy; F[3 * (size_t)i + 2] += fz; }
     if (!FIRST) {
       float* gi = g_qkv + (size_t)i * kProj;
-      st4(gi + col, gq[0]); st4(gi + kF + col, gk[0]); st4(gi + 2 * kF + col, gv);
-      st4(gi + 3 * kF + col, gq[1]); st4(gi + 4 * kF + col, gk[1]);
+      st4(gi + col, gqa); st4(gi + kF + col, gka); st4(gi + 2 * kF + col, gv);
+      st4(gi + 3 * kF + col, gqb); st4(gi + 4 * kF + col, gkb);
       if (lane < kMTot) gev_in[(size_t)i * kMTot + lane] = gevi[lane] + gevacc;
     }
   }
