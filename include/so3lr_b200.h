@@ -126,6 +126,34 @@ SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* sys, void* st
 SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* sys, void* stream, int n_steps, float dt_fs, const float* masses_dev,
                           float* positions_dev, float* velocities_dev, float* forces_dev, double* energy_dev);
 
+/* Domain-decomposed evaluation of one large periodic structure: every rank owns the atoms of its sub-box and holds
+ * copies ("ghosts") of the atoms within three interaction shells (3 x (4.5 A + skin), which also covers the 12 A pair
+ * terms) of it.  The library evaluates one rank's atoms; moving positions, charges and forces between ranks is the
+ * caller's job (so3lr_b200/domain.py does it with NCCL send/recv).  Per evaluation:
+ *   dd_forward : network forward; raw partial charges and Hirshfeld ratios of the owned atoms come out
+ *   (caller: global sum of the raw charges -> charge conservation; halo exchange of q and h)
+ *   dd_pair    : Coulomb + dispersion of every pair that involves an owned atom (half the pair energy is booked
+ *                here, the other half by the partner's owner); the sum of dE/dq over the owned atoms comes out
+ *   (caller: sum of that number over all ranks; dd_backward divides it by the global atom count n_atoms_all)
+ *   dd_backward: reverse pass; forces on all local atoms (owned and ghosts) and the energy of the owned atoms
+ *   (caller: ghost forces go back to their owners and are added there)
+ * The context is created with so3lr_b200_system_create for the largest local atom count it will see (n_graphs = 1,
+ * cutoff_lr > 0); dd_set_atoms installs a new local atom set and invalidates the neighbor lists.
+ * Local atom order: [0, shells4[0]) owned, then ghosts by shell: [.., shells4[1]) within one shell of the sub-box,
+ * [.., shells4[2]) within two, [.., shells4[3] = n_local) the rest.  `cell9` is the rank's local periodic cell; along the
+ * decomposed direction it must exceed the extent of the local atoms by more than the list radius, so that no pair is
+ * found through the wrap.  Z_local_dev: device int32; all other pointers are device pointers.
+ * Replaces: nothing in the reference (it has no multi-device path); the decomposition follows the cutoffs of
+ * so3lr/potential.py:17-29 and so3lr/jaxmd_utils.py:96-121. */
+SO3LR_B200_API int so3lr_b200_dd_set_atoms(so3lr_b200_system* sys, int n_local, const int32_t* shells4, const int32_t* Z_local_dev,
+                                           const float* cell9);
+SO3LR_B200_API int so3lr_b200_dd_forward(so3lr_b200_system* sys, void* stream, const float* R_local_dev, float* q_raw_owned_dev,
+                                         float* h_owned_dev);
+SO3LR_B200_API int so3lr_b200_dd_pair(so3lr_b200_system* sys, void* stream, const float* R_local_dev, const float* q_local_dev,
+                                      const float* h_local_dev, double* gq_sum_dev);
+SO3LR_B200_API int so3lr_b200_dd_backward(so3lr_b200_system* sys, void* stream, const double* gq_sum_all_dev, int64_t n_atoms_all,
+                                          float* F_local_dev, double* energy_owned_dev);
+
 /* Optional timing of kernel groups with CUDA events recorded on the launching stream.  `profile(sys, 1)` starts a
  * fresh recording; `profile_read` synchronises the device, returns the number of groups and fills, per group, the
  * summed device time in ms, the number of timed launches and a static name.  No counterpart in the reference

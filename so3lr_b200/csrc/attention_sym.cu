@@ -105,7 +105,7 @@ __device__ __forceinline__ void filter_gemm(const float* __restrict__ K2f, const
 constexpr int kFwWarpFloats = kSlots * kFwRec + 2 * 32 * EB;   // records | hidden activations (2 filters)
 
 template <bool SPH>
-__global__ void __launch_bounds__(FW_WARPS * 32, 2) attn_fwd_sym_kernel(LayerDev L, int n, const int* __restrict__ row_ptr,
+__global__ void __launch_bounds__(FW_WARPS * 32, 2) attn_fwd_sym_kernel(LayerDev L, int n_recv, int n, const int* __restrict__ row_ptr,
                                                                         const int* __restrict__ nbr_j, const float* __restrict__ dR,
                                                                         const float* __restrict__ qkv, const float* __restrict__ x_in,
                                                                         const float* __restrict__ ev_in, float* __restrict__ xa,
@@ -128,9 +128,9 @@ __global__ void __launch_bounds__(FW_WARPS * 32, 2) attn_fwd_sym_kernel(LayerDev
     b1 = L.sph1_b[lane]; b2 = L.sph1_b[32 + lane];
   }
   const int deg = degree_of(lane < kMTot ? lane : 0);
-  for (int tile = blockIdx.x; tile * FW_WARPS < n; tile += gridDim.x) {
+  for (int tile = blockIdx.x; tile * FW_WARPS < n_recv; tile += gridDim.x) {
     const int i = tile * FW_WARPS + warp;
-    if (i >= n) continue;
+    if (i >= n_recv) continue;
     const float* qi = qkv + (size_t)i * kProj;
     const float4 q1 = ld4(qi + col), q2 = ld4(qi + 3 * kF + col);
     float4 accx = f4_zero();
@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(FW_WARPS * 32, 2) attn_fwd_sym_kernel(LayerDev
 constexpr int kBwWarpFloats = kSlots * kBwRec + 2 * 32 * EB + EB * kDwS;   // records | hidden (silu, silu') | dw staging
 
 template <bool FIRST>
-__global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev L, int n, const int* __restrict__ row_ptr,
+__global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev L, int n_recv, int n, const int* __restrict__ row_ptr,
                                                                         const int* __restrict__ nbr_j, const float* __restrict__ dR,
                                                                         const float* __restrict__ qkv, const float* __restrict__ ev_in,
                                                                         const float* __restrict__ g_xa, const float* __restrict__ gev1,
@@ -263,9 +263,9 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev
   const int col = 4 * lane, grp = lane >> 3;
   const int cg = lane & 7, ep = lane >> 3;      // tile of the second filter GEMM: columns 4cg..4cg+3, edges 2ep, 2ep+1
   const int deg = degree_of(lane < kMTot ? lane : 0);
-  for (int tile = blockIdx.x; tile * BW_WARPS < n; tile += gridDim.x) {
+  for (int tile = blockIdx.x; tile * BW_WARPS < n_recv; tile += gridDim.x) {
     const int i = tile * BW_WARPS + warp;
-    if (i >= n) continue;
+    if (i >= n_recv) continue;
     const float* qi = qkv + (size_t)i * kProj;
     // "a" = the filter of the current pass, "b" = the other one; swapped after each pass
     float4 qa = ld4(qi + col), ka = ld4(qi + kF + col), qb = ld4(qi + 3 * kF + col), kb = ld4(qi + 4 * kF + col);
@@ -518,27 +518,27 @@ int configure_attention_sym_kernels() {
   return kOk;
 }
 
-void launch_attn_fwd_sym(cudaStream_t s, const LayerDev& L, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+void launch_attn_fwd_sym(cudaStream_t s, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
                          const float* qkv, const float* x_in, const float* ev_in, float* xa, float* ev1) {
-  if (n <= 0) return;
-  int blocks = (n + FW_WARPS - 1) / FW_WARPS;
+  if (n_recv <= 0) return;
+  int blocks = (n_recv + FW_WARPS - 1) / FW_WARPS;
   if (blocks > 148 * 2) blocks = 148 * 2;
   if (L.has_spherical)
-    attn_fwd_sym_kernel<true><<<blocks, FW_WARPS * 32, kSmemFwSph, s>>>(L, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
+    attn_fwd_sym_kernel<true><<<blocks, FW_WARPS * 32, kSmemFwSph, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
   else
-    attn_fwd_sym_kernel<false><<<blocks, FW_WARPS * 32, kSmemFwFirst, s>>>(L, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
+    attn_fwd_sym_kernel<false><<<blocks, FW_WARPS * 32, kSmemFwFirst, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
 }
 
-void launch_attn_bwd_sym(cudaStream_t s, const LayerDev& L, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+void launch_attn_bwd_sym(cudaStream_t s, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
                          const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv, float* gev_in,
                          float* F, int first_layer) {
-  if (n <= 0) return;
-  int blocks = (n + BW_WARPS - 1) / BW_WARPS;
+  if (n_recv <= 0) return;
+  int blocks = (n_recv + BW_WARPS - 1) / BW_WARPS;
   if (blocks > 148) blocks = 148;
   if (first_layer)
-    attn_bwd_sym_kernel<true><<<blocks, BW_WARPS * 32, kSmemBwFirst, s>>>(L, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F);
+    attn_bwd_sym_kernel<true><<<blocks, BW_WARPS * 32, kSmemBwFirst, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F);
   else
-    attn_bwd_sym_kernel<false><<<blocks, BW_WARPS * 32, kSmemBw, s>>>(L, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F);
+    attn_bwd_sym_kernel<false><<<blocks, BW_WARPS * 32, kSmemBw, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F);
 }
 
 }  // namespace so3lr

@@ -27,6 +27,9 @@ struct Pool {
     void* p = nullptr;
     if (n == 0) n = 1;
     if (cudaMalloc(&p, n * sizeof(T)) != cudaSuccess) { status = kCudaError; return nullptr; }
+    // rows that a domain-decomposed evaluation never writes (outer ghost shells) are still read and multiplied by zero
+    // cotangents: they must hold finite numbers
+    if (cudaMemset(p, 0, n * sizeof(T)) != cudaSuccess) status = kCudaError;
     ptrs.push_back(p);
     return (T*)p;
   }
@@ -93,6 +96,29 @@ __global__ void unsort_kernel(int n, const int* __restrict__ perm, const float* 
 #pragma unroll
   for (int q = 0; q < 7; ++q)
     if (A.dst[q]) A.dst[q][a] = A.src[q][k];
+}
+__global__ void __launch_bounds__(1024) sum_to_double_kernel(int n, const float* __restrict__ a, double* __restrict__ out) {
+  __shared__ double red[32];
+  double v = 0.0;
+  for (int k = threadIdx.x; k < n; k += blockDim.x) v += (double)a[k];
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double s = 0.0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += red[w];
+    *out = s;
+  }
+}
+// out = a - (*sum / count): removes the mean whose numerator was summed over all ranks
+__global__ void subtract_mean_kernel(int n, const float* __restrict__ a, const double* __restrict__ sum, double count,
+                                     float* __restrict__ out) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = a[i] - (float)(*sum / count);
+}
+__global__ void abs_kernel(int n, const float* __restrict__ a, float* __restrict__ out) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = fabsf(a[i]);
 }
 // velocity Verlet halves.  units: eV, Angstrom, amu, fs -> acceleration = F/m * 9.64853321e-3 A/fs^2
 constexpr float kAccel = 9.648533212331e-3f;
@@ -166,6 +192,8 @@ struct so3lr_b200_system {
   so3lr_b200_model* model = nullptr;
   Profiler prof;
   int n = 0, n_graphs = 1;
+  int n_cap = 0;                 // atoms the per-atom arrays were allocated for
+  int shells[4] = {0, 0, 0, 0};  // domain-decomposed evaluation: owned | +1 | +2 | +3 shells (see struct Shells)
   so3lr_b200_options opt{};
   Cell cell{};
   LrParams lr{};
@@ -275,39 +303,33 @@ int rebuild_lists(so3lr_b200_system* S, cudaStream_t st, const float* R_user, bo
   return kOk;
 }
 
-// forward + backward over prepared lists.  graph_mode: displacements given (dR / dR_lr), gradients per edge.
-int evaluate(so3lr_b200_system* S, cudaStream_t st, const float* R, const int* row_ptr, const int* nbr_j, const int* edge_i,
-             long long n_edges, const int* row_ptr_lr, const int* nbr_j_lr, int graph_mode, const float* dR_in,
-             const float* dR_lr_in, float* g_dR_out, float* g_dR_lr_out, const float* ge, float* F) {
+// Graph-level evaluation (displacements and lists given by the caller, gradients per edge): scatter kernels with atomics,
+// valid for any list.
+int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, const int* nbr_j, const int* edge_i, long long n_edges,
+                   const int* row_ptr_lr, const int* nbr_j_lr, const float* dR_in, const float* dR_lr_in, float* g_dR,
+                   float* g_dR_lr_out, const float* ge) {
   const ModelDev& M = S->model->M;
   const int n = S->n;
-  float* dR = graph_mode ? const_cast<float*>(dR_in) : S->dR;
-  float* g_dR = graph_mode ? g_dR_out : nullptr;
-  const bool fused = !graph_mode;   // positions -> forces: gather-only attention kernels on the symmetric list
+  float* dR = const_cast<float*>(dR_in);
   fill(st, S->e_zbl, n, 0.f); fill(st, S->e_coul, n, 0.f); fill(st, S->e_disp, n, 0.f);
   fill(st, S->gq, n, 0.f); fill(st, S->gh, n, 0.f);
-  if (F) fill(st, F, (size_t)n * 3, 0.f);
-  S->prof.begin(kPGeom, st); launch_sr_geometry_zbl(st, M, S->cell, n, n_edges, edge_i, nbr_j, S->d_Z, R, graph_mode, dR, S->e_zbl, g_dR, ge, fused ? F : nullptr); S->prof.end(st);
+  S->prof.begin(kPGeom, st); launch_sr_geometry_zbl(st, M, S->cell, n, n_edges, edge_i, nbr_j, S->d_Z, nullptr, 1, dR, S->e_zbl, g_dR, ge, nullptr); S->prof.end(st);
   launch_embed(st, M, S->d_Z, n, S->x[0]);
-  S->n_launches += 8;
+  S->n_launches += 7;
   for (int l = 0; l < kNumLayers; ++l) {
     const LayerDev& L = M.layer[l];
     S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], n, S->qkv[l]); S->prof.end(st);
-    S->prof.begin(kPAttnFwd, st);
-    if (fused) launch_attn_fwd_sym(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
-    else launch_attn_fwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
-    S->prof.end(st);
+    S->prof.begin(kPAttnFwd, st); launch_attn_fwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]); S->prof.end(st);
     S->prof.begin(kPPostFwd, st); launch_atom_post_fwd(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]); S->prof.end(st);
     S->n_launches += 3;
   }
   S->prof.begin(kPHeads, st); launch_heads_fwd(st, M, n, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv); S->prof.end(st);
   launch_charge_conserve(st, S->n_graphs, S->d_graph_start, S->q_raw, S->d_total_charge, S->hv, S->q, S->h);
   S->prof.begin(kPPairLr, st);
-  launch_pair_lr(st, S->lr, S->cell, n, row_ptr_lr, nbr_j_lr, S->d_Z, R, S->q, S->h, graph_mode ? 1 : 0, dR_lr_in, g_dR_lr_out,
-                 nullptr, F, S->gq, S->gh, S->e_coul, S->e_disp, ge);
+  launch_pair_lr(st, S->lr, S->cell, n, row_ptr_lr, nbr_j_lr, S->d_Z, nullptr, S->q, S->h, 1, dR_lr_in, g_dR_lr_out, nullptr, nullptr, S->gq,
+                 S->gh, S->e_coul, S->e_disp, ge);
   S->prof.end(st);
   combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom);
-  // backward
   launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw);
   S->prof.begin(kPHeads, st); launch_heads_bwd(st, M, n, S->d_Z, S->ze, S->zq, S->zh, S->hv, ge ? ge : S->ones, S->gq_raw, S->gh, S->g4); S->prof.end(st);
   S->n_launches += 6;
@@ -317,18 +339,7 @@ int evaluate(so3lr_b200_system* S, cudaStream_t st, const float* R, const int* r
   for (int l = kNumLayers - 1; l >= 0; --l) {
     const LayerDev& L = M.layer[l];
     S->prof.begin(kPPostBwd, st); launch_atom_post_bwd(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, gev2, S->g_xa, S->gev1); S->prof.end(st);
-    if (fused) {
-      S->prof.begin(kPAttnBwd, st);
-      launch_attn_bwd_sym(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, F, l == 0 ? 1 : 0);
-      S->prof.end(st);
-      S->n_launches += 1;
-      if (l > 0) {
-        SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)n * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
-        S->prof.begin(kPProjBwd, st); launch_proj_bwd(st, L, S->g_qkv, n, S->g4, 1); S->prof.end(st);
-        float* t = gev2; gev2 = gev_in; gev_in = t;
-        S->n_launches += 2;
-      }
-    } else if (l > 0) {
+    if (l > 0) {
       SO3LR_CUDA_CHECK(cudaMemcpyAsync(gev_in, S->gev1, (size_t)n * kMTot * sizeof(float), cudaMemcpyDeviceToDevice, st));
       fill(st, S->g_qkv, (size_t)n * kProj, 0.f);
       S->prof.begin(kPAttnBwd, st); launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, g_dR, 0); S->prof.end(st);
@@ -344,6 +355,102 @@ int evaluate(so3lr_b200_system* S, cudaStream_t st, const float* R, const int* r
   }
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
+}
+
+// ---- positions -> forces (gather-only kernels on the symmetric short-range list) ----
+// Atom slots are ordered by how far their features are needed: [0, n0) atoms whose energy is evaluated here ("owned"),
+// [n0, n1) atoms within one interaction shell of them, [n1, n2) within two, [n2, n3) within three.  Layer l of the
+// network is evaluated for the atoms that the owned atoms' energies can still see; a single-GPU evaluation has
+// n0 = n1 = n2 = n3 = n.
+struct Shells { int n0, n1, n2, n3; };
+
+// network forward up to the output heads: e_nn, q_raw, hv for the owned atoms; ZBL energy and force; F is zeroed first
+int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const Shells& c, bool owned_side_only, float* F) {
+  const ModelDev& M = S->model->M;
+  const int* row_ptr = S->sr.row_ptr; const int* nbr_j = S->sr.nbr_j; const int* edge_i = S->sr.edge_i;
+  const int nrecv[kNumLayers] = {c.n2, c.n1, c.n0};   // receivers of layer l
+  const int nsend[kNumLayers] = {c.n3, c.n2, c.n1};   // atoms whose q/k/v rows layer l reads
+  fill(st, S->e_zbl, c.n0, 0.f);
+  fill(st, F, (size_t)c.n3 * 3, 0.f);
+  S->prof.begin(kPGeom, st);
+  launch_sr_geometry_zbl(st, M, S->cell, c.n3, S->sr.count, edge_i, nbr_j, S->d_Z, R, 0, S->dR, S->e_zbl, nullptr, nullptr, F,
+                         owned_side_only ? c.n0 : -1);
+  S->prof.end(st);
+  launch_embed(st, M, S->d_Z, c.n3, S->x[0]);
+  S->n_launches += 4;
+  for (int l = 0; l < kNumLayers; ++l) {
+    const LayerDev& L = M.layer[l];
+    S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], nsend[l], S->qkv[l]); S->prof.end(st);
+    S->prof.begin(kPAttnFwd, st);
+    launch_attn_fwd_sym(st, L, nrecv[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
+    S->prof.end(st);
+    S->prof.begin(kPPostFwd, st);
+    launch_atom_post_fwd(st, L, nrecv[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]);
+    S->prof.end(st);
+    S->n_launches += 3;
+  }
+  S->prof.begin(kPHeads, st);
+  launch_heads_fwd(st, M, c.n0, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv);
+  S->prof.end(st);
+  S->n_launches += 1;
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+// reverse pass from the cotangents of the heads (gq_raw, gh on the owned atoms; d/d e_nn = 1) to the forces, added into F
+int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float* F) {
+  const ModelDev& M = S->model->M;
+  const int* row_ptr = S->sr.row_ptr; const int* nbr_j = S->sr.nbr_j;
+  const int npost[kNumLayers] = {c.n2, c.n1, c.n0};   // atoms whose layer-l outputs carry a cotangent
+  const int nattn[kNumLayers] = {c.n3, c.n2, c.n1};   // atoms that receive a cotangent through layer l's attention
+  S->prof.begin(kPHeads, st);
+  launch_heads_bwd(st, M, c.n0, S->d_Z, S->ze, S->zq, S->zh, S->hv, S->ones, S->gq_raw, S->gh, S->g4);
+  S->prof.end(st);
+  float* gev2 = S->gev_a;
+  float* gev_in = S->gev_b;
+  fill(st, gev2, (size_t)c.n0 * kMTot, 0.f);
+  S->n_launches += 2;
+  for (int l = kNumLayers - 1; l >= 0; --l) {
+    const LayerDev& L = M.layer[l];
+    S->prof.begin(kPPostBwd, st);
+    launch_atom_post_bwd(st, L, npost[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, gev2, S->g_xa, S->gev1);
+    S->prof.end(st);
+    if (c.n3 > npost[l]) {   // atoms beyond the layer's receivers have no cotangent of their own (any of them can be a neighbour)
+      fill(st, S->g_xa + (size_t)npost[l] * kF, (size_t)(c.n3 - npost[l]) * kF, 0.f);
+      fill(st, S->gev1 + (size_t)npost[l] * kMTot, (size_t)(c.n3 - npost[l]) * kMTot, 0.f);
+    }
+    S->prof.begin(kPAttnBwd, st);
+    launch_attn_bwd_sym(st, L, nattn[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, F, l == 0 ? 1 : 0);
+    S->prof.end(st);
+    S->n_launches += 2;
+    if (l > 0) {
+      // dL/dx_in = g_xa (skip connection) + projections^T
+      SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)nattn[l] * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
+      S->prof.begin(kPProjBwd, st); launch_proj_bwd(st, L, S->g_qkv, nattn[l], S->g4, 1); S->prof.end(st);
+      float* t = gev2; gev2 = gev_in; gev_in = t;
+      S->n_launches += 2;
+    }
+  }
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+// single-device evaluation: all shells coincide; long-range pairs from the ordered (or half-weight) list with scatter
+int evaluate_fused(so3lr_b200_system* S, cudaStream_t st, const float* R, float* F) {
+  const int n = S->n;
+  const Shells c{n, n, n, n};
+  int rc = fused_forward(S, st, R, c, false, F);
+  if (rc) return rc;
+  fill(st, S->e_coul, n, 0.f); fill(st, S->e_disp, n, 0.f); fill(st, S->gq, n, 0.f); fill(st, S->gh, n, 0.f);
+  launch_charge_conserve(st, S->n_graphs, S->d_graph_start, S->q_raw, S->d_total_charge, S->hv, S->q, S->h);
+  S->prof.begin(kPPairLr, st);
+  launch_pair_lr(st, S->lr, S->cell, n, S->lrl.row_ptr, S->lrl.nbr_j, S->d_Z, R, S->q, S->h, 0, nullptr, nullptr, nullptr, F, S->gq, S->gh,
+                 S->e_coul, S->e_disp, nullptr);
+  S->prof.end(st);
+  combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom);
+  launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw);
+  S->n_launches += 8;
+  return fused_backward(S, st, c, F);
 }
 
 }  // namespace
@@ -412,7 +519,7 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
       }
   SO3LR_CUDA_CHECK(cudaSetDevice(model->device));
   so3lr_b200_system* S = new so3lr_b200_system();
-  S->model = model; S->n = n_atoms; S->n_graphs = n_graphs; S->opt = *options;
+  S->model = model; S->n = n_atoms; S->n_cap = n_atoms; S->n_graphs = n_graphs; S->opt = *options;
   int rc = make_cell(cell9, &S->cell);
   if (rc) { delete S; return rc; }
   // long-range constants
@@ -553,8 +660,7 @@ SO3LR_B200_API int so3lr_b200_system_compute(so3lr_b200_system* S, void* stream,
     gather_positions_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->d_perm, R, S->d_Rs);
     R_eval = S->d_Rs;
   }
-  rc = evaluate(S, st, R_eval, S->sr.row_ptr, S->sr.nbr_j, S->sr.edge_i, S->sr.count, S->lrl.row_ptr, S->lrl.nbr_j, 0, nullptr, nullptr,
-                nullptr, nullptr, nullptr, S->sorted ? S->F_s : Fout);
+  rc = evaluate_fused(S, st, R_eval, S->sorted ? S->F_s : Fout);
   if (rc) return rc;
   launch_graph_reduce(st, S->n_graphs, S->d_graph_start, S->e_atom, S->q, R_eval, S->d_energy, S->d_dipole);
   S->n_launches += 1;
@@ -646,8 +752,8 @@ SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* S, void* stre
   row_ptr_from_sorted_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(n, n_edges, idx_i, S->d_rowptr_g);
   row_ptr_from_sorted_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(n, n_pairs, idx_i_lr, S->d_rowptr_lr_g);
   S->n_launches += 2;
-  int rc = evaluate(S, st, nullptr, S->d_rowptr_g, idx_j, idx_i, n_edges, S->d_rowptr_lr_g, idx_j_lr, 1, edges, edges_lr, g_edges,
-                    g_edges_lr, g_e_atom, nullptr);
+  int rc = evaluate_graph(S, st, S->d_rowptr_g, idx_j, idx_i, n_edges, S->d_rowptr_lr_g, idx_j_lr, edges, edges_lr, g_edges, g_edges_lr,
+                          g_e_atom);
   if (rc) return rc;
   if (e_atom) SO3LR_CUDA_CHECK(cudaMemcpyAsync(e_atom, S->e_atom, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
   if (charges) SO3LR_CUDA_CHECK(cudaMemcpyAsync(charges, S->q, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
@@ -668,6 +774,89 @@ SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* S, void* stream, int
     vv_second_kernel<<<blocks, 256, 0, st>>>(n, dt, masses, V, F);
     S->n_launches += 2;
   }
+  return kOk;
+}
+
+// ---- domain-decomposed evaluation (one context per rank; halo exchange is the caller's job) ----
+SO3LR_B200_API int so3lr_b200_dd_set_atoms(so3lr_b200_system* S, int n_local, const int32_t* shells4, const int32_t* Z_local_dev,
+                                           const float* cell9) {
+  if (!S || !shells4 || !Z_local_dev || n_local <= 0) return kInvalidArgument;
+  if (S->n_graphs != 1) return kInvalidArgument;
+  if (n_local > S->n_cap) return kTooLarge;
+  if (!(shells4[0] > 0 && shells4[0] <= shells4[1] && shells4[1] <= shells4[2] && shells4[2] <= shells4[3] && shells4[3] == n_local))
+    return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  int rc = make_cell(cell9, &S->cell);
+  if (rc) return rc;
+  S->n = n_local;
+  for (int k = 0; k < 4; ++k) S->shells[k] = shells4[k];
+  SO3LR_CUDA_CHECK(cudaMemcpy(S->d_Z0, Z_local_dev, (size_t)n_local * sizeof(int), cudaMemcpyDeviceToDevice));
+  const int gs[2] = {0, n_local};
+  SO3LR_CUDA_CHECK(cudaMemcpy(S->d_graph_start, gs, sizeof(gs), cudaMemcpyHostToDevice));
+  S->d_Z = S->d_Z0; S->sorted = false; S->have_lists = false;
+  S->o_e_atom = S->e_atom; S->o_q = S->q; S->o_h = S->h; S->o_zbl = S->e_zbl; S->o_coul = S->e_coul; S->o_disp = S->e_disp;
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_dd_forward(so3lr_b200_system* S, void* stream, const float* R_local_dev, float* q_raw_owned_dev,
+                                         float* h_owned_dev) {
+  if (!S || !R_local_dev || !q_raw_owned_dev || !h_owned_dev || S->shells[3] != S->n || S->n <= 0) return kInvalidArgument;
+  if (!(S->opt.cutoff_lr > 0.f)) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  const Shells c{S->shells[0], S->shells[1], S->shells[2], S->shells[3]};
+  if (!S->have_lists) {
+    S->prof.begin(kPNlist, st);
+    // short range: rows for every local atom (the reverse pass walks all of them); long range: rows of the owned atoms
+    // only, both directions
+    int rc = nlist_build(S->nws, st, S->cell, S->n, R_local_dev, kCutoffSr + S->opt.skin, 0, nullptr, nullptr, &S->sr, 1, nullptr);
+    if (rc) return rc;
+    rc = nlist_build(S->nws, st, S->cell, S->n, R_local_dev, S->opt.cutoff_lr + S->opt.skin, 0, nullptr, nullptr, &S->lrl, 1, nullptr, c.n0);
+    if (rc) return rc;
+    rc = ensure_edge_buffers(S, S->sr.count);
+    if (rc) return rc;
+    S->prof.end(st);
+    S->have_lists = true;
+    S->n_rebuilds++;
+    S->n_launches += 12;
+  }
+  int rc = fused_forward(S, st, R_local_dev, c, true, S->F_s);
+  if (rc) return rc;
+  SO3LR_CUDA_CHECK(cudaMemcpyAsync(q_raw_owned_dev, S->q_raw, (size_t)c.n0 * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  abs_kernel<<<(c.n0 + 255) / 256, 256, 0, st>>>(c.n0, S->hv, h_owned_dev);
+  S->n_launches += 1;
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_dd_pair(so3lr_b200_system* S, void* stream, const float* R_local_dev, const float* q_local_dev,
+                                      const float* h_local_dev, double* gq_sum_dev) {
+  if (!S || !R_local_dev || !q_local_dev || !h_local_dev || !gq_sum_dev || !S->have_lists) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  const int n0 = S->shells[0];
+  S->prof.begin(kPPairLr, st);
+  launch_pair_lr_owned(st, S->lr, S->cell, n0, S->n, S->lrl.row_ptr, S->lrl.nbr_j, S->d_Z, R_local_dev, q_local_dev, h_local_dev, S->F_s,
+                       S->gq, S->gh, S->e_coul, S->e_disp);
+  S->prof.end(st);
+  sum_to_double_kernel<<<1, 1024, 0, st>>>(n0, S->gq, gq_sum_dev);
+  S->n_launches += 2;
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_dd_backward(so3lr_b200_system* S, void* stream, const double* gq_sum_all_dev, int64_t n_atoms_all,
+                                          float* F_local_dev, double* energy_owned_dev) {
+  if (!S || !F_local_dev || !gq_sum_all_dev || n_atoms_all <= 0 || !S->have_lists) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  const Shells c{S->shells[0], S->shells[1], S->shells[2], S->shells[3]};
+  subtract_mean_kernel<<<(c.n0 + 255) / 256, 256, 0, st>>>(c.n0, S->gq, gq_sum_all_dev, (double)n_atoms_all, S->gq_raw);
+  combine_energy_kernel<<<(c.n0 + 255) / 256, 256, 0, st>>>(c.n0, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom);
+  if (energy_owned_dev) sum_to_double_kernel<<<1, 1024, 0, st>>>(c.n0, S->e_atom, energy_owned_dev);
+  S->n_launches += 3;
+  int rc = fused_backward(S, st, c, S->F_s);
+  if (rc) return rc;
+  SO3LR_CUDA_CHECK(cudaMemcpyAsync(F_local_dev, S->F_s, (size_t)c.n3 * 3 * sizeof(float), cudaMemcpyDeviceToDevice, st));
   return kOk;
 }
 

@@ -36,9 +36,10 @@ void launch_attn_bwd(cudaStream_t s, const LayerDev& L, int n, const int* row_pt
 // dR_ji = -dR_ij), which the cell-list builder guarantees.  The backward kernel writes g_qkv / gev_in rows completely
 // (no pre-fill needed; gev_in includes the skip term gev1) and adds the attention part of the force on atom i to F[i].
 int configure_attention_sym_kernels();
-void launch_attn_fwd_sym(cudaStream_t s, const LayerDev& L, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+// n_recv: rows 0 .. n_recv-1 are evaluated (receivers); n: number of atoms a neighbour index may address.
+void launch_attn_fwd_sym(cudaStream_t s, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
                          const float* qkv, const float* x_in, const float* ev_in, float* xa, float* ev1);
-void launch_attn_bwd_sym(cudaStream_t s, const LayerDev& L, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+void launch_attn_bwd_sym(cudaStream_t s, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
                          const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv, float* gev_in,
                          float* F, int first_layer);
 
@@ -48,7 +49,7 @@ void launch_attn_bwd_sym(cudaStream_t s, const LayerDev& L, int n, const int* ro
 // F_j -= g).  With `dR_given` the displacements are inputs.
 void launch_sr_geometry_zbl(cudaStream_t s, const ModelDev& M, const Cell& cell, int n, long long n_edges, const int* edge_i,
                             const int* nbr_j, const int* Z, const float* R, int dR_given, float* dR, float* e_atom, float* g_dR,
-                            const float* ge, float* F_direct);
+                            const float* ge, float* F_direct, int n_owned = -1);
 // F[i] += g, F[j] -= g for every edge
 void launch_force_scatter(cudaStream_t s, int n, long long n_edges, const int* edge_i, const int* nbr_j, const float* g_dR,
                           float* F);
@@ -58,6 +59,12 @@ void launch_pair_lr(cudaStream_t s, const LrParams& P, const Cell& cell, int n, 
                     const int* Z, const float* R, const float* q, const float* h, int mode, const float* dR_lr,
                     float* g_dR_lr, float* e_atom, float* F, float* gq, float* gh, float* e_coul, float* e_disp,
                     const float* ge);
+// Domain-decomposed variant: rows 0 .. n_owned-1 of a full (both directions) list; every pair energy is booked half on
+// the row atom, and only the derivatives that land on the row atom are produced, at full weight: F[i], gq[i], gh[i],
+// e_coul[i], e_disp[i] are written (not accumulated) by the row's warp -- no atomics.
+void launch_pair_lr_owned(cudaStream_t s, const LrParams& P, const Cell& cell, int n_owned, int n, const int* row_ptr,
+                          const int* nbr_j, const int* Z, const float* R, const float* q, const float* h, float* F_add,
+                          float* gq, float* gh, float* e_coul, float* e_disp);
 // q = q_raw + (Q_g - sum_g q_raw) / n_g ; h = |hv| ; and the transposed operation for the cotangents
 // (atoms of one graph are contiguous: graph g owns atoms graph_start[g] .. graph_start[g+1]-1)
 void launch_charge_conserve(cudaStream_t s, int n_graphs, const int* graph_start, const float* q_raw,
@@ -70,6 +77,7 @@ void launch_graph_reduce(cudaStream_t s, int n_graphs, const int* graph_start, c
 // ---- nlist.cu ----
 struct NeighborListDev {
   int* row_ptr = nullptr;    // n + 1
+  int row_cap = 0;           // allocated entries of row_ptr
   int* nbr_j = nullptr;      // capacity
   int* edge_i = nullptr;     // capacity
   long long capacity = 0;
@@ -83,7 +91,8 @@ void nlist_workspace_destroy(NlistWorkspace*);
 int spatial_order(NlistWorkspace* ws, cudaStream_t s, const Cell& cell, int n, const float* R, float cell_size, int* perm);
 // Builds rows for all i.  ordered: keep j > i only.  seg/graph_start (optional): pairs only inside one graph and the
 // candidate loop runs over the graph's atoms.  Grows `out` when `allow_grow`, otherwise sets *overflow (device int).
+// n_rows >= 0: only the rows of atoms 0 .. n_rows-1 are built (candidates are still all n atoms).
 int nlist_build(NlistWorkspace* ws, cudaStream_t s, const Cell& cell, int n, const float* R, float r_list, int ordered,
-                const int* seg, const int* graph_start, NeighborListDev* out, int allow_grow, int* d_overflow);
+                const int* seg, const int* graph_start, NeighborListDev* out, int allow_grow, int* d_overflow, int n_rows = -1);
 
 }  // namespace so3lr

@@ -255,8 +255,9 @@ int spatial_order(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, co
 }
 
 int nlist_build(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, const float* R, float r_list, int ordered,
-                const int* seg, const int* graph_start, NeighborListDev* out, int allow_grow, int* d_overflow) {
+                const int* seg, const int* graph_start, NeighborListDev* out, int allow_grow, int* d_overflow, int n_rows) {
   if (n <= 0) { out->count = 0; return kOk; }
+  if (n_rows < 0 || n_rows > n) n_rows = n;
   if (n > w->n_cap) {
     int st;
     if ((st = ensure(&w->cell_of, n))) return st;
@@ -270,7 +271,12 @@ int nlist_build(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, cons
     SO3LR_CUDA_CHECK(cudaMalloc((void**)&w->d_total, sizeof(long long)));
     SO3LR_CUDA_CHECK(cudaMallocHost((void**)&w->h_total, sizeof(long long)));
   }
-  if (!out->row_ptr) SO3LR_CUDA_CHECK(cudaMalloc((void**)&out->row_ptr, ((size_t)n + 1) * sizeof(int)));
+  if (n + 1 > out->row_cap) {
+    if (out->row_ptr) cudaFree(out->row_ptr);
+    out->row_ptr = nullptr;
+    SO3LR_CUDA_CHECK(cudaMalloc((void**)&out->row_ptr, ((size_t)n + 1) * sizeof(int)));
+    out->row_cap = n + 1;
+  }
   const float r2max = r_list * r_list;
   const bool by_graph = graph_start != nullptr && !cell.periodic;
   Grid G{};
@@ -317,7 +323,7 @@ int nlist_build(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, cons
     size_t need = 0;
     cub::DeviceRadixSort::SortPairs(nullptr, need, w->cell_of, w->cell_sorted, w->atom_iota, w->atom_sorted, n, 0, bits, s);
     size_t need2 = 0;
-    cub::DeviceScan::ExclusiveSum(nullptr, need2, w->row_count, out->row_ptr, n, s);
+    cub::DeviceScan::ExclusiveSum(nullptr, need2, w->row_count, out->row_ptr, n, s);   // sized for the largest row count
     if (need2 > need) need = need2;
     if (need > w->cub_bytes) {
       if (w->cub_tmp) cudaFree(w->cub_tmp);
@@ -336,15 +342,16 @@ int nlist_build(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, cons
       w->cub_bytes = need;
     }
   }
-  const int blocks = (n + 7) / 8;
+  const int blocks = (n_rows + 7) / 8;
+  if (n_rows == 0) { out->count = 0; return kOk; }
   if (by_graph)
-    build_rows_graph_kernel<false><<<blocks, 256, 0, s>>>(n, R, r2max, ordered, seg, graph_start, w->row_count, nullptr, nullptr, nullptr, 0);
+    build_rows_graph_kernel<false><<<blocks, 256, 0, s>>>(n_rows, R, r2max, ordered, seg, graph_start, w->row_count, nullptr, nullptr, nullptr, 0);
   else
-    build_rows_kernel<false><<<blocks, 256, 0, s>>>(cell, G, n, R, r2max, ordered, seg, w->atom_sorted, w->cell_start,
+    build_rows_kernel<false><<<blocks, 256, 0, s>>>(cell, G, n_rows, R, r2max, ordered, seg, w->atom_sorted, w->cell_start,
                                                     w->row_count, nullptr, nullptr, nullptr, 0);
   size_t tmp = w->cub_bytes;
-  cub::DeviceScan::ExclusiveSum(w->cub_tmp, tmp, w->row_count, out->row_ptr, n, s);
-  finish_scan_kernel<<<1, 32, 0, s>>>(n, w->row_count, out->row_ptr, w->d_total, out->capacity, allow_grow ? nullptr : d_overflow);
+  cub::DeviceScan::ExclusiveSum(w->cub_tmp, tmp, w->row_count, out->row_ptr, n_rows, s);
+  finish_scan_kernel<<<1, 32, 0, s>>>(n_rows, w->row_count, out->row_ptr, w->d_total, out->capacity, allow_grow ? nullptr : d_overflow);
   SO3LR_CUDA_CHECK(cudaMemcpyAsync(w->h_total, w->d_total, sizeof(long long), cudaMemcpyDeviceToHost, s));
   SO3LR_CUDA_CHECK(cudaStreamSynchronize(s));
   const long long total = *w->h_total;
@@ -365,12 +372,12 @@ int nlist_build(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, cons
   if (total <= out->capacity) out->count = total;
   const bool truncated = total > out->capacity;
   if (by_graph)
-    build_rows_graph_kernel<true><<<blocks, 256, 0, s>>>(n, R, r2max, ordered, seg, graph_start, nullptr, out->row_ptr,
+    build_rows_graph_kernel<true><<<blocks, 256, 0, s>>>(n_rows, R, r2max, ordered, seg, graph_start, nullptr, out->row_ptr,
                                                          out->nbr_j, out->edge_i, out->capacity);
   else
-    build_rows_kernel<true><<<blocks, 256, 0, s>>>(cell, G, n, R, r2max, ordered, seg, w->atom_sorted, w->cell_start, nullptr,
+    build_rows_kernel<true><<<blocks, 256, 0, s>>>(cell, G, n_rows, R, r2max, ordered, seg, w->atom_sorted, w->cell_start, nullptr,
                                                    out->row_ptr, out->nbr_j, out->edge_i, out->capacity);
-  if (truncated) clamp_rows_kernel<<<(n + 1 + 255) / 256, 256, 0, s>>>(n, out->row_ptr, out->capacity);
+  if (truncated) clamp_rows_kernel<<<(n_rows + 1 + 255) / 256, 256, 0, s>>>(n_rows, out->row_ptr, out->capacity);
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return truncated ? kOverflow : kOk;
 }

@@ -9,7 +9,7 @@ namespace {
 __global__ void sr_geometry_zbl_kernel(ZblParams zbl, Cell cell, int n, long long n_edges, const int* __restrict__ edge_i,
                                        const int* __restrict__ nbr_j, const int* __restrict__ Z, const float* __restrict__ R,
                                        int dR_given, float* __restrict__ dR, float* __restrict__ e_atom,
-                                       float* __restrict__ g_dR, const float* __restrict__ ge, float* __restrict__ F_direct) {
+                                       float* __restrict__ g_dR, const float* __restrict__ ge, float* __restrict__ F_direct, int n_owned) {
   long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= n_edges) return;
   const int i = edge_i[e], j = nbr_j[e];
@@ -28,7 +28,9 @@ __global__ void sr_geometry_zbl_kernel(ZblParams zbl, Cell cell, int n, long lon
   }
   float gx = 0.f, gy = 0.f, gz = 0.f;
   const float r2 = dx * dx + dy * dy + dz * dz;
-  if (valid && r2 > 0.f && r2 < kZblSwitchOff * kZblSwitchOff) {
+  // n_owned >= 0: only the edges of owned receivers carry energy, and the receiver takes the pair's whole force
+  // (the reversed edge belongs to the other atom's owner)
+  if (valid && r2 > 0.f && r2 < kZblSwitchOff * kZblSwitchOff && (n_owned < 0 || i < n_owned)) {
     const float r = sqrtf(r2);
     float cut, dcut, ez, dez;
     phys_cutoff(r, cut, dcut);
@@ -37,8 +39,11 @@ __global__ void sr_geometry_zbl_kernel(ZblParams zbl, Cell cell, int n, long lon
     const float s = (ge ? ge[i] : 1.f) * dez / r;
     gx = s * dx; gy = s * dy; gz = s * dz;
     if (F_direct) {   // only edges shorter than 1.5 A get here: a handful per atom
-      atomicAdd(F_direct + 3 * (size_t)i, gx); atomicAdd(F_direct + 3 * (size_t)i + 1, gy); atomicAdd(F_direct + 3 * (size_t)i + 2, gz);
-      atomicAdd(F_direct + 3 * (size_t)j, -gx); atomicAdd(F_direct + 3 * (size_t)j + 1, -gy); atomicAdd(F_direct + 3 * (size_t)j + 2, -gz);
+      const float wi = n_owned >= 0 ? 2.f : 1.f;
+      atomicAdd(F_direct + 3 * (size_t)i, wi * gx); atomicAdd(F_direct + 3 * (size_t)i + 1, wi * gy); atomicAdd(F_direct + 3 * (size_t)i + 2, wi * gz);
+      if (n_owned < 0) {
+        atomicAdd(F_direct + 3 * (size_t)j, -gx); atomicAdd(F_direct + 3 * (size_t)j + 1, -gy); atomicAdd(F_direct + 3 * (size_t)j + 2, -gz);
+      }
     }
   }
   if (g_dR) { g_dR[3 * e] = gx; g_dR[3 * e + 1] = gy; g_dR[3 * e + 2] = gz; }
@@ -128,6 +133,49 @@ __global__ void __launch_bounds__(256) pair_lr_kernel(LrParams P, Cell cell, int
   }
 }
 
+// owned rows of a full list: i-side derivatives only, no atomics
+__global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cell, int n_owned, int n, const int* __restrict__ row_ptr,
+                                                            const int* __restrict__ nbr_j, const int* __restrict__ Z,
+                                                            const float* __restrict__ R, const float* __restrict__ q,
+                                                            const float* __restrict__ h, float* __restrict__ F_add,
+                                                            float* __restrict__ gq, float* __restrict__ gh, float* __restrict__ e_coul,
+                                                            float* __restrict__ e_disp) {
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (i >= n_owned) return;
+  const int e0 = row_ptr[i], e1 = row_ptr[i + 1];
+  const float qi = q[i], hi = h[i];
+  const int Zi = Z[i];
+  const float xi = R[3 * (size_t)i], yi = R[3 * (size_t)i + 1], zi = R[3 * (size_t)i + 2];
+  float ec = 0.f, ed = 0.f, fx = 0.f, fy = 0.f, fz = 0.f, gqi = 0.f, ghi = 0.f;
+  for (int e = e0 + lane; e < e1; e += 32) {
+    const int j = nbr_j[e];
+    if (j < 0 || j >= n) continue;
+    float dx = R[3 * (size_t)j] - xi, dy = R[3 * (size_t)j + 1] - yi, dz = R[3 * (size_t)j + 2] - zi;
+    min_image(cell, dx, dy, dz);
+    const float r2 = dx * dx + dy * dy + dz * dz;
+    if (!(r2 > 0.f) || (P.has_cutoff && r2 >= P.rc * P.rc)) continue;
+    const float r = sqrtf(r2);
+    float chi, dchi;
+    coulomb_chi(P, r, chi, dchi);
+    const float qj = q[j], hj = h[j];
+    float e_d, dd_dr, dd_dhi, dd_dhj;
+    dispersion_pair(P, r, Zi, Z[j], hi, hj, e_d, dd_dr, dd_dhi, dd_dhj);
+    ec = fmaf(0.5f * kKe * qi * qj, chi, ec);
+    ed += 0.5f * e_d;
+    gqi = fmaf(kKe * qj, chi, gqi);
+    ghi += dd_dhi;
+    const float s = (kKe * qi * qj * dchi + dd_dr) / r;   // dE_ij/d(dR), dR = R_j - R_i; F_i = +that
+    fx = fmaf(s, dx, fx); fy = fmaf(s, dy, fy); fz = fmaf(s, dz, fz);
+  }
+  ec = warp_sum(ec); ed = warp_sum(ed); gqi = warp_sum(gqi); ghi = warp_sum(ghi);
+  fx = warp_sum(fx); fy = warp_sum(fy); fz = warp_sum(fz);
+  if (lane == 0) {
+    e_coul[i] = ec; e_disp[i] = ed; gq[i] = gqi; gh[i] = ghi;
+    F_add[3 * (size_t)i] += fx; F_add[3 * (size_t)i + 1] += fy; F_add[3 * (size_t)i + 2] += fz;
+  }
+}
+
 // one CTA per graph: q = q_raw + (Q - sum q_raw) / n_g ; h = |hv|
 __global__ void charge_conserve_kernel(int n_graphs, const int* __restrict__ graph_start, const float* __restrict__ q_raw,
                                        const float* __restrict__ total_charge, const float* __restrict__ hv,
@@ -208,10 +256,10 @@ __global__ void graph_reduce_kernel(int n_graphs, const int* __restrict__ graph_
 
 void launch_sr_geometry_zbl(cudaStream_t s, const ModelDev& M, const Cell& cell, int n, long long n_edges, const int* edge_i,
                             const int* nbr_j, const int* Z, const float* R, int dR_given, float* dR, float* e_atom, float* g_dR, const float* ge,
-                            float* F_direct) {
+                            float* F_direct, int n_owned) {
   if (n_edges <= 0) return;
   unsigned blocks = (unsigned)((n_edges + 255) / 256);
-  sr_geometry_zbl_kernel<<<blocks, 256, 0, s>>>(M.zbl, cell, n, n_edges, edge_i, nbr_j, Z, R, dR_given, dR, e_atom, g_dR, ge, F_direct);
+  sr_geometry_zbl_kernel<<<blocks, 256, 0, s>>>(M.zbl, cell, n, n_edges, edge_i, nbr_j, Z, R, dR_given, dR, e_atom, g_dR, ge, F_direct, n_owned);
 }
 
 void launch_force_scatter(cudaStream_t s, int n, long long n_edges, const int* edge_i, const int* nbr_j, const float* g_dR, float* F) {
@@ -229,6 +277,13 @@ void launch_pair_lr(cudaStream_t s, const LrParams& P, const Cell& cell, int n, 
     pair_lr_kernel<0><<<blocks, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, Z, R, q, h, dR_lr, g_dR_lr, e_atom, F, gq, gh, e_coul, e_disp, ge);
   else
     pair_lr_kernel<1><<<blocks, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, Z, R, q, h, dR_lr, g_dR_lr, e_atom, F, gq, gh, e_coul, e_disp, ge);
+}
+
+void launch_pair_lr_owned(cudaStream_t s, const LrParams& P, const Cell& cell, int n_owned, int n, const int* row_ptr,
+                          const int* nbr_j, const int* Z, const float* R, const float* q, const float* h, float* F_add,
+                          float* gq, float* gh, float* e_coul, float* e_disp) {
+  if (n_owned <= 0) return;
+  pair_lr_owned_kernel<<<(n_owned + 7) / 8, 256, 0, s>>>(P, cell, n_owned, n, row_ptr, nbr_j, Z, R, q, h, F_add, gq, gh, e_coul, e_disp);
 }
 
 void launch_charge_conserve(cudaStream_t s, int n_graphs, const int* graph_start, const float* q_raw,

@@ -1,0 +1,458 @@
+"""Spatial domain decomposition of one large periodic structure over several GPUs (one process per GPU).
+
+The box is cut into slabs along the lattice direction with the largest perpendicular width.  Every rank owns the atoms
+of its slab and keeps copies ("ghosts") of the atoms within three interaction shells of it (one shell = 4.5 A + skin;
+three shells also cover the 12 A + skin pair terms).  The library evaluates a rank's atoms in three phases
+(so3lr_b200_dd_forward / _pair / _backward); this module moves data between the ranks:
+
+  per step      positions of ghost atoms            owner -> holder   (send/recv)
+                sum of raw partial charges          all-reduce        (charge conservation)
+                charges and Hirshfeld ratios        owner -> holder   (send/recv)
+                sum of dE/dq                        all-reduce        (reverse of the charge conservation)
+                forces on ghost atoms               holder -> owner   (send/recv, added)
+  per rebuild   all positions and velocities        all-reduce of the scattered owned rows; every rank then selects its
+                                                    own atoms and ghosts, so atoms migrate without extra messages
+
+The reference has no multi-device path; the shells follow from its cutoffs (so3lr/potential.py:17-29).
+The numerical work is behind a small backend interface so that the bookkeeping can be tested on CPU ranks (gloo) with
+a stand-in model; `CudaBackend` is the real one.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+CUTOFF_SR = 4.5
+N_SHELLS = 3
+ACC_UNIT = 9.648533212331e-3      # eV / (A amu) -> A / fs^2
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# communicators
+# ----------------------------------------------------------------------------------------------------------------
+class DistComm:
+    """torch.distributed (NCCL on GPUs, gloo on CPU): one process per rank."""
+
+    def __init__(self):
+        import torch.distributed as dist
+        self.dist = dist
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+
+    def exchange(self, sends: Dict[int, torch.Tensor], recvs: Dict[int, torch.Tensor]):
+        """Send sends[p] to rank p and fill recvs[p] from rank p (every pair of ranks calls this with matching sizes)."""
+        ops = []
+        for p, t in sends.items():
+            if t.numel():
+                ops.append(self.dist.P2POp(self.dist.isend, t.contiguous(), p))
+        for p, t in recvs.items():
+            if t.numel():
+                ops.append(self.dist.P2POp(self.dist.irecv, t, p))
+        if ops:
+            for w in self.dist.batch_isend_irecv(ops):
+                w.wait()
+
+    def all_reduce_sum(self, t):
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return t
+
+    def all_reduce_max(self, t):
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t
+
+
+class ThreadWorld:
+    """Ranks as threads of one process (all on one device): the same driver code, used to test several domains on one GPU."""
+
+    def __init__(self, world):
+        self.world = world
+        self.barrier = threading.Barrier(world)
+        self.box: Dict = {}
+        self.lock = threading.Lock()
+
+    def comm(self, rank):
+        return ThreadComm(self, rank)
+
+
+class ThreadComm:
+    def __init__(self, world: ThreadWorld, rank: int):
+        self.w, self.rank, self.world = world, rank, world.world
+
+    def _sync(self):
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        self.w.barrier.wait()
+
+    def exchange(self, sends, recvs):
+        with self.w.lock:
+            for p, t in sends.items():
+                self.w.box[("x", self.rank, p)] = t.clone()
+        self._sync()
+        for p, t in recvs.items():
+            if t.numel():
+                t.copy_(self.w.box[("x", p, self.rank)])
+        self._sync()
+
+    def _reduce(self, t, op):
+        with self.w.lock:
+            self.w.box[("r", self.rank)] = t.clone()
+        self._sync()
+        parts = [self.w.box[("r", r)] for r in range(self.world)]
+        out = torch.stack(parts).sum(0) if op == "sum" else torch.stack(parts).amax(0)
+        self._sync()
+        t.copy_(out)
+        return t
+
+    def all_reduce_sum(self, t):
+        return self._reduce(t, "sum")
+
+    def all_reduce_max(self, t):
+        return self._reduce(t, "max")
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# geometry of the decomposition
+# ----------------------------------------------------------------------------------------------------------------
+def _spread3(v):
+    v = v & 0x3FF
+    v = (v | (v << 16)) & 0x030000FF
+    v = (v | (v << 8)) & 0x0300F00F
+    v = (v | (v << 4)) & 0x030C30C3
+    v = (v | (v << 2)) & 0x09249249
+    return v
+
+
+class SlabDecomposition:
+    """Slabs along one lattice direction of a periodic cell (rows = lattice vectors)."""
+
+    def __init__(self, cell, world: int, skin: float, cutoff_lr: float, axis: Optional[int] = None):
+        self.cell = np.asarray(cell, dtype=np.float64).reshape(3, 3)
+        self.inv = np.linalg.inv(self.cell)
+        widths = 1.0 / np.linalg.norm(self.inv, axis=0)
+        self.axis = int(np.argmax(widths)) if axis is None else int(axis)
+        self.width = float(widths[self.axis])
+        self.world = int(world)
+        self.shell = CUTOFF_SR + skin
+        self.lr_radius = cutoff_lr + skin
+        if N_SHELLS * self.shell < self.lr_radius:
+            raise ValueError("three short-range shells must cover the long-range list radius")
+        self.sf = self.shell / self.width                    # one shell in fractional units
+        if N_SHELLS * self.sf > 1.0:
+            raise ValueError("the cell is thinner than the halo along the decomposed direction")
+        self.bounds = np.arange(self.world + 1, dtype=np.float64) / self.world
+        self.ext = 1.0 / self.world + 2 * N_SHELLS * self.sf + (self.lr_radius + 1.0) / self.width
+
+    def local_cell(self):
+        c = self.cell.copy()
+        c[self.axis] = self.cell[self.axis] * self.ext
+        return c
+
+    def wrap(self, R):
+        """Positions wrapped into [0, 1) along the decomposed direction and that fractional coordinate (float64;
+        identical on all ranks because they hold identical R)."""
+        inv_col = torch.tensor(self.inv[:, self.axis], dtype=torch.float64, device=R.device)
+        a_vec = torch.tensor(self.cell[self.axis], dtype=torch.float64, device=R.device)
+        s = R.to(torch.float64) @ inv_col
+        k = torch.floor(s)
+        Rw = (R.to(torch.float64) - k[:, None] * a_vec).to(torch.float32)
+        s = Rw.to(torch.float64) @ inv_col
+        return Rw, s.clamp_(0.0, 1.0 - 1e-12)      # float32 rounding may leave s a hair outside [0, 1)
+
+    def owner(self, s):
+        b = torch.tensor(self.bounds, dtype=torch.float64, device=s.device)
+        return (torch.searchsorted(b, s, right=True) - 1).clamp_(0, self.world - 1)
+
+    def selection(self, rank: int, R, s):
+        """Atoms of `rank` in its local order: (global index, image shift along the axis, shell 0..3)."""
+        dev = R.device
+        lo, hi = float(self.bounds[rank]), float(self.bounds[rank + 1])
+        own = self.owner(s) == rank
+        idx = [torch.nonzero(own).squeeze(1)]
+        shift = [torch.zeros_like(idx[0])]
+        shell = [torch.zeros_like(idx[0])]
+        reach = N_SHELLS * self.sf
+        for k in (-1, 0, 1):
+            sp = s + k
+            for side in (0, 1):
+                d = (lo - sp) if side == 0 else (sp - hi)
+                m = (d > 0) & (d <= reach) if side == 0 else (d >= 0) & (d < reach)
+                if k == 0:
+                    m &= ~own
+                g = torch.nonzero(m).squeeze(1)
+                idx.append(g)
+                shift.append(torch.full_like(g, k))
+                shell.append((torch.floor(d[g] / self.sf).to(torch.int64) + 1).clamp_(1, N_SHELLS))
+        idx, shift, shell = torch.cat(idx), torch.cat(shift), torch.cat(shell)
+        # order: shell, then a Morton curve over cells of one shell width (keeps neighbours close in memory)
+        a_vec = torch.tensor(self.cell[self.axis], dtype=torch.float64, device=dev)
+        Rl = R[idx].to(torch.float64) + shift[:, None].to(torch.float64) * a_vec
+        sl = Rl @ torch.tensor(self.inv, dtype=torch.float64, device=dev)
+        sl[:, self.axis] = sl[:, self.axis] - (lo - reach)
+        for k in range(3):
+            if k != self.axis:
+                sl[:, k] = sl[:, k] - torch.floor(sl[:, k])
+        widths = torch.tensor(1.0 / np.linalg.norm(self.inv, axis=0), dtype=torch.float64, device=dev)
+        cells = torch.floor(sl * widths / self.shell).to(torch.int64).clamp_(0, 1023)
+        key = _spread3(cells[:, 0]) | (_spread3(cells[:, 1]) << 1) | (_spread3(cells[:, 2]) << 2)
+        order = torch.argsort(shell * (1 << 32) + key, stable=True)
+        return idx[order], shift[order], shell[order]
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# backends
+# ----------------------------------------------------------------------------------------------------------------
+class CudaBackend:
+    """The three evaluation phases of one rank through the C ABI (so3lr_b200_dd_*)."""
+
+    def __init__(self, cutoff_lr=12.0, damping=2.0, skin=1.0, device=0):
+        from .engine import Model
+        self.cutoff_lr, self.damping, self.skin = cutoff_lr, damping, skin
+        self.device = torch.device("cuda", device)
+        self.model = Model.default(device)
+        self.sys = None
+        self.capacity = 0
+
+    def _stream(self):
+        return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def set_atoms(self, Z_local, shells, cell_local):
+        from ._lib import check, lib
+        from .engine import System, _ptr
+        n = int(Z_local.numel())
+        if n > self.capacity:
+            self.sys = None
+            self.capacity = int(1.2 * n) + 1024
+            self.sys = System(np.ones(self.capacity, np.int32), np.asarray(cell_local), cutoff_lr=self.cutoff_lr, damping=self.damping,
+                              skin=self.skin, lr_format="sparse", model=self.model)
+        self.n, self.shells = n, [int(v) for v in shells]
+        sh = np.asarray(self.shells, dtype=np.int32)
+        c9 = np.ascontiguousarray(np.asarray(cell_local, dtype=np.float32).reshape(9))
+        Zl = Z_local.to(self.device, torch.int32).contiguous()
+        torch.cuda.current_stream(self.device).synchronize()
+        check(lib.so3lr_b200_dd_set_atoms(self.sys._h, n, _ptr(sh), _ptr(Zl), _ptr(c9)), "dd_set_atoms")
+
+    def forward(self, R_local):
+        from ._lib import check, lib
+        from .engine import _ptr
+        n0 = self.shells[0]
+        q = torch.empty(n0, device=self.device)
+        h = torch.empty(n0, device=self.device)
+        self._R = R_local.contiguous()
+        check(lib.so3lr_b200_dd_forward(self.sys._h, self._stream(), _ptr(self._R), _ptr(q), _ptr(h)), "dd_forward")
+        return q, h
+
+    def pair(self, q_local, h_local):
+        from ._lib import check, lib
+        from .engine import _ptr
+        s = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self._q, self._h = q_local.contiguous(), h_local.contiguous()
+        check(lib.so3lr_b200_dd_pair(self.sys._h, self._stream(), _ptr(self._R), _ptr(self._q), _ptr(self._h), _ptr(s)), "dd_pair")
+        return s
+
+    def backward(self, gq_sum_all, n_all):
+        from ._lib import check, lib
+        from .engine import _ptr
+        F = torch.empty(self.n, 3, device=self.device)
+        E = torch.zeros(1, dtype=torch.float64, device=self.device)
+        check(lib.so3lr_b200_dd_backward(self.sys._h, self._stream(), _ptr(gq_sum_all), int(n_all), _ptr(F), _ptr(E)), "dd_backward")
+        return F, E
+
+    def stats(self):
+        return self.sys.stats()
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# the driver of one rank
+# ----------------------------------------------------------------------------------------------------------------
+class DomainSystem:
+    """One rank's share of a periodic structure of `n_all` atoms.
+
+    At construction every rank passes the same global arrays (atomic numbers, positions, optionally velocities and
+    masses); afterwards each rank keeps only its own atoms and ghosts.  `compute()` returns the forces on the owned
+    atoms and the total energy; `nve()` integrates the owned atoms.  `gather_global()` reassembles global arrays.
+    """
+
+    def __init__(self, comm, backend, atomic_numbers, positions, cell, *, skin=1.0, cutoff_lr=12.0, total_charge=0.0,
+                 velocities=None, masses=None, device=None):
+        self.comm, self.backend = comm, backend
+        self.rank, self.world = comm.rank, comm.world
+        self.device = torch.device(device) if device is not None else torch.device("cpu")
+        self.geo = SlabDecomposition(cell, self.world, skin, cutoff_lr)
+        self.skin = skin
+        self.total_charge = float(total_charge)
+        self.Z_all = torch.as_tensor(np.asarray(atomic_numbers), dtype=torch.int32, device=self.device)
+        self.n_all = int(self.Z_all.numel())
+        self.m_all = None if masses is None else torch.as_tensor(np.asarray(masses), dtype=torch.float32, device=self.device)
+        R = torch.as_tensor(np.asarray(positions), dtype=torch.float32, device=self.device)
+        V = None if velocities is None else torch.as_tensor(np.asarray(velocities), dtype=torch.float32, device=self.device)
+        self.n_rebuilds = 0
+        self._partition(R, V)
+
+    # ---- partition / halo plans (all ranks hold identical R_all here) ----
+    def _partition(self, R_all, V_all):
+        geo, dev = self.geo, self.device
+        R_all, s = geo.wrap(R_all)
+        owner_all = geo.owner(s)
+        sel = [geo.selection(p, R_all, s) for p in range(self.world)]
+        idx, shift, shell = sel[self.rank]
+        self.gid, self.shift = idx, shift
+        counts = [int((shell <= k).sum()) for k in range(N_SHELLS + 1)]
+        self.n0, self.n_local = counts[0], counts[-1]
+        self.shells = counts
+        a_vec = torch.tensor(geo.cell[geo.axis], dtype=torch.float32, device=dev)
+        self.shift_vec = shift[:, None].to(torch.float32) * a_vec
+        self.R = (R_all[idx] + self.shift_vec).contiguous()
+        self.R_ref = self.R[: self.n0].clone()
+        self.V = None if V_all is None else V_all[idx[: self.n0]].contiguous()
+        self.m = None if self.m_all is None else self.m_all[idx[: self.n0]].contiguous()
+        # plans: recv_slots[p] = my ghost slots owned by p (my order); send_slots[p] = my owned slots that p holds as ghosts (p's order)
+        slot_of_gid = torch.full((self.n_all,), -1, dtype=torch.int64, device=dev)
+        slot_of_gid[idx[: self.n0]] = torch.arange(self.n0, device=dev)
+        ghost_owner = owner_all[idx[self.n0:]]
+        self.recv_slots, self.send_slots = {}, {}
+        for p in range(self.world):
+            self.recv_slots[p] = torch.nonzero(ghost_owner == p).squeeze(1) + self.n0
+            pidx, _, pshell = sel[p]
+            n0p = int((pshell == 0).sum())
+            pg = pidx[n0p:]
+            mine = owner_all[pg] == self.rank
+            self.send_slots[p] = slot_of_gid[pg[mine]]
+        self.backend.set_atoms(self.Z_all[idx], counts, geo.local_cell())
+        self.n_rebuilds += 1
+
+    # ---- halo traffic ----
+    def _halo_forward(self, owned_rows, local_out):
+        """owned_rows (n0, ...) -> fills ghost rows of local_out (n_local, ...) from their owners."""
+        tail = owned_rows.shape[1:]
+        sends = {p: owned_rows[sl] for p, sl in self.send_slots.items() if p != self.rank}
+        recvs = {p: torch.empty((sl.numel(),) + tail, dtype=owned_rows.dtype, device=self.device)
+                 for p, sl in self.recv_slots.items() if p != self.rank}
+        self.comm.exchange(sends, recvs)
+        local_out[: self.n0] = owned_rows
+        for p, buf in recvs.items():
+            local_out[self.recv_slots[p]] = buf
+        local_out[self.recv_slots[self.rank]] = owned_rows[self.send_slots[self.rank]]     # own periodic images
+        return local_out
+
+    def _halo_reverse_add(self, local_rows):
+        """local_rows (n_local, ...) -> owned rows plus what other ranks accumulated on their copies of my atoms."""
+        tail = local_rows.shape[1:]
+        sends = {p: local_rows[sl] for p, sl in self.recv_slots.items() if p != self.rank}
+        recvs = {p: torch.empty((sl.numel(),) + tail, dtype=local_rows.dtype, device=self.device)
+                 for p, sl in self.send_slots.items() if p != self.rank}
+        self.comm.exchange(sends, recvs)
+        out = local_rows[: self.n0].clone()
+        for p, buf in recvs.items():
+            out.index_add_(0, self.send_slots[p], buf)
+        out.index_add_(0, self.send_slots[self.rank], local_rows[self.recv_slots[self.rank]])
+        return out
+
+    # ---- evaluation ----
+    def _maybe_rebuild(self):
+        d2 = (self.R[: self.n0] - self.R_ref).square().sum(1).amax().reshape(1) if self.n0 else torch.zeros(1, device=self.device)
+        d2 = self.comm.all_reduce_max(d2.to(torch.float32))
+        if not torch.isfinite(d2).all():
+            raise RuntimeError("non-finite positions")
+        if float(d2) > (0.5 * self.skin) ** 2 or self.skin <= 0:
+            R_all = self.gather_global(self.R[: self.n0])
+            V_all = None if self.V is None else self.gather_global(self.V)
+            self._partition(R_all, V_all)
+            return True
+        return False
+
+    def compute(self, check_rebuild=True):
+        """Energy (float64 tensor, total over all ranks) and forces on the owned atoms (n0, 3)."""
+        if check_rebuild:
+            self._maybe_rebuild()
+        # ghost positions follow their owners
+        Rl = torch.empty_like(self.R)
+        self._halo_forward(self.R[: self.n0], Rl)
+        Rl += self.shift_vec
+        self.R = Rl
+        q_raw, h = self.backend.forward(self.R)
+        qsum = self.comm.all_reduce_sum(q_raw.sum(dtype=torch.float64).reshape(1))
+        q = q_raw + ((self.total_charge - qsum) / self.n_all).to(torch.float32)
+        qh = self._halo_forward(torch.stack([q, h], 1), torch.empty(self.n_local, 2, device=self.device))
+        gq_sum = self.comm.all_reduce_sum(self.backend.pair(qh[:, 0].contiguous(), qh[:, 1].contiguous()))
+        F_local, E_own = self.backend.backward(gq_sum, self.n_all)
+        self.F = self._halo_reverse_add(F_local)
+        self.E = self.comm.all_reduce_sum(E_own)
+        self.q, self.h = q, h
+        return self.E, self.F
+
+    def nve(self, n_steps, dt_fs):
+        """Velocity Verlet on the owned atoms (forces of the current positions must be in self.F)."""
+        s = (0.5 * dt_fs * ACC_UNIT / self.m)[:, None]
+        for _ in range(n_steps):
+            self.V += s * self.F
+            self.R[: self.n0] += dt_fs * self.V
+            self.compute()
+            s = (0.5 * dt_fs * ACC_UNIT / self.m)[:, None]      # ownership may have changed
+            self.V += s * self.F
+        return self.E
+
+    # ---- reassembly ----
+    def gather_global(self, owned_rows):
+        """Global (n_all, ...) array in the caller's atom order from the owned rows of every rank (a sum of disjoint
+        scatters, hence exact and identical on all ranks)."""
+        g = torch.zeros((self.n_all,) + owned_rows.shape[1:], dtype=owned_rows.dtype, device=self.device)
+        g[self.gid[: self.n0]] = owned_rows
+        return self.comm.all_reduce_sum(g)
+
+    def global_forces(self):
+        return self.gather_global(self.F)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# benchmark entry (called by bench.py under torchrun)
+# ----------------------------------------------------------------------------------------------------------------
+def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
+    import json
+    import torch.distributed as dist
+    from . import workloads as W
+    dev = torch.device("cuda", local_rank)
+    Z, R, cell = W.water_box(n_mol, box, seed)
+    V, m = W.maxwell_boltzmann(Z, 300.0, seed + 1)
+    N = len(Z)
+    comm = DistComm()
+    backend = CudaBackend(cutoff_lr=12.0, damping=2.0, skin=args.skin, device=local_rank)
+    dom = DomainSystem(comm, backend, Z, R, cell, skin=args.skin, cutoff_lr=12.0, velocities=V, masses=m, device=dev)
+    dom.compute(check_rebuild=False)
+    dt = 0.5
+    for _ in range(args.warmup):
+        dom.nve(1, dt)
+    torch.cuda.synchronize()
+    dist.barrier()
+    st0 = backend.stats()
+    rb0 = dom.n_rebuilds
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    ev[0].record()
+    for _ in range(args.steps):
+        dom.nve(1, dt)
+    ev[1].record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = torch.tensor([ev[0].elapsed_time(ev[1])], dtype=torch.float64, device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    launches = torch.tensor([backend.stats()["launches"] - st0["launches"]], dtype=torch.float64, device=dev)
+    dist.all_reduce(launches, op=dist.ReduceOp.SUM)
+    nloc = torch.tensor([dom.n_local, dom.n0], dtype=torch.float64, device=dev)
+    dist.all_reduce(nloc, op=dist.ReduceOp.SUM)
+    ms = float(ms)
+    if rank == 0:
+        value = N * args.steps / (ms * 1e-3)
+        line = {"metric": "atom-steps/s (E+F)", "value": round(value, 1), "unit": "atom-steps/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": f"{args.workload}: {N} atoms periodic water, cutoffs 4.5/12 A, skin {args.skin} A, NVE dt 0.5 fs from 300 K",
+                           "atoms": N, "decomposition": f"{world} slabs along axis {dom.geo.axis}, halo {N_SHELLS} x {dom.geo.shell:.1f} A",
+                           "local_atoms_sum_over_ranks": int(nloc[0]), "rebuilds_in_timed_steps": dom.n_rebuilds - rb0,
+                           "l2_policy": "inputs larger than L2" if N / world > 200000 else "inputs smaller than L2; no flush",
+                           "ns_per_day": round(args.steps / (ms * 1e-3) * 0.0432, 3)},
+                "e2e": None, "gpu_launches": int(launches), "clocks": None, "roofline": None, "cpu_baseline": None}
+        print(json.dumps(line), flush=True)
