@@ -121,6 +121,7 @@ def run_b200(args, rank, world, local_rank):
     n_mol, box, seed = WORKLOADS[args.workload]
     if world > 1:
         from so3lr_b200 import domain
+        args.clock_sampler, args.algorithmic_bytes, args.peaks = ClockSampler, algorithmic_bytes, _peaks
         return domain.bench_entry(args, rank, world, local_rank, n_mol, box, seed)
 
     Z, R, cell = W.water_box(n_mol, box, seed)

@@ -296,7 +296,9 @@ class DomainSystem:
     # ---- partition / halo plans (all ranks hold identical R_all here) ----
     def _partition(self, R_all, V_all):
         geo, dev = self.geo, self.device
+        R_in = R_all
         R_all, s = geo.wrap(R_all)
+        self.wrap_vec = R_in - R_all          # lattice translation that brought every atom into the cell
         owner_all = geo.owner(s)
         sel = [geo.selection(p, R_all, s) for p in range(self.world)]
         idx, shift, shell = sel[self.rank]
@@ -374,6 +376,40 @@ class DomainSystem:
         self._halo_forward(self.R[: self.n0], Rl)
         Rl += self.shift_vec
         self.R = Rl
+        return self._evaluate()
+
+    def compute_host(self, R_all_host):
+        """The call of a host application that keeps all positions in host memory: (n_all, 3) float32 positions in the
+        caller's atom order go in (every rank passes the same array), total energy and (n_all, 3) forces come back as
+        numpy arrays.  Each rank uploads the positions, picks its own atoms and ghosts (no position halo exchange is
+        needed), evaluates, and the forces are summed over the ranks."""
+        Rh = torch.as_tensor(np.ascontiguousarray(R_all_host, dtype=np.float32))
+        if self.device.type == "cuda":
+            if getattr(self, "_pin", None) is None or self._pin.shape != Rh.shape:
+                self._pin = torch.empty_like(Rh).pin_memory()
+                self._pin_F = torch.empty_like(Rh).pin_memory()
+            self._pin.copy_(Rh)
+            R_all = self._pin.to(self.device, non_blocking=True)
+        else:
+            R_all = Rh.clone()
+        ref = getattr(self, "_R_all_ref", None)
+        moved = True
+        if ref is not None and self.skin > 0:
+            moved = bool(((R_all - ref).square().sum(1).amax() > (0.5 * self.skin) ** 2).item())   # identical on all ranks
+        if moved:
+            self._R_all_ref = R_all.clone()
+            self._partition(R_all, None)
+        else:
+            self.R = (R_all[self.gid] - self.wrap_vec[self.gid] + self.shift_vec).contiguous()
+        E, _ = self._evaluate()
+        F_all = self.global_forces()
+        if self.device.type == "cuda":
+            self._pin_F.copy_(F_all, non_blocking=True)
+            torch.cuda.current_stream(self.device).synchronize()
+            return float(E), self._pin_F.numpy()
+        return float(E), F_all.numpy()
+
+    def _evaluate(self):
         q_raw, h = self.backend.forward(self.R)
         qsum = self.comm.all_reduce_sum(q_raw.sum(dtype=torch.float64).reshape(1))
         q = q_raw + ((self.total_charge - qsum) / self.n_all).to(torch.float32)
@@ -413,6 +449,7 @@ class DomainSystem:
 # ----------------------------------------------------------------------------------------------------------------
 def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
     import json
+    import time
     import torch.distributed as dist
     from . import workloads as W
     dev = torch.device("cuda", local_rank)
@@ -430,6 +467,8 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
     dist.barrier()
     st0 = backend.stats()
     rb0 = dom.n_rebuilds
+    sampler = args.clock_sampler(local_rank)
+    sampler.start()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     ev[0].record()
     for _ in range(args.steps):
@@ -437,6 +476,7 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
     ev[1].record()
     torch.cuda.synchronize()
     dist.barrier()
+    clocks = sampler.stop()
     ms = torch.tensor([ev[0].elapsed_time(ev[1])], dtype=torch.float64, device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     launches = torch.tensor([backend.stats()["launches"] - st0["launches"]], dtype=torch.float64, device=dev)
@@ -444,15 +484,56 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
     nloc = torch.tensor([dom.n_local, dom.n0], dtype=torch.float64, device=dev)
     dist.all_reduce(nloc, op=dist.ReduceOp.SUM)
     ms = float(ms)
+    rebuilds = dom.n_rebuilds - rb0
+    # kernel times of rank 0's share over another K steps
+    backend.sys.profile(True)
+    for _ in range(args.steps):
+        dom.nve(1, dt)
+    prof = backend.sys.profile_read()
+    backend.sys.profile(False)
+    st = backend.stats()
+    # end to end with host buffers: every rank uploads all positions, forces come back summed over the ranks
+    Rh = dom.gather_global(dom.R[: dom.n0]).cpu().numpy()
+    Vh = dom.gather_global(dom.V).cpu().numpy()
+    acc = (0.5 * dt * ACC_UNIT / m).astype(np.float32)[:, None]
+    _, Fh = dom.compute_host(Rh)
+    Fh = Fh.copy()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        Vh += acc * Fh
+        Rh += dt * Vh
+        _, Fh = dom.compute_host(Rh)
+        Vh += acc * Fh
+    torch.cuda.synchronize()
+    dist.barrier()
+    t_e2e = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+    dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
+    t_e2e = float(t_e2e)
     if rank == 0:
         value = N * args.steps / (ms * 1e-3)
+        groups = {k: v for k, v in prof.items() if v[1] > 0}
+        top = max((g for g in groups if args.algorithmic_bytes(g, dom.n_local, st["edges"], st["pairs"])), key=lambda g: groups[g][0])
+        t_launch = groups[top][0] / groups[top][1]
+        ab = args.algorithmic_bytes(top, dom.n_local, st["edges"], st["pairs"])
+        peak, kind = args.peaks()
+        ach = ab / (t_launch * 1e-3) / 1e9
+        roofline = {"kernel": top, "bound": "hbm", "achieved": round(ach, 1), "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s",
+                    "frac": round(ach / peak, 4), "traffic": args.traffic, "algorithmic_bytes_per_launch": ab,
+                    "ms_per_launch": round(t_launch, 4), "scope": "rank 0's sub-box (local atoms incl. ghosts)",
+                    "groups_ms_per_step": {g: round(v[0] / args.steps, 4) for g, v in sorted(groups.items(), key=lambda kv: -kv[1][0])}}
         line = {"metric": "atom-steps/s (E+F)", "value": round(value, 1), "unit": "atom-steps/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": f"{args.workload}: {N} atoms periodic water, cutoffs 4.5/12 A, skin {args.skin} A, NVE dt 0.5 fs from 300 K",
                            "atoms": N, "decomposition": f"{world} slabs along axis {dom.geo.axis}, halo {N_SHELLS} x {dom.geo.shell:.1f} A",
-                           "local_atoms_sum_over_ranks": int(nloc[0]), "rebuilds_in_timed_steps": dom.n_rebuilds - rb0,
+                           "local_atoms_sum_over_ranks": int(nloc[0]), "list_rebuilds_in_timed_steps": rebuilds,
                            "l2_policy": "inputs larger than L2" if N / world > 200000 else "inputs smaller than L2; no flush",
                            "ns_per_day": round(args.steps / (ms * 1e-3) * 0.0432, 3)},
-                "e2e": None, "gpu_launches": int(launches), "clocks": None, "roofline": None, "cpu_baseline": None}
+                "e2e": {"value": round(N * args.steps / t_e2e, 1), "unit": "atom-steps/s", "h2d_bytes_per_step": N * 12 * world,
+                        "d2h_bytes_per_step": (N * 12 + 8) * world, "ms_per_step": round(1e3 * t_e2e / args.steps, 3)},
+                "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": None}
         print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()

@@ -124,6 +124,10 @@ def _worker(rank, world, port, out):
     dom.R[: dom.n0] += torch.tensor(shift)
     E1, _ = dom.compute()
     res.update(E1=float(E1), F1=dom.global_forces().numpy(), rebuilds=dom.n_rebuilds, R1=dom.gather_global(dom.R[: dom.n0]).numpy())
+    # host-buffer entry point: all positions in, total energy and all forces out
+    E2, F2 = dom.compute_host(R)
+    E3, F3 = dom.compute_host(R + 0.01)          # small move: no re-partitioning, same forces
+    res.update(E2=E2, F2=F2.copy(), E3=E3, F3=F3.copy(), rebuilds_host=dom.n_rebuilds)
     if rank == 0:
         torch.save(res, out)
     dist.barrier()
@@ -149,6 +153,10 @@ def test_decomposed_toy_model_matches_single_domain(tmp_path, world):
     E1, F1 = _serial_reference(R1, cell)
     assert abs(res["E1"] - E1) < 1e-6 * max(1.0, abs(E1))
     np.testing.assert_allclose(res["F1"], F1, atol=2e-5)
+    assert abs(res["E2"] - E0) < 1e-6 * max(1.0, abs(E0)) and abs(res["E3"] - E0) < 1e-5 * max(1.0, abs(E0))
+    np.testing.assert_allclose(res["F2"], F0, atol=2e-5)
+    np.testing.assert_allclose(res["F3"], F0, atol=1e-4)
+    assert res["rebuilds_host"] == 3
     # positions come back in the caller's order, wrapped into the cell along the decomposed axis
     d = res["R1"] - R1
     d[:, 0] -= np.round(d[:, 0] / cell[0, 0]) * cell[0, 0]
