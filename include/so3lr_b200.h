@@ -127,32 +127,48 @@ SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* sys, void* stream, i
                           float* positions_dev, float* velocities_dev, float* forces_dev, double* energy_dev);
 
 /* Domain-decomposed evaluation of one large periodic structure: every rank owns the atoms of its sub-box and holds
- * copies ("ghosts") of the atoms within three interaction shells (3 x (4.5 A + skin), which also covers the 12 A pair
- * terms) of it.  The library evaluates one rank's atoms; moving positions, charges and forces between ranks is the
- * caller's job (so3lr_b200/domain.py does it with NCCL send/recv).  Per evaluation:
- *   dd_forward : network forward; raw partial charges and Hirshfeld ratios of the owned atoms come out
- *   (caller: global sum of the raw charges -> charge conservation; halo exchange of q and h)
- *   dd_pair    : Coulomb + dispersion of every pair that involves an owned atom (half the pair energy is booked
- *                here, the other half by the partner's owner); the sum of dE/dq over the owned atoms comes out
- *   (caller: sum of that number over all ranks; dd_backward divides it by the global atom count n_atoms_all)
- *   dd_backward: reverse pass; forces on all local atoms (owned and ghosts) and the energy of the owned atoms
- *   (caller: ghost forces go back to their owners and are added there)
+ * copies ("ghosts") of the atoms within the long-range list radius (12 A + skin) of it; the ghosts within one short-range
+ * shell (4.5 A + skin) also carry features.  The library evaluates one rank's owned atoms layer by layer; between the
+ * calls the caller moves rows between ranks (so3lr_b200/domain.py does it with NCCL send/recv):
+ *   dd_begin                  lists (when invalid), ZBL, embeddings
+ *   for l = 0,1,2: dd_layer_forward(l)
+ *        then (l < 2) the rows of the short-range ghosts in buffers (0, l+1) and (1, l+1) are filled from their owners
+ *   dd_heads                  raw partial charges and Hirshfeld ratios of the owned atoms
+ *        (caller: global sum of the raw charges -> charge conservation; halo exchange of q and h to all ghosts)
+ *   dd_pair                   Coulomb + dispersion of every pair that involves an owned atom (half of each pair energy is
+ *                             booked here); returns the sum of dE/dq over the owned atoms
+ *        (caller: sum of that number over all ranks)
+ *   dd_heads_backward         energy of the owned atoms, cotangents of the final features
+ *   for l = 2,1,0: dd_layer_backward_post(l)
+ *        then the rows of the short-range ghosts in buffers (2) and (3) are filled from their owners
+ *        dd_layer_backward_attn(l)
+ *   dd_forces                 forces on the owned atoms, complete: no ghost forces exist in this scheme
+ * Because the attention kernels gather both directions of every edge towards the owned atom, no rank ever computes on
+ * behalf of a ghost: the work per rank is that of its owned atoms.
  * The context is created with so3lr_b200_system_create for the largest local atom count it will see (n_graphs = 1,
  * cutoff_lr > 0); dd_set_atoms installs a new local atom set and invalidates the neighbor lists.
- * Local atom order: [0, shells4[0]) owned, then ghosts by shell: [.., shells4[1]) within one shell of the sub-box,
- * [.., shells4[2]) within two, [.., shells4[3] = n_local) the rest.  `cell9` is the rank's local periodic cell; along the
- * decomposed direction it must exceed the extent of the local atoms by more than the list radius, so that no pair is
- * found through the wrap.  Z_local_dev: device int32; all other pointers are device pointers.
+ * Local atom order: [0, shells4[0]) owned, [shells4[0], shells4[1]) ghosts within one short-range shell of the sub-box,
+ * then the remaining ghosts up to shells4[3] = n_local (shells4[2] is ignored).  `cell9` is the rank's local periodic
+ * cell; along the decomposed direction it must exceed the extent of the local atoms by more than the list radius, so
+ * that no pair is found through the wrap.  Z_local_dev: device int32; all other pointers are device pointers.
+ * dd_buffer: device address and row length (floats) of an internal per-atom array, rows in local atom order:
+ *   which 0: features x of `layer` (0..3), 1: equivariant features ev of `layer`, 2 / 3: cotangents of the current
+ *   layer's attention outputs (128 / 24 floats per row).
  * Replaces: nothing in the reference (it has no multi-device path); the decomposition follows the cutoffs of
  * so3lr/potential.py:17-29 and so3lr/jaxmd_utils.py:96-121. */
 SO3LR_B200_API int so3lr_b200_dd_set_atoms(so3lr_b200_system* sys, int n_local, const int32_t* shells4, const int32_t* Z_local_dev,
                                            const float* cell9);
-SO3LR_B200_API int so3lr_b200_dd_forward(so3lr_b200_system* sys, void* stream, const float* R_local_dev, float* q_raw_owned_dev,
-                                         float* h_owned_dev);
+SO3LR_B200_API int so3lr_b200_dd_begin(so3lr_b200_system* sys, void* stream, const float* R_local_dev);
+SO3LR_B200_API int so3lr_b200_dd_layer_forward(so3lr_b200_system* sys, void* stream, int layer);
+SO3LR_B200_API int so3lr_b200_dd_heads(so3lr_b200_system* sys, void* stream, float* q_raw_owned_dev, float* h_owned_dev);
 SO3LR_B200_API int so3lr_b200_dd_pair(so3lr_b200_system* sys, void* stream, const float* R_local_dev, const float* q_local_dev,
                                       const float* h_local_dev, double* gq_sum_dev);
-SO3LR_B200_API int so3lr_b200_dd_backward(so3lr_b200_system* sys, void* stream, const double* gq_sum_all_dev, int64_t n_atoms_all,
-                                          float* F_local_dev, double* energy_owned_dev);
+SO3LR_B200_API int so3lr_b200_dd_heads_backward(so3lr_b200_system* sys, void* stream, const double* gq_sum_all_dev,
+                                                int64_t n_atoms_all, double* energy_owned_dev);
+SO3LR_B200_API int so3lr_b200_dd_layer_backward_post(so3lr_b200_system* sys, void* stream, int layer);
+SO3LR_B200_API int so3lr_b200_dd_layer_backward_attn(so3lr_b200_system* sys, void* stream, int layer);
+SO3LR_B200_API int so3lr_b200_dd_forces(so3lr_b200_system* sys, void* stream, float* F_owned_dev);
+SO3LR_B200_API int so3lr_b200_dd_buffer(so3lr_b200_system* sys, int which, int layer, float** ptr, int* row_floats);
 
 /* Optional timing of kernel groups with CUDA events recorded on the launching stream.  `profile(sys, 1)` starts a
  * fresh recording; `profile_read` synchronises the device, returns the number of groups and fills, per group, the

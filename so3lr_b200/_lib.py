@@ -47,9 +47,15 @@ def _load():
         "so3lr_b200_system_graph_eval": (i32, [p, p, i64, p, p, p, i64, p, p, p, p, p, p, p, p, p]),
         "so3lr_b200_system_nve": (i32, [p, p, i32, f32, p, p, p, p, p]),
         "so3lr_b200_dd_set_atoms": (i32, [p, i32, p, p, p]),
-        "so3lr_b200_dd_forward": (i32, [p, p, p, p, p]),
+        "so3lr_b200_dd_begin": (i32, [p, p, p]),
+        "so3lr_b200_dd_layer_forward": (i32, [p, p, i32]),
+        "so3lr_b200_dd_heads": (i32, [p, p, p, p]),
         "so3lr_b200_dd_pair": (i32, [p, p, p, p, p, p]),
-        "so3lr_b200_dd_backward": (i32, [p, p, p, i64, p, p]),
+        "so3lr_b200_dd_heads_backward": (i32, [p, p, p, i64, p]),
+        "so3lr_b200_dd_layer_backward_post": (i32, [p, p, i32]),
+        "so3lr_b200_dd_layer_backward_attn": (i32, [p, p, i32]),
+        "so3lr_b200_dd_forces": (i32, [p, p, p]),
+        "so3lr_b200_dd_buffer": (i32, [p, i32, i32, C.POINTER(p), C.POINTER(i32)]),
         "so3lr_b200_system_profile": (i32, [p, i32]),
         "so3lr_b200_system_profile_read": (i32, [p, i32, p, p, p]),
         "so3lr_b200_neighbor_list_noalloc": (i32, [p, i32, p, p, f32, i32, p, i64, p, p]),

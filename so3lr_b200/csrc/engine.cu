@@ -193,7 +193,8 @@ struct so3lr_b200_system {
   Profiler prof;
   int n = 0, n_graphs = 1;
   int n_cap = 0;                 // atoms the per-atom arrays were allocated for
-  int shells[4] = {0, 0, 0, 0};  // domain-decomposed evaluation: owned | +1 | +2 | +3 shells (see struct Shells)
+  int shells[4] = {0, 0, 0, 0};  // domain-decomposed evaluation: owned | + short-range ghosts | (unused) | all local atoms
+  float *dd_gev2 = nullptr, *dd_gev_in = nullptr;   // ping-pong cotangents of ev between the layers of the reverse pass
   so3lr_b200_options opt{};
   Cell cell{};
   LrParams lr{};
@@ -798,20 +799,18 @@ SO3LR_B200_API int so3lr_b200_dd_set_atoms(so3lr_b200_system* S, int n_local, co
   return kOk;
 }
 
-SO3LR_B200_API int so3lr_b200_dd_forward(so3lr_b200_system* S, void* stream, const float* R_local_dev, float* q_raw_owned_dev,
-                                         float* h_owned_dev) {
-  if (!S || !R_local_dev || !q_raw_owned_dev || !h_owned_dev || S->shells[3] != S->n || S->n <= 0) return kInvalidArgument;
+SO3LR_B200_API int so3lr_b200_dd_begin(so3lr_b200_system* S, void* stream, const float* R_local_dev) {
+  if (!S || !R_local_dev || S->shells[3] != S->n || S->n <= 0) return kInvalidArgument;
   if (!(S->opt.cutoff_lr > 0.f)) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
   cudaStream_t st = (cudaStream_t)stream;
-  const Shells c{S->shells[0], S->shells[1], S->shells[2], S->shells[3]};
+  const int n0 = S->shells[0], n1 = S->shells[1];
   if (!S->have_lists) {
     S->prof.begin(kPNlist, st);
-    // short range: rows for every local atom (the reverse pass walks all of them); long range: rows of the owned atoms
-    // only, both directions
-    int rc = nlist_build(S->nws, st, S->cell, S->n, R_local_dev, kCutoffSr + S->opt.skin, 0, nullptr, nullptr, &S->sr, 1, nullptr);
+    // rows of the owned atoms only: every kernel of the decomposed path gathers towards an owned atom
+    int rc = nlist_build(S->nws, st, S->cell, S->n, R_local_dev, kCutoffSr + S->opt.skin, 0, nullptr, nullptr, &S->sr, 1, nullptr, n0);
     if (rc) return rc;
-    rc = nlist_build(S->nws, st, S->cell, S->n, R_local_dev, S->opt.cutoff_lr + S->opt.skin, 0, nullptr, nullptr, &S->lrl, 1, nullptr, c.n0);
+    rc = nlist_build(S->nws, st, S->cell, S->n, R_local_dev, S->opt.cutoff_lr + S->opt.skin, 0, nullptr, nullptr, &S->lrl, 1, nullptr, n0);
     if (rc) return rc;
     rc = ensure_edge_buffers(S, S->sr.count);
     if (rc) return rc;
@@ -820,11 +819,49 @@ SO3LR_B200_API int so3lr_b200_dd_forward(so3lr_b200_system* S, void* stream, con
     S->n_rebuilds++;
     S->n_launches += 12;
   }
-  int rc = fused_forward(S, st, R_local_dev, c, true, S->F_s);
-  if (rc) return rc;
-  SO3LR_CUDA_CHECK(cudaMemcpyAsync(q_raw_owned_dev, S->q_raw, (size_t)c.n0 * sizeof(float), cudaMemcpyDeviceToDevice, st));
-  abs_kernel<<<(c.n0 + 255) / 256, 256, 0, st>>>(c.n0, S->hv, h_owned_dev);
-  S->n_launches += 1;
+  const ModelDev& M = S->model->M;
+  fill(st, S->e_zbl, n0, 0.f);
+  fill(st, S->F_s, (size_t)n0 * 3, 0.f);
+  S->prof.begin(kPGeom, st);
+  launch_sr_geometry_zbl(st, M, S->cell, S->n, S->sr.count, S->sr.edge_i, S->sr.nbr_j, S->d_Z, R_local_dev, 0, S->dR, S->e_zbl, nullptr, nullptr,
+                         S->F_s, n0);
+  S->prof.end(st);
+  launch_embed(st, M, S->d_Z, n1, S->x[0]);
+  S->n_launches += 4;
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_dd_layer_forward(so3lr_b200_system* S, void* stream, int layer) {
+  if (!S || layer < 0 || layer >= kNumLayers || !S->have_lists) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  const int n0 = S->shells[0], n1 = S->shells[1], l = layer;
+  const LayerDev& L = S->model->M.layer[l];
+  S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], n1, S->qkv[l]); S->prof.end(st);
+  S->prof.begin(kPAttnFwd, st);
+  launch_attn_fwd_sym(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
+  S->prof.end(st);
+  S->prof.begin(kPPostFwd, st);
+  launch_atom_post_fwd(st, L, n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]);
+  S->prof.end(st);
+  S->n_launches += 3;
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_dd_heads(so3lr_b200_system* S, void* stream, float* q_raw_owned_dev, float* h_owned_dev) {
+  if (!S || !q_raw_owned_dev || !h_owned_dev || !S->have_lists) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  const int n0 = S->shells[0];
+  S->prof.begin(kPHeads, st);
+  launch_heads_fwd(st, S->model->M, n0, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv);
+  S->prof.end(st);
+  SO3LR_CUDA_CHECK(cudaMemcpyAsync(q_raw_owned_dev, S->q_raw, (size_t)n0 * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  abs_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->hv, h_owned_dev);
+  S->n_launches += 2;
+  SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
 
@@ -844,20 +881,77 @@ SO3LR_B200_API int so3lr_b200_dd_pair(so3lr_b200_system* S, void* stream, const 
   return kOk;
 }
 
-SO3LR_B200_API int so3lr_b200_dd_backward(so3lr_b200_system* S, void* stream, const double* gq_sum_all_dev, int64_t n_atoms_all,
-                                          float* F_local_dev, double* energy_owned_dev) {
-  if (!S || !F_local_dev || !gq_sum_all_dev || n_atoms_all <= 0 || !S->have_lists) return kInvalidArgument;
+SO3LR_B200_API int so3lr_b200_dd_heads_backward(so3lr_b200_system* S, void* stream, const double* gq_sum_all_dev, int64_t n_atoms_all,
+                                                double* energy_owned_dev) {
+  if (!S || !gq_sum_all_dev || n_atoms_all <= 0 || !S->have_lists) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
   cudaStream_t st = (cudaStream_t)stream;
-  const Shells c{S->shells[0], S->shells[1], S->shells[2], S->shells[3]};
-  subtract_mean_kernel<<<(c.n0 + 255) / 256, 256, 0, st>>>(c.n0, S->gq, gq_sum_all_dev, (double)n_atoms_all, S->gq_raw);
-  combine_energy_kernel<<<(c.n0 + 255) / 256, 256, 0, st>>>(c.n0, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom);
-  if (energy_owned_dev) sum_to_double_kernel<<<1, 1024, 0, st>>>(c.n0, S->e_atom, energy_owned_dev);
-  S->n_launches += 3;
-  int rc = fused_backward(S, st, c, S->F_s);
-  if (rc) return rc;
-  SO3LR_CUDA_CHECK(cudaMemcpyAsync(F_local_dev, S->F_s, (size_t)c.n3 * 3 * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  const int n0 = S->shells[0];
+  subtract_mean_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->gq, gq_sum_all_dev, (double)n_atoms_all, S->gq_raw);
+  combine_energy_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom);
+  if (energy_owned_dev) sum_to_double_kernel<<<1, 1024, 0, st>>>(n0, S->e_atom, energy_owned_dev);
+  S->prof.begin(kPHeads, st);
+  launch_heads_bwd(st, S->model->M, n0, S->d_Z, S->ze, S->zq, S->zh, S->hv, S->ones, S->gq_raw, S->gh, S->g4);
+  S->prof.end(st);
+  S->dd_gev2 = S->gev_a; S->dd_gev_in = S->gev_b;
+  fill(st, S->dd_gev2, (size_t)n0 * kMTot, 0.f);
+  S->n_launches += 5;
+  SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
+}
+
+// cotangents of the layer's attention outputs on the owned atoms (rows [0, n0) of the buffers 2 and 3 of dd_buffer)
+SO3LR_B200_API int so3lr_b200_dd_layer_backward_post(so3lr_b200_system* S, void* stream, int layer) {
+  if (!S || layer < 0 || layer >= kNumLayers || !S->have_lists || !S->dd_gev2) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  const int n0 = S->shells[0], l = layer;
+  S->prof.begin(kPPostBwd, st);
+  launch_atom_post_bwd(st, S->model->M.layer[l], n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, S->dd_gev2, S->g_xa, S->gev1);
+  S->prof.end(st);
+  S->n_launches += 1;
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+// needs the cotangent rows of the short-range ghosts filled in by their owners
+SO3LR_B200_API int so3lr_b200_dd_layer_backward_attn(so3lr_b200_system* S, void* stream, int layer) {
+  if (!S || layer < 0 || layer >= kNumLayers || !S->have_lists || !S->dd_gev2) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  const int n0 = S->shells[0], l = layer;
+  const LayerDev& L = S->model->M.layer[l];
+  S->prof.begin(kPAttnBwd, st);
+  launch_attn_bwd_sym(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, S->dd_gev_in, S->F_s,
+                      l == 0 ? 1 : 0);
+  S->prof.end(st);
+  S->n_launches += 1;
+  if (l > 0) {
+    SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)n0 * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    S->prof.begin(kPProjBwd, st); launch_proj_bwd(st, L, S->g_qkv, n0, S->g4, 1); S->prof.end(st);
+    float* t = S->dd_gev2; S->dd_gev2 = S->dd_gev_in; S->dd_gev_in = t;
+    S->n_launches += 2;
+  }
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_dd_forces(so3lr_b200_system* S, void* stream, float* F_owned_dev) {
+  if (!S || !F_owned_dev) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  SO3LR_CUDA_CHECK(cudaMemcpyAsync(F_owned_dev, S->F_s, (size_t)S->shells[0] * 3 * sizeof(float), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_dd_buffer(so3lr_b200_system* S, int which, int layer, float** ptr, int* row_floats) {
+  if (!S || !ptr || !row_floats) return kInvalidArgument;
+  switch (which) {
+    case 0: if (layer < 0 || layer > kNumLayers) return kInvalidArgument; *ptr = S->x[layer]; *row_floats = kF; return kOk;
+    case 1: if (layer < 0 || layer > kNumLayers) return kInvalidArgument; *ptr = S->ev[layer]; *row_floats = kMTot; return kOk;
+    case 2: *ptr = S->g_xa; *row_floats = kF; return kOk;
+    case 3: *ptr = S->gev1; *row_floats = kMTot; return kOk;
+    default: return kInvalidArgument;
+  }
 }
 
 SO3LR_B200_API int so3lr_b200_system_profile(so3lr_b200_system* S, int enable) {

@@ -1,19 +1,25 @@
 """Spatial domain decomposition of one large periodic structure over several GPUs (one process per GPU).
 
 The box is cut into slabs along the lattice direction with the largest perpendicular width.  Every rank owns the atoms
-of its slab and keeps copies ("ghosts") of the atoms within three interaction shells of it (one shell = 4.5 A + skin;
-three shells also cover the 12 A + skin pair terms).  The library evaluates a rank's atoms in three phases
-(so3lr_b200_dd_forward / _pair / _backward); this module moves data between the ranks:
+of its slab and keeps copies ("ghosts") of the atoms within the long-range list radius (12 A + skin) of it; the ghosts
+within one short-range shell (4.5 A + skin) additionally receive the per-layer features of their owners.  The library
+evaluates a rank's owned atoms layer by layer (so3lr_b200_dd_*); this module moves rows between the ranks:
 
-  per step      positions of ghost atoms            owner -> holder   (send/recv)
-                sum of raw partial charges          all-reduce        (charge conservation)
-                charges and Hirshfeld ratios        owner -> holder   (send/recv)
-                sum of dE/dq                        all-reduce        (reverse of the charge conservation)
-                forces on ghost atoms               holder -> owner   (send/recv, added)
-  per rebuild   all positions and velocities        all-reduce of the scattered owned rows; every rank then selects its
-                                                    own atoms and ghosts, so atoms migrate without extra messages
+  per step      positions of all ghosts                          owner -> holder   (send/recv)
+                features x, ev after layers 0 and 1              owner -> holder   (send/recv, short-range ghosts)
+                sum of raw partial charges                       all-reduce        (charge conservation)
+                charges and Hirshfeld ratios of all ghosts       owner -> holder   (send/recv)
+                sum of dE/dq                                     all-reduce        (reverse of the charge conservation)
+                cotangents of each layer's attention outputs     owner -> holder   (send/recv, short-range ghosts, 3 x)
+  per rebuild   all positions and velocities                     all-reduce of the scattered owned rows; every rank then
+                                                                 selects its own atoms and ghosts, so atoms migrate
+                                                                 without extra messages
 
-The reference has no multi-device path; the shells follow from its cutoffs (so3lr/potential.py:17-29).
+Every kernel of this path gathers towards an owned atom (both directions of an edge are evaluated by the owner of the
+receiving end), so no rank computes on behalf of a ghost and no forces travel: the work per rank is that of its owned
+atoms, and the traffic is a few hundred bytes per ghost atom and layer over NVLink.
+
+The reference has no multi-device path; the radii follow from its cutoffs (so3lr/potential.py:17-29).
 The numerical work is behind a small backend interface so that the bookkeeping can be tested on CPU ranks (gloo) with
 a stand-in model; `CudaBackend` is the real one.
 """
@@ -27,7 +33,6 @@ import numpy as np
 import torch
 
 CUTOFF_SR = 4.5
-N_SHELLS = 3
 ACC_UNIT = 9.648533212331e-3      # eV / (A amu) -> A / fs^2
 
 
@@ -137,15 +142,14 @@ class SlabDecomposition:
         self.axis = int(np.argmax(widths)) if axis is None else int(axis)
         self.width = float(widths[self.axis])
         self.world = int(world)
-        self.shell = CUTOFF_SR + skin
-        self.lr_radius = cutoff_lr + skin
-        if N_SHELLS * self.shell < self.lr_radius:
-            raise ValueError("three short-range shells must cover the long-range list radius")
-        self.sf = self.shell / self.width                    # one shell in fractional units
-        if N_SHELLS * self.sf > 1.0:
+        self.shell = CUTOFF_SR + skin                        # short-range list radius
+        self.lr_radius = max(cutoff_lr + skin, self.shell)   # long-range list radius = halo width
+        self.sf = self.shell / self.width                    # both in fractional units along the axis
+        self.reach = self.lr_radius / self.width
+        if self.reach > 1.0:
             raise ValueError("the cell is thinner than the halo along the decomposed direction")
         self.bounds = np.arange(self.world + 1, dtype=np.float64) / self.world
-        self.ext = 1.0 / self.world + 2 * N_SHELLS * self.sf + (self.lr_radius + 1.0) / self.width
+        self.ext = 1.0 / self.world + 2 * self.reach + (self.lr_radius + 1.0) / self.width
 
     def local_cell(self):
         c = self.cell.copy()
@@ -168,14 +172,15 @@ class SlabDecomposition:
         return (torch.searchsorted(b, s, right=True) - 1).clamp_(0, self.world - 1)
 
     def selection(self, rank: int, R, s):
-        """Atoms of `rank` in its local order: (global index, image shift along the axis, shell 0..3)."""
+        """Atoms of `rank` in its local order: (global index, image shift along the axis, class), class 0 = owned,
+        1 = ghost within the short-range shell of the slab, 2 = ghost within the long-range radius only."""
         dev = R.device
         lo, hi = float(self.bounds[rank]), float(self.bounds[rank + 1])
         own = self.owner(s) == rank
         idx = [torch.nonzero(own).squeeze(1)]
         shift = [torch.zeros_like(idx[0])]
         shell = [torch.zeros_like(idx[0])]
-        reach = N_SHELLS * self.sf
+        reach = self.reach
         for k in (-1, 0, 1):
             sp = s + k
             for side in (0, 1):
@@ -186,7 +191,7 @@ class SlabDecomposition:
                 g = torch.nonzero(m).squeeze(1)
                 idx.append(g)
                 shift.append(torch.full_like(g, k))
-                shell.append((torch.floor(d[g] / self.sf).to(torch.int64) + 1).clamp_(1, N_SHELLS))
+                shell.append(torch.where(d[g] <= self.sf, 1, 2).to(torch.int64))
         idx, shift, shell = torch.cat(idx), torch.cat(shift), torch.cat(shell)
         # order: shell, then a Morton curve over cells of one shell width (keeps neighbours close in memory)
         a_vec = torch.tensor(self.cell[self.axis], dtype=torch.float64, device=dev)
@@ -207,7 +212,15 @@ class SlabDecomposition:
 # backends
 # ----------------------------------------------------------------------------------------------------------------
 class CudaBackend:
-    """The three evaluation phases of one rank through the C ABI (so3lr_b200_dd_*)."""
+    """One rank's evaluation phases through the C ABI (so3lr_b200_dd_*).
+
+    Backend interface used by DomainSystem (a CPU stand-in implements the same methods in the tests):
+      num_layers; set_atoms(Z_local, counts, cell_local); begin(R_local); layer_forward(l); feature_rows(l) -> list of
+      (n_local, d) tensors viewing the layer-l features; heads() -> (q_raw, h) of the owned atoms; pair(q_local, h_local)
+      -> sum of dE/dq over owned atoms; heads_backward(gq_sum_all, n_all) -> energy of the owned atoms;
+      layer_backward_post(l); cotangent_rows() -> list of (n_local, d) tensors; layer_backward_attn(l); forces() -> (n0, 3).
+    """
+    num_layers = 3
 
     def __init__(self, cutoff_lr=12.0, damping=2.0, skin=1.0, device=0):
         from .engine import Model
@@ -220,8 +233,18 @@ class CudaBackend:
     def _stream(self):
         return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
 
-    def set_atoms(self, Z_local, shells, cell_local):
+    def _call(self, name, *args):
         from ._lib import check, lib
+        check(getattr(lib, "so3lr_b200_" + name)(self.sys._h, *args), name)
+
+    def _buffer(self, which, layer):
+        from ._lib import check, lib
+        from .engine import _from_ptr
+        ptr, rf = C.c_void_p(), C.c_int()
+        check(lib.so3lr_b200_dd_buffer(self.sys._h, which, layer, C.byref(ptr), C.byref(rf)), "dd_buffer")
+        return _from_ptr(ptr.value, self.capacity * rf.value, self.device).view(self.capacity, rf.value)[: self.n]
+
+    def set_atoms(self, Z_local, counts, cell_local):
         from .engine import System, _ptr
         n = int(Z_local.numel())
         if n > self.capacity:
@@ -229,38 +252,62 @@ class CudaBackend:
             self.capacity = int(1.2 * n) + 1024
             self.sys = System(np.ones(self.capacity, np.int32), np.asarray(cell_local), cutoff_lr=self.cutoff_lr, damping=self.damping,
                               skin=self.skin, lr_format="sparse", model=self.model)
-        self.n, self.shells = n, [int(v) for v in shells]
-        sh = np.asarray(self.shells, dtype=np.int32)
+        self.n, self.counts = n, [int(v) for v in counts]
+        sh = np.asarray([self.counts[0], self.counts[1], self.counts[1], n], dtype=np.int32)
         c9 = np.ascontiguousarray(np.asarray(cell_local, dtype=np.float32).reshape(9))
         Zl = Z_local.to(self.device, torch.int32).contiguous()
         torch.cuda.current_stream(self.device).synchronize()
-        check(lib.so3lr_b200_dd_set_atoms(self.sys._h, n, _ptr(sh), _ptr(Zl), _ptr(c9)), "dd_set_atoms")
+        self._call("dd_set_atoms", n, _ptr(sh), _ptr(Zl), _ptr(c9))
+        self._x = [self._buffer(0, l) for l in range(4)]
+        self._ev = [self._buffer(1, l) for l in range(4)]
+        self._g = [self._buffer(2, 0), self._buffer(3, 0)]
 
-    def forward(self, R_local):
-        from ._lib import check, lib
+    def begin(self, R_local):
         from .engine import _ptr
-        n0 = self.shells[0]
-        q = torch.empty(n0, device=self.device)
-        h = torch.empty(n0, device=self.device)
         self._R = R_local.contiguous()
-        check(lib.so3lr_b200_dd_forward(self.sys._h, self._stream(), _ptr(self._R), _ptr(q), _ptr(h)), "dd_forward")
+        self._call("dd_begin", self._stream(), _ptr(self._R))
+
+    def layer_forward(self, l):
+        self._call("dd_layer_forward", self._stream(), int(l))
+
+    def feature_rows(self, l):
+        return [self._x[l], self._ev[l]]
+
+    def heads(self):
+        from .engine import _ptr
+        n0 = self.counts[0]
+        q, h = torch.empty(n0, device=self.device), torch.empty(n0, device=self.device)
+        self._call("dd_heads", self._stream(), _ptr(q), _ptr(h))
         return q, h
 
     def pair(self, q_local, h_local):
-        from ._lib import check, lib
         from .engine import _ptr
         s = torch.zeros(1, dtype=torch.float64, device=self.device)
         self._q, self._h = q_local.contiguous(), h_local.contiguous()
-        check(lib.so3lr_b200_dd_pair(self.sys._h, self._stream(), _ptr(self._R), _ptr(self._q), _ptr(self._h), _ptr(s)), "dd_pair")
+        self._call("dd_pair", self._stream(), _ptr(self._R), _ptr(self._q), _ptr(self._h), _ptr(s))
         return s
 
-    def backward(self, gq_sum_all, n_all):
-        from ._lib import check, lib
+    def heads_backward(self, gq_sum_all, n_all):
         from .engine import _ptr
-        F = torch.empty(self.n, 3, device=self.device)
         E = torch.zeros(1, dtype=torch.float64, device=self.device)
-        check(lib.so3lr_b200_dd_backward(self.sys._h, self._stream(), _ptr(gq_sum_all), int(n_all), _ptr(F), _ptr(E)), "dd_backward")
-        return F, E
+        self._gq_sum = gq_sum_all
+        self._call("dd_heads_backward", self._stream(), _ptr(gq_sum_all), C.c_int64(int(n_all)), _ptr(E))
+        return E
+
+    def layer_backward_post(self, l):
+        self._call("dd_layer_backward_post", self._stream(), int(l))
+
+    def cotangent_rows(self):
+        return self._g
+
+    def layer_backward_attn(self, l):
+        self._call("dd_layer_backward_attn", self._stream(), int(l))
+
+    def forces(self):
+        from .engine import _ptr
+        F = torch.empty(self.counts[0], 3, device=self.device)
+        self._call("dd_forces", self._stream(), _ptr(F))
+        return F
 
     def stats(self):
         return self.sys.stats()
@@ -273,8 +320,9 @@ class DomainSystem:
     """One rank's share of a periodic structure of `n_all` atoms.
 
     At construction every rank passes the same global arrays (atomic numbers, positions, optionally velocities and
-    masses); afterwards each rank keeps only its own atoms and ghosts.  `compute()` returns the forces on the owned
-    atoms and the total energy; `nve()` integrates the owned atoms.  `gather_global()` reassembles global arrays.
+    masses); afterwards each rank keeps only its own atoms and ghosts.  `compute()` returns the total energy and the
+    forces on the owned atoms; `nve()` integrates the owned atoms; `compute_host()` is the host-buffer call;
+    `gather_global()` reassembles arrays in the caller's atom order.
     """
 
     def __init__(self, comm, backend, atomic_numbers, positions, cell, *, skin=1.0, cutoff_lr=12.0, total_charge=0.0,
@@ -294,65 +342,70 @@ class DomainSystem:
         self._partition(R, V)
 
     # ---- partition / halo plans (all ranks hold identical R_all here) ----
+    def _peers(self):
+        """Ranks whose slab lies within the halo of mine (periodic), myself included (own periodic images)."""
+        geo, out = self.geo, []
+        for p in range(self.world):
+            gap = min((p - self.rank) % self.world, (self.rank - p) % self.world)
+            if p == self.rank or (gap - 1) / self.world < geo.reach + 1e-9:
+                out.append(p)
+        return out
+
     def _partition(self, R_all, V_all):
         geo, dev = self.geo, self.device
         R_in = R_all
         R_all, s = geo.wrap(R_all)
         self.wrap_vec = R_in - R_all          # lattice translation that brought every atom into the cell
         owner_all = geo.owner(s)
-        sel = [geo.selection(p, R_all, s) for p in range(self.world)]
-        idx, shift, shell = sel[self.rank]
+        peers = self._peers()
+        sel = {p: geo.selection(p, R_all, s) for p in peers}
+        idx, shift, cls = sel[self.rank]
         self.gid, self.shift = idx, shift
-        counts = [int((shell <= k).sum()) for k in range(N_SHELLS + 1)]
-        self.n0, self.n_local = counts[0], counts[-1]
-        self.shells = counts
+        self.n0, self.n1, self.n_local = int((cls == 0).sum()), int((cls <= 1).sum()), int(cls.numel())
         a_vec = torch.tensor(geo.cell[geo.axis], dtype=torch.float32, device=dev)
         self.shift_vec = shift[:, None].to(torch.float32) * a_vec
         self.R = (R_all[idx] + self.shift_vec).contiguous()
         self.R_ref = self.R[: self.n0].clone()
         self.V = None if V_all is None else V_all[idx[: self.n0]].contiguous()
         self.m = None if self.m_all is None else self.m_all[idx[: self.n0]].contiguous()
-        # plans: recv_slots[p] = my ghost slots owned by p (my order); send_slots[p] = my owned slots that p holds as ghosts (p's order)
+        # plans: recv_slots[p] = my ghost slots owned by p (my order); send_slots[p] = my owned slots that p holds as ghosts
+        # (p's order).  The *_sr variants cover the short-range ghosts only (a prefix of each list, since ghosts are
+        # ordered by class).
         slot_of_gid = torch.full((self.n_all,), -1, dtype=torch.int64, device=dev)
         slot_of_gid[idx[: self.n0]] = torch.arange(self.n0, device=dev)
         ghost_owner = owner_all[idx[self.n0:]]
-        self.recv_slots, self.send_slots = {}, {}
-        for p in range(self.world):
-            self.recv_slots[p] = torch.nonzero(ghost_owner == p).squeeze(1) + self.n0
-            pidx, _, pshell = sel[p]
-            n0p = int((pshell == 0).sum())
-            pg = pidx[n0p:]
+        self.recv_slots, self.send_slots, self.recv_sr, self.send_sr = {}, {}, {}, {}
+        for p in peers:
+            r = torch.nonzero(ghost_owner == p).squeeze(1) + self.n0
+            self.recv_slots[p] = r
+            self.recv_sr[p] = r[r < self.n1]
+            pidx, _, pcls = sel[p]
+            n0p = int((pcls == 0).sum())
+            pg, pc = pidx[n0p:], pcls[n0p:]
             mine = owner_all[pg] == self.rank
             self.send_slots[p] = slot_of_gid[pg[mine]]
-        self.backend.set_atoms(self.Z_all[idx], counts, geo.local_cell())
+            self.send_sr[p] = slot_of_gid[pg[mine & (pc == 1)]]
+        self.backend.set_atoms(self.Z_all[idx], [self.n0, self.n1, self.n_local], geo.local_cell())
         self.n_rebuilds += 1
 
     # ---- halo traffic ----
-    def _halo_forward(self, owned_rows, local_out):
-        """owned_rows (n0, ...) -> fills ghost rows of local_out (n_local, ...) from their owners."""
-        tail = owned_rows.shape[1:]
-        sends = {p: owned_rows[sl] for p, sl in self.send_slots.items() if p != self.rank}
-        recvs = {p: torch.empty((sl.numel(),) + tail, dtype=owned_rows.dtype, device=self.device)
-                 for p, sl in self.recv_slots.items() if p != self.rank}
+    def _halo_fill(self, tensors, sr_only=False):
+        """Fill the ghost rows of each (n_local, d) tensor from the owners' rows (rows [0, n0) are the owned ones)."""
+        send_slots = self.send_sr if sr_only else self.send_slots
+        recv_slots = self.recv_sr if sr_only else self.recv_slots
+        width = [t.shape[1] for t in tensors]
+        me = self.rank
+        sends = {p: torch.cat([t[sl] for t in tensors], 1) for p, sl in send_slots.items() if p != me}
+        recvs = {p: torch.empty((sl.numel(), sum(width)), dtype=tensors[0].dtype, device=self.device)
+                 for p, sl in recv_slots.items() if p != me}
         self.comm.exchange(sends, recvs)
-        local_out[: self.n0] = owned_rows
         for p, buf in recvs.items():
-            local_out[self.recv_slots[p]] = buf
-        local_out[self.recv_slots[self.rank]] = owned_rows[self.send_slots[self.rank]]     # own periodic images
-        return local_out
-
-    def _halo_reverse_add(self, local_rows):
-        """local_rows (n_local, ...) -> owned rows plus what other ranks accumulated on their copies of my atoms."""
-        tail = local_rows.shape[1:]
-        sends = {p: local_rows[sl] for p, sl in self.recv_slots.items() if p != self.rank}
-        recvs = {p: torch.empty((sl.numel(),) + tail, dtype=local_rows.dtype, device=self.device)
-                 for p, sl in self.send_slots.items() if p != self.rank}
-        self.comm.exchange(sends, recvs)
-        out = local_rows[: self.n0].clone()
-        for p, buf in recvs.items():
-            out.index_add_(0, self.send_slots[p], buf)
-        out.index_add_(0, self.send_slots[self.rank], local_rows[self.recv_slots[self.rank]])
-        return out
+            o = 0
+            for t, w in zip(tensors, width):
+                t[recv_slots[p]] = buf[:, o:o + w]
+                o += w
+        for t in tensors:                                   # own periodic images
+            t[recv_slots[me]] = t[send_slots[me]]
 
     # ---- evaluation ----
     def _maybe_rebuild(self):
@@ -368,21 +421,20 @@ class DomainSystem:
         return False
 
     def compute(self, check_rebuild=True):
-        """Energy (float64 tensor, total over all ranks) and forces on the owned atoms (n0, 3)."""
+        """Total energy (float64 tensor, all ranks) and forces on the owned atoms (n0, 3)."""
         if check_rebuild:
             self._maybe_rebuild()
         # ghost positions follow their owners
-        Rl = torch.empty_like(self.R)
-        self._halo_forward(self.R[: self.n0], Rl)
-        Rl += self.shift_vec
-        self.R = Rl
+        self.R[self.n0:] = 0.0
+        self._halo_fill([self.R])
+        self.R[self.n0:] += self.shift_vec[self.n0:]
         return self._evaluate()
 
     def compute_host(self, R_all_host):
         """The call of a host application that keeps all positions in host memory: (n_all, 3) float32 positions in the
         caller's atom order go in (every rank passes the same array), total energy and (n_all, 3) forces come back as
         numpy arrays.  Each rank uploads the positions, picks its own atoms and ghosts (no position halo exchange is
-        needed), evaluates, and the forces are summed over the ranks."""
+        needed), evaluates, and the forces are assembled over the ranks."""
         Rh = torch.as_tensor(np.ascontiguousarray(R_all_host, dtype=np.float32))
         if self.device.type == "cuda":
             if getattr(self, "_pin", None) is None or self._pin.shape != Rh.shape:
@@ -410,21 +462,33 @@ class DomainSystem:
         return float(E), F_all.numpy()
 
     def _evaluate(self):
-        q_raw, h = self.backend.forward(self.R)
+        be, L = self.backend, self.backend.num_layers
+        be.begin(self.R)
+        for l in range(L):
+            be.layer_forward(l)
+            if l + 1 < L:
+                self._halo_fill(be.feature_rows(l + 1), sr_only=True)
+        q_raw, h = be.heads()
         qsum = self.comm.all_reduce_sum(q_raw.sum(dtype=torch.float64).reshape(1))
         q = q_raw + ((self.total_charge - qsum) / self.n_all).to(torch.float32)
-        qh = self._halo_forward(torch.stack([q, h], 1), torch.empty(self.n_local, 2, device=self.device))
-        gq_sum = self.comm.all_reduce_sum(self.backend.pair(qh[:, 0].contiguous(), qh[:, 1].contiguous()))
-        F_local, E_own = self.backend.backward(gq_sum, self.n_all)
-        self.F = self._halo_reverse_add(F_local)
+        qh = torch.zeros(self.n_local, 2, device=self.device)
+        qh[: self.n0, 0], qh[: self.n0, 1] = q, h
+        self._halo_fill([qh])
+        gq_sum = self.comm.all_reduce_sum(be.pair(qh[:, 0].contiguous(), qh[:, 1].contiguous()))
+        E_own = be.heads_backward(gq_sum, self.n_all)
+        for l in reversed(range(L)):
+            be.layer_backward_post(l)
+            self._halo_fill(be.cotangent_rows(), sr_only=True)
+            be.layer_backward_attn(l)
+        self.F = be.forces()
         self.E = self.comm.all_reduce_sum(E_own)
         self.q, self.h = q, h
         return self.E, self.F
 
     def nve(self, n_steps, dt_fs):
         """Velocity Verlet on the owned atoms (forces of the current positions must be in self.F)."""
-        s = (0.5 * dt_fs * ACC_UNIT / self.m)[:, None]
         for _ in range(n_steps):
+            s = (0.5 * dt_fs * ACC_UNIT / self.m)[:, None]
             self.V += s * self.F
             self.R[: self.n0] += dt_fs * self.V
             self.compute()
@@ -527,7 +591,7 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
                 "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "config": {"workload": f"{args.workload}: {N} atoms periodic water, cutoffs 4.5/12 A, skin {args.skin} A, NVE dt 0.5 fs from 300 K",
-                           "atoms": N, "decomposition": f"{world} slabs along axis {dom.geo.axis}, halo {N_SHELLS} x {dom.geo.shell:.1f} A",
+                           "atoms": N, "decomposition": f"{world} slabs along axis {dom.geo.axis}, halo {dom.geo.lr_radius:.1f} A (features: {dom.geo.shell:.1f} A)",
                            "local_atoms_sum_over_ranks": int(nloc[0]), "list_rebuilds_in_timed_steps": rebuilds,
                            "l2_policy": "inputs larger than L2" if N / world > 200000 else "inputs smaller than L2; no flush",
                            "ns_per_day": round(args.steps / (ms * 1e-3) * 0.0432, 3)},

@@ -26,66 +26,94 @@ def _min_image(d, cell):
 
 
 class ToyBackend:
-    """E = sum_i a_i^2 + sum_{i<j} q_i q_j chi(r_ij), a_i = sum_j psi(r_ij) over the 4.5 A shell, q_i = tanh(a_i) shifted
-    so that the charges sum to zero.  Implements the forward / pair / backward protocol of so3lr_b200.domain backends."""
+    """Stand-in with the dependency structure of the real evaluation: two message-passing layers over the 4.5 A shell
+    (x_{l+1}[i] = x_l[i] + sum_j psi(r_ij) tanh(x_l[j])), a per-atom energy x_L^2, raw charges tanh(x_L) made neutral
+    globally, and a pair term sum_{i<j} q_i q_j chi(r_ij) over the long range.  Implements the backend protocol of
+    so3lr_b200.domain: everything is evaluated for the owned atoms only, by gathering from owned and ghost rows."""
+    num_layers = 2
 
-    def __init__(self):
-        self.n_set = 0
-
-    def set_atoms(self, Z_local, shells, cell_local):
-        self.shells = [int(v) for v in shells]
+    def set_atoms(self, Z_local, counts, cell_local):
+        self.n0, self.n1, self.n = [int(v) for v in counts]
         self.cell = torch.tensor(np.asarray(cell_local), dtype=torch.float64)
-        self.n_set += 1
+        self.x = [torch.ones(self.n, 1, dtype=torch.float64) for _ in range(self.num_layers + 1)]
+        self.G = torch.zeros(self.n, 1, dtype=torch.float64)
 
     @staticmethod
     def psi(r):
         return torch.where(r < RC_SR, (1 - r / RC_SR) ** 3, torch.zeros_like(r))
 
     @staticmethod
+    def dpsi(r):
+        return torch.where(r < RC_SR, -3 * (1 - r / RC_SR) ** 2 / RC_SR, torch.zeros_like(r))
+
+    @staticmethod
     def chi(r):
         return torch.where(r < RC_LR, (1 - r / RC_LR) ** 3 / (1 + r), torch.zeros_like(r))
 
-    def forward(self, R_local):
-        n0 = self.shells[0]
-        self.R = R_local.detach().to(torch.float64).requires_grad_(True)
-        d = _min_image(self.R[None, :, :] - self.R[:n0, None, :], self.cell)
-        r = d.norm(dim=-1)
-        mask = torch.ones_like(r, dtype=torch.bool)
-        mask[torch.arange(n0), torch.arange(n0)] = False
-        self.r = torch.where(mask, r, torch.full_like(r, 1e3))
-        self.a = self.psi(self.r).sum(1)
-        self.q_raw = torch.tanh(self.a)
-        return self.q_raw.detach().float(), self.a.detach().abs().float()
+    @staticmethod
+    def dchi(r):
+        return torch.where(r < RC_LR, -3 * (1 - r / RC_LR) ** 2 / RC_LR / (1 + r) - (1 - r / RC_LR) ** 3 / (1 + r) ** 2,
+                           torch.zeros_like(r))
+
+    def begin(self, R_local):
+        n0 = self.n0
+        R = R_local.detach().to(torch.float64)
+        self.d = _min_image(R[None, :, :] - R[:n0, None, :], self.cell)          # (n0, n, 3): R_j - R_i
+        r = self.d.norm(dim=-1)
+        r[torch.arange(n0), torch.arange(n0)] = 1e3
+        self.r = r
+        self.F = torch.zeros(n0, 3, dtype=torch.float64)
+        for x in self.x:
+            x.fill_(1.0)
+
+    def layer_forward(self, l):
+        n0 = self.n0
+        msg = (self.psi(self.r) * torch.tanh(self.x[l][:, 0])[None, :]).sum(1)
+        self.x[l + 1][:n0, 0] = self.x[l][:n0, 0] + msg
+
+    def feature_rows(self, l):
+        return [self.x[l]]
+
+    def heads(self):
+        xL = self.x[-1][: self.n0, 0]
+        return torch.tanh(xL).float(), xL.abs().float()
 
     def pair(self, q_local, h_local):
-        n0 = self.shells[0]
-        self.q_in = q_local.detach().to(torch.float64)
-        qi = self.q_in[:n0].clone().requires_grad_(True)
-        # derivatives that land on the owned atom, full weight; partner values are constants
-        e_side = (qi[:, None] * self.q_in[None, :] * self.chi(self.r)).sum()
-        self.gq, = torch.autograd.grad(e_side, qi, retain_graph=True)
-        self.e_side = e_side
+        n0 = self.n0
+        q = q_local.detach().to(torch.float64)
+        chi = self.chi(self.r)
+        self.e_pair_half = 0.5 * (q[:n0, None] * q[None, :] * chi).sum()
+        self.gq = (q[None, :] * chi).sum(1)                                        # dE/dq_i over all pairs of i
+        s = (q[:n0, None] * q[None, :] * self.dchi(self.r) / self.r)[..., None] * self.d
+        self.F += s.sum(1)                                                         # F_i = +dE_ij/d(R_j - R_i)
         return self.gq.sum().reshape(1)
 
-    def backward(self, gq_sum_all, n_all):
-        n0 = self.shells[0]
+    def heads_backward(self, gq_sum_all, n_all):
+        n0 = self.n0
+        xL = self.x[-1][:n0, 0]
         gq_raw = self.gq - gq_sum_all / n_all
-        # owned energy: a_i^2 + half of every pair the atom takes part in
-        E_own = (self.a ** 2).sum() + 0.5 * self.e_side.detach()
-        # gradient w.r.t. local positions: network part (through a and through q_raw with its cotangent) + pair geometry
-        qi_const = self.q_in[:n0]
-        pair_geom = (qi_const[:, None] * self.q_in[None, :] * self.chi(self.r)).sum()   # i-side: d/dR_i of all pairs of i
-        # d(pair_geom)/dR_j for ghosts j must not be counted here (the owner of j does it): subtract by detaching R_j
-        Rj = self.R.detach()
-        d2 = _min_image(Rj[None, :, :] - self.R[:n0, None, :], self.cell)
-        r2 = d2.norm(dim=-1)
-        mask = torch.ones_like(r2, dtype=torch.bool)
-        mask[torch.arange(n0), torch.arange(n0)] = False
-        r2 = torch.where(mask, r2, torch.full_like(r2, 1e3))
-        pair_i_side = (qi_const[:, None] * self.q_in[None, :] * self.chi(r2)).sum()
-        loss = (self.a ** 2).sum() + (self.q_raw * gq_raw.detach()).sum() + pair_i_side
-        g, = torch.autograd.grad(loss, self.R)
-        return (-g).float(), E_own.reshape(1)
+        self.g = 2 * xL + gq_raw * (1 - torch.tanh(xL) ** 2)                        # cotangent of x_L, owned atoms
+        return ((xL ** 2).sum() + self.e_pair_half).reshape(1)
+
+    def layer_backward_post(self, l):
+        self.G.zero_()
+        self.G[: self.n0, 0] = self.g
+
+    def cotangent_rows(self):
+        return [self.G]
+
+    def layer_backward_attn(self, l):
+        n0 = self.n0
+        G, x = self.G[:, 0], self.x[l][:, 0]
+        t = torch.tanh(x)
+        psi, dpsi = self.psi(self.r), self.dpsi(self.r)
+        # both directions of every edge, gathered towards the owned atom i
+        self.g = G[:n0] + (psi * G[None, :]).sum(1) * (1 - t[:n0] ** 2)
+        coef = dpsi * (G[:n0, None] * t[None, :] + G[None, :] * t[:n0, None]) / self.r   # dE/dr_ij / r
+        self.F += (coef[..., None] * self.d).sum(1)
+
+    def forces(self):
+        return self.F.float()
 
 
 def _serial_reference(R, cell):
@@ -93,10 +121,12 @@ def _serial_reference(R, cell):
     c = torch.tensor(cell, dtype=torch.float64)
     d = _min_image(R[None] - R[:, None], c)
     r = d.norm(dim=-1) + torch.eye(len(R), dtype=torch.float64) * 1e3
-    a = ToyBackend.psi(r).sum(1)
-    q = torch.tanh(a)
+    x = torch.ones(len(R), dtype=torch.float64)
+    for _ in range(ToyBackend.num_layers):
+        x = x + (ToyBackend.psi(r) * torch.tanh(x)[None, :]).sum(1)
+    q = torch.tanh(x)
     q = q - q.mean()
-    E = (a ** 2).sum() + 0.5 * (q[:, None] * q[None, :] * ToyBackend.chi(r)).sum()
+    E = (x ** 2).sum() + 0.5 * (q[:, None] * q[None, :] * ToyBackend.chi(r)).sum()
     F = -torch.autograd.grad(E, R)[0]
     return E.item(), F.numpy()
 
@@ -163,7 +193,7 @@ def test_decomposed_toy_model_matches_single_domain(tmp_path, world):
     np.testing.assert_allclose(d, 0, atol=1e-4)
 
 
-def test_slab_selection_covers_every_neighbour_within_three_shells():
+def test_slab_selection_holds_every_partner_of_an_owned_atom():
     R, cell = _problem(seed=5, n=400)
     geo = D.SlabDecomposition(cell, 3, skin=1.0, cutoff_lr=RC_LR)
     Rt = torch.tensor(R)
@@ -171,20 +201,26 @@ def test_slab_selection_covers_every_neighbour_within_three_shells():
     owner = geo.owner(s)
     total_owned = 0
     for rank in range(3):
-        idx, shift, shell = geo.selection(rank, Rw, s)
-        n0 = int((shell == 0).sum())
+        idx, shift, cls = geo.selection(rank, Rw, s)
+        n0 = int((cls == 0).sum())
         total_owned += n0
-        assert (shell[:-1] <= shell[1:]).all()                       # owned first, then shell by shell
+        assert (cls[:-1] <= cls[1:]).all()                           # owned first, then short-range ghosts, then the rest
         assert (owner[idx[:n0]] == rank).all()
         Rl = Rw[idx].double() + shift[:, None].double() * torch.tensor(cell[geo.axis])
-        # every atom image within 4.5 + skin of an owned atom is present locally (brute force over images)
         own_pos = Rl[:n0]
+        have = {}
+        for g, k, c in zip(idx.tolist(), shift.tolist(), cls.tolist()):
+            have[(g, k)] = c
+        # every atom image within the short-range (long-range) list radius of an owned atom is present locally, and the
+        # short-range ones are classed as feature-carrying ghosts (brute force over images)
         for k in (-1, 0, 1):
             img = Rw.double() + k * torch.tensor(cell[geo.axis])
             d = (img[None] - own_pos[:, None])
             d[..., 1] -= torch.round(d[..., 1] / cell[1, 1]) * cell[1, 1]
             d[..., 2] -= torch.round(d[..., 2] / cell[2, 2]) * cell[2, 2]
-            need = torch.nonzero((d.norm(dim=-1) < geo.shell).any(0)).squeeze(1)
-            have = set(zip(idx.tolist(), shift.tolist()))
-            assert all((int(g), k) in have for g in need)
+            dist = d.norm(dim=-1)
+            for g in torch.nonzero((dist < geo.lr_radius).any(0)).squeeze(1).tolist():
+                assert (g, k) in have
+            for g in torch.nonzero((dist < geo.shell).any(0)).squeeze(1).tolist():
+                assert have[(g, k)] <= 1
     assert total_owned == len(R)
