@@ -393,6 +393,11 @@ class DomainSystem:
         """Fill the ghost rows of each (n_local, d) tensor from the owners' rows (rows [0, n0) are the owned ones)."""
         send_slots = self.send_sr if sr_only else self.send_slots
         recv_slots = self.recv_sr if sr_only else self.recv_slots
+        ev = None
+        if getattr(self, "time_halo", False) and self.device.type == "cuda":      # device time of the exchanges, for the benchmark
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
+            self._halo_events.append(ev)
         width = [t.shape[1] for t in tensors]
         me = self.rank
         sends = {p: torch.cat([t[sl] for t in tensors], 1) for p, sl in send_slots.items() if p != me}
@@ -406,6 +411,8 @@ class DomainSystem:
                 o += w
         for t in tensors:                                   # own periodic images
             t[recv_slots[me]] = t[send_slots[me]]
+        if ev is not None:
+            ev[1].record()
 
     # ---- evaluation ----
     def _maybe_rebuild(self):
@@ -414,9 +421,16 @@ class DomainSystem:
         if not torch.isfinite(d2).all():
             raise RuntimeError("non-finite positions")
         if float(d2) > (0.5 * self.skin) ** 2 or self.skin <= 0:
+            import time
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            t0 = time.perf_counter()
             R_all = self.gather_global(self.R[: self.n0])
             V_all = None if self.V is None else self.gather_global(self.V)
             self._partition(R_all, V_all)
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            self.t_repartition = getattr(self, "t_repartition", 0.0) + time.perf_counter() - t0
             return True
         return False
 
@@ -551,10 +565,13 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
     rebuilds = dom.n_rebuilds - rb0
     # kernel times of rank 0's share over another K steps
     backend.sys.profile(True)
+    dom.time_halo, dom._halo_events = True, []
     for _ in range(args.steps):
         dom.nve(1, dt)
     prof = backend.sys.profile_read()
     backend.sys.profile(False)
+    dom.time_halo = False
+    halo_ms = sum(a.elapsed_time(b) for a, b in dom._halo_events) / args.steps
     st = backend.stats()
     # end to end with host buffers: every rank uploads all positions, forces come back summed over the ranks
     Rh = dom.gather_global(dom.R[: dom.n0]).cpu().numpy()
@@ -586,6 +603,7 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
         roofline = {"kernel": top, "bound": "hbm", "achieved": round(ach, 1), "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s",
                     "frac": round(ach / peak, 4), "traffic": args.traffic, "algorithmic_bytes_per_launch": ab,
                     "ms_per_launch": round(t_launch, 4), "scope": "rank 0's sub-box (local atoms incl. ghosts)",
+                    "halo_exchange_ms_per_step": round(halo_ms, 3),
                     "groups_ms_per_step": {g: round(v[0] / args.steps, 4) for g, v in sorted(groups.items(), key=lambda kv: -kv[1][0])}}
         line = {"metric": "atom-steps/s (E+F)", "value": round(value, 1), "unit": "atom-steps/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
@@ -593,6 +611,7 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
                 "config": {"workload": f"{args.workload}: {N} atoms periodic water, cutoffs 4.5/12 A, skin {args.skin} A, NVE dt 0.5 fs from 300 K",
                            "atoms": N, "decomposition": f"{world} slabs along axis {dom.geo.axis}, halo {dom.geo.lr_radius:.1f} A (features: {dom.geo.shell:.1f} A)",
                            "local_atoms_sum_over_ranks": int(nloc[0]), "list_rebuilds_in_timed_steps": rebuilds,
+                           "repartition_ms_each": round(1e3 * getattr(dom, "t_repartition", 0.0) / max(1, dom.n_rebuilds - 1), 2),
                            "l2_policy": "inputs larger than L2" if N / world > 200000 else "inputs smaller than L2; no flush",
                            "ns_per_day": round(args.steps / (ms * 1e-3) * 0.0432, 3)},
                 "e2e": {"value": round(N * args.steps / t_e2e, 1), "unit": "atom-steps/s", "h2d_bytes_per_step": N * 12 * world,
