@@ -2,6 +2,7 @@
 #include "../../include/so3lr_b200.h"
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <limits>
 #include <vector>
@@ -358,6 +359,27 @@ int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, co
   return kOk;
 }
 
+// SO3LR_B200_ATTENTION=simt selects the FP32 shared-memory filter GEMMs instead of the tensor-core ones (for comparison runs)
+bool use_mma_attention() {
+  static const bool v = [] {
+    const char* e = std::getenv("SO3LR_B200_ATTENTION");
+    return !(e && std::strcmp(e, "simt") == 0);
+  }();
+  return v;
+}
+void attn_fwd_dispatch(cudaStream_t st, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+                       const float* qkv, const float* x_in, const float* ev_in, float* xa, float* ev1) {
+  if (L.has_spherical && use_mma_attention()) launch_attn_fwd_mma(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
+  else launch_attn_fwd_sym(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
+}
+void attn_bwd_dispatch(cudaStream_t st, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+                       const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv, float* gev_in, float* F,
+                       int first_layer) {
+  if (!first_layer && L.has_spherical && use_mma_attention())
+    launch_attn_bwd_mma(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F);
+  else launch_attn_bwd_sym(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F, first_layer);
+}
+
 // ---- positions -> forces (gather-only kernels on the symmetric short-range list) ----
 // Atom slots are ordered by how far their features are needed: [0, n0) atoms whose energy is evaluated here ("owned"),
 // [n0, n1) atoms within one interaction shell of them, [n1, n2) within two, [n2, n3) within three.  Layer l of the
@@ -383,7 +405,7 @@ int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const S
     const LayerDev& L = M.layer[l];
     S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], nsend[l], S->qkv[l]); S->prof.end(st);
     S->prof.begin(kPAttnFwd, st);
-    launch_attn_fwd_sym(st, L, nrecv[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
+    attn_fwd_dispatch(st, L, nrecv[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
     S->prof.end(st);
     S->prof.begin(kPPostFwd, st);
     launch_atom_post_fwd(st, L, nrecv[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]);
@@ -421,7 +443,7 @@ int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float
       fill(st, S->gev1 + (size_t)npost[l] * kMTot, (size_t)(c.n3 - npost[l]) * kMTot, 0.f);
     }
     S->prof.begin(kPAttnBwd, st);
-    launch_attn_bwd_sym(st, L, nattn[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, F, l == 0 ? 1 : 0);
+    attn_bwd_dispatch(st, L, nattn[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, F, l == 0 ? 1 : 0);
     S->prof.end(st);
     S->n_launches += 2;
     if (l > 0) {
@@ -487,6 +509,7 @@ SO3LR_B200_API int so3lr_b200_model_create(const float* blob_host, size_t n_floa
   if (rc == kOk) rc = configure_atom_kernels();
   if (rc == kOk) rc = configure_attention_kernels();
   if (rc == kOk) rc = configure_attention_sym_kernels();
+  if (rc == kOk) rc = configure_attention_mma_kernels();
   if (rc != kOk) { so3lr_b200_model_destroy(m); return rc; }
   *out = m;
   return kOk;
@@ -840,7 +863,7 @@ SO3LR_B200_API int so3lr_b200_dd_layer_forward(so3lr_b200_system* S, void* strea
   const LayerDev& L = S->model->M.layer[l];
   S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], n1, S->qkv[l]); S->prof.end(st);
   S->prof.begin(kPAttnFwd, st);
-  launch_attn_fwd_sym(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
+  attn_fwd_dispatch(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
   S->prof.end(st);
   S->prof.begin(kPPostFwd, st);
   launch_atom_post_fwd(st, L, n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]);
@@ -922,8 +945,8 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_attn(so3lr_b200_system* S, void*
   const int n0 = S->shells[0], l = layer;
   const LayerDev& L = S->model->M.layer[l];
   S->prof.begin(kPAttnBwd, st);
-  launch_attn_bwd_sym(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, S->dd_gev_in, S->F_s,
-                      l == 0 ? 1 : 0);
+  attn_bwd_dispatch(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, S->dd_gev_in, S->F_s,
+                    l == 0 ? 1 : 0);
   S->prof.end(st);
   S->n_launches += 1;
   if (l > 0) {

@@ -43,6 +43,16 @@ void launch_attn_bwd_sym(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
                          const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv, float* gev_in,
                          float* F, int first_layer);
 
+// ---- attention_mma.cu ----
+// Same contracts as the *_sym launchers, for layers with a spherical filter (L.has_spherical): the per-edge filter
+// contractions run as FP16-split tensor-core MMAs with FP32-level accuracy.
+int configure_attention_mma_kernels();
+void launch_attn_fwd_mma(cudaStream_t s, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+                         const float* qkv, const float* x_in, const float* ev_in, float* xa, float* ev1);
+void launch_attn_bwd_mma(cudaStream_t s, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+                         const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv, float* gev_in,
+                         float* F);
+
 // ---- pair_kernels.cu ----
 // dR for every short-range edge from positions (+ minimum image), ZBL energy into e_atom[centre], ZBL gradient
 // written to g_dR (initialises it) when g_dR is given, and/or added straight into the forces F_direct (F_i += g,
