@@ -367,6 +367,34 @@ bool use_mma_attention() {
   }();
   return v;
 }
+// SO3LR_B200_DENSE=simt selects the FP32 shared-memory versions of the per-atom dense blocks
+bool use_mma_dense() {
+  static const bool v = [] {
+    const char* e = std::getenv("SO3LR_B200_DENSE");
+    return !(e && std::strcmp(e, "simt") == 0);
+  }();
+  return v;
+}
+void post_fwd_dispatch(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, float* z1, float* x3, float* gate,
+                       float* x4, float* ev2) {
+  if (use_mma_dense()) launch_atom_post_fwd_mma(s, L, n, xa, ev1, z1, x3, gate, x4, ev2);
+  else launch_atom_post_fwd(s, L, n, xa, ev1, z1, x3, gate, x4, ev2);
+}
+void post_bwd_dispatch(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, const float* z1, const float* x3,
+                       const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1) {
+  if (use_mma_dense()) launch_atom_post_bwd_mma(s, L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1);
+  else launch_atom_post_bwd(s, L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1);
+}
+void heads_fwd_dispatch(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* x, float* ze, float* zq, float* zh,
+                        float* e_nn, float* q_raw, float* hv) {
+  if (use_mma_dense()) launch_heads_fwd_mma(s, M, n, Z, x, ze, zq, zh, e_nn, q_raw, hv);
+  else launch_heads_fwd(s, M, n, Z, x, ze, zq, zh, e_nn, q_raw, hv);
+}
+void heads_bwd_dispatch(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* ze, const float* zq, const float* zh,
+                        const float* hv, const float* ge, const float* gq, const float* gh, float* gx) {
+  if (use_mma_dense()) launch_heads_bwd_mma(s, M, n, Z, ze, zq, zh, hv, ge, gq, gh, gx);
+  else launch_heads_bwd(s, M, n, Z, ze, zq, zh, hv, ge, gq, gh, gx);
+}
 void attn_fwd_dispatch(cudaStream_t st, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
                        const float* qkv, const float* x_in, const float* ev_in, float* xa, float* ev1) {
   if (L.has_spherical && use_mma_attention()) launch_attn_fwd_mma(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
@@ -408,12 +436,12 @@ int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const S
     attn_fwd_dispatch(st, L, nrecv[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
     S->prof.end(st);
     S->prof.begin(kPPostFwd, st);
-    launch_atom_post_fwd(st, L, nrecv[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]);
+    post_fwd_dispatch(st, L, nrecv[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]);
     S->prof.end(st);
     S->n_launches += 3;
   }
   S->prof.begin(kPHeads, st);
-  launch_heads_fwd(st, M, c.n0, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv);
+  heads_fwd_dispatch(st, M, c.n0, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv);
   S->prof.end(st);
   S->n_launches += 1;
   SO3LR_CUDA_CHECK(cudaGetLastError());
@@ -427,7 +455,7 @@ int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float
   const int npost[kNumLayers] = {c.n2, c.n1, c.n0};   // atoms whose layer-l outputs carry a cotangent
   const int nattn[kNumLayers] = {c.n3, c.n2, c.n1};   // atoms that receive a cotangent through layer l's attention
   S->prof.begin(kPHeads, st);
-  launch_heads_bwd(st, M, c.n0, S->d_Z, S->ze, S->zq, S->zh, S->hv, S->ones, S->gq_raw, S->gh, S->g4);
+  heads_bwd_dispatch(st, M, c.n0, S->d_Z, S->ze, S->zq, S->zh, S->hv, S->ones, S->gq_raw, S->gh, S->g4);
   S->prof.end(st);
   float* gev2 = S->gev_a;
   float* gev_in = S->gev_b;
@@ -436,7 +464,7 @@ int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float
   for (int l = kNumLayers - 1; l >= 0; --l) {
     const LayerDev& L = M.layer[l];
     S->prof.begin(kPPostBwd, st);
-    launch_atom_post_bwd(st, L, npost[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, gev2, S->g_xa, S->gev1);
+    post_bwd_dispatch(st, L, npost[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, gev2, S->g_xa, S->gev1);
     S->prof.end(st);
     if (c.n3 > npost[l]) {   // atoms beyond the layer's receivers have no cotangent of their own (any of them can be a neighbour)
       fill(st, S->g_xa + (size_t)npost[l] * kF, (size_t)(c.n3 - npost[l]) * kF, 0.f);
@@ -510,6 +538,7 @@ SO3LR_B200_API int so3lr_b200_model_create(const float* blob_host, size_t n_floa
   if (rc == kOk) rc = configure_attention_kernels();
   if (rc == kOk) rc = configure_attention_sym_kernels();
   if (rc == kOk) rc = configure_attention_mma_kernels();
+  if (rc == kOk) rc = configure_atom_mma_kernels();
   if (rc != kOk) { so3lr_b200_model_destroy(m); return rc; }
   *out = m;
   return kOk;
@@ -866,7 +895,7 @@ SO3LR_B200_API int so3lr_b200_dd_layer_forward(so3lr_b200_system* S, void* strea
   attn_fwd_dispatch(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
   S->prof.end(st);
   S->prof.begin(kPPostFwd, st);
-  launch_atom_post_fwd(st, L, n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]);
+  post_fwd_dispatch(st, L, n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]);
   S->prof.end(st);
   S->n_launches += 3;
   SO3LR_CUDA_CHECK(cudaGetLastError());
@@ -879,7 +908,7 @@ SO3LR_B200_API int so3lr_b200_dd_heads(so3lr_b200_system* S, void* stream, float
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0];
   S->prof.begin(kPHeads, st);
-  launch_heads_fwd(st, S->model->M, n0, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv);
+  heads_fwd_dispatch(st, S->model->M, n0, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv);
   S->prof.end(st);
   SO3LR_CUDA_CHECK(cudaMemcpyAsync(q_raw_owned_dev, S->q_raw, (size_t)n0 * sizeof(float), cudaMemcpyDeviceToDevice, st));
   abs_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->hv, h_owned_dev);
@@ -914,7 +943,7 @@ SO3LR_B200_API int so3lr_b200_dd_heads_backward(so3lr_b200_system* S, void* stre
   combine_energy_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom);
   if (energy_owned_dev) sum_to_double_kernel<<<1, 1024, 0, st>>>(n0, S->e_atom, energy_owned_dev);
   S->prof.begin(kPHeads, st);
-  launch_heads_bwd(st, S->model->M, n0, S->d_Z, S->ze, S->zq, S->zh, S->hv, S->ones, S->gq_raw, S->gh, S->g4);
+  heads_bwd_dispatch(st, S->model->M, n0, S->d_Z, S->ze, S->zq, S->zh, S->hv, S->ones, S->gq_raw, S->gh, S->g4);
   S->prof.end(st);
   S->dd_gev2 = S->gev_a; S->dd_gev_in = S->gev_b;
   fill(st, S->dd_gev2, (size_t)n0 * kMTot, 0.f);
@@ -930,7 +959,7 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_post(so3lr_b200_system* S, void*
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0], l = layer;
   S->prof.begin(kPPostBwd, st);
-  launch_atom_post_bwd(st, S->model->M.layer[l], n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, S->dd_gev2, S->g_xa, S->gev1);
+  post_bwd_dispatch(st, S->model->M.layer[l], n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, S->dd_gev2, S->g_xa, S->gev1);
   S->prof.end(st);
   S->n_launches += 1;
   SO3LR_CUDA_CHECK(cudaGetLastError());

@@ -18,6 +18,17 @@ void launch_heads_fwd(cudaStream_t s, const ModelDev& M, int n, const int* Z, co
 void launch_heads_bwd(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* ze, const float* zq, const float* zh,
                       const float* hv, const float* ge, const float* gq, const float* gh, float* gx);
 
+// ---- atom_kernels_mma.cu: the same four blocks with their contractions as FP16-split tensor-core MMAs ----
+int configure_atom_mma_kernels();
+void launch_atom_post_fwd_mma(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, float* z1, float* x3,
+                              float* gate, float* x4, float* ev2);
+void launch_atom_post_bwd_mma(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, const float* z1,
+                              const float* x3, const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1);
+void launch_heads_fwd_mma(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* x, float* ze, float* zq, float* zh,
+                          float* e_nn, float* q_raw, float* hv);
+void launch_heads_bwd_mma(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* ze, const float* zq, const float* zh,
+                          const float* hv, const float* ge, const float* gq, const float* gh, float* gx);
+
 // ---- attention.cu ----
 // Short-range edges are grouped by receiver: edges row_ptr[i] .. row_ptr[i+1]-1 belong to centre i and hold the
 // neighbour index nbr_j[e] and the displacement dR[e] (3 floats).  Edges with |dR| >= 4.5, |dR| == 0 or

@@ -1,6 +1,8 @@
 // Host-side preparation of the SO3LR weights: radial-filter tables, transposed kernels, ZBL constants.
 #include "model.h"
 
+#include <cuda_fp16.h>
+
 #include <cmath>
 #include <cstring>
 #include <vector>
@@ -72,6 +74,30 @@ void radial_filters(const float* blob, const BlobOffsets& O, int layer, double r
       }
     }
   }
+}
+
+// FP16 pair (x, y) and the pair of their residuals scaled by 2048, as the device code splits its operands
+void split2_host(float x, float y, unsigned& hi, unsigned& lo) {
+  const __half hx = __float2half_rn(x), hy = __float2half_rn(y);
+  const __half lx = __float2half_rn((x - __half2float(hx)) * 2048.f), ly = __float2half_rn((y - __half2float(hy)) * 2048.f);
+  auto bits = [](__half h) { unsigned short u; std::memcpy(&u, &h, 2); return (unsigned)u; };
+  hi = bits(hx) | (bits(hy) << 16);
+  lo = bits(lx) | (bits(ly) << 16);
+}
+// B[k][n] (K x N, row-major; transpose = read W as [N][K]) -> fragment order of mma.m16n8k16 (.col B operand)
+std::vector<float> pack_fragments(const float* W, int K, int N, bool transpose) {
+  std::vector<float> out((size_t)(K / 16) * (N / 8) * 32 * 4);
+  auto B = [&](int k, int n) { return transpose ? W[(size_t)n * K + k] : W[(size_t)k * N + n]; };
+  for (int ks = 0; ks < K / 16; ++ks)
+    for (int nt = 0; nt < N / 8; ++nt)
+      for (int lane = 0; lane < 32; ++lane) {
+        const int g = lane >> 2, q = lane & 3, n = 8 * nt + g, k0 = 16 * ks + 2 * q;
+        unsigned v[4];
+        split2_host(B(k0, n), B(k0 + 1, n), v[0], v[2]);
+        split2_host(B(k0 + 8, n), B(k0 + 9, n), v[1], v[3]);
+        std::memcpy(&out[(((size_t)ks * (N / 8) + nt) * 32 + lane) * 4], v, 16);
+      }
+  return out;
 }
 
 struct Uploader {
@@ -172,6 +198,10 @@ int build_model(const float* blob, size_t n_floats, ModelDev* M, std::vector<voi
         else ig[(i - 128) * 4 + (o - 128)] = v;
       }
     D.ex_xx = U.up(xx); D.ex_xxT = U.upT(xx.data(), 128, 128);
+    auto frag = [&](const float* W, int K, int N, bool tr) { return reinterpret_cast<const uint4*>(U.up(pack_fragments(W, K, N, tr))); };
+    D.res1_f = frag(blob + L.res1_k, kF, kF, false); D.res1T_f = frag(blob + L.res1_k, kF, kF, true);
+    D.res2_f = frag(blob + L.res2_k, kF, kF, false); D.res2T_f = frag(blob + L.res2_k, kF, kF, true);
+    D.exxx_f = frag(xx.data(), kF, kF, false); D.exxxT_f = frag(xx.data(), kF, kF, true);
     D.ex_xg = U.up(xg); D.ex_ix = U.up(ix); D.ex_ig = U.up(ig);
     D.ex_bx = U.up(blob + L.exch_b, 128); D.ex_bg = U.up(blob + L.exch_b + 128, 4);
   }
@@ -188,6 +218,14 @@ int build_model(const float* blob, size_t n_floats, ModelDev* M, std::vector<voi
   M->h_reg_b = U.up(blob + O.h_reg_b, 64);
   M->h_fin_k = U.up(blob + O.h_fin_k, 64 * 64); M->h_fin_kT = U.upT(blob + O.h_fin_k, 64, 64);
   M->h_fin_b = U.up(blob + O.h_fin_b, 64);
+  {
+    auto frag = [&](const float* W, int K, int N, bool tr) { return reinterpret_cast<const uint4*>(U.up(pack_fragments(W, K, N, tr))); };
+    // transposed kernels: B[k][n] = W[n][k] with W stored [N_in = n][K_out = k]
+    M->e_reg_f = frag(blob + O.e_reg_k, kF, kF, false); M->e_regT_f = frag(blob + O.e_reg_k, kF, kF, true);
+    M->q_reg_f = frag(blob + O.q_reg_k, kF, kF, false); M->q_regT_f = frag(blob + O.q_reg_k, kF, kF, true);
+    M->h_reg_f = frag(blob + O.h_reg_k, kF, 64, false); M->h_regT_f = frag(blob + O.h_reg_k, 64, kF, true);
+    M->h_fin_f = frag(blob + O.h_fin_k, 64, 64, false); M->h_finT_f = frag(blob + O.h_fin_k, 64, 64, true);
+  }
   // ZBL constants: softplus of the raw parameters, weights normalised to one
   double a[4], c[4], cs = 0.0;
   for (int k = 0; k < 4; ++k) { a[k] = softplus_d(blob[O.zbl[k]]); c[k] = softplus_d(blob[O.zbl[4 + k]]); cs += c[k]; }

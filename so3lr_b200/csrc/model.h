@@ -17,6 +17,9 @@ struct LayerDev {
   const float *ln1_s, *ln1_b, *ln2_s, *ln2_b;
   const float *res1_k, *res1_kT, *res1_b, *res2_k, *res2_kT, *res2_b;   // [in][out] and transposed
   const float *ex_xx, *ex_xxT;  // [128][128] features -> features
+  // the same dense kernels as tensor-core B operands: FP16 hi / scaled-lo pairs in mma.m16n8k16 fragment order,
+  // [K/16][N/8][32 lanes] x {b0hi, b1hi, b0lo, b1lo} (see atom_kernels_mma.cu); "T" = transposed kernel (reverse pass)
+  const uint4 *res1_f, *res1T_f, *res2_f, *res2T_f, *exxx_f, *exxxT_f;
   const float* ex_xg;           // [128][4]   features -> gates
   const float* ex_ix;           // [4][128]   invariants -> features
   const float* ex_ig;           // [4][4]     invariants -> gates
@@ -36,6 +39,7 @@ struct ModelDev {
   float q_fin_b;
   // Hirshfeld head
   const float *h_embed0, *h_embed1, *h_reg_k, *h_reg_kT, *h_reg_b, *h_fin_k, *h_fin_kT, *h_fin_b;
+  const uint4 *e_reg_f, *e_regT_f, *q_reg_f, *q_regT_f, *h_reg_f, *h_regT_f, *h_fin_f, *h_finT_f;   // fragment-order copies
   // charge / spin embeddings (only evaluated when a graph carries charge or unpaired electrons)
   const float *cs_embed_q[2], *cs_embed_k[2], *cs_embed_v[2], *cs_res0[2], *cs_res1[2];
   ZblParams zbl;
