@@ -195,6 +195,8 @@ struct so3lr_b200_system {
   int n = 0, n_graphs = 1;
   int n_cap = 0;                 // atoms the per-atom arrays were allocated for
   int shells[4] = {0, 0, 0, 0};  // domain-decomposed evaluation: owned | + short-range ghosts | (unused) | all local atoms
+  SpeciesTables sp{};            // per-element-pair tables of the first layer
+  float* GV = nullptr;           // n_cap x 32 scratch of the tabulated first-layer reverse pass
   float *dd_gev2 = nullptr, *dd_gev_in = nullptr;   // ping-pong cotangents of ev between the layers of the reverse pass
   so3lr_b200_options opt{};
   Cell cell{};
@@ -368,6 +370,14 @@ bool use_mma_attention() {
   return v;
 }
 // SO3LR_B200_DENSE=simt selects the FP32 shared-memory versions of the per-atom dense blocks
+// SO3LR_B200_LAYER0=generic evaluates the first layer with the generic attention kernels instead of the element-pair tables
+bool use_layer0_tables() {
+  static const bool v = [] {
+    const char* e = std::getenv("SO3LR_B200_LAYER0");
+    return !(e && std::strcmp(e, "generic") == 0);
+  }();
+  return v;
+}
 bool use_mma_dense() {
   static const bool v = [] {
     const char* e = std::getenv("SO3LR_B200_DENSE");
@@ -427,14 +437,21 @@ int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const S
   launch_sr_geometry_zbl(st, M, S->cell, c.n3, S->sr.count, edge_i, nbr_j, S->d_Z, R, 0, S->dR, S->e_zbl, nullptr, nullptr, F,
                          owned_side_only ? c.n0 : -1);
   S->prof.end(st);
-  launch_embed(st, M, S->d_Z, c.n3, S->x[0]);
+  const bool tab0 = S->sp.n_species > 0 && use_layer0_tables();
+  if (!tab0) launch_embed(st, M, S->d_Z, c.n3, S->x[0]);
   S->n_launches += 4;
   for (int l = 0; l < kNumLayers; ++l) {
     const LayerDev& L = M.layer[l];
-    S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], nsend[l], S->qkv[l]); S->prof.end(st);
-    S->prof.begin(kPAttnFwd, st);
-    attn_fwd_dispatch(st, L, nrecv[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
-    S->prof.end(st);
+    if (l == 0 && tab0) {
+      S->prof.begin(kPAttnFwd, st);
+      launch_layer0_fwd_tab(st, S->sp, M, nrecv[0], c.n3, row_ptr, nbr_j, S->dR, S->d_Z, S->xa[0], S->ev1[0]);
+      S->prof.end(st);
+    } else {
+      S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], nsend[l], S->qkv[l]); S->prof.end(st);
+      S->prof.begin(kPAttnFwd, st);
+      attn_fwd_dispatch(st, L, nrecv[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
+      S->prof.end(st);
+    }
     S->prof.begin(kPPostFwd, st);
     post_fwd_dispatch(st, L, nrecv[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]);
     S->prof.end(st);
@@ -471,7 +488,10 @@ int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float
       fill(st, S->gev1 + (size_t)npost[l] * kMTot, (size_t)(c.n3 - npost[l]) * kMTot, 0.f);
     }
     S->prof.begin(kPAttnBwd, st);
-    attn_bwd_dispatch(st, L, nattn[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, F, l == 0 ? 1 : 0);
+    if (l == 0 && S->sp.n_species > 0 && use_layer0_tables())
+      launch_layer0_bwd_tab(st, S->sp, nattn[0], c.n3, c.n3, row_ptr, nbr_j, S->dR, S->d_Z, S->g_xa, S->gev1, S->GV, F);
+    else
+      attn_bwd_dispatch(st, L, nattn[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, F, l == 0 ? 1 : 0);
     S->prof.end(st);
     S->n_launches += 2;
     if (l > 0) {
@@ -622,6 +642,7 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
   S->gev_a = A.get<float>((size_t)n * kMTot); S->gev_b = A.get<float>((size_t)n * kMTot); S->gev1 = A.get<float>((size_t)n * kMTot);
   S->g_qkv = A.get<float>((size_t)n * kProj);
   S->F_int = A.get<float>((size_t)n * 3);
+  S->GV = A.get<float>((size_t)n * 4 * kMaxTabSpecies);
   S->d_energy = A.get<double>(n_graphs); S->d_dipole = A.get<float>((size_t)n_graphs * 3);
   S->d_Rstage = A.get<float>((size_t)n * 3);
   if (A.status != kOk) { A.release(); delete S; return A.status; }
@@ -640,6 +661,7 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
             cudaStreamCreateWithFlags(&S->own_stream, cudaStreamNonBlocking) == cudaSuccess;
   if (!ok) { so3lr_b200_system_destroy(S); return kCudaError; }
   fill(nullptr, S->ones, n, 1.f);
+  if (species_tables_build(nullptr, model->M, Z, n, &S->sp) != kOk) { so3lr_b200_system_destroy(S); return kCudaError; }
   cudaDeviceSynchronize();
   S->nws = nlist_workspace_create();
   *out = S;
@@ -651,6 +673,7 @@ SO3LR_B200_API int so3lr_b200_system_destroy(so3lr_b200_system* S) {
   cudaSetDevice(S->model->device);
   cudaDeviceSynchronize();
   S->pool.release();
+  species_tables_free(&S->sp);
   S->prof.destroy();
   nlist_workspace_destroy(S->nws);
   for (NeighborListDev* L : {&S->sr, &S->lrl}) { cudaFree(L->row_ptr); cudaFree(L->nbr_j); cudaFree(L->edge_i); }
@@ -844,6 +867,13 @@ SO3LR_B200_API int so3lr_b200_dd_set_atoms(so3lr_b200_system* S, int n_local, co
   S->n = n_local;
   for (int k = 0; k < 4; ++k) S->shells[k] = shells4[k];
   SO3LR_CUDA_CHECK(cudaMemcpy(S->d_Z0, Z_local_dev, (size_t)n_local * sizeof(int), cudaMemcpyDeviceToDevice));
+  {
+    std::vector<int> zh((size_t)n_local);
+    SO3LR_CUDA_CHECK(cudaMemcpy(zh.data(), Z_local_dev, (size_t)n_local * sizeof(int), cudaMemcpyDeviceToHost));
+    rc = species_tables_build(nullptr, S->model->M, zh.data(), n_local, &S->sp);
+    if (rc) return rc;
+    SO3LR_CUDA_CHECK(cudaDeviceSynchronize());
+  }
   const int gs[2] = {0, n_local};
   SO3LR_CUDA_CHECK(cudaMemcpy(S->d_graph_start, gs, sizeof(gs), cudaMemcpyHostToDevice));
   S->d_Z = S->d_Z0; S->sorted = false; S->have_lists = false;
@@ -878,7 +908,7 @@ SO3LR_B200_API int so3lr_b200_dd_begin(so3lr_b200_system* S, void* stream, const
   launch_sr_geometry_zbl(st, M, S->cell, S->n, S->sr.count, S->sr.edge_i, S->sr.nbr_j, S->d_Z, R_local_dev, 0, S->dR, S->e_zbl, nullptr, nullptr,
                          S->F_s, n0);
   S->prof.end(st);
-  launch_embed(st, M, S->d_Z, n1, S->x[0]);
+  if (!(S->sp.n_species > 0 && use_layer0_tables())) launch_embed(st, M, S->d_Z, n1, S->x[0]);
   S->n_launches += 4;
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
@@ -890,10 +920,16 @@ SO3LR_B200_API int so3lr_b200_dd_layer_forward(so3lr_b200_system* S, void* strea
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0], n1 = S->shells[1], l = layer;
   const LayerDev& L = S->model->M.layer[l];
-  S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], n1, S->qkv[l]); S->prof.end(st);
-  S->prof.begin(kPAttnFwd, st);
-  attn_fwd_dispatch(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
-  S->prof.end(st);
+  if (l == 0 && S->sp.n_species > 0 && use_layer0_tables()) {
+    S->prof.begin(kPAttnFwd, st);
+    launch_layer0_fwd_tab(st, S->sp, S->model->M, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->d_Z, S->xa[0], S->ev1[0]);
+    S->prof.end(st);
+  } else {
+    S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], n1, S->qkv[l]); S->prof.end(st);
+    S->prof.begin(kPAttnFwd, st);
+    attn_fwd_dispatch(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
+    S->prof.end(st);
+  }
   S->prof.begin(kPPostFwd, st);
   post_fwd_dispatch(st, L, n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]);
   S->prof.end(st);
@@ -974,8 +1010,11 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_attn(so3lr_b200_system* S, void*
   const int n0 = S->shells[0], l = layer;
   const LayerDev& L = S->model->M.layer[l];
   S->prof.begin(kPAttnBwd, st);
-  attn_bwd_dispatch(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, S->dd_gev_in, S->F_s,
-                    l == 0 ? 1 : 0);
+  if (l == 0 && S->sp.n_species > 0 && use_layer0_tables())
+    launch_layer0_bwd_tab(st, S->sp, n0, S->shells[1], S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->d_Z, S->g_xa, S->gev1, S->GV, S->F_s);
+  else
+    attn_bwd_dispatch(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, S->dd_gev_in, S->F_s,
+                      l == 0 ? 1 : 0);
   S->prof.end(st);
   S->n_launches += 1;
   if (l > 0) {

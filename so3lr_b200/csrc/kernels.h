@@ -64,6 +64,26 @@ void launch_attn_bwd_mma(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
                          const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv, float* gev_in,
                          float* F);
 
+// ---- layer0_tab.cu: first layer through per-element-pair tables (its inputs depend on the elements only) ----
+constexpr int kMaxTabSpecies = 8;
+struct SpeciesTables {
+  int n_species = 0;               // 0: not available (more than kMaxTabSpecies elements): use the generic kernels
+  int species[kMaxTabSpecies] = {};
+  float* table = nullptr;          // [kMaxTabSpecies^2][kTableGrid][16]
+  float* v_sp = nullptr;           // [species][128] value rows
+  int* slot = nullptr;             // [119] atomic number -> species slot
+  float* qkv_sp = nullptr;         // scratch of the build
+  float* x_sp = nullptr;
+  int* z_sp = nullptr;
+};
+int species_tables_build(cudaStream_t st, const ModelDev& M, const int* Z_host, int n, SpeciesTables* T);
+void species_tables_free(SpeciesTables* T);
+void launch_layer0_fwd_tab(cudaStream_t s, const SpeciesTables& T, const ModelDev& M, int n_recv, int n, const int* row_ptr,
+                           const int* nbr_j, const float* dR, const int* Z, float* xa, float* ev1);
+// g_xa must be valid for atoms [0, n_gv) (every possible neighbour of a receiver); GV is a scratch of n_gv x 32 floats
+void launch_layer0_bwd_tab(cudaStream_t s, const SpeciesTables& T, int n_recv, int n_gv, int n, const int* row_ptr, const int* nbr_j,
+                           const float* dR, const int* Z, const float* g_xa, const float* gev1, float* GV, float* F);
+
 // ---- pair_kernels.cu ----
 // dR for every short-range edge from positions (+ minimum image), ZBL energy into e_atom[centre], ZBL gradient
 // written to g_dR (initialises it) when g_dR is given, and/or added straight into the forces F_direct (F_i += g,
