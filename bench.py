@@ -108,6 +108,16 @@ def algorithmic_bytes(group, N, E, P):
     return None
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch and atom of each group's dominant kernel, from the ncu captures on
+# the 98,304-atom box (profiles/attn_mma_water_98k.md); traffic grows with the atom count at fixed density
+NCU_TRAFFIC_PER_ATOM = {"attn_bwd": 859.2e6 / 98304, "attn_fwd": 555.5e6 / 98304, "pair_lr": 192.9e6 / 98304}
+
+
+def ncu_traffic(group, n_atoms):
+    t = NCU_TRAFFIC_PER_ATOM.get(group)
+    return None if t is None else int(t * n_atoms)
+
+
 def run_b200(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -121,7 +131,7 @@ def run_b200(args, rank, world, local_rank):
     n_mol, box, seed = WORKLOADS[args.workload]
     if world > 1:
         from so3lr_b200 import domain
-        args.clock_sampler, args.algorithmic_bytes, args.peaks = ClockSampler, algorithmic_bytes, _peaks
+        args.clock_sampler, args.algorithmic_bytes, args.peaks, args.ncu_traffic = ClockSampler, algorithmic_bytes, _peaks, ncu_traffic
         return domain.bench_entry(args, rank, world, local_rank, n_mol, box, seed)
 
     Z, R, cell = W.water_box(n_mol, box, seed)
@@ -171,7 +181,8 @@ def run_b200(args, rank, world, local_rank):
     peak, peak_kind = _peaks()
     achieved = ab / (t_launch * 1e-3) / 1e9
     roofline = {"kernel": top, "bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "peak_kind": f"of {peak_kind}",
-                "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": args.traffic,
+                "unit": "GB/s", "frac": round(achieved / peak, 4),
+                "traffic": args.traffic if args.traffic is not None else ncu_traffic(top, N),
                 "algorithmic_bytes_per_launch": ab, "ms_per_launch": round(t_launch, 4),
                 "groups_ms_per_step": {g: round(v[0] / args.steps, 4) for g, v in sorted(groups.items(), key=lambda kv: -kv[1][0])}}
 

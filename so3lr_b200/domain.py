@@ -601,7 +601,9 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
         peak, kind = args.peaks()
         ach = ab / (t_launch * 1e-3) / 1e9
         roofline = {"kernel": top, "bound": "hbm", "achieved": round(ach, 1), "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s",
-                    "frac": round(ach / peak, 4), "traffic": args.traffic, "algorithmic_bytes_per_launch": ab,
+                    "frac": round(ach / peak, 4),
+                    "traffic": args.traffic if args.traffic is not None else args.ncu_traffic(top, dom.n0),
+                    "algorithmic_bytes_per_launch": ab,
                     "ms_per_launch": round(t_launch, 4), "scope": "rank 0's sub-box (local atoms incl. ghosts)",
                     "halo_exchange_ms_per_step": round(halo_ms, 3),
                     "groups_ms_per_step": {g: round(v[0] / args.steps, 4) for g, v in sorted(groups.items(), key=lambda kv: -kv[1][0])}}
