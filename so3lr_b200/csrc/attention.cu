@@ -39,15 +39,15 @@ __device__ __forceinline__ Hermite hermite_at(float r) {
   t -= (float)g;
   float t2 = t * t, t3 = t2 * t;
   H.g = g;
-  H.h00 = 2.f * t3 - 3.f * t2 + 1.f; H.h10 = t3 - 2.f * t2 + t; H.h01 = -2.f * t3 + 3.f * t2; H.h11 = t3 - t2;
+  H.h00 = 1.f; H.h10 = t3 - 2.f * t2 + t; H.h01 = -2.f * t3 + 3.f * t2; H.h11 = t3 - t2;
   const float ih = 1.0f / kTableH;
-  H.d00 = (6.f * t2 - 6.f * t) * ih; H.d10 = (3.f * t2 - 4.f * t + 1.f) * ih; H.d01 = (-6.f * t2 + 6.f * t) * ih;
+  H.d00 = 0.f; H.d10 = (3.f * t2 - 4.f * t + 1.f) * ih; H.d01 = (-6.f * t2 + 6.f * t) * ih;
   H.d11 = (3.f * t2 - 2.f * t) * ih;
   return H;
 }
-// table layout: [g][0][256] values, [g][1][256] slopes * spacing
+// table layout per interval g: [g][4][256] = value, slope * spacing, value difference to the next knot, next slope * spacing
 __device__ __forceinline__ void table_eval(const float* __restrict__ tab, const Hermite& H, int col, float4& w, float4* dw) {
-  const float* p0 = tab + (size_t)H.g * 512 + col;
+  const float* p0 = tab + (size_t)H.g * 1024 + col;   // interval rows: v0, h m0, v1 - v0, h m1
   float4 v0 = ld4(p0), m0 = ld4(p0 + 256), v1 = ld4(p0 + 512), m1 = ld4(p0 + 768);
   w.x = H.h00 * v0.x + H.h10 * m0.x + H.h01 * v1.x + H.h11 * m1.x;
   w.y = H.h00 * v0.y + H.h10 * m0.y + H.h01 * v1.y + H.h11 * m1.y;

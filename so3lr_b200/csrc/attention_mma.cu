@@ -73,9 +73,9 @@ __device__ __forceinline__ void hermite_weights(float r, int& g, float4& hv, flo
   g = g > kTableGrid - 2 ? kTableGrid - 2 : g;
   t -= (float)g;
   const float t2 = t * t, t3 = t2 * t;
-  hv = make_float4(2.f * t3 - 3.f * t2 + 1.f, t3 - 2.f * t2 + t, -2.f * t3 + 3.f * t2, t3 - t2);
+  hv = make_float4(1.f, t3 - 2.f * t2 + t, -2.f * t3 + 3.f * t2, t3 - t2);      // applied to (v0, h m0, v1 - v0, h m1)
   const float ih = 1.0f / kTableH;
-  hd = make_float4((6.f * t2 - 6.f * t) * ih, (3.f * t2 - 4.f * t + 1.f) * ih, (-6.f * t2 + 6.f * t) * ih, (3.f * t2 - 2.f * t) * ih);
+  hd = make_float4(0.f, (3.f * t2 - 4.f * t + 1.f) * ih, (-6.f * t2 + 6.f * t) * ih, (3.f * t2 - 2.f * t) * ih);
 }
 
 __device__ __forceinline__ void invariants(const float* __restrict__ evi, const float* __restrict__ evj, float* s) {
@@ -217,7 +217,7 @@ __device__ __forceinline__ FwEdge fw_load_edge(const float* rec, int slot, int f
   const float4 r0 = ld4(rp);
   e.hv = ld4(rp + 4);
   e.sc = r0.y;
-  const float* p0 = table + (size_t)__float_as_int(r0.z) * 512 + f * kF + col;
+  const float* p0 = table + (size_t)__float_as_int(r0.z) * 1024 + f * kF + col;
   e.v0 = ld4(p0); e.m0 = ld4(p0 + 256); e.v1 = ld4(p0 + 512); e.m1 = ld4(p0 + 768);
   const float* kj = qkv + (size_t)__float_as_int(r0.x) * kProj;
   e.kf = ld4(kj + (f ? 4 * kF : kF) + col);
@@ -233,7 +233,7 @@ __device__ __forceinline__ BwEdge bw_load_edge(const float* rec, int slot, int f
   e.hv = ld4(rp + 4); e.hd = ld4(rp + 8);
   e.sc = r0.y; e.dcn = r0.w;
   const int j2 = __float_as_int(r0.x);
-  const float* p0 = table + (size_t)__float_as_int(r0.z) * 512 + f * kF + col;
+  const float* p0 = table + (size_t)__float_as_int(r0.z) * 1024 + f * kF + col;
   e.v0 = ld4(p0); e.m0 = ld4(p0 + 256); e.v1 = ld4(p0 + 512); e.m1 = ld4(p0 + 768);
   const float* kj = qkv + (size_t)j2 * kProj + f * 3 * kF;
   e.qj = ld4(kj + col); e.kj = ld4(kj + kF + col);

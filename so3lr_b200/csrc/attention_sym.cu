@@ -47,9 +47,9 @@ __device__ __forceinline__ void hermite_weights(float r, int& g, float4& hv, flo
   g = g > kTableGrid - 2 ? kTableGrid - 2 : g;
   t -= (float)g;
   const float t2 = t * t, t3 = t2 * t;
-  hv = make_float4(2.f * t3 - 3.f * t2 + 1.f, t3 - 2.f * t2 + t, -2.f * t3 + 3.f * t2, t3 - t2);
+  hv = make_float4(1.f, t3 - 2.f * t2 + t, -2.f * t3 + 3.f * t2, t3 - t2);      // applied to (v0, h m0, v1 - v0, h m1)
   const float ih = 1.0f / kTableH;
-  hd = make_float4((6.f * t2 - 6.f * t) * ih, (3.f * t2 - 4.f * t + 1.f) * ih, (-6.f * t2 + 6.f * t) * ih, (3.f * t2 - 2.f * t) * ih);
+  hd = make_float4(0.f, (3.f * t2 - 4.f * t + 1.f) * ih, (-6.f * t2 + 6.f * t) * ih, (3.f * t2 - 2.f * t) * ih);
 }
 
 // per-degree invariants of d = ev_j - ev_i (24 components each, read with 128-bit loads)
@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(FW_WARPS * 32, 2) attn_fwd_sym_kernel(LayerDev
           const float4 r0 = ld4(rp), hv = ld4(rp + 4);
           const int j2 = __float_as_int(r0.x), g = __float_as_int(r0.z);
           const float sc = r0.y;
-          const float* p0 = L.table + (size_t)g * 512 + col;
+          const float* p0 = L.table + (size_t)g * 1024 + col;
           {
             const float4 v0 = ld4(p0), m0 = ld4(p0 + 256), v1 = ld4(p0 + 512), m1 = ld4(p0 + 768);
             w1[k] = f4_fma(hv.x, v0, f4_fma(hv.y, m0, f4_fma(hv.z, v1, f4_fma(hv.w, m1, w1[k]))));
@@ -360,7 +360,7 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev
             const float4 r0 = ld4(rp), hv = ld4(rp + 4), hd = ld4(rp + 8);
             const int j2 = __float_as_int(r0.x), g = __float_as_int(r0.z);
             const float sc = r0.y, dcn = r0.w;
-            const float* p0 = L.table + (size_t)g * 512 + f * kF + col;
+            const float* p0 = L.table + (size_t)g * 1024 + f * kF + col;
             const float4 v0 = ld4(p0), m0 = ld4(p0 + 256), v1 = ld4(p0 + 512), m1 = ld4(p0 + 768);
             w[k] = f4_fma(hv.x, v0, f4_fma(hv.y, m0, f4_fma(hv.z, v1, f4_fma(hv.w, m1, w[k]))));
             const float4 td = f4_fma(hd.x, v0, f4_fma(hd.y, m0, f4_fma(hd.z, v1, f4_fma(hd.w, m1, f4_zero()))));

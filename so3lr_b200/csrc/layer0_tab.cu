@@ -3,10 +3,11 @@
 // The inputs of layer 0 are constants of the atom's element: x0 = embedding[Z], ev0 = 0.  Its q/k/v rows therefore
 // depend on the element only and the attention logits of an edge depend on (Z_i, Z_j, r) only:
 //     D_h(Z_i, Z_j, r) = sum_{t in h} q_{Z_i}[t] k_{Z_j}[t] w(r)[t],
-// where w(r) is the tabulated radial filter (cubic Hermite knots).  The Hermite interpolant is linear in its knot data, so
-// contracting the knots with q*k once per element pair gives a table with 8 values + 8 slopes per knot (4 heads of the
-// invariant branch, 4 degrees of the equivariant branch) that reproduces the generic kernel's logits exactly (up to the
-// order of additions) at 128 bytes of table traffic per edge instead of 4 KB of filter rows plus 1.5 KB of neighbour rows.
+// where w(r) is the tabulated radial filter (cubic Hermite, four rows per interval: value, slope, value difference, far
+// slope).  The interpolant is linear in those rows, so contracting them with q*k once per element pair gives a table of
+// 4 x 8 numbers per interval (4 heads of the invariant branch, 4 degrees of the equivariant branch) that reproduces the
+// generic kernel's logits (up to the order of additions) at 128 bytes of table traffic per edge instead of 4 KB of filter
+// rows plus 1.5 KB of neighbour rows.
 //   forward : lane = list entry; per edge a table lookup, the cutoff, the spherical harmonics; per-element sums of the
 //             invariant coefficients are combined with the element's v row at the end
 //   backward: only forces leave layer 0.  Lane = list entry evaluates both directions of the edge (the list is symmetric)
@@ -32,9 +33,9 @@ __device__ __forceinline__ void hermite_weights(float r, int& g, float4& hv, flo
   g = g > kTableGrid - 2 ? kTableGrid - 2 : g;
   t -= (float)g;
   const float t2 = t * t, t3 = t2 * t;
-  hv = make_float4(2.f * t3 - 3.f * t2 + 1.f, t3 - 2.f * t2 + t, -2.f * t3 + 3.f * t2, t3 - t2);
+  hv = make_float4(1.f, t3 - 2.f * t2 + t, -2.f * t3 + 3.f * t2, t3 - t2);      // applied to (v0, h m0, v1 - v0, h m1)
   const float ih = 1.0f / kTableH;
-  hd = make_float4((6.f * t2 - 6.f * t) * ih, (3.f * t2 - 4.f * t + 1.f) * ih, (-6.f * t2 + 6.f * t) * ih, (3.f * t2 - 2.f * t) * ih);
+  hd = make_float4(0.f, (3.f * t2 - 4.f * t + 1.f) * ih, (-6.f * t2 + 6.f * t) * ih, (3.f * t2 - 2.f * t) * ih);
 }
 
 // 32 per-lane partials -> lane L holds the total of entry L
@@ -63,21 +64,22 @@ __device__ __forceinline__ float warp_transpose_reduce32(float (&v)[32], int lan
   return keep + __shfl_xor_sync(0xffffffffu, send, 1);
 }
 
-// table[(a * SP + b)][knot][16]: 0-3 values of the 4 invariant heads, 4-7 values of the 4 degrees, 8-15 their slopes
+// table[(a * SP + b)][interval][32]: the four interval rows of the radial table (value, slope, value difference, far
+// slope) contracted with q_a * k_b per head: entry 8 * row + 4 * filter + head.  Sums are formed in double precision.
 __global__ void build_pair_table_kernel(const float* __restrict__ radial, const float* __restrict__ qkv_sp, int n_sp,
                                         float* __restrict__ table) {
   const int a = blockIdx.x / n_sp, b = blockIdx.x % n_sp;
   const float* qa = qkv_sp + (size_t)a * kProj;
   const float* kb = qkv_sp + (size_t)b * kProj;
-  for (int idx = threadIdx.x; idx < kTableGrid * 16; idx += blockDim.x) {
-    const int knot = idx >> 4, o = idx & 15;
-    const int grp = o & 3, filt = (o >> 2) & 1, slope = o >> 3;
-    const float* w = radial + ((size_t)knot * 2 + slope) * 256 + filt * kF + 32 * grp;
+  for (int idx = threadIdx.x; idx < (kTableGrid - 1) * 32; idx += blockDim.x) {
+    const int iv = idx >> 5, o = idx & 31;
+    const int grp = o & 3, filt = (o >> 2) & 1, row = o >> 3;
+    const float* w = radial + ((size_t)iv * 4 + row) * 256 + filt * kF + 32 * grp;
     const float* q = qa + (filt ? 3 * kF : 0) + 32 * grp;
     const float* k = kb + (filt ? 4 * kF : kF) + 32 * grp;
-    float s = 0.f;
-    for (int t = 0; t < 32; ++t) s = fmaf(q[t] * k[t], w[t], s);
-    table[((size_t)(a * SP + b) * kTableGrid + knot) * 16 + o] = s;
+    double s = 0.0;
+    for (int t = 0; t < 32; ++t) s += (double)q[t] * (double)k[t] * (double)w[t];
+    table[((size_t)(a * SP + b) * (kTableGrid - 1) + iv) * 32 + o] = (float)s;
   }
 }
 
@@ -107,9 +109,9 @@ __global__ void __launch_bounds__(256) layer0_fwd_tab_kernel(SpeciesTables T, co
     hermite_weights(r, g, hv, hd);
     const int Zj = Z[j];
     const int zj = T.slot[Zj < 0 ? 0 : (Zj > 118 ? 118 : Zj)];
-    const float* row = T.table + ((size_t)(zi * SP + zj) * kTableGrid + g) * 16;
+    const float* row = T.table + ((size_t)(zi * SP + zj) * (kTableGrid - 1) + g) * 32;
     const float4 v0a = ld4(row), v0b = ld4(row + 4), m0a = ld4(row + 8), m0b = ld4(row + 12);
-    const float4 v1a = ld4(row + 16), v1b = ld4(row + 20), m1a = ld4(row + 24), m1b = ld4(row + 28);
+    const float4 v1a = ld4(row + 16), v1b = ld4(row + 20), m1a = ld4(row + 24), m1b = ld4(row + 28);   // "v1" = value difference
     float a1[4], a2[4];
     a1[0] = sc * (hv.x * v0a.x + hv.y * m0a.x + hv.z * v1a.x + hv.w * m1a.x);
     a1[1] = sc * (hv.x * v0a.y + hv.y * m0a.y + hv.z * v1a.y + hv.w * m1a.y);
@@ -222,7 +224,7 @@ __global__ void __launch_bounds__(256) layer0_bwd_tab_kernel(SpeciesTables T, in
     float gr = 0.f, a2A[4], a2B[4];
 #pragma unroll
     for (int dir = 0; dir < 2; ++dir) {
-      const float* row = T.table + ((size_t)((dir ? zj : zi) * SP + (dir ? zi : zj)) * kTableGrid + g) * 16;
+      const float* row = T.table + ((size_t)((dir ? zj : zi) * SP + (dir ? zi : zj)) * (kTableGrid - 1) + g) * 32;
       const float4 v0a = ld4(row), v0b = ld4(row + 4), m0a = ld4(row + 8), m0b = ld4(row + 12);
       const float4 v1a = ld4(row + 16), v1b = ld4(row + 20), m1a = ld4(row + 24), m1b = ld4(row + 28);
       const float4 d1 = dir ? dB1 : dA1;
@@ -281,7 +283,7 @@ int species_tables_build(cudaStream_t st, const ModelDev& M, const int* Z_host, 
   for (int k = 0; same && k < (int)sp.size(); ++k) same = T->species[k] == sp[k];
   if (same && T->table) return kOk;
   if (!T->table) {
-    SO3LR_CUDA_CHECK(cudaMalloc((void**)&T->table, (size_t)SP * SP * kTableGrid * 16 * sizeof(float)));
+    SO3LR_CUDA_CHECK(cudaMalloc((void**)&T->table, (size_t)SP * SP * (kTableGrid - 1) * 32 * sizeof(float)));
     SO3LR_CUDA_CHECK(cudaMalloc((void**)&T->v_sp, (size_t)SP * kF * sizeof(float)));
     SO3LR_CUDA_CHECK(cudaMalloc((void**)&T->slot, 119 * sizeof(int)));
     SO3LR_CUDA_CHECK(cudaMalloc((void**)&T->qkv_sp, (size_t)SP * kProj * sizeof(float)));

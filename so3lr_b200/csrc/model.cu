@@ -165,15 +165,22 @@ int build_model(const float* blob, size_t n_floats, ModelDev* M, std::vector<voi
     D.proj = U.up(P);
     D.projT = U.up(PT);
     // radial tables
-    std::vector<float> tab((size_t)kTableGrid * 2 * 256);
-    std::vector<double> w(256), dw(256);
-    for (int g = 0; g < kTableGrid; ++g) {
-      double r = (double)g * (double)kTableH;
-      radial_filters(blob, O, l, r, w.data(), dw.data());
+    // per interval g (between knots g and g+1) four rows of 256: value at g, slope at g (x spacing), value difference
+    // to knot g+1 (formed in double precision: the derivative of the interpolant is built from this difference, and a
+    // difference of two rounded values would lose 1/spacing in accuracy), slope at g+1 (x spacing)
+    std::vector<float> tab((size_t)(kTableGrid - 1) * 4 * 256);
+    std::vector<double> w(256), dw(256), w1(256), dw1(256);
+    radial_filters(blob, O, l, 0.0, w.data(), dw.data());
+    for (int g = 0; g + 1 < kTableGrid; ++g) {
+      double r1 = (double)(g + 1) * (double)kTableH;
+      radial_filters(blob, O, l, r1, w1.data(), dw1.data());
       for (int j = 0; j < 256; ++j) {
-        tab[((size_t)g * 2 + 0) * 256 + j] = (float)w[j];
-        tab[((size_t)g * 2 + 1) * 256 + j] = (float)(dw[j] * (double)kTableH);
+        tab[((size_t)g * 4 + 0) * 256 + j] = (float)w[j];
+        tab[((size_t)g * 4 + 1) * 256 + j] = (float)(dw[j] * (double)kTableH);
+        tab[((size_t)g * 4 + 2) * 256 + j] = (float)(w1[j] - w[j]);
+        tab[((size_t)g * 4 + 3) * 256 + j] = (float)(dw1[j] * (double)kTableH);
       }
+      w.swap(w1); dw.swap(dw1);
     }
     D.table = U.up(tab);
     std::vector<float> s1k(2 * 4 * 32), s1b(2 * 32), s2k(2 * 32 * 128);

@@ -10,7 +10,7 @@ namespace so3lr {
 struct LayerDev {
   const float* projT;   // [5][4][32 j][32 i]   forward projection  (out_i = sum_j W[h][i][j] x[h][j])
   const float* proj;    // [5][4][32 i][32 j]   as stored; used by the backward projection
-  const float* table;   // [kTableGrid][2][256] radial filters: value, h * d/dr ; (w1 | w2)
+  const float* table;   // [kTableGrid-1][4][256] radial filters per interval: value, h*slope, value difference, h*slope at the far knot; (w1 | w2)
   const float* sph1_k;  // [2][4][32]   spherical filter, first layer kernel (filter, invariant, hidden)
   const float* sph1_b;  // [2][32]
   const float* sph2_k;  // [2][32][128] second layer kernel (filter, hidden, feature); bias is folded into `table`

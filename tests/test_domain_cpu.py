@@ -224,3 +224,50 @@ def test_slab_selection_holds_every_partner_of_an_owned_atom():
             for g in torch.nonzero((dist < geo.shell).any(0)).squeeze(1).tolist():
                 assert have[(g, k)] <= 1
     assert total_owned == len(R)
+
+
+# ---- independent structures over ranks: partition logic and result gathering (no GPU: a stand-in evaluator) ----
+class _FakeSystem:
+    def __init__(self, Z, cell, **kw):
+        self.Z = Z
+        gs = kw.get("graph_start")
+        self.gs = np.array([0, len(Z)]) if gs is None else np.asarray(gs)
+
+    def compute_host(self, R):
+        e = np.array([float((self.Z[a:b] * R[a:b, 0]).sum()) for a, b in zip(self.gs[:-1], self.gs[1:])])
+        return dict(energy=e, forces=-R * self.Z[:, None], partial_charges=R[:, 1].copy(), hirshfeld_ratios=R[:, 2].copy(),
+                    dipole_vec=np.zeros((len(e), 3), np.float32))
+
+
+def _batch_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+    from so3lr_b200 import batch as B
+    from so3lr_b200 import workloads as W
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    Z, R, gs = W.molecule_batch(23, seed=1001)
+    sb = B.ShardedBatch(Z, gs, world, rank, system_factory=_FakeSystem)
+    res = B.gather_results(sb.compute_host(R), world)
+    if rank == 0:
+        torch.save(res, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_graph_shards_cover_the_batch_and_are_balanced(tmp_path):
+    from so3lr_b200 import batch as B
+    from so3lr_b200 import workloads as W
+    Z, R, gs = W.molecule_batch(23, seed=1001)
+    for world in (1, 2, 3, 8, 40):
+        ranges = [B.shard_graphs(gs, world, r) for r in range(world)]
+        assert ranges[0][0] == 0 and ranges[-1][1] == 23
+        assert all(a[1] == b[0] for a, b in zip(ranges[:-1], ranges[1:]))
+        if world <= 8:
+            atoms = [gs[b] - gs[a] for a, b in ranges]
+            assert max(atoms) - min(atoms) <= 2 * 40            # within two molecules of each other
+    out = str(tmp_path / "b.pt")
+    mp.spawn(_batch_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    res = torch.load(out, weights_only=False)
+    ref = _FakeSystem(Z, None, graph_start=gs).compute_host(R.astype(np.float32))
+    np.testing.assert_allclose(res["energy"], ref["energy"], rtol=1e-6)
+    np.testing.assert_allclose(res["forces"], ref["forces"])

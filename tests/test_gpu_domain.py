@@ -101,3 +101,17 @@ def test_decomposed_nve_tracks_single_device_and_migrates(reference_goldens):
     d = Rdd - R_ref
     d -= np.round(d / 24.9) * 24.9
     assert np.abs(d).max() < 5e-2 and np.median(np.abs(d)) < 1e-4, (np.abs(d).max(), np.median(np.abs(d)))
+
+
+def test_sharded_molecule_batch_matches_unsharded(oracle_params):
+    """Independent structures split over two ranks (evaluated one after the other on this GPU): same numbers as one batch."""
+    from so3lr_b200 import batch as B
+    from so3lr_b200 import workloads as W
+    from so3lr_b200.engine import System
+    Z, R, gs = W.molecule_batch(9, seed=1001)
+    R = np.asarray(R, dtype=np.float32)
+    whole = System(Z, None, cutoff_lr=1000.0, damping=2.0, lr_format="sparse", graph_start=gs).compute_host(R)
+    parts = [B.ShardedBatch(Z, gs, 2, r).compute_host(R) for r in range(2)]
+    np.testing.assert_allclose(np.concatenate([p["energy"] for p in parts]), whole["energy"], rtol=1e-6)
+    np.testing.assert_allclose(np.concatenate([p["forces"] for p in parts]), whole["forces"], atol=2e-5)
+    np.testing.assert_allclose(np.concatenate([p["dipole_vec"] for p in parts]), whole["dipole_vec"], atol=2e-5)
