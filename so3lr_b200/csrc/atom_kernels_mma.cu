@@ -100,6 +100,37 @@ __device__ __forceinline__ void gemm_mma(const float* At, const uint4* __restric
     for (int e = 0; e < 4; ++e) acc[nt][e] = fmaf(cross[nt][e], kLoInv, acc[nt][e]);
 }
 
+// One 32 x 32 block: acc[nt][e] (+)= sum_{k<32} A[row][k0 + k] * B[k][col], B in fragment order ([2][4][32]).
+template <bool ACCUM>
+__device__ __forceinline__ void gemm_block32(const float* At, int k0, const uint4* __restrict__ Bf, float (&acc)[4][4]) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3, r = 16 * (threadIdx.x >> 5) + g;
+  float cross[4][4];
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { cross[nt][e] = 0.f; if (!ACCUM) acc[nt][e] = 0.f; }
+#pragma unroll
+  for (int ks = 0; ks < 2; ++ks) {
+    const float* a = At + (k0 + 16 * ks + 2 * q) * TS + r;
+    unsigned ah[4], al[4];
+    split2(a[0], a[TS], ah[0], al[0]);
+    split2(a[8], a[TS + 8], ah[1], al[1]);
+    split2(a[8 * TS], a[9 * TS], ah[2], al[2]);
+    split2(a[8 * TS + 8], a[9 * TS + 8], ah[3], al[3]);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const uint4 b = Bf[(ks * 4 + nt) * 32 + lane];
+      mma16816(cross[nt], ah[0], ah[1], ah[2], ah[3], b.z, b.w);
+      mma16816(cross[nt], al[0], al[1], al[2], al[3], b.x, b.y);
+      mma16816(acc[nt], ah[0], ah[1], ah[2], ah[3], b.x, b.y);
+    }
+  }
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[nt][e] = fmaf(cross[nt][e], kLoInv, acc[nt][e]);
+}
+
 // per-row LayerNorm statistics over 128 features held feature-major in T
 __device__ __forceinline__ void ln_stats(const float* T, int r, float& mean, float& rstd) {
   float s = 0.f;
@@ -128,7 +159,8 @@ __device__ __forceinline__ float quad_sum(float v) {
 __global__ void __launch_bounds__(NT) atom_post_fwd_mma_kernel(LayerDev L, int n, const float* __restrict__ xa,
                                                                const float* __restrict__ ev1, float* __restrict__ z1_out,
                                                                float* __restrict__ x3_out, float* __restrict__ gate_out,
-                                                               float* __restrict__ x4_out, float* __restrict__ ev2_out) {
+                                                               float* __restrict__ x4_out, float* __restrict__ ev2_out,
+                                                               const uint4* __restrict__ proj_next, float* __restrict__ qkv_next) {
   extern __shared__ float sm[];
   float* At = sm;                  // 128*TS
   float* Bt = At + kF * TS;        // 128*TS
@@ -226,6 +258,22 @@ __global__ void __launch_bounds__(NT) atom_post_fwd_mma_kernel(LayerDev L, int n
   }
   __syncthreads();
   store_tile_T<kF>(x4_out, Bt, row0, n);
+  // q/k/v rows of the next layer straight from the x4 tile: 5 projections x 4 heads of 32 x 32
+  if (proj_next) {
+#pragma unroll 1
+    for (int h = 0; h < 4; ++h)
+#pragma unroll 1
+      for (int w = 0; w < 5; ++w) {
+        float pa[4][4];
+        gemm_block32<false>(Bt, 32 * h, proj_next + (size_t)(w * 4 + h) * 256, pa);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          const int c = w * kF + 32 * h + 8 * nt + 2 * fr.q;
+          if (row0 + fr.row(0) < n) *reinterpret_cast<float2*>(qkv_next + (size_t)(row0 + fr.row(0)) * kProj + c) = make_float2(pa[nt][0], pa[nt][1]);
+          if (row0 + fr.row(2) < n) *reinterpret_cast<float2*>(qkv_next + (size_t)(row0 + fr.row(2)) * kProj + c) = make_float2(pa[nt][2], pa[nt][3]);
+        }
+      }
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -235,7 +283,8 @@ __global__ void __launch_bounds__(NT) atom_post_bwd_mma_kernel(LayerDev L, int n
                                                                const float* __restrict__ ev1, const float* __restrict__ z1,
                                                                const float* __restrict__ x3, const float* __restrict__ gate,
                                                                const float* __restrict__ g4, const float* __restrict__ gev2,
-                                                               float* __restrict__ g_xa, float* __restrict__ gev1) {
+                                                               float* g_xa, float* __restrict__ gev1,
+                                                               const uint4* __restrict__ projT_up, const float* __restrict__ g_qkv_up) {
   extern __shared__ float sm[];
   float* At = sm;
   float* Bt = At + kF * TS;
@@ -247,8 +296,45 @@ __global__ void __launch_bounds__(NT) atom_post_bwd_mma_kernel(LayerDev L, int n
   const int row0 = blockIdx.x * TA;
   const Frag fr;
 
+  if (projT_up) {
+    // cotangent of this layer's output from the layer above: skip connection (its g_xa, still in the g_xa buffer: this
+    // CTA reads its rows before it overwrites them at the end) + transposed q/k/v projections of its g_qkv
+    float ga[16][4];
+#pragma unroll 1
+    for (int w = 0; w < 5; ++w) {
+      __syncthreads();
+      for (int rr = threadIdx.x >> 5; rr < TA; rr += NT / 32) {
+        const int a = row0 + rr, lane = threadIdx.x & 31;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) At[(lane + 32 * c) * TS + rr] = (a < n) ? g_qkv_up[(size_t)a * kProj + w * kF + lane + 32 * c] : 0.f;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        float pa[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) pa[nt][e] = w ? ga[4 * h + nt][e] : 0.f;
+        gemm_block32<true>(At, 32 * h, projT_up + (size_t)(w * 4 + h) * 256, pa);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) ga[4 * h + nt][e] = pa[nt][e];
+      }
+    }
+    __syncthreads();
+    load_tile_T<kF>(Bt, g_xa, row0, n);
+    __syncthreads();
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) Bt[fr.col(nt, e) * TS + fr.row(e)] += ga[nt][e];
+    __syncthreads();
+  } else {
+    load_tile_T<kF>(Bt, g4, row0, n);
+  }
   load_tile_T<kF>(At, x3, row0, n);
-  load_tile_T<kF>(Bt, g4, row0, n);
   load_tile_T<kF>(Ct, xa, row0, n);
   __syncthreads();
   if (tid < TA) {
@@ -534,14 +620,15 @@ int configure_atom_mma_kernels() {
 }
 
 void launch_atom_post_fwd_mma(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, float* z1, float* x3,
-                              float* gate, float* x4, float* ev2) {
+                              float* gate, float* x4, float* ev2, const uint4* proj_next, float* qkv_next) {
   if (n <= 0) return;
-  atom_post_fwd_mma_kernel<<<(n + TA - 1) / TA, NT, kSmemPostFwd, s>>>(L, n, xa, ev1, z1, x3, gate, x4, ev2);
+  atom_post_fwd_mma_kernel<<<(n + TA - 1) / TA, NT, kSmemPostFwd, s>>>(L, n, xa, ev1, z1, x3, gate, x4, ev2, proj_next, qkv_next);
 }
 void launch_atom_post_bwd_mma(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, const float* z1,
-                              const float* x3, const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1) {
+                              const float* x3, const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1,
+                              const uint4* projT_up, const float* g_qkv_up) {
   if (n <= 0) return;
-  atom_post_bwd_mma_kernel<<<(n + TA - 1) / TA, NT, kSmemPostBwd, s>>>(L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1);
+  atom_post_bwd_mma_kernel<<<(n + TA - 1) / TA, NT, kSmemPostBwd, s>>>(L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1, projT_up, g_qkv_up);
 }
 void launch_heads_fwd_mma(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* x, float* ze, float* zq, float* zh,
                           float* e_nn, float* q_raw, float* hv) {

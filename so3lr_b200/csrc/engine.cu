@@ -385,14 +385,18 @@ bool use_mma_dense() {
   }();
   return v;
 }
+// With the tensor-core dense blocks the q/k/v projections ride along: the forward block also emits the next layer's
+// q/k/v rows, the reverse block forms its input cotangent from the upper layer's g_xa and g_qkv.  `next` / `up` = that
+// neighbouring layer (nullptr: no fusion at this end of the network).
 void post_fwd_dispatch(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, float* z1, float* x3, float* gate,
-                       float* x4, float* ev2) {
-  if (use_mma_dense()) launch_atom_post_fwd_mma(s, L, n, xa, ev1, z1, x3, gate, x4, ev2);
+                       float* x4, float* ev2, const LayerDev* next, float* qkv_next) {
+  if (use_mma_dense()) launch_atom_post_fwd_mma(s, L, n, xa, ev1, z1, x3, gate, x4, ev2, next ? next->proj_f : nullptr, qkv_next);
   else launch_atom_post_fwd(s, L, n, xa, ev1, z1, x3, gate, x4, ev2);
 }
 void post_bwd_dispatch(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, const float* z1, const float* x3,
-                       const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1) {
-  if (use_mma_dense()) launch_atom_post_bwd_mma(s, L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1);
+                       const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1, const LayerDev* up,
+                       const float* g_qkv_up) {
+  if (use_mma_dense()) launch_atom_post_bwd_mma(s, L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1, up ? up->projT_f : nullptr, g_qkv_up);
   else launch_atom_post_bwd(s, L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1);
 }
 void heads_fwd_dispatch(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* x, float* ze, float* zq, float* zh,
@@ -438,6 +442,7 @@ int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const S
                          owned_side_only ? c.n0 : -1);
   S->prof.end(st);
   const bool tab0 = S->sp.n_species > 0 && use_layer0_tables();
+  const bool fuse = use_mma_dense();   // q/k/v rows of layer l+1 come out of layer l's dense block
   if (!tab0) launch_embed(st, M, S->d_Z, c.n3, S->x[0]);
   S->n_launches += 4;
   for (int l = 0; l < kNumLayers; ++l) {
@@ -447,13 +452,15 @@ int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const S
       launch_layer0_fwd_tab(st, S->sp, M, nrecv[0], c.n3, row_ptr, nbr_j, S->dR, S->d_Z, S->xa[0], S->ev1[0]);
       S->prof.end(st);
     } else {
-      S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], nsend[l], S->qkv[l]); S->prof.end(st);
+      if (!(fuse && l > 0)) { S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], nsend[l], S->qkv[l]); S->prof.end(st); }
       S->prof.begin(kPAttnFwd, st);
       attn_fwd_dispatch(st, L, nrecv[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
       S->prof.end(st);
     }
     S->prof.begin(kPPostFwd, st);
-    post_fwd_dispatch(st, L, nrecv[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]);
+    const bool emit = fuse && l + 1 < kNumLayers;
+    post_fwd_dispatch(st, L, nrecv[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1],
+                      emit ? &M.layer[l + 1] : nullptr, emit ? S->qkv[l + 1] : nullptr);
     S->prof.end(st);
     S->n_launches += 3;
   }
@@ -480,8 +487,10 @@ int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float
   S->n_launches += 2;
   for (int l = kNumLayers - 1; l >= 0; --l) {
     const LayerDev& L = M.layer[l];
+    const bool fused_in = use_mma_dense() && l + 1 < kNumLayers;   // cotangent formed from the layer above inside the block
     S->prof.begin(kPPostBwd, st);
-    post_bwd_dispatch(st, L, npost[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, gev2, S->g_xa, S->gev1);
+    post_bwd_dispatch(st, L, npost[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, gev2, S->g_xa, S->gev1,
+                      fused_in ? &M.layer[l + 1] : nullptr, S->g_qkv);
     S->prof.end(st);
     if (c.n3 > npost[l]) {   // atoms beyond the layer's receivers have no cotangent of their own (any of them can be a neighbour)
       fill(st, S->g_xa + (size_t)npost[l] * kF, (size_t)(c.n3 - npost[l]) * kF, 0.f);
@@ -495,11 +504,13 @@ int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float
     S->prof.end(st);
     S->n_launches += 2;
     if (l > 0) {
-      // dL/dx_in = g_xa (skip connection) + projections^T
-      SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)nattn[l] * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
-      S->prof.begin(kPProjBwd, st); launch_proj_bwd(st, L, S->g_qkv, nattn[l], S->g4, 1); S->prof.end(st);
+      if (!use_mma_dense()) {
+        // dL/dx_in = g_xa (skip connection) + projections^T
+        SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)nattn[l] * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
+        S->prof.begin(kPProjBwd, st); launch_proj_bwd(st, L, S->g_qkv, nattn[l], S->g4, 1); S->prof.end(st);
+        S->n_launches += 2;
+      }
       float* t = gev2; gev2 = gev_in; gev_in = t;
-      S->n_launches += 2;
     }
   }
   SO3LR_CUDA_CHECK(cudaGetLastError());
@@ -925,13 +936,20 @@ SO3LR_B200_API int so3lr_b200_dd_layer_forward(so3lr_b200_system* S, void* strea
     launch_layer0_fwd_tab(st, S->sp, S->model->M, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->d_Z, S->xa[0], S->ev1[0]);
     S->prof.end(st);
   } else {
-    S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], n1, S->qkv[l]); S->prof.end(st);
+    // with the tensor-core dense blocks the owned rows of q/k/v came out of the previous layer's block; the ghost rows
+    // (features just received from their owners) are projected here
+    const int first = (use_mma_dense() && l > 0) ? n0 : 0;
+    S->prof.begin(kPProj, st);
+    launch_proj_fwd(st, L, S->x[l] + (size_t)first * kF, n1 - first, S->qkv[l] + (size_t)first * kProj);
+    S->prof.end(st);
     S->prof.begin(kPAttnFwd, st);
     attn_fwd_dispatch(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
     S->prof.end(st);
   }
+  const bool emit = use_mma_dense() && l + 1 < kNumLayers;
   S->prof.begin(kPPostFwd, st);
-  post_fwd_dispatch(st, L, n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]);
+  post_fwd_dispatch(st, L, n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1],
+                    emit ? &S->model->M.layer[l + 1] : nullptr, emit ? S->qkv[l + 1] : nullptr);
   S->prof.end(st);
   S->n_launches += 3;
   SO3LR_CUDA_CHECK(cudaGetLastError());
@@ -994,8 +1012,10 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_post(so3lr_b200_system* S, void*
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0], l = layer;
+  const bool fused_in = use_mma_dense() && l + 1 < kNumLayers;
   S->prof.begin(kPPostBwd, st);
-  post_bwd_dispatch(st, S->model->M.layer[l], n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, S->dd_gev2, S->g_xa, S->gev1);
+  post_bwd_dispatch(st, S->model->M.layer[l], n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, S->dd_gev2, S->g_xa, S->gev1,
+                    fused_in ? &S->model->M.layer[l + 1] : nullptr, S->g_qkv);
   S->prof.end(st);
   S->n_launches += 1;
   SO3LR_CUDA_CHECK(cudaGetLastError());
@@ -1018,10 +1038,12 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_attn(so3lr_b200_system* S, void*
   S->prof.end(st);
   S->n_launches += 1;
   if (l > 0) {
-    SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)n0 * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
-    S->prof.begin(kPProjBwd, st); launch_proj_bwd(st, L, S->g_qkv, n0, S->g4, 1); S->prof.end(st);
+    if (!use_mma_dense()) {
+      SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)n0 * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
+      S->prof.begin(kPProjBwd, st); launch_proj_bwd(st, L, S->g_qkv, n0, S->g4, 1); S->prof.end(st);
+      S->n_launches += 2;
+    }
     float* t = S->dd_gev2; S->dd_gev2 = S->dd_gev_in; S->dd_gev_in = t;
-    S->n_launches += 2;
   }
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;

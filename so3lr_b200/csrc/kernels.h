@@ -20,10 +20,14 @@ void launch_heads_bwd(cudaStream_t s, const ModelDev& M, int n, const int* Z, co
 
 // ---- atom_kernels_mma.cu: the same four blocks with their contractions as FP16-split tensor-core MMAs ----
 int configure_atom_mma_kernels();
+// proj_next / qkv_next (optional): also write the next layer's q/k/v rows (proj_next = that layer's proj_f).
 void launch_atom_post_fwd_mma(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, float* z1, float* x3,
-                              float* gate, float* x4, float* ev2);
+                              float* gate, float* x4, float* ev2, const uint4* proj_next, float* qkv_next);
+// projT_up / g_qkv_up (optional): instead of reading g4, form it as (rows of g_xa left by the layer above) + the transposed
+// projections (projT_up = that layer's projT_f) of that layer's g_qkv.
 void launch_atom_post_bwd_mma(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, const float* z1,
-                              const float* x3, const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1);
+                              const float* x3, const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1,
+                              const uint4* projT_up, const float* g_qkv_up);
 void launch_heads_fwd_mma(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* x, float* ze, float* zq, float* zh,
                           float* e_nn, float* q_raw, float* hv);
 void launch_heads_bwd_mma(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* ze, const float* zq, const float* zh,

@@ -164,6 +164,19 @@ int build_model(const float* blob, size_t n_floats, ModelDev* M, std::vector<voi
     }
     D.proj = U.up(P);
     D.projT = U.up(PT);
+    {
+      std::vector<float> pf, pb;
+      for (int w = 0; w < 5; ++w)
+        for (int h = 0; h < 4; ++h) {
+          const float* W = blob + L.W[w] + (size_t)h * 32 * 32;    // [i][j]
+          std::vector<float> a = pack_fragments(W, 32, 32, true);   // B[k = j][n = i] = W[i][j]
+          std::vector<float> b = pack_fragments(W, 32, 32, false);  // B[k = i][n = j] = W[i][j]
+          pf.insert(pf.end(), a.begin(), a.end());
+          pb.insert(pb.end(), b.begin(), b.end());
+        }
+      D.proj_f = reinterpret_cast<const uint4*>(U.up(pf));
+      D.projT_f = reinterpret_cast<const uint4*>(U.up(pb));
+    }
     // radial tables
     // per interval g (between knots g and g+1) four rows of 256: value at g, slope at g (x spacing), value difference
     // to knot g+1 (formed in double precision: the derivative of the interpolant is built from this difference, and a

@@ -20,6 +20,9 @@ struct LayerDev {
   // the same dense kernels as tensor-core B operands: FP16 hi / scaled-lo pairs in mma.m16n8k16 fragment order,
   // [K/16][N/8][32 lanes] x {b0hi, b1hi, b0lo, b1lo} (see atom_kernels_mma.cu); "T" = transposed kernel (reverse pass)
   const uint4 *res1_f, *res1T_f, *res2_f, *res2T_f, *exxx_f, *exxxT_f;
+  // q/k/v projections of this layer as 20 blocks (projection w = 0..4, head h = 0..3) of 32 x 32, fragment order
+  // [w*4+h][2][4][32]: proj_f for out_i = sum_j W[i][j] x_j, projT_f for the reverse contraction over i
+  const uint4 *proj_f, *projT_f;
   const float* ex_xg;           // [128][4]   features -> gates
   const float* ex_ix;           // [4][128]   invariants -> features
   const float* ex_ig;           // [4][4]     invariants -> gates
