@@ -203,6 +203,9 @@ SO3LR_B200_API void so3lr_b200_host_sph_harm(float x, float y, float z, float* y
 SO3LR_B200_API void so3lr_b200_host_sph_harm_vjp(float x, float y, float z, const float* g24, float* g3);
 SO3LR_B200_API void so3lr_b200_host_pair_terms(float r, int zi, int zj, float qi, float qj, float hi, float hj, float cutoff_lr,
                                 float damping, float* out8);
+/* out4 = dispersion energy, d/dr, d/dh_i, d/dh_j of one pair as the pair kernels evaluate it (hand-derived partials) */
+SO3LR_B200_API void so3lr_b200_host_dispersion_fast(float r, int zi, int zj, float hi, float hj, float cutoff_lr, float damping,
+                                                    float* out4);
 SO3LR_B200_API void so3lr_b200_host_zbl(const float* blob_host, float r, int zi, int zj, float* out2);
 SO3LR_B200_API void so3lr_b200_host_radial_filter(const float* blob_host, int layer, double r, double* w256, double* dw256);
 

@@ -1112,6 +1112,12 @@ SO3LR_B200_API void so3lr_b200_host_pair_terms(float r, int zi, int zj, float qi
   dispersion_pair(P, r, zi, zj, hi, hj, out8[3], out8[4], out8[5], out8[6]);
   out8[7] = 0.f;
 }
+SO3LR_B200_API void so3lr_b200_host_dispersion_fast(float r, int zi, int zj, float hi, float hj, float cutoff_lr, float damping, float* out4) {
+  LrParams P{};
+  P.has_cutoff = cutoff_lr > 0.f; P.rc = cutoff_lr; P.cuton = kCutonFraction * cutoff_lr; P.has_damping = damping > 0.f;
+  P.disp_on = cutoff_lr - damping; P.pair_factor = 1.f;
+  dispersion_pair_fast(P, r, zi, zj, hi, hj, out4[0], out4[1], out4[2], out4[3]);
+}
 SO3LR_B200_API void so3lr_b200_host_zbl(const float* blob, float r, int zi, int zj, float* out2) {
   BlobOffsets O = blob_offsets();
   ZblParams z{};

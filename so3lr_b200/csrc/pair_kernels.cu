@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(256) pair_lr_kernel(LrParams P, Cell cell, int
         const float kq = pf * kKe;
         const float e_c = kq * qi * qj * chi;
         float e_d, dd_dr, dd_dhi, dd_dhj;
-        dispersion_pair(P, r, Zi, Z[j], hi, hj, e_d, dd_dr, dd_dhi, dd_dhj);
+        dispersion_pair_fast(P, r, Zi, Z[j], hi, hj, e_d, dd_dr, dd_dhi, dd_dhj);
         e_d *= pf; dd_dr *= pf; dd_dhi *= pf; dd_dhj *= pf;
         ec += e_c; ed += e_d;
         gqi = fmaf(kq * qj, chi, gqi);
@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cel
     coulomb_chi(P, r, chi, dchi);
     const float qj = q[j], hj = h[j];
     float e_d, dd_dr, dd_dhi, dd_dhj;
-    dispersion_pair(P, r, Zi, Z[j], hi, hj, e_d, dd_dr, dd_dhi, dd_dhj);
+    dispersion_pair_fast(P, r, Zi, Z[j], hi, hj, e_d, dd_dr, dd_dhi, dd_dhj);
     ec = fmaf(0.5f * kKe * qi * qj, chi, ec);
     ed += 0.5f * e_d;
     gqi = fmaf(kKe * qj, chi, gqi);

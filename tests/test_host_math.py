@@ -69,6 +69,12 @@ def test_pair_terms_match_oracle(cutoff, damping):
         np.testing.assert_allclose(out[3], ed.item(), rtol=5e-5, atol=1e-7)
         np.testing.assert_allclose(out[4], ded_r.item(), rtol=2e-4, atol=1e-7)
         np.testing.assert_allclose(out[5:7], ded_h.numpy(), rtol=2e-4, atol=1e-7)
+        # the hand-derived form the pair kernels use
+        o4 = np.zeros(4, np.float32)
+        lib.so3lr_b200_host_dispersion_fast(r, zi, zj, hi, hj, cutoff, damping, _p(o4))
+        np.testing.assert_allclose(o4[0], ed.item(), rtol=5e-5, atol=1e-7)
+        np.testing.assert_allclose(o4[1], ded_r.item(), rtol=2e-4, atol=1e-7)
+        np.testing.assert_allclose(o4[2:4], ded_h.numpy(), rtol=2e-4, atol=1e-7)
 
 
 def test_zbl_matches_oracle(oracle_params):
