@@ -615,38 +615,38 @@ int configure_atom_kernels() {
 void launch_embed(cudaStream_t s, const ModelDev& M, const int* Z, int n, float* x) {
   if (n <= 0) return;
   size_t tot = (size_t)n * kF;
-  embed_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, s>>>(M.embed_z, Z, n, x);
+  { embed_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, s>>>(M.embed_z, Z, n, x); count_launch(); }
 }
 void launch_proj_fwd(cudaStream_t s, const LayerDev& L, const float* x, int n, float* qkv) {
   if (n <= 0) return;
   int blocks = (n + PROJ_TILE - 1) / PROJ_TILE;
-  proj_fwd_kernel<<<blocks, 640, 0, s>>>(L.projT, x, n, qkv);
+  { proj_fwd_kernel<<<blocks, 640, 0, s>>>(L.projT, x, n, qkv); count_launch(); }
 }
 void launch_proj_bwd(cudaStream_t s, const LayerDev& L, const float* g_qkv, int n, float* gx, int accumulate) {
   if (n <= 0) return;
   int blocks = (n + PROJ_TILE - 1) / PROJ_TILE;
   if (blocks > 148 * 2) blocks = 148 * 2;
-  proj_bwd_kernel<<<blocks, 512, kSmemProjBwd, s>>>(L.proj, g_qkv, n, gx, accumulate);
+  { proj_bwd_kernel<<<blocks, 512, kSmemProjBwd, s>>>(L.proj, g_qkv, n, gx, accumulate); count_launch(); }
 }
 void launch_atom_post_fwd(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, float* z1,
                           float* x3, float* gate, float* x4, float* ev2) {
   if (n <= 0) return;
-  atom_post_fwd_kernel<<<(n + TA - 1) / TA, NT, kSmemPostFwd, s>>>(L, n, xa, ev1, z1, x3, gate, x4, ev2);
+  { atom_post_fwd_kernel<<<(n + TA - 1) / TA, NT, kSmemPostFwd, s>>>(L, n, xa, ev1, z1, x3, gate, x4, ev2); count_launch(); }
 }
 void launch_atom_post_bwd(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, const float* z1,
                           const float* x3, const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1) {
   if (n <= 0) return;
-  atom_post_bwd_kernel<<<(n + TA - 1) / TA, NT, kSmemPostBwd, s>>>(L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1);
+  { atom_post_bwd_kernel<<<(n + TA - 1) / TA, NT, kSmemPostBwd, s>>>(L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1); count_launch(); }
 }
 void launch_heads_fwd(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* x, float* ze, float* zq, float* zh,
                       float* e_nn, float* q_raw, float* hv) {
   if (n <= 0) return;
-  heads_fwd_kernel<<<(n + TA - 1) / TA, NT, kSmemHeads, s>>>(M, n, Z, x, ze, zq, zh, e_nn, q_raw, hv);
+  { heads_fwd_kernel<<<(n + TA - 1) / TA, NT, kSmemHeads, s>>>(M, n, Z, x, ze, zq, zh, e_nn, q_raw, hv); count_launch(); }
 }
 void launch_heads_bwd(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* ze, const float* zq, const float* zh,
                       const float* hv, const float* ge, const float* gq, const float* gh, float* gx) {
   if (n <= 0) return;
-  heads_bwd_kernel<<<(n + TA - 1) / TA, NT, kSmemHeads, s>>>(M, n, Z, ze, zq, zh, hv, ge, gq, gh, gx);
+  { heads_bwd_kernel<<<(n + TA - 1) / TA, NT, kSmemHeads, s>>>(M, n, Z, ze, zq, zh, hv, ge, gq, gh, gx); count_launch(); }
 }
 
 }  // namespace so3lr

@@ -622,23 +622,23 @@ int configure_atom_mma_kernels() {
 void launch_atom_post_fwd_mma(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, float* z1, float* x3,
                               float* gate, float* x4, float* ev2, const uint4* proj_next, float* qkv_next) {
   if (n <= 0) return;
-  atom_post_fwd_mma_kernel<<<(n + TA - 1) / TA, NT, kSmemPostFwd, s>>>(L, n, xa, ev1, z1, x3, gate, x4, ev2, proj_next, qkv_next);
+  { atom_post_fwd_mma_kernel<<<(n + TA - 1) / TA, NT, kSmemPostFwd, s>>>(L, n, xa, ev1, z1, x3, gate, x4, ev2, proj_next, qkv_next); count_launch(); }
 }
 void launch_atom_post_bwd_mma(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, const float* z1,
                               const float* x3, const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1,
                               const uint4* projT_up, const float* g_qkv_up) {
   if (n <= 0) return;
-  atom_post_bwd_mma_kernel<<<(n + TA - 1) / TA, NT, kSmemPostBwd, s>>>(L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1, projT_up, g_qkv_up);
+  { atom_post_bwd_mma_kernel<<<(n + TA - 1) / TA, NT, kSmemPostBwd, s>>>(L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1, projT_up, g_qkv_up); count_launch(); }
 }
 void launch_heads_fwd_mma(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* x, float* ze, float* zq, float* zh,
                           float* e_nn, float* q_raw, float* hv) {
   if (n <= 0) return;
-  heads_fwd_mma_kernel<<<(n + TA - 1) / TA, NT, kSmemHeads, s>>>(M, n, Z, x, ze, zq, zh, e_nn, q_raw, hv);
+  { heads_fwd_mma_kernel<<<(n + TA - 1) / TA, NT, kSmemHeads, s>>>(M, n, Z, x, ze, zq, zh, e_nn, q_raw, hv); count_launch(); }
 }
 void launch_heads_bwd_mma(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* ze, const float* zq, const float* zh,
                           const float* hv, const float* ge, const float* gq, const float* gh, float* gx) {
   if (n <= 0) return;
-  heads_bwd_mma_kernel<<<(n + TA - 1) / TA, NT, kSmemHeads, s>>>(M, n, Z, ze, zq, zh, hv, ge, gq, gh, gx);
+  { heads_bwd_mma_kernel<<<(n + TA - 1) / TA, NT, kSmemHeads, s>>>(M, n, Z, ze, zq, zh, hv, ge, gq, gh, gx); count_launch(); }
 }
 
 }  // namespace so3lr

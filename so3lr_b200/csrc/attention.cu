@@ -338,9 +338,9 @@ void launch_attn_fwd(cudaStream_t s, const LayerDev& L, int n, const int* row_pt
   if (n <= 0) return;
   int blocks = (n + WARPS - 1) / WARPS;
   if (L.has_spherical)
-    attn_fwd_kernel<true><<<blocks, WARPS * 32, kSmemFwd, s>>>(L, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
+    { attn_fwd_kernel<true><<<blocks, WARPS * 32, kSmemFwd, s>>>(L, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1); count_launch(); }
   else
-    attn_fwd_kernel<false><<<blocks, WARPS * 32, 0, s>>>(L, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
+    { attn_fwd_kernel<false><<<blocks, WARPS * 32, 0, s>>>(L, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1); count_launch(); }
 }
 
 void launch_attn_bwd(cudaStream_t s, const LayerDev& L, int n, const int* row_ptr, const int* nbr_j, const float* dR,
@@ -349,9 +349,9 @@ void launch_attn_bwd(cudaStream_t s, const LayerDev& L, int n, const int* row_pt
   if (n <= 0) return;
   int blocks = (n + WARPS - 1) / WARPS;
   if (first_layer)
-    attn_bwd_kernel<true><<<blocks, WARPS * 32, 0, s>>>(L, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, g_dR);
+    { attn_bwd_kernel<true><<<blocks, WARPS * 32, 0, s>>>(L, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, g_dR); count_launch(); }
   else
-    attn_bwd_kernel<false><<<blocks, WARPS * 32, kSmemBwd, s>>>(L, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, g_dR);
+    { attn_bwd_kernel<false><<<blocks, WARPS * 32, kSmemBwd, s>>>(L, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, g_dR); count_launch(); }
 }
 
 }  // namespace so3lr

@@ -630,7 +630,7 @@ void launch_attn_fwd_mma(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
   if (n_recv <= 0) return;
   int blocks = (n_recv + FW_WARPS - 1) / FW_WARPS;
   if (blocks > 148) blocks = 148;
-  attn_fwd_mma_kernel<<<blocks, FW_WARPS * 32, kSmemFw, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
+  { attn_fwd_mma_kernel<<<blocks, FW_WARPS * 32, kSmemFw, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1); count_launch(); }
 }
 
 void launch_attn_bwd_mma(cudaStream_t s, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
@@ -639,7 +639,7 @@ void launch_attn_bwd_mma(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
   if (n_recv <= 0) return;
   int blocks = (n_recv + BW_WARPS - 1) / BW_WARPS;
   if (blocks > 148) blocks = 148;
-  attn_bwd_mma_kernel<<<blocks, BW_WARPS * 32, kSmemBw, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F);
+  { attn_bwd_mma_kernel<<<blocks, BW_WARPS * 32, kSmemBw, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F); count_launch(); }
 }
 
 }  // namespace so3lr

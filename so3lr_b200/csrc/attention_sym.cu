@@ -524,9 +524,9 @@ void launch_attn_fwd_sym(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
   int blocks = (n_recv + FW_WARPS - 1) / FW_WARPS;
   if (blocks > 148 * 2) blocks = 148 * 2;
   if (L.has_spherical)
-    attn_fwd_sym_kernel<true><<<blocks, FW_WARPS * 32, kSmemFwSph, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
+    { attn_fwd_sym_kernel<true><<<blocks, FW_WARPS * 32, kSmemFwSph, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1); count_launch(); }
   else
-    attn_fwd_sym_kernel<false><<<blocks, FW_WARPS * 32, kSmemFwFirst, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
+    { attn_fwd_sym_kernel<false><<<blocks, FW_WARPS * 32, kSmemFwFirst, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1); count_launch(); }
 }
 
 void launch_attn_bwd_sym(cudaStream_t s, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
@@ -536,9 +536,9 @@ void launch_attn_bwd_sym(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
   int blocks = (n_recv + BW_WARPS - 1) / BW_WARPS;
   if (blocks > 148) blocks = 148;
   if (first_layer)
-    attn_bwd_sym_kernel<true><<<blocks, BW_WARPS * 32, kSmemBwFirst, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F);
+    { attn_bwd_sym_kernel<true><<<blocks, BW_WARPS * 32, kSmemBwFirst, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F); count_launch(); }
   else
-    attn_bwd_sym_kernel<false><<<blocks, BW_WARPS * 32, kSmemBw, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F);
+    { attn_bwd_sym_kernel<false><<<blocks, BW_WARPS * 32, kSmemBw, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F); count_launch(); }
 }
 
 }  // namespace so3lr

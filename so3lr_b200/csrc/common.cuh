@@ -32,6 +32,10 @@ enum Status : int {
     }                                                                                 \
   } while (0)
 
+// Every kernel launch of the library is followed by count_launch(): the evaluation context whose entry point is running
+// on this host thread keeps the total (so3lr_b200_system_stats).
+void count_launch(int kernels = 1);
+
 constexpr float kCutoffSr = 4.5f;
 constexpr float kAvgNumNeighbors = 13.168995780096482f;
 constexpr float kLnEps = 1e-6f;

@@ -18,6 +18,15 @@ struct so3lr_b200_model {
 };
 
 namespace {
+thread_local int64_t* tl_launch_counter = nullptr;   // the running entry point's context counter
+}
+namespace so3lr {
+void count_launch(int kernels) {
+  if (tl_launch_counter) *tl_launch_counter += kernels;
+}
+}  // namespace so3lr
+
+namespace {
 
 // tracked device allocation
 struct Pool {
@@ -248,7 +257,7 @@ namespace {
 void fill(cudaStream_t s, float* p, size_t n, float v) {
   if (n == 0) return;
   if (v == 0.f) { cudaMemsetAsync(p, 0, n * sizeof(float), s); return; }
-  fill_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p, n, v);
+  { fill_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p, n, v); count_launch(); }
 }
 
 int ensure_edge_buffers(so3lr_b200_system* S, long long n_edges) {
@@ -271,8 +280,8 @@ int rebuild_lists(so3lr_b200_system* S, cudaStream_t st, const float* R_user, bo
   if (S->sorted) {
     int rc0 = spatial_order(S->nws, st, S->cell, S->n, R_user, r_sr, S->d_perm);
     if (rc0) return rc0;
-    gather_positions_kernel<<<nb, 256, 0, st>>>(S->n, S->d_perm, R_user, S->d_Rs);
-    gather_int_kernel<<<nb, 256, 0, st>>>(S->n, S->d_perm, S->d_Z0, S->d_Zs);
+    { gather_positions_kernel<<<nb, 256, 0, st>>>(S->n, S->d_perm, R_user, S->d_Rs); count_launch(); }
+    { gather_int_kernel<<<nb, 256, 0, st>>>(S->n, S->d_perm, S->d_Z0, S->d_Zs); count_launch(); }
     R = S->d_Rs;
     S->d_Z = S->d_Zs;
     S->o_e_atom = S->u_e_atom; S->o_q = S->u_q; S->o_h = S->u_h; S->o_zbl = S->u_zbl; S->o_coul = S->u_coul; S->o_disp = S->u_disp;
@@ -303,7 +312,6 @@ int rebuild_lists(so3lr_b200_system* S, cudaStream_t st, const float* R_user, bo
   if (rc) return rc;
   S->have_lists = true;
   S->n_rebuilds++;
-  S->n_launches += 12;
   return kOk;
 }
 
@@ -319,13 +327,11 @@ int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, co
   fill(st, S->gq, n, 0.f); fill(st, S->gh, n, 0.f);
   S->prof.begin(kPGeom, st); launch_sr_geometry_zbl(st, M, S->cell, n, n_edges, edge_i, nbr_j, S->d_Z, nullptr, 1, dR, S->e_zbl, g_dR, ge, nullptr); S->prof.end(st);
   launch_embed(st, M, S->d_Z, n, S->x[0]);
-  S->n_launches += 7;
   for (int l = 0; l < kNumLayers; ++l) {
     const LayerDev& L = M.layer[l];
     S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], n, S->qkv[l]); S->prof.end(st);
     S->prof.begin(kPAttnFwd, st); launch_attn_fwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]); S->prof.end(st);
     S->prof.begin(kPPostFwd, st); launch_atom_post_fwd(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]); S->prof.end(st);
-    S->n_launches += 3;
   }
   S->prof.begin(kPHeads, st); launch_heads_fwd(st, M, n, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv); S->prof.end(st);
   launch_charge_conserve(st, S->n_graphs, S->d_graph_start, S->q_raw, S->d_total_charge, S->hv, S->q, S->h);
@@ -333,10 +339,9 @@ int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, co
   launch_pair_lr(st, S->lr, S->cell, n, row_ptr_lr, nbr_j_lr, S->d_Z, nullptr, S->q, S->h, 1, dR_lr_in, g_dR_lr_out, nullptr, nullptr, S->gq,
                  S->gh, S->e_coul, S->e_disp, ge);
   S->prof.end(st);
-  combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom);
+  { combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
   launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw);
   S->prof.begin(kPHeads, st); launch_heads_bwd(st, M, n, S->d_Z, S->ze, S->zq, S->zh, S->hv, ge ? ge : S->ones, S->gq_raw, S->gh, S->g4); S->prof.end(st);
-  S->n_launches += 6;
   float* gev2 = S->gev_a;
   float* gev_in = S->gev_b;
   fill(st, gev2, (size_t)n * kMTot, 0.f);
@@ -351,10 +356,8 @@ int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, co
       SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)n * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
       S->prof.begin(kPProjBwd, st); launch_proj_bwd(st, L, S->g_qkv, n, S->g4, 1); S->prof.end(st);
       float* t = gev2; gev2 = gev_in; gev_in = t;
-      S->n_launches += 6;
     } else {
       S->prof.begin(kPAttnBwd, st); launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, nullptr, nullptr, g_dR, 1); S->prof.end(st);
-      S->n_launches += 2;
     }
   }
   SO3LR_CUDA_CHECK(cudaGetLastError());
@@ -444,7 +447,6 @@ int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const S
   const bool tab0 = S->sp.n_species > 0 && use_layer0_tables();
   const bool fuse = use_mma_dense();   // q/k/v rows of layer l+1 come out of layer l's dense block
   if (!tab0) launch_embed(st, M, S->d_Z, c.n3, S->x[0]);
-  S->n_launches += 4;
   for (int l = 0; l < kNumLayers; ++l) {
     const LayerDev& L = M.layer[l];
     if (l == 0 && tab0) {
@@ -462,12 +464,10 @@ int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const S
     post_fwd_dispatch(st, L, nrecv[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1],
                       emit ? &M.layer[l + 1] : nullptr, emit ? S->qkv[l + 1] : nullptr);
     S->prof.end(st);
-    S->n_launches += 3;
   }
   S->prof.begin(kPHeads, st);
   heads_fwd_dispatch(st, M, c.n0, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv);
   S->prof.end(st);
-  S->n_launches += 1;
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
@@ -484,7 +484,6 @@ int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float
   float* gev2 = S->gev_a;
   float* gev_in = S->gev_b;
   fill(st, gev2, (size_t)c.n0 * kMTot, 0.f);
-  S->n_launches += 2;
   for (int l = kNumLayers - 1; l >= 0; --l) {
     const LayerDev& L = M.layer[l];
     const bool fused_in = use_mma_dense() && l + 1 < kNumLayers;   // cotangent formed from the layer above inside the block
@@ -502,13 +501,11 @@ int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float
     else
       attn_bwd_dispatch(st, L, nattn[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, F, l == 0 ? 1 : 0);
     S->prof.end(st);
-    S->n_launches += 2;
     if (l > 0) {
       if (!use_mma_dense()) {
         // dL/dx_in = g_xa (skip connection) + projections^T
         SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)nattn[l] * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
         S->prof.begin(kPProjBwd, st); launch_proj_bwd(st, L, S->g_qkv, nattn[l], S->g4, 1); S->prof.end(st);
-        S->n_launches += 2;
       }
       float* t = gev2; gev2 = gev_in; gev_in = t;
     }
@@ -529,9 +526,8 @@ int evaluate_fused(so3lr_b200_system* S, cudaStream_t st, const float* R, float*
   launch_pair_lr(st, S->lr, S->cell, n, S->lrl.row_ptr, S->lrl.nbr_j, S->d_Z, R, S->q, S->h, 0, nullptr, nullptr, nullptr, F, S->gq, S->gh,
                  S->e_coul, S->e_disp, nullptr);
   S->prof.end(st);
-  combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom);
+  { combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
   launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw);
-  S->n_launches += 8;
   return fused_backward(S, st, c, F);
 }
 
@@ -603,6 +599,7 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
       }
   SO3LR_CUDA_CHECK(cudaSetDevice(model->device));
   so3lr_b200_system* S = new so3lr_b200_system();
+  tl_launch_counter = &S->n_launches;
   S->model = model; S->n = n_atoms; S->n_cap = n_atoms; S->n_graphs = n_graphs; S->opt = *options;
   int rc = make_cell(cell9, &S->cell);
   if (rc) { delete S; return rc; }
@@ -681,6 +678,7 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
 
 SO3LR_B200_API int so3lr_b200_system_destroy(so3lr_b200_system* S) {
   if (!S) return kOk;
+  if (tl_launch_counter == &S->n_launches) tl_launch_counter = nullptr;
   cudaSetDevice(S->model->device);
   cudaDeviceSynchronize();
   S->pool.release();
@@ -716,10 +714,9 @@ static int prepare_lists(so3lr_b200_system* S, cudaStream_t st, const float* R, 
     else {
       float thr = 0.5f * S->opt.skin;
       SO3LR_CUDA_CHECK(cudaMemsetAsync(S->d_flag, 0, sizeof(int), st));
-      moved_kernel<<<(S->n + 255) / 256, 256, 0, st>>>(S->n, R, S->d_Rref, thr * thr, S->d_flag);
+      { moved_kernel<<<(S->n + 255) / 256, 256, 0, st>>>(S->n, R, S->d_Rref, thr * thr, S->d_flag); count_launch(); }
       SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_flag, S->d_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
       SO3LR_CUDA_CHECK(cudaStreamSynchronize(st));
-      S->n_launches += 1;
       if (*S->h_flag & 2) return kNotFinite;
       rebuild = *S->h_flag != 0;
     }
@@ -737,6 +734,7 @@ SO3LR_B200_API int so3lr_b200_system_compute(so3lr_b200_system* S, void* stream,
                               float* charges, float* hirshfeld, float* dipole) {
   if (!S || !R) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   cudaStream_t st = (cudaStream_t)stream;
   int rc = prepare_lists(S, st, R);
   if (rc) return rc;
@@ -744,18 +742,16 @@ SO3LR_B200_API int so3lr_b200_system_compute(so3lr_b200_system* S, void* stream,
   const int n = S->n;
   const float* R_eval = R;
   if (S->sorted) {
-    gather_positions_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->d_perm, R, S->d_Rs);
+    { gather_positions_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->d_perm, R, S->d_Rs); count_launch(); }
     R_eval = S->d_Rs;
   }
   rc = evaluate_fused(S, st, R_eval, S->sorted ? S->F_s : Fout);
   if (rc) return rc;
   launch_graph_reduce(st, S->n_graphs, S->d_graph_start, S->e_atom, S->q, R_eval, S->d_energy, S->d_dipole);
-  S->n_launches += 1;
   if (S->sorted) {
     UnsortArgs A{{S->e_atom, S->q, S->h, S->e_zbl, S->e_coul, S->e_disp, nullptr},
                  {S->u_e_atom, S->u_q, S->u_h, S->u_zbl, S->u_coul, S->u_disp, nullptr}};
-    unsort_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->d_perm, S->F_s, Fout, A);
-    S->n_launches += 2;
+    { unsort_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->d_perm, S->F_s, Fout, A); count_launch(); }
   }
   if (e_atom) SO3LR_CUDA_CHECK(cudaMemcpyAsync(e_atom, S->o_e_atom, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
   if (energy) SO3LR_CUDA_CHECK(cudaMemcpyAsync(energy, S->d_energy, (size_t)S->n_graphs * sizeof(double), cudaMemcpyDeviceToDevice, st));
@@ -769,6 +765,7 @@ SO3LR_B200_API int so3lr_b200_system_compute_host(so3lr_b200_system* S, const fl
                                    float* h_host, float* dip_host) {
   if (!S || !R_host) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   cudaStream_t st = S->own_stream;
   const int n = S->n;
   std::memcpy(S->h_R, R_host, (size_t)n * 3 * sizeof(float));
@@ -810,6 +807,7 @@ SO3LR_B200_API int so3lr_b200_system_export_list(so3lr_b200_system* S, void* str
                                   int64_t* count_host, int* overflow_host) {
   if (!S || !R || !idx || capacity <= 0) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   cudaStream_t st = (cudaStream_t)stream;
   S->have_lists = false;
   int rc = prepare_lists(S, st, R, false);   // lists in the caller's atom order
@@ -817,7 +815,7 @@ SO3LR_B200_API int so3lr_b200_system_export_list(so3lr_b200_system* S, void* str
   S->have_lists = false;                      // the next evaluation rebuilds them in its own (sorted) order
   const NeighborListDev& L = which == 0 ? S->sr : S->lrl;
   long long cnt = L.count < capacity ? L.count : capacity;
-  export_list_kernel<<<(unsigned)((capacity + 255) / 256), 256, 0, st>>>(S->n, cnt, capacity, L.edge_i, L.nbr_j, idx);
+  { export_list_kernel<<<(unsigned)((capacity + 255) / 256), 256, 0, st>>>(S->n, cnt, capacity, L.edge_i, L.nbr_j, idx); count_launch(); }
   SO3LR_CUDA_CHECK(cudaStreamSynchronize(st));
   if (count_host) *count_host = L.count;
   if (overflow_host) *overflow_host = L.count > capacity ? 1 : 0;
@@ -831,14 +829,14 @@ SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* S, void* stre
   if (!S || !idx_i || !idx_j || !edges || !g_edges || n_edges < 0 || n_pairs < 0) return kInvalidArgument;
   if (n_pairs > 0 && (!idx_i_lr || !idx_j_lr || !edges_lr || !g_edges_lr)) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   cudaStream_t st = (cudaStream_t)stream;
   const int n = S->n;
   // graph-level lists are in the caller's atom order
   S->d_Z = S->d_Z0; S->sorted = false; S->have_lists = false;
   S->o_e_atom = S->e_atom; S->o_q = S->q; S->o_h = S->h; S->o_zbl = S->e_zbl; S->o_coul = S->e_coul; S->o_disp = S->e_disp;
-  row_ptr_from_sorted_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(n, n_edges, idx_i, S->d_rowptr_g);
-  row_ptr_from_sorted_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(n, n_pairs, idx_i_lr, S->d_rowptr_lr_g);
-  S->n_launches += 2;
+  { row_ptr_from_sorted_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(n, n_edges, idx_i, S->d_rowptr_g); count_launch(); }
+  { row_ptr_from_sorted_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(n, n_pairs, idx_i_lr, S->d_rowptr_lr_g); count_launch(); }
   int rc = evaluate_graph(S, st, S->d_rowptr_g, idx_j, idx_i, n_edges, S->d_rowptr_lr_g, idx_j_lr, edges, edges_lr, g_edges, g_edges_lr,
                           g_e_atom);
   if (rc) return rc;
@@ -852,14 +850,14 @@ SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* S, void* stream, int
                           float* F, double* energy) {
   if (!S || !masses || !R || !V || !F || n_steps < 0) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   cudaStream_t st = (cudaStream_t)stream;
   const int n = S->n, blocks = (n + 255) / 256;
   for (int step = 0; step < n_steps; ++step) {
-    vv_first_kernel<<<blocks, 256, 0, st>>>(n, dt, masses, R, V, F);
+    { vv_first_kernel<<<blocks, 256, 0, st>>>(n, dt, masses, R, V, F); count_launch(); }
     int rc = so3lr_b200_system_compute(S, st, R, F, nullptr, step == n_steps - 1 ? energy : nullptr, nullptr, nullptr, nullptr);
     if (rc) return rc;
-    vv_second_kernel<<<blocks, 256, 0, st>>>(n, dt, masses, V, F);
-    S->n_launches += 2;
+    { vv_second_kernel<<<blocks, 256, 0, st>>>(n, dt, masses, V, F); count_launch(); }
   }
   return kOk;
 }
@@ -873,6 +871,7 @@ SO3LR_B200_API int so3lr_b200_dd_set_atoms(so3lr_b200_system* S, int n_local, co
   if (!(shells4[0] > 0 && shells4[0] <= shells4[1] && shells4[1] <= shells4[2] && shells4[2] <= shells4[3] && shells4[3] == n_local))
     return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   int rc = make_cell(cell9, &S->cell);
   if (rc) return rc;
   S->n = n_local;
@@ -896,6 +895,7 @@ SO3LR_B200_API int so3lr_b200_dd_begin(so3lr_b200_system* S, void* stream, const
   if (!S || !R_local_dev || S->shells[3] != S->n || S->n <= 0) return kInvalidArgument;
   if (!(S->opt.cutoff_lr > 0.f)) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0], n1 = S->shells[1];
   if (!S->have_lists) {
@@ -910,7 +910,6 @@ SO3LR_B200_API int so3lr_b200_dd_begin(so3lr_b200_system* S, void* stream, const
     S->prof.end(st);
     S->have_lists = true;
     S->n_rebuilds++;
-    S->n_launches += 12;
   }
   const ModelDev& M = S->model->M;
   fill(st, S->e_zbl, n0, 0.f);
@@ -920,7 +919,6 @@ SO3LR_B200_API int so3lr_b200_dd_begin(so3lr_b200_system* S, void* stream, const
                          S->F_s, n0);
   S->prof.end(st);
   if (!(S->sp.n_species > 0 && use_layer0_tables())) launch_embed(st, M, S->d_Z, n1, S->x[0]);
-  S->n_launches += 4;
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
@@ -928,6 +926,7 @@ SO3LR_B200_API int so3lr_b200_dd_begin(so3lr_b200_system* S, void* stream, const
 SO3LR_B200_API int so3lr_b200_dd_layer_forward(so3lr_b200_system* S, void* stream, int layer) {
   if (!S || layer < 0 || layer >= kNumLayers || !S->have_lists) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0], n1 = S->shells[1], l = layer;
   const LayerDev& L = S->model->M.layer[l];
@@ -951,7 +950,6 @@ SO3LR_B200_API int so3lr_b200_dd_layer_forward(so3lr_b200_system* S, void* strea
   post_fwd_dispatch(st, L, n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1],
                     emit ? &S->model->M.layer[l + 1] : nullptr, emit ? S->qkv[l + 1] : nullptr);
   S->prof.end(st);
-  S->n_launches += 3;
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
@@ -959,14 +957,14 @@ SO3LR_B200_API int so3lr_b200_dd_layer_forward(so3lr_b200_system* S, void* strea
 SO3LR_B200_API int so3lr_b200_dd_heads(so3lr_b200_system* S, void* stream, float* q_raw_owned_dev, float* h_owned_dev) {
   if (!S || !q_raw_owned_dev || !h_owned_dev || !S->have_lists) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0];
   S->prof.begin(kPHeads, st);
   heads_fwd_dispatch(st, S->model->M, n0, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv);
   S->prof.end(st);
   SO3LR_CUDA_CHECK(cudaMemcpyAsync(q_raw_owned_dev, S->q_raw, (size_t)n0 * sizeof(float), cudaMemcpyDeviceToDevice, st));
-  abs_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->hv, h_owned_dev);
-  S->n_launches += 2;
+  { abs_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->hv, h_owned_dev); count_launch(); }
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
@@ -975,14 +973,14 @@ SO3LR_B200_API int so3lr_b200_dd_pair(so3lr_b200_system* S, void* stream, const 
                                       const float* h_local_dev, double* gq_sum_dev) {
   if (!S || !R_local_dev || !q_local_dev || !h_local_dev || !gq_sum_dev || !S->have_lists) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0];
   S->prof.begin(kPPairLr, st);
   launch_pair_lr_owned(st, S->lr, S->cell, n0, S->n, S->lrl.row_ptr, S->lrl.nbr_j, S->d_Z, R_local_dev, q_local_dev, h_local_dev, S->F_s,
                        S->gq, S->gh, S->e_coul, S->e_disp);
   S->prof.end(st);
-  sum_to_double_kernel<<<1, 1024, 0, st>>>(n0, S->gq, gq_sum_dev);
-  S->n_launches += 2;
+  { sum_to_double_kernel<<<1, 1024, 0, st>>>(n0, S->gq, gq_sum_dev); count_launch(); }
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
@@ -991,17 +989,17 @@ SO3LR_B200_API int so3lr_b200_dd_heads_backward(so3lr_b200_system* S, void* stre
                                                 double* energy_owned_dev) {
   if (!S || !gq_sum_all_dev || n_atoms_all <= 0 || !S->have_lists) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0];
-  subtract_mean_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->gq, gq_sum_all_dev, (double)n_atoms_all, S->gq_raw);
-  combine_energy_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom);
-  if (energy_owned_dev) sum_to_double_kernel<<<1, 1024, 0, st>>>(n0, S->e_atom, energy_owned_dev);
+  { subtract_mean_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->gq, gq_sum_all_dev, (double)n_atoms_all, S->gq_raw); count_launch(); }
+  { combine_energy_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
+  if (energy_owned_dev) { sum_to_double_kernel<<<1, 1024, 0, st>>>(n0, S->e_atom, energy_owned_dev); count_launch(); }
   S->prof.begin(kPHeads, st);
   heads_bwd_dispatch(st, S->model->M, n0, S->d_Z, S->ze, S->zq, S->zh, S->hv, S->ones, S->gq_raw, S->gh, S->g4);
   S->prof.end(st);
   S->dd_gev2 = S->gev_a; S->dd_gev_in = S->gev_b;
   fill(st, S->dd_gev2, (size_t)n0 * kMTot, 0.f);
-  S->n_launches += 5;
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
@@ -1010,6 +1008,7 @@ SO3LR_B200_API int so3lr_b200_dd_heads_backward(so3lr_b200_system* S, void* stre
 SO3LR_B200_API int so3lr_b200_dd_layer_backward_post(so3lr_b200_system* S, void* stream, int layer) {
   if (!S || layer < 0 || layer >= kNumLayers || !S->have_lists || !S->dd_gev2) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0], l = layer;
   const bool fused_in = use_mma_dense() && l + 1 < kNumLayers;
@@ -1017,7 +1016,6 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_post(so3lr_b200_system* S, void*
   post_bwd_dispatch(st, S->model->M.layer[l], n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, S->dd_gev2, S->g_xa, S->gev1,
                     fused_in ? &S->model->M.layer[l + 1] : nullptr, S->g_qkv);
   S->prof.end(st);
-  S->n_launches += 1;
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
@@ -1026,6 +1024,7 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_post(so3lr_b200_system* S, void*
 SO3LR_B200_API int so3lr_b200_dd_layer_backward_attn(so3lr_b200_system* S, void* stream, int layer) {
   if (!S || layer < 0 || layer >= kNumLayers || !S->have_lists || !S->dd_gev2) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0], l = layer;
   const LayerDev& L = S->model->M.layer[l];
@@ -1036,12 +1035,10 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_attn(so3lr_b200_system* S, void*
     attn_bwd_dispatch(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, S->dd_gev_in, S->F_s,
                       l == 0 ? 1 : 0);
   S->prof.end(st);
-  S->n_launches += 1;
   if (l > 0) {
     if (!use_mma_dense()) {
       SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)n0 * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
       S->prof.begin(kPProjBwd, st); launch_proj_bwd(st, L, S->g_qkv, n0, S->g4, 1); S->prof.end(st);
-      S->n_launches += 2;
     }
     float* t = S->dd_gev2; S->dd_gev2 = S->dd_gev_in; S->dd_gev_in = t;
   }
@@ -1052,6 +1049,7 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_attn(so3lr_b200_system* S, void*
 SO3LR_B200_API int so3lr_b200_dd_forces(so3lr_b200_system* S, void* stream, float* F_owned_dev) {
   if (!S || !F_owned_dev) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   SO3LR_CUDA_CHECK(cudaMemcpyAsync(F_owned_dev, S->F_s, (size_t)S->shells[0] * 3 * sizeof(float), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
   return kOk;
 }
@@ -1077,6 +1075,7 @@ SO3LR_B200_API int so3lr_b200_system_profile(so3lr_b200_system* S, int enable) {
 SO3LR_B200_API int so3lr_b200_system_profile_read(so3lr_b200_system* S, int max_groups, float* ms_total, int64_t* launches, const char** names) {
   if (!S || !ms_total || !launches) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
   SO3LR_CUDA_CHECK(cudaDeviceSynchronize());
   int ng = max_groups < (int)kPGroups ? max_groups : (int)kPGroups;
   for (int g = 0; g < ng; ++g) { ms_total[g] = 0.f; launches[g] = 0; if (names) names[g] = kProfNames[g]; }

@@ -302,7 +302,7 @@ int species_tables_build(cudaStream_t st, const ModelDev& M, const int* Z_host, 
   launch_proj_fwd(st, M.layer[0], T->x_sp, ns, T->qkv_sp);
   SO3LR_CUDA_CHECK(cudaMemcpy2DAsync(T->v_sp, kF * sizeof(float), T->qkv_sp + 2 * kF, kProj * sizeof(float), kF * sizeof(float), ns,
                                      cudaMemcpyDeviceToDevice, st));
-  build_pair_table_kernel<<<ns * ns, 256, 0, st>>>(M.layer[0].table, T->qkv_sp, ns, T->table);
+  { build_pair_table_kernel<<<ns * ns, 256, 0, st>>>(M.layer[0].table, T->qkv_sp, ns, T->table); count_launch(); }
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
@@ -315,14 +315,14 @@ void species_tables_free(SpeciesTables* T) {
 void launch_layer0_fwd_tab(cudaStream_t s, const SpeciesTables& T, const ModelDev& M, int n_recv, int n, const int* row_ptr,
                            const int* nbr_j, const float* dR, const int* Z, float* xa, float* ev1) {
   if (n_recv <= 0) return;
-  layer0_fwd_tab_kernel<<<(n_recv + 7) / 8, 256, 0, s>>>(T, M.embed_z, n_recv, n, row_ptr, nbr_j, dR, Z, xa, ev1);
+  { layer0_fwd_tab_kernel<<<(n_recv + 7) / 8, 256, 0, s>>>(T, M.embed_z, n_recv, n, row_ptr, nbr_j, dR, Z, xa, ev1); count_launch(); }
 }
 
 void launch_layer0_bwd_tab(cudaStream_t s, const SpeciesTables& T, int n_recv, int n_gv, int n, const int* row_ptr, const int* nbr_j,
                            const float* dR, const int* Z, const float* g_xa, const float* gev1, float* GV, float* F) {
   if (n_recv <= 0) return;
-  layer0_gv_kernel<<<(n_gv + 7) / 8, 256, 0, s>>>(T, n_gv, g_xa, GV);
-  layer0_bwd_tab_kernel<<<(n_recv + 7) / 8, 256, 0, s>>>(T, n_recv, n, row_ptr, nbr_j, dR, Z, GV, gev1, F);
+  { layer0_gv_kernel<<<(n_gv + 7) / 8, 256, 0, s>>>(T, n_gv, g_xa, GV); count_launch(); }
+  { layer0_bwd_tab_kernel<<<(n_recv + 7) / 8, 256, 0, s>>>(T, n_recv, n, row_ptr, nbr_j, dR, Z, GV, gev1, F); count_launch(); }
 }
 
 }  // namespace so3lr

@@ -251,7 +251,7 @@ int spatial_order(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, co
     if (nc > 1024) nc = 1024;
     G.nc[k] = nc; G.wrap[k] = 1;
   }
-  morton_keys_kernel<<<(n + 255) / 256, 256, 0, s>>>(cell, G, n, R, w->key, w->atom_iota);
+  { morton_keys_kernel<<<(n + 255) / 256, 256, 0, s>>>(cell, G, n, R, w->key, w->atom_iota); count_launch(); }
   size_t need = 0;
   cub::DeviceRadixSort::SortPairs(nullptr, need, w->key, w->key_sorted, w->atom_iota, perm, n, 0, 30, s);
   if (need > w->sort_bytes) {
@@ -262,6 +262,7 @@ int spatial_order(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, co
   }
   size_t tmp = w->sort_bytes;
   cub::DeviceRadixSort::SortPairs(w->sort_tmp, tmp, w->key, w->key_sorted, w->atom_iota, perm, n, 0, 30, s);
+  count_launch(6);   // histogram, prefix, four 8-bit passes
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
@@ -330,7 +331,7 @@ int nlist_build(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, cons
       if ((st = ensure(&w->cell_start, (size_t)n_cells + 1))) return st;
       w->cell_cap = n_cells + 1;
     }
-    assign_cells_kernel<<<(n + 255) / 256, 256, 0, s>>>(cell, G, n, R, w->cell_of, w->atom_iota);
+    { assign_cells_kernel<<<(n + 255) / 256, 256, 0, s>>>(cell, G, n, R, w->cell_of, w->atom_iota); count_launch(); }
     int bits = 1;
     while ((1 << bits) < n_cells && bits < 31) ++bits;
     size_t need = 0;
@@ -345,8 +346,9 @@ int nlist_build(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, cons
     }
     size_t tmp = w->cub_bytes;
     cub::DeviceRadixSort::SortPairs(w->cub_tmp, tmp, w->cell_of, w->cell_sorted, w->atom_iota, w->atom_sorted, n, 0, bits, s);
-    cell_bounds_kernel<<<(n + 1 + 255) / 256, 256, 0, s>>>(n, n_cells, w->cell_sorted, w->cell_start);
-    gather_sorted_positions_kernel<<<(n + 255) / 256, 256, 0, s>>>(n, R, w->atom_sorted, w->pos_sorted);
+    count_launch(2 + (bits + 7) / 8);
+    { cell_bounds_kernel<<<(n + 1 + 255) / 256, 256, 0, s>>>(n, n_cells, w->cell_sorted, w->cell_start); count_launch(); }
+    { gather_sorted_positions_kernel<<<(n + 255) / 256, 256, 0, s>>>(n, R, w->atom_sorted, w->pos_sorted); count_launch(); }
   } else {
     size_t need = 0;
     cub::DeviceScan::ExclusiveSum(nullptr, need, w->row_count, out->row_ptr, n, s);
@@ -359,13 +361,14 @@ int nlist_build(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, cons
   const int blocks = (n_rows + 7) / 8;
   if (n_rows == 0) { out->count = 0; return kOk; }
   if (by_graph)
-    build_rows_graph_kernel<false><<<blocks, 256, 0, s>>>(n_rows, R, r2max, ordered, seg, graph_start, w->row_count, nullptr, nullptr, nullptr, 0);
+    { build_rows_graph_kernel<false><<<blocks, 256, 0, s>>>(n_rows, R, r2max, ordered, seg, graph_start, w->row_count, nullptr, nullptr, nullptr, 0); count_launch(); }
   else
-    build_rows_kernel<false><<<blocks, 256, 0, s>>>(cell, G, n_rows, R, r2max, ordered, seg, w->pos_sorted, w->cell_start,
-                                                    w->row_count, nullptr, nullptr, nullptr, 0);
+    { build_rows_kernel<false><<<blocks, 256, 0, s>>>(cell, G, n_rows, R, r2max, ordered, seg, w->pos_sorted, w->cell_start,
+                                                    w->row_count, nullptr, nullptr, nullptr, 0); count_launch(); }
   size_t tmp = w->cub_bytes;
   cub::DeviceScan::ExclusiveSum(w->cub_tmp, tmp, w->row_count, out->row_ptr, n_rows, s);
-  finish_scan_kernel<<<1, 32, 0, s>>>(n_rows, w->row_count, out->row_ptr, w->d_total, out->capacity, allow_grow ? nullptr : d_overflow);
+  count_launch(2);
+  { finish_scan_kernel<<<1, 32, 0, s>>>(n_rows, w->row_count, out->row_ptr, w->d_total, out->capacity, allow_grow ? nullptr : d_overflow); count_launch(); }
   SO3LR_CUDA_CHECK(cudaMemcpyAsync(w->h_total, w->d_total, sizeof(long long), cudaMemcpyDeviceToHost, s));
   SO3LR_CUDA_CHECK(cudaStreamSynchronize(s));
   const long long total = *w->h_total;
@@ -386,12 +389,12 @@ int nlist_build(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, cons
   if (total <= out->capacity) out->count = total;
   const bool truncated = total > out->capacity;
   if (by_graph)
-    build_rows_graph_kernel<true><<<blocks, 256, 0, s>>>(n_rows, R, r2max, ordered, seg, graph_start, nullptr, out->row_ptr,
-                                                         out->nbr_j, out->edge_i, out->capacity);
+    { build_rows_graph_kernel<true><<<blocks, 256, 0, s>>>(n_rows, R, r2max, ordered, seg, graph_start, nullptr, out->row_ptr,
+                                                         out->nbr_j, out->edge_i, out->capacity); count_launch(); }
   else
-    build_rows_kernel<true><<<blocks, 256, 0, s>>>(cell, G, n_rows, R, r2max, ordered, seg, w->pos_sorted, w->cell_start, nullptr,
-                                                   out->row_ptr, out->nbr_j, out->edge_i, out->capacity);
-  if (truncated) clamp_rows_kernel<<<(n_rows + 1 + 255) / 256, 256, 0, s>>>(n_rows, out->row_ptr, out->capacity);
+    { build_rows_kernel<true><<<blocks, 256, 0, s>>>(cell, G, n_rows, R, r2max, ordered, seg, w->pos_sorted, w->cell_start, nullptr,
+                                                   out->row_ptr, out->nbr_j, out->edge_i, out->capacity); count_launch(); }
+  if (truncated) { clamp_rows_kernel<<<(n_rows + 1 + 255) / 256, 256, 0, s>>>(n_rows, out->row_ptr, out->capacity); count_launch(); }
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return truncated ? kOverflow : kOk;
 }

@@ -259,13 +259,13 @@ void launch_sr_geometry_zbl(cudaStream_t s, const ModelDev& M, const Cell& cell,
                             float* F_direct, int n_owned) {
   if (n_edges <= 0) return;
   unsigned blocks = (unsigned)((n_edges + 255) / 256);
-  sr_geometry_zbl_kernel<<<blocks, 256, 0, s>>>(M.zbl, cell, n, n_edges, edge_i, nbr_j, Z, R, dR_given, dR, e_atom, g_dR, ge, F_direct, n_owned);
+  { sr_geometry_zbl_kernel<<<blocks, 256, 0, s>>>(M.zbl, cell, n, n_edges, edge_i, nbr_j, Z, R, dR_given, dR, e_atom, g_dR, ge, F_direct, n_owned); count_launch(); }
 }
 
 void launch_force_scatter(cudaStream_t s, int n, long long n_edges, const int* edge_i, const int* nbr_j, const float* g_dR, float* F) {
   if (n_edges <= 0) return;
   unsigned blocks = (unsigned)((n_edges + 255) / 256);
-  force_scatter_kernel<<<blocks, 256, 0, s>>>(n, n_edges, edge_i, nbr_j, g_dR, F);
+  { force_scatter_kernel<<<blocks, 256, 0, s>>>(n, n_edges, edge_i, nbr_j, g_dR, F); count_launch(); }
 }
 
 void launch_pair_lr(cudaStream_t s, const LrParams& P, const Cell& cell, int n, const int* row_ptr, const int* nbr_j,
@@ -274,31 +274,31 @@ void launch_pair_lr(cudaStream_t s, const LrParams& P, const Cell& cell, int n, 
   if (n <= 0) return;
   int blocks = (n + 7) / 8;
   if (mode == 0)
-    pair_lr_kernel<0><<<blocks, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, Z, R, q, h, dR_lr, g_dR_lr, e_atom, F, gq, gh, e_coul, e_disp, ge);
+    { pair_lr_kernel<0><<<blocks, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, Z, R, q, h, dR_lr, g_dR_lr, e_atom, F, gq, gh, e_coul, e_disp, ge); count_launch(); }
   else
-    pair_lr_kernel<1><<<blocks, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, Z, R, q, h, dR_lr, g_dR_lr, e_atom, F, gq, gh, e_coul, e_disp, ge);
+    { pair_lr_kernel<1><<<blocks, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, Z, R, q, h, dR_lr, g_dR_lr, e_atom, F, gq, gh, e_coul, e_disp, ge); count_launch(); }
 }
 
 void launch_pair_lr_owned(cudaStream_t s, const LrParams& P, const Cell& cell, int n_owned, int n, const int* row_ptr,
                           const int* nbr_j, const int* Z, const float* R, const float* q, const float* h, float* F_add,
                           float* gq, float* gh, float* e_coul, float* e_disp) {
   if (n_owned <= 0) return;
-  pair_lr_owned_kernel<<<(n_owned + 7) / 8, 256, 0, s>>>(P, cell, n_owned, n, row_ptr, nbr_j, Z, R, q, h, F_add, gq, gh, e_coul, e_disp);
+  { pair_lr_owned_kernel<<<(n_owned + 7) / 8, 256, 0, s>>>(P, cell, n_owned, n, row_ptr, nbr_j, Z, R, q, h, F_add, gq, gh, e_coul, e_disp); count_launch(); }
 }
 
 void launch_charge_conserve(cudaStream_t s, int n_graphs, const int* graph_start, const float* q_raw,
                             const float* total_charge, const float* hv, float* q, float* h) {
   if (n_graphs <= 0) return;
-  charge_conserve_kernel<<<n_graphs, 256, 0, s>>>(n_graphs, graph_start, q_raw, total_charge, hv, q, h);
+  { charge_conserve_kernel<<<n_graphs, 256, 0, s>>>(n_graphs, graph_start, q_raw, total_charge, hv, q, h); count_launch(); }
 }
 void launch_charge_conserve_bwd(cudaStream_t s, int n_graphs, const int* graph_start, const float* gq, float* gq_raw) {
   if (n_graphs <= 0) return;
-  charge_conserve_bwd_kernel<<<n_graphs, 256, 0, s>>>(n_graphs, graph_start, gq, gq_raw);
+  { charge_conserve_bwd_kernel<<<n_graphs, 256, 0, s>>>(n_graphs, graph_start, gq, gq_raw); count_launch(); }
 }
 void launch_graph_reduce(cudaStream_t s, int n_graphs, const int* graph_start, const float* e_atom, const float* q,
                          const float* R, double* e_graph, float* dipole) {
   if (n_graphs <= 0) return;
-  graph_reduce_kernel<<<n_graphs, 256, 0, s>>>(n_graphs, graph_start, e_atom, q, R, e_graph, dipole);
+  { graph_reduce_kernel<<<n_graphs, 256, 0, s>>>(n_graphs, graph_start, e_atom, q, R, e_graph, dipole); count_launch(); }
 }
 
 }  // namespace so3lr
