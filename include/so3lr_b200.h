@@ -126,6 +126,33 @@ SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* sys, void* st
 SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* sys, void* stream, int n_steps, float dt_fs, const float* masses_dev,
                           float* positions_dev, float* velocities_dev, float* forces_dev, double* energy_dev);
 
+/* Nose-Hoover chain thermostat (Martyna-Tuckerman-Klein propagation, Suzuki-Yoshida factorisation), as
+ * jax_md.simulate.nvt_nose_hoover applies it: half a thermostat step, velocity Verlet, half a thermostat step.
+ * The chain lives in SO3LR_B200_NHC_STATE_DOUBLES doubles on the device:
+ *   [0] kinetic energy the chain last saw (eV)   [1] momentum scale not yet applied to the velocities
+ *   [2, 10) chain positions                       [10, 18) chain momenta (eV fs)
+ * chain_length 1..8, chain_steps >= 1, sy_steps in {1, 3, 5, 7}; tau in fs, kT in eV; the chain masses are
+ * kT tau^2 (times dof for the first), dof = 3 n_atoms.
+ * Replaces: jax_md.simulate.nvt_nose_hoover as created in so3lr/cli/so3lr_md.py:1047-1075 with the settings of
+ *           so3lr/cli/so3lr_md.py:1698-1707 (defaults so3lr/cli/so3lr_cli.py:114-116). */
+#define SO3LR_B200_NHC_MAX_CHAIN 8
+#define SO3LR_B200_NHC_STATE_DOUBLES 18
+/* Zeroes a chain (scale = 1). */
+SO3LR_B200_API int so3lr_b200_nhc_init(void* stream, double* chain_dev);
+/* Advances a chain by n_half_steps half steps.  When ke_partials_dev is given, the kinetic energy is first set to the
+ * sum of its n_partials entries (eV); a domain-decomposed run passes the all-reduced kinetic energy as one entry.
+ * The momentum scale of the half steps is multiplied into chain_dev[1], or replaces it when fresh_scale is non-zero
+ * (the velocities have taken up the previous value). */
+SO3LR_B200_API int so3lr_b200_nhc_half_steps(void* stream, double* chain_dev, int chain_length, int chain_steps, int sy_steps,
+                                             double dt_fs, double tau_fs, double kT, double dof, int n_half_steps,
+                                             int fresh_scale, const double* ke_partials_dev, int n_partials);
+/* n_steps NVT steps driven by the library, same buffers and units as so3lr_b200_system_nve.  On return the velocities
+ * carry every scale (chain_dev[1] is 1) and chain_dev[0] holds their kinetic energy. */
+SO3LR_B200_API int so3lr_b200_system_nvt(so3lr_b200_system* sys, void* stream, int n_steps, float dt_fs, double kT, double tau_fs,
+                                         int chain_length, int chain_steps, int sy_steps, const float* masses_dev,
+                                         float* positions_dev, float* velocities_dev, float* forces_dev, double* chain_dev,
+                                         double* energy_dev);
+
 /* Domain-decomposed evaluation of one large periodic structure: every rank owns the atoms of its sub-box and holds
  * copies ("ghosts") of the atoms within the long-range list radius (12 A + skin) of it; the ghosts within one short-range
  * shell (4.5 A + skin) also carry features.  The library evaluates one rank's owned atoms layer by layer; between the

@@ -30,7 +30,7 @@ def _load():
             f"{LIB_PATH} not found. Build it with `python so3lr_b200/build.py` (needs nvcc); "
             "so3lr_b200 has no CPU fallback.")
     lib = C.CDLL(LIB_PATH)
-    p, i32, i64, f32 = C.c_void_p, C.c_int, C.c_int64, C.c_float
+    p, i32, i64, f32, f64 = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_double
     sig = {
         "so3lr_b200_version": (i32, []),
         "so3lr_b200_status_string": (C.c_char_p, [i32]),
@@ -46,6 +46,9 @@ def _load():
         "so3lr_b200_system_export_list": (i32, [p, p, p, i32, p, i64, C.POINTER(i64), C.POINTER(i32)]),
         "so3lr_b200_system_graph_eval": (i32, [p, p, i64, p, p, p, i64, p, p, p, p, p, p, p, p, p]),
         "so3lr_b200_system_nve": (i32, [p, p, i32, f32, p, p, p, p, p]),
+        "so3lr_b200_nhc_init": (i32, [p, p]),
+        "so3lr_b200_nhc_half_steps": (i32, [p, p, i32, i32, i32, f64, f64, f64, f64, i32, i32, p, i32]),
+        "so3lr_b200_system_nvt": (i32, [p, p, i32, f32, f64, f64, i32, i32, i32, p, p, p, p, p, p]),
         "so3lr_b200_dd_set_atoms": (i32, [p, i32, p, p, p]),
         "so3lr_b200_dd_begin": (i32, [p, p, p]),
         "so3lr_b200_dd_layer_forward": (i32, [p, p, i32]),

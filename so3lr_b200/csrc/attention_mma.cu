@@ -458,11 +458,11 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_mma_kernel(LayerDev
           BwEdge nx1 = bw_load_edge(rec, g0 + 1, f, col, L.table, qkv, g_xa);
           // four edges per trip (the body is large; a fully unrolled loop overflows the instruction cache)
 #pragma unroll 1
-          for (int kb = 0; kb < GE; kb += 4) {
+          for (int k4 = 0; k4 < GE; k4 += 4) {
             float gr4[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              const int k = kb + u;
+              const int k = k4 + u;
               BwEdge nx2 = nx1;                 // loads run two edges ahead of the arithmetic
               if (k + 2 < GE) nx2 = bw_load_edge(rec, g0 + k + 2, f, col, L.table, qkv, g_xa);
               float* rp = rec + (g0 + k) * kBwRec;
@@ -493,7 +493,7 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_mma_kernel(LayerDev
               st4(wt + k * kWS + col, dw);      // the lane overwrites exactly the words it read: dw takes the place of w
               cur = nx1; nx1 = nx2;
             }
-            // d/dr of the four edges: lane partials -> totals; lane (16a + 8b) ends up with edge kb + 2a + b
+            // d/dr of the four edges: lane partials -> totals; lane (16a + 8b) ends up with edge k4 + 2a + b
             {
               float s0 = (lane & 16) ? gr4[0] : gr4[2], k0 = (lane & 16) ? gr4[2] : gr4[0];
               float s1 = (lane & 16) ? gr4[1] : gr4[3], k1 = (lane & 16) ? gr4[3] : gr4[1];
@@ -503,7 +503,7 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_mma_kernel(LayerDev
               float v = ((lane & 8) ? k1 : k0) + __shfl_xor_sync(0xffffffffu, s2, 8);
               v += __shfl_xor_sync(0xffffffffu, v, 4); v += __shfl_xor_sync(0xffffffffu, v, 2); v += __shfl_xor_sync(0xffffffffu, v, 1);
               if ((lane & 7) == 0) {
-                float* gp = rec + (g0 + kb + ((lane >> 4) & 1) * 2 + ((lane >> 3) & 1)) * kBwRec + 36;
+                float* gp = rec + (g0 + k4 + ((lane >> 4) & 1) * 2 + ((lane >> 3) & 1)) * kBwRec + 36;
                 *gp = f ? *gp + v : v;
               }
             }

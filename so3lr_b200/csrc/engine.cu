@@ -8,6 +8,7 @@
 #include <vector>
 
 #include "kernels.h"
+#include "md.h"
 
 using namespace so3lr;
 
@@ -250,6 +251,7 @@ struct so3lr_b200_system {
   float* d_Rstage = nullptr;
   cudaStream_t own_stream = nullptr;
   int64_t n_rebuilds = 0, n_launches = 0;
+  double* ke_partials = nullptr;   // one kinetic-energy share per block of the velocity kernels
 };
 
 namespace {
@@ -859,6 +861,60 @@ SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* S, void* stream, int
     if (rc) return rc;
     { vv_second_kernel<<<blocks, 256, 0, st>>>(n, dt, masses, V, F); count_launch(); }
   }
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_nhc_init(void* stream, double* chain) {
+  if (!chain) return kInvalidArgument;
+  tl_launch_counter = nullptr;
+  nhc_init((cudaStream_t)stream, chain);
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_nhc_half_steps(void* stream, double* chain, int chain_length, int chain_steps, int sy_steps, double dt,
+                                             double tau, double kT, double dof, int n_half_steps, int fresh_scale,
+                                             const double* ke_partials, int n_partials) {
+  if (!chain || n_half_steps < 0 || (ke_partials && n_partials <= 0)) return kInvalidArgument;
+  if (!nhc_settings_ok(chain_length, chain_steps, sy_steps, dt, tau, kT, dof)) return kInvalidArgument;
+  tl_launch_counter = nullptr;
+  nhc_half_steps((cudaStream_t)stream, chain, chain_length, chain_steps, sy_steps, dt, tau, kT, dof, n_half_steps, fresh_scale,
+                 ke_partials, n_partials);
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_nvt(so3lr_b200_system* S, void* stream, int n_steps, float dt, double kT, double tau,
+                                         int chain_length, int chain_steps, int sy_steps, const float* masses, float* R, float* V,
+                                         float* F, double* chain, double* energy) {
+  if (!S || !masses || !R || !V || !F || !chain || n_steps < 0) return kInvalidArgument;
+  const int n = S->n;
+  const double dof = 3.0 * (double)n;
+  if (!nhc_settings_ok(chain_length, chain_steps, sy_steps, dt, tau, kT, dof)) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int blocks = (n + 255) / 256;
+  if (!S->ke_partials) {
+    S->ke_partials = S->pool.get<double>((size_t)(S->n_cap + 255) / 256);
+    if (!S->ke_partials) return kCudaError;
+  }
+  if (n_steps == 0) return kOk;
+  // the chain's first half step of step 0 works on the kinetic energy of the velocities as they are now
+  md_kinetic_partials(st, n, masses, V, S->ke_partials);
+  nhc_half_steps(st, chain, chain_length, chain_steps, sy_steps, dt, tau, kT, dof, 1, 1, S->ke_partials, blocks);
+  for (int step = 0; step < n_steps; ++step) {
+    md_first_half(st, n, dt, masses, R, V, F, chain);
+    int rc = so3lr_b200_system_compute(S, st, R, F, nullptr, step == n_steps - 1 ? energy : nullptr, nullptr, nullptr, nullptr);
+    if (rc) return rc;
+    md_second_half(st, n, dt, masses, V, F, S->ke_partials);
+    // the second half step of this MD step and the first of the next act on the velocities back to back: one launch, and
+    // their product is applied by the next step's first kernel
+    nhc_half_steps(st, chain, chain_length, chain_steps, sy_steps, dt, tau, kT, dof, step == n_steps - 1 ? 1 : 2, 1, S->ke_partials,
+                   blocks);
+  }
+  md_apply_scale(st, n, V, chain);
+  SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
 

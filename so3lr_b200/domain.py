@@ -218,7 +218,8 @@ class CudaBackend:
       num_layers; set_atoms(Z_local, counts, cell_local); begin(R_local); layer_forward(l); feature_rows(l) -> list of
       (n_local, d) tensors viewing the layer-l features; heads() -> (q_raw, h) of the owned atoms; pair(q_local, h_local)
       -> sum of dE/dq over owned atoms; heads_backward(gq_sum_all, n_all) -> energy of the owned atoms;
-      layer_backward_post(l); cotangent_rows() -> list of (n_local, d) tensors; layer_backward_attn(l); forces() -> (n0, 3).
+      layer_backward_post(l); cotangent_rows() -> list of (n_local, d) tensors; layer_backward_attn(l); forces() -> (n0, 3);
+      for the thermostat: nhc_state() -> chain tensor, nhc_half_steps(chain, n_half, dt, kT, tau, dof, kinetic_energy, ...).
     """
     num_layers = 3
 
@@ -261,6 +262,14 @@ class CudaBackend:
         self._x = [self._buffer(0, l) for l in range(4)]
         self._ev = [self._buffer(1, l) for l in range(4)]
         self._g = [self._buffer(2, 0), self._buffer(3, 0)]
+
+    def nhc_state(self):
+        from .engine import nhc_state
+        return nhc_state(self.device)
+
+    def nhc_half_steps(self, chain, n_half, dt_fs, kT, tau_fs, dof, kinetic_energy, **kw):
+        from .engine import nhc_half_steps
+        nhc_half_steps(chain, n_half, dt_fs, kT, tau_fs, dof, kinetic_energy, **kw)
 
     def begin(self, R_local):
         from .engine import _ptr
@@ -514,6 +523,36 @@ class DomainSystem:
             self.compute()
             s = (0.5 * dt_fs * ACC_UNIT / self.m)[:, None]      # ownership may have changed
             self.V += s * self.F
+        return self.E
+
+    def kinetic_energy(self):
+        """Kinetic energy of all atoms (eV) as a one-element float64 tensor, identical on every rank."""
+        v = self.V.double()
+        ke = 0.5 * (self.m.double() * (v * v).sum(1)).sum().reshape(1) / ACC_UNIT
+        return self.comm.all_reduce_sum(ke)
+
+    def nvt(self, n_steps, dt_fs, kT, tau_fs, chain, chain_length=3, chain_steps=2, sy_steps=3):
+        """Velocity Verlet under a Nose-Hoover chain thermostat on the owned atoms (forces of the current positions must be
+        in self.F).  Every rank carries the same chain (`chain` from backend.nhc_state()) and advances it with the all-reduced
+        kinetic energy, so the ranks scale their velocities by the same factor without a further exchange.  Mirrors
+        jax_md.simulate.nvt_nose_hoover as driven by so3lr/cli/so3lr_md.py:1047-1075."""
+        if n_steps <= 0:
+            return self.E
+        dof = 3.0 * self.n_all
+        kw = dict(chain_length=chain_length, chain_steps=chain_steps, sy_steps=sy_steps)
+        self.backend.nhc_half_steps(chain, 1, dt_fs, kT, tau_fs, dof, self.kinetic_energy(), **kw)
+        for step in range(n_steps):
+            self.V *= chain[1].to(self.V.dtype)
+            s = (0.5 * dt_fs * ACC_UNIT / self.m)[:, None]
+            self.V += s * self.F
+            self.R[: self.n0] += dt_fs * self.V
+            self.compute()
+            s = (0.5 * dt_fs * ACC_UNIT / self.m)[:, None]      # ownership may have changed
+            self.V += s * self.F
+            # the second half step of this MD step and the first of the next act back to back on the velocities
+            self.backend.nhc_half_steps(chain, 1 if step == n_steps - 1 else 2, dt_fs, kT, tau_fs, dof, self.kinetic_energy(), **kw)
+        self.V *= chain[1].to(self.V.dtype)
+        chain[1] = 1.0
         return self.E
 
     # ---- reassembly ----

@@ -171,6 +171,45 @@ class System:
         return E
 
 
+    def nvt(self, n_steps, dt_fs, kT, tau_fs, masses, positions, velocities, forces, chain, chain_length=3, chain_steps=2,
+            sy_steps=3):
+        """In-place velocity-Verlet steps under a Nose-Hoover chain thermostat (kT in eV, tau in fs); `chain` comes from
+        nhc_state() and carries the thermostat between calls.  Returns the per-graph energy of the last step."""
+        E = torch.empty(self.n_graphs, dtype=torch.float64, device=self.device)
+        s = torch.cuda.current_stream(self.device)
+        check(lib.so3lr_b200_system_nvt(self._h, C.c_void_p(s.cuda_stream), int(n_steps), float(dt_fs), float(kT), float(tau_fs),
+                                        int(chain_length), int(chain_steps), int(sy_steps), _ptr(masses), _ptr(positions),
+                                        _ptr(velocities), _ptr(forces), _ptr(chain), _ptr(E)), "nvt")
+        return E
+
+
+NHC_STATE_DOUBLES = 18
+NHC_MAX_CHAIN = 8
+
+
+def nhc_state(device):
+    """A zeroed thermostat chain on `device`: [0] kinetic energy (eV), [1] momentum scale not yet applied, [2:10] chain
+    positions, [10:18] chain momenta (eV fs)."""
+    chain = torch.empty(NHC_STATE_DOUBLES, dtype=torch.float64, device=device)
+    with torch.cuda.device(chain.device):
+        s = torch.cuda.current_stream(chain.device)
+        check(lib.so3lr_b200_nhc_init(C.c_void_p(s.cuda_stream), _ptr(chain)), "nhc_init")
+    return chain
+
+
+def nhc_half_steps(chain, n_half_steps, dt_fs, kT, tau_fs, dof, kinetic_energy=None, chain_length=3, chain_steps=2, sy_steps=3,
+                   fresh_scale=True):
+    """Advances `chain` by half thermostat steps.  `kinetic_energy` (float64 CUDA tensor, eV; its entries are summed) replaces
+    the kinetic energy the chain holds.  The momentum scale of the half steps lands in chain[1]."""
+    ke = kinetic_energy
+    assert ke is None or (ke.is_cuda and ke.dtype == torch.float64 and ke.is_contiguous())
+    with torch.cuda.device(chain.device):
+        s = torch.cuda.current_stream(chain.device)
+        check(lib.so3lr_b200_nhc_half_steps(C.c_void_p(s.cuda_stream), _ptr(chain), int(chain_length), int(chain_steps), int(sy_steps),
+                                            float(dt_fs), float(tau_fs), float(kT), float(dof), int(n_half_steps),
+                                            1 if fresh_scale else 0, _ptr(ke), 0 if ke is None else int(ke.numel())), "nhc_half_steps")
+
+
 def _from_ptr(ptr, n, device):
     """float32 CUDA tensor viewing `n` floats at a raw device address."""
     iface = {"shape": (n,), "typestr": "<f4", "data": (int(ptr), False), "version": 2}

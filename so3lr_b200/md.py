@@ -1,0 +1,111 @@
+"""Host-side mirror of the integrator factories the reference builds its MD loops from.
+
+The reference calls jax_md.simulate.nve / nvt_nose_hoover, which return an (init_fn, apply_fn) pair working on a state
+record (so3lr/cli/so3lr_md.py:1011-1075), and steps the pair inside lax.fori_loop together with the two neighbor-list
+updates (so3lr/cli/so3lr_md.py:1115-1222, 1815-1822).  Here the pair drives so3lr_b200_system_nve / _nvt: positions,
+velocities, forces and the thermostat chain stay on the device, the skin test and list rebuilds happen inside the library's
+force evaluation, and apply_fn takes the number of steps to run before it returns (the body of the reference's inner loop).
+
+Units: Angstrom, fs, amu, eV (kT in eV: kT = KB * T).  The reference converts its inputs with jax-md's metal unit system
+(so3lr/cli/so3lr_md.py:124-161); a time of 1 ps there is 1000 fs here.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from .engine import System, nhc_state
+
+KB = 8.617333262e-5               # eV / K
+ACC_UNIT = 9.648533212331e-3      # eV / (A amu) -> A / fs^2
+
+
+@dataclass
+class MDState:
+    """Counterpart of jax-md's NVEState / NVTNoseHooverState: everything a step needs, resident on the device."""
+    position: torch.Tensor          # (n, 3) float32
+    velocity: torch.Tensor          # (n, 3) float32, A / fs
+    force: torch.Tensor             # (n, 3) float32, eV / A
+    mass: torch.Tensor              # (n,) float32, amu
+    chain: Optional[torch.Tensor]   # thermostat chain (None for NVE), see so3lr_b200.engine.nhc_state
+    energy: Optional[torch.Tensor] = None     # potential energy per graph after the last step
+
+    @property
+    def momentum(self):
+        return self.velocity * self.mass[:, None]
+
+
+def kinetic_energy(state: MDState) -> float:
+    """0.5 sum m v^2 in eV (jax_md.quantity.kinetic_energy, used at so3lr/cli/so3lr_md.py:912-916)."""
+    v = state.velocity.double()
+    return float(0.5 * (state.mass.double() * (v * v).sum(1)).sum() / ACC_UNIT)
+
+
+def temperature(state: MDState) -> float:
+    """Kinetic temperature in K with 3 n degrees of freedom (jax_md.quantity.temperature, so3lr/cli/so3lr_md.py:979-982)."""
+    return 2.0 * kinetic_energy(state) / (3.0 * state.mass.numel() * KB)
+
+
+def _init_state(system: System, R, mass, velocity, kT, seed, chain):
+    dev = system.device
+    R = torch.as_tensor(np.asarray(R, dtype=np.float32) if not torch.is_tensor(R) else R).to(dev, torch.float32).contiguous().clone()
+    m = torch.as_tensor(np.asarray(mass, dtype=np.float32) if not torch.is_tensor(mass) else mass).to(dev, torch.float32)
+    m = m.expand(R.shape[0]).contiguous() if m.dim() == 0 or m.numel() == 1 else m.contiguous()
+    if velocity is None:
+        # Maxwell-Boltzmann draw at kT with the centre-of-mass motion removed (jax-md's initialize_momenta)
+        g = torch.Generator(device="cpu").manual_seed(int(seed))
+        v = torch.randn(R.shape, generator=g, dtype=torch.float64) * torch.sqrt(kT * ACC_UNIT / m.double().cpu())[:, None]
+        v -= (v * m.double().cpu()[:, None]).sum(0) / m.double().sum().cpu()
+        V = v.to(dev, torch.float32).contiguous()
+    else:
+        V = torch.as_tensor(np.asarray(velocity, dtype=np.float32) if not torch.is_tensor(velocity) else velocity)
+        V = V.to(dev, torch.float32).contiguous().clone()
+    out = system.compute(R)
+    return MDState(R, V, out["forces"].clone(), m, chain, out["energy"].clone())
+
+
+def nve(system: System, dt: float):
+    """(init_fn, apply_fn) for velocity Verlet; dt in fs.  Mirrors create_nve_fn (so3lr/cli/so3lr_md.py:1011-1045)."""
+
+    def init_fn(R, mass, velocity=None, kT=0.0, seed=0):
+        return _init_state(system, R, mass, velocity, kT, seed, None)
+
+    def apply_fn(state: MDState, n_steps: int = 1):
+        state.energy = system.nve(n_steps, dt, state.mass, state.position, state.velocity, state.force)
+        return state
+
+    return init_fn, apply_fn
+
+
+def nvt_nose_hoover(system: System, dt: float, kT: float, chain_length: int = 3, chain_steps: int = 2, sy_steps: int = 3,
+                    tau: Optional[float] = None):
+    """(init_fn, apply_fn) for velocity Verlet under a Nose-Hoover chain; dt and tau in fs, kT in eV, tau = 100 dt when
+    not given (the reference passes tau = dt * nhc_thermo, so3lr/cli/so3lr_md.py:1698-1707).  Mirrors create_nhc_fn
+    (so3lr/cli/so3lr_md.py:1047-1075)."""
+    tau = 100.0 * dt if tau is None else float(tau)
+
+    def init_fn(R, mass, velocity=None, seed=0):
+        return _init_state(system, R, mass, velocity, kT, seed, nhc_state(system.device))
+
+    def apply_fn(state: MDState, n_steps: int = 1, kT: float = kT):
+        state.energy = system.nvt(n_steps, dt, kT, tau, state.mass, state.position, state.velocity, state.force, state.chain,
+                                  chain_length=chain_length, chain_steps=chain_steps, sy_steps=sy_steps)
+        return state
+
+    apply_fn.settings = dict(chain_length=chain_length, chain_steps=chain_steps, sy_steps=sy_steps, tau=tau, kT=kT, dt=dt)
+    return init_fn, apply_fn
+
+
+def nvt_nose_hoover_invariant(state: MDState, kT: float, tau: float, chain_length: int = 3) -> float:
+    """Conserved quantity of the thermostatted dynamics in eV (jax_md.simulate.nvt_nose_hoover_invariant, used at
+    so3lr/cli/so3lr_md.py:931-939): E_pot + KE + sum p_xi^2 / 2Q + dof kT xi_0 + kT sum_{k>0} xi_k."""
+    c = state.chain.cpu().numpy()
+    L = chain_length
+    dof = 3.0 * state.mass.numel()
+    Q = kT * tau ** 2 * np.ones(L)
+    Q[0] *= dof
+    xi, p = c[2:2 + L], c[10:10 + L]
+    return float(state.energy.sum()) + kinetic_energy(state) + float(np.sum(p * p / (2 * Q))) + dof * kT * xi[0] + kT * float(xi[1:].sum())

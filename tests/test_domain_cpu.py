@@ -14,6 +14,7 @@ import pytest
 import torch
 import torch.multiprocessing as mp
 
+from oracle import md_oracle as MD
 from so3lr_b200 import domain as D
 
 RC_SR, RC_LR = 4.5, 9.0
@@ -115,6 +116,23 @@ class ToyBackend:
     def forces(self):
         return self.F.float()
 
+    # thermostat chain with the layout of the device one: [0] kinetic energy, [1] waiting scale, [2:10] xi, [10:18] p_xi
+    def nhc_state(self):
+        c = torch.zeros(18, dtype=torch.float64)
+        c[1] = 1.0
+        return c
+
+    def nhc_half_steps(self, chain, n_half, dt_fs, kT, tau_fs, dof, kinetic_energy, chain_length=3, chain_steps=2, sy_steps=3):
+        c = MD.Chain(chain_length, dof, float(kinetic_energy.sum()), kT, tau_fs)
+        c.xi[:] = chain[2:2 + chain_length].numpy()
+        c.p_xi[:] = chain[10:10 + chain_length].numpy()
+        scale = 1.0
+        for _ in range(n_half):
+            scale *= MD.chain_half_step(c, dt_fs, kT, chain_steps, sy_steps)
+        chain[0], chain[1] = c.ke, scale
+        chain[2:2 + chain_length] = torch.from_numpy(c.xi)
+        chain[10:10 + chain_length] = torch.from_numpy(c.p_xi)
+
 
 def _serial_reference(R, cell):
     R = torch.tensor(R, dtype=torch.float64, requires_grad=True)
@@ -138,6 +156,17 @@ def _problem(seed=3, n=160, box=(46.0, 19.0, 19.5)):
     return R.astype(np.float32), cell
 
 
+NVT_STEPS, NVT_DT, NVT_KT, NVT_TAU = 6, 0.5, 0.5, 20.0
+
+
+def _nvt_problem():
+    R, _ = _problem()
+    rng = np.random.default_rng(11)
+    m = rng.uniform(1.0, 16.0, size=len(R)).astype(np.float32)
+    V = (rng.normal(size=R.shape) * 0.05 / np.sqrt(m)[:, None]).astype(np.float32)
+    return R, V, m
+
+
 def _worker(rank, world, port, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     import torch.distributed as dist
@@ -158,6 +187,13 @@ def _worker(rank, world, port, out):
     E2, F2 = dom.compute_host(R)
     E3, F3 = dom.compute_host(R + 0.01)          # small move: no re-partitioning, same forces
     res.update(E2=E2, F2=F2.copy(), E3=E3, F3=F3.copy(), rebuilds_host=dom.n_rebuilds)
+    # thermostatted steps: every rank advances its own copy of the chain with the all-reduced kinetic energy
+    Rt, Vt, mt = _nvt_problem()
+    dom = D.DomainSystem(D.DistComm(), ToyBackend(), Z, Rt, cell, skin=1.0, cutoff_lr=RC_LR, velocities=Vt, masses=mt)
+    dom.compute(check_rebuild=False)
+    chain = dom.backend.nhc_state()
+    dom.nvt(NVT_STEPS, NVT_DT, NVT_KT, NVT_TAU, chain)
+    res.update(Rt=dom.gather_global(dom.R[: dom.n0]).numpy(), Vt=dom.gather_global(dom.V).numpy(), chain=chain.numpy().copy())
     if rank == 0:
         torch.save(res, out)
     dist.barrier()
@@ -187,6 +223,21 @@ def test_decomposed_toy_model_matches_single_domain(tmp_path, world):
     np.testing.assert_allclose(res["F2"], F0, atol=2e-5)
     np.testing.assert_allclose(res["F3"], F0, atol=1e-4)
     assert res["rebuilds_host"] == 3
+    # thermostatted trajectory against the serial integrator of the oracle with the serial forces
+    Rt, Vt, mt = _nvt_problem()
+    force = lambda X: _serial_reference(X, cell)
+    Rs, Vs, ms = Rt.astype(np.float64), Vt.astype(np.float64), mt.astype(np.float64)
+    _, Fs = force(Rs)
+    c = MD.nvt_init(Vs, ms, NVT_KT, NVT_TAU, 3)
+    for _ in range(NVT_STEPS):
+        Rs, Vs, Fs, _ = MD.nvt_step(force, c, Rs, Vs, Fs, ms, NVT_DT, NVT_KT, 2, 3)
+    dt_ = res["Rt"] - Rs
+    dt_[:, 0] -= np.round(dt_[:, 0] / cell[0, 0]) * cell[0, 0]
+    np.testing.assert_allclose(dt_, 0, atol=2e-5)
+    np.testing.assert_allclose(res["Vt"], Vs, atol=2e-6, rtol=1e-5)
+    np.testing.assert_allclose(res["chain"][2:5], c.xi, rtol=1e-5, atol=1e-9)
+    np.testing.assert_allclose(res["chain"][10:13], c.p_xi, rtol=1e-4, atol=1e-7)
+    assert res["chain"][1] == 1.0
     # positions come back in the caller's order, wrapped into the cell along the decomposed axis
     d = res["R1"] - R1
     d[:, 0] -= np.round(d[:, 0] / cell[0, 0]) * cell[0, 0]

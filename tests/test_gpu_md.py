@@ -1,0 +1,177 @@
+"""MD step bodies on the device (velocity Verlet, Nose-Hoover chain) against the oracle's float64 integrators.
+
+Tolerances: the chain itself runs in double on the device -> 1e-12 relative against the oracle's chain; a trajectory of a
+few steps with float32 positions, velocities and forces -> positions 2e-5 A, velocities 2e-6 A/fs (measured ~1e-6 / 1e-7).
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import md_oracle as MD
+from oracle import so3lr_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+KT300 = 300.0 * MD.KB
+
+
+@pytest.mark.parametrize("chain_length,chain_steps,sy_steps", [(3, 2, 3), (1, 1, 1), (5, 3, 5), (8, 1, 7), (2, 4, 3)])
+def test_chain_kernel_matches_oracle(chain_length, chain_steps, sy_steps):
+    from so3lr_b200.engine import nhc_half_steps, nhc_state
+    rng = np.random.default_rng(chain_length * 100 + sy_steps)
+    dof, kT, tau, dt = 3 * 500.0, KT300, 50.0, 0.5
+    chain = nhc_state("cuda:0")
+    c = MD.Chain(chain_length, dof, 0.0, kT, tau)
+    total = 1.0
+    for it in range(40):
+        # kinetic energies away from equipartition so that the chain is driven
+        parts = rng.uniform(0.2, 1.8, size=7) * 0.5 * dof * kT / 7 * (0.5 if it % 3 else 1.6)
+        ke = torch.tensor(parts, dtype=torch.float64, device="cuda")
+        n_half = 1 + it % 2
+        fresh = it % 4 != 3
+        nhc_half_steps(chain, n_half, dt, kT, tau, dof, ke, chain_length=chain_length, chain_steps=chain_steps, sy_steps=sy_steps,
+                       fresh_scale=fresh)
+        c.ke = float(parts.sum())
+        s = 1.0
+        for _ in range(n_half):
+            s *= MD.chain_half_step(c, dt, kT, chain_steps, sy_steps)
+        total = s if fresh else total * s
+        got = chain.cpu().numpy()
+        assert abs(got[1] / total - 1.0) < 1e-12
+        assert abs(got[0] / c.ke - 1.0) < 1e-12
+        np.testing.assert_allclose(got[2:2 + chain_length], c.xi, rtol=1e-10, atol=1e-14)
+        np.testing.assert_allclose(got[10:10 + chain_length], c.p_xi, rtol=1e-10, atol=1e-12)
+    # without partials the chain continues from the kinetic energy it holds
+    nhc_half_steps(chain, 1, dt, kT, tau, dof, None, chain_length=chain_length, chain_steps=chain_steps, sy_steps=sy_steps)
+    s = MD.chain_half_step(c, dt, kT, chain_steps, sy_steps)
+    got = chain.cpu().numpy()
+    assert abs(got[1] / s - 1.0) < 1e-12 and abs(got[0] / c.ke - 1.0) < 1e-12
+
+
+def test_chain_settings_are_checked():
+    from so3lr_b200.engine import nhc_half_steps, nhc_state
+    chain = nhc_state("cuda:0")
+    for kw in (dict(chain_length=0), dict(chain_length=9), dict(sy_steps=2), dict(sy_steps=9), dict(chain_steps=0)):
+        with pytest.raises(RuntimeError):
+            nhc_half_steps(chain, 1, 0.5, KT300, 50.0, 300.0, None, **kw)
+    with pytest.raises(RuntimeError):
+        nhc_half_steps(chain, 1, 0.5, -1.0, 50.0, 300.0, None)
+
+
+def _molecule(g, name):
+    Z = g[f"{name}_Z"]
+    R = np.asarray(g[f"{name}_R"] - g[f"{name}_R"].mean(0), dtype=np.float32)
+    masses = {1: 1.008, 6: 12.011, 7: 14.007, 8: 15.999, 16: 32.06}
+    m = np.array([masses[int(z)] for z in Z], dtype=np.float32)
+    rng = np.random.default_rng(21)
+    V = (rng.normal(size=R.shape) * np.sqrt(KT300 * MD.ACC / m)[:, None]).astype(np.float32)
+    return Z, R, V, m
+
+
+def test_nvt_and_nve_trajectories_match_oracle(oracle_params, reference_goldens):
+    from so3lr_b200.engine import System, nhc_state
+    Z, R, V, m = _molecule(reference_goldens, "atat")
+    dt, tau, steps = 0.5, 10.0, 6       # a short tau so that the thermostat visibly acts within the few steps
+
+    def force(X):
+        ref = O.energy_forces(oracle_params, X, Z, None, cutoff_lr=12.0, damping=2.0)
+        return ref["energy"], ref["forces"]
+
+    s = System(Z, None, cutoff_lr=12.0, damping=2.0)
+    md = torch.tensor(m, device="cuda")
+    # NVT, in two calls so that the chain is carried between them
+    Rd, Vd = torch.tensor(R, device="cuda"), torch.tensor(V * 1.5, device="cuda")     # hotter than the target
+    Fd = s.compute(Rd)["forces"].clone()
+    chain = nhc_state("cuda:0")
+    s.nvt(2, dt, KT300, tau, md, Rd, Vd, Fd, chain)
+    E = s.nvt(steps - 2, dt, KT300, tau, md, Rd, Vd, Fd, chain)
+    Ro, Vo, mo = R.astype(np.float64), V.astype(np.float64) * 1.5, m.astype(np.float64)
+    Eo, Fo = force(Ro)
+    c = MD.nvt_init(Vo, mo, KT300, tau, 3)
+    scale_seen = 1.0
+    for _ in range(steps):
+        ke0 = c.ke
+        Ro, Vo, Fo, Eo = MD.nvt_step(force, c, Ro, Vo, Fo, mo, dt, KT300, 2, 3)
+        scale_seen = min(scale_seen, c.ke / max(ke0, 1e-30))
+    got = chain.cpu().numpy()
+    assert np.abs(Rd.cpu().numpy() - Ro).max() < 2e-5
+    assert np.abs(Vd.cpu().numpy() - Vo).max() < 2e-6
+    assert np.abs(Fd.cpu().numpy() - Fo).max() < 1e-4
+    assert abs(float(E.sum()) - Eo) < 1e-5 * abs(Eo)
+    assert got[1] == 1.0 and abs(got[0] / c.ke - 1.0) < 1e-5
+    np.testing.assert_allclose(got[2:5], c.xi, rtol=1e-4, atol=1e-9)
+    np.testing.assert_allclose(got[10:13], c.p_xi, rtol=1e-4, atol=1e-7)
+    assert abs(c.xi[0]) > 1e-4          # the thermostat did act
+    # NVE
+    Rd, Vd = torch.tensor(R, device="cuda"), torch.tensor(V, device="cuda")
+    Fd = s.compute(Rd)["forces"].clone()
+    s.nve(steps, dt, md, Rd, Vd, Fd)
+    Ro, Vo, Fo, Eo = MD.nve(force, R.astype(np.float64), V.astype(np.float64), mo, dt, steps)
+    assert np.abs(Rd.cpu().numpy() - Ro).max() < 2e-5
+    assert np.abs(Vd.cpu().numpy() - Vo).max() < 2e-6
+
+
+def test_nvt_water_box_conserves_extended_energy_and_cools_towards_target():
+    """Size-independent properties on a periodic box, through the (init_fn, apply_fn) pair the reference's MD loop is
+    written against: the thermostat's conserved quantity stays put while heat is drawn from a start twice as hot as the
+    target."""
+    from so3lr_b200 import md
+    from so3lr_b200 import workloads as W
+    from so3lr_b200.engine import System
+    Z, R, cell = W.water_box(512, 24.9, 7, jitter=0.02)
+    V, m = W.maxwell_boltzmann(Z, 600.0, 8)
+    s = System(Z, cell, cutoff_lr=12.0, damping=2.0, skin=0.5)
+    dt, tau, dof = 0.25, 25.0, 3.0 * len(Z)
+    init_fn, apply_fn = md.nvt_nose_hoover(s, dt, KT300, chain_length=3, chain_steps=2, sy_steps=3, tau=tau)
+    state = init_fn(R, m, velocity=V)
+    assert abs(md.temperature(state) - 600.0) < 30.0
+    H0, ke0 = md.nvt_nose_hoover_invariant(state, KT300, tau), md.kinetic_energy(state)
+    for _ in range(4):
+        state = apply_fn(state, 30)
+    H1, ke1 = md.nvt_nose_hoover_invariant(state, KT300, tau), md.kinetic_energy(state)
+    assert abs(H1 - H0) < 2e-3 * dof * KT300, (H0, H1)      # float32 positions and forces
+    assert ke1 < 0.9 * ke0                                  # heat was drawn out
+    assert abs(float(state.chain[0]) / ke1 - 1.0) < 1e-5 and float(state.chain[1]) == 1.0
+    # NVE from the same factory shape: total energy stays put
+    init_fn, apply_fn = md.nve(s, dt)
+    state = init_fn(R, m, velocity=V)
+    E0 = float(state.energy.sum()) + md.kinetic_energy(state)
+    state = apply_fn(state, 60)
+    assert abs(float(state.energy.sum()) + md.kinetic_energy(state) - E0) < 2e-3 * dof * KT300
+
+
+def test_decomposed_nvt_tracks_single_device():
+    from so3lr_b200 import domain as D
+    from so3lr_b200 import workloads as W
+    from so3lr_b200.engine import System, nhc_state
+    from test_gpu_domain import _run_threads
+    Z, R, cell = W.water_box(512, 24.9, 11, jitter=0.02)
+    R = np.asarray(R, dtype=np.float32)
+    V, m = W.maxwell_boltzmann(Z, 450.0, 12)
+    V = np.asarray(V, dtype=np.float32)
+    skin, dt, tau, steps = 0.5, 0.5, 20.0, 12
+    s = System(Z, cell, cutoff_lr=12.0, damping=2.0, skin=skin)
+    Rd, Vd = torch.tensor(R, device="cuda"), torch.tensor(V, device="cuda")
+    md = torch.tensor(np.asarray(m, dtype=np.float32), device="cuda")
+    Fd = s.compute(Rd)["forces"].clone()
+    chain = nhc_state("cuda:0")
+    s.nvt(steps, dt, KT300, tau, md, Rd, Vd, Fd, chain)
+    ref_chain = chain.cpu().numpy()
+
+    def fn(comm, rank):
+        be = D.CudaBackend(cutoff_lr=12.0, damping=2.0, skin=skin, device=0)
+        dom = D.DomainSystem(comm, be, Z, R, cell, skin=skin, cutoff_lr=12.0, velocities=V, masses=m, device="cuda:0")
+        dom.compute(check_rebuild=False)
+        ch = be.nhc_state()
+        dom.nvt(steps, dt, KT300, tau, ch)
+        return dom.gather_global(dom.R[: dom.n0]).cpu().numpy(), dom.gather_global(dom.V).cpu().numpy(), ch.cpu().numpy()
+
+    res = _run_threads(2, fn)
+    np.testing.assert_array_equal(res[0][2], res[1][2])          # both ranks hold the same chain, bit for bit
+    Rdd, Vdd, ch = res[0]
+    d = Rdd - Rd.cpu().numpy()
+    d -= np.round(d / 24.9) * 24.9
+    assert np.abs(d).max() < 1e-3 and np.median(np.abs(d)) < 2e-5, (np.abs(d).max(), np.median(np.abs(d)))
+    assert np.median(np.abs(Vdd - Vd.cpu().numpy())) < 2e-6
+    np.testing.assert_allclose(ch[2:5], ref_chain[2:5], rtol=1e-3, atol=1e-8)
+    np.testing.assert_allclose(ch[10:13], ref_chain[10:13], rtol=1e-3, atol=1e-5)
