@@ -36,6 +36,10 @@ WORKLOADS = {
     "water_98k": (32768, 99.2, 1003),           # profiling-sized case: working set above the L2, a few GB on the device
     "water_1m": (333333, 215.0, 1004),
 }
+# step body each workload is posed with: thermostatted (Nose-Hoover chain of length 3, 2 chain steps, 3 Suzuki-Yoshida
+# factors, tau = 100 dt, 300 K) or plain velocity Verlet
+ENSEMBLE = {"water_192": "nvt", "water_24k": "nvt", "water_98k": "nvt", "water_1m": "nve"}
+KT_300 = 300.0 * 8.617333262e-5
 
 
 def _peaks():
@@ -132,6 +136,7 @@ def run_b200(args, rank, world, local_rank):
     if world > 1:
         from so3lr_b200 import domain
         args.clock_sampler, args.algorithmic_bytes, args.peaks, args.ncu_traffic = ClockSampler, algorithmic_bytes, _peaks, ncu_traffic
+        args.default_ensemble = ENSEMBLE[args.workload]
         return domain.bench_entry(args, rank, world, local_rank, n_mol, box, seed)
 
     Z, R, cell = W.water_box(n_mol, box, seed)
@@ -146,9 +151,16 @@ def run_b200(args, rank, world, local_rank):
     Fd = out["forces"].clone()
     torch.cuda.synchronize()
     dt = 0.5
+    ensemble = args.ensemble or ENSEMBLE[args.workload]
+    if ensemble == "nvt":
+        from so3lr_b200.engine import nhc_state
+        chain = nhc_state(dev)
+        step = lambda: sysm.nvt(1, dt, KT_300, 100.0 * dt, md, Rd, Vd, Fd, chain, chain_length=3, chain_steps=2, sy_steps=3)
+    else:
+        step = lambda: sysm.nve(1, dt, md, Rd, Vd, Fd)
 
     for _ in range(args.warmup):
-        sysm.nve(1, dt, md, Rd, Vd, Fd)
+        step()
     torch.cuda.synchronize()
     st0 = sysm.stats()
     sampler = ClockSampler(local_rank)
@@ -157,7 +169,7 @@ def run_b200(args, rank, world, local_rank):
     torch.cuda.synchronize()
     ev[0].record()
     for _ in range(args.steps):
-        sysm.nve(1, dt, md, Rd, Vd, Fd)
+        step()
     ev[1].record()
     torch.cuda.synchronize()
     clocks = sampler.stop()
@@ -169,7 +181,7 @@ def run_b200(args, rank, world, local_rank):
     # per-kernel device times over another K steps of the same trajectory (CUDA events on the launching stream)
     sysm.profile(True)
     for _ in range(args.steps):
-        sysm.nve(1, dt, md, Rd, Vd, Fd)
+        step()
     prof = sysm.profile_read()
     sysm.profile(False)
     st2 = sysm.stats()
@@ -210,7 +222,8 @@ def run_b200(args, rank, world, local_rank):
     line = {"metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: {N} atoms periodic water, cutoffs 4.5/12 A, skin {skin} A, NVE dt 0.5 fs from 300 K",
+            "config": {"workload": f"{args.workload}: {N} atoms periodic water, cutoffs 4.5/12 A, skin {skin} A, "
+                                   + ("NVT (Nose-Hoover chain 3) at 300 K, dt 0.5 fs" if ensemble == "nvt" else "NVE dt 0.5 fs from 300 K"),
                        "atoms": N, "sr_list_edges": E_list, "lr_list_pairs": P_list,
                        "list_rebuilds_in_timed_steps": st1["rebuilds"] - st0["rebuilds"],
                        "l2_policy": "inputs larger than L2 (activations > 1 GB per step)" if N > 200000 else "inputs smaller than L2; no flush",
@@ -273,6 +286,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="water_1m", choices=sorted(WORKLOADS))
     ap.add_argument("--skin", type=float, default=1.0)
+    ap.add_argument("--ensemble", default=None, choices=["nve", "nvt"], help="step body (default: the one the workload is posed with)")
     ap.add_argument("--cpu-molecules", type=int, default=1024, help="molecules in the CPU-baseline sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the roofline kernel (from profiles/)")

@@ -169,9 +169,9 @@ int make_cell(const float* cell9, Cell* c) {
 
 // Optional per-kernel-group timing with CUDA events on the launching stream.
 enum ProfGroup { kPNlist = 0, kPGeom, kPProj, kPAttnFwd, kPPostFwd, kPHeads, kPPairLr, kPPostBwd, kPAttnBwd, kPProjBwd, kPScatter,
-                 kPMisc, kPGroups };
+                 kPMisc, kPMd, kPGroups };
 static const char* kProfNames[kPGroups] = {"nlist", "sr_geometry_zbl", "proj_fwd", "attn_fwd", "atom_post_fwd", "heads", "pair_lr",
-                                           "atom_post_bwd", "attn_bwd", "proj_bwd", "force_scatter", "misc"};
+                                           "atom_post_bwd", "attn_bwd", "proj_bwd", "force_scatter", "misc", "md_step"};
 struct Profiler {
   bool on = false;
   std::vector<cudaEvent_t> a, b;
@@ -856,10 +856,14 @@ SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* S, void* stream, int
   cudaStream_t st = (cudaStream_t)stream;
   const int n = S->n, blocks = (n + 255) / 256;
   for (int step = 0; step < n_steps; ++step) {
+    S->prof.begin(kPMd, st);
     { vv_first_kernel<<<blocks, 256, 0, st>>>(n, dt, masses, R, V, F); count_launch(); }
+    S->prof.end(st);
     int rc = so3lr_b200_system_compute(S, st, R, F, nullptr, step == n_steps - 1 ? energy : nullptr, nullptr, nullptr, nullptr);
     if (rc) return rc;
+    S->prof.begin(kPMd, st);
     { vv_second_kernel<<<blocks, 256, 0, st>>>(n, dt, masses, V, F); count_launch(); }
+    S->prof.end(st);
   }
   return kOk;
 }
@@ -901,19 +905,25 @@ SO3LR_B200_API int so3lr_b200_system_nvt(so3lr_b200_system* S, void* stream, int
   }
   if (n_steps == 0) return kOk;
   // the chain's first half step of step 0 works on the kinetic energy of the velocities as they are now
+  S->prof.begin(kPMd, st);
   md_kinetic_partials(st, n, masses, V, S->ke_partials);
   nhc_half_steps(st, chain, chain_length, chain_steps, sy_steps, dt, tau, kT, dof, 1, 1, S->ke_partials, blocks);
+  S->prof.end(st);
   for (int step = 0; step < n_steps; ++step) {
+    S->prof.begin(kPMd, st);
     md_first_half(st, n, dt, masses, R, V, F, chain);
+    S->prof.end(st);
     int rc = so3lr_b200_system_compute(S, st, R, F, nullptr, step == n_steps - 1 ? energy : nullptr, nullptr, nullptr, nullptr);
     if (rc) return rc;
+    S->prof.begin(kPMd, st);
     md_second_half(st, n, dt, masses, V, F, S->ke_partials);
     // the second half step of this MD step and the first of the next act on the velocities back to back: one launch, and
     // their product is applied by the next step's first kernel
     nhc_half_steps(st, chain, chain_length, chain_steps, sy_steps, dt, tau, kT, dof, step == n_steps - 1 ? 1 : 2, 1, S->ke_partials,
                    blocks);
+    if (step == n_steps - 1) md_apply_scale(st, n, V, chain);
+    S->prof.end(st);
   }
-  md_apply_scale(st, n, V, chain);
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }

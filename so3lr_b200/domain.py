@@ -584,11 +584,17 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
     dom = DomainSystem(comm, backend, Z, R, cell, skin=args.skin, cutoff_lr=12.0, velocities=V, masses=m, device=dev)
     dom.compute(check_rebuild=False)
     dt = 0.5
+    ensemble = getattr(args, "ensemble", None) or getattr(args, "default_ensemble", "nve")
+    if ensemble == "nvt":
+        chain = backend.nhc_state()
+        step = lambda: dom.nvt(1, dt, 300.0 * 8.617333262e-5, 100.0 * dt, chain, chain_length=3, chain_steps=2, sy_steps=3)
+    else:
+        step = lambda: dom.nve(1, dt)
     for k in range(args.warmup):
         if k == 1:
             dom.repartition()          # first-use costs of the re-partitioning path (NCCL setup for its message sizes) are warm-up
             dom.compute(check_rebuild=False)
-        dom.nve(1, dt)
+        step()
     torch.cuda.synchronize()
     dist.barrier()
     st0 = backend.stats()
@@ -598,7 +604,7 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     ev[0].record()
     for _ in range(args.steps):
-        dom.nve(1, dt)
+        step()
     ev[1].record()
     torch.cuda.synchronize()
     dist.barrier()
@@ -615,7 +621,7 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
     backend.sys.profile(True)
     dom.time_halo, dom._halo_events = True, []
     for _ in range(args.steps):
-        dom.nve(1, dt)
+        step()
     prof = backend.sys.profile_read()
     backend.sys.profile(False)
     dom.time_halo = False
@@ -658,7 +664,8 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
         line = {"metric": "atom-steps/s (E+F)", "value": round(value, 1), "unit": "atom-steps/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": f"{args.workload}: {N} atoms periodic water, cutoffs 4.5/12 A, skin {args.skin} A, NVE dt 0.5 fs from 300 K",
+                "config": {"workload": f"{args.workload}: {N} atoms periodic water, cutoffs 4.5/12 A, skin {args.skin} A, "
+                                       + ("NVT (Nose-Hoover chain 3) at 300 K, dt 0.5 fs" if ensemble == "nvt" else "NVE dt 0.5 fs from 300 K"),
                            "atoms": N, "decomposition": f"{world} slabs along axis {dom.geo.axis}, halo {dom.geo.lr_radius:.1f} A (features: {dom.geo.shell:.1f} A)",
                            "local_atoms_sum_over_ranks": int(nloc[0]), "list_rebuilds_in_timed_steps": rebuilds,
                            "repartition_ms_each": round(1e3 * getattr(dom, "t_repartition", 0.0) / max(1, dom.n_rebuilds - 1), 2),

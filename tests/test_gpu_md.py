@@ -125,19 +125,22 @@ def test_nvt_water_box_conserves_extended_energy_and_cools_towards_target():
     init_fn, apply_fn = md.nvt_nose_hoover(s, dt, KT300, chain_length=3, chain_steps=2, sy_steps=3, tau=tau)
     state = init_fn(R, m, velocity=V)
     assert abs(md.temperature(state) - 600.0) < 30.0
-    H0, ke0 = md.nvt_nose_hoover_invariant(state, KT300, tau), md.kinetic_energy(state)
+    H0 = md.nvt_nose_hoover_invariant(state, KT300, tau)
     for _ in range(4):
         state = apply_fn(state, 30)
-    H1, ke1 = md.nvt_nose_hoover_invariant(state, KT300, tau), md.kinetic_energy(state)
+    H1, ke_nvt = md.nvt_nose_hoover_invariant(state, KT300, tau), md.kinetic_energy(state)
     assert abs(H1 - H0) < 2e-3 * dof * KT300, (H0, H1)      # float32 positions and forces
-    assert ke1 < 0.9 * ke0                                  # heat was drawn out
-    assert abs(float(state.chain[0]) / ke1 - 1.0) < 1e-5 and float(state.chain[1]) == 1.0
-    # NVE from the same factory shape: total energy stays put
+    assert abs(float(state.chain[0]) / ke_nvt - 1.0) < 1e-5 and float(state.chain[1]) == 1.0
+    assert float(state.chain[2]) > 0 and float(state.chain[10]) > 0     # the first thermostat has been taking heat up
+    # NVE from the same factory shape and the same start: total energy stays put, and without the thermostat the box
+    # (which starts far from equilibrium and heats up either way) ends hotter
     init_fn, apply_fn = md.nve(s, dt)
     state = init_fn(R, m, velocity=V)
     E0 = float(state.energy.sum()) + md.kinetic_energy(state)
-    state = apply_fn(state, 60)
-    assert abs(float(state.energy.sum()) + md.kinetic_energy(state) - E0) < 2e-3 * dof * KT300
+    state = apply_fn(state, 120)
+    ke_nve = md.kinetic_energy(state)
+    assert abs(float(state.energy.sum()) + ke_nve - E0) < 2e-3 * dof * KT300
+    assert ke_nvt < 0.97 * ke_nve, (ke_nvt, ke_nve)
 
 
 def test_decomposed_nvt_tracks_single_device():
