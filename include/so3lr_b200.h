@@ -126,6 +126,16 @@ SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* sys, void* st
 SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* sys, void* stream, int n_steps, float dt_fs, const float* masses_dev,
                           float* positions_dev, float* velocities_dev, float* forces_dev, double* energy_dev);
 
+/* Strain derivative of the energy, dE/d eps_ab = sum over pairs of dR_a dE/d(dR)_b (eV; symmetric), accumulated beside the
+ * forces by the same kernels when enabled (single-structure contexts only).  The stress of a periodic cell is this divided by
+ * the cell volume; the pressure the reference's barostat uses is (2 KE - trace) / (3 V).  so3lr_b200_system_virial copies the
+ * 3x3 matrix (row-major, 9 doubles) of the latest evaluation; for a domain-decomposed context it is the share of the
+ * rank's owned atoms, to be summed over the ranks.
+ * Replaces: the strain perturbation of so3lr/jaxmd_utils.py:48-51 differentiated by jax_md.quantity.stress / pressure,
+ *           and the ASE calculator's stress (so3lr/ase_utils.py:10,22; tests/test_ase.py:145-172). */
+SO3LR_B200_API int so3lr_b200_system_enable_virial(so3lr_b200_system* sys, int enable);
+SO3LR_B200_API int so3lr_b200_system_virial(so3lr_b200_system* sys, void* stream, double* virial9_dev);
+
 /* Nose-Hoover chain thermostat (Martyna-Tuckerman-Klein propagation, Suzuki-Yoshida factorisation), as
  * jax_md.simulate.nvt_nose_hoover applies it: half a thermostat step, velocity Verlet, half a thermostat step.
  * The chain lives in SO3LR_B200_NHC_STATE_DOUBLES doubles on the device:

@@ -412,6 +412,9 @@ def energy_forces(P, R, Z, cell=None, *, cutoff_lr: Optional[float] = 12.0, damp
     else:
         idx_i, idx_j, idx_i_lr, idx_j_lr = lists
     Rt = torch.tensor(R, dtype=_dt(), requires_grad=True)
+    # homogeneous strain r -> (1 + eps) r applied to every displacement (the `perturbation` of so3lr/jaxmd_utils.py:48-51);
+    # dE/d eps at eps = 0 is the virial, stress = virial / volume
+    eps = torch.zeros(3, 3, dtype=_dt(), requires_grad=True)
     ii, jj = torch.as_tensor(idx_i.astype(np.int64)), torch.as_tensor(idx_j.astype(np.int64))
     il, jl = torch.as_tensor(idx_i_lr.astype(np.int64)), torch.as_tensor(idx_j_lr.astype(np.int64))
 
@@ -421,14 +424,15 @@ def energy_forces(P, R, Z, cell=None, *, cutoff_lr: Optional[float] = 12.0, damp
             c = torch.tensor(np.asarray(cell, dtype=np.float64), dtype=_dt())
             s = dR.detach() @ torch.linalg.inv(c)
             dR = dR - torch.round(s) @ c
-        return dR
+        return dR + dR @ eps.T
 
     e_atom, aux = energy_from_graph(P, Z, disp(ii, jj), idx_i, idx_j, disp(il, jl), idx_i_lr, idx_j_lr,
                                     lr_format=lr_format, cutoff_lr=cutoff_lr, damping=damping,
                                     total_charge=total_charge, num_unpaired=num_unpaired,
                                     batch_segments=batch_segments, num_graphs=num_graphs, record=record)
     E = e_atom.sum()
-    F = -torch.autograd.grad(E, Rt)[0]
+    gR, gE = torch.autograd.grad(E, (Rt, eps))
+    F = -gR
     bs = aux["batch_segments"]
     q = aux["partial_charges"].detach()
     dip = torch.zeros(num_graphs, 3, dtype=_dt()).index_add(0, bs, q[:, None] * Rt.detach())
@@ -438,7 +442,7 @@ def energy_forces(P, R, Z, cell=None, *, cutoff_lr: Optional[float] = 12.0, damp
                dipole_vec=dip.numpy(), zbl_repulsion=aux["zbl_repulsion"].detach().numpy(),
                electrostatic_energy=aux["electrostatic_energy"].detach().numpy(),
                dispersion_energy=aux["dispersion_energy"].detach().numpy(),
-               num_edges=len(idx_i), num_pairs=len(idx_i_lr))
+               num_edges=len(idx_i), num_pairs=len(idx_i_lr), virial=gE.numpy())
     return out
 
 

@@ -391,16 +391,18 @@ except Exception:  # ase not installed: a duck-typed stand-in with the same entr
 
 class So3lrCalculatorB200(_AseCalculator):
     """so3lr/ase_utils.py:7-28.  `get_potential_energy(atoms)` / `get_forces(atoms)`; `atoms` needs
-    get_positions(), get_atomic_numbers(), get_cell(), get_pbc().  Stress and Hessian raise NotImplementedError,
-    as the reference does when they are not enabled (tests/test_ase.py:145-172)."""
-    implemented_properties = ["energy", "forces", "charges", "hirshfeld_ratios", "dipole"]
+    get_positions(), get_atomic_numbers(), get_cell(), get_pbc().  With calculate_stress=True `get_stress(atoms)` returns the
+    stress of a periodic cell in Voigt order (xx, yy, zz, yz, xz, xy), eV/A^3; without it get_stress raises NotImplementedError
+    as the reference does (tests/test_ase.py:145-172).  The Hessian is not provided."""
+    implemented_properties = ["energy", "forces", "charges", "hirshfeld_ratios", "dipole", "stress"]
 
     def __init__(self, lr_cutoff=12.0, dispersion_energy_cutoff_lr_damping=2.0, calculate_stress=False, calculate_hessian=False,
                  dtype=np.float32, skin=0.0, device=None, **kwargs):
         if _AseCalculator is not object:
             super().__init__(**kwargs)
-        if calculate_stress or calculate_hessian:
-            raise NotImplementedError("stress and Hessian are not provided by so3lr_b200")
+        if calculate_hessian:
+            raise NotImplementedError("the Hessian is not provided by so3lr_b200")
+        self.calculate_stress = bool(calculate_stress)
         if np.dtype(dtype) != np.float32:
             raise NotImplementedError("so3lr_b200 computes in float32")
         self.lr_cutoff, self.damping, self.skin = lr_cutoff, dispersion_energy_cutoff_lr_damping, skin
@@ -419,10 +421,15 @@ class So3lrCalculatorB200(_AseCalculator):
             else:
                 self._sys = System(Z, cell, cutoff_lr=self.lr_cutoff, damping=self.damping, skin=self.skin,
                                    device=self.device.index or 0)
+                if self.calculate_stress:
+                    self._sys.enable_virial(True)
             self._key = key
         out = self._sys.compute_host(np.asarray(atoms.get_positions(), dtype=np.float32))
         self.results = dict(energy=float(out["energy"].sum()), forces=out["forces"].astype(np.float64),
                             charges=out["partial_charges"], hirshfeld_ratios=out["hirshfeld_ratios"], dipole=out["dipole_vec"][0])
+        if self.calculate_stress and cell is not None:
+            w = self._sys.virial().cpu().numpy() / abs(np.linalg.det(cell))
+            self.results["stress"] = np.array([w[0, 0], w[1, 1], w[2, 2], w[1, 2], w[0, 2], w[0, 1]])
         return self.results
 
     def calculate(self, atoms=None, properties=("energy",), system_changes=_all_changes):
@@ -437,7 +444,12 @@ class So3lrCalculatorB200(_AseCalculator):
         return self._evaluate(atoms)["forces"]
 
     def get_stress(self, atoms=None, **kw):
-        raise NotImplementedError("stress is not provided by so3lr_b200")
+        if not self.calculate_stress:
+            raise NotImplementedError("create the calculator with calculate_stress=True")
+        res = self._evaluate(atoms)
+        if "stress" not in res:
+            raise NotImplementedError("stress needs a periodic cell")
+        return res["stress"]
 
 
 def make_ase_calculator(lr_cutoff=12.0, dispersion_energy_cutoff_lr_damping=2.0, calculate_stress=False, calculate_hessian=False,

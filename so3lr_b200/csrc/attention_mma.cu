@@ -364,7 +364,7 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_mma_kernel(LayerDev
                                                                         const float* __restrict__ qkv, const float* __restrict__ ev_in,
                                                                         const float* __restrict__ g_xa, const float* __restrict__ gev1,
                                                                         float* __restrict__ g_qkv, float* __restrict__ gev_in,
-                                                                        float* __restrict__ F) {
+                                                                        float* __restrict__ F, float* __restrict__ virial) {
   extern __shared__ float4 sm4[];
   float* sm = reinterpret_cast<float*>(sm4);
   SharedWeights W;
@@ -564,6 +564,7 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_mma_kernel(LayerDev
       __syncwarp();
       // ---- phase C: lane = record: angular part and the force on atom i ----
       const int ndone = nproc < total ? nproc : total;
+      VirialAcc va;
       for (int slot = lane; slot < ndone; slot += 32) {
         const float* rp = rec + slot * kBwRec;
         const int j2 = __float_as_int(rp[0]);
@@ -585,10 +586,16 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_mma_kernel(LayerDev
         float gux, guy, guz;
         sph_harm_24_vjp(uu.x, uu.y, uu.z, gY, gux, guy, guz);
         const float gd = gux * uu.x + guy * uu.y + guz * uu.z;
-        fx += g_r * uu.x + (gux - gd * uu.x) * uu.w;
-        fy += g_r * uu.y + (guy - gd * uu.y) * uu.w;
-        fz += g_r * uu.z + (guz - gd * uu.z) * uu.w;
+        const float fsx = g_r * uu.x + (gux - gd * uu.x) * uu.w;
+        const float fsy = g_r * uu.y + (guy - gd * uu.y) * uu.w;
+        const float fsz = g_r * uu.z + (guz - gd * uu.z) * uu.w;
+        fx += fsx; fy += fsy; fz += fsz;
+        if (virial) {
+          const float r = 1.f / uu.w;
+          va.add(0.5f * r, uu.x, uu.y, uu.z, fsx, fsy, fsz);
+        }
       }
+      if (virial) va.flush_warp(virial, (size_t)i, lane);
       for (int pp = 0; pp < ndone; ++pp) {
         const float* rp = rec + pp * kBwRec;
         const int j2 = __float_as_int(rp[0]);
@@ -635,11 +642,11 @@ void launch_attn_fwd_mma(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
 
 void launch_attn_bwd_mma(cudaStream_t s, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
                          const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv, float* gev_in,
-                         float* F) {
+                         float* F, float* virial) {
   if (n_recv <= 0) return;
   int blocks = (n_recv + BW_WARPS - 1) / BW_WARPS;
   if (blocks > 148) blocks = 148;
-  { attn_bwd_mma_kernel<<<blocks, BW_WARPS * 32, kSmemBw, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F); count_launch(); }
+  { attn_bwd_mma_kernel<<<blocks, BW_WARPS * 32, kSmemBw, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F, virial); count_launch(); }
 }
 
 }  // namespace so3lr

@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev
                                                                         const float* __restrict__ qkv, const float* __restrict__ ev_in,
                                                                         const float* __restrict__ g_xa, const float* __restrict__ gev1,
                                                                         float* __restrict__ g_qkv, float* __restrict__ gev_in,
-                                                                        float* __restrict__ F) {
+                                                                        float* __restrict__ F, float* __restrict__ virial) {
   extern __shared__ float4 sm4[];
   float* sm = reinterpret_cast<float*>(sm4);
   float* K2 = sm;                     // [2][32][128]
@@ -449,6 +449,7 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev
       __syncwarp();
       // ---- phase C: lane = record: angular part and the force on atom i ----
       const int ndone = nproc < total ? nproc : total;   // processed records that are real edges
+      VirialAcc va;
       for (int slot = lane; slot < ndone; slot += 32) {
         const float* rp = rec + slot * kBwRec;
         const int j2 = __float_as_int(rp[0]);
@@ -470,10 +471,16 @@ __global__ void __launch_bounds__(BW_WARPS * 32, 1) attn_bwd_sym_kernel(LayerDev
         float gux, guy, guz;
         sph_harm_24_vjp(uu.x, uu.y, uu.z, gY, gux, guy, guz);
         const float gd = gux * uu.x + guy * uu.y + guz * uu.z;
-        fx += g_r * uu.x + (gux - gd * uu.x) * uu.w;
-        fy += g_r * uu.y + (guy - gd * uu.y) * uu.w;
-        fz += g_r * uu.z + (guz - gd * uu.z) * uu.w;
+        const float fsx = g_r * uu.x + (gux - gd * uu.x) * uu.w;
+        const float fsy = g_r * uu.y + (guy - gd * uu.y) * uu.w;
+        const float fsz = g_r * uu.z + (guz - gd * uu.z) * uu.w;
+        fx += fsx; fy += fsy; fz += fsz;
+        if (virial) {
+          const float r = 1.f / uu.w;
+          va.add(0.5f * r, uu.x, uu.y, uu.z, fsx, fsy, fsz);
+        }
       }
+      if (virial) va.flush_warp(virial, (size_t)i, lane);
       if (!FIRST) {
         // lane = component m: d/d ev_i through the invariants, - ds_l * 2 (ev_j - ev_i)_m / sqrt(2l+1)
         for (int pp = 0; pp < ndone; ++pp) {
@@ -531,14 +538,14 @@ void launch_attn_fwd_sym(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
 
 void launch_attn_bwd_sym(cudaStream_t s, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
                          const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv, float* gev_in,
-                         float* F, int first_layer) {
+                         float* F, int first_layer, float* virial) {
   if (n_recv <= 0) return;
   int blocks = (n_recv + BW_WARPS - 1) / BW_WARPS;
   if (blocks > 148) blocks = 148;
   if (first_layer)
-    { attn_bwd_sym_kernel<true><<<blocks, BW_WARPS * 32, kSmemBwFirst, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F); count_launch(); }
+    { attn_bwd_sym_kernel<true><<<blocks, BW_WARPS * 32, kSmemBwFirst, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F, virial); count_launch(); }
   else
-    { attn_bwd_sym_kernel<false><<<blocks, BW_WARPS * 32, kSmemBw, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F); count_launch(); }
+    { attn_bwd_sym_kernel<false><<<blocks, BW_WARPS * 32, kSmemBw, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F, virial); count_launch(); }
 }
 
 }  // namespace so3lr

@@ -63,6 +63,29 @@ SO3LR_D float warp_sum(float v) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
+// Strain derivative of the energy ("virial"), dE/d eps_ab = sum over directed edges of dR_a * dE/d(dR)_b.  The gather
+// kernels give every atom i the force f it receives through each of its edges (both directions of the pair), and then
+// dE/d eps = 1/2 sum_i sum_j dR_ij (x) f_ij.  The sum is symmetric, so six symmetrised components are kept per atom, in
+// the order xx yy zz yz xz xy.  `w` is the weight of dR (x) f for the calling kernel (1/2 in the gather kernels).
+struct VirialAcc {
+  float xx = 0.f, yy = 0.f, zz = 0.f, yz = 0.f, xz = 0.f, xy = 0.f;
+  SO3LR_D void add(float w, float dx, float dy, float dz, float fx, float fy, float fz) {
+    const float wx = w * dx, wy = w * dy, wz = w * dz;
+    xx = fmaf(wx, fx, xx); yy = fmaf(wy, fy, yy); zz = fmaf(wz, fz, zz);
+    yz = fmaf(0.5f * wy, fz, fmaf(0.5f * wz, fy, yz));
+    xz = fmaf(0.5f * wx, fz, fmaf(0.5f * wz, fx, xz));
+    xy = fmaf(0.5f * wx, fy, fmaf(0.5f * wy, fx, xy));
+  }
+  // all lanes of the warp that owns atom i call this; lane 0 adds the warp's total to the atom's row
+  SO3LR_D void flush_warp(float* __restrict__ W, size_t i, int lane) {
+    const float a = warp_sum(xx), b = warp_sum(yy), c = warp_sum(zz), d = warp_sum(yz), e = warp_sum(xz), f = warp_sum(xy);
+    if (lane == 0) {
+      float* w = W + 6 * i;
+      w[0] += a; w[1] += b; w[2] += c; w[3] += d; w[4] += e; w[5] += f;
+    }
+  }
+};
+
 // sum inside aligned groups of 8 lanes
 SO3LR_D float group8_sum(float v) {
   v += __shfl_xor_sync(0xffffffffu, v, 1);

@@ -121,6 +121,39 @@ __global__ void __launch_bounds__(1024) sum_to_double_kernel(int n, const float*
     *out = s;
   }
 }
+// per-atom virial rows (xx yy zz yz xz xy) -> per-block sums in double -> the symmetric 3x3 total
+__global__ void __launch_bounds__(256) virial_partial_kernel(int n, const float* __restrict__ W, double* __restrict__ partials) {
+  __shared__ double sh[6][8];
+  double a[6] = {0.0, 0.0, 0.0, 0.0, 0.0, 0.0};
+  for (int i = blockIdx.x * 256 + threadIdx.x; i < n; i += gridDim.x * 256)
+#pragma unroll
+    for (int k = 0; k < 6; ++k) a[k] += (double)W[6 * (size_t)i + k];
+#pragma unroll
+  for (int k = 0; k < 6; ++k) {
+    double v = a[k];
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) sh[k][threadIdx.x >> 5] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < 6) {
+    double v = 0.0;
+    for (int w = 0; w < 8; ++w) v += sh[threadIdx.x][w];
+    partials[6 * blockIdx.x + threadIdx.x] = v;
+  }
+}
+__global__ void virial_final_kernel(int n_blocks, const double* __restrict__ partials, double* __restrict__ out9) {
+  __shared__ double v[6];
+  if (threadIdx.x < 6) {
+    double s = 0.0;
+    for (int b = 0; b < n_blocks; ++b) s += partials[6 * b + threadIdx.x];
+    v[threadIdx.x] = s;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    out9[0] = v[0]; out9[4] = v[1]; out9[8] = v[2];
+    out9[5] = out9[7] = v[3]; out9[2] = out9[6] = v[4]; out9[1] = out9[3] = v[5];
+  }
+}
 // out = a - (*sum / count): removes the mean whose numerator was summed over all ranks
 __global__ void subtract_mean_kernel(int n, const float* __restrict__ a, const double* __restrict__ sum, double count,
                                      float* __restrict__ out) {
@@ -252,6 +285,12 @@ struct so3lr_b200_system {
   cudaStream_t own_stream = nullptr;
   int64_t n_rebuilds = 0, n_launches = 0;
   double* ke_partials = nullptr;   // one kinetic-energy share per block of the velocity kernels
+  // strain derivative of the energy (on request): per-atom rows of six symmetrised components, block partials, 3x3 total
+  bool want_virial = false;
+  float* virial = nullptr;
+  double* virial_partials = nullptr;
+  double* virial_sum = nullptr;
+  float* vir() const { return want_virial ? virial : nullptr; }
 };
 
 namespace {
@@ -421,10 +460,10 @@ void attn_fwd_dispatch(cudaStream_t st, const LayerDev& L, int n_recv, int n, co
 }
 void attn_bwd_dispatch(cudaStream_t st, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
                        const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv, float* gev_in, float* F,
-                       int first_layer) {
+                       int first_layer, float* virial) {
   if (!first_layer && L.has_spherical && use_mma_attention())
-    launch_attn_bwd_mma(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F);
-  else launch_attn_bwd_sym(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F, first_layer);
+    launch_attn_bwd_mma(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F, virial);
+  else launch_attn_bwd_sym(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F, first_layer, virial);
 }
 
 // ---- positions -> forces (gather-only kernels on the symmetric short-range list) ----
@@ -434,6 +473,14 @@ void attn_bwd_dispatch(cudaStream_t st, const LayerDev& L, int n_recv, int n, co
 // n0 = n1 = n2 = n3 = n.
 struct Shells { int n0, n1, n2, n3; };
 
+// sum of the per-atom virial rows of the atoms whose energy is evaluated here
+void reduce_virial(so3lr_b200_system* S, cudaStream_t st, int n0) {
+  int blocks = (n0 + 255) / 256;
+  if (blocks > 592) blocks = 592;
+  { virial_partial_kernel<<<blocks, 256, 0, st>>>(n0, S->virial, S->virial_partials); count_launch(); }
+  { virial_final_kernel<<<1, 32, 0, st>>>(blocks, S->virial_partials, S->virial_sum); count_launch(); }
+}
+
 // network forward up to the output heads: e_nn, q_raw, hv for the owned atoms; ZBL energy and force; F is zeroed first
 int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const Shells& c, bool owned_side_only, float* F) {
   const ModelDev& M = S->model->M;
@@ -442,9 +489,10 @@ int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const S
   const int nsend[kNumLayers] = {c.n3, c.n2, c.n1};   // atoms whose q/k/v rows layer l reads
   fill(st, S->e_zbl, c.n0, 0.f);
   fill(st, F, (size_t)c.n3 * 3, 0.f);
+  if (S->vir()) fill(st, S->virial, (size_t)c.n3 * 6, 0.f);
   S->prof.begin(kPGeom, st);
   launch_sr_geometry_zbl(st, M, S->cell, c.n3, S->sr.count, edge_i, nbr_j, S->d_Z, R, 0, S->dR, S->e_zbl, nullptr, nullptr, F,
-                         owned_side_only ? c.n0 : -1);
+                         owned_side_only ? c.n0 : -1, S->vir());
   S->prof.end(st);
   const bool tab0 = S->sp.n_species > 0 && use_layer0_tables();
   const bool fuse = use_mma_dense();   // q/k/v rows of layer l+1 come out of layer l's dense block
@@ -499,9 +547,10 @@ int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float
     }
     S->prof.begin(kPAttnBwd, st);
     if (l == 0 && S->sp.n_species > 0 && use_layer0_tables())
-      launch_layer0_bwd_tab(st, S->sp, nattn[0], c.n3, c.n3, row_ptr, nbr_j, S->dR, S->d_Z, S->g_xa, S->gev1, S->GV, F);
+      launch_layer0_bwd_tab(st, S->sp, nattn[0], c.n3, c.n3, row_ptr, nbr_j, S->dR, S->d_Z, S->g_xa, S->gev1, S->GV, F, S->vir());
     else
-      attn_bwd_dispatch(st, L, nattn[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, F, l == 0 ? 1 : 0);
+      attn_bwd_dispatch(st, L, nattn[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, F, l == 0 ? 1 : 0,
+                        S->vir());
     S->prof.end(st);
     if (l > 0) {
       if (!use_mma_dense()) {
@@ -512,6 +561,7 @@ int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float
       float* t = gev2; gev2 = gev_in; gev_in = t;
     }
   }
+  if (S->vir()) reduce_virial(S, st, c.n0);
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
@@ -526,7 +576,7 @@ int evaluate_fused(so3lr_b200_system* S, cudaStream_t st, const float* R, float*
   launch_charge_conserve(st, S->n_graphs, S->d_graph_start, S->q_raw, S->d_total_charge, S->hv, S->q, S->h);
   S->prof.begin(kPPairLr, st);
   launch_pair_lr(st, S->lr, S->cell, n, S->lrl.row_ptr, S->lrl.nbr_j, S->d_Z, R, S->q, S->h, 0, nullptr, nullptr, nullptr, F, S->gq, S->gh,
-                 S->e_coul, S->e_disp, nullptr);
+                 S->e_coul, S->e_disp, nullptr, S->vir());
   S->prof.end(st);
   { combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
   launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw);
@@ -868,6 +918,27 @@ SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* S, void* stream, int
   return kOk;
 }
 
+SO3LR_B200_API int so3lr_b200_system_enable_virial(so3lr_b200_system* S, int enable) {
+  if (!S) return kInvalidArgument;
+  if (S->n_graphs != 1) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  if (enable && !S->virial) {
+    S->virial = S->pool.get<float>((size_t)S->n_cap * 6);
+    S->virial_partials = S->pool.get<double>(6 * 592);
+    S->virial_sum = S->pool.get<double>(9);
+    if (S->pool.status != kOk) return S->pool.status;
+  }
+  S->want_virial = enable != 0;
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_virial(so3lr_b200_system* S, void* stream, double* virial9_dev) {
+  if (!S || !virial9_dev || !S->want_virial || !S->virial_sum) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  SO3LR_CUDA_CHECK(cudaMemcpyAsync(virial9_dev, S->virial_sum, 9 * sizeof(double), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+  return kOk;
+}
+
 SO3LR_B200_API int so3lr_b200_nhc_init(void* stream, double* chain) {
   if (!chain) return kInvalidArgument;
   tl_launch_counter = nullptr;
@@ -980,9 +1051,10 @@ SO3LR_B200_API int so3lr_b200_dd_begin(so3lr_b200_system* S, void* stream, const
   const ModelDev& M = S->model->M;
   fill(st, S->e_zbl, n0, 0.f);
   fill(st, S->F_s, (size_t)n0 * 3, 0.f);
+  if (S->vir()) fill(st, S->virial, (size_t)n0 * 6, 0.f);
   S->prof.begin(kPGeom, st);
   launch_sr_geometry_zbl(st, M, S->cell, S->n, S->sr.count, S->sr.edge_i, S->sr.nbr_j, S->d_Z, R_local_dev, 0, S->dR, S->e_zbl, nullptr, nullptr,
-                         S->F_s, n0);
+                         S->F_s, n0, S->vir());
   S->prof.end(st);
   if (!(S->sp.n_species > 0 && use_layer0_tables())) launch_embed(st, M, S->d_Z, n1, S->x[0]);
   SO3LR_CUDA_CHECK(cudaGetLastError());
@@ -1044,7 +1116,7 @@ SO3LR_B200_API int so3lr_b200_dd_pair(so3lr_b200_system* S, void* stream, const 
   const int n0 = S->shells[0];
   S->prof.begin(kPPairLr, st);
   launch_pair_lr_owned(st, S->lr, S->cell, n0, S->n, S->lrl.row_ptr, S->lrl.nbr_j, S->d_Z, R_local_dev, q_local_dev, h_local_dev, S->F_s,
-                       S->gq, S->gh, S->e_coul, S->e_disp);
+                       S->gq, S->gh, S->e_coul, S->e_disp, S->vir());
   S->prof.end(st);
   { sum_to_double_kernel<<<1, 1024, 0, st>>>(n0, S->gq, gq_sum_dev); count_launch(); }
   SO3LR_CUDA_CHECK(cudaGetLastError());
@@ -1096,11 +1168,12 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_attn(so3lr_b200_system* S, void*
   const LayerDev& L = S->model->M.layer[l];
   S->prof.begin(kPAttnBwd, st);
   if (l == 0 && S->sp.n_species > 0 && use_layer0_tables())
-    launch_layer0_bwd_tab(st, S->sp, n0, S->shells[1], S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->d_Z, S->g_xa, S->gev1, S->GV, S->F_s);
+    launch_layer0_bwd_tab(st, S->sp, n0, S->shells[1], S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->d_Z, S->g_xa, S->gev1, S->GV, S->F_s, S->vir());
   else
     attn_bwd_dispatch(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, S->dd_gev_in, S->F_s,
-                      l == 0 ? 1 : 0);
+                      l == 0 ? 1 : 0, S->vir());
   S->prof.end(st);
+  if (l == 0 && S->vir()) reduce_virial(S, st, n0);
   if (l > 0) {
     if (!use_mma_dense()) {
       SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)n0 * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));

@@ -56,7 +56,7 @@ void launch_attn_fwd_sym(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
                          const float* qkv, const float* x_in, const float* ev_in, float* xa, float* ev1);
 void launch_attn_bwd_sym(cudaStream_t s, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
                          const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv, float* gev_in,
-                         float* F, int first_layer);
+                         float* F, int first_layer, float* virial = nullptr);
 
 // ---- attention_mma.cu ----
 // Same contracts as the *_sym launchers, for layers with a spherical filter (L.has_spherical): the per-edge filter
@@ -66,7 +66,7 @@ void launch_attn_fwd_mma(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
                          const float* qkv, const float* x_in, const float* ev_in, float* xa, float* ev1);
 void launch_attn_bwd_mma(cudaStream_t s, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
                          const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv, float* gev_in,
-                         float* F);
+                         float* F, float* virial = nullptr);
 
 // ---- layer0_tab.cu: first layer through per-element-pair tables (its inputs depend on the elements only) ----
 constexpr int kMaxTabSpecies = 8;
@@ -86,7 +86,8 @@ void launch_layer0_fwd_tab(cudaStream_t s, const SpeciesTables& T, const ModelDe
                            const int* nbr_j, const float* dR, const int* Z, float* xa, float* ev1);
 // g_xa must be valid for atoms [0, n_gv) (every possible neighbour of a receiver); GV is a scratch of n_gv x 32 floats
 void launch_layer0_bwd_tab(cudaStream_t s, const SpeciesTables& T, int n_recv, int n_gv, int n, const int* row_ptr, const int* nbr_j,
-                           const float* dR, const int* Z, const float* g_xa, const float* gev1, float* GV, float* F);
+                           const float* dR, const int* Z, const float* g_xa, const float* gev1, float* GV, float* F,
+                           float* virial = nullptr);
 
 // ---- pair_kernels.cu ----
 // dR for every short-range edge from positions (+ minimum image), ZBL energy into e_atom[centre], ZBL gradient
@@ -94,7 +95,7 @@ void launch_layer0_bwd_tab(cudaStream_t s, const SpeciesTables& T, int n_recv, i
 // F_j -= g).  With `dR_given` the displacements are inputs.
 void launch_sr_geometry_zbl(cudaStream_t s, const ModelDev& M, const Cell& cell, int n, long long n_edges, const int* edge_i,
                             const int* nbr_j, const int* Z, const float* R, int dR_given, float* dR, float* e_atom, float* g_dR,
-                            const float* ge, float* F_direct, int n_owned = -1);
+                            const float* ge, float* F_direct, int n_owned = -1, float* virial = nullptr);
 // F[i] += g, F[j] -= g for every edge
 void launch_force_scatter(cudaStream_t s, int n, long long n_edges, const int* edge_i, const int* nbr_j, const float* g_dR,
                           float* F);
@@ -103,13 +104,13 @@ void launch_force_scatter(cudaStream_t s, int n, long long n_edges, const int* e
 void launch_pair_lr(cudaStream_t s, const LrParams& P, const Cell& cell, int n, const int* row_ptr, const int* nbr_j,
                     const int* Z, const float* R, const float* q, const float* h, int mode, const float* dR_lr,
                     float* g_dR_lr, float* e_atom, float* F, float* gq, float* gh, float* e_coul, float* e_disp,
-                    const float* ge);
+                    const float* ge, float* virial = nullptr);
 // Domain-decomposed variant: rows 0 .. n_owned-1 of a full (both directions) list; every pair energy is booked half on
 // the row atom, and only the derivatives that land on the row atom are produced, at full weight: F[i], gq[i], gh[i],
 // e_coul[i], e_disp[i] are written (not accumulated) by the row's warp -- no atomics.
 void launch_pair_lr_owned(cudaStream_t s, const LrParams& P, const Cell& cell, int n_owned, int n, const int* row_ptr,
                           const int* nbr_j, const int* Z, const float* R, const float* q, const float* h, float* F_add,
-                          float* gq, float* gh, float* e_coul, float* e_disp);
+                          float* gq, float* gh, float* e_coul, float* e_disp, float* virial = nullptr);
 // q = q_raw + (Q_g - sum_g q_raw) / n_g ; h = |hv| ; and the transposed operation for the cotangents
 // (atoms of one graph are contiguous: graph g owns atoms graph_start[g] .. graph_start[g+1]-1)
 void launch_charge_conserve(cudaStream_t s, int n_graphs, const int* graph_start, const float* q_raw,

@@ -175,7 +175,8 @@ __global__ void __launch_bounds__(256) layer0_gv_kernel(SpeciesTables T, int n, 
 __global__ void __launch_bounds__(256) layer0_bwd_tab_kernel(SpeciesTables T, int n_recv, int n, const int* __restrict__ row_ptr,
                                                              const int* __restrict__ nbr_j, const float* __restrict__ dR,
                                                              const int* __restrict__ Z, const float* __restrict__ GV,
-                                                             const float* __restrict__ gev1, float* __restrict__ F) {
+                                                             const float* __restrict__ gev1, float* __restrict__ F,
+                                                             float* __restrict__ virial) {
   const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (i >= n_recv) return;
@@ -189,6 +190,7 @@ __global__ void __launch_bounds__(256) layer0_bwd_tab_kernel(SpeciesTables T, in
     gevi[4 * c] = v.x; gevi[4 * c + 1] = v.y; gevi[4 * c + 2] = v.z; gevi[4 * c + 3] = v.w;
   }
   float fx = 0.f, fy = 0.f, fz = 0.f;
+  VirialAcc va;
   const int e0 = row_ptr[i], e1 = row_ptr[i + 1];
   for (int e = e0 + lane; e < e1; e += 32) {
     const int j = nbr_j[e];
@@ -257,12 +259,15 @@ __global__ void __launch_bounds__(256) layer0_bwd_tab_kernel(SpeciesTables T, in
     float gux, guy, guz;
     sph_harm_24_vjp(ux, uy, uz, gY, gux, guy, guz);
     const float gd = gux * ux + guy * uy + guz * uz;
-    fx += gr * ux + (gux - gd * ux) * ir;
-    fy += gr * uy + (guy - gd * uy) * ir;
-    fz += gr * uz + (guz - gd * uz) * ir;
+    const float fsx = gr * ux + (gux - gd * ux) * ir;
+    const float fsy = gr * uy + (guy - gd * uy) * ir;
+    const float fsz = gr * uz + (guz - gd * uz) * ir;
+    fx += fsx; fy += fsy; fz += fsz;
+    if (virial) va.add(0.5f, dx, dy, dz, fsx, fsy, fsz);
   }
   fx = warp_sum(fx); fy = warp_sum(fy); fz = warp_sum(fz);
   if (lane == 0) { F[3 * (size_t)i] += fx; F[3 * (size_t)i + 1] += fy; F[3 * (size_t)i + 2] += fz; }
+  if (virial) va.flush_warp(virial, (size_t)i, lane);
 }
 
 }  // namespace
@@ -319,10 +324,10 @@ void launch_layer0_fwd_tab(cudaStream_t s, const SpeciesTables& T, const ModelDe
 }
 
 void launch_layer0_bwd_tab(cudaStream_t s, const SpeciesTables& T, int n_recv, int n_gv, int n, const int* row_ptr, const int* nbr_j,
-                           const float* dR, const int* Z, const float* g_xa, const float* gev1, float* GV, float* F) {
+                           const float* dR, const int* Z, const float* g_xa, const float* gev1, float* GV, float* F, float* virial) {
   if (n_recv <= 0) return;
   { layer0_gv_kernel<<<(n_gv + 7) / 8, 256, 0, s>>>(T, n_gv, g_xa, GV); count_launch(); }
-  { layer0_bwd_tab_kernel<<<(n_recv + 7) / 8, 256, 0, s>>>(T, n_recv, n, row_ptr, nbr_j, dR, Z, GV, gev1, F); count_launch(); }
+  { layer0_bwd_tab_kernel<<<(n_recv + 7) / 8, 256, 0, s>>>(T, n_recv, n, row_ptr, nbr_j, dR, Z, GV, gev1, F, virial); count_launch(); }
 }
 
 }  // namespace so3lr

@@ -9,7 +9,8 @@ namespace {
 __global__ void sr_geometry_zbl_kernel(ZblParams zbl, Cell cell, int n, long long n_edges, const int* __restrict__ edge_i,
                                        const int* __restrict__ nbr_j, const int* __restrict__ Z, const float* __restrict__ R,
                                        int dR_given, float* __restrict__ dR, float* __restrict__ e_atom,
-                                       float* __restrict__ g_dR, const float* __restrict__ ge, float* __restrict__ F_direct, int n_owned) {
+                                       float* __restrict__ g_dR, const float* __restrict__ ge, float* __restrict__ F_direct, int n_owned,
+                                       float* __restrict__ virial) {
   long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (e >= n_edges) return;
   const int i = edge_i[e], j = nbr_j[e];
@@ -38,6 +39,11 @@ __global__ void sr_geometry_zbl_kernel(ZblParams zbl, Cell cell, int n, long lon
     atomicAdd(e_atom + i, ez);
     const float s = (ge ? ge[i] : 1.f) * dez / r;
     gx = s * dx; gy = s * dy; gz = s * dz;
+    if (virial) {     // every directed edge carries its own energy: dE/d eps += dR (x) g
+      float* w = virial + 6 * (size_t)i;
+      atomicAdd(w, dx * gx); atomicAdd(w + 1, dy * gy); atomicAdd(w + 2, dz * gz);
+      atomicAdd(w + 3, dy * gz); atomicAdd(w + 4, dx * gz); atomicAdd(w + 5, dx * gy);
+    }
     if (F_direct) {   // only edges shorter than 1.5 A get here: a handful per atom
       const float wi = n_owned >= 0 ? 2.f : 1.f;
       atomicAdd(F_direct + 3 * (size_t)i, wi * gx); atomicAdd(F_direct + 3 * (size_t)i + 1, wi * gy); atomicAdd(F_direct + 3 * (size_t)i + 2, wi * gz);
@@ -70,10 +76,12 @@ __global__ void __launch_bounds__(256) pair_lr_kernel(LrParams P, Cell cell, int
                                                       const float* __restrict__ h, const float* __restrict__ dR_lr,
                                                       float* __restrict__ g_dR_lr, float* __restrict__ e_atom,
                                                       float* __restrict__ F, float* __restrict__ gq, float* __restrict__ gh,
-                                                      float* __restrict__ e_coul, float* __restrict__ e_disp, const float* __restrict__ ge) {
+                                                      float* __restrict__ e_coul, float* __restrict__ e_disp, const float* __restrict__ ge,
+                                                      float* __restrict__ virial) {
   const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (i >= n) return;
+  VirialAcc va;
   const int e0 = row_ptr[i], e1 = row_ptr[i + 1];
   if (e0 == e1) return;
   const float qi = q[i], hi = h[i];
@@ -114,6 +122,7 @@ __global__ void __launch_bounds__(256) pair_lr_kernel(LrParams P, Cell cell, int
         const float s = de_dr / r;
         gx = s * dx; gy = s * dy; gz = s * dz;   // dE/d(dR), dR = R_j - R_i
         if (MODE == 0) {
+          if (virial) va.add(1.f, dx, dy, dz, gx, gy, gz);     // every listed pair carries its own share of the energy
           fx += gx; fy += gy; fz += gz;
           atomicAdd(F + 3 * (size_t)j, -gx); atomicAdd(F + 3 * (size_t)j + 1, -gy); atomicAdd(F + 3 * (size_t)j + 2, -gz);
         }
@@ -131,6 +140,7 @@ __global__ void __launch_bounds__(256) pair_lr_kernel(LrParams P, Cell cell, int
     atomicAdd(gh + i, gei * ghi);
     if (MODE == 0) { atomicAdd(F + 3 * (size_t)i, fx); atomicAdd(F + 3 * (size_t)i + 1, fy); atomicAdd(F + 3 * (size_t)i + 2, fz); }
   }
+  if (MODE == 0 && virial) va.flush_warp(virial, (size_t)i, lane);
 }
 
 // owned rows of a full list: i-side derivatives only, no atomics
@@ -139,7 +149,7 @@ __global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cel
                                                             const float* __restrict__ R, const float* __restrict__ q,
                                                             const float* __restrict__ h, float* __restrict__ F_add,
                                                             float* __restrict__ gq, float* __restrict__ gh, float* __restrict__ e_coul,
-                                                            float* __restrict__ e_disp) {
+                                                            float* __restrict__ e_disp, float* __restrict__ virial) {
   const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (i >= n_owned) return;
@@ -148,6 +158,7 @@ __global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cel
   const int Zi = Z[i];
   const float xi = R[3 * (size_t)i], yi = R[3 * (size_t)i + 1], zi = R[3 * (size_t)i + 2];
   float ec = 0.f, ed = 0.f, fx = 0.f, fy = 0.f, fz = 0.f, gqi = 0.f, ghi = 0.f;
+  VirialAcc va;
   for (int e = e0 + lane; e < e1; e += 32) {
     const int j = nbr_j[e];
     if (j < 0 || j >= n) continue;
@@ -167,6 +178,7 @@ __global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cel
     ghi += dd_dhi;
     const float s = (kKe * qi * qj * dchi + dd_dr) / r;   // dE_ij/d(dR), dR = R_j - R_i; F_i = +that
     fx = fmaf(s, dx, fx); fy = fmaf(s, dy, fy); fz = fmaf(s, dz, fz);
+    if (virial) va.add(0.5f * s, dx, dy, dz, dx, dy, dz);
   }
   ec = warp_sum(ec); ed = warp_sum(ed); gqi = warp_sum(gqi); ghi = warp_sum(ghi);
   fx = warp_sum(fx); fy = warp_sum(fy); fz = warp_sum(fz);
@@ -174,6 +186,7 @@ __global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cel
     e_coul[i] = ec; e_disp[i] = ed; gq[i] = gqi; gh[i] = ghi;
     F_add[3 * (size_t)i] += fx; F_add[3 * (size_t)i + 1] += fy; F_add[3 * (size_t)i + 2] += fz;
   }
+  if (virial) va.flush_warp(virial, (size_t)i, lane);
 }
 
 // one CTA per graph: q = q_raw + (Q - sum q_raw) / n_g ; h = |hv|
@@ -256,10 +269,10 @@ __global__ void graph_reduce_kernel(int n_graphs, const int* __restrict__ graph_
 
 void launch_sr_geometry_zbl(cudaStream_t s, const ModelDev& M, const Cell& cell, int n, long long n_edges, const int* edge_i,
                             const int* nbr_j, const int* Z, const float* R, int dR_given, float* dR, float* e_atom, float* g_dR, const float* ge,
-                            float* F_direct, int n_owned) {
+                            float* F_direct, int n_owned, float* virial) {
   if (n_edges <= 0) return;
   unsigned blocks = (unsigned)((n_edges + 255) / 256);
-  { sr_geometry_zbl_kernel<<<blocks, 256, 0, s>>>(M.zbl, cell, n, n_edges, edge_i, nbr_j, Z, R, dR_given, dR, e_atom, g_dR, ge, F_direct, n_owned); count_launch(); }
+  { sr_geometry_zbl_kernel<<<blocks, 256, 0, s>>>(M.zbl, cell, n, n_edges, edge_i, nbr_j, Z, R, dR_given, dR, e_atom, g_dR, ge, F_direct, n_owned, virial); count_launch(); }
 }
 
 void launch_force_scatter(cudaStream_t s, int n, long long n_edges, const int* edge_i, const int* nbr_j, const float* g_dR, float* F) {
@@ -270,20 +283,21 @@ void launch_force_scatter(cudaStream_t s, int n, long long n_edges, const int* e
 
 void launch_pair_lr(cudaStream_t s, const LrParams& P, const Cell& cell, int n, const int* row_ptr, const int* nbr_j,
                     const int* Z, const float* R, const float* q, const float* h, int mode, const float* dR_lr,
-                    float* g_dR_lr, float* e_atom, float* F, float* gq, float* gh, float* e_coul, float* e_disp, const float* ge) {
+                    float* g_dR_lr, float* e_atom, float* F, float* gq, float* gh, float* e_coul, float* e_disp, const float* ge,
+                    float* virial) {
   if (n <= 0) return;
   int blocks = (n + 7) / 8;
   if (mode == 0)
-    { pair_lr_kernel<0><<<blocks, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, Z, R, q, h, dR_lr, g_dR_lr, e_atom, F, gq, gh, e_coul, e_disp, ge); count_launch(); }
+    { pair_lr_kernel<0><<<blocks, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, Z, R, q, h, dR_lr, g_dR_lr, e_atom, F, gq, gh, e_coul, e_disp, ge, virial); count_launch(); }
   else
-    { pair_lr_kernel<1><<<blocks, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, Z, R, q, h, dR_lr, g_dR_lr, e_atom, F, gq, gh, e_coul, e_disp, ge); count_launch(); }
+    { pair_lr_kernel<1><<<blocks, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, Z, R, q, h, dR_lr, g_dR_lr, e_atom, F, gq, gh, e_coul, e_disp, ge, virial); count_launch(); }
 }
 
 void launch_pair_lr_owned(cudaStream_t s, const LrParams& P, const Cell& cell, int n_owned, int n, const int* row_ptr,
                           const int* nbr_j, const int* Z, const float* R, const float* q, const float* h, float* F_add,
-                          float* gq, float* gh, float* e_coul, float* e_disp) {
+                          float* gq, float* gh, float* e_coul, float* e_disp, float* virial) {
   if (n_owned <= 0) return;
-  { pair_lr_owned_kernel<<<(n_owned + 7) / 8, 256, 0, s>>>(P, cell, n_owned, n, row_ptr, nbr_j, Z, R, q, h, F_add, gq, gh, e_coul, e_disp); count_launch(); }
+  { pair_lr_owned_kernel<<<(n_owned + 7) / 8, 256, 0, s>>>(P, cell, n_owned, n, row_ptr, nbr_j, Z, R, q, h, F_add, gq, gh, e_coul, e_disp, virial); count_launch(); }
 }
 
 void launch_charge_conserve(cudaStream_t s, int n_graphs, const int* graph_start, const float* q_raw,

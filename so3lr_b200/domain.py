@@ -230,6 +230,7 @@ class CudaBackend:
         self.model = Model.default(device)
         self.sys = None
         self.capacity = 0
+        self.want_virial = False
 
     def _stream(self):
         return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
@@ -253,6 +254,8 @@ class CudaBackend:
             self.capacity = int(1.2 * n) + 1024
             self.sys = System(np.ones(self.capacity, np.int32), np.asarray(cell_local), cutoff_lr=self.cutoff_lr, damping=self.damping,
                               skin=self.skin, lr_format="sparse", model=self.model)
+            if self.want_virial:
+                self.sys.enable_virial(True)
         self.n, self.counts = n, [int(v) for v in counts]
         sh = np.asarray([self.counts[0], self.counts[1], self.counts[1], n], dtype=np.int32)
         c9 = np.ascontiguousarray(np.asarray(cell_local, dtype=np.float32).reshape(9))
@@ -262,6 +265,15 @@ class CudaBackend:
         self._x = [self._buffer(0, l) for l in range(4)]
         self._ev = [self._buffer(1, l) for l in range(4)]
         self._g = [self._buffer(2, 0), self._buffer(3, 0)]
+
+    def enable_virial(self, on=True):
+        self.want_virial = bool(on)
+        if self.sys is not None:
+            self.sys.enable_virial(on)
+
+    def virial(self):
+        """Share of the owned atoms in dE/d eps, (3,3) float64."""
+        return self.sys.virial()
 
     def nhc_state(self):
         from .engine import nhc_state
@@ -524,6 +536,10 @@ class DomainSystem:
             s = (0.5 * dt_fs * ACC_UNIT / self.m)[:, None]      # ownership may have changed
             self.V += s * self.F
         return self.E
+
+    def virial(self):
+        """dE/d eps (3,3) float64 of the latest evaluation, summed over the ranks (backend.enable_virial() first)."""
+        return self.comm.all_reduce_sum(self.backend.virial().reshape(9).clone()).reshape(3, 3)
 
     def kinetic_energy(self):
         """Kinetic energy of all atoms (eV) as a one-element float64 tensor, identical on every rank."""

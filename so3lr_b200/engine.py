@@ -77,6 +77,8 @@ class System:
         check(lib.so3lr_b200_system_create(self.model._h, self.n, _ptr(Z), self.n_graphs, _ptr(gs), _ptr(tq), _ptr(ts),
                                            _ptr(c9), C.byref(opt), C.byref(h)), "system_create")
         self._h = h
+        self._cell = None if cell is None else np.asarray(cell, dtype=np.float64).reshape(3, 3)
+        self._virial = False
 
     def __del__(self):
         h = getattr(self, "_h", None)
@@ -87,6 +89,20 @@ class System:
     def set_cell(self, cell):
         c9 = np.ascontiguousarray(np.asarray(cell, dtype=np.float32).reshape(9))
         check(lib.so3lr_b200_system_set_cell(self._h, _ptr(c9)), "set_cell")
+        self._cell = np.asarray(cell, dtype=np.float64).reshape(3, 3)
+
+    def enable_virial(self, on=True):
+        """Also accumulate the strain derivative of the energy (single-structure contexts); compute() then returns
+        'virial' (3,3) float64 = dE/d eps in eV and, for a periodic cell, 'stress' = virial / volume in eV/A^3."""
+        check(lib.so3lr_b200_system_enable_virial(self._h, 1 if on else 0), "enable_virial")
+        self._virial = bool(on)
+
+    def virial(self, stream=None):
+        """dE/d eps (3,3) float64 of the latest evaluation."""
+        w = torch.empty(3, 3, dtype=torch.float64, device=self.device)
+        s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        check(lib.so3lr_b200_system_virial(self._h, C.c_void_p(s.cuda_stream), _ptr(w)), "virial")
+        return w
 
     def compute(self, positions, stream=None):
         """positions: float32 CUDA tensor (n,3).  Returns dict of CUDA tensors (async on the current stream)."""
@@ -100,6 +116,10 @@ class System:
         check(lib.so3lr_b200_system_compute(self._h, C.c_void_p(s.cuda_stream), _ptr(R), _ptr(out["forces"]), _ptr(out["e_atom"]),
                                             _ptr(out["energy"]), _ptr(out["partial_charges"]), _ptr(out["hirshfeld_ratios"]),
                                             _ptr(out["dipole_vec"])), "system_compute")
+        if getattr(self, "_virial", False):
+            out["virial"] = self.virial(s)
+            if self._cell is not None:
+                out["stress"] = out["virial"] / abs(float(np.linalg.det(self._cell)))
         return out
 
     def compute_host(self, positions, want_aux=True):
