@@ -51,17 +51,25 @@ def _peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs.
+
+    One nvidia-smi process polls the given GPUs (all of them when `indices` is None).  It is started ahead of the warm-up,
+    because its start-up (NVML initialisation over every GPU of the box) disturbs running CUDA work for a moment; only the
+    samples that arrive between begin() and end() are used (the nearest ones when the region was shorter than a poll)."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index=0):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, indices=0, period_ms=200):
+        self.indices = None if indices is None else ([indices] if isinstance(indices, int) else list(indices))
+        self.period_ms, self.rows, self.proc = period_ms, [], None
+        self.t0 = self.t1 = None
 
     def start(self):
+        cmd = ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", str(self.period_ms)]
+        if self.indices is not None:
+            cmd.insert(1, "--id=" + ",".join(str(i) for i in self.indices))
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
@@ -69,19 +77,33 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
+
+    def begin(self):
+        self.t0 = time.perf_counter()
+
+    def end(self):
+        self.t1 = time.perf_counter()
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        if self.t1 is None:
+            self.end()
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
+        t0 = self.t0 if self.t0 is not None else 0.0
+        rows = [r for t, r in self.rows if t0 <= t <= self.t1 + 0.05]
+        if not rows and self.rows:     # region shorter than one poll: the samples next to it
+            mid = 0.5 * (t0 + self.t1)
+            n_gpu = 1 if self.indices is None else len(self.indices)
+            rows = [r for _, r in sorted(self.rows, key=lambda tr: abs(tr[0] - mid))[: 2 * n_gpu]]
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in rows:
             try:
                 sm.append(float(r[0])); mx.append(float(r[1]))
             except Exception:
@@ -159,19 +181,21 @@ def run_b200(args, rank, world, local_rank):
     else:
         step = lambda: sysm.nve(1, dt, md, Rd, Vd, Fd)
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
     st0 = sysm.stats()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     torch.cuda.synchronize()
+    sampler.begin()
     ev[0].record()
     for _ in range(args.steps):
         step()
     ev[1].record()
     torch.cuda.synchronize()
+    sampler.end()
     clocks = sampler.stop()
     ms = ev[0].elapsed_time(ev[1])
     st1 = sysm.stats()
@@ -207,12 +231,19 @@ def run_b200(args, rank, world, local_rank):
         o = sysm.compute_host(Rh, want_aux=False)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
+    tmp = np.empty_like(Rh)
+
+    def kick(F):               # in place, no temporaries: the host integrator is part of the step
+        np.multiply(F, acc, out=tmp)
+        np.add(Vh, tmp, out=Vh)
+
     for _ in range(args.steps):
-        Vh += acc * Fh
-        Rh += dt * Vh
+        kick(Fh)
+        np.multiply(Vh, np.float32(dt), out=tmp)
+        np.add(Rh, tmp, out=Rh)
         o = sysm.compute_host(Rh, want_aux=False)
         Fh = o["forces"]
-        Vh += acc * Fh
+        kick(Fh)
     torch.cuda.synchronize()
     t_e2e = time.perf_counter() - t0
     e2e = {"value": round(N * args.steps / t_e2e, 1), "unit": UNIT, "h2d_bytes_per_step": N * 12, "d2h_bytes_per_step": N * 12 + 8,
@@ -226,7 +257,9 @@ def run_b200(args, rank, world, local_rank):
                                    + ("NVT (Nose-Hoover chain 3) at 300 K, dt 0.5 fs" if ensemble == "nvt" else "NVE dt 0.5 fs from 300 K"),
                        "atoms": N, "sr_list_edges": E_list, "lr_list_pairs": P_list,
                        "list_rebuilds_in_timed_steps": st1["rebuilds"] - st0["rebuilds"],
-                       "l2_policy": "inputs larger than L2 (activations > 1 GB per step)" if N > 200000 else "inputs smaller than L2; no flush",
+                       "l2_policy": ("inputs larger than L2: a step streams about 18 kB per atom (q/k/v rows 2.5 kB per layer, "
+                                     "activations, cotangents, both neighbor lists)" if N * 18e3 > 126e6
+                                     else "inputs smaller than L2; no flush"),
                        "ns_per_day": round(args.steps / (ms * 1e-3) * 0.0432, 3)},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu}
     print(json.dumps(line), flush=True)

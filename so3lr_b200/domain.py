@@ -435,13 +435,21 @@ class DomainSystem:
         if ev is not None:
             ev[1].record()
 
+    def _mark(self, name):
+        """Device-side time stamps of the step's phases (benchmark only): the time between two marks covers the kernels, the
+        messages and any wait for a neighbouring rank that fall between them."""
+        if getattr(self, "time_phases", False) and self.device.type == "cuda":
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self._phase_events.append((name, e))
+
     # ---- evaluation ----
     def _maybe_rebuild(self):
         d2 = (self.R[: self.n0] - self.R_ref).square().sum(1).amax().reshape(1) if self.n0 else torch.zeros(1, device=self.device)
-        d2 = self.comm.all_reduce_max(d2.to(torch.float32))
-        if not torch.isfinite(d2).all():
+        d2 = float(self.comm.all_reduce_max(d2.to(torch.float32)))      # the step's one host read
+        if not np.isfinite(d2):
             raise RuntimeError("non-finite positions")
-        if float(d2) > (0.5 * self.skin) ** 2 or self.skin <= 0:
+        if d2 > (0.5 * self.skin) ** 2 or self.skin <= 0:
             import time
             if self.device.type == "cuda":
                 torch.cuda.synchronize(self.device)
@@ -463,12 +471,15 @@ class DomainSystem:
 
     def compute(self, check_rebuild=True):
         """Total energy (float64 tensor, all ranks) and forces on the owned atoms (n0, 3)."""
+        self._mark("step_start")
         if check_rebuild:
             self._maybe_rebuild()
+        self._mark("skin_test_repartition")
         # ghost positions follow their owners
         self.R[self.n0:] = 0.0
         self._halo_fill([self.R])
         self.R[self.n0:] += self.shift_vec[self.n0:]
+        self._mark("halo_positions")
         return self._evaluate()
 
     def compute_host(self, R_all_host):
@@ -505,24 +516,35 @@ class DomainSystem:
     def _evaluate(self):
         be, L = self.backend, self.backend.num_layers
         be.begin(self.R)
+        self._mark("lists_zbl")
         for l in range(L):
             be.layer_forward(l)
+            self._mark(f"layer{l}_forward")
             if l + 1 < L:
                 self._halo_fill(be.feature_rows(l + 1), sr_only=True)
+                self._mark(f"halo_features{l + 1}")
         q_raw, h = be.heads()
         qsum = self.comm.all_reduce_sum(q_raw.sum(dtype=torch.float64).reshape(1))
         q = q_raw + ((self.total_charge - qsum) / self.n_all).to(torch.float32)
         qh = torch.zeros(self.n_local, 2, device=self.device)
         qh[: self.n0, 0], qh[: self.n0, 1] = q, h
+        self._mark("heads_charge_sum")
         self._halo_fill([qh])
+        self._mark("halo_charges")
         gq_sum = self.comm.all_reduce_sum(be.pair(qh[:, 0].contiguous(), qh[:, 1].contiguous()))
+        self._mark("pair_terms")
         E_own = be.heads_backward(gq_sum, self.n_all)
+        self._mark("heads_backward")
         for l in reversed(range(L)):
             be.layer_backward_post(l)
+            self._mark(f"layer{l}_backward_dense")
             self._halo_fill(be.cotangent_rows(), sr_only=True)
+            self._mark(f"halo_cotangents{l}")
             be.layer_backward_attn(l)
+            self._mark(f"layer{l}_backward_attention")
         self.F = be.forces()
         self.E = self.comm.all_reduce_sum(E_own)
+        self._mark("forces_energy_sum")
         self.q, self.h = q, h
         return self.E, self.F
 
@@ -599,6 +621,10 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
     backend = CudaBackend(cutoff_lr=12.0, damping=2.0, skin=args.skin, device=local_rank)
     dom = DomainSystem(comm, backend, Z, R, cell, skin=args.skin, cutoff_lr=12.0, velocities=V, masses=m, device=dev)
     dom.compute(check_rebuild=False)
+    # one clock sampler for all GPUs, on rank 0, started ahead of the warm-up (its start-up disturbs running CUDA work)
+    sampler = args.clock_sampler(list(range(world))) if rank == 0 else None
+    if sampler:
+        sampler.start()
     dt = 0.5
     ensemble = getattr(args, "ensemble", None) or getattr(args, "default_ensemble", "nve")
     if ensemble == "nvt":
@@ -615,16 +641,20 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
     dist.barrier()
     st0 = backend.stats()
     rb0 = dom.n_rebuilds
-    sampler = args.clock_sampler(local_rank)
-    sampler.start()
+    if sampler:
+        sampler.begin()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
     ev[0].record()
+    t_host0 = time.perf_counter()
     for _ in range(args.steps):
         step()
+    host_ms = 1e3 * (time.perf_counter() - t_host0) / args.steps      # host time to enqueue a step (includes its waits on the device)
     ev[1].record()
     torch.cuda.synchronize()
     dist.barrier()
-    clocks = sampler.stop()
+    if sampler:
+        sampler.end()
+    clocks = sampler.stop() if sampler else None
     ms = torch.tensor([ev[0].elapsed_time(ev[1])], dtype=torch.float64, device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     launches = torch.tensor([backend.stats()["launches"] - st0["launches"]], dtype=torch.float64, device=dev)
@@ -636,11 +666,17 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
     # kernel times of rank 0's share over another K steps
     backend.sys.profile(True)
     dom.time_halo, dom._halo_events = True, []
+    dom.time_phases, dom._phase_events = True, []
     for _ in range(args.steps):
         step()
+    dom._mark("integrator")
     prof = backend.sys.profile_read()
     backend.sys.profile(False)
-    dom.time_halo = False
+    dom.time_halo = dom.time_phases = False
+    timeline = {}
+    for (_, a), (name, b) in zip(dom._phase_events[:-1], dom._phase_events[1:]):
+        key = "integrator" if name == "step_start" else name
+        timeline[key] = timeline.get(key, 0.0) + a.elapsed_time(b) / args.steps
     halo_ms = sum(a.elapsed_time(b) for a, b in dom._halo_events) / args.steps
     st = backend.stats()
     # end to end with host buffers: every rank uploads all positions, forces come back summed over the ranks
@@ -652,11 +688,18 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
     torch.cuda.synchronize()
     dist.barrier()
     t0 = time.perf_counter()
+    tmp = np.empty_like(Rh)
+
+    def kick(F):               # in place, no temporaries: the host integrator is part of the step
+        np.multiply(F, acc, out=tmp)
+        np.add(Vh, tmp, out=Vh)
+
     for _ in range(args.steps):
-        Vh += acc * Fh
-        Rh += dt * Vh
+        kick(Fh)
+        np.multiply(Vh, np.float32(dt), out=tmp)
+        np.add(Rh, tmp, out=Rh)
         _, Fh = dom.compute_host(Rh)
-        Vh += acc * Fh
+        kick(Fh)
     torch.cuda.synchronize()
     dist.barrier()
     t_e2e = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
@@ -676,6 +719,7 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
                     "algorithmic_bytes_per_launch": ab,
                     "ms_per_launch": round(t_launch, 4), "scope": "rank 0's sub-box (local atoms incl. ghosts)",
                     "halo_exchange_ms_per_step": round(halo_ms, 3),
+                    "timeline_ms_per_step": {k: round(v, 3) for k, v in timeline.items()},
                     "groups_ms_per_step": {g: round(v[0] / args.steps, 4) for g, v in sorted(groups.items(), key=lambda kv: -kv[1][0])}}
         line = {"metric": "atom-steps/s (E+F)", "value": round(value, 1), "unit": "atom-steps/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
@@ -685,7 +729,9 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
                            "atoms": N, "decomposition": f"{world} slabs along axis {dom.geo.axis}, halo {dom.geo.lr_radius:.1f} A (features: {dom.geo.shell:.1f} A)",
                            "local_atoms_sum_over_ranks": int(nloc[0]), "list_rebuilds_in_timed_steps": rebuilds,
                            "repartition_ms_each": round(1e3 * getattr(dom, "t_repartition", 0.0) / max(1, dom.n_rebuilds - 1), 2),
-                           "l2_policy": "inputs larger than L2" if N / world > 200000 else "inputs smaller than L2; no flush",
+                           "l2_policy": ("inputs larger than L2: a step streams about 18 kB per local atom"
+                                         if dom.n0 * 18e3 > 126e6 else "inputs smaller than L2; no flush"),
+                           "host_ms_per_step": round(host_ms, 3),
                            "ns_per_day": round(args.steps / (ms * 1e-3) * 0.0432, 3)},
                 "e2e": {"value": round(N * args.steps / t_e2e, 1), "unit": "atom-steps/s", "h2d_bytes_per_step": N * 12 * world,
                         "d2h_bytes_per_step": (N * 12 + 8) * world, "ms_per_step": round(1e3 * t_e2e / args.steps, 3)},
