@@ -163,6 +163,27 @@ SO3LR_B200_API int so3lr_b200_system_nvt(so3lr_b200_system* sys, void* stream, i
                                          float* positions_dev, float* velocities_dev, float* forces_dev, double* chain_dev,
                                          double* energy_dev);
 
+/* NPT: isotropic Martyna-Tobias-Klein barostat with Nose-Hoover chains on the particles and on the box, in the form
+ * jax_md.simulate.npt_nose_hoover integrates it.  The box coordinate is eps = ln(V/V0)/3 (V0 = volume of the reference cell
+ * cell0), its momentum has the mass 3 (n_atoms + 1) kT tau_b^2; positions are Cartesian and scale with the box.
+ * State, SO3LR_B200_NPT_STATE_DOUBLES doubles on the device: [0,18) thermostat chain, [18,36) barostat chain (layout of
+ * so3lr_b200_nhc_*), [36] eps, [37] its momentum (eV fs), [38..41] coefficients of the current step, [42] volume.
+ * pressure in eV/A^3 (1 bar = 6.241509074e-7).  The context must have the virial enabled and hold the evaluation of the
+ * positions passed in (call so3lr_b200_system_compute after enabling it); the cell of the context follows the box, the
+ * neighbor lists are kept across the rescaling and rebuilt by the skin test.  cell_out9 (host, optional) receives the
+ * cell after the last step.
+ * Replaces: jax_md.simulate.npt_nose_hoover as created in so3lr/cli/so3lr_md.py:1089-1107 (barostat tau = dt * nhc_baro,
+ *           :1709-1711) and stepped at :1254-1282, where the box is read back with jax_md.simulate.npt_box. */
+#define SO3LR_B200_NPT_STATE_DOUBLES 44
+SO3LR_B200_API int so3lr_b200_npt_init(void* stream, double* state_dev);
+SO3LR_B200_API int so3lr_b200_system_npt(so3lr_b200_system* sys, void* stream, int n_steps, float dt_fs, double kT, double pressure,
+                                         double tau_t_fs, double tau_b_fs, int chain_length, int chain_steps, int sy_steps,
+                                         const float* masses_dev, float* positions_dev, float* velocities_dev, float* forces_dev,
+                                         double* state_dev, const float* cell0_9, float* cell_out9, double* energy_dev);
+/* Replaces the cell by a slightly rescaled one without discarding the neighbor lists (the caller has moved the positions
+ * with the cell; the next evaluation's skin test decides about a rebuild).  so3lr_b200_system_set_cell discards them. */
+SO3LR_B200_API int so3lr_b200_system_rescale_cell(so3lr_b200_system* sys, const float* cell9);
+
 /* Domain-decomposed evaluation of one large periodic structure: every rank owns the atoms of its sub-box and holds
  * copies ("ghosts") of the atoms within the long-range list radius (12 A + skin) of it; the ghosts within one short-range
  * shell (4.5 A + skin) also carry features.  The library evaluates one rank's owned atoms layer by layer; between the

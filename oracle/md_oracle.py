@@ -133,3 +133,81 @@ def nvt_invariant(c: Chain, E_pot, V, m, kT):
     H = E_pot + kinetic_energy(V, m)
     H += float(np.sum(c.p_xi ** 2 / (2.0 * c.Q))) + c.dof * kT * c.xi[0] + kT * float(np.sum(c.xi[1:]))
     return H
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# NPT: isotropic Martyna-Tobias-Klein barostat with Nose-Hoover chains on the particles and on the box, in the form
+# jax_md.simulate.npt_nose_hoover integrates it (created at so3lr/cli/so3lr_md.py:1078-1107 with the thermostat settings
+# of :1698-1707 and the barostat's tau = dt * nhc_baro, :1709-1711; the box after a step is read back at :1270-1282).
+# The box coordinate is eps = (1/3) ln(V / V0); its momentum p_eps has the mass W = 3 (N + 1) kT tau_b^2.
+# Positions are Cartesian here and scale with the box.  force_fn(R, cell) -> (E, F, virial) with virial = dE/d strain (3x3).
+# ----------------------------------------------------------------------------------------------------------------------
+BAR = 6.241509074e-7             # eV / A^3 per bar
+
+
+def sinhx_x(x):
+    """sinh(x)/x by its series (the step's arguments are ~1e-4)."""
+    x2 = x * x
+    return 1 + x2 / 6 + x2 ** 2 / 120 + x2 ** 3 / 5040 + x2 ** 4 / 362880 + x2 ** 5 / 39916800
+
+
+class NPTState:
+    def __init__(self, R, V, m, cell0, kT, tau_t, tau_b, chain_length, force_fn):
+        self.R, self.V, self.m = np.array(R, dtype=np.float64), np.array(V, dtype=np.float64), np.array(m, dtype=np.float64)
+        self.cell0 = np.array(cell0, dtype=np.float64)
+        self.V0 = abs(np.linalg.det(self.cell0))
+        self.N = len(self.m)
+        self.eps, self.p_eps = 0.0, 0.0
+        self.tau_b = float(tau_b)
+        self.W = 3.0 * (self.N + 1) * kT * self.tau_b ** 2
+        self.thermostat = Chain(chain_length, 3 * self.N, kinetic_energy(self.V, self.m), kT, tau_t)
+        self.barostat = Chain(chain_length, 1, 0.0, kT, tau_b)
+        self.E, self.F, self.virial = force_fn(self.R, self.cell())
+
+    def volume(self):
+        return self.V0 * np.exp(3.0 * self.eps)
+
+    def cell(self):
+        return self.cell0 * np.exp(self.eps)
+
+
+def npt_step(force_fn, s: NPTState, dt, kT, pressure, chain_steps, sy_steps):
+    """One step; pressure in eV/A^3."""
+    N, a = s.N, ACC / s.m[:, None]
+    alpha = 1.0 + 1.0 / N
+    s.barostat.set_mass(kT)
+    s.thermostat.set_mass(kT)
+    s.W = 3.0 * (N + 1) * kT * s.tau_b ** 2
+    s.p_eps *= chain_half_step(s.barostat, dt, kT, chain_steps, sy_steps)
+    s.V = s.V * chain_half_step(s.thermostat, dt, kT, chain_steps, sy_steps)
+
+    def box_force():
+        ke2 = 2.0 * kinetic_energy(s.V, s.m)
+        return alpha * ke2 - np.trace(s.virial) - 3.0 * pressure * s.volume()
+
+    def kick():
+        x = alpha * (s.p_eps / s.W) * dt / 2
+        s.V = s.V * np.exp(-x) + (dt / 2) * a * s.F * sinhx_x(x / 2) * np.exp(-x / 2)
+
+    s.p_eps += dt / 2 * box_force()
+    kick()
+    v_eps = s.p_eps / s.W
+    s.eps += v_eps * dt
+    x = v_eps * dt
+    s.R = s.R * np.exp(x) + dt * s.V * np.exp(x / 2) * sinhx_x(x / 2)
+    s.E, s.F, s.virial = force_fn(s.R, s.cell())
+    kick()
+    s.p_eps += dt / 2 * box_force()
+    s.thermostat.ke = kinetic_energy(s.V, s.m)
+    s.barostat.ke = s.p_eps ** 2 / (2.0 * s.W)
+    s.V = s.V * chain_half_step(s.thermostat, dt, kT, chain_steps, sy_steps)
+    s.p_eps *= chain_half_step(s.barostat, dt, kT, chain_steps, sy_steps)
+    return s
+
+
+def npt_invariant(s: NPTState, kT, pressure):
+    """Conserved quantity of the NPT dynamics: E_pot + KE + p_eps^2 / 2W + P V + both chains' energies."""
+    H = s.E + kinetic_energy(s.V, s.m) + s.p_eps ** 2 / (2.0 * s.W) + pressure * s.volume()
+    for c in (s.thermostat, s.barostat):
+        H += float(np.sum(c.p_xi ** 2 / (2.0 * c.Q))) + c.dof * kT * c.xi[0] + kT * float(np.sum(c.xi[1:]))
+    return H

@@ -261,6 +261,8 @@ struct so3lr_b200_system {
   float* d_Rref = nullptr;
   int* d_flag = nullptr;
   int* h_flag = nullptr;   // pinned
+  double* h_box = nullptr; // pinned: the box coordinate read back by the NPT step
+  bool virial_fresh = false;   // virial_sum belongs to the latest evaluation
   bool have_lists = false;
   // graph-level row pointers
   int *d_rowptr_g = nullptr, *d_rowptr_lr_g = nullptr;
@@ -479,6 +481,7 @@ void reduce_virial(so3lr_b200_system* S, cudaStream_t st, int n0) {
   if (blocks > 592) blocks = 592;
   { virial_partial_kernel<<<blocks, 256, 0, st>>>(n0, S->virial, S->virial_partials); count_launch(); }
   { virial_final_kernel<<<1, 32, 0, st>>>(blocks, S->virial_partials, S->virial_sum); count_launch(); }
+  S->virial_fresh = true;
 }
 
 // network forward up to the output heads: e_nn, q_raw, hv for the owned atoms; ZBL energy and force; F is zeroed first
@@ -740,6 +743,7 @@ SO3LR_B200_API int so3lr_b200_system_destroy(so3lr_b200_system* S) {
   for (NeighborListDev* L : {&S->sr, &S->lrl}) { cudaFree(L->row_ptr); cudaFree(L->nbr_j); cudaFree(L->edge_i); }
   cudaFree(S->dR);
   if (S->h_flag) cudaFreeHost(S->h_flag);
+  if (S->h_box) cudaFreeHost(S->h_box);
   if (S->h_R) cudaFreeHost(S->h_R);
   if (S->h_F) cudaFreeHost(S->h_F);
   if (S->h_q) cudaFreeHost(S->h_q);
@@ -756,7 +760,14 @@ SO3LR_B200_API int so3lr_b200_system_set_cell(so3lr_b200_system* S, const float*
   int rc = make_cell(cell9, &S->cell);
   if (rc) return rc;
   S->have_lists = false;
+  S->virial_fresh = false;
   return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_rescale_cell(so3lr_b200_system* S, const float* cell9) {
+  if (!S || !cell9 || !S->cell.periodic) return kInvalidArgument;
+  S->virial_fresh = false;
+  return make_cell(cell9, &S->cell);
 }
 
 static int prepare_lists(so3lr_b200_system* S, cudaStream_t st, const float* R, bool allow_sort = true) {
@@ -929,6 +940,7 @@ SO3LR_B200_API int so3lr_b200_system_enable_virial(so3lr_b200_system* S, int ena
     if (S->pool.status != kOk) return S->pool.status;
   }
   S->want_virial = enable != 0;
+  S->virial_fresh = false;
   return kOk;
 }
 
@@ -994,6 +1006,74 @@ SO3LR_B200_API int so3lr_b200_system_nvt(so3lr_b200_system* S, void* stream, int
                    blocks);
     if (step == n_steps - 1) md_apply_scale(st, n, V, chain);
     S->prof.end(st);
+  }
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_npt_init(void* stream, double* state) {
+  if (!state) return kInvalidArgument;
+  tl_launch_counter = nullptr;
+  npt_init((cudaStream_t)stream, state);
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_npt(so3lr_b200_system* S, void* stream, int n_steps, float dt, double kT, double pressure,
+                                         double tau_t, double tau_b, int chain_length, int chain_steps, int sy_steps,
+                                         const float* masses, float* R, float* V, float* F, double* state, const float* cell0_9,
+                                         float* cell_out9, double* energy) {
+  if (!S || !masses || !R || !V || !F || !state || !cell0_9 || n_steps < 0) return kInvalidArgument;
+  if (!S->cell.periodic || S->n_graphs != 1 || !S->want_virial) return kInvalidArgument;
+  const int n = S->n;
+  if (!nhc_settings_ok(chain_length, chain_steps, sy_steps, dt, tau_t, kT, 3.0 * n) || !(tau_b > 0.0) || !std::isfinite(pressure))
+    return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int blocks = (n + 255) / 256;
+  if (!S->ke_partials) {
+    S->ke_partials = S->pool.get<double>((size_t)(S->n_cap + 255) / 256);
+    if (!S->ke_partials) return kCudaError;
+  }
+  if (!S->h_box && cudaMallocHost((void**)&S->h_box, sizeof(double)) != cudaSuccess) return kCudaError;
+  double h0[9];
+  for (int k = 0; k < 9; ++k) h0[k] = cell0_9[k];
+  const double V0 = std::fabs(h0[0] * (h0[4] * h0[8] - h0[5] * h0[7]) - h0[1] * (h0[3] * h0[8] - h0[5] * h0[6]) +
+                              h0[2] * (h0[3] * h0[7] - h0[4] * h0[6]));
+  if (!(V0 > 0.0)) return kInvalidArgument;
+  NptParams p{chain_length, chain_steps, sy_steps, n, (double)dt, kT, pressure, tau_t, tau_b, V0};
+  double* box = state + 2 * kNhcStateDoubles;
+  float cell9[9];
+  for (int step = 0; step < n_steps; ++step) {
+    // the box's first half kick needs the virial of the positions as they are: the forces in F came with it
+    if (!S->virial_fresh) return kInvalidArgument;
+    S->prof.begin(kPMd, st);
+    if (step == 0) md_kinetic_partials(st, n, masses, V, S->ke_partials);
+    npt_pre(st, state, p, S->virial_sum, step == 0 ? S->ke_partials : nullptr, blocks);
+    npt_first_half(st, n, masses, R, V, F, state);
+    S->prof.end(st);
+    // the evaluation needs the new cell on the host: one 8-byte read per step
+    SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_box, box, sizeof(double), cudaMemcpyDeviceToHost, st));
+    SO3LR_CUDA_CHECK(cudaStreamSynchronize(st));
+    if (!std::isfinite(*S->h_box)) return kNotFinite;
+    const double scale = std::exp(*S->h_box);
+    for (int k = 0; k < 9; ++k) cell9[k] = (float)(h0[k] * scale);
+    int rc = make_cell(cell9, &S->cell);     // lists stay: the skin test sees the atoms' affine motion like any other
+    if (rc) return rc;
+    rc = so3lr_b200_system_compute(S, st, R, F, nullptr, step == n_steps - 1 ? energy : nullptr, nullptr, nullptr, nullptr);
+    if (rc) return rc;
+    S->prof.begin(kPMd, st);
+    npt_second_half(st, n, masses, V, F, state, S->ke_partials);
+    npt_post(st, state, p, S->virial_sum, S->ke_partials, blocks);
+    if (step == n_steps - 1) md_apply_scale(st, n, V, state);
+    S->prof.end(st);
+  }
+  if (cell_out9) {
+    SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_box, box, sizeof(double), cudaMemcpyDeviceToHost, st));
+    SO3LR_CUDA_CHECK(cudaStreamSynchronize(st));
+    const double scale = std::exp(*S->h_box);
+    for (int k = 0; k < 9; ++k) cell_out9[k] = (float)(h0[k] * scale);
   }
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;

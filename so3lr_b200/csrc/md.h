@@ -8,6 +8,18 @@ constexpr int kNhcMaxChain = 8;
 // [2, 2+8) chain positions, [10, 18) chain momenta (eV fs)
 constexpr int kNhcStateDoubles = 2 + 2 * kNhcMaxChain;
 
+// NPT state on the device: thermostat chain | barostat chain | box block (eps, p_eps, four step coefficients, volume, spare)
+constexpr int kNptStateDoubles = 2 * kNhcStateDoubles + 8;
+struct NptParams {
+  int chain_length, chain_steps, sy_steps, n_atoms;
+  double dt, kT, pressure, tau_t, tau_b, V0;
+};
+void npt_init(cudaStream_t st, double* state);
+void npt_pre(cudaStream_t st, double* state, const NptParams& p, const double* virial9, const double* partials, int n_partials);
+void npt_post(cudaStream_t st, double* state, const NptParams& p, const double* virial9, const double* partials, int n_partials);
+void npt_first_half(cudaStream_t st, int n, const float* m, float* R, float* V, const float* F, const double* state);
+void npt_second_half(cudaStream_t st, int n, const float* m, float* V, const float* F, const double* state, double* partials);
+
 int nhc_settings_ok(int chain_length, int chain_steps, int sy_steps, double dt, double tau, double kT, double dof);
 void nhc_init(cudaStream_t st, double* chain);
 void nhc_half_steps(cudaStream_t st, double* chain, int chain_length, int chain_steps, int sy_steps, double dt, double tau, double kT,

@@ -203,8 +203,43 @@ class System:
         return E
 
 
+    def rescale_cell(self, cell):
+        """New, slightly rescaled cell; the neighbor lists are kept (the positions must have moved with the cell)."""
+        c9 = np.ascontiguousarray(np.asarray(cell, dtype=np.float32).reshape(9))
+        check(lib.so3lr_b200_system_rescale_cell(self._h, _ptr(c9)), "rescale_cell")
+        self._cell = np.asarray(cell, dtype=np.float64).reshape(3, 3)
+
+    def npt(self, n_steps, dt_fs, kT, pressure, tau_t_fs, tau_b_fs, masses, positions, velocities, forces, state, cell0,
+            chain_length=3, chain_steps=2, sy_steps=3):
+        """In-place NPT steps (isotropic barostat with Nose-Hoover chains; pressure in eV/A^3); `state` comes from npt_state()
+        and `cell0` is the reference cell the box coordinate refers to.  The virial must be enabled and the latest evaluation
+        must be the one of `positions`.  Returns (per-graph energy of the last step, the cell after it)."""
+        E = torch.empty(self.n_graphs, dtype=torch.float64, device=self.device)
+        c0 = np.ascontiguousarray(np.asarray(cell0, dtype=np.float32).reshape(9))
+        cout = np.empty(9, np.float32)
+        s = torch.cuda.current_stream(self.device)
+        check(lib.so3lr_b200_system_npt(self._h, C.c_void_p(s.cuda_stream), int(n_steps), float(dt_fs), float(kT), float(pressure),
+                                        float(tau_t_fs), float(tau_b_fs), int(chain_length), int(chain_steps), int(sy_steps),
+                                        _ptr(masses), _ptr(positions), _ptr(velocities), _ptr(forces), _ptr(state), _ptr(c0),
+                                        _ptr(cout), _ptr(E)), "npt")
+        self._cell = cout.astype(np.float64).reshape(3, 3)
+        return E, self._cell.copy()
+
+
 NHC_STATE_DOUBLES = 18
 NHC_MAX_CHAIN = 8
+NPT_STATE_DOUBLES = 44
+BAR = 6.241509074e-7              # eV / A^3 per bar
+
+
+def npt_state(device):
+    """A zeroed NPT state on `device`: [0:18] thermostat chain, [18:36] barostat chain, [36] eps = ln(V/V0)/3, [37] its
+    momentum, [38:42] step coefficients, [42] volume."""
+    st = torch.empty(NPT_STATE_DOUBLES, dtype=torch.float64, device=device)
+    with torch.cuda.device(st.device):
+        s = torch.cuda.current_stream(st.device)
+        check(lib.so3lr_b200_npt_init(C.c_void_p(s.cuda_stream), _ptr(st)), "npt_init")
+    return st
 
 
 def nhc_state(device):

@@ -17,7 +17,7 @@ from typing import Optional
 import numpy as np
 import torch
 
-from .engine import System, nhc_state
+from .engine import BAR, System, nhc_state, npt_state  # noqa: F401
 
 KB = 8.617333262e-5               # eV / K
 ACC_UNIT = 9.648533212331e-3      # eV / (A amu) -> A / fs^2
@@ -32,6 +32,8 @@ class MDState:
     mass: torch.Tensor              # (n,) float32, amu
     chain: Optional[torch.Tensor]   # thermostat chain (None for NVE), see so3lr_b200.engine.nhc_state
     energy: Optional[torch.Tensor] = None     # potential energy per graph after the last step
+    box: Optional[np.ndarray] = None          # NPT: the current cell (3,3), lattice vectors as rows
+    reference_box: Optional[np.ndarray] = None
 
     @property
     def momentum(self):
@@ -109,3 +111,61 @@ def nvt_nose_hoover_invariant(state: MDState, kT: float, tau: float, chain_lengt
     Q[0] *= dof
     xi, p = c[2:2 + L], c[10:10 + L]
     return float(state.energy.sum()) + kinetic_energy(state) + float(np.sum(p * p / (2 * Q))) + dof * kT * xi[0] + kT * float(xi[1:].sum())
+
+
+def npt_nose_hoover(system: System, dt: float, pressure: float, kT: float, barostat_kwargs: Optional[dict] = None,
+                    thermostat_kwargs: Optional[dict] = None):
+    """(init_fn, apply_fn) for the isotropic Martyna-Tobias-Klein barostat with Nose-Hoover chains on particles and box;
+    dt and the taus in fs, kT in eV, pressure in eV/A^3 (BAR converts).  The kwargs carry chain_length / chain_steps /
+    sy_steps / tau as the reference passes them (so3lr/cli/so3lr_md.py:1698-1711); tau defaults to 100 dt (thermostat) and
+    1000 dt (barostat).  Both chains share the thermostat's chain_length / chain_steps / sy_steps.  Mirrors create_npt_nhc_fn
+    (so3lr/cli/so3lr_md.py:1089-1107); the cell of `system` follows the box, read it with npt_box(state)."""
+    tk = dict(chain_length=3, chain_steps=2, sy_steps=3, tau=100.0 * dt)
+    tk.update(thermostat_kwargs or {})
+    bk = dict(tk, tau=1000.0 * dt)
+    bk.update(barostat_kwargs or {})
+    if any(bk[k] != tk[k] for k in ("chain_length", "chain_steps", "sy_steps")):
+        raise NotImplementedError("the two chains share their length and factorisation")
+
+    def init_fn(R, box, mass, velocity=None, seed=0):
+        system.enable_virial(True)
+        system.set_cell(box)
+        state = _init_state(system, R, mass, velocity, kT, seed, npt_state(system.device))
+        state.box = np.asarray(box, dtype=np.float64).reshape(3, 3).copy()
+        state.reference_box = state.box.copy()
+        return state
+
+    def apply_fn(state: MDState, n_steps: int = 1, kT: float = kT, pressure: float = pressure):
+        state.energy, state.box = system.npt(n_steps, dt, kT, pressure, tk["tau"], bk["tau"], state.mass, state.position,
+                                             state.velocity, state.force, state.chain, state.reference_box,
+                                             chain_length=tk["chain_length"], chain_steps=tk["chain_steps"], sy_steps=tk["sy_steps"])
+        return state
+
+    apply_fn.settings = dict(thermostat=tk, barostat=bk, kT=kT, pressure=pressure, dt=dt)
+    return init_fn, apply_fn
+
+
+def npt_box(state: MDState) -> np.ndarray:
+    """The cell after the latest step (jax_md.simulate.npt_box, used at so3lr/cli/so3lr_md.py:1270)."""
+    return state.box
+
+
+def pressure(system: System, state: MDState) -> float:
+    """Instantaneous pressure in eV/A^3: (2 KE - trace of the virial) / (3 V), from the latest evaluation."""
+    vol = abs(float(np.linalg.det(state.box)))
+    return (2.0 * kinetic_energy(state) - float(torch.trace(system.virial()))) / (3.0 * vol)
+
+
+def npt_nose_hoover_invariant(state: MDState, kT: float, pressure: float, tau_t: float, tau_b: float, chain_length: int = 3) -> float:
+    """Conserved quantity of the NPT dynamics in eV (jax_md.simulate.npt_nose_hoover_invariant, so3lr/cli/so3lr_md.py:940-949)."""
+    c = state.chain.cpu().numpy()
+    L, n = chain_length, state.mass.numel()
+    vol = abs(float(np.linalg.det(state.box)))
+    W = 3.0 * (n + 1) * kT * tau_b ** 2
+    H = float(state.energy.sum()) + kinetic_energy(state) + c[37] ** 2 / (2.0 * W) + pressure * vol
+    for off, dof, tau in ((0, 3.0 * n, tau_t), (18, 1.0, tau_b)):
+        Q = kT * tau ** 2 * np.ones(L)
+        Q[0] *= dof
+        xi, p = c[off + 2:off + 2 + L], c[off + 10:off + 10 + L]
+        H += float(np.sum(p * p / (2 * Q))) + dof * kT * xi[0] + kT * float(xi[1:].sum())
+    return H

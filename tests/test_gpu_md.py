@@ -178,3 +178,75 @@ def test_decomposed_nvt_tracks_single_device():
     assert np.median(np.abs(Vdd - Vd.cpu().numpy())) < 2e-6
     np.testing.assert_allclose(ch[2:5], ref_chain[2:5], rtol=1e-3, atol=1e-8)
     np.testing.assert_allclose(ch[10:13], ref_chain[10:13], rtol=1e-3, atol=1e-5)
+
+
+def test_npt_trajectory_matches_oracle(oracle_params):
+    """A few NPT steps of the 192-atom water box against the oracle's float64 integrator driven by the oracle's energy, forces
+    and strain derivative.  Short time constants so that box and chains move visibly within the few steps."""
+    from so3lr_b200 import md
+    from so3lr_b200 import workloads as W
+    from so3lr_b200.engine import System
+    Z, R, cell = W.water_box(64, 12.42, 1000)
+    R = np.asarray(R, dtype=np.float32)
+    cell = np.asarray(cell, dtype=np.float64)
+    V, m = W.maxwell_boltzmann(Z, 300.0, 3)
+    V, m = np.asarray(V, dtype=np.float32), np.asarray(m, dtype=np.float32)
+    dt, tau_t, tau_b, steps, lr = 0.5, 10.0, 40.0, 5, 5.5
+    P_target = 1000.0 * md.BAR
+
+    def force(X, c):
+        ref = O.energy_forces(oracle_params, X, Z, c, cutoff_lr=lr, damping=2.0)
+        return ref["energy"], ref["forces"], ref["virial"]
+
+    s = System(Z, cell, cutoff_lr=lr, damping=2.0, skin=0.3)
+    init_fn, apply_fn = md.npt_nose_hoover(s, dt, P_target, KT300, barostat_kwargs=dict(tau=tau_b), thermostat_kwargs=dict(tau=tau_t))
+    state = init_fn(R, cell, m, velocity=V)
+    state = apply_fn(state, 2)
+    state = apply_fn(state, steps - 2)          # the state is carried between calls
+    o = MD.NPTState(R.astype(np.float64), V.astype(np.float64), m.astype(np.float64), cell, KT300, tau_t, tau_b, 3, force)
+    for _ in range(steps):
+        MD.npt_step(force, o, dt, KT300, P_target, 2, 3)
+    c = state.chain.cpu().numpy()
+    assert abs(o.eps) > 1e-7                                     # the box did move
+    assert abs(c[36] - o.eps) < 2e-3 * abs(o.eps) + 1e-9, (c[36], o.eps)
+    assert abs(c[37] - o.p_eps) < 2e-3 * abs(o.p_eps), (c[37], o.p_eps)
+    np.testing.assert_allclose(md.npt_box(state), o.cell(), rtol=2e-6)
+    assert np.abs(state.position.cpu().numpy() - o.R).max() < 5e-5
+    assert np.abs(state.velocity.cpu().numpy() - o.V).max() < 3e-6
+    assert abs(float(state.energy.sum()) - o.E) < 1e-5 * abs(o.E)
+    np.testing.assert_allclose(c[2:5], o.thermostat.xi, rtol=1e-3, atol=1e-9)
+    np.testing.assert_allclose(c[10:13], o.thermostat.p_xi, rtol=1e-3, atol=1e-6)
+    np.testing.assert_allclose(c[20:23], o.barostat.xi, rtol=1e-2, atol=1e-9)
+    np.testing.assert_allclose(c[28:31], o.barostat.p_xi, rtol=1e-2, atol=1e-6)
+    assert c[1] == 1.0 and abs(c[42] / o.volume() - 1.0) < 1e-6
+
+
+def test_npt_water_box_conserves_its_invariant_and_moves_towards_the_target_pressure():
+    from so3lr_b200 import md
+    from so3lr_b200 import workloads as W
+    from so3lr_b200.engine import System
+    Z, R, cell = W.water_box(512, 24.9, 7, jitter=0.02)
+    cell = np.asarray(cell, dtype=np.float64)
+    V, m = W.maxwell_boltzmann(Z, 300.0, 8)
+    s = System(Z, cell, cutoff_lr=12.0, damping=2.0, skin=0.5)
+    dt, tau_t, tau_b = 0.25, 25.0, 100.0
+    init_fn, apply_fn = md.npt_nose_hoover(s, dt, 0.0, KT300, barostat_kwargs=dict(tau=tau_b), thermostat_kwargs=dict(tau=tau_t))
+    state = init_fn(R, cell, m, velocity=V)
+    p0 = md.pressure(s, state)
+    target = p0 - np.sign(p0) * 2000.0 * md.BAR           # 2 kbar towards zero from where the start happens to be
+    init_fn, apply_fn = md.npt_nose_hoover(s, dt, target, KT300, barostat_kwargs=dict(tau=tau_b), thermostat_kwargs=dict(tau=tau_t))
+    state = init_fn(R, cell, m, velocity=V)
+    H0 = md.npt_nose_hoover_invariant(state, KT300, target, tau_t, tau_b)
+    vol0 = abs(np.linalg.det(state.box))
+    for _ in range(4):
+        state = apply_fn(state, 25)
+    H1 = md.npt_nose_hoover_invariant(state, KT300, target, tau_t, tau_b)
+    dof = 3.0 * len(Z)
+    assert abs(H1 - H0) < 2e-3 * dof * KT300, (H0, H1)
+    vol1 = abs(np.linalg.det(md.npt_box(state)))
+    # pressure above the target expands the box, below it compresses it
+    assert (vol1 - vol0) * np.sign(p0 - target) > 0, (vol0, vol1, p0, target)
+    # the context's cell followed the box: a fresh context at the final cell gives the same energy and forces
+    chk = System(Z, md.npt_box(state), cutoff_lr=12.0, damping=2.0).compute(state.position)
+    assert abs(float(chk["energy"].sum()) - float(state.energy.sum())) < 1e-5 * abs(float(state.energy.sum()))
+    assert np.abs(chk["forces"].cpu().numpy() - state.force.cpu().numpy()).max() < 2e-4
