@@ -136,7 +136,7 @@ def algorithmic_bytes(group, N, E, P):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch and atom of each group's dominant kernel, from the ncu captures on
 # the 98,304-atom box (profiles/attn_mma_water_98k.md); traffic grows with the atom count at fixed density
-NCU_TRAFFIC_PER_ATOM = {"attn_bwd": 859.2e6 / 98304, "attn_fwd": 555.5e6 / 98304, "pair_lr": 192.9e6 / 98304}
+NCU_TRAFFIC_PER_ATOM = {"attn_bwd": 865.3e6 / 98304, "attn_fwd": 558.3e6 / 98304, "pair_lr": 192.0e6 / 98304}
 
 
 def ncu_traffic(group, n_atoms):

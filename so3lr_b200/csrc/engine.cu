@@ -279,6 +279,7 @@ struct so3lr_b200_system {
   long long edge_cap = 0;
   float* F_int = nullptr;
   double* d_energy = nullptr;
+  double* red_scratch = nullptr;   // block partials of the whole-structure sums (charge, energy, dipole)
   float* d_dipole = nullptr;
   // host staging
   float *h_R = nullptr, *h_F = nullptr, *h_q = nullptr, *h_h = nullptr, *h_dip = nullptr;
@@ -377,13 +378,13 @@ int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, co
     S->prof.begin(kPPostFwd, st); launch_atom_post_fwd(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]); S->prof.end(st);
   }
   S->prof.begin(kPHeads, st); launch_heads_fwd(st, M, n, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv); S->prof.end(st);
-  launch_charge_conserve(st, S->n_graphs, S->d_graph_start, S->q_raw, S->d_total_charge, S->hv, S->q, S->h);
+  launch_charge_conserve(st, S->n_graphs, S->d_graph_start, S->q_raw, S->d_total_charge, S->hv, S->q, S->h, S->n, S->red_scratch);
   S->prof.begin(kPPairLr, st);
   launch_pair_lr(st, S->lr, S->cell, n, row_ptr_lr, nbr_j_lr, S->d_Z, nullptr, S->q, S->h, 1, dR_lr_in, g_dR_lr_out, nullptr, nullptr, S->gq,
                  S->gh, S->e_coul, S->e_disp, ge);
   S->prof.end(st);
   { combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
-  launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw);
+  launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw, S->n, S->red_scratch);
   S->prof.begin(kPHeads, st); launch_heads_bwd(st, M, n, S->d_Z, S->ze, S->zq, S->zh, S->hv, ge ? ge : S->ones, S->gq_raw, S->gh, S->g4); S->prof.end(st);
   float* gev2 = S->gev_a;
   float* gev_in = S->gev_b;
@@ -576,13 +577,13 @@ int evaluate_fused(so3lr_b200_system* S, cudaStream_t st, const float* R, float*
   int rc = fused_forward(S, st, R, c, false, F);
   if (rc) return rc;
   fill(st, S->e_coul, n, 0.f); fill(st, S->e_disp, n, 0.f); fill(st, S->gq, n, 0.f); fill(st, S->gh, n, 0.f);
-  launch_charge_conserve(st, S->n_graphs, S->d_graph_start, S->q_raw, S->d_total_charge, S->hv, S->q, S->h);
+  launch_charge_conserve(st, S->n_graphs, S->d_graph_start, S->q_raw, S->d_total_charge, S->hv, S->q, S->h, S->n, S->red_scratch);
   S->prof.begin(kPPairLr, st);
   launch_pair_lr(st, S->lr, S->cell, n, S->lrl.row_ptr, S->lrl.nbr_j, S->d_Z, R, S->q, S->h, 0, nullptr, nullptr, nullptr, F, S->gq, S->gh,
                  S->e_coul, S->e_disp, nullptr, S->vir());
   S->prof.end(st);
   { combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
-  launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw);
+  launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw, S->n, S->red_scratch);
   return fused_backward(S, st, c, F);
 }
 
@@ -707,6 +708,7 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
   S->F_int = A.get<float>((size_t)n * 3);
   S->GV = A.get<float>((size_t)n * 4 * kMaxTabSpecies);
   S->d_energy = A.get<double>(n_graphs); S->d_dipole = A.get<float>((size_t)n_graphs * 3);
+  S->red_scratch = A.get<double>(4 * 296);
   S->d_Rstage = A.get<float>((size_t)n * 3);
   if (A.status != kOk) { A.release(); delete S; return A.status; }
   bool ok = cudaMemcpy(S->d_Z0, Z, (size_t)n * sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess &&
@@ -810,7 +812,7 @@ SO3LR_B200_API int so3lr_b200_system_compute(so3lr_b200_system* S, void* stream,
   }
   rc = evaluate_fused(S, st, R_eval, S->sorted ? S->F_s : Fout);
   if (rc) return rc;
-  launch_graph_reduce(st, S->n_graphs, S->d_graph_start, S->e_atom, S->q, R_eval, S->d_energy, S->d_dipole);
+  launch_graph_reduce(st, S->n_graphs, S->d_graph_start, S->e_atom, S->q, R_eval, S->d_energy, S->d_dipole, S->n, S->red_scratch);
   if (S->sorted) {
     UnsortArgs A{{S->e_atom, S->q, S->h, S->e_zbl, S->e_coul, S->e_disp, nullptr},
                  {S->u_e_atom, S->u_q, S->u_h, S->u_zbl, S->u_coul, S->u_disp, nullptr}};

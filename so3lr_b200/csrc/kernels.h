@@ -113,12 +113,14 @@ void launch_pair_lr_owned(cudaStream_t s, const LrParams& P, const Cell& cell, i
                           float* gq, float* gh, float* e_coul, float* e_disp, float* virial = nullptr);
 // q = q_raw + (Q_g - sum_g q_raw) / n_g ; h = |hv| ; and the transposed operation for the cotangents
 // (atoms of one graph are contiguous: graph g owns atoms graph_start[g] .. graph_start[g+1]-1)
+// n_atoms / scratch (optional, 4 * 296 doubles): a single large structure is spread over many CTAs instead of one.
 void launch_charge_conserve(cudaStream_t s, int n_graphs, const int* graph_start, const float* q_raw,
-                            const float* total_charge, const float* hv, float* q, float* h);
-void launch_charge_conserve_bwd(cudaStream_t s, int n_graphs, const int* graph_start, const float* gq, float* gq_raw);
+                            const float* total_charge, const float* hv, float* q, float* h, int n_atoms = 0, double* scratch = nullptr);
+void launch_charge_conserve_bwd(cudaStream_t s, int n_graphs, const int* graph_start, const float* gq, float* gq_raw, int n_atoms = 0,
+                                double* scratch = nullptr);
 // per-graph energy (double) and dipole sums
 void launch_graph_reduce(cudaStream_t s, int n_graphs, const int* graph_start, const float* e_atom, const float* q,
-                         const float* R, double* e_graph, float* dipole);
+                         const float* R, double* e_graph, float* dipole, int n_atoms = 0, double* scratch = nullptr);
 
 // ---- nlist.cu ----
 struct NeighborListDev {

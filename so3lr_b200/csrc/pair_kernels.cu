@@ -265,6 +265,82 @@ __global__ void graph_reduce_kernel(int n_graphs, const int* __restrict__ graph_
   }
 }
 
+// ---- one structure with many atoms: the same three operations spread over many CTAs (sums in double, fixed order) ----
+constexpr int kWideBlocks = 296;      // two CTAs per SM
+constexpr int kWideMinAtoms = 16384;
+
+__device__ double block_sum_double_256(double v, double* sh) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  double s = 0.0;
+  if (threadIdx.x == 0)
+    for (int w = 0; w < 8; ++w) s += sh[w];
+  __syncthreads();
+  return s;       // valid in thread 0
+}
+
+// partials[b][0] = sum a ; with R: partials[b][1..3] = sum q R
+__global__ void __launch_bounds__(256) wide_partial_kernel(int n, const float* __restrict__ a, const float* __restrict__ q,
+                                                           const float* __restrict__ R, double* __restrict__ partials) {
+  __shared__ double sh[8];
+  double v[4] = {0.0, 0.0, 0.0, 0.0};
+  for (int i = blockIdx.x * 256 + threadIdx.x; i < n; i += gridDim.x * 256) {
+    v[0] += (double)a[i];
+    if (R) {
+      const float qa = q[i];
+      v[1] += (double)(qa * R[3 * (size_t)i]); v[2] += (double)(qa * R[3 * (size_t)i + 1]); v[3] += (double)(qa * R[3 * (size_t)i + 2]);
+    }
+  }
+  for (int k = 0; k < (R ? 4 : 1); ++k) {
+    const double s = block_sum_double_256(v[k], sh);
+    if (threadIdx.x == 0) partials[4 * blockIdx.x + k] = s;
+  }
+}
+
+__device__ double wide_total(const double* __restrict__ partials, int n_blocks, int k, double* sh) {
+  // every CTA forms the same total from the same partials in the same order
+  double v = 0.0;
+  for (int b = threadIdx.x; b < n_blocks; b += 256) v += partials[4 * b + k];
+  const double s = block_sum_double_256(v, sh);
+  __shared__ double total;
+  if (threadIdx.x == 0) total = s;
+  __syncthreads();
+  return total;
+}
+
+__global__ void __launch_bounds__(256) charge_conserve_wide_kernel(int n, const float* __restrict__ q_raw, const float* __restrict__ total_charge,
+                                                                   const float* __restrict__ hv, float* __restrict__ q, float* __restrict__ h,
+                                                                   const double* __restrict__ partials, int n_blocks) {
+  __shared__ double sh[8];
+  const float Q = total_charge ? total_charge[0] : 0.f;
+  const float corr = (Q - (float)wide_total(partials, n_blocks, 0, sh)) / (float)n;
+  for (int i = blockIdx.x * 256 + threadIdx.x; i < n; i += gridDim.x * 256) {
+    q[i] = q_raw[i] + corr;
+    h[i] = fabsf(hv[i]);
+  }
+}
+
+__global__ void __launch_bounds__(256) charge_conserve_bwd_wide_kernel(int n, const float* __restrict__ gq, float* __restrict__ gq_raw,
+                                                                       const double* __restrict__ partials, int n_blocks) {
+  __shared__ double sh[8];
+  const float mean = (float)wide_total(partials, n_blocks, 0, sh) / (float)n;
+  for (int i = blockIdx.x * 256 + threadIdx.x; i < n; i += gridDim.x * 256) gq_raw[i] = gq[i] - mean;
+}
+
+__global__ void __launch_bounds__(256) graph_reduce_wide_kernel(const double* __restrict__ partials, int n_blocks, int with_dipole,
+                                                                double* __restrict__ e_graph, float* __restrict__ dipole) {
+  __shared__ double sh[8];
+  for (int k = 0; k < (with_dipole ? 4 : 1); ++k) {
+    const double t = wide_total(partials, n_blocks, k, sh);
+    if (threadIdx.x == 0) {
+      if (k == 0) e_graph[0] = t;
+      else if (dipole) dipole[k - 1] = (float)t;
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace
 
 void launch_sr_geometry_zbl(cudaStream_t s, const ModelDev& M, const Cell& cell, int n, long long n_edges, const int* edge_i,
@@ -301,17 +377,36 @@ void launch_pair_lr_owned(cudaStream_t s, const LrParams& P, const Cell& cell, i
 }
 
 void launch_charge_conserve(cudaStream_t s, int n_graphs, const int* graph_start, const float* q_raw,
-                            const float* total_charge, const float* hv, float* q, float* h) {
+                            const float* total_charge, const float* hv, float* q, float* h, int n_atoms, double* scratch) {
   if (n_graphs <= 0) return;
+  if (n_graphs == 1 && scratch && n_atoms >= kWideMinAtoms) {
+    wide_partial_kernel<<<kWideBlocks, 256, 0, s>>>(n_atoms, q_raw, nullptr, nullptr, scratch);
+    charge_conserve_wide_kernel<<<kWideBlocks, 256, 0, s>>>(n_atoms, q_raw, total_charge, hv, q, h, scratch, kWideBlocks);
+    count_launch(2);
+    return;
+  }
   { charge_conserve_kernel<<<n_graphs, 256, 0, s>>>(n_graphs, graph_start, q_raw, total_charge, hv, q, h); count_launch(); }
 }
-void launch_charge_conserve_bwd(cudaStream_t s, int n_graphs, const int* graph_start, const float* gq, float* gq_raw) {
+void launch_charge_conserve_bwd(cudaStream_t s, int n_graphs, const int* graph_start, const float* gq, float* gq_raw, int n_atoms,
+                                double* scratch) {
   if (n_graphs <= 0) return;
+  if (n_graphs == 1 && scratch && n_atoms >= kWideMinAtoms) {
+    wide_partial_kernel<<<kWideBlocks, 256, 0, s>>>(n_atoms, gq, nullptr, nullptr, scratch);
+    charge_conserve_bwd_wide_kernel<<<kWideBlocks, 256, 0, s>>>(n_atoms, gq, gq_raw, scratch, kWideBlocks);
+    count_launch(2);
+    return;
+  }
   { charge_conserve_bwd_kernel<<<n_graphs, 256, 0, s>>>(n_graphs, graph_start, gq, gq_raw); count_launch(); }
 }
 void launch_graph_reduce(cudaStream_t s, int n_graphs, const int* graph_start, const float* e_atom, const float* q,
-                         const float* R, double* e_graph, float* dipole) {
+                         const float* R, double* e_graph, float* dipole, int n_atoms, double* scratch) {
   if (n_graphs <= 0) return;
+  if (n_graphs == 1 && scratch && n_atoms >= kWideMinAtoms) {
+    wide_partial_kernel<<<kWideBlocks, 256, 0, s>>>(n_atoms, e_atom, q, R, scratch);
+    graph_reduce_wide_kernel<<<1, 256, 0, s>>>(scratch, kWideBlocks, R ? 1 : 0, e_graph, dipole);
+    count_launch(2);
+    return;
+  }
   { graph_reduce_kernel<<<n_graphs, 256, 0, s>>>(n_graphs, graph_start, e_atom, q, R, e_graph, dipole); count_launch(); }
 }
 
