@@ -88,14 +88,14 @@ def load_params(path: str = DEFAULT_BLOB) -> Dict[str, torch.Tensor]:
 # ----------------------------------------------------------------------------------------------------------
 def min_image(dR: np.ndarray, cell: Optional[np.ndarray]) -> np.ndarray:
     """Minimum-image displacement for a cell whose ROWS are the lattice vectors.  float32 in, float32 out.
-    s = dR @ inv(cell); s -= rint(s); dR = s @ cell  (the same operation order as the CUDA kernels)."""
+    k = rint(dR @ inv(cell)); dR = dR - k @ cell  (the same operation order as the CUDA kernels and as the float64 path of
+    energy_forces: the lattice translation is subtracted from dR itself, which keeps dR's precision across the boundary)."""
     if cell is None:
         return dR
     cell = np.asarray(cell, dtype=np.float32)
     inv = np.linalg.inv(cell.astype(np.float64)).astype(np.float32)
-    s = (dR[..., 0:1] * inv[0] + dR[..., 1:2] * inv[1]) + dR[..., 2:3] * inv[2]
-    s = s - np.rint(s)
-    return (s[..., 0:1] * cell[0] + s[..., 1:2] * cell[1]) + s[..., 2:3] * cell[2]
+    k = np.rint((dR[..., 0:1] * inv[0] + dR[..., 1:2] * inv[1]) + dR[..., 2:3] * inv[2])
+    return dR - ((k[..., 0:1] * cell[0] + k[..., 1:2] * cell[1]) + k[..., 2:3] * cell[2])
 
 
 def neighbor_list(R: np.ndarray, cell: Optional[np.ndarray], cutoff: float, ordered: bool = False, chunk: int = 512):

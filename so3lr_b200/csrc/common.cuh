@@ -185,25 +185,26 @@ struct Cell {
   int periodic;   // 0: free space
 };
 
-// minimum-image displacement, identical operation order to oracle.min_image
+// minimum-image displacement: dR - round(dR h^-1) h, the operation order of oracle.min_image.  The lattice translation is
+// subtracted from dR directly (it is not rebuilt from the fractional remainder), so the result keeps the full float32
+// precision of dR however many cells the two positions are apart; for an orthorhombic cell the subtraction is exact up to
+// one rounding.
 SO3LR_HD void min_image(const Cell& c, float& dx, float& dy, float& dz) {
   if (!c.periodic) return;
 #ifdef __CUDA_ARCH__
-  float s0 = __fadd_rn(__fadd_rn(__fmul_rn(dx, c.hinv[0]), __fmul_rn(dy, c.hinv[3])), __fmul_rn(dz, c.hinv[6]));
-  float s1 = __fadd_rn(__fadd_rn(__fmul_rn(dx, c.hinv[1]), __fmul_rn(dy, c.hinv[4])), __fmul_rn(dz, c.hinv[7]));
-  float s2 = __fadd_rn(__fadd_rn(__fmul_rn(dx, c.hinv[2]), __fmul_rn(dy, c.hinv[5])), __fmul_rn(dz, c.hinv[8]));
-  s0 = __fsub_rn(s0, rintf(s0)); s1 = __fsub_rn(s1, rintf(s1)); s2 = __fsub_rn(s2, rintf(s2));
-  dx = __fadd_rn(__fadd_rn(__fmul_rn(s0, c.h[0]), __fmul_rn(s1, c.h[3])), __fmul_rn(s2, c.h[6]));
-  dy = __fadd_rn(__fadd_rn(__fmul_rn(s0, c.h[1]), __fmul_rn(s1, c.h[4])), __fmul_rn(s2, c.h[7]));
-  dz = __fadd_rn(__fadd_rn(__fmul_rn(s0, c.h[2]), __fmul_rn(s1, c.h[5])), __fmul_rn(s2, c.h[8]));
+  const float k0 = rintf(__fadd_rn(__fadd_rn(__fmul_rn(dx, c.hinv[0]), __fmul_rn(dy, c.hinv[3])), __fmul_rn(dz, c.hinv[6])));
+  const float k1 = rintf(__fadd_rn(__fadd_rn(__fmul_rn(dx, c.hinv[1]), __fmul_rn(dy, c.hinv[4])), __fmul_rn(dz, c.hinv[7])));
+  const float k2 = rintf(__fadd_rn(__fadd_rn(__fmul_rn(dx, c.hinv[2]), __fmul_rn(dy, c.hinv[5])), __fmul_rn(dz, c.hinv[8])));
+  dx = __fsub_rn(dx, __fadd_rn(__fadd_rn(__fmul_rn(k0, c.h[0]), __fmul_rn(k1, c.h[3])), __fmul_rn(k2, c.h[6])));
+  dy = __fsub_rn(dy, __fadd_rn(__fadd_rn(__fmul_rn(k0, c.h[1]), __fmul_rn(k1, c.h[4])), __fmul_rn(k2, c.h[7])));
+  dz = __fsub_rn(dz, __fadd_rn(__fadd_rn(__fmul_rn(k0, c.h[2]), __fmul_rn(k1, c.h[5])), __fmul_rn(k2, c.h[8])));
 #else
-  float s0 = (dx * c.hinv[0] + dy * c.hinv[3]) + dz * c.hinv[6];
-  float s1 = (dx * c.hinv[1] + dy * c.hinv[4]) + dz * c.hinv[7];
-  float s2 = (dx * c.hinv[2] + dy * c.hinv[5]) + dz * c.hinv[8];
-  s0 -= rintf(s0); s1 -= rintf(s1); s2 -= rintf(s2);
-  dx = (s0 * c.h[0] + s1 * c.h[3]) + s2 * c.h[6];
-  dy = (s0 * c.h[1] + s1 * c.h[4]) + s2 * c.h[7];
-  dz = (s0 * c.h[2] + s1 * c.h[5]) + s2 * c.h[8];
+  const float k0 = rintf((dx * c.hinv[0] + dy * c.hinv[3]) + dz * c.hinv[6]);
+  const float k1 = rintf((dx * c.hinv[1] + dy * c.hinv[4]) + dz * c.hinv[7]);
+  const float k2 = rintf((dx * c.hinv[2] + dy * c.hinv[5]) + dz * c.hinv[8]);
+  dx = dx - ((k0 * c.h[0] + k1 * c.h[3]) + k2 * c.h[6]);
+  dy = dy - ((k0 * c.h[1] + k1 * c.h[4]) + k2 * c.h[7]);
+  dz = dz - ((k0 * c.h[2] + k1 * c.h[5]) + k2 * c.h[8]);
 #endif
 }
 
