@@ -176,11 +176,11 @@ class NeighborFn:
         return b.T.copy()   # jax-md boxes hold lattice vectors as columns
 
     def _cartesian(self, R, box):
-        R = torch.as_tensor(R, dtype=torch.float32, device=self.device)
+        R = (torch.as_tensor(R) if not torch.is_tensor(R) else R.detach()).to(self.device)
         cell = self._cell(box)
         if cell is not None and self.fractional:
-            R = R @ torch.tensor(cell, dtype=torch.float32, device=self.device)
-        return R.contiguous(), cell
+            R = R.double() @ torch.tensor(cell, dtype=torch.float64, device=self.device)
+        return R.float().contiguous(), cell
 
     def _system(self, n, cell):
         key = (n, None if cell is None else cell.tobytes())
@@ -204,12 +204,21 @@ class NeighborFn:
         return NeighborList(self, idx, count, ovf, Rc)
 
     def _update(self, nbrs, R, box):
+        """jax-md's update protocol: the list is kept while no atom has moved further than dr_threshold / 2 since it was
+        built, also when the box has changed meanwhile (an NPT run rescales it every step, so3lr/cli/so3lr_md.py:1270-1282:
+        the Cartesian positions carry the rescaling, so the same test covers it); otherwise it is rebuilt into the same
+        capacity and an overflow is flagged, never raised."""
         Rc, cell = self._cartesian(R, box)
-        s = self._system(Rc.shape[0], cell)
-        if self.dr_threshold > 0 and cell is not None and self._cell_key[1] == cell.tobytes():
+        n = Rc.shape[0]
+        same_kind = self._sys is not None and self._cell_key[0] == n and (cell is None) == (self._cell_key[1] is None)
+        if self.dr_threshold > 0 and same_kind and nbrs.reference_position.shape == Rc.shape:
             moved = (Rc - nbrs.reference_position).square().sum(-1).max() > (0.5 * self.dr_threshold) ** 2
             if not bool(moved):
+                if cell is not None and self._cell_key[1] != cell.tobytes():
+                    self._sys.rescale_cell(cell)
+                    self._cell_key = (n, cell.tobytes())
                 return nbrs
+        s = self._system(n, cell)
         idx, count, ovf = s.neighbor_list(Rc, 1, nbrs.capacity)
         return NeighborList(self, idx, count, ovf or nbrs.did_buffer_overflow, Rc)
 
@@ -235,40 +244,73 @@ def _min_image(dR, cell_t):
     return dR - torch.round(s) @ cell_t
 
 
+class _Transform(torch.autograd.Function):
+    """Fractional -> Cartesian positions with jax-md's convention for the derivative (jax_md.space.transform has a custom
+    JVP whose tangent is dR + transform(dbox, R)): the gradient with respect to fractional positions is the real-space one,
+    which is why the reference compares `quantity.force(energy_fn)(R0_fractional, ...)` with forces in eV/A directly
+    (tests/test_jaxmd.py:86-101)."""
+
+    @staticmethod
+    def forward(ctx, R, cell_t):
+        return R @ cell_t
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
 def neighbor_list_featurizer(displacement_fn, species, fractional_coordinates=True, device=None):
-    """so3lr/jaxmd_utils.py:11-77: endpoints gather, minimum-image displacement, Graph assembly."""
+    """so3lr/jaxmd_utils.py:11-77: endpoints gather, minimum-image displacement, Graph assembly.  Positions and box keep the
+    precision they are given in (float64 positions in a 1000 A box lose nothing); the displacements are handed to the
+    float32 kernels."""
     dev = _dev(device)
     species_t = torch.as_tensor(np.asarray(species), dtype=torch.int32, device=dev)
 
     def featurize(R, neighbor, neighbor_lr, **kwargs):
+        R = torch.as_tensor(R, device=dev) if not torch.is_tensor(R) else R.to(dev)
+        if R.dtype not in (torch.float32, torch.float64):
+            R = R.float()
         n = R.shape[0]
         box = kwargs.get("box")
         cell_t = None
         if box is not None:
-            b = torch.as_tensor(box, dtype=torch.float32, device=dev)
+            b = torch.as_tensor(box, dtype=R.dtype, device=dev)
             if b.shape == (3, 3):
                 cell_t = b.T
             elif b.shape == (3,):
                 cell_t = torch.diag(b)
             elif b.shape == (1,) or b.ndim == 0:
-                cell_t = torch.eye(3, device=dev) * b.reshape(-1)[0]
+                cell_t = torch.eye(3, dtype=R.dtype, device=dev) * b.reshape(-1)[0]
             else:
                 raise ValueError(f"Invalid box shape {tuple(b.shape)}. Expected (3, 3), (3,), or (1,).")
         for k in ("k_grid", "k_smearing", "perturbation"):
             if kwargs.get(k) is not None:
                 raise NotImplementedError(f"`{k}` is not supported by this library")
-        Rc = R @ cell_t if (cell_t is not None and fractional_coordinates) else R
+        Rc = _Transform.apply(R, cell_t) if (cell_t is not None and fractional_coordinates) else R
+        neighbor, neighbor_lr = torch.as_tensor(neighbor, device=dev), torch.as_tensor(neighbor_lr, device=dev)
         idx_i, idx_j = neighbor[0].long(), neighbor[1].long()
         idx_i_lr, idx_j_lr = neighbor_lr[0].long(), neighbor_lr[1].long()
         cl = lambda a: a.clamp(max=n - 1)   # JAX gathers clamp the padding index N to N-1
         # the kernels take dR = R_j - R_i; the energy does not depend on the sign convention
-        dR = _min_image(Rc[cl(idx_j)] - Rc[cl(idx_i)], cell_t)
-        dR_lr = _min_image(Rc[cl(idx_j_lr)] - Rc[cl(idx_i_lr)], cell_t)
+        dR = _min_image(Rc[cl(idx_j)] - Rc[cl(idx_i)], cell_t).float()
+        dR_lr = _min_image(Rc[cl(idx_j_lr)] - Rc[cl(idx_i_lr)], cell_t).float()
         return Graph(positions=None, nodes=species_t, edges=dR, centers=neighbor[0], others=neighbor[1], mask=None,
                      total_charge=torch.zeros(1), num_unpaired_electrons=torch.zeros(1), edges_lr=dR_lr, idx_i_lr=neighbor_lr[0],
                      idx_j_lr=neighbor_lr[1], cell=cell_t)
 
     return featurize
+
+
+def force(energy_fn):
+    """jax_md.quantity.force: R, **kwargs -> -dE/dR (README.md:241, tests/test_jaxmd.py:81 of the reference)."""
+
+    def force_fn(R, **kwargs):
+        Rg = (torch.as_tensor(R) if not torch.is_tensor(R) else R).detach().clone().requires_grad_(True)
+        E = energy_fn(Rg, **kwargs)
+        (g,) = torch.autograd.grad(E, Rg)
+        return -g
+
+    return force_fn
 
 
 def to_jax_md(potential, displacement_or_metric, box_size, species=None, dr_threshold: float = 0.0, capacity_multiplier: float = 1.25,

@@ -1,0 +1,200 @@
+"""The reference-facing Python surface (so3lr_b200.api) exercised the way the reference's own tests exercise theirs
+(tests/test_jaxmd.py, tests/test_ase.py, examples/evaluate_so3lr_on_dataset.ipynb), against the reference's golden vectors.
+
+Tolerances: the reference's tests run in float64 with atol 1e-6 on the energy and 1e-4 (5e-4 for water) on the forces; the
+kernels here compute in float32, so the energy is compared to 1e-5 relative and the forces to the same 1e-4 / 5e-4.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import so3lr_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+lr_cutoff, lr_cutoff_damp = 12.0, 2.0
+capacity_multiplier, buffer_size_multiplier_sr, buffer_size_multiplier_lr, minimum_cell_size_multiplier_sr = 1.25, 1.25, 1.25, 1.0
+
+
+def _potential():
+    from so3lr_b200 import So3lrPotential
+    return So3lrPotential(lr_cutoff=lr_cutoff, dispersion_energy_cutoff_lr_damping=lr_cutoff_damp, dtype=np.float32)
+
+
+def _check(g, name, energy, forces, f_tol=1e-4):
+    target_e, target_f = float(g[f"{name}_energy_jaxmd"]), g[f"{name}_forces_jaxmd"]
+    assert abs(float(energy) - target_e) < 1e-5 * abs(target_e)
+    np.testing.assert_allclose(target_f, forces.detach().cpu().numpy(), atol=f_tol)
+    with np.testing.assert_raises(AssertionError):
+        np.testing.assert_allclose(target_f, np.zeros_like(target_f))
+
+
+@pytest.mark.parametrize("name", ["atat", "dha", "bb"])
+def test_molecules_with_box(reference_goldens, name):
+    """tests/test_jaxmd.py:26-107: the molecule in the middle of a 999.999 A box, fractional coordinates."""
+    from so3lr_b200 import api, to_jax_md
+    g = reference_goldens
+    species = g[f"{name}_Z"]
+    box = np.array([999.999, 999.999, 999.999])
+    pos = g[f"{name}_R"] - g[f"{name}_R"].mean(0) + box / 2
+    R0 = torch.tensor(pos / box[0], dtype=torch.float64)
+    neighbor_fn, neighbor_fn_lr, energy_fn = to_jax_md(
+        potential=_potential(), displacement_or_metric=None, box_size=box, species=species,
+        capacity_multiplier=capacity_multiplier, buffer_size_multiplier_sr=buffer_size_multiplier_sr,
+        buffer_size_multiplier_lr=buffer_size_multiplier_lr, minimum_cell_size_multiplier_sr=minimum_cell_size_multiplier_sr,
+        disable_cell_list=True)
+    force_fn = api.force(energy_fn)
+    nbrs = neighbor_fn.allocate(R0, box=box)
+    nbrs_lr = neighbor_fn_lr.allocate(R0, box=box)
+    assert not nbrs.did_buffer_overflow and not nbrs_lr.did_buffer_overflow
+    energy = energy_fn(R0, neighbor=nbrs.idx, neighbor_lr=nbrs_lr.idx, box=box)
+    forces = force_fn(R0, neighbor=nbrs.idx, neighbor_lr=nbrs_lr.idx, box=box)
+    _check(g, name, energy, forces)
+
+
+@pytest.mark.parametrize("name", ["atat", "dha", "bb"])
+def test_molecules_free(reference_goldens, name):
+    """tests/test_jaxmd.py:109-185: free space, Cartesian coordinates, box None."""
+    from so3lr_b200 import api, to_jax_md
+    g = reference_goldens
+    species, box = g[f"{name}_Z"], None
+    R0 = torch.tensor(g[f"{name}_R"], dtype=torch.float64)
+    neighbor_fn, neighbor_fn_lr, energy_fn = to_jax_md(
+        potential=_potential(), displacement_or_metric=None, box_size=box, species=species,
+        capacity_multiplier=capacity_multiplier, buffer_size_multiplier_sr=buffer_size_multiplier_sr,
+        buffer_size_multiplier_lr=buffer_size_multiplier_lr, minimum_cell_size_multiplier_sr=minimum_cell_size_multiplier_sr,
+        disable_cell_list=True)
+    force_fn = api.force(energy_fn)
+    nbrs = neighbor_fn.allocate(R0, box=box)
+    nbrs_lr = neighbor_fn_lr.allocate(R0, box=box)
+    energy = energy_fn(R0, neighbor=nbrs.idx, neighbor_lr=nbrs_lr.idx, box=box)
+    forces = force_fn(R0, neighbor=nbrs.idx, neighbor_lr=nbrs_lr.idx, box=box)
+    _check(g, name, energy, forces)
+    # has_aux: per-atom energies and the observables of the potential (so3lr/jaxmd_utils.py:138-141)
+    e_atom, aux = energy_fn(R0, neighbor=nbrs.idx, neighbor_lr=nbrs_lr.idx, box=box, has_aux=True)
+    assert e_atom.shape == (len(species),) and abs(float(e_atom.sum()) - float(energy)) < 1e-4
+    for key in ("partial_charges", "hirshfeld_ratios", "zbl_repulsion", "electrostatic_energy", "dispersion_energy"):
+        assert aux[key].shape == (len(species),)
+    assert abs(float(aux["partial_charges"].sum())) < 1e-4
+
+
+def test_water_periodic(reference_goldens):
+    """tests/test_jaxmd.py:188-258: the 1536-atom water box, fractional coordinates, box given by its three edges."""
+    from so3lr_b200 import api, to_jax_md
+    g = reference_goldens
+    species = g["water_Z"]
+    box = np.diag(g["water_cell"].T).copy()
+    R0 = torch.tensor(g["water_R"] / box, dtype=torch.float64)
+    neighbor_fn, neighbor_fn_lr, energy_fn = to_jax_md(
+        potential=_potential(), displacement_or_metric=None, box_size=box, species=species,
+        capacity_multiplier=capacity_multiplier, buffer_size_multiplier_sr=buffer_size_multiplier_sr,
+        buffer_size_multiplier_lr=buffer_size_multiplier_lr, minimum_cell_size_multiplier_sr=minimum_cell_size_multiplier_sr)
+    force_fn = api.force(energy_fn)
+    nbrs = neighbor_fn.allocate(R0, box=box)
+    nbrs_lr = neighbor_fn_lr.allocate(R0, box=box)
+    assert nbrs.idx.shape[0] == 2 and nbrs.idx.dtype == torch.int32
+    assert int((nbrs.idx[0] < len(species)).sum()) == 59280 and int((nbrs_lr.idx[0] < len(species)).sum()) == 557360
+    assert int(nbrs.idx.max()) == len(species)                       # padded with N
+    energy = energy_fn(R0, neighbor=nbrs.idx, neighbor_lr=nbrs_lr.idx, box=box)
+    forces = force_fn(R0, neighbor=nbrs.idx, neighbor_lr=nbrs_lr.idx, box=box)
+    _check(g, "water", energy, forces, f_tol=5e-4)
+
+
+def test_neighbor_list_protocol(reference_goldens):
+    """allocate / update / overflow as the reference's MD loop uses them (so3lr/cli/so3lr_md.py:836-877, 1143-1152), and
+    the box that an NPT run passes to every update (:1270-1282)."""
+    from so3lr_b200 import neighbor_list
+    g = reference_goldens
+    n = len(g["water_Z"])
+    box = np.diag(g["water_cell"].T).copy()
+    frac = torch.tensor(g["water_R"] / box, dtype=torch.float64)
+    fn = neighbor_list(None, box, 4.5, dr_threshold=0.5, capacity_multiplier=1.25, fractional_coordinates=True, format=1)
+    nbrs = fn.allocate(frac, box=box)
+    assert not nbrs.did_buffer_overflow and nbrs.capacity >= int(1.25 * nbrs.count)
+    ref_i, ref_j = O.neighbor_list(g["water_R"].astype(np.float32), g["water_cell"], 5.0, ordered=False)
+    got = nbrs.idx[:, : nbrs.count].cpu().numpy()
+    order = np.lexsort((got[1], got[0]))
+    np.testing.assert_array_equal(got[:, order], np.stack([ref_i, ref_j]).astype(np.int32))      # list radius = cutoff + threshold
+    # a small move and a slightly rescaled box (same fractional coordinates): the list object is kept
+    rng = np.random.default_rng(0)
+    same = nbrs.update(frac + torch.tensor(rng.normal(scale=0.02, size=frac.shape) / box), box=box * (1.0 + 1e-5))
+    assert same is nbrs
+    # a move beyond half the threshold: rebuilt into the same capacity
+    far = frac.clone(); far[0, 0] += 0.4 / box[0]
+    nb2 = nbrs.update(far, box=box)
+    assert nb2 is not nbrs and nb2.capacity == nbrs.capacity and not nb2.did_buffer_overflow
+    # a box 5 % larger: every atom moved, the list is rebuilt and equals a fresh one at that box
+    big = box * 1.05
+    nb3 = nb2.update(frac, box=big)
+    fresh = neighbor_list(None, big, 4.5, dr_threshold=0.5, fractional_coordinates=True, format=1).allocate(frac, box=big)
+    assert nb3.count == fresh.count
+    a, b = nb3.idx[:, : nb3.count].cpu().numpy(), fresh.idx[:, : fresh.count].cpu().numpy()
+    np.testing.assert_array_equal(a[:, np.lexsort((a[1], a[0]))], b[:, np.lexsort((b[1], b[0]))])
+    # overflow is a flag, not an exception: a denser configuration does not fit the old capacity
+    small = box * 0.8
+    nb4 = nb3.update(frac, box=small)
+    assert nb4.did_buffer_overflow and nb4.capacity == nbrs.capacity
+    # ordered format keeps i < j only
+    fn_lr = neighbor_list(None, box, 12.0, fractional_coordinates=True, format=2)
+    lr = fn_lr.allocate(frac, box=box)
+    v = lr.idx[:, : lr.count]
+    assert lr.count == 557360 and bool((v[0] < v[1]).all()) and int(lr.idx[:, lr.count:].min()) == n
+
+
+class _Atoms:
+    def __init__(self, Z, R, cell=None):
+        self.Z, self.R, self.cell = Z, R, cell
+
+    def get_atomic_numbers(self): return self.Z
+    def get_positions(self): return self.R
+    def get_cell(self): return np.zeros((3, 3)) if self.cell is None else self.cell
+    def get_pbc(self): return np.array([self.cell is not None] * 3)
+
+
+@pytest.mark.parametrize("name", ["atat", "dha", "bb", "water"])
+def test_ase_calculator(reference_goldens, name):
+    """tests/test_ase.py:9-142: energy and forces of the four structures through the calculator."""
+    from so3lr_b200 import So3lrCalculator
+    g = reference_goldens
+    cell = np.asarray(g["water_cell"], dtype=np.float64) if name == "water" else None
+    atoms = _Atoms(g[f"{name}_Z"], np.asarray(g[f"{name}_R"], dtype=np.float64), cell)
+    calc = So3lrCalculator(lr_cutoff=lr_cutoff, dispersion_energy_cutoff_lr_damping=lr_cutoff_damp)
+    energy, forces = calc.get_potential_energy(atoms), calc.get_forces(atoms)
+    target_e, target_f = float(g[f"{name}_energy_ase"]), g[f"{name}_forces_ase"]
+    assert abs(energy - target_e) < 1e-5 * abs(target_e)
+    np.testing.assert_allclose(target_f, forces, atol=5e-4 if name == "water" else 1e-4)
+
+
+def test_batched_calculator_matches_oracle(oracle_params):
+    """so3lr/base_calculator.py:57-122 as driven by examples/evaluate_so3lr_on_dataset.ipynb: a padded batch of molecules
+    with directed long-range lists; the last graph and the last node are padding and come back as zeros."""
+    from so3lr_b200 import So3lr
+    from so3lr_b200 import workloads as W
+    Z, R, gs = W.molecule_batch(5, seed=1001)
+    R = np.asarray(R, dtype=np.float32)
+    n, n_graph = len(Z), len(gs) - 1
+    seg = np.repeat(np.arange(n_graph), np.diff(gs))
+    ii, jj = O.neighbor_list(R, None, 4.5, ordered=False)
+    keep = seg[ii] == seg[jj]
+    ii, jj = ii[keep], jj[keep]
+    il = np.concatenate([np.repeat(np.arange(a, b), b - a) for a, b in zip(gs[:-1], gs[1:])])
+    jl = np.concatenate([np.tile(np.arange(a, b), b - a) for a, b in zip(gs[:-1], gs[1:])])
+    keep = il != jl
+    il, jl = il[keep], jl[keep]
+    pad = lambda a, m: np.concatenate([a, np.full(m - len(a), n)]).astype(np.int32)        # padding entries carry index n
+    inputs = dict(positions=np.concatenate([R, np.zeros((1, 3), np.float32)]), atomic_numbers=np.concatenate([Z, [1]]),
+                  idx_i=pad(ii, len(ii) + 7), idx_j=pad(jj, len(jj) + 7), idx_i_lr=pad(il, len(il) + 5), idx_j_lr=pad(jl, len(jl) + 5),
+                  cell=None, total_charge=np.zeros(n_graph + 1), num_unpaired_electrons=np.zeros(n_graph + 1),
+                  batch_segments=np.concatenate([seg, [n_graph]]), node_mask=np.concatenate([np.ones(n, bool), [False]]),
+                  graph_mask=np.concatenate([np.ones(n_graph, bool), [False]]))
+    # padding indices point at the padding node (index n of n + 1 nodes), as jraph-style padding does
+    out = So3lr(lr_cutoff=1000.0, dispersion_energy_cutoff_lr_damping=lr_cutoff_damp)(inputs)
+    ref = O.energy_forces(oracle_params, R.astype(np.float64), Z, None, cutoff_lr=1000.0, damping=lr_cutoff_damp, lr_format="sparse",
+                          batch_segments=seg, num_graphs=n_graph)
+    assert out["energy"].shape == (n_graph + 1,) and float(out["energy"][-1]) == 0.0
+    np.testing.assert_allclose(out["energy"][:-1].cpu().numpy(), ref["energy_per_graph"], rtol=1e-5)
+    np.testing.assert_allclose(out["forces"][:-1].cpu().numpy(), ref["forces"], atol=1e-4)
+    assert float(out["forces"][-1].abs().max()) == 0.0
+    np.testing.assert_allclose(out["dipole_vec"][:-1].cpu().numpy(), ref["dipole_vec"], atol=5e-5)
+    np.testing.assert_allclose(out["hirshfeld_ratios"][:-1].cpu().numpy(), ref["hirshfeld_ratios"], atol=1e-5)
+    assert float(out["hirshfeld_ratios"][-1]) == 0.0
