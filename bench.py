@@ -39,6 +39,8 @@ WORKLOADS = {
 # step body each workload is posed with: thermostatted (Nose-Hoover chain of length 3, 2 chain steps, 3 Suzuki-Yoshida
 # factors, tau = 100 dt, 300 K) or plain velocity Verlet
 ENSEMBLE = {"water_192": "nvt", "water_24k": "nvt", "water_98k": "nvt", "water_1m": "nve"}
+MOLECULE_BATCHES = {"molecules_512": (512, 1001)}      # independent gas-phase molecules of 10-40 atoms, all-pairs long range
+BAR = 6.241509074e-7                                    # eV / A^3
 KT_300 = 300.0 * 8.617333262e-5
 
 
@@ -154,6 +156,8 @@ def run_b200(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    if args.workload in MOLECULE_BATCHES:
+        return run_molecules(args, rank, world, local_rank)
     n_mol, box, seed = WORKLOADS[args.workload]
     if world > 1:
         from so3lr_b200 import domain
@@ -178,6 +182,13 @@ def run_b200(args, rank, world, local_rank):
         from so3lr_b200.engine import nhc_state
         chain = nhc_state(dev)
         step = lambda: sysm.nvt(1, dt, KT_300, 100.0 * dt, md, Rd, Vd, Fd, chain, chain_length=3, chain_steps=2, sy_steps=3)
+    elif ensemble == "npt":
+        # 300 K, 1 bar, thermostat tau = 100 dt, barostat tau = 1000 dt (the reference's defaults)
+        from so3lr_b200.engine import npt_state
+        sysm.enable_virial(True)
+        Fd = sysm.compute(Rd)["forces"].clone()
+        npt = npt_state(dev)
+        step = lambda: sysm.npt(1, dt, KT_300, 1.0 * BAR, 100.0 * dt, 1000.0 * dt, md, Rd, Vd, Fd, npt, cell)
     else:
         step = lambda: sysm.nve(1, dt, md, Rd, Vd, Fd)
 
@@ -254,7 +265,9 @@ def run_b200(args, rank, world, local_rank):
             "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"{args.workload}: {N} atoms periodic water, cutoffs 4.5/12 A, skin {skin} A, "
-                                   + ("NVT (Nose-Hoover chain 3) at 300 K, dt 0.5 fs" if ensemble == "nvt" else "NVE dt 0.5 fs from 300 K"),
+                                   + {"nvt": "NVT (Nose-Hoover chain 3) at 300 K, dt 0.5 fs",
+                                      "npt": "NPT (MTK barostat, Nose-Hoover chains 3) at 300 K and 1 bar, dt 0.5 fs",
+                                      "nve": "NVE dt 0.5 fs from 300 K"}[ensemble],
                        "atoms": N, "sr_list_edges": E_list, "lr_list_pairs": P_list,
                        "list_rebuilds_in_timed_steps": st1["rebuilds"] - st0["rebuilds"],
                        "l2_policy": ("inputs larger than L2: a step streams about 18 kB per atom (q/k/v rows 2.5 kB per layer, "
@@ -262,6 +275,97 @@ def run_b200(args, rank, world, local_rank):
                                      else "inputs smaller than L2; no flush"),
                        "ns_per_day": round(args.steps / (ms * 1e-3) * 0.0432, 3)},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu}
+    print(json.dumps(line), flush=True)
+
+
+def run_molecules(args, rank, world, local_rank):
+    """Batch of independent molecules (energy, forces, dipole, Hirshfeld ratios per structure; all-pairs long range).  A step
+    is one evaluation of the whole batch with freshly built neighbor lists (skin 0), as when a new batch arrives; with N
+    ranks every rank evaluates its contiguous share of the graphs and nothing is exchanged."""
+    import torch
+    import torch.distributed as dist
+    from so3lr_b200 import batch as B
+    from so3lr_b200 import workloads as W
+    dev = torch.device("cuda", local_rank)
+    n_graphs, seed = MOLECULE_BATCHES[args.workload]
+    Z, R, gs = W.molecule_batch(n_graphs, seed)
+    R = np.asarray(R, dtype=np.float32)
+    N = len(Z)
+    sb = B.ShardedBatch(Z, gs, world, rank, lr_cutoff=1000.0, damping=2.0, device=local_rank)
+    sysm = sb.system
+    Rd = torch.tensor(R[sb.a0:sb.a1], device=dev)
+    sampler = ClockSampler(list(range(world))) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    for _ in range(args.warmup):
+        out = sysm.compute(Rd)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    st0 = sysm.stats()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    if sampler:
+        sampler.begin()
+    ev[0].record()
+    for _ in range(args.steps):
+        out = sysm.compute(Rd)
+    ev[1].record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    if sampler:
+        sampler.end()
+    clocks = sampler.stop() if sampler else None
+    ms = torch.tensor([ev[0].elapsed_time(ev[1])], dtype=torch.float64, device=dev)
+    launches = torch.tensor([float(sysm.stats()["launches"] - st0["launches"])], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(launches, op=dist.ReduceOp.SUM)
+    ms = float(ms)
+    sysm.profile(True)
+    for _ in range(args.steps):
+        sysm.compute(Rd)
+    prof = sysm.profile_read()
+    sysm.profile(False)
+    st = sysm.stats()
+    # end to end: positions of the whole batch in host memory, results back on the host
+    sb.compute_host(R)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        res = sb.compute_host(R)
+    torch.cuda.synchronize()
+    t_e2e = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
+    t_e2e = float(t_e2e)
+    if rank != 0:
+        return
+    n_loc = sb.a1 - sb.a0
+    groups = {k: v for k, v in prof.items() if v[1] > 0}
+    top = max((g for g in groups if algorithmic_bytes(g, n_loc, st["edges"], st["pairs"])), key=lambda g: groups[g][0])
+    t_launch = groups[top][0] / groups[top][1]
+    ab = algorithmic_bytes(top, n_loc, st["edges"], st["pairs"])
+    peak, kind = _peaks()
+    ach = ab / (t_launch * 1e-3) / 1e9
+    roofline = {"kernel": top, "bound": "hbm", "achieved": round(ach, 1), "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s",
+                "frac": round(ach / peak, 4), "traffic": None, "algorithmic_bytes_per_launch": ab, "ms_per_launch": round(t_launch, 4),
+                "scope": "rank 0's share of the graphs",
+                "groups_ms_per_step": {g: round(v[0] / args.steps, 4) for g, v in sorted(groups.items(), key=lambda kv: -kv[1][0])}}
+    cpu = None
+    line = {"metric": METRIC, "value": round(N * args.steps / (ms * 1e-3), 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {n_graphs} independent molecules of 10-40 atoms ({N} atoms), all-pairs long range "
+                                   "(lr cutoff 1000 A), energy + forces + dipole + Hirshfeld ratios per structure, lists rebuilt every step",
+                       "atoms": N, "graphs": n_graphs, "graphs_rank0": sb.n_graphs_local, "sr_list_edges_rank0": st["edges"],
+                       "lr_list_pairs_rank0": st["pairs"], "structures_per_s": round(n_graphs * args.steps / (ms * 1e-3), 1),
+                       "l2_policy": "inputs larger than L2: a step streams about 18 kB per atom (0.23 GB for the batch)"},
+            "e2e": {"value": round(N * args.steps / t_e2e, 1), "unit": UNIT, "h2d_bytes_per_step": N * 12,
+                    "d2h_bytes_per_step": N * 20 + n_graphs * 20, "ms_per_step": round(1e3 * t_e2e / args.steps, 3)},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu}
     print(json.dumps(line), flush=True)
 
 
@@ -317,9 +421,9 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="water_1m", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="water_1m", choices=sorted(WORKLOADS) + sorted(MOLECULE_BATCHES))
     ap.add_argument("--skin", type=float, default=1.0)
-    ap.add_argument("--ensemble", default=None, choices=["nve", "nvt"], help="step body (default: the one the workload is posed with)")
+    ap.add_argument("--ensemble", default=None, choices=["nve", "nvt", "npt"], help="step body (default: the one the workload is posed with)")
     ap.add_argument("--cpu-molecules", type=int, default=1024, help="molecules in the CPU-baseline sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the roofline kernel (from profiles/)")
@@ -327,6 +431,8 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     rank = int(os.environ.get("RANK", 0)); world = int(os.environ.get("WORLD_SIZE", 1)); local_rank = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
+        if args.workload in MOLECULE_BATCHES:
+            raise SystemExit("--impl reference times the periodic water workloads only")
         run_reference(args, rank, world)
     else:
         run_b200(args, rank, world, local_rank)
