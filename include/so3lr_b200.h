@@ -180,6 +180,20 @@ SO3LR_B200_API int so3lr_b200_system_npt(so3lr_b200_system* sys, void* stream, i
                                          double tau_t_fs, double tau_b_fs, int chain_length, int chain_steps, int sy_steps,
                                          const float* masses_dev, float* positions_dev, float* velocities_dev, float* forces_dev,
                                          double* state_dev, const float* cell0_9, float* cell_out9, double* energy_dev);
+/* The box-and-chains part of an NPT step alone, for drivers that update the atoms themselves (the decomposed driver does):
+ * npt_pre before the force evaluation (half steps of both chains, half kick of the box momentum, the box coordinate moves;
+ * leaves the step's coefficients in state[38..41] and multiplies the thermostat's momentum scale into state[1]), npt_post
+ * after the atoms' second kick (box half kick, chains' half steps; state[1] = the thermostat's scale).  virial9_dev and
+ * kinetic_energy_dev (one double, eV) are totals over all ranks; V0 is the volume of the reference cell; n_atoms the number
+ * of atoms of the whole structure.  The atoms' updates with the coefficients c1 = state[38], c2 = state[39], r1 = state[40],
+ * r2 = state[41] are  v <- state[1] v;  v <- c1 v + c2 a;  R <- r1 R + r2 v  before, and  v <- c1 v + c2 a  after the
+ * evaluation (a = 9.648533212331e-3 F / m). */
+SO3LR_B200_API int so3lr_b200_npt_pre(void* stream, double* state_dev, int n_atoms, float dt_fs, double kT, double pressure,
+                                      double tau_t_fs, double tau_b_fs, int chain_length, int chain_steps, int sy_steps, double V0,
+                                      const double* virial9_dev, const double* kinetic_energy_dev);
+SO3LR_B200_API int so3lr_b200_npt_post(void* stream, double* state_dev, int n_atoms, float dt_fs, double kT, double pressure,
+                                       double tau_t_fs, double tau_b_fs, int chain_length, int chain_steps, int sy_steps, double V0,
+                                       const double* virial9_dev, const double* kinetic_energy_dev);
 /* Replaces the cell by a slightly rescaled one without discarding the neighbor lists (the caller has moved the positions
  * with the cell; the next evaluation's skin test decides about a rebuild).  so3lr_b200_system_set_cell discards them. */
 SO3LR_B200_API int so3lr_b200_system_rescale_cell(so3lr_b200_system* sys, const float* cell9);

@@ -54,6 +54,8 @@ def _load():
         "so3lr_b200_npt_init": (i32, [p, p]),
         "so3lr_b200_system_npt": (i32, [p, p, i32, f32, f64, f64, f64, f64, i32, i32, i32, p, p, p, p, p, p, p, p]),
         "so3lr_b200_system_rescale_cell": (i32, [p, p]),
+        "so3lr_b200_npt_pre": (i32, [p, p, i32, f32, f64, f64, f64, f64, i32, i32, i32, f64, p, p]),
+        "so3lr_b200_npt_post": (i32, [p, p, i32, f32, f64, f64, f64, f64, i32, i32, i32, f64, p, p]),
         "so3lr_b200_dd_set_atoms": (i32, [p, i32, p, p, p]),
         "so3lr_b200_dd_begin": (i32, [p, p, p]),
         "so3lr_b200_dd_layer_forward": (i32, [p, p, i32]),

@@ -1021,6 +1021,39 @@ SO3LR_B200_API int so3lr_b200_npt_init(void* stream, double* state) {
   return kOk;
 }
 
+// The two box/chain kernels of an NPT step for callers that move the atoms themselves (the decomposed driver): `virial9`
+// and `kinetic_energy` (one double, eV; may be NULL in npt_pre to keep the chain's own value) are sums over all ranks.
+static int npt_params_ok(int n_atoms, float dt, double kT, double pressure, double tau_t, double tau_b, int chain_length, int chain_steps,
+                         int sy_steps, double V0) {
+  return n_atoms > 0 && nhc_settings_ok(chain_length, chain_steps, sy_steps, dt, tau_t, kT, 3.0 * n_atoms) && tau_b > 0.0 &&
+         std::isfinite(pressure) && V0 > 0.0;
+}
+
+SO3LR_B200_API int so3lr_b200_npt_pre(void* stream, double* state, int n_atoms, float dt, double kT, double pressure, double tau_t,
+                                      double tau_b, int chain_length, int chain_steps, int sy_steps, double V0, const double* virial9,
+                                      const double* kinetic_energy) {
+  if (!state || !virial9 || !npt_params_ok(n_atoms, dt, kT, pressure, tau_t, tau_b, chain_length, chain_steps, sy_steps, V0))
+    return kInvalidArgument;
+  tl_launch_counter = nullptr;
+  NptParams p{chain_length, chain_steps, sy_steps, n_atoms, (double)dt, kT, pressure, tau_t, tau_b, V0};
+  npt_pre((cudaStream_t)stream, state, p, virial9, kinetic_energy, 1);
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_npt_post(void* stream, double* state, int n_atoms, float dt, double kT, double pressure, double tau_t,
+                                       double tau_b, int chain_length, int chain_steps, int sy_steps, double V0, const double* virial9,
+                                       const double* kinetic_energy) {
+  if (!state || !virial9 || !kinetic_energy ||
+      !npt_params_ok(n_atoms, dt, kT, pressure, tau_t, tau_b, chain_length, chain_steps, sy_steps, V0))
+    return kInvalidArgument;
+  tl_launch_counter = nullptr;
+  NptParams p{chain_length, chain_steps, sy_steps, n_atoms, (double)dt, kT, pressure, tau_t, tau_b, V0};
+  npt_post((cudaStream_t)stream, state, p, virial9, kinetic_energy, 1);
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
 SO3LR_B200_API int so3lr_b200_system_npt(so3lr_b200_system* S, void* stream, int n_steps, float dt, double kT, double pressure,
                                          double tau_t, double tau_b, int chain_length, int chain_steps, int sy_steps,
                                          const float* masses, float* R, float* V, float* F, double* state, const float* cell0_9,

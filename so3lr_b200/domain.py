@@ -151,6 +151,18 @@ class SlabDecomposition:
         self.bounds = np.arange(self.world + 1, dtype=np.float64) / self.world
         self.ext = 1.0 / self.world + 2 * self.reach + (self.lr_radius + 1.0) / self.width
 
+    def rescale(self, factor: float):
+        """The cell grows by `factor` in every direction (isotropic barostat); the slab boundaries and the halo stay what
+        they are in fractional coordinates until the next partition recomputes them from the new widths."""
+        self.cell = self.cell * float(factor)
+        self.inv = np.linalg.inv(self.cell)
+        self.width *= float(factor)
+        self.sf = self.shell / self.width
+        self.reach = self.lr_radius / self.width
+        if self.reach > 1.0:
+            raise ValueError("the cell is thinner than the halo along the decomposed direction")
+        self.ext = 1.0 / self.world + 2 * self.reach + (self.lr_radius + 1.0) / self.width
+
     def local_cell(self):
         c = self.cell.copy()
         c[self.axis] = self.cell[self.axis] * self.ext
@@ -274,6 +286,17 @@ class CudaBackend:
     def virial(self):
         """Share of the owned atoms in dE/d eps, (3,3) float64."""
         return self.sys.virial()
+
+    def rescale_cell(self, cell_local):
+        self.sys.rescale_cell(cell_local)
+
+    def npt_state(self):
+        from .engine import npt_state
+        return npt_state(self.device)
+
+    def npt_box_step(self, which, state, *args, **kw):
+        from .engine import npt_box_step
+        npt_box_step(which, state, *args, **kw)
 
     def nhc_state(self):
         from .engine import nhc_state
@@ -592,6 +615,42 @@ class DomainSystem:
         self.V *= chain[1].to(self.V.dtype)
         chain[1] = 1.0
         return self.E
+
+    def npt(self, n_steps, dt_fs, kT, pressure, tau_t_fs, tau_b_fs, state, cell0, chain_length=3, chain_steps=2, sy_steps=3):
+        """NPT steps (isotropic Martyna-Tobias-Klein barostat, Nose-Hoover chains on particles and box) on the owned atoms.
+        Every rank carries the same box-and-chains `state` (backend.npt_state()) and advances it with the all-reduced kinetic
+        energy and virial, so all ranks rescale box, positions and velocities alike.  `cell0` is the reference cell of the
+        box coordinate; backend.enable_virial() and a compute() must precede the first call.  Returns the energy and the
+        cell after the last step.  Mirrors jax_md.simulate.npt_nose_hoover as driven by so3lr/cli/so3lr_md.py:1089-1107,
+        1254-1282."""
+        cell0 = np.asarray(cell0, dtype=np.float64).reshape(3, 3)
+        V0 = abs(float(np.linalg.det(cell0)))
+        kw = dict(chain_length=chain_length, chain_steps=chain_steps, sy_steps=sy_steps)
+        args = (self.n_all, dt_fs, kT, pressure, tau_t_fs, tau_b_fs, V0)
+        if getattr(self, "_virial_all", None) is None:
+            self._virial_all = self.virial().contiguous()
+        for step in range(n_steps):
+            self.backend.npt_box_step("pre", state, *args, self._virial_all, self.kinetic_energy() if step == 0 else None, **kw)
+            acc = (ACC_UNIT / self.m)[:, None]
+            c1, c2 = state[38].to(self.V.dtype), state[39].to(self.V.dtype)
+            self.V = self.V * (state[1].to(self.V.dtype) * c1) + (c2 * acc) * self.F
+            # the box moves by ~1e-6 per step: add the increment (r1 - 1) R instead of multiplying by r1 in float32
+            Ro = self.R[: self.n0]
+            self.R[: self.n0] = Ro + (Ro * (state[40] - 1.0).to(self.R.dtype) + state[41].to(self.R.dtype) * self.V)
+            # the new cell on the host: the step's one extra host read
+            scale = float(torch.exp(state[36]))
+            self.geo.rescale(scale * np.cbrt(V0 / abs(np.linalg.det(self.geo.cell))))
+            a_vec = torch.tensor(self.geo.cell[self.geo.axis], dtype=torch.float32, device=self.device)
+            self.shift_vec = self.shift[:, None].to(torch.float32) * a_vec
+            self.backend.rescale_cell(self.geo.local_cell())
+            self.compute()
+            self._virial_all = self.virial().contiguous()
+            acc = (ACC_UNIT / self.m)[:, None]              # ownership may have changed
+            self.V = self.V * state[38].to(self.V.dtype) + (state[39].to(self.V.dtype) * acc) * self.F
+            self.backend.npt_box_step("post", state, *args, self._virial_all, self.kinetic_energy(), **kw)
+        self.V = self.V * state[1].to(self.V.dtype)
+        state[1] = 1.0
+        return self.E, self.geo.cell.copy()
 
     # ---- reassembly ----
     def gather_global(self, owned_rows):

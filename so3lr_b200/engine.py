@@ -232,6 +232,20 @@ NPT_STATE_DOUBLES = 44
 BAR = 6.241509074e-7              # eV / A^3 per bar
 
 
+def npt_box_step(which, state, n_atoms, dt_fs, kT, pressure, tau_t_fs, tau_b_fs, V0, virial, kinetic_energy, chain_length=3,
+                 chain_steps=2, sy_steps=3):
+    """so3lr_b200_npt_pre (`which` = "pre") / so3lr_b200_npt_post ("post") on `state`: the box-and-chains part of an NPT step.
+    `virial` (3,3) and `kinetic_energy` (1,) are float64 CUDA tensors holding totals over all ranks."""
+    fn = lib.so3lr_b200_npt_pre if which == "pre" else lib.so3lr_b200_npt_post
+    assert virial.is_cuda and virial.dtype == torch.float64 and virial.is_contiguous()
+    assert kinetic_energy is None or (kinetic_energy.is_cuda and kinetic_energy.dtype == torch.float64)
+    with torch.cuda.device(state.device):
+        s = torch.cuda.current_stream(state.device)
+        check(fn(C.c_void_p(s.cuda_stream), _ptr(state), int(n_atoms), float(dt_fs), float(kT), float(pressure), float(tau_t_fs),
+                 float(tau_b_fs), int(chain_length), int(chain_steps), int(sy_steps), float(V0), _ptr(virial), _ptr(kinetic_energy)),
+              "npt_" + which)
+
+
 def npt_state(device):
     """A zeroed NPT state on `device`: [0:18] thermostat chain, [18:36] barostat chain, [36] eps = ln(V/V0)/3, [37] its
     momentum, [38:42] step coefficients, [42] volume."""

@@ -253,3 +253,49 @@ def test_npt_water_box_conserves_its_invariant_and_moves_towards_the_target_pres
     chk = System(Z, md.npt_box(state), cutoff_lr=12.0, damping=2.0).compute(state.position)
     assert abs(float(chk["energy"].sum()) - float(state.energy.sum())) < 1e-5 * abs(float(state.energy.sum()))
     assert np.abs(chk["forces"].cpu().numpy() - state.force.cpu().numpy()).max() < 2e-4
+
+
+def test_decomposed_npt_tracks_single_device():
+    from so3lr_b200 import domain as D
+    from so3lr_b200 import md
+    from so3lr_b200 import workloads as W
+    from so3lr_b200.engine import System, npt_state
+    from test_gpu_domain import _run_threads
+    Z, R, cell = W.water_box(512, 24.9, 11, jitter=0.02)
+    R, cell = np.asarray(R, dtype=np.float32), np.asarray(cell, dtype=np.float64)
+    V, m = W.maxwell_boltzmann(Z, 300.0, 12)
+    V, m = np.asarray(V, dtype=np.float32), np.asarray(m, dtype=np.float32)
+    skin, dt, tau_t, tau_b, steps = 0.5, 0.5, 20.0, 60.0, 10
+    P_target = 1000.0 * md.BAR
+    s = System(Z, cell, cutoff_lr=12.0, damping=2.0, skin=skin)
+    s.enable_virial(True)
+    Rd, Vd = torch.tensor(R, device="cuda"), torch.tensor(V, device="cuda")
+    mdv = torch.tensor(m, device="cuda")
+    Fd = s.compute(Rd)["forces"].clone()
+    st = npt_state("cuda:0")
+    _, cell_ref = s.npt(steps, dt, KT300, P_target, tau_t, tau_b, mdv, Rd, Vd, Fd, st, cell)
+    ref = st.cpu().numpy()
+    assert abs(ref[36]) > 1e-6                     # the box moved
+
+    def fn(comm, rank):
+        be = D.CudaBackend(cutoff_lr=12.0, damping=2.0, skin=skin, device=0)
+        be.enable_virial(True)
+        dom = D.DomainSystem(comm, be, Z, R, cell, skin=skin, cutoff_lr=12.0, velocities=V, masses=m, device="cuda:0")
+        dom.compute(check_rebuild=False)
+        state = be.npt_state()
+        dom.npt(4, dt, KT300, P_target, tau_t, tau_b, state, cell)
+        _, c = dom.npt(steps - 4, dt, KT300, P_target, tau_t, tau_b, state, cell)
+        return dom.gather_global(dom.R[: dom.n0]).cpu().numpy(), dom.gather_global(dom.V).cpu().numpy(), state.cpu().numpy(), c
+
+    res = _run_threads(2, fn)
+    np.testing.assert_array_equal(res[0][2], res[1][2])          # both ranks hold the same box and chains, bit for bit
+    Rdd, Vdd, stt, c = res[0]
+    assert abs(stt[36] - ref[36]) < 1e-3 * abs(ref[36]) + 1e-9, (stt[36], ref[36])
+    assert abs(stt[37] - ref[37]) < 2e-3 * abs(ref[37]), (stt[37], ref[37])
+    np.testing.assert_allclose(c, cell_ref, rtol=1e-6)
+    d = Rdd - Rd.cpu().numpy()
+    d -= np.round(d / c[0, 0]) * c[0, 0]
+    assert np.abs(d).max() < 1e-3 and np.median(np.abs(d)) < 2e-5, (np.abs(d).max(), np.median(np.abs(d)))
+    assert np.median(np.abs(Vdd - Vd.cpu().numpy())) < 2e-6
+    np.testing.assert_allclose(stt[2:5], ref[2:5], rtol=1e-3, atol=1e-8)
+    assert stt[1] == 1.0
