@@ -747,16 +747,19 @@ def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
     torch.cuda.synchronize()
     dist.barrier()
     t0 = time.perf_counter()
-    tmp = np.empty_like(Rh)
+    # the host integrator is part of the step; it works on flat views (numpy's inner loops over a last axis of 3 are slow)
+    acc3 = np.ascontiguousarray(np.repeat(acc, 3, axis=1)).reshape(-1)
+    Rh, Vh = np.ascontiguousarray(Rh), np.ascontiguousarray(Vh)
+    Rf, Vf, tmp = Rh.reshape(-1), Vh.reshape(-1), np.empty(Rh.size, np.float32)
 
-    def kick(F):               # in place, no temporaries: the host integrator is part of the step
-        np.multiply(F, acc, out=tmp)
-        np.add(Vh, tmp, out=Vh)
+    def kick(F):
+        np.multiply(np.ascontiguousarray(F).reshape(-1), acc3, out=tmp)
+        np.add(Vf, tmp, out=Vf)
 
     for _ in range(args.steps):
         kick(Fh)
-        np.multiply(Vh, np.float32(dt), out=tmp)
-        np.add(Rh, tmp, out=Rh)
+        np.multiply(Vf, np.float32(dt), out=tmp)
+        np.add(Rf, tmp, out=Rf)
         _, Fh = dom.compute_host(Rh)
         kick(Fh)
     torch.cuda.synchronize()
