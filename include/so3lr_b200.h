@@ -271,6 +271,12 @@ SO3LR_B200_API int so3lr_b200_neighbor_list_noalloc(void* stream, int n_atoms, c
                                                     int64_t* count_dev, int* overflow_dev);
 
 /* Host-callable pieces of the device math, exported for the CPU tests (no GPU needed). */
+/* 64-bit total of a device array of per-row pair counts, formed the way the list builder forms it ahead of its 32-bit
+ * offset scan; returns SO3LR_B200_TOO_LARGE when the offsets of such a list would leave the int32 range (the builder then
+ * refuses the list before filling it).  Test support for the capacity protocol of partition.neighbor_list
+ * (so3lr/cli/so3lr_md.py:836-877). */
+SO3LR_B200_API int so3lr_b200_list_row_total(void* stream, const int32_t* row_count_dev, int n_rows, int64_t* total_host);
+
 SO3LR_B200_API void so3lr_b200_host_sph_harm(float x, float y, float z, float* y24);
 SO3LR_B200_API void so3lr_b200_host_sph_harm_vjp(float x, float y, float z, const float* g24, float* g3);
 SO3LR_B200_API void so3lr_b200_host_pair_terms(float r, int zi, int zj, float qi, float qj, float hi, float hj, float cutoff_lr,
@@ -280,6 +286,8 @@ SO3LR_B200_API void so3lr_b200_host_dispersion_fast(float r, int zi, int zj, flo
                                                     float* out4);
 SO3LR_B200_API void so3lr_b200_host_zbl(const float* blob_host, float r, int zi, int zj, float* out2);
 SO3LR_B200_API void so3lr_b200_host_radial_filter(const float* blob_host, int layer, double r, double* w256, double* dw256);
+/* the same filters through the 64-term Chebyshev expansion that the tiled tensor-core attention kernels contract on the fly */
+SO3LR_B200_API void so3lr_b200_host_radial_filter_chebyshev(const float* blob_host, int layer, double r, double* w256, double* dw256);
 
 #ifdef __cplusplus
 }

@@ -69,12 +69,14 @@ def _load():
         "so3lr_b200_system_profile": (i32, [p, i32]),
         "so3lr_b200_system_profile_read": (i32, [p, i32, p, p, p]),
         "so3lr_b200_neighbor_list_noalloc": (i32, [p, i32, p, p, f32, i32, p, i64, p, p]),
+        "so3lr_b200_list_row_total": (i32, [p, p, i32, C.POINTER(i64)]),
         "so3lr_b200_host_sph_harm": (None, [f32, f32, f32, p]),
         "so3lr_b200_host_sph_harm_vjp": (None, [f32, f32, f32, p, p]),
         "so3lr_b200_host_pair_terms": (None, [f32, i32, i32, f32, f32, f32, f32, f32, f32, p]),
         "so3lr_b200_host_dispersion_fast": (None, [f32, i32, i32, f32, f32, f32, f32, p]),
         "so3lr_b200_host_zbl": (None, [p, f32, i32, i32, p]),
         "so3lr_b200_host_radial_filter": (None, [p, i32, C.c_double, p, p]),
+        "so3lr_b200_host_radial_filter_chebyshev": (None, [p, i32, C.c_double, p, p]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

@@ -49,6 +49,17 @@ constexpr float kZblSwitchOff = 1.5f;
 constexpr int kTableGrid = 1024;                 // radial-filter table points on [0, 4.5]
 constexpr float kTableH = kCutoffSr / (kTableGrid - 1);
 
+// Radial filters of the tiled attention kernels: 64 Chebyshev polynomials of t = kChebA * x + kChebB, x = exp(-kChebHalfGamma r),
+// which maps r in [0, 4.5] onto t in [1, -1].  In this variable the filters are smooth enough that 64 terms reproduce them to
+// 2e-8 and their r-derivative to 4e-6 of their largest value.
+constexpr int kChebM = 64;
+constexpr double kChebHalfGammaD = 0.5 * 0.9448630809783936;       // half the Bernstein decay constant (a float32 number)
+constexpr double kChebX0D = 0.11932052347400147;                    // exp(-kChebHalfGammaD * 4.5)
+constexpr float kChebHalfGamma = (float)kChebHalfGammaD;
+constexpr float kChebA = (float)(2.0 / (1.0 - kChebX0D));
+constexpr float kChebB = (float)(-(1.0 + kChebX0D) / (1.0 - kChebX0D));
+constexpr int kTcImageBytes = 2 * 32768 + 4 * 8192;                 // C hi | C lo | K2 hi [2] | K2 lo [2]
+
 SO3LR_HD int degree_of(int m) { return m < 3 ? 0 : (m < 8 ? 1 : (m < 15 ? 2 : 3)); }
 
 SO3LR_D float silu_f(float x) { return x / (1.f + __expf(-x)); }

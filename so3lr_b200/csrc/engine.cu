@@ -29,6 +29,13 @@ void count_launch(int kernels) {
 
 namespace {
 
+// first atomic number outside [1, kMaxZ] (0 -> -1 so that the result is non-zero), 0 when all are supported
+int first_unsupported_element(const int32_t* Z, int n) {
+  for (int a = 0; a < n; ++a)
+    if (Z[a] < 1 || Z[a] > kMaxZ) return Z[a] == 0 ? -1 : Z[a];
+  return 0;
+}
+
 // tracked device allocation
 struct Pool {
   std::vector<void*> ptrs;
@@ -257,10 +264,12 @@ struct so3lr_b200_system {
   float* d_total_charge = nullptr;
   // lists
   NeighborListDev sr, lrl;
+  int sr_rows = 0;               // rows of the short-range list (all atoms, or the owned ones of a decomposed evaluation)
+  ValidEdges ve;                 // its entries inside the cutoff, compacted at every evaluation
   NlistWorkspace* nws = nullptr;
   float* d_Rref = nullptr;
-  int* d_flag = nullptr;
-  int* h_flag = nullptr;   // pinned
+  int* d_flag = nullptr;   // [0] skin test of the current step, [1] sticky error word of the tensor-core kernels' bounded waits
+  int* h_flag = nullptr;   // pinned copy of both
   double* h_box = nullptr; // pinned: the box coordinate read back by the NPT step
   bool virial_fresh = false;   // virial_sum belongs to the latest evaluation
   bool have_lists = false;
@@ -311,7 +320,7 @@ int ensure_edge_buffers(so3lr_b200_system* S, long long n_edges) {
   S->dR = nullptr;
   SO3LR_CUDA_CHECK(cudaMalloc((void**)&S->dR, (size_t)cap * 3 * sizeof(float)));
   S->edge_cap = cap;
-  return kOk;
+  return valid_edges_reserve(&S->ve, S->n_cap, cap);
 }
 
 constexpr int kSortMinAtoms = 512;
@@ -354,6 +363,7 @@ int rebuild_lists(so3lr_b200_system* S, cudaStream_t st, const float* R_user, bo
   SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->d_Rref, R_user, (size_t)S->n * 3 * sizeof(float), cudaMemcpyDeviceToDevice, st));
   rc = ensure_edge_buffers(S, S->sr.count);
   if (rc) return rc;
+  S->sr_rows = S->n;
   S->have_lists = true;
   S->n_rebuilds++;
   return kOk;
@@ -408,14 +418,21 @@ int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, co
   return kOk;
 }
 
-// SO3LR_B200_ATTENTION=simt selects the FP32 shared-memory filter GEMMs instead of the tensor-core ones (for comparison runs)
-bool use_mma_attention() {
-  static const bool v = [] {
+// Attention kernels of the layers with a spherical filter.  SO3LR_B200_ATTENTION (for comparison runs): "tc" tiled tcgen05
+// kernels, "tcf" tiled forward with the warp-per-receiver reverse kernel, "mma" warp-per-receiver mma.sync kernels, "simt"
+// FP32 shared-memory filter GEMMs.
+enum AttentionMode { kAttnSimt = 0, kAttnMma = 1, kAttnTcFwd = 2, kAttnTc = 3 };
+int attention_mode() {
+  static const int v = [] {
     const char* e = std::getenv("SO3LR_B200_ATTENTION");
-    return !(e && std::strcmp(e, "simt") == 0);
+    if (e && std::strcmp(e, "simt") == 0) return (int)kAttnSimt;
+    if (e && std::strcmp(e, "tcf") == 0) return (int)kAttnTcFwd;
+    if (e && std::strcmp(e, "tc") == 0) return (int)kAttnTc;
+    return (int)kAttnMma;
   }();
   return v;
 }
+bool use_mma_attention() { return attention_mode() >= kAttnMma; }
 // SO3LR_B200_DENSE=simt selects the FP32 shared-memory versions of the per-atom dense blocks
 // SO3LR_B200_LAYER0=generic evaluates the first layer with the generic attention kernels instead of the element-pair tables
 bool use_layer0_tables() {
@@ -456,15 +473,18 @@ void heads_bwd_dispatch(cudaStream_t s, const ModelDev& M, int n, const int* Z, 
   if (use_mma_dense()) launch_heads_bwd_mma(s, M, n, Z, ze, zq, zh, hv, ge, gq, gh, gx);
   else launch_heads_bwd(s, M, n, Z, ze, zq, zh, hv, ge, gq, gh, gx);
 }
-void attn_fwd_dispatch(cudaStream_t st, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+void attn_fwd_dispatch(so3lr_b200_system* S, cudaStream_t st, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
                        const float* qkv, const float* x_in, const float* ev_in, float* xa, float* ev1) {
-  if (L.has_spherical && use_mma_attention()) launch_attn_fwd_mma(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
+  if (L.has_spherical && attention_mode() >= kAttnTcFwd) launch_attn_fwd_tc(st, L, S->ve, n_recv, qkv, x_in, ev_in, xa, ev1, S->d_flag + 1);
+  else if (L.has_spherical && use_mma_attention()) launch_attn_fwd_mma(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
   else launch_attn_fwd_sym(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1);
 }
-void attn_bwd_dispatch(cudaStream_t st, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+void attn_bwd_dispatch(so3lr_b200_system* S, cudaStream_t st, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
                        const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv, float* gev_in, float* F,
                        int first_layer, float* virial) {
-  if (!first_layer && L.has_spherical && use_mma_attention())
+  if (!first_layer && L.has_spherical && attention_mode() == kAttnTc)
+    launch_attn_bwd_tc(st, L, S->ve, n_recv, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F, virial, S->d_flag + 1);
+  else if (!first_layer && L.has_spherical && use_mma_attention())
     launch_attn_bwd_mma(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F, virial);
   else launch_attn_bwd_sym(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F, first_layer, virial);
 }
@@ -497,6 +517,10 @@ int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const S
   S->prof.begin(kPGeom, st);
   launch_sr_geometry_zbl(st, M, S->cell, c.n3, S->sr.count, edge_i, nbr_j, S->d_Z, R, 0, S->dR, S->e_zbl, nullptr, nullptr, F,
                          owned_side_only ? c.n0 : -1, S->vir());
+  if (attention_mode() >= kAttnTcFwd) {
+    int rcv = valid_edges_build(&S->ve, st, S->sr_rows, c.n3, row_ptr, nbr_j, S->dR);
+    if (rcv) return rcv;
+  }
   S->prof.end(st);
   const bool tab0 = S->sp.n_species > 0 && use_layer0_tables();
   const bool fuse = use_mma_dense();   // q/k/v rows of layer l+1 come out of layer l's dense block
@@ -510,7 +534,7 @@ int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const S
     } else {
       if (!(fuse && l > 0)) { S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], nsend[l], S->qkv[l]); S->prof.end(st); }
       S->prof.begin(kPAttnFwd, st);
-      attn_fwd_dispatch(st, L, nrecv[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
+      attn_fwd_dispatch(S, st, L, nrecv[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
       S->prof.end(st);
     }
     S->prof.begin(kPPostFwd, st);
@@ -553,7 +577,7 @@ int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float
     if (l == 0 && S->sp.n_species > 0 && use_layer0_tables())
       launch_layer0_bwd_tab(st, S->sp, nattn[0], c.n3, c.n3, row_ptr, nbr_j, S->dR, S->d_Z, S->g_xa, S->gev1, S->GV, F, S->vir());
     else
-      attn_bwd_dispatch(st, L, nattn[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, F, l == 0 ? 1 : 0,
+      attn_bwd_dispatch(S, st, L, nattn[l], c.n3, row_ptr, nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, F, l == 0 ? 1 : 0,
                         S->vir());
     S->prof.end(st);
     if (l > 0) {
@@ -621,6 +645,7 @@ SO3LR_B200_API int so3lr_b200_model_create(const float* blob_host, size_t n_floa
   if (rc == kOk) rc = configure_attention_kernels();
   if (rc == kOk) rc = configure_attention_sym_kernels();
   if (rc == kOk) rc = configure_attention_mma_kernels();
+  if (rc == kOk) rc = configure_attention_tc_kernels();
   if (rc == kOk) rc = configure_atom_mma_kernels();
   if (rc != kOk) { so3lr_b200_model_destroy(m); return rc; }
   *out = m;
@@ -641,6 +666,11 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
   if (!model || !Z || !out || !options || n_atoms <= 0 || n_graphs <= 0) return kInvalidArgument;
   if (n_atoms > 64 * 1000 * 1000) return kTooLarge;
   if (n_graphs > 1 && !graph_start) return kInvalidArgument;
+  if (int bad = first_unsupported_element(Z, n_atoms)) {
+    std::fprintf(stderr, "so3lr_b200: atomic number %d is outside the supported range 1..%d (free-atom polarisabilities and C6 "
+                         "coefficients of the dispersion term are tabulated for these elements only)\n", bad == -1 ? 0 : bad, kMaxZ);
+    return kInvalidArgument;
+  }
   if (num_unpaired)
     for (int g = 0; g < n_graphs; ++g)
       if (num_unpaired[g] != 0.f) {
@@ -691,7 +721,7 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
   }
   std::vector<float> tq(n_graphs, 0.f);
   if (total_charge) for (int g = 0; g < n_graphs; ++g) tq[g] = total_charge[g];
-  S->d_Rref = A.get<float>((size_t)n * 3); S->d_flag = A.get<int>(1);
+  S->d_Rref = A.get<float>((size_t)n * 3); S->d_flag = A.get<int>(2);
   S->d_rowptr_g = A.get<int>((size_t)n + 1); S->d_rowptr_lr_g = A.get<int>((size_t)n + 1);
   for (int l = 0; l <= kNumLayers; ++l) { S->x[l] = A.get<float>((size_t)n * kF); S->ev[l] = A.get<float>((size_t)n * kMTot); }
   for (int l = 0; l < kNumLayers; ++l) {
@@ -716,7 +746,7 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
             cudaMemcpy(S->d_graph_start, gs.data(), (size_t)(n_graphs + 1) * sizeof(int), cudaMemcpyHostToDevice) == cudaSuccess &&
             cudaMemcpy(S->d_total_charge, tq.data(), (size_t)n_graphs * sizeof(float), cudaMemcpyHostToDevice) == cudaSuccess &&
             cudaMemset(S->ev[0], 0, (size_t)n * kMTot * sizeof(float)) == cudaSuccess &&
-            cudaMallocHost((void**)&S->h_flag, sizeof(int)) == cudaSuccess &&
+            cudaMallocHost((void**)&S->h_flag, 2 * sizeof(int)) == cudaSuccess &&
             cudaMallocHost((void**)&S->h_R, (size_t)n * 3 * sizeof(float)) == cudaSuccess &&
             cudaMallocHost((void**)&S->h_F, (size_t)n * 3 * sizeof(float)) == cudaSuccess &&
             cudaMallocHost((void**)&S->h_q, (size_t)n * sizeof(float)) == cudaSuccess &&
@@ -738,12 +768,14 @@ SO3LR_B200_API int so3lr_b200_system_destroy(so3lr_b200_system* S) {
   if (tl_launch_counter == &S->n_launches) tl_launch_counter = nullptr;
   cudaSetDevice(S->model->device);
   cudaDeviceSynchronize();
+  tc_debug_print();
   S->pool.release();
   species_tables_free(&S->sp);
   S->prof.destroy();
   nlist_workspace_destroy(S->nws);
   for (NeighborListDev* L : {&S->sr, &S->lrl}) { cudaFree(L->row_ptr); cudaFree(L->nbr_j); cudaFree(L->edge_i); }
   cudaFree(S->dR);
+  valid_edges_free(&S->ve);
   if (S->h_flag) cudaFreeHost(S->h_flag);
   if (S->h_box) cudaFreeHost(S->h_box);
   if (S->h_R) cudaFreeHost(S->h_R);
@@ -780,8 +812,12 @@ static int prepare_lists(so3lr_b200_system* S, cudaStream_t st, const float* R, 
       float thr = 0.5f * S->opt.skin;
       SO3LR_CUDA_CHECK(cudaMemsetAsync(S->d_flag, 0, sizeof(int), st));
       { moved_kernel<<<(S->n + 255) / 256, 256, 0, st>>>(S->n, R, S->d_Rref, thr * thr, S->d_flag); count_launch(); }
-      SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_flag, S->d_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
+      SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_flag, S->d_flag, 2 * sizeof(int), cudaMemcpyDeviceToHost, st));
       SO3LR_CUDA_CHECK(cudaStreamSynchronize(st));
+      if (S->h_flag[1]) {
+        std::fprintf(stderr, "so3lr_b200: a bounded wait on the tensor-core pipeline ran out in an earlier evaluation\n");
+        return kCudaError;
+      }
       if (*S->h_flag & 2) return kNotFinite;
       rebuild = *S->h_flag != 0;
     }
@@ -1132,6 +1168,10 @@ SO3LR_B200_API int so3lr_b200_dd_set_atoms(so3lr_b200_system* S, int n_local, co
   {
     std::vector<int> zh((size_t)n_local);
     SO3LR_CUDA_CHECK(cudaMemcpy(zh.data(), Z_local_dev, (size_t)n_local * sizeof(int), cudaMemcpyDeviceToHost));
+    if (int bad = first_unsupported_element(zh.data(), n_local)) {
+      std::fprintf(stderr, "so3lr_b200: atomic number %d is outside the supported range 1..%d\n", bad == -1 ? 0 : bad, kMaxZ);
+      return kInvalidArgument;
+    }
     rc = species_tables_build(nullptr, S->model->M, zh.data(), n_local, &S->sp);
     if (rc) return rc;
     SO3LR_CUDA_CHECK(cudaDeviceSynchronize());
@@ -1159,6 +1199,7 @@ SO3LR_B200_API int so3lr_b200_dd_begin(so3lr_b200_system* S, void* stream, const
     if (rc) return rc;
     rc = ensure_edge_buffers(S, S->sr.count);
     if (rc) return rc;
+    S->sr_rows = n0;
     S->prof.end(st);
     S->have_lists = true;
     S->n_rebuilds++;
@@ -1170,6 +1211,10 @@ SO3LR_B200_API int so3lr_b200_dd_begin(so3lr_b200_system* S, void* stream, const
   S->prof.begin(kPGeom, st);
   launch_sr_geometry_zbl(st, M, S->cell, S->n, S->sr.count, S->sr.edge_i, S->sr.nbr_j, S->d_Z, R_local_dev, 0, S->dR, S->e_zbl, nullptr, nullptr,
                          S->F_s, n0, S->vir());
+  if (attention_mode() >= kAttnTcFwd) {
+    int rcv = valid_edges_build(&S->ve, st, S->sr_rows, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR);
+    if (rcv) return rcv;
+  }
   S->prof.end(st);
   if (!(S->sp.n_species > 0 && use_layer0_tables())) launch_embed(st, M, S->d_Z, n1, S->x[0]);
   SO3LR_CUDA_CHECK(cudaGetLastError());
@@ -1195,7 +1240,7 @@ SO3LR_B200_API int so3lr_b200_dd_layer_forward(so3lr_b200_system* S, void* strea
     launch_proj_fwd(st, L, S->x[l] + (size_t)first * kF, n1 - first, S->qkv[l] + (size_t)first * kProj);
     S->prof.end(st);
     S->prof.begin(kPAttnFwd, st);
-    attn_fwd_dispatch(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
+    attn_fwd_dispatch(S, st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
     S->prof.end(st);
   }
   const bool emit = use_mma_dense() && l + 1 < kNumLayers;
@@ -1285,7 +1330,7 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_attn(so3lr_b200_system* S, void*
   if (l == 0 && S->sp.n_species > 0 && use_layer0_tables())
     launch_layer0_bwd_tab(st, S->sp, n0, S->shells[1], S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->d_Z, S->g_xa, S->gev1, S->GV, S->F_s, S->vir());
   else
-    attn_bwd_dispatch(st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, S->dd_gev_in, S->F_s,
+    attn_bwd_dispatch(S, st, L, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, S->dd_gev_in, S->F_s,
                       l == 0 ? 1 : 0, S->vir());
   S->prof.end(st);
   if (l == 0 && S->vir()) reduce_virial(S, st, n0);
@@ -1386,6 +1431,16 @@ SO3LR_B200_API void so3lr_b200_host_zbl(const float* blob, float r, int zi, int 
 }
 SO3LR_B200_API void so3lr_b200_host_radial_filter(const float* blob, int layer, double r, double* w256, double* dw256) {
   radial_filter_reference(blob, layer, r, w256, dw256);
+}
+SO3LR_B200_API int so3lr_b200_list_row_total(void* stream, const int32_t* row_count_dev, int n_rows, int64_t* total_host) {
+  if (!row_count_dev || !total_host || n_rows < 0) return kInvalidArgument;
+  long long t = 0;
+  const int rc = nlist_row_total((cudaStream_t)stream, n_rows, row_count_dev, &t);
+  *total_host = t;
+  return rc;
+}
+SO3LR_B200_API void so3lr_b200_host_radial_filter_chebyshev(const float* blob, int layer, double r, double* w256, double* dw256) {
+  radial_filter_chebyshev(blob, layer, r, w256, dw256);
 }
 
 }  // extern "C"

@@ -68,6 +68,36 @@ void launch_attn_bwd_mma(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
                          const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv, float* gev_in,
                          float* F, float* virial = nullptr);
 
+// ---- attention_tc.cu: layers with a spherical filter as CTA-tiled tcgen05 kernels ----
+// Short-range list entries inside the cutoff, compacted once per evaluation and grouped by receiver: entry p of row i
+// (row_ptr[i] <= p < row_ptr[i + 1]) holds the receiver i[p], the sender j[p] and d[p] = (dx, dy, dz, |dR|).
+struct ValidEdges {
+  int* row_ptr = nullptr;   // n_rows + 1
+  int* count = nullptr;     // per-row counts (scratch of the build)
+  int* i = nullptr;
+  int* j = nullptr;
+  float4* d = nullptr;
+  void* cub_tmp = nullptr;
+  size_t cub_bytes = 0;
+  int row_cap = 0;
+  long long capacity = 0;
+  int n_rows = 0;           // rows of the latest build
+};
+int configure_attention_tc_kernels();
+void tc_debug_print();
+// (re)allocates for n_rows receivers and `capacity` entries (the capacity of the list they are compacted from)
+int valid_edges_reserve(ValidEdges* V, int n_rows, long long capacity);
+void valid_edges_free(ValidEdges* V);
+// no host synchronisation: counts stay on the device
+int valid_edges_build(ValidEdges* V, cudaStream_t s, int n_rows, int n, const int* row_ptr, const int* nbr_j, const float* dR);
+// Same results as launch_attn_fwd_sym for rows [0, n_recv).  `err` (device int) is set to 1 when a bounded wait on the
+// tensor-core pipeline ran out; the outputs are then incomplete.
+int launch_attn_fwd_tc(cudaStream_t s, const LayerDev& L, const ValidEdges& V, int n_recv, const float* qkv, const float* x_in,
+                       const float* ev_in, float* xa, float* ev1, int* err);
+// Same results as launch_attn_bwd_sym (first_layer = 0) for rows [0, n_recv): writes g_qkv and gev_in rows, adds to F (and virial).
+int launch_attn_bwd_tc(cudaStream_t s, const LayerDev& L, const ValidEdges& V, int n_recv, const float* qkv, const float* ev_in,
+                       const float* g_xa, const float* gev1, float* g_qkv, float* gev_in, float* F, float* virial, int* err);
+
 // ---- layer0_tab.cu: first layer through per-element-pair tables (its inputs depend on the elements only) ----
 constexpr int kMaxTabSpecies = 8;
 struct SpeciesTables {
@@ -140,6 +170,9 @@ int spatial_order(NlistWorkspace* ws, cudaStream_t s, const Cell& cell, int n, c
 // Builds rows for all i.  ordered: keep j > i only.  seg/graph_start (optional): pairs only inside one graph and the
 // candidate loop runs over the graph's atoms.  Grows `out` when `allow_grow`, otherwise sets *overflow (device int).
 // n_rows >= 0: only the rows of atoms 0 .. n_rows-1 are built (candidates are still all n atoms).
+// 64-bit sum of per-row pair counts as the builder forms it before its 32-bit scan; kTooLarge when the CSR offsets would
+// leave the int range (the builder returns the same status before it fills a single row)
+int nlist_row_total(cudaStream_t s, int n, const int* row_count_dev, long long* total_host);
 int nlist_build(NlistWorkspace* ws, cudaStream_t s, const Cell& cell, int n, const float* R, float r_list, int ordered,
                 const int* seg, const int* graph_start, NeighborListDev* out, int allow_grow, int* d_overflow, int n_rows = -1);
 

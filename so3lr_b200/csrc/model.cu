@@ -100,6 +100,97 @@ std::vector<float> pack_fragments(const float* W, int K, int N, bool transpose) 
   return out;
 }
 
+// Chebyshev coefficients coef[m][c] (m < kChebM, c < 256) of both radial filters of a layer in the variable
+// t = A x + B, x = exp(-hg r), sampled at 256 Chebyshev-Gauss nodes (A, B, hg are the float32 constants the kernels use)
+void chebyshev_coefficients(const float* blob, const BlobOffsets& O, int layer, std::vector<double>& coef) {
+  const int N = 256;
+  const double A = (double)kChebA, B = (double)kChebB, hg = (double)kChebHalfGamma;
+  std::vector<double> w((size_t)N * 256), dw(256);
+  for (int k = 0; k < N; ++k) {
+    const double t = std::cos(M_PI * (k + 0.5) / N);
+    const double x = (t - B) / A;
+    const double r = -std::log(x) / hg;
+    radial_filters(blob, O, layer, r, &w[(size_t)k * 256], dw.data());
+  }
+  coef.assign((size_t)kChebM * 256, 0.0);
+  for (int m = 0; m < kChebM; ++m)
+    for (int k = 0; k < N; ++k) {
+      const double c = std::cos(M_PI * m * (k + 0.5) / N) * (m == 0 ? 1.0 : 2.0) / N;
+      for (int j = 0; j < 256; ++j) coef[(size_t)m * 256 + j] += c * w[(size_t)k * 256 + j];
+    }
+}
+
+// FP16 hi and 2048-scaled lo of x (the split every tensor-core operand of the library uses)
+void split_half(float x, unsigned short& hi, unsigned short& lo) {
+  const __half h = __float2half_rn(x);
+  const __half l = __float2half_rn((x - __half2float(h)) * 2048.f);
+  std::memcpy(&hi, &h, 2);
+  std::memcpy(&lo, &l, 2);
+}
+
+// Operand image of attention_tc.cu: 8 x 8 core matrices (8 rows of 16 bytes).  Radial coefficients C[m][c]: core (m/8, c/8)
+// at (m/8) * 4096 + (c/8) * 128; second spherical layer K2_f[h][n]: core (h/8, n/8) at (h/8) * 2048 + (n/8) * 128.
+// term held by column / row k of the Chebyshev block: even terms first, then the odd ones
+int cheb_term(int k) { return k < kChebM / 2 ? 2 * k : 2 * (k - kChebM / 2) + 1; }
+
+// Forward-kernel image: B operands with K contiguous.  CT[n][k] = coefficient of term cheb_term(k) of feature n: core
+// (n/8, k/8) at (n/8) * 1024 + (k/8) * 128; K2T_f[n][h]: core (n/8, h/8) at (n/8) * 512 + (h/8) * 128.
+std::vector<float> tc_image_forward(const float* blob, const BlobOffsets& O, int layer) {
+  std::vector<unsigned char> img(kTcImageBytes, 0);
+  std::vector<double> coef;
+  chebyshev_coefficients(blob, O, layer, coef);
+  auto put = [&](size_t base_hi, size_t base_lo, size_t off, float v) {
+    unsigned short hi, lo;
+    split_half(v, hi, lo);
+    std::memcpy(&img[base_hi + off], &hi, 2);
+    std::memcpy(&img[base_lo + off], &lo, 2);
+  };
+  for (int k = 0; k < kChebM; ++k)
+    for (int n = 0; n < 256; ++n)
+      put(0, 32768, (size_t)(n / 8) * 1024 + (size_t)(k / 8) * 128 + (n % 8) * 16 + (k % 8) * 2, (float)coef[(size_t)cheb_term(k) * 256 + n]);
+  const LayerOffsets& L = O.layer[layer];
+  for (int f = 0; f < 2; ++f) {
+    const float* K2 = blob + L.sph_l2_k[f];
+    for (int h = 0; h < 32; ++h)
+      for (int n = 0; n < kF; ++n)
+        put(65536 + (size_t)f * 8192, 65536 + 16384 + (size_t)f * 8192, (size_t)(n / 8) * 512 + (size_t)(h / 8) * 128 + (n % 8) * 16 + (h % 8) * 2,
+            K2[h * kF + n]);
+  }
+  std::vector<float> out(kTcImageBytes / 4);
+  std::memcpy(out.data(), img.data(), kTcImageBytes);
+  return out;
+}
+
+std::vector<float> tc_image(const float* blob, const BlobOffsets& O, int layer) {
+  std::vector<unsigned char> img(kTcImageBytes, 0);
+  std::vector<double> coef;
+  chebyshev_coefficients(blob, O, layer, coef);
+  auto put = [&](size_t base_hi, size_t base_lo, size_t off, float v) {
+    unsigned short hi, lo;
+    split_half(v, hi, lo);
+    std::memcpy(&img[base_hi + off], &hi, 2);
+    std::memcpy(&img[base_lo + off], &lo, 2);
+  };
+  // row k of the image holds the term m(k): even terms first (k < 32: m = 2k), then the odd ones (m = 2 (k - 32) + 1), the
+  // order in which the kernels generate the polynomials
+  for (int k = 0; k < kChebM; ++k) {
+    const int m = cheb_term(k);
+    for (int c = 0; c < 256; ++c)
+      put(0, 32768, (size_t)(k / 8) * 4096 + (size_t)(c / 8) * 128 + (k % 8) * 16 + (c % 8) * 2, (float)coef[(size_t)m * 256 + c]);
+  }
+  const LayerOffsets& L = O.layer[layer];
+  for (int f = 0; f < 2; ++f) {
+    const float* K2 = blob + L.sph_l2_k[f];
+    for (int h = 0; h < 32; ++h)
+      for (int n = 0; n < kF; ++n)
+        put(65536 + (size_t)f * 8192, 65536 + 16384 + (size_t)f * 8192, (size_t)(h / 8) * 2048 + (size_t)(n / 8) * 128 + (h % 8) * 16 + (n % 8) * 2,
+            K2[h * kF + n]);
+  }
+  std::vector<float> out(kTcImageBytes / 4);
+  std::memcpy(out.data(), img.data(), kTcImageBytes);
+  return out;
+}
+
 struct Uploader {
   std::vector<void*>* owned;
   int status = kOk;
@@ -120,6 +211,28 @@ struct Uploader {
 };
 
 }  // namespace
+
+void radial_filter_chebyshev(const float* blob, int layer, double r, double* w256, double* dw256) {
+  BlobOffsets O = blob_offsets();
+  std::vector<double> coef;
+  chebyshev_coefficients(blob, O, layer, coef);
+  const double x = std::exp(-(double)kChebHalfGamma * r), t = (double)kChebA * x + (double)kChebB;
+  const double dtdr = -(double)kChebA * (double)kChebHalfGamma * x;
+  std::vector<double> T(kChebM), dT(kChebM);   // dT_m/dt = m U_{m-1}
+  double Um1 = 0.0, U0 = 1.0;                  // U_{-1}, U_0
+  T[0] = 1.0; T[1] = t; dT[0] = 0.0; dT[1] = 1.0;
+  for (int m = 2; m < kChebM; ++m) {
+    T[m] = 2.0 * t * T[m - 1] - T[m - 2];
+    const double U1 = 2.0 * t * U0 - Um1;      // U_{m-1}
+    Um1 = U0; U0 = U1;
+    dT[m] = m * U0;
+  }
+  for (int c = 0; c < 256; ++c) {
+    double a = 0.0, b = 0.0;
+    for (int m = 0; m < kChebM; ++m) { a += coef[(size_t)m * 256 + c] * T[m]; b += coef[(size_t)m * 256 + c] * dT[m]; }
+    w256[c] = a; dw256[c] = b * dtdr;
+  }
+}
 
 void radial_filter_reference(const float* blob, int layer, double r, double* w256, double* dw256) {
   BlobOffsets O = blob_offsets();
@@ -196,6 +309,8 @@ int build_model(const float* blob, size_t n_floats, ModelDev* M, std::vector<voi
       w.swap(w1); dw.swap(dw1);
     }
     D.table = U.up(tab);
+    D.tc_img = reinterpret_cast<const unsigned char*>(U.up(tc_image(blob, O, l)));
+    D.tc_img_fwd = reinterpret_cast<const unsigned char*>(U.up(tc_image_forward(blob, O, l)));
     std::vector<float> s1k(2 * 4 * 32), s1b(2 * 32), s2k(2 * 32 * 128);
     for (int f = 0; f < 2; ++f) {
       std::memcpy(&s1k[f * 128], blob + L.sph_l1_k[f], 128 * sizeof(float));

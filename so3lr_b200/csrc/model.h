@@ -11,6 +11,11 @@ struct LayerDev {
   const float* projT;   // [5][4][32 j][32 i]   forward projection  (out_i = sum_j W[h][i][j] x[h][j])
   const float* proj;    // [5][4][32 i][32 j]   as stored; used by the backward projection
   const float* table;   // [kTableGrid-1][4][256] radial filters per interval: value, h*slope, value difference, h*slope at the far knot; (w1 | w2)
+  // Operand image of the tiled tensor-core attention kernels (attention_tc.cu), copied verbatim into shared memory:
+  // Chebyshev coefficients of both radial filters (the tied output biases folded into the constant term) and the second
+  // spherical layer, each as FP16 hi / 2048-scaled-lo pairs in 8 x 8 core-matrix order (kTcImageBytes bytes)
+  const unsigned char* tc_img;
+  const unsigned char* tc_img_fwd;   // the same numbers with K contiguous per output feature (forward kernel: K-major B operands)
   const float* sph1_k;  // [2][4][32]   spherical filter, first layer kernel (filter, invariant, hidden)
   const float* sph1_b;  // [2][32]
   const float* sph2_k;  // [2][32][128] second layer kernel (filter, hidden, feature); bias is folded into `table`
@@ -51,6 +56,10 @@ struct ModelDev {
 // Builds every derived array on the host (double precision where it matters) and uploads it.
 // `owned` receives the device allocations so the handle can free them.
 int build_model(const float* blob, size_t n_floats, ModelDev* out, std::vector<void*>* owned);
+
+// Chebyshev expansion of the radial filters used by the tiled attention kernels: w_c(r) = sum_m coef[m][c] T_m(t(r)) with
+// t = kChebA * exp(-kChebHalfGamma * r) + kChebB on r in [0, 4.5] (host evaluation in double; for tests)
+void radial_filter_chebyshev(const float* blob, int layer, double r, double* w256, double* dw256);
 
 // host helper exposed for tests: evaluate the radial-filter table entry (value, derivative) directly
 void radial_filter_reference(const float* blob, int layer, double r, double* w256, double* dw256);

@@ -180,13 +180,28 @@ __global__ void __launch_bounds__(256) build_rows_graph_kernel(int n, const floa
   if (!FILL && lane == 0) row_count[i] = count;
 }
 
-__global__ void finish_scan_kernel(int n, const int* __restrict__ row_count, int* __restrict__ row_ptr, long long* total,
-                                   long long capacity, int* overflow) {
-  // row_ptr[0..n-1] hold the exclusive scan already; close it and report the total
+// 64-bit sum of the per-row counts.  The exclusive scan that follows runs in 32 bits (CSR offsets are int): this total, not
+// the scan's last element, decides whether the list fits, so a sum beyond 2^31 is seen before any offset is used.
+__global__ void __launch_bounds__(256) row_total_kernel(int n, const int* __restrict__ row_count, unsigned long long* __restrict__ total) {
+  __shared__ unsigned long long red[8];
+  unsigned long long v = 0;
+  for (int k = blockIdx.x * 256 + threadIdx.x; k < n; k += gridDim.x * 256) v += (unsigned long long)(unsigned)row_count[k];
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long t = 0;
+    for (int w = 0; w < 8; ++w) t += red[w];
+    if (t) atomicAdd(total, t);
+  }
+}
+
+__global__ void finish_scan_kernel(int n, int* __restrict__ row_ptr, const long long* __restrict__ total, long long capacity, int* overflow) {
+  // row_ptr[0..n-1] hold the exclusive scan already; close it with the 64-bit total (clamped: a total beyond the int range
+  // is rejected on the host before any row is filled)
   if (threadIdx.x == 0 && blockIdx.x == 0) {
-    long long t = n > 0 ? (long long)row_ptr[n - 1] + row_count[n - 1] : 0;
-    row_ptr[n] = (int)t;
-    *total = t;
+    const long long t = *total;
+    row_ptr[n] = t > 2147483647LL ? 2147483647 : (int)t;
     if (overflow && t > capacity) *overflow = 1;
   }
 }
@@ -223,6 +238,22 @@ int ensure(T** p, size_t n) {
 }
 
 }  // namespace
+
+int nlist_row_total(cudaStream_t s, int n, const int* row_count_dev, long long* total_host) {
+  unsigned long long* d = nullptr;
+  SO3LR_CUDA_CHECK(cudaMalloc((void**)&d, sizeof(unsigned long long)));
+  SO3LR_CUDA_CHECK(cudaMemsetAsync(d, 0, sizeof(unsigned long long), s));
+  int tb = (n + 255) / 256;
+  if (tb > 1024) tb = 1024;
+  if (n > 0) { row_total_kernel<<<tb, 256, 0, s>>>(n, row_count_dev, d); count_launch(); }
+  unsigned long long t = 0;
+  cudaError_t e = cudaMemcpyAsync(&t, d, sizeof(t), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  cudaFree(d);
+  if (e != cudaSuccess) return kCudaError;
+  *total_host = (long long)t;
+  return t > 2147483000ULL ? kTooLarge : kOk;
+}
 
 int spatial_order(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, const float* R, float cell_size, int* perm) {
   if (n <= 0 || !cell.periodic) return kInvalidArgument;
@@ -365,10 +396,13 @@ int nlist_build(NlistWorkspace* w, cudaStream_t s, const Cell& cell, int n, cons
   else
     { build_rows_kernel<false><<<blocks, 256, 0, s>>>(cell, G, n_rows, R, r2max, ordered, seg, w->pos_sorted, w->cell_start,
                                                     w->row_count, nullptr, nullptr, nullptr, 0); count_launch(); }
+  SO3LR_CUDA_CHECK(cudaMemsetAsync(w->d_total, 0, sizeof(long long), s));
+  { int tb = (n_rows + 255) / 256; if (tb > 1024) tb = 1024;
+    row_total_kernel<<<tb, 256, 0, s>>>(n_rows, w->row_count, reinterpret_cast<unsigned long long*>(w->d_total)); count_launch(); }
   size_t tmp = w->cub_bytes;
   cub::DeviceScan::ExclusiveSum(w->cub_tmp, tmp, w->row_count, out->row_ptr, n_rows, s);
   count_launch(2);
-  { finish_scan_kernel<<<1, 32, 0, s>>>(n_rows, w->row_count, out->row_ptr, w->d_total, out->capacity, allow_grow ? nullptr : d_overflow); count_launch(); }
+  { finish_scan_kernel<<<1, 32, 0, s>>>(n_rows, out->row_ptr, w->d_total, out->capacity, allow_grow ? nullptr : d_overflow); count_launch(); }
   SO3LR_CUDA_CHECK(cudaMemcpyAsync(w->h_total, w->d_total, sizeof(long long), cudaMemcpyDeviceToHost, s));
   SO3LR_CUDA_CHECK(cudaStreamSynchronize(s));
   const long long total = *w->h_total;

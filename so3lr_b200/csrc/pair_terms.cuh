@@ -33,7 +33,9 @@ SO3LR_HD Dual3 dpowi(Dual3 a, int n) {  // integer power by repeated multiplicat
   return r;
 }
 
-// Free-atom reference data (atomic units) for Z = 1..18: static polarisability and C6.
+// Free-atom reference data (atomic units) for Z = 1..18: static polarisability and C6.  Contexts reject any other element at
+// creation (so3lr_b200_system_create, so3lr_b200_dd_set_atoms), so the fall-through value is never used in an evaluation.
+constexpr int kMaxZ = 18;
 SO3LR_HD float alpha_free(int Z) {
   const float t[18] = {4.5f, 1.38f, 164.2f, 38.0f, 21.0f, 12.0f, 7.4f, 5.4f, 3.8f, 2.67f, 162.7f, 71.0f, 60.0f, 37.0f, 25.0f, 19.6f, 15.0f, 11.1f};
   return (Z >= 1 && Z <= 18) ? t[Z - 1] : 1.0f;

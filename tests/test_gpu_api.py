@@ -198,3 +198,27 @@ def test_batched_calculator_matches_oracle(oracle_params):
     np.testing.assert_allclose(out["dipole_vec"][:-1].cpu().numpy(), ref["dipole_vec"], atol=5e-5)
     np.testing.assert_allclose(out["hirshfeld_ratios"][:-1].cpu().numpy(), ref["hirshfeld_ratios"], atol=1e-5)
     assert float(out["hirshfeld_ratios"][-1]) == 0.0
+
+
+def test_ethanol_dipole_and_hirshfeld_reference_vector(reference_goldens):
+    """The reference's published float32 outputs for ethanol frame 49 through its batched calculator with lr_cutoff = 100
+    (examples/evaluate_so3lr_on_dataset.ipynb): energy 1e-5 relative, forces 1e-4 eV/A, dipole and Hirshfeld ratios 1e-5.
+    Inputs are padded the way the notebook pads them (one padding node, one padding graph)."""
+    from so3lr_b200 import So3lr
+    g = reference_goldens
+    Z, R = g["ethanol_Z"], np.asarray(g["ethanol_R"], dtype=np.float32)
+    n = len(Z)
+    ii, jj = O.neighbor_list(R, None, 4.5, ordered=False)
+    il, jl = np.nonzero(~np.eye(n, dtype=bool))
+    pad = lambda a, m: np.concatenate([a, np.full(m - len(a), n)]).astype(np.int32)
+    inputs = dict(positions=np.concatenate([R, np.zeros((1, 3), np.float32)]), atomic_numbers=np.concatenate([Z, [1]]),
+                  idx_i=pad(ii, len(ii) + 1), idx_j=pad(jj, len(jj) + 1), idx_i_lr=pad(il, len(il) + 1), idx_j_lr=pad(jl, len(jl) + 1),
+                  cell=None, total_charge=np.zeros(2), num_unpaired_electrons=np.zeros(2),
+                  batch_segments=np.concatenate([np.zeros(n, np.int64), [1]]), node_mask=np.concatenate([np.ones(n, bool), [False]]),
+                  graph_mask=np.array([True, False]))
+    out = So3lr(lr_cutoff=100.0)(inputs)
+    e = float(out["energy"][0])
+    assert abs(e - float(g["ethanol_energy"])) < 1e-5 * abs(float(g["ethanol_energy"]))
+    np.testing.assert_allclose(out["forces"][:n].cpu().numpy(), g["ethanol_forces"], atol=1e-4)
+    np.testing.assert_allclose(out["dipole_vec"][0].cpu().numpy(), g["ethanol_dipole_vec"], atol=1e-5)
+    np.testing.assert_allclose(out["hirshfeld_ratios"][:n].cpu().numpy(), g["ethanol_hirshfeld_ratios"], atol=1e-5)

@@ -115,3 +115,19 @@ def test_radial_filter_table_function(oracle_params):
             np.testing.assert_allclose(w, wt.detach().numpy(), atol=1e-9)
             g = torch.autograd.grad(wt[7] + wt[200], d)[0].item()
             np.testing.assert_allclose(dw[7] + dw[200], g, rtol=1e-8, atol=1e-9)
+
+
+def test_radial_filter_chebyshev_expansion():
+    """The 64-term Chebyshev expansion that the tiled attention kernels contract on the tensor cores reproduces the radial
+    filters and their r-derivatives over the whole cutoff range (largest |w| is 6-12, largest |dw/dr| 28-51)."""
+    blob = np.load(O.DEFAULT_BLOB)["blob"].astype(np.float32)
+    for layer in (1, 2):
+        worst = worst_d = 0.0
+        for r in np.concatenate([np.linspace(0.02, 4.49, 60), [0.9572, 1.09, 1.5139, 2.76]]):
+            w = np.zeros(256); dw = np.zeros(256); wc = np.zeros(256); dwc = np.zeros(256)
+            lib.so3lr_b200_host_radial_filter(_p(blob), layer, float(r), _p(w), _p(dw))
+            lib.so3lr_b200_host_radial_filter_chebyshev(_p(blob), layer, float(r), _p(wc), _p(dwc))
+            worst = max(worst, np.abs(w - wc).max())
+            worst_d = max(worst_d, np.abs(dw - dwc).max())
+        assert worst < 1e-6, (layer, worst)
+        assert worst_d < 5e-4, (layer, worst_d)

@@ -35,3 +35,14 @@ def test_periodic_water_matches_reference_goldens(oracle_params, reference_golde
     assert abs(out["energy"] - float(g["water_energy_jaxmd"])) < 1e-4
     np.testing.assert_allclose(out["energy"], float(g["water_energy_ase"]), rtol=1e-6)
     np.testing.assert_allclose(out["forces"], g["water_forces_ase"], atol=5e-4)
+
+
+def test_ethanol_dipole_and_hirshfeld_match_the_reference_notebook(oracle_params, reference_goldens):
+    """The reference's one published vector for the dipole and the Hirshfeld ratios: ethanol frame 49 evaluated in float32 by
+    So3lr(calculate_forces=True, lr_cutoff=100) (examples/evaluate_so3lr_on_dataset.ipynb, output of `pprint(output)`)."""
+    g = reference_goldens
+    out = O.energy_forces(oracle_params, g["ethanol_R"], g["ethanol_Z"], None, cutoff_lr=100.0, damping=2.0, lr_format="sparse")
+    assert abs(out["energy"] - float(g["ethanol_energy"])) < 1e-5 * abs(float(g["ethanol_energy"]))
+    np.testing.assert_allclose(out["forces"], g["ethanol_forces"], atol=1e-5)
+    np.testing.assert_allclose(out["dipole_vec"][0], g["ethanol_dipole_vec"], atol=1e-5)
+    np.testing.assert_allclose(out["hirshfeld_ratios"], g["ethanol_hirshfeld_ratios"], atol=1e-5)
