@@ -74,6 +74,17 @@ SO3LR_B200_API int so3lr_b200_system_destroy(so3lr_b200_system* sys);
 /* New cell (NPT); forces a list rebuild on the next evaluation. */
 SO3LR_B200_API int so3lr_b200_system_set_cell(so3lr_b200_system* sys, const float* cell);
 
+/* Deferred skin test.  By default every evaluation with skin > 0 reads one flag word back from the device (has an atom
+ * moved further than skin / 2 since the lists were built?) before it launches its kernels: one host wait per step.  With
+ * this mode on, the flag of step k is copied to pinned memory asynchronously and read at step k + 1, so an evaluation only
+ * enqueues work on the caller's stream; the trigger distance becomes skin / 2 - margin so that the lists still cover the one
+ * extra step (margin >= the largest displacement of an atom in one step; 0.05 A covers a 0.5 fs step far beyond 1000 K).
+ * Non-finite positions and a timed-out tensor-core wait are likewise reported by the following call.  A step that does
+ * rebuild its lists still synchronises (list sizes are read back to size the buffers).
+ * Replaces: the `nbrs.update` + `did_buffer_overflow` polling of so3lr/cli/so3lr_md.py:862-876,1143-1152, which XLA runs
+ * inside the compiled step without a host round trip. */
+SO3LR_B200_API int so3lr_b200_system_defer_skin_test(so3lr_b200_system* sys, int enable, float margin);
+
 /* Energy + forces from positions that already live on the device (positions_dev: n_atoms x 3 float32, Cartesian,
  * Angstrom).  Outputs are device pointers and may be NULL when not wanted:
  *   forces_dev (n_atoms x 3), e_atom_dev (n_atoms), energy_dev (n_graphs doubles), charges_dev (n_atoms),

@@ -39,6 +39,7 @@ def _load():
         "so3lr_b200_system_create": (i32, [p, i32, p, i32, p, p, p, p, C.POINTER(Options), C.POINTER(p)]),
         "so3lr_b200_system_destroy": (i32, [p]),
         "so3lr_b200_system_set_cell": (i32, [p, p]),
+        "so3lr_b200_system_defer_skin_test": (i32, [p, i32, f32]),
         "so3lr_b200_system_compute": (i32, [p, p, p, p, p, p, p, p, p]),
         "so3lr_b200_system_compute_host": (i32, [p, p, p, p, p, p, p]),
         "so3lr_b200_system_aux": (i32, [p, C.POINTER(p), C.POINTER(p), C.POINTER(p)]),

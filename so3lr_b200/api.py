@@ -79,10 +79,16 @@ class So3lrPotentialB200:
     (so3lr/jaxmd_utils.py:99,113,138-141): attributes `cutoff`, `long_range_cutoff`; `pot(graph)` -> per-atom
     energies, `pot(graph, has_aux=True)` -> (energies, aux dict)."""
 
+    MAX_CACHED_SYSTEMS = 4      # evaluation contexts kept per potential (each holds every per-atom workspace of its system)
+
     def __init__(self, lr_cutoff=12.0, dispersion_energy_cutoff_lr_damping=2.0, neighborlist_format_lr="ordered_sparse",
                  dtype=np.float32, device=None):
-        if np.dtype(dtype) != np.float32:
-            raise NotImplementedError("so3lr_b200 computes in float32 (the reference CLI default, so3lr_cli.py:99)")
+        """`dtype` is the dtype of the returned energies and gradients, as in the reference where it "determines the output
+        dtype" of float32 parameters (tests/test_jaxmd.py:210-212): float32 or float64.  The kernels compute in float32 either
+        way; with float64 the float32 results are widened, so they carry float32 accuracy (1e-7 relative on energies)."""
+        if np.dtype(dtype) not in (np.dtype(np.float32), np.dtype(np.float64)):
+            raise ValueError("dtype must be float32 or float64")
+        self.dtype = torch.float64 if np.dtype(dtype) == np.dtype(np.float64) else torch.float32
         self.cutoff = CUTOFF_SR
         self.long_range_cutoff = lr_cutoff
         self.damping = dispersion_energy_cutoff_lr_damping
@@ -90,24 +96,34 @@ class So3lrPotentialB200:
         self.device = _dev(device)
         self._systems = {}
 
-    def system_for(self, species, cell=None, graph_start=None):
+    def system_for(self, species, cell=None, graph_start=None, total_charge=None, num_unpaired=None):
         Z = np.ascontiguousarray(species.detach().cpu().numpy() if torch.is_tensor(species) else species, dtype=np.int32)
-        key = (Z.tobytes(), None if graph_start is None else np.asarray(graph_start).tobytes())
-        s = self._systems.get(key)
+        n_graphs = 1 if graph_start is None else len(graph_start) - 1
+
+        def per_graph(v):
+            if v is None:
+                return None
+            a = np.asarray(torch.as_tensor(v).detach().cpu(), dtype=np.float32).reshape(-1)
+            a = np.broadcast_to(a, (n_graphs,)) if a.size == 1 else a[:n_graphs]
+            return None if not a.any() else np.ascontiguousarray(a)
+
+        tq, ts = per_graph(total_charge), per_graph(num_unpaired)
+        key = (Z.tobytes(), None if graph_start is None else np.asarray(graph_start).tobytes(),
+               None if tq is None else tq.tobytes(), None if ts is None else ts.tobytes())
+        s = self._systems.pop(key, None)
         if s is None:
             s = System(Z, None, cutoff_lr=self.long_range_cutoff, damping=self.damping, lr_format=self.neighborlist_format_lr,
-                       graph_start=graph_start, device=self.device.index or 0)
-            self._systems[key] = s
+                       graph_start=graph_start, total_charge=tq, num_unpaired=ts, device=self.device.index or 0)
+        self._systems[key] = s                      # most recently used last
+        while len(self._systems) > self.MAX_CACHED_SYSTEMS:
+            self._systems.pop(next(iter(self._systems)))
         return s
 
     def __call__(self, graph: Graph, has_aux: bool = False):
         for name in ("k_grid", "k_smearing"):
             if getattr(graph, name) is not None:
                 raise NotImplementedError("k-space electrostatics (Ewald / PME) is not part of this library")
-        tq = graph.total_charge
-        if tq is not None and float(torch.as_tensor(tq).abs().sum()) != 0.0:
-            raise NotImplementedError("charged systems are not supported")
-        s = self.system_for(graph.nodes)
+        s = self.system_for(graph.nodes, total_charge=graph.total_charge, num_unpaired=graph.num_unpaired_electrons)
         edges, edges_lr = graph.edges, graph.edges_lr
         idx_i, idx_j, idx_i_lr, idx_j_lr = graph.centers, graph.others, graph.idx_i_lr, graph.idx_j_lr
         # the kernels want lists grouped by centre; jax-md style lists already are
@@ -120,10 +136,11 @@ class So3lrPotentialB200:
             idx_i_lr, idx_j_lr, edges_lr = idx_i_lr[perm_lr], idx_j_lr[perm_lr], edges_lr[perm_lr]
         aux = {}
         e = _GraphEnergy.apply(edges.to(self.device, torch.float32), edges_lr.to(self.device, torch.float32), s, idx_i, idx_j,
-                               idx_i_lr, idx_j_lr, aux)
+                               idx_i_lr, idx_j_lr, aux).to(self.dtype)
         if not has_aux:
             return e
         aux.update(s.aux())
+        aux = {k: (v.to(self.dtype) if torch.is_tensor(v) and v.is_floating_point() else v) for k, v in aux.items()}
         if graph.positions is not None:
             aux["dipole_vec"] = (aux["partial_charges"][:, None] * graph.positions).sum(0)
         return e, aux
@@ -259,10 +276,12 @@ class _Transform(torch.autograd.Function):
         return g, None
 
 
-def neighbor_list_featurizer(displacement_fn, species, fractional_coordinates=True, device=None):
-    """so3lr/jaxmd_utils.py:11-77: endpoints gather, minimum-image displacement, Graph assembly.  Positions and box keep the
-    precision they are given in (float64 positions in a 1000 A box lose nothing); the displacements are handed to the
-    float32 kernels."""
+def neighbor_list_featurizer(displacement_fn, species, fractional_coordinates=True, device=None, total_charge=0.0):
+    """so3lr/jaxmd_utils.py:11-77 (and its CLI twin with `total_charge`, so3lr/cli/so3lr_md.py:606-685): endpoints gather,
+    minimum-image displacement, Graph assembly.  Positions and box keep the precision they are given in (float64 positions in
+    a 1000 A box lose nothing); the displacements are handed to the float32 kernels.  `perturbation` (a scalar or a 3x3
+    matrix) deforms every displacement, dR -> perturbation dR, as jax-md's displacement functions do with that keyword; it is
+    differentiable, which is how the reference's NPT obtains the strain derivative of the energy (jaxmd_utils.py:48-51)."""
     dev = _dev(device)
     species_t = torch.as_tensor(np.asarray(species), dtype=torch.int32, device=dev)
 
@@ -283,20 +302,30 @@ def neighbor_list_featurizer(displacement_fn, species, fractional_coordinates=Tr
                 cell_t = torch.eye(3, dtype=R.dtype, device=dev) * b.reshape(-1)[0]
             else:
                 raise ValueError(f"Invalid box shape {tuple(b.shape)}. Expected (3, 3), (3,), or (1,).")
-        for k in ("k_grid", "k_smearing", "perturbation"):
+        for k in ("k_grid", "k_smearing"):
             if kwargs.get(k) is not None:
-                raise NotImplementedError(f"`{k}` is not supported by this library")
+                raise NotImplementedError(f"`{k}` (k-space electrostatics) is not supported by this library")
+        pert = kwargs.get("perturbation")
         Rc = _Transform.apply(R, cell_t) if (cell_t is not None and fractional_coordinates) else R
         neighbor, neighbor_lr = torch.as_tensor(neighbor, device=dev), torch.as_tensor(neighbor_lr, device=dev)
         idx_i, idx_j = neighbor[0].long(), neighbor[1].long()
         idx_i_lr, idx_j_lr = neighbor_lr[0].long(), neighbor_lr[1].long()
         cl = lambda a: a.clamp(max=n - 1)   # JAX gathers clamp the padding index N to N-1
         # the kernels take dR = R_j - R_i; the energy does not depend on the sign convention
-        dR = _min_image(Rc[cl(idx_j)] - Rc[cl(idx_i)], cell_t).float()
-        dR_lr = _min_image(Rc[cl(idx_j_lr)] - Rc[cl(idx_i_lr)], cell_t).float()
-        return Graph(positions=None, nodes=species_t, edges=dR, centers=neighbor[0], others=neighbor[1], mask=None,
-                     total_charge=torch.zeros(1), num_unpaired_electrons=torch.zeros(1), edges_lr=dR_lr, idx_i_lr=neighbor_lr[0],
-                     idx_j_lr=neighbor_lr[1], cell=cell_t)
+        dR = _min_image(Rc[cl(idx_j)] - Rc[cl(idx_i)], cell_t)
+        dR_lr = _min_image(Rc[cl(idx_j_lr)] - Rc[cl(idx_i_lr)], cell_t)
+        if pert is not None:
+            p = pert if torch.is_tensor(pert) else torch.as_tensor(pert)
+            p = p.to(device=dev, dtype=dR.dtype)
+            if p.ndim == 0 or p.numel() == 1:
+                dR, dR_lr = dR * p.reshape(()), dR_lr * p.reshape(())
+            else:
+                dR, dR_lr = dR @ p.T, dR_lr @ p.T
+                if cell_t is not None:
+                    cell_t = cell_t @ p.T
+        return Graph(positions=None, nodes=species_t, edges=dR.float(), centers=neighbor[0], others=neighbor[1], mask=None,
+                     total_charge=torch.tensor([float(total_charge)]), num_unpaired_electrons=torch.zeros(1), edges_lr=dR_lr.float(),
+                     idx_i_lr=neighbor_lr[0], idx_j_lr=neighbor_lr[1], cell=cell_t)
 
     return featurize
 
@@ -316,8 +345,9 @@ def force(energy_fn):
 def to_jax_md(potential, displacement_or_metric, box_size, species=None, dr_threshold: float = 0.0, capacity_multiplier: float = 1.25,
               buffer_size_multiplier_sr: float = 1.25, buffer_size_multiplier_lr: float = 1.25,
               minimum_cell_size_multiplier_sr: float = 1.0, minimum_cell_size_multiplier_lr: float = 1.0,
-              disable_cell_list: bool = False, fractional_coordinates: bool = True, **neighbor_kwargs):
-    """so3lr/jaxmd_utils.py:80-143: returns (neighbor_fn, neighbor_fn_lr, energy_fn)."""
+              disable_cell_list: bool = False, fractional_coordinates: bool = True, total_charge: float = 0.0, **neighbor_kwargs):
+    """so3lr/jaxmd_utils.py:80-143 (with the `total_charge` of the CLI's variant, so3lr/cli/so3lr_md.py:690-782): returns
+    (neighbor_fn, neighbor_fn_lr, energy_fn)."""
     neighbor_fn = neighbor_list(displacement_or_metric, box_size, potential.cutoff, dr_threshold, capacity_multiplier,
                                 buffer_size_multiplier_sr, minimum_cell_size_multiplier_sr,
                                 fractional_coordinates=fractional_coordinates, format=1, disable_cell_list=disable_cell_list,
@@ -327,7 +357,7 @@ def to_jax_md(potential, displacement_or_metric, box_size, species=None, dr_thre
                                    fractional_coordinates=fractional_coordinates, format=2, disable_cell_list=disable_cell_list,
                                    **neighbor_kwargs)
     featurizer = neighbor_list_featurizer(displacement_or_metric, species, fractional_coordinates=fractional_coordinates,
-                                          device=potential.device)
+                                          device=potential.device, total_charge=total_charge)
 
     def energy_fn(R, neighbor, neighbor_lr, has_aux=False, **energy_fn_kwargs):
         graph = featurizer(R, neighbor, neighbor_lr, **energy_fn_kwargs)
@@ -368,12 +398,9 @@ def make_so3lr(lr_cutoff=12.0, dispersion_energy_cutoff_lr_damping=2.0, calculat
             n_graphs = int(gm_t.shape[0])
         if np.any(np.diff(bs_np) < 0):
             raise ValueError("batch_segments must be non-decreasing (atoms of one graph contiguous)")
-        for key in ("total_charge", "num_unpaired_electrons"):
-            v = inputs.get(key)
-            if v is not None and float(torch.as_tensor(v).abs().sum()) != 0.0:
-                raise NotImplementedError(f"non-zero {key} is not supported")
         graph_start = np.searchsorted(bs_np, np.arange(n_graphs + 1)).astype(np.int32)
-        s = pot.system_for(Z, graph_start=graph_start if n_graphs > 1 else None)
+        s = pot.system_for(Z, graph_start=graph_start if n_graphs > 1 else None, total_charge=inputs.get("total_charge"),
+                           num_unpaired=inputs.get("num_unpaired_electrons"))
         cell = inputs.get("cell")
         cell_t = None
         if cell is not None:
@@ -445,8 +472,9 @@ class So3lrCalculatorB200(_AseCalculator):
         if calculate_hessian:
             raise NotImplementedError("the Hessian is not provided by so3lr_b200")
         self.calculate_stress = bool(calculate_stress)
-        if np.dtype(dtype) != np.float32:
-            raise NotImplementedError("so3lr_b200 computes in float32")
+        if np.dtype(dtype) not in (np.dtype(np.float32), np.dtype(np.float64)):
+            raise ValueError("dtype must be float32 or float64")
+        self.dtype = np.dtype(dtype)        # results are float32 computations, returned in this dtype
         self.lr_cutoff, self.damping, self.skin = lr_cutoff, dispersion_energy_cutoff_lr_damping, skin
         self.device = _dev(device)
         self._sys, self._key = None, None
@@ -456,19 +484,24 @@ class So3lrCalculatorB200(_AseCalculator):
         Z = np.asarray(atoms.get_atomic_numbers(), dtype=np.int32)
         pbc = np.asarray(atoms.get_pbc()).any()
         cell = np.asarray(atoms.get_cell(), dtype=np.float64) if pbc else None
-        key = (Z.tobytes(), None if cell is None else cell.tobytes())
+        info = getattr(atoms, "info", None) or {}
+        charge = float(info.get("charge", 0.0))
+        unpaired = float(info.get("multiplicity", 1.0)) - 1.0
+        key = (Z.tobytes(), None if cell is None else cell.tobytes(), charge, unpaired)
         if self._key != key:
-            if self._sys is not None and self._key[0] == key[0] and cell is not None and self._key[1] is not None:
+            if self._sys is not None and self._key[0] == key[0] and cell is not None and self._key[1] is not None and self._key[2:] == key[2:]:
                 self._sys.set_cell(cell)
             else:
                 self._sys = System(Z, cell, cutoff_lr=self.lr_cutoff, damping=self.damping, skin=self.skin,
+                                   total_charge=[charge] if charge else None, num_unpaired=[unpaired] if unpaired else None,
                                    device=self.device.index or 0)
                 if self.calculate_stress:
                     self._sys.enable_virial(True)
             self._key = key
         out = self._sys.compute_host(np.asarray(atoms.get_positions(), dtype=np.float32))
         self.results = dict(energy=float(out["energy"].sum()), forces=out["forces"].astype(np.float64),
-                            charges=out["partial_charges"], hirshfeld_ratios=out["hirshfeld_ratios"], dipole=out["dipole_vec"][0])
+                            charges=out["partial_charges"].astype(self.dtype), hirshfeld_ratios=out["hirshfeld_ratios"].astype(self.dtype),
+                            dipole=out["dipole_vec"][0].astype(self.dtype))
         if self.calculate_stress and cell is not None:
             w = self._sys.virial().cpu().numpy() / abs(np.linalg.det(cell))
             self.results["stress"] = np.array([w[0, 0], w[1, 1], w[2, 2], w[1, 2], w[0, 2], w[0, 1]])

@@ -625,7 +625,7 @@ void launch_proj_fwd(cudaStream_t s, const LayerDev& L, const float* x, int n, f
 void launch_proj_bwd(cudaStream_t s, const LayerDev& L, const float* g_qkv, int n, float* gx, int accumulate) {
   if (n <= 0) return;
   int blocks = (n + PROJ_TILE - 1) / PROJ_TILE;
-  if (blocks > 148 * 2) blocks = 148 * 2;
+  if (blocks > sm_count() * 2) blocks = sm_count() * 2;
   { proj_bwd_kernel<<<blocks, 512, kSmemProjBwd, s>>>(L.proj, g_qkv, n, gx, accumulate); count_launch(); }
 }
 void launch_atom_post_fwd(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, float* z1,

@@ -636,7 +636,7 @@ void launch_attn_fwd_mma(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
                          const float* qkv, const float* x_in, const float* ev_in, float* xa, float* ev1) {
   if (n_recv <= 0) return;
   int blocks = (n_recv + FW_WARPS - 1) / FW_WARPS;
-  if (blocks > 148) blocks = 148;
+  if (blocks > sm_count()) blocks = sm_count();
   { attn_fwd_mma_kernel<<<blocks, FW_WARPS * 32, kSmemFw, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1); count_launch(); }
 }
 
@@ -645,7 +645,7 @@ void launch_attn_bwd_mma(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
                          float* F, float* virial) {
   if (n_recv <= 0) return;
   int blocks = (n_recv + BW_WARPS - 1) / BW_WARPS;
-  if (blocks > 148) blocks = 148;
+  if (blocks > sm_count()) blocks = sm_count();
   { attn_bwd_mma_kernel<<<blocks, BW_WARPS * 32, kSmemBw, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F, virial); count_launch(); }
 }
 

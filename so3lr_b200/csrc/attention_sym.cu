@@ -529,7 +529,7 @@ void launch_attn_fwd_sym(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
                          const float* qkv, const float* x_in, const float* ev_in, float* xa, float* ev1) {
   if (n_recv <= 0) return;
   int blocks = (n_recv + FW_WARPS - 1) / FW_WARPS;
-  if (blocks > 148 * 2) blocks = 148 * 2;
+  if (blocks > sm_count() * 2) blocks = sm_count() * 2;
   if (L.has_spherical)
     { attn_fwd_sym_kernel<true><<<blocks, FW_WARPS * 32, kSmemFwSph, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, x_in, ev_in, xa, ev1); count_launch(); }
   else
@@ -541,7 +541,7 @@ void launch_attn_bwd_sym(cudaStream_t s, const LayerDev& L, int n_recv, int n, c
                          float* F, int first_layer, float* virial) {
   if (n_recv <= 0) return;
   int blocks = (n_recv + BW_WARPS - 1) / BW_WARPS;
-  if (blocks > 148) blocks = 148;
+  if (blocks > sm_count()) blocks = sm_count();
   if (first_layer)
     { attn_bwd_sym_kernel<true><<<blocks, BW_WARPS * 32, kSmemBwFirst, s>>>(L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F, virial); count_launch(); }
   else

@@ -60,15 +60,13 @@ constexpr int kEvStride = 28;                                // floats per stage
 constexpr int kOffFwStIJ = kOffFwMisc + 64;                  // staged inputs of the next tile: (i, j) | displacement | ev rows of both atoms
 constexpr int kOffFwStD = kOffFwStIJ + TE * 8;
 constexpr int kOffFwStEv = kOffFwStD + TE * 16;
-constexpr int kOffFwOps = kOffFwStEv + TE * 2 * kEvStride * 4;   // 2 x 18 precomputed MMAs
-constexpr int kSmemFwd = kOffFwOps + 36 * 32;
+constexpr int kSmemFwd = kOffFwStEv + TE * 2 * kEvStride * 4;
 // reverse kernel: the filter tile holds 64 edges at a time
 constexpr int kOffBwW = kOffA + kARegion;
 constexpr int kOffBwRec = kOffBwW + 64 * kWStride * 4;
 constexpr int kOffBwSph = kOffBwRec + TE * kBwRec * 4;
 constexpr int kOffBwMisc = kOffBwSph + 320 * 4;
-constexpr int kOffBwOps = kOffBwMisc + 64;                   // 2 x 18 forward + 2 x 48 reverse precomputed MMAs
-constexpr int kSmemBwd = kOffBwOps + (36 + 96) * 32;
+constexpr int kSmemBwd = kOffBwMisc + 64;
 static_assert(kSmemFwd <= 232448 && kSmemBwd <= 232448, "shared memory budget of one CTA per SM");
 
 __device__ __forceinline__ float invw(int l) {
@@ -221,17 +219,17 @@ __device__ __forceinline__ void store_chebyshev(unsigned char* a_hi, int row, fl
   store_chebyshev_half(a_hi, row, r, valid, 1);
 }
 // hidden layer of spherical filter f into chunks 8 + 4 f .. 11 + 4 f
-__device__ __forceinline__ void store_spherical_hidden_f(unsigned char* a_hi, int row, const float* s, const float* sph, int f) {
+__device__ __forceinline__ void store_spherical_hidden_f(unsigned char* a_hi, int row, const float* s, const float* sph8, int f) {
+  // sph8: per (filter, hidden unit) eight floats: the four first-layer weights, the bias, padding
 #pragma unroll
   for (int c8 = 0; c8 < 4; ++c8) {
     float v[8];
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
-      const int c = 8 * c8 + q;
-      float z = sph[256 + f * 32 + c];
-#pragma unroll
-      for (int l = 0; l < 4; ++l) z = fmaf(s[l], sph[f * 128 + l * 32 + c], z);
-      v[q] = silu_f(z);
+      const float* p = sph8 + (f * 32 + 8 * c8 + q) * 8;
+      const float4 k = ld4(p);
+      const float z = fmaf(s[0], k.x, fmaf(s[1], k.y, fmaf(s[2], k.z, fmaf(s[3], k.w, p[4]))));
+      v[q] = __fdividef(z, 1.f + __expf(-z));
     }
     store_chunk(a_hi, 8 + 4 * f + c8, row, v);
   }
@@ -255,80 +253,69 @@ __device__ __forceinline__ void store_spherical_hidden(unsigned char* a_hi, int 
     }
 }
 
-// One tcgen05.mma with all its operands, precomputed once per kernel: the issuing thread only reads the entry and fires.
-struct __align__(16) MmaOp {
-  unsigned long long a, b;     // shared-memory matrix descriptors
-  uint32_t d, idesc, acc, pad; // TMEM address of the accumulator, instruction descriptor, accumulate flag
-};
-__device__ __forceinline__ void put_op(MmaOp* ops, int& n, uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-  MmaOp o;
-  o.a = a; o.b = b; o.d = d; o.idesc = idesc; o.acc = acc; o.pad = 0;
-  ops[n++] = o;
+// Descriptors differ only in their start-address field (bits 0..13, in units of 16 bytes): desc(addr) = base + (addr >> 4).
+// The issuing thread keeps everything in registers -- shared-memory loads inside the issue loop wait behind the operand
+// traffic of the MMAs already running and throttle the chain.
+__device__ __forceinline__ uint64_t desc_base(uint32_t lbo, uint32_t sbo) {
+  return ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | ((uint64_t)1 << 46);
 }
-__device__ __forceinline__ void issue_ops(const MmaOp* ops, int n) {
-#pragma unroll 2
-  for (int k = 0; k < n; ++k) {
-    const uint4 lo = *reinterpret_cast<const uint4*>(&ops[k]);
-    const uint4 hi = *(reinterpret_cast<const uint4*>(&ops[k]) + 1);
-    const uint64_t a = ((uint64_t)lo.y << 32) | lo.x, b = ((uint64_t)lo.w << 32) | lo.z;
-    umma(hi.x, a, b, hi.y, hi.z);
-  }
-}
-constexpr int kFwdOps = 24;        // forward kernel: 4 K-steps x 3 MMAs of N = 256 (radial) + 2 filters x 2 K-steps x 3 MMAs of N = 128
 constexpr int kFilterOps = 18;     // per filter: 4 K-steps of Chebyshev terms + 2 of the spherical hidden layer, 3 MMAs each
-constexpr int kReverseOps = 48;    // per filter: 8 K-steps of features x (radial | spherical) x 3 MMAs
 
-// Forward kernel, K-major weight image (rows = output features, 8 consecutive K entries per 16 bytes):
-//   CT hi | CT lo : [256 features][64 terms], core (n/8, k/8) at (n/8) * 1024 + (k/8) * 128           (2 x 32 KB)
-//   K2T_f hi | lo : [128 features][32 hidden], core (n/8, k/8) at (n/8) * 512 + (k/8) * 128           (4 x 8 KB)
-__device__ __noinline__ void build_forward_ops(MmaOp* ops, uint32_t tmem, uint32_t a_hi, uint32_t img) {
-  const uint32_t a_lo = a_hi + kAHalf;
-  const uint32_t c_hi = img, c_lo = img + 32768;
+// Forward kernel, K-major weight image (rows = output features, 8 consecutive K entries per 16 bytes; the core matrices of
+// one K chunk are contiguous over the rows, the layout the tensor cores fetch fastest):
+//   CT hi | CT lo : [256 features][64 terms], core (n/8, k/8) at (k/8) * 4096 + (n/8) * 128           (2 x 32 KB)
+//   K2T_f hi | lo : [128 features][32 hidden], core (n/8, k/8) at (k/8) * 2048 + (n/8) * 128          (4 x 8 KB)
+// w = Phi * C + hs_f * K2_f: main accumulators in TMEM columns [0, 256), cross accumulators in [256, 512)
+__device__ __noinline__ void issue_forward_mma(uint32_t tmem, uint32_t a_hi, uint32_t img) {
+  const uint64_t da = desc_base(kLboA, 128) + (a_hi >> 4), dal = da + (kAHalf >> 4);
+  const uint64_t dc = desc_base(4096, 128) + (img >> 4), dcl = dc + (32768 >> 4);
+  const uint64_t dk = desc_base(2048, 128) + ((img + 65536) >> 4), dkl = dk + (16384 >> 4);
   const uint32_t id256 = make_idesc(256, 0), id128 = make_idesc(128, 0);
-  int n = 0;
+#pragma unroll
   for (int ks = 0; ks < 4; ++ks) {
-    const uint64_t ah = make_desc(a_hi + ks * 2 * kLboA, kLboA, 128), al = make_desc(a_lo + ks * 2 * kLboA, kLboA, 128);
-    const uint64_t bh = make_desc(c_hi + ks * 2 * 128, 128, 1024), bl = make_desc(c_lo + ks * 2 * 128, 128, 1024);
-    put_op(ops, n, tmem, ah, bh, id256, ks > 0);
-    put_op(ops, n, tmem + 256, ah, bl, id256, ks > 0);
-    put_op(ops, n, tmem + 256, al, bh, id256, 1);
+    const uint64_t ah = da + ks * (2 * kLboA >> 4), al = dal + ks * (2 * kLboA >> 4);
+    const uint64_t bh = dc + ks * (2 * 4096 >> 4), bl = dcl + ks * (2 * 4096 >> 4);
+    umma(tmem, ah, bh, id256, ks > 0);
+    umma(tmem + 256, ah, bl, id256, ks > 0);
+    umma(tmem + 256, al, bh, id256, 1);
   }
-  for (int f = 0; f < 2; ++f) {
-    const uint32_t k2_hi = img + 65536 + (uint32_t)f * 8192, k2_lo = k2_hi + 16384;
+#pragma unroll
+  for (int f = 0; f < 2; ++f)
+#pragma unroll
     for (int ks = 0; ks < 2; ++ks) {
       const int chunk = 8 + 4 * f + 2 * ks;
-      const uint64_t ah = make_desc(a_hi + chunk * kLboA, kLboA, 128), al = make_desc(a_lo + chunk * kLboA, kLboA, 128);
-      const uint64_t bh = make_desc(k2_hi + ks * 2 * 128, 128, 512), bl = make_desc(k2_lo + ks * 2 * 128, 128, 512);
-      put_op(ops, n, tmem + 128 * f, ah, bh, id128, 1);
-      put_op(ops, n, tmem + 256 + 128 * f, ah, bl, id128, 1);
-      put_op(ops, n, tmem + 256 + 128 * f, al, bh, id128, 1);
+      const uint64_t ah = da + chunk * (kLboA >> 4), al = dal + chunk * (kLboA >> 4);
+      const uint64_t bh = dk + (f * 8192 + ks * 2 * 2048 >> 4), bl = dkl + (f * 8192 + ks * 2 * 2048 >> 4);
+      umma(tmem + 128 * f, ah, bh, id128, 1);
+      umma(tmem + 256 + 128 * f, ah, bl, id128, 1);
+      umma(tmem + 256 + 128 * f, al, bh, id128, 1);
     }
-  }
 }
 
-// w_f = Phi * C_f + hs_f * K2_f for the 128 rows of the A operand and one filter f: main accumulators in TMEM columns
-// [128 f, 128 f + 128), cross accumulators 256 columns above
-__device__ __noinline__ void build_filter_ops(MmaOp* ops, uint32_t tmem, uint32_t a_hi, uint32_t img, int f) {
-  const uint32_t a_lo = a_hi + kAHalf;
-  const uint32_t c_hi = img + (uint32_t)f * 16 * 128, c_lo = c_hi + 32768;
-  const uint32_t k2_hi = img + 65536 + (uint32_t)f * 8192, k2_lo = k2_hi + 16384;
+// Reverse kernel, one image for both directions (see model.cu): C[m][c] core (m/8, c/8) at (m/8) * 4096 + (c/8) * 128,
+// K2_f[h][n] core (h/8, n/8) at (h/8) * 2048 + (n/8) * 128.  Forward product (MN-major B): w_f = Phi * C_f + hs_f * K2_f,
+// main accumulators in TMEM columns [128 f, 128 f + 128), cross 256 columns above.
+__device__ __noinline__ void issue_filter_mma(uint32_t tmem, uint32_t a_hi, uint32_t img, int f) {
+  const uint64_t da = desc_base(kLboA, 128) + (a_hi >> 4), dal = da + (kAHalf >> 4);
+  const uint64_t dc = desc_base(4096, 128) + ((img + f * 16 * 128) >> 4), dcl = dc + (32768 >> 4);
+  const uint64_t dk = desc_base(2048, 128) + ((img + 65536 + f * 8192) >> 4), dkl = dk + (16384 >> 4);
   const uint32_t id128 = make_idesc(128, 1);
   const uint32_t d_main = tmem + 128 * f, d_cross = d_main + 256;
-  int n = 0;
-  for (int ks = 0; ks < 4; ++ks) {      // K = 16 Chebyshev terms per step: two core matrices of A, two of C
-    const uint64_t ah = make_desc(a_hi + ks * 2 * kLboA, kLboA, 128), al = make_desc(a_lo + ks * 2 * kLboA, kLboA, 128);
-    const uint64_t bh = make_desc(c_hi + ks * 2 * 4096, 4096, 128), bl = make_desc(c_lo + ks * 2 * 4096, 4096, 128);
-    put_op(ops, n, d_main, ah, bh, id128, ks > 0);
-    put_op(ops, n, d_cross, ah, bl, id128, ks > 0);
-    put_op(ops, n, d_cross, al, bh, id128, 1);
+#pragma unroll
+  for (int ks = 0; ks < 4; ++ks) {
+    const uint64_t ah = da + ks * (2 * kLboA >> 4), al = dal + ks * (2 * kLboA >> 4);
+    const uint64_t bh = dc + ks * (2 * 4096 >> 4), bl = dcl + ks * (2 * 4096 >> 4);
+    umma(d_main, ah, bh, id128, ks > 0);
+    umma(d_cross, ah, bl, id128, ks > 0);
+    umma(d_cross, al, bh, id128, 1);
   }
+#pragma unroll
   for (int ks = 0; ks < 2; ++ks) {
-    const int chunk = 8 + 4 * f + 2 * ks;
-    const uint64_t ah = make_desc(a_hi + chunk * kLboA, kLboA, 128), al = make_desc(a_lo + chunk * kLboA, kLboA, 128);
-    const uint64_t bh = make_desc(k2_hi + ks * 2 * 2048, 2048, 128), bl = make_desc(k2_lo + ks * 2 * 2048, 2048, 128);
-    put_op(ops, n, d_main, ah, bh, id128, 1);
-    put_op(ops, n, d_cross, ah, bl, id128, 1);
-    put_op(ops, n, d_cross, al, bh, id128, 1);
+    const uint64_t ah = da + (8 + 4 * f + 2 * ks) * (kLboA >> 4), al = dal + (8 + 4 * f + 2 * ks) * (kLboA >> 4);
+    const uint64_t bh = dk + ks * (2 * 2048 >> 4), bl = dkl + ks * (2 * 2048 >> 4);
+    umma(d_main, ah, bh, id128, 1);
+    umma(d_cross, ah, bl, id128, 1);
+    umma(d_cross, al, bh, id128, 1);
   }
 }
 
@@ -467,14 +454,7 @@ __global__ void __launch_bounds__(kFwThreads, 1) attn_fwd_tc_kernel(const unsign
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_p;
-  MmaOp* ops = reinterpret_cast<MmaOp*>(smem + kOffFwOps);
-  if (tid == 0) {
-    const uint32_t a_hi = smem_u32(smem + kOffA), img = smem_u32(smem + kOffImg);
-    if (dbg && dbg[15]) { build_filter_ops(ops, tmem, a_hi, img, 0); build_filter_ops(ops + kFilterOps, tmem, a_hi, img, 1); }
-    else build_forward_ops(ops, tmem, a_hi, img);
-  }
-  const int n_ops = (dbg && dbg[15]) ? 2 * kFilterOps : kFwdOps;
-  __syncthreads();
+  const uint32_t a_hi = smem_u32(smem + kOffA), img = smem_u32(smem + kOffImg);
   const int col = 4 * lane;
   const int deg = degree_of(lane < kMTot ? lane : 0);
   const int k0 = 8 * warp;               // this warp's rows of the tile in the edge loop
@@ -532,9 +512,18 @@ __global__ void __launch_bounds__(kFwThreads, 1) attn_fwd_tc_kernel(const unsign
     bool done = true;
     if (tid == 0) {
       tc_fence_after();
-      issue_ops(ops, n_ops);
+#ifdef SO3LR_TC_TIMING
+      const long long q0 = clock64();
+#endif
+      issue_forward_mma(tmem, a_hi, img);
       umma_commit(mbar0);
+#ifdef SO3LR_TC_TIMING
+      const long long q1 = clock64();
+#endif
       done = mbar_wait(mbar0, parity);
+#ifdef SO3LR_TC_TIMING
+      if (dbg && blockIdx.x == 0) { dbg[9] += q1 - q0; dbg[10] += clock64() - q1; }
+#endif
     }
     if (!__syncthreads_and(done)) {
       if (tid == 0) atomicExch(err, 1);
@@ -640,24 +629,25 @@ namespace {
 // record fields (floats): 0 j | 1 i | 2 cutoff / nbar | 3 its r-derivative | 4-7 invariants | 8-11 their cotangents |
 // 12-15 dA, 16-19 dB: cotangents of the equivariant logits of edge (i<-j) and (j<-i) | 20-23, 24-27 those logits x cutoff |
 // 28-30 unit vector | 31 1/r | 32 d/dr | 33 r | 34 1 for a list entry, 0 for a padding row
-// [dPhi | dhs_f] = dw_f * [C_f^T | K2_f^T]: main accumulators in TMEM columns [128 f, 128 f + 96), cross 256 columns above
-__device__ __noinline__ void build_reverse_ops(MmaOp* ops, uint32_t tmem, uint32_t a_hi, uint32_t img, int f) {
-  const uint32_t a_lo = a_hi + kAHalf;
-  const uint32_t c_hi = img + (uint32_t)f * 16 * 128, c_lo = c_hi + 32768;
-  const uint32_t k2_hi = img + 65536 + (uint32_t)f * 8192, k2_lo = k2_hi + 16384;
+// [dPhi | dhs_f] = dw_f * [C_f^T | K2_f^T] (K-major B from the same image): main accumulators in TMEM columns
+// [128 f, 128 f + 96), cross 256 columns above
+__device__ __noinline__ void issue_reverse_mma(uint32_t tmem, uint32_t a_hi, uint32_t img, int f) {
+  const uint64_t da = desc_base(kLboA, 128) + (a_hi >> 4), dal = da + (kAHalf >> 4);
+  const uint64_t dc = desc_base(128, 4096) + ((img + f * 16 * 128) >> 4), dcl = dc + (32768 >> 4);
+  const uint64_t dk = desc_base(128, 2048) + ((img + 65536 + f * 8192) >> 4), dkl = dk + (16384 >> 4);
   const uint32_t id64 = make_idesc(64, 0), id32 = make_idesc(32, 0);
   const uint32_t d_rad = tmem + 128 * f, d_sph = d_rad + 64;
-  int n = 0;
+#pragma unroll
   for (int ks = 0; ks < 8; ++ks) {      // K = 16 features per step
-    const uint64_t ah = make_desc(a_hi + ks * 2 * kLboA, kLboA, 128), al = make_desc(a_lo + ks * 2 * kLboA, kLboA, 128);
-    const uint64_t ch = make_desc(c_hi + ks * 2 * 128, 128, 4096), cl = make_desc(c_lo + ks * 2 * 128, 128, 4096);
-    const uint64_t kh = make_desc(k2_hi + ks * 2 * 128, 128, 2048), kl = make_desc(k2_lo + ks * 2 * 128, 128, 2048);
-    put_op(ops, n, d_rad, ah, ch, id64, ks > 0);
-    put_op(ops, n, d_rad + 256, ah, cl, id64, ks > 0);
-    put_op(ops, n, d_rad + 256, al, ch, id64, 1);
-    put_op(ops, n, d_sph, ah, kh, id32, ks > 0);
-    put_op(ops, n, d_sph + 256, ah, kl, id32, ks > 0);
-    put_op(ops, n, d_sph + 256, al, kh, id32, 1);
+    const uint64_t ah = da + ks * (2 * kLboA >> 4), al = dal + ks * (2 * kLboA >> 4);
+    const uint64_t ch = dc + ks * (2 * 128 >> 4), cl = dcl + ks * (2 * 128 >> 4);
+    const uint64_t kh = dk + ks * (2 * 128 >> 4), kl = dkl + ks * (2 * 128 >> 4);
+    umma(d_rad, ah, ch, id64, ks > 0);
+    umma(d_rad + 256, ah, cl, id64, ks > 0);
+    umma(d_rad + 256, al, ch, id64, 1);
+    umma(d_sph, ah, kh, id32, ks > 0);
+    umma(d_sph + 256, ah, kl, id32, ks > 0);
+    umma(d_sph + 256, al, kh, id32, 1);
   }
 }
 
@@ -747,7 +737,7 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_tc_kernel(const unsigned char
                                                              const float* __restrict__ ev_in, const float* __restrict__ g_xa,
                                                              const float* __restrict__ gev1, float* __restrict__ g_qkv,
                                                              float* __restrict__ gev_in, float* __restrict__ F, float* __restrict__ virial,
-                                                             int* __restrict__ err) {
+                                                             int* __restrict__ err, long long* __restrict__ dbg) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float* rec = reinterpret_cast<float*>(smem + kOffBwRec);
@@ -775,20 +765,19 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_tc_kernel(const unsigned char
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_p;
-  MmaOp* ops = reinterpret_cast<MmaOp*>(smem + kOffBwOps);
-  if (tid == 0) {
-    const uint32_t a_hi = smem_u32(smem + kOffA), img = smem_u32(smem + kOffImg);
-    build_filter_ops(ops, tmem, a_hi, img, 0);
-    build_filter_ops(ops + kFilterOps, tmem, a_hi, img, 1);
-    build_reverse_ops(ops + 2 * kFilterOps, tmem, a_hi, img, 0);
-    build_reverse_ops(ops + 2 * kFilterOps + kReverseOps, tmem, a_hi, img, 1);
-  }
-  __syncthreads();
+  const uint32_t a_hi = smem_u32(smem + kOffA), img = smem_u32(smem + kOffImg);
   unsigned char* a_ptr = smem + kOffA;
   const int pad_i = ve_i[n_edges - 1];
   const int deg = degree_of(lane < kMTot ? lane : 0);
   uint32_t parity = 0;
   bool failed = false;
+#ifdef SO3LR_TC_TIMING
+  long long bph[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  long long bc0 = clock64();
+#define BW_MARK(k) do { if (dbg && tid == 32) { const long long c = clock64(); bph[k] += c - bc0; bc0 = c; } } while (0)
+#else
+#define BW_MARK(k) do { } while (0)
+#endif
   for (long long tile = tile0; tile < tile1 && !failed; ++tile) {
     // ---- per-edge preparation ----
     {
@@ -840,16 +829,19 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_tc_kernel(const unsigned char
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    BW_MARK(0);
     bool done = true;
     if (tid == 0) {
       tc_fence_after();
-      issue_ops(ops, 2 * kFilterOps);
+      issue_filter_mma(tmem, a_hi, img, 0);
+      issue_filter_mma(tmem, a_hi, img, 1);
       umma_commit(mbar);
       done = mbar_wait(mbar, parity);     // one thread polls; the others park at the barrier below
     }
     parity ^= 1;
     if (!__syncthreads_and(done)) { failed = true; break; }
     tc_fence_after();
+    BW_MARK(1);
 #pragma unroll 1
     for (int f = 0; f < 2 && !failed; ++f) {
 #pragma unroll 1
@@ -857,9 +849,12 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_tc_kernel(const unsigned char
         if (((warp & 3) >> 1) == hh) tmem_to_tile(tmem, f, warp, lane, 64 * hh, wt);
         tc_fence_before();
         __syncthreads();
+        BW_MARK(2);
         if (f == 0) reverse_edge_run<0>(rec, wt, 8 * warp, 64 * hh + 8 * warp, a_ptr, lane, qkv, g_xa, g_qkv);
         else reverse_edge_run<1>(rec, wt, 8 * warp, 64 * hh + 8 * warp, a_ptr, lane, qkv, g_xa, g_qkv);
+        BW_MARK(3);
         __syncthreads();
+        BW_MARK(4);
       }
       fence_async_smem();
       tc_fence_before();
@@ -867,13 +862,14 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_tc_kernel(const unsigned char
       done = true;
       if (tid == 0) {
         tc_fence_after();
-        issue_ops(ops + 2 * kFilterOps + f * kReverseOps, kReverseOps);
+        issue_reverse_mma(tmem, a_hi, img, f);
         umma_commit(mbar);
         done = mbar_wait(mbar, parity);
       }
       parity ^= 1;
       if (!__syncthreads_and(done)) { failed = true; break; }
       tc_fence_after();
+      BW_MARK(5);
       // ---- per edge: radial derivative (threads 0..127) and the spherical hidden layer (threads 128..255) ----
       {
         const int row = tid & 127;
@@ -932,6 +928,7 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_tc_kernel(const unsigned char
       }
       tc_fence_before();
       __syncthreads();
+      BW_MARK(6);
     }
     if (failed) break;
     // ---- angular part and the force on the receiver (threads 0..127); cotangent of ev (warps 4..7) ----
@@ -992,7 +989,11 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_tc_kernel(const unsigned char
       if (cur_i >= 0 && lane < kMTot && acc != 0.f) atomicAdd(gev_in + (size_t)cur_i * kMTot + lane, acc);
     }
     __syncthreads();
+    BW_MARK(7);
   }
+#ifdef SO3LR_TC_TIMING
+  if (dbg && tid == 32 && blockIdx.x == 0) { for (int q = 0; q < 8; ++q) dbg[16 + q] = bph[q]; dbg[24] = tile1 - tile0; }
+#endif
   if (failed && tid == 0) atomicExch(err, 1);
   tc_fence_before();
   __syncthreads();
@@ -1066,8 +1067,7 @@ static long long* tc_debug_buffer() {
   static long long* buf = [] {
     long long* p = nullptr;
     if (std::getenv("SO3LR_B200_TC_DEBUG")) {
-      cudaMalloc((void**)&p, 16 * sizeof(long long)); cudaMemset(p, 0, 16 * sizeof(long long));
-      if (std::getenv("SO3LR_B200_TC_MNIMG")) { long long one = 1; cudaMemcpy(p + 15, &one, sizeof(one), cudaMemcpyHostToDevice); }
+      cudaMalloc((void**)&p, 32 * sizeof(long long)); cudaMemset(p, 0, 32 * sizeof(long long));
     }
     return p;
   }();
@@ -1076,22 +1076,16 @@ static long long* tc_debug_buffer() {
 void tc_debug_print() {
   long long* d = tc_debug_buffer();
   if (!d) return;
-  long long h[16];
+  long long h[32];
   cudaDeviceSynchronize();
   cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost);
+  if (h[24]) std::fprintf(stderr, "tc bwd phases (cycles per tile, %lld tiles): prep %lld | mma1 %lld | tmem->tile %lld | edge loop %lld | sync %lld | mma2 %lld | epilogue %lld | phase C %lld\n",
+               h[24], h[16] / h[24], h[17] / h[24], h[18] / h[24], h[19] / h[24], h[20] / h[24], h[21] / h[24], h[22] / h[24], h[23] / h[24]);
+  std::fprintf(stderr, "tc fwd mma issue %lld wait %lld cycles per tile\n", h[9] / (h[8] ? h[8] : 1), h[10] / (h[8] ? h[8] : 1));
   std::fprintf(stderr, "tc fwd phases (cycles per tile, %lld tiles): prep %lld | sync %lld | mma+wait %lld | tmem0 %lld | loop0 %lld | sync %lld | tmem1 %lld | loop1 %lld\n",
                h[8], h[0] / (h[8] ? h[8] : 1), h[1] / (h[8] ? h[8] : 1), h[2] / (h[8] ? h[8] : 1), h[3] / (h[8] ? h[8] : 1), h[4] / (h[8] ? h[8] : 1),
                h[5] / (h[8] ? h[8] : 1), h[6] / (h[8] ? h[8] : 1), h[7] / (h[8] ? h[8] : 1));
 }
-static int sm_count() {
-  static int v = [] {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    return n;
-  }();
-  return v;
-}
-
 int launch_attn_fwd_tc(cudaStream_t s, const LayerDev& L, const ValidEdges& V, int n_recv, const float* qkv, const float* x_in,
                        const float* ev_in, float* xa, float* ev1, int* err) {
   if (n_recv <= 0) return kOk;
@@ -1099,7 +1093,7 @@ int launch_attn_fwd_tc(cudaStream_t s, const LayerDev& L, const ValidEdges& V, i
   // the kernel adds the attention sums onto the skip connection
   SO3LR_CUDA_CHECK(cudaMemcpyAsync(xa, x_in, (size_t)n_recv * kF * sizeof(float), cudaMemcpyDeviceToDevice, s));
   SO3LR_CUDA_CHECK(cudaMemcpyAsync(ev1, ev_in, (size_t)n_recv * kMTot * sizeof(float), cudaMemcpyDeviceToDevice, s));
-  { attn_fwd_tc_kernel<<<sm_count(), kFwThreads, kSmemFwd, s>>>(std::getenv("SO3LR_B200_TC_MNIMG") ? L.tc_img : L.tc_img_fwd, L.sph1_k, L.sph1_b, n_recv, V.row_ptr, V.i, V.j, V.d, qkv, ev_in, xa, ev1, err, tc_debug_buffer()); count_launch(); }
+  { attn_fwd_tc_kernel<<<sm_count(), kFwThreads, kSmemFwd, s>>>(L.tc_img_fwd, L.sph1_k, L.sph1_b, n_recv, V.row_ptr, V.i, V.j, V.d, qkv, ev_in, xa, ev1, err, tc_debug_buffer()); count_launch(); }
   return kOk;
 }
 
@@ -1111,7 +1105,7 @@ int launch_attn_bwd_tc(cudaStream_t s, const LayerDev& L, const ValidEdges& V, i
   SO3LR_CUDA_CHECK(cudaMemsetAsync(g_qkv, 0, (size_t)n_recv * kProj * sizeof(float), s));
   SO3LR_CUDA_CHECK(cudaMemcpyAsync(gev_in, gev1, (size_t)n_recv * kMTot * sizeof(float), cudaMemcpyDeviceToDevice, s));
   { attn_bwd_tc_kernel<<<sm_count(), 256, kSmemBwd, s>>>(L.tc_img, L.sph1_k, L.sph1_b, n_recv, V.row_ptr, V.i, V.j, V.d, qkv, ev_in, g_xa, gev1, g_qkv,
-                                                       gev_in, F, virial, err); count_launch(); }
+                                                       gev_in, F, virial, err, tc_debug_buffer()); count_launch(); }
   return kOk;
 }
 

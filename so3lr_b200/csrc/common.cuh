@@ -36,6 +36,9 @@ enum Status : int {
 // on this host thread keeps the total (so3lr_b200_system_stats).
 void count_launch(int kernels = 1);
 
+// multiprocessors of the current device (queried once per device ordinal); persistent kernels launch one CTA per SM
+int sm_count();
+
 constexpr float kCutoffSr = 4.5f;
 constexpr float kAvgNumNeighbors = 13.168995780096482f;
 constexpr float kLnEps = 1e-6f;

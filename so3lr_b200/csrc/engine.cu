@@ -208,10 +208,13 @@ int make_cell(const float* cell9, Cell* c) {
 }  // namespace
 
 // Optional per-kernel-group timing with CUDA events on the launching stream.
+// attn_fwd / attn_bwd: the kernels of the two layers with a spherical filter (one launch per layer); the first layer's
+// tabulated kernels have groups of their own, so that a group's time divided by its launches is one kernel's time
 enum ProfGroup { kPNlist = 0, kPGeom, kPProj, kPAttnFwd, kPPostFwd, kPHeads, kPPairLr, kPPostBwd, kPAttnBwd, kPProjBwd, kPScatter,
-                 kPMisc, kPMd, kPGroups };
+                 kPMisc, kPMd, kPLayer0Fwd, kPLayer0Bwd, kPGroups };
 static const char* kProfNames[kPGroups] = {"nlist", "sr_geometry_zbl", "proj_fwd", "attn_fwd", "atom_post_fwd", "heads", "pair_lr",
-                                           "atom_post_bwd", "attn_bwd", "proj_bwd", "force_scatter", "misc", "md_step"};
+                                           "atom_post_bwd", "attn_bwd", "proj_bwd", "force_scatter", "misc", "md_step",
+                                           "layer0_fwd", "layer0_bwd"};
 struct Profiler {
   bool on = false;
   std::vector<cudaEvent_t> a, b;
@@ -241,6 +244,11 @@ struct Profiler {
 
 struct so3lr_b200_system {
   so3lr_b200_model* model = nullptr;
+  // the model as this context sees it: a copy of the shared tables whose atom-embedding table is replaced by a context-owned
+  // one when the structure carries a total charge or unpaired electrons (the charge / spin embeddings depend on the element,
+  // the charge and the composition only); batches of several graphs get a per-atom embedding instead
+  ModelDev mctx{};
+  float* x0_atom = nullptr;
   Profiler prof;
   int n = 0, n_graphs = 1;
   int n_cap = 0;                 // atoms the per-atom arrays were allocated for
@@ -270,6 +278,14 @@ struct so3lr_b200_system {
   float* d_Rref = nullptr;
   int* d_flag = nullptr;   // [0] skin test of the current step, [1] sticky error word of the tensor-core kernels' bounded waits
   int* h_flag = nullptr;   // pinned copy of both
+  // deferred skin test: the flags of step k are read by the host at step k + 1 (two pinned slots and an event each), so a
+  // step never waits for the device; the trigger distance is lowered by `skin_margin` to cover the extra step
+  bool deferred_skin = false;
+  float skin_margin = 0.f;
+  int* h_flag2 = nullptr;            // pinned, 2 slots x 2 ints
+  cudaEvent_t flag_event[2] = {nullptr, nullptr};
+  bool flag_pending[2] = {false, false};
+  int flag_slot = 0;
   double* h_box = nullptr; // pinned: the box coordinate read back by the NPT step
   bool virial_fresh = false;   // virial_sum belongs to the latest evaluation
   bool have_lists = false;
@@ -307,6 +323,16 @@ struct so3lr_b200_system {
 
 namespace {
 
+// initial features of atoms [0, n): per-atom rows when the context carries them (charged batches), else the element table
+int embed_atoms(so3lr_b200_system* S, cudaStream_t st, int n, float* x) {
+  if (S->x0_atom) {
+    SO3LR_CUDA_CHECK(cudaMemcpyAsync(x, S->x0_atom, (size_t)n * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    return kOk;
+  }
+  launch_embed(st, S->mctx, S->d_Z, n, x);
+  return kOk;
+}
+
 void fill(cudaStream_t s, float* p, size_t n, float v) {
   if (n == 0) return;
   if (v == 0.f) { cudaMemsetAsync(p, 0, n * sizeof(float), s); return; }
@@ -314,7 +340,7 @@ void fill(cudaStream_t s, float* p, size_t n, float v) {
 }
 
 int ensure_edge_buffers(so3lr_b200_system* S, long long n_edges) {
-  if (n_edges <= S->edge_cap) return kOk;
+  if (n_edges <= S->edge_cap) return valid_edges_reserve(&S->ve, S->n_cap, S->edge_cap);   // row arrays exist even without edges
   long long cap = n_edges + n_edges / 4 + 1024;
   if (S->dR) cudaFree(S->dR);
   S->dR = nullptr;
@@ -374,13 +400,13 @@ int rebuild_lists(so3lr_b200_system* S, cudaStream_t st, const float* R_user, bo
 int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, const int* nbr_j, const int* edge_i, long long n_edges,
                    const int* row_ptr_lr, const int* nbr_j_lr, const float* dR_in, const float* dR_lr_in, float* g_dR,
                    float* g_dR_lr_out, const float* ge) {
-  const ModelDev& M = S->model->M;
+  const ModelDev& M = S->mctx;
   const int n = S->n;
   float* dR = const_cast<float*>(dR_in);
   fill(st, S->e_zbl, n, 0.f); fill(st, S->e_coul, n, 0.f); fill(st, S->e_disp, n, 0.f);
   fill(st, S->gq, n, 0.f); fill(st, S->gh, n, 0.f);
   S->prof.begin(kPGeom, st); launch_sr_geometry_zbl(st, M, S->cell, n, n_edges, edge_i, nbr_j, S->d_Z, nullptr, 1, dR, S->e_zbl, g_dR, ge, nullptr); S->prof.end(st);
-  launch_embed(st, M, S->d_Z, n, S->x[0]);
+  { int rce = embed_atoms(S, st, n, S->x[0]); if (rce) return rce; }
   for (int l = 0; l < kNumLayers; ++l) {
     const LayerDev& L = M.layer[l];
     S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], n, S->qkv[l]); S->prof.end(st);
@@ -418,17 +444,18 @@ int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, co
   return kOk;
 }
 
-// Attention kernels of the layers with a spherical filter.  SO3LR_B200_ATTENTION (for comparison runs): "tc" tiled tcgen05
-// kernels, "tcf" tiled forward with the warp-per-receiver reverse kernel, "mma" warp-per-receiver mma.sync kernels, "simt"
-// FP32 shared-memory filter GEMMs.
+// Attention kernels of the layers with a spherical filter.  Default: the tiled tcgen05 forward kernel with the
+// warp-per-receiver mma.sync reverse kernel (the faster one of the two reverse kernels at present).  SO3LR_B200_ATTENTION
+// selects the others for comparison runs: "tc" tiled tcgen05 kernels in both directions, "mma" warp-per-receiver mma.sync
+// kernels in both, "simt" FP32 shared-memory filter GEMMs.
 enum AttentionMode { kAttnSimt = 0, kAttnMma = 1, kAttnTcFwd = 2, kAttnTc = 3 };
 int attention_mode() {
   static const int v = [] {
     const char* e = std::getenv("SO3LR_B200_ATTENTION");
     if (e && std::strcmp(e, "simt") == 0) return (int)kAttnSimt;
-    if (e && std::strcmp(e, "tcf") == 0) return (int)kAttnTcFwd;
+    if (e && std::strcmp(e, "mma") == 0) return (int)kAttnMma;
     if (e && std::strcmp(e, "tc") == 0) return (int)kAttnTc;
-    return (int)kAttnMma;
+    return (int)kAttnTcFwd;
   }();
   return v;
 }
@@ -496,10 +523,12 @@ void attn_bwd_dispatch(so3lr_b200_system* S, cudaStream_t st, const LayerDev& L,
 // n0 = n1 = n2 = n3 = n.
 struct Shells { int n0, n1, n2, n3; };
 
+constexpr int kVirialBlocks = 1024;   // capacity of the block-partials buffer of the virial reduction
 // sum of the per-atom virial rows of the atoms whose energy is evaluated here
 void reduce_virial(so3lr_b200_system* S, cudaStream_t st, int n0) {
   int blocks = (n0 + 255) / 256;
-  if (blocks > 592) blocks = 592;
+  const int max_blocks = 4 * sm_count() < kVirialBlocks ? 4 * sm_count() : kVirialBlocks;   // four CTAs per SM, bounded by the partials buffer
+  if (blocks > max_blocks) blocks = max_blocks;
   { virial_partial_kernel<<<blocks, 256, 0, st>>>(n0, S->virial, S->virial_partials); count_launch(); }
   { virial_final_kernel<<<1, 32, 0, st>>>(blocks, S->virial_partials, S->virial_sum); count_launch(); }
   S->virial_fresh = true;
@@ -507,7 +536,7 @@ void reduce_virial(so3lr_b200_system* S, cudaStream_t st, int n0) {
 
 // network forward up to the output heads: e_nn, q_raw, hv for the owned atoms; ZBL energy and force; F is zeroed first
 int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const Shells& c, bool owned_side_only, float* F) {
-  const ModelDev& M = S->model->M;
+  const ModelDev& M = S->mctx;
   const int* row_ptr = S->sr.row_ptr; const int* nbr_j = S->sr.nbr_j; const int* edge_i = S->sr.edge_i;
   const int nrecv[kNumLayers] = {c.n2, c.n1, c.n0};   // receivers of layer l
   const int nsend[kNumLayers] = {c.n3, c.n2, c.n1};   // atoms whose q/k/v rows layer l reads
@@ -524,11 +553,11 @@ int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const S
   S->prof.end(st);
   const bool tab0 = S->sp.n_species > 0 && use_layer0_tables();
   const bool fuse = use_mma_dense();   // q/k/v rows of layer l+1 come out of layer l's dense block
-  if (!tab0) launch_embed(st, M, S->d_Z, c.n3, S->x[0]);
+  if (!tab0) { int rce = embed_atoms(S, st, c.n3, S->x[0]); if (rce) return rce; }
   for (int l = 0; l < kNumLayers; ++l) {
     const LayerDev& L = M.layer[l];
     if (l == 0 && tab0) {
-      S->prof.begin(kPAttnFwd, st);
+      S->prof.begin(kPLayer0Fwd, st);
       launch_layer0_fwd_tab(st, S->sp, M, nrecv[0], c.n3, row_ptr, nbr_j, S->dR, S->d_Z, S->xa[0], S->ev1[0]);
       S->prof.end(st);
     } else {
@@ -552,7 +581,7 @@ int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const S
 
 // reverse pass from the cotangents of the heads (gq_raw, gh on the owned atoms; d/d e_nn = 1) to the forces, added into F
 int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float* F) {
-  const ModelDev& M = S->model->M;
+  const ModelDev& M = S->mctx;
   const int* row_ptr = S->sr.row_ptr; const int* nbr_j = S->sr.nbr_j;
   const int npost[kNumLayers] = {c.n2, c.n1, c.n0};   // atoms whose layer-l outputs carry a cotangent
   const int nattn[kNumLayers] = {c.n3, c.n2, c.n1};   // atoms that receive a cotangent through layer l's attention
@@ -573,7 +602,7 @@ int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float
       fill(st, S->g_xa + (size_t)npost[l] * kF, (size_t)(c.n3 - npost[l]) * kF, 0.f);
       fill(st, S->gev1 + (size_t)npost[l] * kMTot, (size_t)(c.n3 - npost[l]) * kMTot, 0.f);
     }
-    S->prof.begin(kPAttnBwd, st);
+    S->prof.begin(l == 0 ? kPLayer0Bwd : kPAttnBwd, st);
     if (l == 0 && S->sp.n_species > 0 && use_layer0_tables())
       launch_layer0_bwd_tab(st, S->sp, nattn[0], c.n3, c.n3, row_ptr, nbr_j, S->dR, S->d_Z, S->g_xa, S->gev1, S->GV, F, S->vir());
     else
@@ -609,6 +638,74 @@ int evaluate_fused(so3lr_b200_system* S, cudaStream_t st, const float* R, float*
   { combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
   launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw, S->n, S->red_scratch);
   return fused_backward(S, st, c, F);
+}
+
+// Charge and spin embeddings (feature_embeddings_1 / _2 of the parameter tree; inputs total_charge / num_unpaired_electrons of
+// so3lr/base_calculator.py:57-86).  Per graph and embedding: y_i = softplus(<query[Z_i], key[psi < 0]> / sqrt(128)),
+// a_i = psi * y_i / sum_graph y, e_i = a_i * value[psi < 0], output e + W1^T silu(W0^T silu(e)) (bias-free residual block).
+// They depend on the element, the graph's composition and psi only -- not on positions -- so they are evaluated once per
+// context, on the host in double precision, and folded into the initial features: x0 = (embed[Z] + charge + spin) / sqrt(3).
+// `out` receives per (graph, element) rows [n_graphs][119][128], already divided by sqrt(3); returns false when every psi is 0.
+bool charge_spin_rows(const ModelDev& M, int n, const int32_t* Z, int n_graphs, const std::vector<int>& gs, const float* total_charge,
+                      const float* num_unpaired, std::vector<float>* out, int* status) {
+  bool any = false;
+  for (int g = 0; g < n_graphs; ++g) any |= (total_charge && total_charge[g] != 0.f) || (num_unpaired && num_unpaired[g] != 0.f);
+  *status = kOk;
+  if (!any) return false;
+  out->assign((size_t)n_graphs * kZEmbed * kF, 0.f);
+  std::vector<float> q((size_t)kZEmbed * kF), k(2 * kF), v(2 * kF), r0((size_t)kF * kF), r1((size_t)kF * kF);
+  auto silu = [](double x) { return x / (1.0 + std::exp(-x)); };
+  for (int e = 0; e < 2; ++e) {
+    const float* psi_all = e == 0 ? total_charge : num_unpaired;
+    if (!psi_all) continue;
+    bool used = false;
+    for (int g = 0; g < n_graphs; ++g) used |= psi_all[g] != 0.f;
+    if (!used) continue;
+    if (cudaMemcpy(q.data(), M.cs_embed_q[e], q.size() * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(k.data(), M.cs_embed_k[e], k.size() * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(v.data(), M.cs_embed_v[e], v.size() * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(r0.data(), M.cs_res0[e], r0.size() * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess ||
+        cudaMemcpy(r1.data(), M.cs_res1[e], r1.size() * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) {
+      *status = kCudaError;
+      return false;
+    }
+    for (int g = 0; g < n_graphs; ++g) {
+      const double psi = psi_all[g];
+      if (psi == 0.0) continue;
+      const int idx = psi < 0.0 ? 1 : 0;
+      double y[kZEmbed];
+      bool present[kZEmbed] = {};
+      for (int a = gs[g]; a < gs[g + 1]; ++a) present[Z[a]] = true;
+      for (int z = 0; z < kZEmbed; ++z) {
+        if (!present[z]) continue;
+        double d = 0.0;
+        for (int c = 0; c < kF; ++c) d += (double)q[(size_t)z * kF + c] * (double)k[idx * kF + c];
+        d /= std::sqrt((double)kF);
+        y[z] = d > 30.0 ? d : std::log1p(std::exp(d));
+      }
+      double den = 0.0;
+      for (int a = gs[g]; a < gs[g + 1]; ++a) den += y[Z[a]];
+      for (int z = 0; z < kZEmbed; ++z) {
+        if (!present[z]) continue;
+        const double a = psi * y[z] / den;
+        double ev[kF], t0[kF], t1[kF];
+        for (int c = 0; c < kF; ++c) ev[c] = a * (double)v[idx * kF + c];
+        for (int o = 0; o < kF; ++o) {
+          double acc = 0.0;
+          for (int c = 0; c < kF; ++c) acc += silu(ev[c]) * (double)r0[(size_t)c * kF + o];
+          t0[o] = acc;
+        }
+        for (int o = 0; o < kF; ++o) {
+          double acc = 0.0;
+          for (int c = 0; c < kF; ++c) acc += silu(t0[c]) * (double)r1[(size_t)c * kF + o];
+          t1[o] = acc;
+        }
+        float* row = out->data() + ((size_t)g * kZEmbed + z) * kF;
+        for (int c = 0; c < kF; ++c) row[c] += (float)((ev[c] + t1[c]) / std::sqrt(3.0));
+      }
+    }
+  }
+  return true;
 }
 
 }  // namespace
@@ -671,22 +768,10 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
                          "coefficients of the dispersion term are tabulated for these elements only)\n", bad == -1 ? 0 : bad, kMaxZ);
     return kInvalidArgument;
   }
-  if (num_unpaired)
-    for (int g = 0; g < n_graphs; ++g)
-      if (num_unpaired[g] != 0.f) {
-        std::fprintf(stderr, "so3lr_b200: open-shell graphs (num_unpaired_electrons != 0) are not supported\n");
-        return kInvalidArgument;
-      }
-  if (total_charge)
-    for (int g = 0; g < n_graphs; ++g)
-      if (total_charge[g] != 0.f) {
-        std::fprintf(stderr, "so3lr_b200: charged graphs (total_charge != 0) are not supported by the feature embedding\n");
-        return kInvalidArgument;
-      }
   SO3LR_CUDA_CHECK(cudaSetDevice(model->device));
   so3lr_b200_system* S = new so3lr_b200_system();
   tl_launch_counter = &S->n_launches;
-  S->model = model; S->n = n_atoms; S->n_cap = n_atoms; S->n_graphs = n_graphs; S->opt = *options;
+  S->model = model; S->mctx = model->M; S->n = n_atoms; S->n_cap = n_atoms; S->n_graphs = n_graphs; S->opt = *options;
   int rc = make_cell(cell9, &S->cell);
   if (rc) { delete S; return rc; }
   // long-range constants
@@ -756,7 +841,38 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
             cudaStreamCreateWithFlags(&S->own_stream, cudaStreamNonBlocking) == cudaSuccess;
   if (!ok) { so3lr_b200_system_destroy(S); return kCudaError; }
   fill(nullptr, S->ones, n, 1.f);
-  if (species_tables_build(nullptr, model->M, Z, n, &S->sp) != kOk) { so3lr_b200_system_destroy(S); return kCudaError; }
+  {
+    // charge / spin embeddings: per-element table for one structure, per-atom rows for a batch
+    std::vector<float> rows;
+    int cs_status = kOk;
+    const bool charged = charge_spin_rows(model->M, n, Z, n_graphs, gs, total_charge, num_unpaired, &rows, &cs_status);
+    if (cs_status != kOk) { so3lr_b200_system_destroy(S); return cs_status; }
+    if (charged) {
+      std::vector<float> base((size_t)kZEmbed * kF);
+      if (cudaMemcpy(base.data(), model->M.embed_z, base.size() * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        so3lr_b200_system_destroy(S); return kCudaError;
+      }
+      if (n_graphs == 1) {
+        for (size_t k = 0; k < base.size(); ++k) base[k] += rows[k];
+        float* d = S->pool.get<float>(base.size());
+        if (!d || cudaMemcpy(d, base.data(), base.size() * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) {
+          so3lr_b200_system_destroy(S); return kCudaError;
+        }
+        S->mctx.embed_z = d;
+      } else {
+        std::vector<float> x0((size_t)n * kF);
+        for (int a = 0; a < n; ++a)
+          for (int c = 0; c < kF; ++c)
+            x0[(size_t)a * kF + c] = base[(size_t)Z[a] * kF + c] + rows[((size_t)seg[a] * kZEmbed + Z[a]) * kF + c];
+        S->x0_atom = S->pool.get<float>(x0.size());
+        if (!S->x0_atom || cudaMemcpy(S->x0_atom, x0.data(), x0.size() * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) {
+          so3lr_b200_system_destroy(S); return kCudaError;
+        }
+      }
+    }
+  }
+  // a batch with per-atom initial features cannot use the per-element-pair tables of the first layer
+  if (!S->x0_atom && species_tables_build(nullptr, S->mctx, Z, n, &S->sp) != kOk) { so3lr_b200_system_destroy(S); return kCudaError; }
   cudaDeviceSynchronize();
   S->nws = nlist_workspace_create();
   *out = S;
@@ -777,6 +893,8 @@ SO3LR_B200_API int so3lr_b200_system_destroy(so3lr_b200_system* S) {
   cudaFree(S->dR);
   valid_edges_free(&S->ve);
   if (S->h_flag) cudaFreeHost(S->h_flag);
+  if (S->h_flag2) cudaFreeHost(S->h_flag2);
+  for (int k = 0; k < 2; ++k) if (S->flag_event[k]) cudaEventDestroy(S->flag_event[k]);
   if (S->h_box) cudaFreeHost(S->h_box);
   if (S->h_R) cudaFreeHost(S->h_R);
   if (S->h_F) cudaFreeHost(S->h_F);
@@ -798,6 +916,19 @@ SO3LR_B200_API int so3lr_b200_system_set_cell(so3lr_b200_system* S, const float*
   return kOk;
 }
 
+SO3LR_B200_API int so3lr_b200_system_defer_skin_test(so3lr_b200_system* S, int enable, float margin) {
+  if (!S || !(margin >= 0.f)) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  if (enable && !S->h_flag2) {
+    SO3LR_CUDA_CHECK(cudaMallocHost((void**)&S->h_flag2, 4 * sizeof(int)));
+    for (int k = 0; k < 2; ++k) SO3LR_CUDA_CHECK(cudaEventCreateWithFlags(&S->flag_event[k], cudaEventDisableTiming));
+  }
+  S->deferred_skin = enable != 0;
+  S->skin_margin = margin;
+  S->flag_pending[0] = S->flag_pending[1] = false;
+  return kOk;
+}
+
 SO3LR_B200_API int so3lr_b200_system_rescale_cell(so3lr_b200_system* S, const float* cell9) {
   if (!S || !cell9 || !S->cell.periodic) return kInvalidArgument;
   S->virial_fresh = false;
@@ -808,7 +939,30 @@ static int prepare_lists(so3lr_b200_system* S, cudaStream_t st, const float* R, 
   bool rebuild = !S->have_lists;
   if (!rebuild) {
     if (S->opt.skin <= 0.f) rebuild = true;
-    else {
+    else if (S->deferred_skin) {
+      // this step's test goes to one pinned slot; the decision uses the other slot, written during the previous step
+      const int cur = S->flag_slot, prev = cur ^ 1;
+      float thr = 0.5f * S->opt.skin - S->skin_margin;
+      if (thr < 0.f) thr = 0.f;
+      SO3LR_CUDA_CHECK(cudaMemsetAsync(S->d_flag, 0, sizeof(int), st));
+      { moved_kernel<<<(S->n + 255) / 256, 256, 0, st>>>(S->n, R, S->d_Rref, thr * thr, S->d_flag); count_launch(); }
+      SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->h_flag2 + 2 * cur, S->d_flag, 2 * sizeof(int), cudaMemcpyDeviceToHost, st));
+      SO3LR_CUDA_CHECK(cudaEventRecord(S->flag_event[cur], st));
+      S->flag_pending[cur] = true;
+      S->flag_slot = prev;
+      if (S->flag_pending[prev]) {
+        SO3LR_CUDA_CHECK(cudaEventSynchronize(S->flag_event[prev]));    // a whole step old: already complete in steady state
+        S->flag_pending[prev] = false;
+        const int* f = S->h_flag2 + 2 * prev;
+        if (f[1]) {
+          std::fprintf(stderr, "so3lr_b200: a bounded wait on the tensor-core pipeline ran out in an earlier evaluation\n");
+          return kCudaError;
+        }
+        if (f[0] & 2) return kNotFinite;
+        rebuild = f[0] != 0;
+      }
+      if (rebuild) { S->flag_pending[0] = S->flag_pending[1] = false; }
+    } else {
       float thr = 0.5f * S->opt.skin;
       SO3LR_CUDA_CHECK(cudaMemsetAsync(S->d_flag, 0, sizeof(int), st));
       { moved_kernel<<<(S->n + 255) / 256, 256, 0, st>>>(S->n, R, S->d_Rref, thr * thr, S->d_flag); count_launch(); }
@@ -973,7 +1127,7 @@ SO3LR_B200_API int so3lr_b200_system_enable_virial(so3lr_b200_system* S, int ena
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
   if (enable && !S->virial) {
     S->virial = S->pool.get<float>((size_t)S->n_cap * 6);
-    S->virial_partials = S->pool.get<double>(6 * 592);
+    S->virial_partials = S->pool.get<double>(6 * kVirialBlocks);
     S->virial_sum = S->pool.get<double>(9);
     if (S->pool.status != kOk) return S->pool.status;
   }
@@ -1155,6 +1309,11 @@ SO3LR_B200_API int so3lr_b200_dd_set_atoms(so3lr_b200_system* S, int n_local, co
                                            const float* cell9) {
   if (!S || !shells4 || !Z_local_dev || n_local <= 0) return kInvalidArgument;
   if (S->n_graphs != 1) return kInvalidArgument;
+  if (S->mctx.embed_z != S->model->M.embed_z) {
+    std::fprintf(stderr, "so3lr_b200: a decomposed evaluation of a charged or open-shell structure is not supported (the charge embedding "
+                         "needs the composition of the whole structure)\n");
+    return kInvalidArgument;
+  }
   if (n_local > S->n_cap) return kTooLarge;
   if (!(shells4[0] > 0 && shells4[0] <= shells4[1] && shells4[1] <= shells4[2] && shells4[2] <= shells4[3] && shells4[3] == n_local))
     return kInvalidArgument;
@@ -1172,7 +1331,7 @@ SO3LR_B200_API int so3lr_b200_dd_set_atoms(so3lr_b200_system* S, int n_local, co
       std::fprintf(stderr, "so3lr_b200: atomic number %d is outside the supported range 1..%d\n", bad == -1 ? 0 : bad, kMaxZ);
       return kInvalidArgument;
     }
-    rc = species_tables_build(nullptr, S->model->M, zh.data(), n_local, &S->sp);
+    rc = species_tables_build(nullptr, S->mctx, zh.data(), n_local, &S->sp);
     if (rc) return rc;
     SO3LR_CUDA_CHECK(cudaDeviceSynchronize());
   }
@@ -1204,7 +1363,7 @@ SO3LR_B200_API int so3lr_b200_dd_begin(so3lr_b200_system* S, void* stream, const
     S->have_lists = true;
     S->n_rebuilds++;
   }
-  const ModelDev& M = S->model->M;
+  const ModelDev& M = S->mctx;
   fill(st, S->e_zbl, n0, 0.f);
   fill(st, S->F_s, (size_t)n0 * 3, 0.f);
   if (S->vir()) fill(st, S->virial, (size_t)n0 * 6, 0.f);
@@ -1216,7 +1375,7 @@ SO3LR_B200_API int so3lr_b200_dd_begin(so3lr_b200_system* S, void* stream, const
     if (rcv) return rcv;
   }
   S->prof.end(st);
-  if (!(S->sp.n_species > 0 && use_layer0_tables())) launch_embed(st, M, S->d_Z, n1, S->x[0]);
+  if (!(S->sp.n_species > 0 && use_layer0_tables())) launch_embed(st, M, S->d_Z, n1, S->x[0]);   // decomposed contexts are neutral
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }
@@ -1227,10 +1386,10 @@ SO3LR_B200_API int so3lr_b200_dd_layer_forward(so3lr_b200_system* S, void* strea
   tl_launch_counter = &S->n_launches;
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0], n1 = S->shells[1], l = layer;
-  const LayerDev& L = S->model->M.layer[l];
+  const LayerDev& L = S->mctx.layer[l];
   if (l == 0 && S->sp.n_species > 0 && use_layer0_tables()) {
-    S->prof.begin(kPAttnFwd, st);
-    launch_layer0_fwd_tab(st, S->sp, S->model->M, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->d_Z, S->xa[0], S->ev1[0]);
+    S->prof.begin(kPLayer0Fwd, st);
+    launch_layer0_fwd_tab(st, S->sp, S->mctx, n0, S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->d_Z, S->xa[0], S->ev1[0]);
     S->prof.end(st);
   } else {
     // with the tensor-core dense blocks the owned rows of q/k/v came out of the previous layer's block; the ghost rows
@@ -1246,7 +1405,7 @@ SO3LR_B200_API int so3lr_b200_dd_layer_forward(so3lr_b200_system* S, void* strea
   const bool emit = use_mma_dense() && l + 1 < kNumLayers;
   S->prof.begin(kPPostFwd, st);
   post_fwd_dispatch(st, L, n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1],
-                    emit ? &S->model->M.layer[l + 1] : nullptr, emit ? S->qkv[l + 1] : nullptr);
+                    emit ? &S->mctx.layer[l + 1] : nullptr, emit ? S->qkv[l + 1] : nullptr);
   S->prof.end(st);
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
@@ -1259,7 +1418,7 @@ SO3LR_B200_API int so3lr_b200_dd_heads(so3lr_b200_system* S, void* stream, float
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0];
   S->prof.begin(kPHeads, st);
-  heads_fwd_dispatch(st, S->model->M, n0, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv);
+  heads_fwd_dispatch(st, S->mctx, n0, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv);
   S->prof.end(st);
   SO3LR_CUDA_CHECK(cudaMemcpyAsync(q_raw_owned_dev, S->q_raw, (size_t)n0 * sizeof(float), cudaMemcpyDeviceToDevice, st));
   { abs_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->hv, h_owned_dev); count_launch(); }
@@ -1294,7 +1453,7 @@ SO3LR_B200_API int so3lr_b200_dd_heads_backward(so3lr_b200_system* S, void* stre
   { combine_energy_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
   if (energy_owned_dev) { sum_to_double_kernel<<<1, 1024, 0, st>>>(n0, S->e_atom, energy_owned_dev); count_launch(); }
   S->prof.begin(kPHeads, st);
-  heads_bwd_dispatch(st, S->model->M, n0, S->d_Z, S->ze, S->zq, S->zh, S->hv, S->ones, S->gq_raw, S->gh, S->g4);
+  heads_bwd_dispatch(st, S->mctx, n0, S->d_Z, S->ze, S->zq, S->zh, S->hv, S->ones, S->gq_raw, S->gh, S->g4);
   S->prof.end(st);
   S->dd_gev2 = S->gev_a; S->dd_gev_in = S->gev_b;
   fill(st, S->dd_gev2, (size_t)n0 * kMTot, 0.f);
@@ -1311,8 +1470,8 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_post(so3lr_b200_system* S, void*
   const int n0 = S->shells[0], l = layer;
   const bool fused_in = use_mma_dense() && l + 1 < kNumLayers;
   S->prof.begin(kPPostBwd, st);
-  post_bwd_dispatch(st, S->model->M.layer[l], n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, S->dd_gev2, S->g_xa, S->gev1,
-                    fused_in ? &S->model->M.layer[l + 1] : nullptr, S->g_qkv);
+  post_bwd_dispatch(st, S->mctx.layer[l], n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, S->dd_gev2, S->g_xa, S->gev1,
+                    fused_in ? &S->mctx.layer[l + 1] : nullptr, S->g_qkv);
   S->prof.end(st);
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
@@ -1325,8 +1484,8 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_attn(so3lr_b200_system* S, void*
   tl_launch_counter = &S->n_launches;
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0], l = layer;
-  const LayerDev& L = S->model->M.layer[l];
-  S->prof.begin(kPAttnBwd, st);
+  const LayerDev& L = S->mctx.layer[l];
+  S->prof.begin(l == 0 ? kPLayer0Bwd : kPAttnBwd, st);
   if (l == 0 && S->sp.n_species > 0 && use_layer0_tables())
     launch_layer0_bwd_tab(st, S->sp, n0, S->shells[1], S->n, S->sr.row_ptr, S->sr.nbr_j, S->dR, S->d_Z, S->g_xa, S->gev1, S->GV, S->F_s, S->vir());
   else

@@ -134,7 +134,7 @@ void split_half(float x, unsigned short& hi, unsigned short& lo) {
 int cheb_term(int k) { return k < kChebM / 2 ? 2 * k : 2 * (k - kChebM / 2) + 1; }
 
 // Forward-kernel image: B operands with K contiguous.  CT[n][k] = coefficient of term cheb_term(k) of feature n: core
-// (n/8, k/8) at (n/8) * 1024 + (k/8) * 128; K2T_f[n][h]: core (n/8, h/8) at (n/8) * 512 + (h/8) * 128.
+// (n/8, k/8) at (k/8) * 4096 + (n/8) * 128; K2T_f[n][h]: core (n/8, h/8) at (h/8) * 2048 + (n/8) * 128.
 std::vector<float> tc_image_forward(const float* blob, const BlobOffsets& O, int layer) {
   std::vector<unsigned char> img(kTcImageBytes, 0);
   std::vector<double> coef;
@@ -147,13 +147,13 @@ std::vector<float> tc_image_forward(const float* blob, const BlobOffsets& O, int
   };
   for (int k = 0; k < kChebM; ++k)
     for (int n = 0; n < 256; ++n)
-      put(0, 32768, (size_t)(n / 8) * 1024 + (size_t)(k / 8) * 128 + (n % 8) * 16 + (k % 8) * 2, (float)coef[(size_t)cheb_term(k) * 256 + n]);
+      put(0, 32768, (size_t)(k / 8) * 4096 + (size_t)(n / 8) * 128 + (n % 8) * 16 + (k % 8) * 2, (float)coef[(size_t)cheb_term(k) * 256 + n]);
   const LayerOffsets& L = O.layer[layer];
   for (int f = 0; f < 2; ++f) {
     const float* K2 = blob + L.sph_l2_k[f];
     for (int h = 0; h < 32; ++h)
       for (int n = 0; n < kF; ++n)
-        put(65536 + (size_t)f * 8192, 65536 + 16384 + (size_t)f * 8192, (size_t)(n / 8) * 512 + (size_t)(h / 8) * 128 + (n % 8) * 16 + (h % 8) * 2,
+        put(65536 + (size_t)f * 8192, 65536 + 16384 + (size_t)f * 8192, (size_t)(h / 8) * 2048 + (size_t)(n / 8) * 128 + (n % 8) * 16 + (h % 8) * 2,
             K2[h * kF + n]);
   }
   std::vector<float> out(kTcImageBytes / 4);
@@ -211,6 +211,18 @@ struct Uploader {
 };
 
 }  // namespace
+
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] <= 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
 
 void radial_filter_chebyshev(const float* blob, int layer, double r, double* w256, double* dw256) {
   BlobOffsets O = blob_offsets();

@@ -5,7 +5,7 @@
 // fail for lack of memory and, when it succeeds, stalls every stream of the device.  The same holds for any host
 // program that hands its GPU memory out from a fixed arena.  so3lr_b200_neighbor_list_noalloc therefore builds a
 // jax-md style pair list using only the caller's buffers plus one fixed scratch array that lives in the library
-// image: kRowScratch below, 2 x (SO3LR_B200_NOALLOC_MAX_ATOMS + 1) int32 = 128 KiB, resident on every GPU that loads
+// image: kRowScratch below, 2 x (SO3LR_B200_NOALLOC_MAX_ATOMS + 1) int32 = 128 KiB + 8 bytes, resident on every GPU that loads
 // the library until the process exits.
 //
 // All calls (from any thread or stream) share that array on a device: two calls whose kernels overlap on the GPU race
@@ -150,6 +150,16 @@ extern "C" SO3LR_B200_API int so3lr_b200_neighbor_list_noalloc(void* stream, int
     inv[6] = (h[3] * h[7] - h[4] * h[6]) / det; inv[7] = (h[1] * h[6] - h[0] * h[7]) / det; inv[8] = (h[0] * h[4] - h[1] * h[3]) / det;
     for (int k = 0; k < 9; ++k) { c.h[k] = (float)h[k]; c.hinv[k] = (float)inv[k]; }
     c.periodic = 1;
+    // every pair is tested at its nearest image only: that is the full list as long as no second image can fall inside the
+    // cutoff, i.e. each perpendicular width of the cell (1 / |column k of the inverse|) is at least twice the cutoff
+    for (int k = 0; k < 3; ++k) {
+      const double width = 1.0 / std::sqrt(inv[k] * inv[k] + inv[3 + k] * inv[3 + k] + inv[6 + k] * inv[6 + k]);
+      if (width < 2.0 * (double)r_cutoff) {
+        std::fprintf(stderr, "so3lr_b200_neighbor_list_noalloc: perpendicular cell width %.4f A is below twice the cutoff %.4f A\n",
+                     width, (double)r_cutoff);
+        return kInvalidArgument;
+      }
+    }
   }
   int* scratch = nullptr;
   int rc = scratch_for_current_device(&scratch);
@@ -164,6 +174,7 @@ extern "C" SO3LR_B200_API int so3lr_b200_neighbor_list_noalloc(void* stream, int
   scan_rows_kernel<<<1, 1024, 0, st>>>(n_atoms, row_count, row_start, (long long)capacity, count_ll, overflow_dev);
   rows_all_pairs_kernel<true><<<blocks, 256, 0, st>>>(c, n_atoms, positions_dev, r2, ordered, nullptr, row_start, idx_dev, (long long)capacity);
   pad_list_kernel<<<(unsigned)((capacity + 255) / 256), 256, 0, st>>>(n_atoms, count_ll, (long long)capacity, idx_dev);
+  count_launch(4);
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
 }

@@ -208,9 +208,10 @@ __global__ void charge_conserve_kernel(int n_graphs, const int* __restrict__ gra
   }
   __syncthreads();
   const float Q = total_charge ? total_charge[g] : 0.f;
-  const float corr = a1 > a0 ? (Q - red[0]) / (float)(a1 - a0) : 0.f;
+  // the shift is applied in double: rounded to float32 first, its relative error times the atom count would show up in sum q
+  const double corr = a1 > a0 ? ((double)Q - (double)red[0]) / (double)(a1 - a0) : 0.0;
   for (int a = a0 + threadIdx.x; a < a1; a += blockDim.x) {
-    q[a] = q_raw[a] + corr;
+    q[a] = (float)((double)q_raw[a] + corr);
     h[a] = fabsf(hv[a]);
   }
 }
@@ -266,7 +267,7 @@ __global__ void graph_reduce_kernel(int n_graphs, const int* __restrict__ graph_
 }
 
 // ---- one structure with many atoms: the same three operations spread over many CTAs (sums in double, fixed order) ----
-constexpr int kWideBlocks = 296;      // two CTAs per SM
+constexpr int kWideBlocks = 296;      // two CTAs per SM of a 148-SM part; a fixed count keeps the order of the double sums independent of the device
 constexpr int kWideMinAtoms = 16384;
 
 __device__ double block_sum_double_256(double v, double* sh) {
@@ -314,9 +315,10 @@ __global__ void __launch_bounds__(256) charge_conserve_wide_kernel(int n, const 
                                                                    const double* __restrict__ partials, int n_blocks) {
   __shared__ double sh[8];
   const float Q = total_charge ? total_charge[0] : 0.f;
-  const float corr = (Q - (float)wide_total(partials, n_blocks, 0, sh)) / (float)n;
+  // in double: a float32 shift carries a relative error of 6e-8, which times a million atoms is a visible net charge
+  const double corr = ((double)Q - wide_total(partials, n_blocks, 0, sh)) / (double)n;
   for (int i = blockIdx.x * 256 + threadIdx.x; i < n; i += gridDim.x * 256) {
-    q[i] = q_raw[i] + corr;
+    q[i] = (float)((double)q_raw[i] + corr);
     h[i] = fabsf(hv[i]);
   }
 }

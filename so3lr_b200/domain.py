@@ -467,12 +467,40 @@ class DomainSystem:
             self._phase_events.append((name, e))
 
     # ---- evaluation ----
-    def _maybe_rebuild(self):
+    def defer_skin_test(self, on=True, margin=0.05):
+        """Read the skin test one step late: the largest squared displacement of step k is all-reduced on the device, copied to
+        pinned memory asynchronously and looked at when step k + 1 starts, so no rank waits for its device (or for the slowest
+        rank's host) inside a step.  The trigger distance is lowered to skin / 2 - margin so the lists cover the extra step
+        (margin >= the largest displacement of an atom in one step)."""
+        self._defer, self._margin, self._pending = bool(on), float(margin), None
+
+    def _skin_value(self):
         d2 = (self.R[: self.n0] - self.R_ref).square().sum(1).amax().reshape(1) if self.n0 else torch.zeros(1, device=self.device)
-        d2 = float(self.comm.all_reduce_max(d2.to(torch.float32)))      # the step's one host read
+        return self.comm.all_reduce_max(d2.to(torch.float32))
+
+    def _maybe_rebuild(self):
+        thr = 0.5 * self.skin
+        if getattr(self, "_defer", False) and self.skin > 0 and self.device.type == "cuda":
+            thr = max(thr - self._margin, 0.0)
+            cur = self._skin_value()
+            if getattr(self, "_pin_d2", None) is None:
+                self._pin_d2 = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+                self._ev_d2 = [torch.cuda.Event() for _ in range(2)]
+                self._slot = 0
+            k = self._slot
+            self._pin_d2[k].copy_(cur, non_blocking=True)
+            self._ev_d2[k].record()
+            prev, self._pending, self._slot = self._pending, k, k ^ 1
+            if prev is None:
+                return False
+            self._ev_d2[prev].synchronize()              # a whole step old
+            d2 = float(self._pin_d2[prev])
+        else:
+            d2 = float(self._skin_value())      # the step's one host read
         if not np.isfinite(d2):
             raise RuntimeError("non-finite positions")
-        if d2 > (0.5 * self.skin) ** 2 or self.skin <= 0:
+        if d2 > thr ** 2 or self.skin <= 0:
+            self._pending = None
             import time
             if self.device.type == "cuda":
                 torch.cuda.synchronize(self.device)
@@ -662,141 +690,3 @@ class DomainSystem:
 
     def global_forces(self):
         return self.gather_global(self.F)
-
-
-# ----------------------------------------------------------------------------------------------------------------
-# benchmark entry (called by bench.py under torchrun)
-# ----------------------------------------------------------------------------------------------------------------
-def bench_entry(args, rank, world, local_rank, n_mol, box, seed):
-    import json
-    import time
-    import torch.distributed as dist
-    from . import workloads as W
-    dev = torch.device("cuda", local_rank)
-    Z, R, cell = W.water_box(n_mol, box, seed)
-    V, m = W.maxwell_boltzmann(Z, 300.0, seed + 1)
-    N = len(Z)
-    comm = DistComm()
-    backend = CudaBackend(cutoff_lr=12.0, damping=2.0, skin=args.skin, device=local_rank)
-    dom = DomainSystem(comm, backend, Z, R, cell, skin=args.skin, cutoff_lr=12.0, velocities=V, masses=m, device=dev)
-    dom.compute(check_rebuild=False)
-    # one clock sampler for all GPUs, on rank 0, started ahead of the warm-up (its start-up disturbs running CUDA work)
-    sampler = args.clock_sampler(list(range(world))) if rank == 0 else None
-    if sampler:
-        sampler.start()
-    dt = 0.5
-    ensemble = getattr(args, "ensemble", None) or getattr(args, "default_ensemble", "nve")
-    if ensemble == "nvt":
-        chain = backend.nhc_state()
-        step = lambda: dom.nvt(1, dt, 300.0 * 8.617333262e-5, 100.0 * dt, chain, chain_length=3, chain_steps=2, sy_steps=3)
-    else:
-        step = lambda: dom.nve(1, dt)
-    for k in range(args.warmup):
-        if k == 1:
-            dom.repartition()          # first-use costs of the re-partitioning path (NCCL setup for its message sizes) are warm-up
-            dom.compute(check_rebuild=False)
-        step()
-    torch.cuda.synchronize()
-    dist.barrier()
-    st0 = backend.stats()
-    rb0 = dom.n_rebuilds
-    if sampler:
-        sampler.begin()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    ev[0].record()
-    t_host0 = time.perf_counter()
-    for _ in range(args.steps):
-        step()
-    host_ms = 1e3 * (time.perf_counter() - t_host0) / args.steps      # host time to enqueue a step (includes its waits on the device)
-    ev[1].record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    if sampler:
-        sampler.end()
-    clocks = sampler.stop() if sampler else None
-    ms = torch.tensor([ev[0].elapsed_time(ev[1])], dtype=torch.float64, device=dev)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    launches = torch.tensor([backend.stats()["launches"] - st0["launches"]], dtype=torch.float64, device=dev)
-    dist.all_reduce(launches, op=dist.ReduceOp.SUM)
-    nloc = torch.tensor([dom.n_local, dom.n0], dtype=torch.float64, device=dev)
-    dist.all_reduce(nloc, op=dist.ReduceOp.SUM)
-    ms = float(ms)
-    rebuilds = dom.n_rebuilds - rb0
-    # kernel times of rank 0's share over another K steps
-    backend.sys.profile(True)
-    dom.time_halo, dom._halo_events = True, []
-    dom.time_phases, dom._phase_events = True, []
-    for _ in range(args.steps):
-        step()
-    dom._mark("integrator")
-    prof = backend.sys.profile_read()
-    backend.sys.profile(False)
-    dom.time_halo = dom.time_phases = False
-    timeline = {}
-    for (_, a), (name, b) in zip(dom._phase_events[:-1], dom._phase_events[1:]):
-        key = "integrator" if name == "step_start" else name
-        timeline[key] = timeline.get(key, 0.0) + a.elapsed_time(b) / args.steps
-    halo_ms = sum(a.elapsed_time(b) for a, b in dom._halo_events) / args.steps
-    st = backend.stats()
-    # end to end with host buffers: every rank uploads all positions, forces come back summed over the ranks
-    Rh = dom.gather_global(dom.R[: dom.n0]).cpu().numpy()
-    Vh = dom.gather_global(dom.V).cpu().numpy()
-    acc = (0.5 * dt * ACC_UNIT / m).astype(np.float32)[:, None]
-    _, Fh = dom.compute_host(Rh)
-    Fh = Fh.copy()
-    torch.cuda.synchronize()
-    dist.barrier()
-    t0 = time.perf_counter()
-    # the host integrator is part of the step: fused in-place updates on flat views (one pass each over the arrays; numpy's
-    # inner loops over a last axis of 3 are slow and every temporary is another 12 MB of host traffic per rank)
-    acc3 = torch.from_numpy(np.ascontiguousarray(np.repeat(acc, 3, axis=1)).reshape(-1))
-    Rh, Vh = np.ascontiguousarray(Rh), np.ascontiguousarray(Vh)
-    Rt, Vt = torch.from_numpy(Rh).view(-1), torch.from_numpy(Vh).view(-1)
-
-    def kick(F):
-        Vt.addcmul_(torch.from_numpy(np.ascontiguousarray(F)).view(-1), acc3)
-
-    for _ in range(args.steps):
-        kick(Fh)
-        Rt.add_(Vt, alpha=dt)
-        _, Fh = dom.compute_host(Rh)
-        kick(Fh)
-    torch.cuda.synchronize()
-    dist.barrier()
-    t_e2e = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
-    dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
-    t_e2e = float(t_e2e)
-    if rank == 0:
-        value = N * args.steps / (ms * 1e-3)
-        groups = {k: v for k, v in prof.items() if v[1] > 0}
-        top = max((g for g in groups if args.algorithmic_bytes(g, dom.n_local, st["edges"], st["pairs"])), key=lambda g: groups[g][0])
-        t_launch = groups[top][0] / groups[top][1]
-        ab = args.algorithmic_bytes(top, dom.n_local, st["edges"], st["pairs"])
-        peak, kind = args.peaks()
-        ach = ab / (t_launch * 1e-3) / 1e9
-        roofline = {"kernel": top, "bound": "hbm", "achieved": round(ach, 1), "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s",
-                    "frac": round(ach / peak, 4),
-                    "traffic": args.traffic if args.traffic is not None else args.ncu_traffic(top, dom.n0),
-                    "algorithmic_bytes_per_launch": ab,
-                    "ms_per_launch": round(t_launch, 4), "scope": "rank 0's sub-box (local atoms incl. ghosts)",
-                    "halo_exchange_ms_per_step": round(halo_ms, 3),
-                    "timeline_ms_per_step": {k: round(v, 3) for k, v in timeline.items()},
-                    "groups_ms_per_step": {g: round(v[0] / args.steps, 4) for g, v in sorted(groups.items(), key=lambda kv: -kv[1][0])}}
-        line = {"metric": "atom-steps/s (E+F)", "value": round(value, 1), "unit": "atom-steps/s", "n_gpus": world, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
-                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": f"{args.workload}: {N} atoms periodic water, cutoffs 4.5/12 A, skin {args.skin} A, "
-                                       + ("NVT (Nose-Hoover chain 3) at 300 K, dt 0.5 fs" if ensemble == "nvt" else "NVE dt 0.5 fs from 300 K"),
-                           "atoms": N, "decomposition": f"{world} slabs along axis {dom.geo.axis}, halo {dom.geo.lr_radius:.1f} A (features: {dom.geo.shell:.1f} A)",
-                           "local_atoms_sum_over_ranks": int(nloc[0]), "list_rebuilds_in_timed_steps": rebuilds,
-                           "repartition_ms_each": round(1e3 * getattr(dom, "t_repartition", 0.0) / max(1, dom.n_rebuilds - 1), 2),
-                           "l2_policy": ("inputs larger than L2: a step streams about 18 kB per local atom"
-                                         if dom.n0 * 18e3 > 126e6 else "inputs smaller than L2; no flush"),
-                           "host_ms_per_step": round(host_ms, 3),
-                           "ns_per_day": round(args.steps / (ms * 1e-3) * 0.0432, 3)},
-                "e2e": {"value": round(N * args.steps / t_e2e, 1), "unit": "atom-steps/s", "h2d_bytes_per_step": N * 12 * world,
-                        "d2h_bytes_per_step": (N * 12 + 8) * world, "ms_per_step": round(1e3 * t_e2e / args.steps, 3)},
-                "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": None}
-        print(json.dumps(line), flush=True)
-    dist.barrier()
-    dist.destroy_process_group()

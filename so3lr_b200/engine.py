@@ -91,6 +91,10 @@ class System:
         check(lib.so3lr_b200_system_set_cell(self._h, _ptr(c9)), "set_cell")
         self._cell = np.asarray(cell, dtype=np.float64).reshape(3, 3)
 
+    def defer_skin_test(self, on=True, margin=0.05):
+        """Read the skin-test flag one step late (no host wait per step); lists are rebuilt at skin / 2 - margin instead."""
+        check(lib.so3lr_b200_system_defer_skin_test(self._h, 1 if on else 0, float(margin)), "defer_skin_test")
+
     def enable_virial(self, on=True):
         """Also accumulate the strain derivative of the energy (single-structure contexts); compute() then returns
         'virial' (3,3) float64 = dE/d eps in eV and, for a periodic cell, 'stress' = virial / volume in eV/A^3."""

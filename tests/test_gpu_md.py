@@ -299,3 +299,29 @@ def test_decomposed_npt_tracks_single_device():
     assert np.median(np.abs(Vdd - Vd.cpu().numpy())) < 2e-6
     np.testing.assert_allclose(stt[2:5], ref[2:5], rtol=1e-3, atol=1e-8)
     assert stt[1] == 1.0
+
+
+def test_deferred_skin_test_gives_the_same_trajectory():
+    """so3lr_b200_system_defer_skin_test: the rebuild decision is read one step late (no host wait per step) and the trigger
+    distance is lowered by the margin.  Lists built earlier or later hold the same pairs inside the cutoff, so the trajectory
+    equals the default mode's up to the order of float32 sums, and the lists are still rebuilt on the way."""
+    from so3lr_b200 import workloads as W
+    from so3lr_b200.engine import System
+    Z, R, cell = W.water_box(64, 12.42, 1000)
+    V, m = W.maxwell_boltzmann(Z, 600.0, 3)
+    res = []
+    for deferred in (False, True):
+        s = System(Z, cell, cutoff_lr=6.0, damping=2.0, skin=0.4)
+        if deferred:
+            s.defer_skin_test(True, margin=0.05)
+        Rd = torch.tensor(R, dtype=torch.float32, device="cuda")
+        Vd = torch.tensor(V, dtype=torch.float32, device="cuda")
+        md = torch.tensor(m, dtype=torch.float32, device="cuda")
+        Fd = s.compute(Rd)["forces"].clone()
+        s.nve(120, 0.5, md, Rd, Vd, Fd)
+        torch.cuda.synchronize()
+        res.append((Rd.cpu().numpy(), Fd.cpu().numpy(), s.stats()["rebuilds"]))
+    (R0, F0, n0), (R1, F1, n1) = res
+    assert n0 >= 2 and n1 >= n0                      # the lowered trigger rebuilds at least as often
+    assert np.abs(R1 - R0).max() < 2e-3 and np.abs(F1 - F0).max() < 5e-2      # chaotic growth of float32 differences over 120 steps
+    assert np.median(np.abs(R1 - R0)) < 2e-5

@@ -1,4 +1,5 @@
-"""The allocation-free pair-list entry point against the allocating one (so3lr_b200_system_export_list).
+"""The allocation-free pair-list entry point against the allocating one (so3lr_b200_system_export_list) and against the
+CPU oracle's pair sets.
 
 Collected last on purpose: a run that stops at the first failure has then already run every other test.  The entry
 point keeps its scratch in a fixed array inside the library, so the second of two back-to-back calls starts from the
@@ -78,3 +79,34 @@ def test_no_alloc_free_space_and_size_limit(reference_goldens):
     with pytest.raises(So3lrB200Error) as e:
         neighbor_list_noalloc(big, None, 4.5, False, idx, count, overflow)
     assert e.value.status == 5
+
+
+@pytest.mark.parametrize("ordered", [False, True])
+def test_no_alloc_list_matches_oracle_in_a_triclinic_cell(ordered):
+    """Directly against the oracle's pair set, in a sheared cell, two calls in a row; and the documented precondition (every
+    perpendicular cell width at least twice the cutoff) is enforced instead of silently returning a minimum-image list."""
+    from oracle import so3lr_oracle as O
+    from so3lr_b200 import workloads as W
+    from so3lr_b200._lib import So3lrB200Error
+    from so3lr_b200.engine import neighbor_list_noalloc
+    Z, R, _ = W.water_box(216, 18.7, 5)
+    cell = np.array([[18.7, 0, 0], [3.1, 18.7, 0], [-2.0, 4.0, 18.7]])
+    R = np.asarray(R, dtype=np.float32)
+    rc = 5.5
+    ii, jj = O.neighbor_list(R, cell, rc, ordered=ordered)
+    want = np.stack([ii, jj], 1)
+    want = want[np.lexsort((want[:, 1], want[:, 0]))]
+    cap = len(ii) + 11
+    Rt = torch.tensor(R, device="cuda")
+    idx = torch.empty((2, cap), dtype=torch.int32, device="cuda")
+    count = torch.zeros(1, dtype=torch.int64, device="cuda")
+    overflow = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        idx.fill_(-3)
+        neighbor_list_noalloc(Rt, cell, rc, ordered, idx, count, overflow)
+        torch.cuda.synchronize()
+        assert int(count.item()) == len(ii) and int(overflow.item()) == 0
+        assert np.array_equal(_pairs(idx.cpu().numpy(), len(ii)), want)
+    with pytest.raises(So3lrB200Error) as e:          # 18.7 A wide cell, 9.5 A cutoff: a second image would be inside
+        neighbor_list_noalloc(Rt, cell, 9.5, ordered, idx, count, overflow)
+    assert e.value.status == 1
