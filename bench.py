@@ -224,6 +224,8 @@ def run_b200(args, rank, world, local_rank):
     N = len(Z)
     skin = args.skin
     sysm = System(Z, cell, cutoff_lr=12.0, damping=2.0, skin=skin, device=local_rank)
+    if skin > 0.1:
+        sysm.defer_skin_test(True, 0.05)     # no host wait inside a step: the rebuild decision is taken one step late
     Rd = torch.tensor(R, dtype=torch.float32, device=dev)
     Vd = torch.tensor(V, dtype=torch.float32, device=dev)
     md = torch.tensor(m, dtype=torch.float32, device=dev)
@@ -354,6 +356,7 @@ def run_domain(args, rank, world, local_rank):
     ensemble = args.ensemble or ENSEMBLE[args.workload]
     if ensemble == "npt":
         backend.enable_virial(True)
+    dom.defer_skin_test(True, 0.05)      # no host read inside a step: the rebuild decision is taken one step late
     dom.compute(check_rebuild=False)
     # one clock sampler for all GPUs, on rank 0, started ahead of the warm-up (its start-up disturbs running CUDA work)
     sampler = ClockSampler(list(range(world))) if rank == 0 else None

@@ -41,7 +41,8 @@ constexpr int kAHalf = 16 * kLboA;            // one FP16 matrix of 128 rows x 1
 constexpr int kWStride = 132;                 // floats per row of the filter tile
 constexpr int kFwRec = 36;                    // floats per forward record: j | i | cutoff / nbar | - | Y[24] | padding (bank spread)
 constexpr int kFwThreads = 512;
-constexpr int kBwRec = 36;
+constexpr int kBwRec = 52;                    // floats per reverse record (48 used; 52 spreads consecutive rows over the banks)
+constexpr int kBwThreads = 512;
 constexpr float kInvNbar = 1.0f / kAvgNumNeighbors;
 constexpr float kRc2 = kCutoffSr * kCutoffSr;
 constexpr float kLoScale = 2048.f, kLoInv = 1.f / 2048.f;
@@ -65,7 +66,7 @@ constexpr int kSmemFwd = kOffFwStEv + TE * 2 * kEvStride * 4;
 constexpr int kOffBwW = kOffA + kARegion;
 constexpr int kOffBwRec = kOffBwW + 64 * kWStride * 4;
 constexpr int kOffBwSph = kOffBwRec + TE * kBwRec * 4;
-constexpr int kOffBwMisc = kOffBwSph + 320 * 4;
+constexpr int kOffBwMisc = kOffBwSph + 512 * 4;
 constexpr int kSmemBwd = kOffBwMisc + 64;
 static_assert(kSmemFwd <= 232448 && kSmemBwd <= 232448, "shared memory budget of one CTA per SM");
 
@@ -292,29 +293,24 @@ __device__ __noinline__ void issue_forward_mma(uint32_t tmem, uint32_t a_hi, uin
     }
 }
 
-// Reverse kernel, one image for both directions (see model.cu): C[m][c] core (m/8, c/8) at (m/8) * 4096 + (c/8) * 128,
-// K2_f[h][n] core (h/8, n/8) at (h/8) * 2048 + (n/8) * 128.  Forward product (MN-major B): w_f = Phi * C_f + hs_f * K2_f,
-// main accumulators in TMEM columns [128 f, 128 f + 128), cross 256 columns above.
+// Reverse kernel, one image for both directions, per filter f (24,576 bytes each; hi of f = 0, 1 then lo of f = 0, 1): the 96
+// rows [64 Chebyshev terms | 32 hidden units] by the 128 features of the filter, core (row / 8, feature / 8) at
+// (feature / 8) * 1536 + (row / 8) * 128 with the 8 features of a core row contiguous.
+// Forward product (B read MN-major: N = features, K = rows): w_f = [Phi | hs_f] * [C_f ; K2_f], main accumulators in TMEM
+// columns [128 f, 128 f + 128), cross 256 columns above.
+constexpr int kRevImgFilter = 16 * 1536;
 __device__ __noinline__ void issue_filter_mma(uint32_t tmem, uint32_t a_hi, uint32_t img, int f) {
   const uint64_t da = desc_base(kLboA, 128) + (a_hi >> 4), dal = da + (kAHalf >> 4);
-  const uint64_t dc = desc_base(4096, 128) + ((img + f * 16 * 128) >> 4), dcl = dc + (32768 >> 4);
-  const uint64_t dk = desc_base(2048, 128) + ((img + 65536 + f * 8192) >> 4), dkl = dk + (16384 >> 4);
+  const uint64_t db = desc_base(128, 1536) + ((img + f * kRevImgFilter) >> 4), dbl = db + (2 * kRevImgFilter >> 4);
   const uint32_t id128 = make_idesc(128, 1);
   const uint32_t d_main = tmem + 128 * f, d_cross = d_main + 256;
 #pragma unroll
-  for (int ks = 0; ks < 4; ++ks) {
-    const uint64_t ah = da + ks * (2 * kLboA >> 4), al = dal + ks * (2 * kLboA >> 4);
-    const uint64_t bh = dc + ks * (2 * 4096 >> 4), bl = dcl + ks * (2 * 4096 >> 4);
+  for (int ks = 0; ks < 6; ++ks) {      // K = 16 rows per step: Chebyshev chunks 0..7 of A, then the two chunks pairs of hs_f
+    const int chunk = ks < 4 ? 2 * ks : 8 + 4 * f + 2 * (ks - 4);
+    const uint64_t ah = da + chunk * (kLboA >> 4), al = dal + chunk * (kLboA >> 4);
+    const uint64_t bh = db + ks * (2 * 128 >> 4), bl = dbl + ks * (2 * 128 >> 4);
     umma(d_main, ah, bh, id128, ks > 0);
     umma(d_cross, ah, bl, id128, ks > 0);
-    umma(d_cross, al, bh, id128, 1);
-  }
-#pragma unroll
-  for (int ks = 0; ks < 2; ++ks) {
-    const uint64_t ah = da + (8 + 4 * f + 2 * ks) * (kLboA >> 4), al = dal + (8 + 4 * f + 2 * ks) * (kLboA >> 4);
-    const uint64_t bh = dk + ks * (2 * 2048 >> 4), bl = dkl + ks * (2 * 2048 >> 4);
-    umma(d_main, ah, bh, id128, 1);
-    umma(d_cross, ah, bl, id128, 1);
     umma(d_cross, al, bh, id128, 1);
   }
 }
@@ -629,115 +625,180 @@ namespace {
 // record fields (floats): 0 j | 1 i | 2 cutoff / nbar | 3 its r-derivative | 4-7 invariants | 8-11 their cotangents |
 // 12-15 dA, 16-19 dB: cotangents of the equivariant logits of edge (i<-j) and (j<-i) | 20-23, 24-27 those logits x cutoff |
 // 28-30 unit vector | 31 1/r | 32 d/dr | 33 r | 34 1 for a list entry, 0 for a padding row
-// [dPhi | dhs_f] = dw_f * [C_f^T | K2_f^T] (K-major B from the same image): main accumulators in TMEM columns
-// [128 f, 128 f + 96), cross 256 columns above
+// [dPhi | dhs_f] = dw_f * [C_f^T | K2_f^T] (the same image read K-major: N = 96 rows, K = features): main accumulators in TMEM
+// columns [128 f, 128 f + 96), cross 256 columns above
 __device__ __noinline__ void issue_reverse_mma(uint32_t tmem, uint32_t a_hi, uint32_t img, int f) {
   const uint64_t da = desc_base(kLboA, 128) + (a_hi >> 4), dal = da + (kAHalf >> 4);
-  const uint64_t dc = desc_base(128, 4096) + ((img + f * 16 * 128) >> 4), dcl = dc + (32768 >> 4);
-  const uint64_t dk = desc_base(128, 2048) + ((img + 65536 + f * 8192) >> 4), dkl = dk + (16384 >> 4);
-  const uint32_t id64 = make_idesc(64, 0), id32 = make_idesc(32, 0);
-  const uint32_t d_rad = tmem + 128 * f, d_sph = d_rad + 64;
+  const uint64_t db = desc_base(1536, 128) + ((img + f * kRevImgFilter) >> 4), dbl = db + (2 * kRevImgFilter >> 4);
+  const uint32_t id96 = make_idesc(96, 0);
+  const uint32_t d_main = tmem + 128 * f, d_cross = d_main + 256;
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks) {      // K = 16 features per step
     const uint64_t ah = da + ks * (2 * kLboA >> 4), al = dal + ks * (2 * kLboA >> 4);
-    const uint64_t ch = dc + ks * (2 * 128 >> 4), cl = dcl + ks * (2 * 128 >> 4);
-    const uint64_t kh = dk + ks * (2 * 128 >> 4), kl = dkl + ks * (2 * 128 >> 4);
-    umma(d_rad, ah, ch, id64, ks > 0);
-    umma(d_rad + 256, ah, cl, id64, ks > 0);
-    umma(d_rad + 256, al, ch, id64, 1);
-    umma(d_sph, ah, kh, id32, ks > 0);
-    umma(d_sph + 256, ah, kl, id32, ks > 0);
-    umma(d_sph + 256, al, kh, id32, 1);
+    const uint64_t bh = db + ks * (2 * 1536 >> 4), bl = dbl + ks * (2 * 1536 >> 4);
+    umma(d_main, ah, bh, id96, ks > 0);
+    umma(d_cross, ah, bl, id96, ks > 0);
+    umma(d_cross, al, bh, id96, 1);
   }
 }
 
-// Edge loop of the reverse pass for filter F over the 8 tile rows [row0, row0 + 8) of one warp (lane = 4 features).
+// Sender-side q / k rows of four consecutive tile rows for the reverse edge loop of filter F (lane = 4 features)
+struct RevLoads {
+  float4 qj[4], kj[4], qa, ka;     // senders' rows; q / k of the first row's receiver
+};
 template <int F>
-__device__ __forceinline__ void reverse_edge_run(float* rec, const float* wt, int wrow0, int row0, unsigned char* a_hi, int lane,
-                                                 const float* __restrict__ qkv, const float* __restrict__ g_xa,
-                                                 float* __restrict__ g_qkv) {
+__device__ __forceinline__ void reverse_prefetch(RevLoads& L, const float* rec, int row0, int lane, const float* __restrict__ qkv) {
+  const int col = 4 * lane;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const float* pj = qkv + (size_t)__float_as_int(rec[(row0 + u) * kBwRec]) * kProj + F * 3 * kF;
+    L.qj[u] = ld4(pj + col);
+    L.kj[u] = ld4(pj + kF + col);
+  }
+  const float* pi = qkv + (size_t)__float_as_int(rec[row0 * kBwRec + 1]) * kProj + F * 3 * kF;
+  L.qa = ld4(pi + col);
+  L.ka = ld4(pi + kF + col);
+}
+
+// Value path of the invariant filter, split off the edge loop so that it runs while the tensor cores are busy.
+// Before the loop (rows [row0, row0 + 8) of one warp): cotangents of the invariant logits of both directions of every edge,
+// daA_h = <g_xa[i], v[j]>_h and daB_h = <g_xa[j], v[i]>_h, into record fields 36..39 and 40..43.
+__device__ __forceinline__ void value_logit_cotangents(float* rec, int row0, int lane, const float* __restrict__ qkv,
+                                                       const float* __restrict__ g_xa) {
   const int col = 4 * lane, grp = lane >> 3, cg = lane & 7;
   int cur_i = -1;
-  float4 qa = f4_zero(), ka = f4_zero(), v_i = f4_zero(), gx_i = f4_zero();
-  float4 gq = f4_zero(), gk = f4_zero(), gv = f4_zero();
-  auto flush = [&]() {
-    if (cur_i < 0) return;
-    float* gi = g_qkv + (size_t)cur_i * kProj + F * 3 * kF + col;
-    if (f4_nonzero(gq)) atomicAdd(reinterpret_cast<float4*>(gi), gq);
-    if (f4_nonzero(gk)) atomicAdd(reinterpret_cast<float4*>(gi + kF), gk);
-    if (F == 0 && f4_nonzero(gv)) atomicAdd(reinterpret_cast<float4*>(gi + 2 * kF), gv);
-  };
+  float4 v_i = f4_zero(), gx_i = f4_zero();
 #pragma unroll 1
   for (int k0 = 0; k0 < 8; k0 += 4) {
-    float4 wv[4], qj[4], kj[4], vj[4], gxj[4], r0[4];
+    float4 vj[4], gxj[4];
+    int ii[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const float* rp = rec + (row0 + k0 + u) * kBwRec;
-      r0[u] = ld4(rp);
-      const int j = __float_as_int(r0[u].x);
-      const float* pj = qkv + (size_t)j * kProj + F * 3 * kF;
-      qj[u] = ld4(pj + col); kj[u] = ld4(pj + kF + col);
-      if (F == 0) { vj[u] = ld4(pj + 2 * kF + col); gxj[u] = ld4(g_xa + (size_t)j * kF + col); }
-      wv[u] = ld4(wt + (wrow0 + k0 + u) * kWStride + col);
+      const int j = __float_as_int(rp[0]);
+      ii[u] = __float_as_int(rp[1]);
+      vj[u] = ld4(qkv + (size_t)j * kProj + 2 * kF + col);
+      gxj[u] = ld4(g_xa + (size_t)j * kF + col);
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const int row = row0 + k0 + u;
-      float* rp = rec + row * kBwRec;
-      const int i = __float_as_int(r0[u].y);
-      const float sc = r0[u].z, dcn = r0[u].w;
-      if (i != cur_i) {
-        flush();
-        cur_i = i;
-        gq = f4_zero(); gk = f4_zero(); gv = f4_zero();
-        const float* pi = qkv + (size_t)i * kProj + F * 3 * kF;
-        qa = ld4(pi + col); ka = ld4(pi + kF + col);
-        if (F == 0) { v_i = ld4(pi + 2 * kF + col); gx_i = ld4(g_xa + (size_t)i * kF + col); }
+      if (ii[u] != cur_i) {
+        cur_i = ii[u];
+        v_i = ld4(qkv + (size_t)cur_i * kProj + 2 * kF + col);
+        gx_i = ld4(g_xa + (size_t)cur_i * kF + col);
       }
-      const float4 w = wv[u];
-      const float DA = group8_sum(dot3(qa, w, kj[u]));
-      const float DB = group8_sum(dot3(qj[u], w, ka));
-      float daA, daB;
-      if (F == 0) {
-        daA = group8_sum(dot2(gx_i, vj[u]));
-        daB = group8_sum(dot2(gxj[u], v_i));
-        gv = f4_fma(sc * DB, gxj[u], gv);
-      } else {
-        daA = rp[12 + grp];
-        daB = rp[16 + grp];
-        if (cg == 0) { rp[20 + grp] = sc * DA; rp[24 + grp] = sc * DB; }
+      const float daA = group8_sum(dot2(gx_i, vj[u])), daB = group8_sum(dot2(gxj[u], v_i));
+      if (cg == 0) {
+        float* rp = rec + (row0 + k0 + u) * kBwRec;
+        rp[36 + grp] = daA;
+        rp[40 + grp] = daB;
       }
-      const float dDA = sc * daA, dDB = sc * daB;
-      gq = make_float4(fmaf(dDA * w.x, kj[u].x, gq.x), fmaf(dDA * w.y, kj[u].y, gq.y), fmaf(dDA * w.z, kj[u].z, gq.z), fmaf(dDA * w.w, kj[u].w, gq.w));
-      gk = make_float4(fmaf(dDB * w.x, qj[u].x, gk.x), fmaf(dDB * w.y, qj[u].y, gk.y), fmaf(dDB * w.z, qj[u].z, gk.z), fmaf(dDB * w.w, qj[u].w, gk.w));
-      float dwv[4] = {fmaf(dDA * qa.x, kj[u].x, dDB * qj[u].x * ka.x), fmaf(dDA * qa.y, kj[u].y, dDB * qj[u].y * ka.y),
-                      fmaf(dDA * qa.z, kj[u].z, dDB * qj[u].z * ka.z), fmaf(dDA * qa.w, kj[u].w, dDB * qj[u].w * ka.w)};
-      // dw as A operand of the second MMA chain: row = edge, columns 4 lane .. 4 lane + 3 of the hi and the lo matrix
-      {
-        uint2 h, l;
-        split2(dwv[0], dwv[1], h.x, l.x); split2(dwv[2], dwv[3], h.y, l.y);
-        unsigned char* p = a_hi + (lane >> 1) * kLboA + row * 16 + (lane & 1) * 8;
-        *reinterpret_cast<uint2*>(p) = h;
-        *reinterpret_cast<uint2*>(p + kAHalf) = l;
-      }
-      // cutoff part of d/dr, summed over the four heads
-      float gc = dcn * fmaf(daA, DA, daB * DB);
-      gc += __shfl_xor_sync(0xffffffffu, gc, 8);
-      gc += __shfl_xor_sync(0xffffffffu, gc, 16);
-      if (lane == 0) rp[32] += gc;
     }
   }
-  flush();
+}
+// After the loop: cotangent of this receiver's value row, gv_i = sum_edges (cutoff x logit of edge j<-i)_h g_xa[j] (fields 44..47)
+__device__ __forceinline__ void value_cotangent(const float* rec, int row0, int lane, const float* __restrict__ g_xa, float* __restrict__ g_qkv) {
+  const int col = 4 * lane, grp = lane >> 3;
+  float4 gxj[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) gxj[u] = ld4(g_xa + (size_t)__float_as_int(rec[(row0 + u) * kBwRec]) * kF + col);
+  int cur_i = __float_as_int(rec[row0 * kBwRec + 1]);
+  float4 gv = f4_zero();
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const float* rp = rec + (row0 + u) * kBwRec;
+    const int i = __float_as_int(rp[1]);
+    if (i != cur_i) {
+      if (f4_nonzero(gv)) red_add_v4(g_qkv + (size_t)cur_i * kProj + 2 * kF + col, gv);
+      cur_i = i;
+      gv = f4_zero();
+    }
+    gv = f4_fma(rp[44 + grp], gxj[u], gv);
+  }
+  if (f4_nonzero(gv)) red_add_v4(g_qkv + (size_t)cur_i * kProj + 2 * kF + col, gv);
 }
 
-__global__ void __launch_bounds__(256, 1) attn_bwd_tc_kernel(const unsigned char* __restrict__ img_g, const float* __restrict__ sph1_k,
-                                                             const float* __restrict__ sph1_b, int n_recv, const int* __restrict__ vrow_ptr,
-                                                             const int* __restrict__ ve_i, const int* __restrict__ ve_j,
-                                                             const float4* __restrict__ ve_d, const float* __restrict__ qkv,
-                                                             const float* __restrict__ ev_in, const float* __restrict__ g_xa,
-                                                             const float* __restrict__ gev1, float* __restrict__ g_qkv,
-                                                             float* __restrict__ gev_in, float* __restrict__ F, float* __restrict__ virial,
-                                                             int* __restrict__ err, long long* __restrict__ dbg) {
+// Reverse edge loop of filter F over four tile rows [row0, row0 + 4) of one warp: logits of both directions of every edge,
+// cotangents of this receiver's q / k rows (added to g_qkv with vector reductions when the receiver changes), dw into the
+// A operand of the second MMA chain, the cutoff part of d/dr into the records.  The cotangents of the logits come from the
+// records (fields 36.. for the invariant filter, 12.. for the equivariant one); cutoff x logit goes back (44.. / 20.., 24..).
+template <int F>
+__device__ __forceinline__ void reverse_edges4(const RevLoads& L, float* rec, const float* wt, int wrow0, int row0, unsigned char* a_hi,
+                                               int lane, const float* __restrict__ qkv, float* __restrict__ g_qkv) {
+  const int col = 4 * lane, grp = lane >> 3, cg = lane & 7;
+  int cur_i = __float_as_int(rec[row0 * kBwRec + 1]);
+  float4 qa = L.qa, ka = L.ka;
+  float4 gq = f4_zero(), gk = f4_zero();
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int row = row0 + u;
+    float* rp = rec + row * kBwRec;
+    const float4 r0 = ld4(rp);
+    const int i = __float_as_int(r0.y);
+    const float sc = r0.z, dcn = r0.w;
+    if (i != cur_i) {      // rare: a run of four rows mostly stays with one receiver
+      {
+        float* gi = g_qkv + (size_t)cur_i * kProj + F * 3 * kF + col;
+        if (f4_nonzero(gq)) red_add_v4(gi, gq);
+        if (f4_nonzero(gk)) red_add_v4(gi + kF, gk);
+      }
+      cur_i = i;
+      gq = f4_zero(); gk = f4_zero();
+      const float* pi = qkv + (size_t)i * kProj + F * 3 * kF;
+      qa = ld4(pi + col); ka = ld4(pi + kF + col);
+    }
+    const float4 w = ld4(wt + (wrow0 + u) * kWStride + col);
+    const float4 qj = L.qj[u], kj = L.kj[u];
+    const float DA = group8_sum(dot3(qa, w, kj));
+    const float DB = group8_sum(dot3(qj, w, ka));
+    const float daA = rp[(F ? 12 : 36) + grp], daB = rp[(F ? 16 : 40) + grp];
+    if (cg == 0) {
+      if (F) { rp[20 + grp] = sc * DA; rp[24 + grp] = sc * DB; }
+      else rp[44 + grp] = sc * DB;
+    }
+    const float dDA = sc * daA, dDB = sc * daB;
+    gq = make_float4(fmaf(dDA * w.x, kj.x, gq.x), fmaf(dDA * w.y, kj.y, gq.y), fmaf(dDA * w.z, kj.z, gq.z), fmaf(dDA * w.w, kj.w, gq.w));
+    gk = make_float4(fmaf(dDB * w.x, qj.x, gk.x), fmaf(dDB * w.y, qj.y, gk.y), fmaf(dDB * w.z, qj.z, gk.z), fmaf(dDB * w.w, qj.w, gk.w));
+    const float dw0 = fmaf(dDA * qa.x, kj.x, dDB * qj.x * ka.x), dw1 = fmaf(dDA * qa.y, kj.y, dDB * qj.y * ka.y);
+    const float dw2 = fmaf(dDA * qa.z, kj.z, dDB * qj.z * ka.z), dw3 = fmaf(dDA * qa.w, kj.w, dDB * qj.w * ka.w);
+    // dw as A operand of the second MMA chain: row = edge, columns 4 lane .. 4 lane + 3 of the hi and the lo matrix
+    {
+      uint2 h, l;
+      split2(dw0, dw1, h.x, l.x); split2(dw2, dw3, h.y, l.y);
+      unsigned char* p = a_hi + (lane >> 1) * kLboA + row * 16 + (lane & 1) * 8;
+      *reinterpret_cast<uint2*>(p) = h;
+      *reinterpret_cast<uint2*>(p + kAHalf) = l;
+    }
+    // cutoff part of d/dr, summed over the four heads
+    float gc = dcn * fmaf(daA, DA, daB * DB);
+    gc += __shfl_xor_sync(0xffffffffu, gc, 8);
+    gc += __shfl_xor_sync(0xffffffffu, gc, 16);
+    if (lane == 0) rp[32] += gc;
+  }
+  float* gi = g_qkv + (size_t)cur_i * kProj + F * 3 * kF + col;
+  if (f4_nonzero(gq)) red_add_v4(gi, gq);
+  if (f4_nonzero(gk)) red_add_v4(gi + kF, gk);
+}
+
+// record fields (floats): 0 j | 1 i | 2 cutoff / nbar | 3 its r-derivative | 4-7 invariants | 8-11 their cotangents |
+// 12-15 dA, 16-19 dB: cotangents of the equivariant logits of edge (i<-j) and (j<-i) | 20-23, 24-27 those logits x cutoff |
+// 28-30 unit vector | 31 1/r | 32 d/dr (cutoff part + even Chebyshev terms) | 33 r | 34 1 for a list entry, 0 for a padding row |
+// 35 d/dr (odd Chebyshev terms) | 36-39, 40-43 cotangents of the invariant logits of edge (i<-j) and (j<-i) |
+// 44-47 invariant logit of edge (j<-i) x cutoff
+//
+// 16 warps.  Per tile: (1) four threads per edge prepare records and the A operand; (2) MMA chain w = Phi C + hs K2 (both filters);
+// (3) per filter, in two halves of 64 rows: tensor memory -> shared tile, reverse edge loop (4 rows per warp, sender rows
+// prefetched across the barriers), dw into the A operand; (4) per filter: MMA chain [dPhi | dhs] = dw [C^T | K2^T], then per
+// edge the radial derivative and the spherical hidden layer; (5) angular part, force on the receiver, cotangent of ev.
+__global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsigned char* __restrict__ img_g, const float* __restrict__ sph1_k,
+                                                                    const float* __restrict__ sph1_b, int n_recv,
+                                                                    const int* __restrict__ vrow_ptr, const int* __restrict__ ve_i,
+                                                                    const int* __restrict__ ve_j, const float4* __restrict__ ve_d,
+                                                                    const float* __restrict__ qkv, const float* __restrict__ ev_in,
+                                                                    const float* __restrict__ g_xa, const float* __restrict__ gev1,
+                                                                    float* __restrict__ g_qkv, float* __restrict__ gev_in,
+                                                                    float* __restrict__ F, float* __restrict__ virial,
+                                                                    int* __restrict__ err, long long* __restrict__ dbg) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float* rec = reinterpret_cast<float*>(smem + kOffBwRec);
@@ -749,8 +810,11 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_tc_kernel(const unsigned char
   const long long n_tiles = (n_edges + TE - 1) / TE;
   const long long tile0 = n_tiles * blockIdx.x / gridDim.x, tile1 = n_tiles * (blockIdx.x + 1) / gridDim.x;
   if (tile0 >= tile1) return;
-  for (int k = tid; k < kTcImageBytes / 16; k += 256) reinterpret_cast<uint4*>(smem + kOffImg)[k] = reinterpret_cast<const uint4*>(img_g)[k];
-  for (int k = tid; k < 320; k += 256) sph[k] = k < 256 ? sph1_k[k] : sph1_b[k - 256];
+  for (int k = tid; k < kTcImageBytes / 16; k += kBwThreads) reinterpret_cast<uint4*>(smem + kOffImg)[k] = reinterpret_cast<const uint4*>(img_g)[k];
+  for (int k = tid; k < 512; k += kBwThreads) {      // [filter][hidden unit][w0 w1 w2 w3 b - - -]
+    const int q = k & 7, c = (k >> 3) & 31, f = k >> 8;
+    sph[k] = q < 4 ? sph1_k[f * 128 + q * 32 + c] : (q == 4 ? sph1_b[f * 32 + c] : 0.f);
+  }
   const uint32_t mbar = smem_u32(mbar_p);
   if (tid == 0) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(mbar));
@@ -769,6 +833,8 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_tc_kernel(const unsigned char
   unsigned char* a_ptr = smem + kOffA;
   const int pad_i = ve_i[n_edges - 1];
   const int deg = degree_of(lane < kMTot ? lane : 0);
+  const int quad = warp & 3;                    // TMEM lane quadrant of this warp
+  const int wrow = 4 * warp;                    // this warp's 4 rows inside a 64-row half of the tile
   uint32_t parity = 0;
   bool failed = false;
 #ifdef SO3LR_TC_TIMING
@@ -781,101 +847,125 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_tc_kernel(const unsigned char
   for (long long tile = tile0; tile < tile1 && !failed; ++tile) {
     // ---- per-edge preparation ----
     {
-      const int row = tid & 127;
+      const int row = tid & 127, role = tid >> 7;
       const long long e = tile * TE + row;
       const bool valid = e < n_edges;
       int i = pad_i, j = pad_i;
       if (valid) { i = ve_i[e]; j = ve_j[e]; }
       float* rp = rec + row * kBwRec;
-      if (tid < 128) {
+      if (role < 2) {
         float4 d = make_float4(1.f, 0.f, 0.f, 1.f);
         if (valid) d = ve_d[e];
-        const float r = d.w, ir = 1.f / r;
+        const float r = d.w;
+        const float ir = 1.f / r;
         const float ux = d.x * ir, uy = d.y * ir, uz = d.z * ir;
-        float cut, dcut;
-        phys_cutoff(r, cut, dcut);
-        float Y[kMTot];
-        sph_harm_24(ux, uy, uz, Y);
-        float dA[4] = {0.f, 0.f, 0.f, 0.f}, dB[4] = {0.f, 0.f, 0.f, 0.f};
-        const float* gevi = gev1 + (size_t)i * kMTot;
-        const float* gevj = gev1 + (size_t)j * kMTot;
+        if (role == 0) {
+          float cut, dcut;
+          phys_cutoff(r, cut, dcut);
+          st4(rp, make_float4(__int_as_float(j), __int_as_float(i), valid ? cut * kInvNbar : 0.f, valid ? dcut * kInvNbar : 0.f));
+          st4(rp + 8, f4_zero());
+          st4(rp + 20, f4_zero());
+          st4(rp + 24, f4_zero());
+          st4(rp + 28, make_float4(ux, uy, uz, ir));
+          st4(rp + 32, make_float4(0.f, r, valid ? 1.f : 0.f, 0.f));
+        } else {
+          float Y[kMTot];
+          sph_harm_24(ux, uy, uz, Y);
+          float dA[4] = {0.f, 0.f, 0.f, 0.f}, dB[4] = {0.f, 0.f, 0.f, 0.f};
+          const float* gevi = gev1 + (size_t)i * kMTot;
+          const float* gevj = gev1 + (size_t)j * kMTot;
 #pragma unroll
-        for (int c = 0; c < 6; ++c) {
-          const float4 a = ld4(gevi + 4 * c), b = ld4(gevj + 4 * c);
-          const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+          for (int c = 0; c < 6; ++c) {
+            const float4 a = ld4(gevi + 4 * c), b = ld4(gevj + 4 * c);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            dA[degree_of(4 * c + q)] = fmaf(av[q], Y[4 * c + q], dA[degree_of(4 * c + q)]);
-            dB[degree_of(4 * c + q)] = fmaf(bv[q], Y[4 * c + q], dB[degree_of(4 * c + q)]);
+            for (int q = 0; q < 4; ++q) {
+              dA[degree_of(4 * c + q)] = fmaf(av[q], Y[4 * c + q], dA[degree_of(4 * c + q)]);
+              dB[degree_of(4 * c + q)] = fmaf(bv[q], Y[4 * c + q], dB[degree_of(4 * c + q)]);
+            }
           }
+          dB[0] = -dB[0]; dB[2] = -dB[2];   // Y_lm(-u) = (-1)^l Y_lm(u)
+          st4(rp + 12, make_float4(dA[0], dA[1], dA[2], dA[3]));
+          st4(rp + 16, make_float4(dB[0], dB[1], dB[2], dB[3]));
         }
-        dB[0] = -dB[0]; dB[2] = -dB[2];   // Y_lm(-u) = (-1)^l Y_lm(u)
-        st4(rp, make_float4(__int_as_float(j), __int_as_float(i), valid ? cut * kInvNbar : 0.f, valid ? dcut * kInvNbar : 0.f));
-        st4(rp + 8, f4_zero());
-        st4(rp + 12, make_float4(dA[0], dA[1], dA[2], dA[3]));
-        st4(rp + 16, make_float4(dB[0], dB[1], dB[2], dB[3]));
-        st4(rp + 20, f4_zero());
-        st4(rp + 24, f4_zero());
-        st4(rp + 28, make_float4(ux, uy, uz, ir));
-        st4(rp + 32, make_float4(0.f, r, valid ? 1.f : 0.f, 0.f));
-        store_chebyshev(a_ptr, row, r, valid);
+        store_chebyshev_half(a_ptr, row, r, valid, role);
       } else {
         float s[4];
         invariants(ev_in + (size_t)i * kMTot, ev_in + (size_t)j * kMTot, s);
-        st4(rp + 4, make_float4(s[0], s[1], s[2], s[3]));
-        store_spherical_hidden(a_ptr, row, s, sph);
+        if (role == 2) st4(rp + 4, make_float4(s[0], s[1], s[2], s[3]));
+        store_spherical_hidden_f(a_ptr, row, s, sph, role - 2);
       }
     }
+    BW_MARK(0);
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
-    BW_MARK(0);
-    bool done = true;
+    BW_MARK(1);
     if (tid == 0) {
       tc_fence_after();
       issue_filter_mma(tmem, a_hi, img, 0);
       issue_filter_mma(tmem, a_hi, img, 1);
       umma_commit(mbar);
-      done = mbar_wait(mbar, parity);     // one thread polls; the others park at the barrier below
     }
+    __syncwarp();
+    // while the tensor cores run: the value path's logit cotangents (8 rows per warp), then the sender rows of the first edge run
+    value_logit_cotangents(rec, 8 * warp, lane, qkv, g_xa);
+    RevLoads L;
+    reverse_prefetch<0>(L, rec, wrow, lane, qkv);
+    bool done = true;
+    if (tid == 0) done = mbar_wait(mbar, parity);     // one thread polls; the others park at the barrier below
     parity ^= 1;
     if (!__syncthreads_and(done)) { failed = true; break; }
     tc_fence_after();
-    BW_MARK(1);
+    BW_MARK(2);
 #pragma unroll 1
     for (int f = 0; f < 2 && !failed; ++f) {
 #pragma unroll 1
       for (int hh = 0; hh < 2; ++hh) {
-        if (((warp & 3) >> 1) == hh) tmem_to_tile(tmem, f, warp, lane, 64 * hh, wt);
+        if ((quad >> 1) == hh) {          // the 8 warps whose TMEM lanes hold this half: 32 columns each
+          float v[32];
+          const int col = 32 * (warp >> 2);
+          tmem_ld32_combined(tmem + ((uint32_t)(32 * quad) << 16) + 128 * f + col, v);
+          float* p = wt + (32 * (quad & 1) + lane) * kWStride + col;
+#pragma unroll
+          for (int k = 0; k < 32; k += 4) st4(p + k, make_float4(v[k], v[k + 1], v[k + 2], v[k + 3]));
+        }
         tc_fence_before();
         __syncthreads();
-        BW_MARK(2);
-        if (f == 0) reverse_edge_run<0>(rec, wt, 8 * warp, 64 * hh + 8 * warp, a_ptr, lane, qkv, g_xa, g_qkv);
-        else reverse_edge_run<1>(rec, wt, 8 * warp, 64 * hh + 8 * warp, a_ptr, lane, qkv, g_xa, g_qkv);
         BW_MARK(3);
-        __syncthreads();
+        if (f == 0) {
+          reverse_edges4<0>(L, rec, wt, wrow, 64 * hh + wrow, a_ptr, lane, qkv, g_qkv);
+          if (hh == 0) reverse_prefetch<0>(L, rec, 64 + wrow, lane, qkv);      // next run: second half of filter 0
+          else reverse_prefetch<1>(L, rec, wrow, lane, qkv);                   // next run: first half of filter 1
+        } else {
+          reverse_edges4<1>(L, rec, wt, wrow, 64 * hh + wrow, a_ptr, lane, qkv, g_qkv);
+          if (hh == 0) reverse_prefetch<1>(L, rec, 64 + wrow, lane, qkv);
+        }
         BW_MARK(4);
+        __syncthreads();
       }
       fence_async_smem();
       tc_fence_before();
       __syncthreads();
-      done = true;
       if (tid == 0) {
         tc_fence_after();
         issue_reverse_mma(tmem, a_hi, img, f);
         umma_commit(mbar);
-        done = mbar_wait(mbar, parity);
       }
+      __syncwarp();
+      if (f == 0) value_cotangent(rec, 8 * warp, lane, g_xa, g_qkv);      // while the tensor cores run
+      done = true;
+      if (tid == 0) done = mbar_wait(mbar, parity);
       parity ^= 1;
       if (!__syncthreads_and(done)) { failed = true; break; }
       tc_fence_after();
       BW_MARK(5);
-      // ---- per edge: radial derivative (threads 0..127) and the spherical hidden layer (threads 128..255) ----
+      // ---- per edge: radial derivative (even terms: threads 0..127, odd terms: 128..255), spherical hidden layer (256..383) ----
       {
-        const int row = tid & 127;
+        const int row = tid & 127, role = tid >> 7;
         float* rp = rec + row * kBwRec;
-        const uint32_t lane_base = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + 128 * f;
-        if (tid < 128) {
+        const uint32_t lane_base = tmem + ((uint32_t)(32 * quad) << 16) + 128 * f;
+        if (role < 2) {
           const float r = rp[33];
           const float x = expf(-kChebHalfGamma * r);
           const float t = fmaf(kChebA, x, kChebB), t2 = 2.f * t;
@@ -883,47 +973,32 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_tc_kernel(const unsigned char
           // T_m' = m U_{m-1}; columns 0..31 hold m = 2c (U of odd index), columns 32..63 hold m = 2c + 1 (U of even index);
           // both run U_{n+2} = 2 T_2 U_n - U_{n-2}
           const float T2x2 = 2.f * fmaf(t2, t, -1.f);
+          float v[32];
+          tmem_ld32_combined(lane_base + 32 * role, v);
+          float up = role ? -1.f : -t2, uc = role ? 1.f : 0.f;      // (U_{-2}, U_0) or (U_{-3}, U_{-1})
           float acc = 0.f;
-          {
-            float v[32];
-            tmem_ld32_combined(lane_base, v);
-            float up = -t2, uc = 0.f;      // U_{-3}, U_{-1}
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              acc = fmaf(v[c] * (float)(2 * c), uc, acc);
-              const float un = fmaf(T2x2, uc, -up);
-              up = uc; uc = un;
-            }
+          for (int c = 0; c < 32; ++c) {
+            acc = fmaf(v[c] * (float)(2 * c + role), uc, acc);
+            const float un = fmaf(T2x2, uc, -up);
+            up = uc; uc = un;
           }
-          {
-            float v[32];
-            tmem_ld32_combined(lane_base + 32, v);
-            float up = -1.f, uc = 1.f;     // U_{-2}, U_0
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              acc = fmaf(v[c] * (float)(2 * c + 1), uc, acc);
-              const float un = fmaf(T2x2, uc, -up);
-              up = uc; uc = un;
-            }
-          }
-          rp[32] += acc * dtdr;
-        } else {
+          rp[role ? 35 : 32] += acc * dtdr;
+        } else if (role == 2) {
           float v[32];
           tmem_ld32_combined(lane_base + 64, v);
           const float4 s4 = ld4(rp + 4);
-          const float s[4] = {s4.x, s4.y, s4.z, s4.w};
-          float ds[4] = {0.f, 0.f, 0.f, 0.f};
+          float ds0 = 0.f, ds1 = 0.f, ds2 = 0.f, ds3 = 0.f;
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
-            float z = sph[256 + f * 32 + c];
-#pragma unroll
-            for (int l = 0; l < 4; ++l) z = fmaf(s[l], sph[f * 128 + l * 32 + c], z);
+            const float* p = sph + (f * 32 + c) * 8;
+            const float4 k = ld4(p);
+            const float z = fmaf(s4.x, k.x, fmaf(s4.y, k.y, fmaf(s4.z, k.z, fmaf(s4.w, k.w, p[4]))));
             const float dz = v[c] * dsilu_f(z);
-#pragma unroll
-            for (int l = 0; l < 4; ++l) ds[l] = fmaf(dz, sph[f * 128 + l * 32 + c], ds[l]);
+            ds0 = fmaf(dz, k.x, ds0); ds1 = fmaf(dz, k.y, ds1); ds2 = fmaf(dz, k.z, ds2); ds3 = fmaf(dz, k.w, ds3);
           }
           const float4 o = ld4(rp + 8);
-          st4(rp + 8, make_float4(o.x + ds[0], o.y + ds[1], o.z + ds[2], o.w + ds[3]));
+          st4(rp + 8, make_float4(o.x + ds0, o.y + ds1, o.z + ds2, o.w + ds3));
         }
       }
       tc_fence_before();
@@ -931,13 +1006,13 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_tc_kernel(const unsigned char
       BW_MARK(6);
     }
     if (failed) break;
-    // ---- angular part and the force on the receiver (threads 0..127); cotangent of ev (warps 4..7) ----
+    // ---- angular part and the force on the receiver (threads 0..127); cotangent of ev (warps 8..15, 16 rows each) ----
     if (tid < 128) {
       const float* rp = rec + tid * kBwRec;
       if (rp[34] != 0.f) {
         const int j = __float_as_int(rp[0]), i = __float_as_int(rp[1]);
         const float4 aA = ld4(rp + 20), aB = ld4(rp + 24), uu = ld4(rp + 28);
-        const float g_r = rp[32];
+        const float g_r = rp[32] + rp[35];
         const float* gevi = gev1 + (size_t)i * kMTot;
         const float* gevj = gev1 + (size_t)j * kMTot;
         const float aAv[4] = {aA.x, aA.y, aA.z, aA.w}, aBv[4] = {aB.x, aB.y, aB.z, aB.w};
@@ -969,12 +1044,12 @@ __global__ void __launch_bounds__(256, 1) attn_bwd_tc_kernel(const unsigned char
           atomicAdd(w + 5, 0.5f * (wx * fsy + wy * fsx));
         }
       }
-    } else {
+    } else if (warp >= 8) {
       int cur_i = -1;
       float acc = 0.f;
-      const int k0 = 32 * (warp - 4);
+      const int k0 = 16 * (warp - 8);
 #pragma unroll 4
-      for (int k = k0; k < k0 + 32; ++k) {
+      for (int k = k0; k < k0 + 16; ++k) {
         const float* rp = rec + k * kBwRec;
         const int j = __float_as_int(rp[0]), i = __float_as_int(rp[1]);
         if (i != cur_i) {
@@ -1079,7 +1154,7 @@ void tc_debug_print() {
   long long h[32];
   cudaDeviceSynchronize();
   cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost);
-  if (h[24]) std::fprintf(stderr, "tc bwd phases (cycles per tile, %lld tiles): prep %lld | mma1 %lld | tmem->tile %lld | edge loop %lld | sync %lld | mma2 %lld | epilogue %lld | phase C %lld\n",
+  if (h[24]) std::fprintf(stderr, "tc bwd phases (cycles per tile, %lld tiles): prep %lld | sync %lld | mma1 %lld | sync+tmem->tile %lld | edge loop %lld | sync+mma2 %lld | epilogue %lld | phase C %lld\n",
                h[24], h[16] / h[24], h[17] / h[24], h[18] / h[24], h[19] / h[24], h[20] / h[24], h[21] / h[24], h[22] / h[24], h[23] / h[24]);
   std::fprintf(stderr, "tc fwd mma issue %lld wait %lld cycles per tile\n", h[9] / (h[8] ? h[8] : 1), h[10] / (h[8] ? h[8] : 1));
   std::fprintf(stderr, "tc fwd phases (cycles per tile, %lld tiles): prep %lld | sync %lld | mma+wait %lld | tmem0 %lld | loop0 %lld | sync %lld | tmem1 %lld | loop1 %lld\n",
@@ -1104,7 +1179,7 @@ int launch_attn_bwd_tc(cudaStream_t s, const LayerDev& L, const ValidEdges& V, i
   // the kernel adds into the receivers' rows: cotangents of q/k/v start at zero, that of ev at the skip term
   SO3LR_CUDA_CHECK(cudaMemsetAsync(g_qkv, 0, (size_t)n_recv * kProj * sizeof(float), s));
   SO3LR_CUDA_CHECK(cudaMemcpyAsync(gev_in, gev1, (size_t)n_recv * kMTot * sizeof(float), cudaMemcpyDeviceToDevice, s));
-  { attn_bwd_tc_kernel<<<sm_count(), 256, kSmemBwd, s>>>(L.tc_img, L.sph1_k, L.sph1_b, n_recv, V.row_ptr, V.i, V.j, V.d, qkv, ev_in, g_xa, gev1, g_qkv,
+  { attn_bwd_tc_kernel<<<sm_count(), kBwThreads, kSmemBwd, s>>>(L.tc_img, L.sph1_k, L.sph1_b, n_recv, V.row_ptr, V.i, V.j, V.d, qkv, ev_in, g_xa, gev1, g_qkv,
                                                        gev_in, F, virial, err, tc_debug_buffer()); count_launch(); }
   return kOk;
 }

@@ -128,13 +128,13 @@ void split_half(float x, unsigned short& hi, unsigned short& lo) {
   std::memcpy(&lo, &l, 2);
 }
 
-// Operand image of attention_tc.cu: 8 x 8 core matrices (8 rows of 16 bytes).  Radial coefficients C[m][c]: core (m/8, c/8)
-// at (m/8) * 4096 + (c/8) * 128; second spherical layer K2_f[h][n]: core (h/8, n/8) at (h/8) * 2048 + (n/8) * 128.
-// term held by column / row k of the Chebyshev block: even terms first, then the odd ones
+// term held by column / row k of the Chebyshev block: even terms first, then the odd ones (the order in which the kernels
+// generate the polynomials)
 int cheb_term(int k) { return k < kChebM / 2 ? 2 * k : 2 * (k - kChebM / 2) + 1; }
 
 // Forward-kernel image: B operands with K contiguous.  CT[n][k] = coefficient of term cheb_term(k) of feature n: core
 // (n/8, k/8) at (k/8) * 4096 + (n/8) * 128; K2T_f[n][h]: core (n/8, h/8) at (h/8) * 2048 + (n/8) * 128.
+// Layout: CT hi | CT lo (32 KB each) | K2T hi f = 0, 1 | K2T lo f = 0, 1 (8 KB each).
 std::vector<float> tc_image_forward(const float* blob, const BlobOffsets& O, int layer) {
   std::vector<unsigned char> img(kTcImageBytes, 0);
   std::vector<double> coef;
@@ -161,30 +161,27 @@ std::vector<float> tc_image_forward(const float* blob, const BlobOffsets& O, int
   return out;
 }
 
+// Operand image of the reverse attention kernel (attention_tc.cu): 8 x 8 core matrices (8 rows of 16 bytes).  Per filter f the 96
+// rows [64 Chebyshev terms in the order of cheb_term | 32 hidden units of the spherical filter] by the filter's 128 features;
+// core (row / 8, feature / 8) at (feature / 8) * 1536 + (row / 8) * 128.  Layout: hi f = 0 | hi f = 1 | lo f = 0 | lo f = 1.
 std::vector<float> tc_image(const float* blob, const BlobOffsets& O, int layer) {
   std::vector<unsigned char> img(kTcImageBytes, 0);
   std::vector<double> coef;
   chebyshev_coefficients(blob, O, layer, coef);
-  auto put = [&](size_t base_hi, size_t base_lo, size_t off, float v) {
-    unsigned short hi, lo;
-    split_half(v, hi, lo);
-    std::memcpy(&img[base_hi + off], &hi, 2);
-    std::memcpy(&img[base_lo + off], &lo, 2);
-  };
-  // row k of the image holds the term m(k): even terms first (k < 32: m = 2k), then the odd ones (m = 2 (k - 32) + 1), the
-  // order in which the kernels generate the polynomials
-  for (int k = 0; k < kChebM; ++k) {
-    const int m = cheb_term(k);
-    for (int c = 0; c < 256; ++c)
-      put(0, 32768, (size_t)(k / 8) * 4096 + (size_t)(c / 8) * 128 + (k % 8) * 16 + (c % 8) * 2, (float)coef[(size_t)m * 256 + c]);
-  }
+  const size_t per_filter = 16 * 1536;
+  static_assert(4 * 16 * 1536 == kTcImageBytes, "image size");
   const LayerOffsets& L = O.layer[layer];
   for (int f = 0; f < 2; ++f) {
     const float* K2 = blob + L.sph_l2_k[f];
-    for (int h = 0; h < 32; ++h)
-      for (int n = 0; n < kF; ++n)
-        put(65536 + (size_t)f * 8192, 65536 + 16384 + (size_t)f * 8192, (size_t)(h / 8) * 2048 + (size_t)(n / 8) * 128 + (h % 8) * 16 + (n % 8) * 2,
-            K2[h * kF + n]);
+    for (int row = 0; row < 96; ++row)
+      for (int n = 0; n < kF; ++n) {
+        const float v = row < kChebM ? (float)coef[(size_t)cheb_term(row) * 256 + f * kF + n] : K2[(row - kChebM) * kF + n];
+        unsigned short hi, lo;
+        split_half(v, hi, lo);
+        const size_t off = (size_t)(n / 8) * 1536 + (size_t)(row / 8) * 128 + (row % 8) * 16 + (n % 8) * 2;
+        std::memcpy(&img[f * per_filter + off], &hi, 2);
+        std::memcpy(&img[(2 + f) * per_filter + off], &lo, 2);
+      }
   }
   std::vector<float> out(kTcImageBytes / 4);
   std::memcpy(out.data(), img.data(), kTcImageBytes);
