@@ -444,18 +444,18 @@ int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, co
   return kOk;
 }
 
-// Attention kernels of the layers with a spherical filter.  Default: the tiled tcgen05 forward kernel with the
-// warp-per-receiver mma.sync reverse kernel (the faster one of the two reverse kernels at present).  SO3LR_B200_ATTENTION
-// selects the others for comparison runs: "tc" tiled tcgen05 kernels in both directions, "mma" warp-per-receiver mma.sync
-// kernels in both, "simt" FP32 shared-memory filter GEMMs.
+// Attention kernels of the layers with a spherical filter.  Default: the tiled tcgen05 kernels in both directions.
+// SO3LR_B200_ATTENTION selects the earlier generations for comparison runs (all are covered by tests/test_gpu_modes.py):
+// "tcf" tiled forward with the warp-per-receiver mma.sync reverse kernel, "mma" warp-per-receiver mma.sync kernels in both
+// directions, "simt" FP32 shared-memory filter GEMMs.
 enum AttentionMode { kAttnSimt = 0, kAttnMma = 1, kAttnTcFwd = 2, kAttnTc = 3 };
 int attention_mode() {
   static const int v = [] {
     const char* e = std::getenv("SO3LR_B200_ATTENTION");
     if (e && std::strcmp(e, "simt") == 0) return (int)kAttnSimt;
     if (e && std::strcmp(e, "mma") == 0) return (int)kAttnMma;
-    if (e && std::strcmp(e, "tc") == 0) return (int)kAttnTc;
-    return (int)kAttnTcFwd;
+    if (e && std::strcmp(e, "tcf") == 0) return (int)kAttnTcFwd;
+    return (int)kAttnTc;
   }();
   return v;
 }

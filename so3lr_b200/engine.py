@@ -103,27 +103,34 @@ class System:
 
     def virial(self, stream=None):
         """dE/d eps (3,3) float64 of the latest evaluation."""
-        w = torch.empty(3, 3, dtype=torch.float64, device=self.device)
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(s):      # the result is allocated on the stream the kernels run on
+            w = torch.empty(3, 3, dtype=torch.float64, device=self.device)
         check(lib.so3lr_b200_system_virial(self._h, C.c_void_p(s.cuda_stream), _ptr(w)), "virial")
         return w
 
     def compute(self, positions, stream=None):
-        """positions: float32 CUDA tensor (n,3).  Returns dict of CUDA tensors (async on the current stream)."""
-        R = positions.to(self.device, torch.float32).contiguous()
-        n, g = self.n, self.n_graphs
-        out = dict(forces=torch.empty(n, 3, device=self.device), e_atom=torch.empty(n, device=self.device),
-                   energy=torch.empty(g, dtype=torch.float64, device=self.device),
-                   partial_charges=torch.empty(n, device=self.device), hirshfeld_ratios=torch.empty(n, device=self.device),
-                   dipole_vec=torch.empty(g, 3, device=self.device))
+        """positions: float32 CUDA tensor (n,3).  Returns dict of CUDA tensors (async on `stream`, default: the current one).
+        Temporaries and outputs are created under `stream`, so the caching allocator ties their lifetime to the stream the
+        kernels are enqueued on; a caller that passes another stream orders it against the producer of `positions` itself."""
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        n, g = self.n, self.n_graphs
+        with torch.cuda.stream(s):
+            R = positions.to(self.device, torch.float32).contiguous()
+            out = dict(forces=torch.empty(n, 3, device=self.device), e_atom=torch.empty(n, device=self.device),
+                       energy=torch.empty(g, dtype=torch.float64, device=self.device),
+                       partial_charges=torch.empty(n, device=self.device), hirshfeld_ratios=torch.empty(n, device=self.device),
+                       dipole_vec=torch.empty(g, 3, device=self.device))
+            if R.data_ptr() == positions.data_ptr():
+                positions.record_stream(s)
         check(lib.so3lr_b200_system_compute(self._h, C.c_void_p(s.cuda_stream), _ptr(R), _ptr(out["forces"]), _ptr(out["e_atom"]),
                                             _ptr(out["energy"]), _ptr(out["partial_charges"]), _ptr(out["hirshfeld_ratios"]),
                                             _ptr(out["dipole_vec"])), "system_compute")
         if getattr(self, "_virial", False):
             out["virial"] = self.virial(s)
             if self._cell is not None:
-                out["stress"] = out["virial"] / abs(float(np.linalg.det(self._cell)))
+                with torch.cuda.stream(s):
+                    out["stress"] = out["virial"] / abs(float(np.linalg.det(self._cell)))
         return out
 
     def compute_host(self, positions, want_aux=True):

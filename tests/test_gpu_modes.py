@@ -1,7 +1,7 @@
 """The kernel variants that environment switches select (read once per process, hence child processes): every variant of
 the attention kernels, the dense blocks and the first layer gives the same energies and forces as the default build-up.
 
-  SO3LR_B200_ATTENTION = tc | mma | simt   (default: tiled tcgen05 forward + warp-per-receiver mma.sync reverse)
+  SO3LR_B200_ATTENTION = tcf | mma | simt  (default: tiled tcgen05 kernels in both directions)
   SO3LR_B200_DENSE     = simt              (default: FP16-split mma.sync dense blocks)
   SO3LR_B200_LAYER0    = generic           (default: per-element-pair tables)
 """
@@ -47,7 +47,7 @@ def _run(tmp_path, name, env):
 
 def test_kernel_variants_agree(tmp_path):
     ref = _run(tmp_path, "default", {})
-    variants = {"attention_tc": {"SO3LR_B200_ATTENTION": "tc"}, "attention_mma": {"SO3LR_B200_ATTENTION": "mma"},
+    variants = {"attention_tcf": {"SO3LR_B200_ATTENTION": "tcf"}, "attention_mma": {"SO3LR_B200_ATTENTION": "mma"},
                 "attention_simt": {"SO3LR_B200_ATTENTION": "simt"}, "dense_simt": {"SO3LR_B200_DENSE": "simt"},
                 "layer0_generic": {"SO3LR_B200_LAYER0": "generic"}}
     for name, env in variants.items():
