@@ -460,7 +460,7 @@ int attention_mode() {
   return v;
 }
 bool use_mma_attention() { return attention_mode() >= kAttnMma; }
-// SO3LR_B200_DENSE=simt selects the FP32 shared-memory versions of the per-atom dense blocks
+// SO3LR_B200_DENSE=simt selects the FP32 shared-memory versions of the per-atom dense blocks (see use_tc_dense below)
 // SO3LR_B200_LAYER0=generic evaluates the first layer with the generic attention kernels instead of the element-pair tables
 bool use_layer0_tables() {
   static const bool v = [] {
@@ -476,18 +476,29 @@ bool use_mma_dense() {
   }();
   return v;
 }
+// The post-attention blocks run on the tcgen05 kernels of dense_tc.cu unless SO3LR_B200_DENSE names an earlier generation
+// ("mma": mma.sync kernels, "simt": FP32 shared-memory kernels); the output heads use the mma.sync kernels in both cases.
+bool use_tc_dense() {
+  static const bool v = [] {
+    const char* e = std::getenv("SO3LR_B200_DENSE");
+    return !(e && (std::strcmp(e, "simt") == 0 || std::strcmp(e, "mma") == 0));
+  }();
+  return v;
+}
 // With the tensor-core dense blocks the q/k/v projections ride along: the forward block also emits the next layer's
 // q/k/v rows, the reverse block forms its input cotangent from the upper layer's g_xa and g_qkv.  `next` / `up` = that
 // neighbouring layer (nullptr: no fusion at this end of the network).
 void post_fwd_dispatch(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, float* z1, float* x3, float* gate,
-                       float* x4, float* ev2, const LayerDev* next, float* qkv_next) {
-  if (use_mma_dense()) launch_atom_post_fwd_mma(s, L, n, xa, ev1, z1, x3, gate, x4, ev2, next ? next->proj_f : nullptr, qkv_next);
+                       float* x4, float* ev2, const LayerDev* next, float* qkv_next, int* err) {
+  if (use_tc_dense()) launch_atom_post_fwd_tc(s, L, n, xa, ev1, z1, x3, gate, x4, ev2, next ? next->proj_u : nullptr, qkv_next, err);
+  else if (use_mma_dense()) launch_atom_post_fwd_mma(s, L, n, xa, ev1, z1, x3, gate, x4, ev2, next ? next->proj_f : nullptr, qkv_next);
   else launch_atom_post_fwd(s, L, n, xa, ev1, z1, x3, gate, x4, ev2);
 }
 void post_bwd_dispatch(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, const float* z1, const float* x3,
                        const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1, const LayerDev* up,
-                       const float* g_qkv_up) {
-  if (use_mma_dense()) launch_atom_post_bwd_mma(s, L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1, up ? up->projT_f : nullptr, g_qkv_up);
+                       const float* g_qkv_up, int* err) {
+  if (use_tc_dense()) launch_atom_post_bwd_tc(s, L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1, up ? up->projT_u : nullptr, g_qkv_up, err);
+  else if (use_mma_dense()) launch_atom_post_bwd_mma(s, L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1, up ? up->projT_f : nullptr, g_qkv_up);
   else launch_atom_post_bwd(s, L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1);
 }
 void heads_fwd_dispatch(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* x, float* ze, float* zq, float* zh,
@@ -569,7 +580,7 @@ int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const S
     S->prof.begin(kPPostFwd, st);
     const bool emit = fuse && l + 1 < kNumLayers;
     post_fwd_dispatch(st, L, nrecv[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1],
-                      emit ? &M.layer[l + 1] : nullptr, emit ? S->qkv[l + 1] : nullptr);
+                      emit ? &M.layer[l + 1] : nullptr, emit ? S->qkv[l + 1] : nullptr, S->d_flag + 1);
     S->prof.end(st);
   }
   S->prof.begin(kPHeads, st);
@@ -596,7 +607,7 @@ int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float
     const bool fused_in = use_mma_dense() && l + 1 < kNumLayers;   // cotangent formed from the layer above inside the block
     S->prof.begin(kPPostBwd, st);
     post_bwd_dispatch(st, L, npost[l], S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, gev2, S->g_xa, S->gev1,
-                      fused_in ? &M.layer[l + 1] : nullptr, S->g_qkv);
+                      fused_in ? &M.layer[l + 1] : nullptr, S->g_qkv, S->d_flag + 1);
     S->prof.end(st);
     if (c.n3 > npost[l]) {   // atoms beyond the layer's receivers have no cotangent of their own (any of them can be a neighbour)
       fill(st, S->g_xa + (size_t)npost[l] * kF, (size_t)(c.n3 - npost[l]) * kF, 0.f);
@@ -744,6 +755,7 @@ SO3LR_B200_API int so3lr_b200_model_create(const float* blob_host, size_t n_floa
   if (rc == kOk) rc = configure_attention_mma_kernels();
   if (rc == kOk) rc = configure_attention_tc_kernels();
   if (rc == kOk) rc = configure_atom_mma_kernels();
+  if (rc == kOk) rc = configure_dense_tc_kernels();
   if (rc != kOk) { so3lr_b200_model_destroy(m); return rc; }
   *out = m;
   return kOk;
@@ -885,6 +897,7 @@ SO3LR_B200_API int so3lr_b200_system_destroy(so3lr_b200_system* S) {
   cudaSetDevice(S->model->device);
   cudaDeviceSynchronize();
   tc_debug_print();
+  dense_debug_print();
   S->pool.release();
   species_tables_free(&S->sp);
   S->prof.destroy();
@@ -1405,7 +1418,7 @@ SO3LR_B200_API int so3lr_b200_dd_layer_forward(so3lr_b200_system* S, void* strea
   const bool emit = use_mma_dense() && l + 1 < kNumLayers;
   S->prof.begin(kPPostFwd, st);
   post_fwd_dispatch(st, L, n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1],
-                    emit ? &S->mctx.layer[l + 1] : nullptr, emit ? S->qkv[l + 1] : nullptr);
+                    emit ? &S->mctx.layer[l + 1] : nullptr, emit ? S->qkv[l + 1] : nullptr, S->d_flag + 1);
   S->prof.end(st);
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
@@ -1471,7 +1484,7 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_post(so3lr_b200_system* S, void*
   const bool fused_in = use_mma_dense() && l + 1 < kNumLayers;
   S->prof.begin(kPPostBwd, st);
   post_bwd_dispatch(st, S->mctx.layer[l], n0, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, S->dd_gev2, S->g_xa, S->gev1,
-                    fused_in ? &S->mctx.layer[l + 1] : nullptr, S->g_qkv);
+                    fused_in ? &S->mctx.layer[l + 1] : nullptr, S->g_qkv, S->d_flag + 1);
   S->prof.end(st);
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;

@@ -33,6 +33,16 @@ void launch_heads_fwd_mma(cudaStream_t s, const ModelDev& M, int n, const int* Z
 void launch_heads_bwd_mma(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* ze, const float* zq, const float* zh,
                           const float* hv, const float* ge, const float* gq, const float* gh, float* gx);
 
+// ---- dense_tc.cu: the per-atom blocks on tcgen05 (persistent CTAs, 128-atom tiles, accumulators in tensor memory) ----
+// err: device word that receives 2 when a bounded barrier wait inside a kernel ran out
+int configure_dense_tc_kernels();
+void dense_debug_print();   // development aid of timing builds; prints nothing otherwise
+void launch_atom_post_fwd_tc(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, float* z1, float* x3, float* gate,
+                             float* x4, float* ev2, const unsigned char* proj_u, float* qkv_next, int* err);
+void launch_atom_post_bwd_tc(cudaStream_t s, const LayerDev& L, int n, const float* xa, const float* ev1, const float* z1, const float* x3,
+                             const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1, const unsigned char* projT_u,
+                             const float* g_qkv_up, int* err);
+
 // ---- attention.cu ----
 // Short-range edges are grouped by receiver: edges row_ptr[i] .. row_ptr[i+1]-1 belong to centre i and hold the
 // neighbour index nbr_j[e] and the displacement dR[e] (3 floats).  Edges with |dR| >= 4.5, |dR| == 0 or

@@ -100,6 +100,25 @@ std::vector<float> pack_fragments(const float* W, int K, int N, bool transpose) 
   return out;
 }
 
+// B[k][n] (K x N; transpose = read W as [N][K]) -> operand image of the tcgen05 dense-block kernels: hi matrix, then lo matrix,
+// each with K contiguous in 8 x 8 core matrices: element (k, n) at (k/8) * 16 N + (n/8) * 128 + (n%8) * 16 + (k%8) * 2 bytes
+void umma_image_append(std::vector<unsigned char>& out, const float* W, int K, int N, bool transpose) {
+  const size_t half = (size_t)K * N * 2, base = out.size();
+  out.resize(base + 2 * half);
+  for (int k = 0; k < K; ++k)
+    for (int n = 0; n < N; ++n) {
+      const float v = transpose ? W[(size_t)n * K + k] : W[(size_t)k * N + n];
+      unsigned short hi, lo;
+      const __half h = __float2half_rn(v);
+      const __half l = __float2half_rn((v - __half2float(h)) * 2048.f);
+      std::memcpy(&hi, &h, 2);
+      std::memcpy(&lo, &l, 2);
+      const size_t off = (size_t)(k / 8) * 16 * N + (size_t)(n / 8) * 128 + (n % 8) * 16 + (k % 8) * 2;
+      std::memcpy(&out[base + off], &hi, 2);
+      std::memcpy(&out[base + half + off], &lo, 2);
+    }
+}
+
 // Chebyshev coefficients coef[m][c] (m < kChebM, c < 256) of both radial filters of a layer in the variable
 // t = A x + B, x = exp(-hg r), sampled at 256 Chebyshev-Gauss nodes (A, B, hg are the float32 constants the kernels use)
 void chebyshev_coefficients(const float* blob, const BlobOffsets& O, int layer, std::vector<double>& coef) {
@@ -199,6 +218,13 @@ struct Uploader {
     return (const float*)d;
   }
   const float* up(const float* p, size_t n) { return up(std::vector<float>(p, p + n)); }
+  const unsigned char* up_bytes(const std::vector<unsigned char>& v) {   // cudaMalloc alignment (256 B) satisfies bulk copies
+    void* d = nullptr;
+    if (cudaMalloc(&d, v.size()) != cudaSuccess) { status = kCudaError; return nullptr; }
+    if (cudaMemcpy(d, v.data(), v.size(), cudaMemcpyHostToDevice) != cudaSuccess) { status = kCudaError; }
+    owned->push_back(d);
+    return (const unsigned char*)d;
+  }
   const float* upT(const float* p, int rows, int cols) {  // [rows][cols] -> [cols][rows]
     std::vector<float> t((size_t)rows * cols);
     for (int r = 0; r < rows; ++r)
@@ -298,6 +324,27 @@ int build_model(const float* blob, size_t n_floats, ModelDev* M, std::vector<voi
         }
       D.proj_f = reinterpret_cast<const uint4*>(U.up(pf));
       D.projT_f = reinterpret_cast<const uint4*>(U.up(pb));
+      // tcgen05 images: forward per head B[k = j][n = 32 w + i] = W[w][h][i][j]; reverse per (w, h) B[k = i][n = j]
+      // forward: blocks of 16 KB in the order head 0 | head 1 | head 2 | k2 of all heads | head 3 (the kernel loads the first four
+      // with one copy and the last one into the place of head 0 once that has been used).  Head block: [K = 32][N = 128 = the
+      // first four projections side by side]; k2 block: per head [K = 32][N = 32], 4 KB each
+      std::vector<unsigned char> uf, ub;
+      std::vector<float> blk(32 * 128);
+      auto head_block = [&](int h) {
+        for (int w = 0; w < 4; ++w) {
+          const float* W = blob + L.W[w] + (size_t)h * 32 * 32;
+          for (int i = 0; i < 32; ++i)
+            for (int j = 0; j < 32; ++j) blk[(size_t)j * 128 + 32 * w + i] = W[i * 32 + j];
+        }
+        umma_image_append(uf, blk.data(), 32, 128, false);
+      };
+      head_block(0); head_block(1); head_block(2);
+      for (int h = 0; h < 4; ++h) umma_image_append(uf, blob + L.W[4] + (size_t)h * 32 * 32, 32, 32, true);   // B[k = j][n = i] = W[i][j]
+      head_block(3);
+      for (int w = 0; w < 5; ++w)
+        for (int h = 0; h < 4; ++h) umma_image_append(ub, blob + L.W[w] + (size_t)h * 32 * 32, 32, 32, false);
+      D.proj_u = U.up_bytes(uf);
+      D.projT_u = U.up_bytes(ub);
     }
     // radial tables
     // per interval g (between knots g and g+1) four rows of 256: value at g, slope at g (x spacing), value difference
@@ -346,6 +393,10 @@ int build_model(const float* blob, size_t n_floats, ModelDev* M, std::vector<voi
     D.res1_f = frag(blob + L.res1_k, kF, kF, false); D.res1T_f = frag(blob + L.res1_k, kF, kF, true);
     D.res2_f = frag(blob + L.res2_k, kF, kF, false); D.res2T_f = frag(blob + L.res2_k, kF, kF, true);
     D.exxx_f = frag(xx.data(), kF, kF, false); D.exxxT_f = frag(xx.data(), kF, kF, true);
+    auto uimg = [&](const float* W, int K, int N, bool tr) { std::vector<unsigned char> b; umma_image_append(b, W, K, N, tr); return U.up_bytes(b); };
+    D.res1_u = uimg(blob + L.res1_k, kF, kF, false); D.res1T_u = uimg(blob + L.res1_k, kF, kF, true);
+    D.res2_u = uimg(blob + L.res2_k, kF, kF, false); D.res2T_u = uimg(blob + L.res2_k, kF, kF, true);
+    D.exxx_u = uimg(xx.data(), kF, kF, false); D.exxxT_u = uimg(xx.data(), kF, kF, true);
     D.ex_xg = U.up(xg); D.ex_ix = U.up(ix); D.ex_ig = U.up(ig);
     D.ex_bx = U.up(blob + L.exch_b, 128); D.ex_bg = U.up(blob + L.exch_b + 128, 4);
   }
@@ -369,6 +420,11 @@ int build_model(const float* blob, size_t n_floats, ModelDev* M, std::vector<voi
     M->q_reg_f = frag(blob + O.q_reg_k, kF, kF, false); M->q_regT_f = frag(blob + O.q_reg_k, kF, kF, true);
     M->h_reg_f = frag(blob + O.h_reg_k, kF, 64, false); M->h_regT_f = frag(blob + O.h_reg_k, 64, kF, true);
     M->h_fin_f = frag(blob + O.h_fin_k, 64, 64, false); M->h_finT_f = frag(blob + O.h_fin_k, 64, 64, true);
+    auto uimg = [&](const float* W, int K, int N, bool tr) { std::vector<unsigned char> b; umma_image_append(b, W, K, N, tr); return U.up_bytes(b); };
+    M->e_reg_u = uimg(blob + O.e_reg_k, kF, kF, false); M->e_regT_u = uimg(blob + O.e_reg_k, kF, kF, true);
+    M->q_reg_u = uimg(blob + O.q_reg_k, kF, kF, false); M->q_regT_u = uimg(blob + O.q_reg_k, kF, kF, true);
+    M->h_reg_u = uimg(blob + O.h_reg_k, kF, 64, false); M->h_regT_u = uimg(blob + O.h_reg_k, 64, kF, true);
+    M->h_fin_u = uimg(blob + O.h_fin_k, 64, 64, false); M->h_finT_u = uimg(blob + O.h_fin_k, 64, 64, true);
   }
   // ZBL constants: softplus of the raw parameters, weights normalised to one
   double a[4], c[4], cs = 0.0;

@@ -28,6 +28,12 @@ struct LayerDev {
   // q/k/v projections of this layer as 20 blocks (projection w = 0..4, head h = 0..3) of 32 x 32, fragment order
   // [w*4+h][2][4][32]: proj_f for out_i = sum_j W[i][j] x_j, projT_f for the reverse contraction over i
   const uint4 *proj_f, *projT_f;
+  // B operands of the tcgen05 dense-block kernels (dense_tc.cu): FP16 hi matrix then 2048-scaled lo matrix, K contiguous,
+  // element (k, n) at (k/8) * 16 N + (n/8) * 128 + (n%8) * 16 + (k%8) * 2 bytes.  res1/res2/exxx: [128 x 128] forward and
+  // transposed; proj_u: five blocks of 16 KB: heads 0, 1, 2 as [K = 32 inputs of the head][N = 128 = projections 0..3, output i], the fifth
+  // projection of all heads as four [32 x 32] blocks, head 3;
+  // projT_u: per projection w and head h the [K = 32 outputs i][N = 32 inputs j] block (20 x 4,096 bytes)
+  const unsigned char *res1_u, *res2_u, *exxx_u, *res1T_u, *res2T_u, *exxxT_u, *proj_u, *projT_u;
   const float* ex_xg;           // [128][4]   features -> gates
   const float* ex_ix;           // [4][128]   invariants -> features
   const float* ex_ig;           // [4][4]     invariants -> gates
@@ -48,6 +54,7 @@ struct ModelDev {
   // Hirshfeld head
   const float *h_embed0, *h_embed1, *h_reg_k, *h_reg_kT, *h_reg_b, *h_fin_k, *h_fin_kT, *h_fin_b;
   const uint4 *e_reg_f, *e_regT_f, *q_reg_f, *q_regT_f, *h_reg_f, *h_regT_f, *h_fin_f, *h_finT_f;   // fragment-order copies
+  const unsigned char *e_reg_u, *e_regT_u, *q_reg_u, *q_regT_u, *h_reg_u, *h_regT_u, *h_fin_u, *h_finT_u;   // tcgen05 operand images
   // charge / spin embeddings (only evaluated when a graph carries charge or unpaired electrons)
   const float *cs_embed_q[2], *cs_embed_k[2], *cs_embed_v[2], *cs_res0[2], *cs_res1[2];
   ZblParams zbl;

@@ -2,7 +2,7 @@
 the attention kernels, the dense blocks and the first layer gives the same energies and forces as the default build-up.
 
   SO3LR_B200_ATTENTION = tcf | mma | simt  (default: tiled tcgen05 kernels in both directions)
-  SO3LR_B200_DENSE     = simt              (default: FP16-split mma.sync dense blocks)
+  SO3LR_B200_DENSE     = mma | simt        (default: tcgen05 post-attention blocks, mma.sync heads)
   SO3LR_B200_LAYER0    = generic           (default: per-element-pair tables)
 """
 import os
@@ -48,7 +48,8 @@ def _run(tmp_path, name, env):
 def test_kernel_variants_agree(tmp_path):
     ref = _run(tmp_path, "default", {})
     variants = {"attention_tcf": {"SO3LR_B200_ATTENTION": "tcf"}, "attention_mma": {"SO3LR_B200_ATTENTION": "mma"},
-                "attention_simt": {"SO3LR_B200_ATTENTION": "simt"}, "dense_simt": {"SO3LR_B200_DENSE": "simt"},
+                "attention_simt": {"SO3LR_B200_ATTENTION": "simt"}, "dense_mma": {"SO3LR_B200_DENSE": "mma"},
+                "dense_simt": {"SO3LR_B200_DENSE": "simt"},
                 "layer0_generic": {"SO3LR_B200_LAYER0": "generic"}}
     for name, env in variants.items():
         got = _run(tmp_path, name, env)
