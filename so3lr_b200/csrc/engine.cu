@@ -299,6 +299,7 @@ struct so3lr_b200_system {
   float *ze = nullptr, *zq = nullptr, *zh = nullptr, *e_nn = nullptr, *q_raw = nullptr, *hv = nullptr, *q = nullptr, *h = nullptr;
   float *e_atom = nullptr, *e_zbl = nullptr, *e_coul = nullptr, *e_disp = nullptr;
   float *gq = nullptr, *gh = nullptr, *gq_raw = nullptr, *ones = nullptr;
+  float* pair_pack = nullptr;   // (x, y, z, q) | (Fx, Fy, Fz, dE/dq) | (h, alpha_free, c6_free, -) per atom for the packed long-range kernel
   float *g4 = nullptr, *g_xa = nullptr, *gev_a = nullptr, *gev_b = nullptr, *gev1 = nullptr, *g_qkv = nullptr;
   float* dR = nullptr;
   long long edge_cap = 0;
@@ -643,8 +644,8 @@ int evaluate_fused(so3lr_b200_system* S, cudaStream_t st, const float* R, float*
   fill(st, S->e_coul, n, 0.f); fill(st, S->e_disp, n, 0.f); fill(st, S->gq, n, 0.f); fill(st, S->gh, n, 0.f);
   launch_charge_conserve(st, S->n_graphs, S->d_graph_start, S->q_raw, S->d_total_charge, S->hv, S->q, S->h, S->n, S->red_scratch);
   S->prof.begin(kPPairLr, st);
-  launch_pair_lr(st, S->lr, S->cell, n, S->lrl.row_ptr, S->lrl.nbr_j, S->d_Z, R, S->q, S->h, 0, nullptr, nullptr, nullptr, F, S->gq, S->gh,
-                 S->e_coul, S->e_disp, nullptr, S->vir());
+  launch_pair_lr_packed(st, S->lr, S->cell, n, S->lrl.row_ptr, S->lrl.nbr_j, S->d_Z, R, S->q, S->h, S->pair_pack, F, S->gq, S->gh, S->e_coul,
+                        S->e_disp, S->vir());
   S->prof.end(st);
   { combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
   launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw, S->n, S->red_scratch);
@@ -829,6 +830,7 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
   S->e_nn = A.get<float>(n); S->q_raw = A.get<float>(n); S->hv = A.get<float>(n); S->q = A.get<float>(n); S->h = A.get<float>(n);
   S->e_atom = A.get<float>(n); S->e_zbl = A.get<float>(n); S->e_coul = A.get<float>(n); S->e_disp = A.get<float>(n);
   S->gq = A.get<float>(n); S->gh = A.get<float>(n); S->gq_raw = A.get<float>(n); S->ones = A.get<float>(n);
+  S->pair_pack = A.get<float>((size_t)n * 12);
   S->g4 = A.get<float>((size_t)n * kF); S->g_xa = A.get<float>((size_t)n * kF);
   S->gev_a = A.get<float>((size_t)n * kMTot); S->gev_b = A.get<float>((size_t)n * kMTot); S->gev1 = A.get<float>((size_t)n * kMTot);
   S->g_qkv = A.get<float>((size_t)n * kProj);

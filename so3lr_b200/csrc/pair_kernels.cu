@@ -143,6 +143,150 @@ __global__ void __launch_bounds__(256) pair_lr_kernel(LrParams P, Cell cell, int
   if (MODE == 0 && virial) va.flush_warp(virial, (size_t)i, lane);
 }
 
+// Device forms of the pair terms for the packed kernel: the same functions as coulomb_chi / dispersion_pair_fast / switching
+// of pair_terms.cuh with approximate reciprocals and exponentials (rcp.approx, ex2.approx, lg2.approx: 1-2 ulp each) in place
+// of IEEE divisions and libm calls, and the switch written with one exponential:
+//   s(1-c) / (s(1-c) + s(c)),  s(a) = exp(-1/a)   ==   1 / (1 + E),  E = exp(1/(1-c) - 1/c)
+__device__ __forceinline__ float rcp_fast(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void switching_dev(float x, float on, float off, float& f, float& df) {
+  const float iw = rcp_fast(off - on);
+  const float c = (x - on) * iw;
+  if (c <= 0.f) { f = 1.f; df = 0.f; return; }
+  if (c >= 1.f) { f = 0.f; df = 0.f; return; }
+  const float ia = rcp_fast(1.f - c), ib = rcp_fast(c);
+  const float t = fminf(fmaxf(ia - ib, -80.f), 80.f);
+  const float E = __expf(t);
+  f = rcp_fast(1.f + E);
+  df = -(E * f) * (f * (ia * ia + ib * ib)) * iw;   // in this order no intermediate leaves the float range
+}
+__device__ __forceinline__ void coulomb_chi_dev(const LrParams& p, float r, float rinv, float& chi, float& dchi) {
+  const float inv_sig = 1.f / kSigmaCoulomb;
+  const float x = r * inv_sig;
+  const float pot = erff(x) * rinv;
+  const float dpot = (1.1283791670955126f * inv_sig * __expf(-x * x) - pot) * rinv;
+  if (!p.has_cutoff) { chi = pot; dchi = dpot; return; }
+  float f, df;
+  switching_dev(r, p.cuton, p.rc, f, df);
+  chi = (pot - p.v_rc) - (1.f - f) * (r - p.rc) * p.dv_rc;
+  dchi = dpot - (1.f - f) * p.dv_rc + df * (r - p.rc) * p.dv_rc;
+}
+// ai = alpha_free h, ci = c6_free h^2 of both atoms come precomputed per atom
+__device__ __forceinline__ void dispersion_pair_dev(const LrParams& P, float r, float alf_i, float c6f_i, float hi, float alf_j, float c6f_j,
+                                                    float hj, float& e, float& de_dr, float& de_dhi, float& de_dhj) {
+  const float ai = alf_i * hi, aj = alf_j * hj, ci = c6f_i * hi * hi, cj = c6f_j * hj * hj;
+  const float iden = rcp_fast(ai * ai * cj + aj * aj * ci);
+  const float c6 = 2.f * ci * cj * ai * aj * iden;
+  const float dlc6_dhi = (rcp_fast(ai) - 2.f * ai * cj * iden) * alf_i + (rcp_fast(ci) - aj * aj * iden) * 2.f * c6f_i * hi;
+  const float dlc6_dhj = (rcp_fast(aj) - 2.f * aj * ci * iden) * alf_j + (rcp_fast(cj) - ai * ai * iden) * 2.f * c6f_j * hj;
+  const float aij = 0.5f * (ai + aj);
+  const float a17 = exp2f(__log2f(aij) * (1.f / 7.f));
+  const float fs = 2.5527961000248887f;
+  const float rv = fs * a17;
+  const float sg = ((-0.00078893f * rv + 0.04125273f) * rv + 0.24428889f) * rv + (-0.00433008f);
+  const float dsg = ((3.f * -0.00078893f) * rv + 2.f * 0.04125273f) * rv + 0.24428889f;
+  const float ig = 2.f * sg * sg;
+  const float kp = kDispersionScale * 2.f * 2.54f;
+  const float p = kp * a17;
+  const float R = r * (1.f / kBohr);
+  const float R2 = R * R, p2 = p * p;
+  const float R4 = R2 * R2, p4 = p2 * p2;
+  const float R6 = R4 * R2, p6 = p4 * p2, R8 = R4 * R4, p8 = p4 * p4, R10 = R8 * R2, p10 = p8 * p2;
+  const float i6 = rcp_fast(R6 + p6), i8 = rcp_fast(R8 + p8), i10 = rcp_fast(R10 + p10);
+  const float t8 = 5.f * ig, t10 = 30.625f * ig * ig;
+  const float T = i6 + t8 * i8 + t10 * i10;
+  const float dT_dR = -(6.f * R4 * R * i6 * i6 + t8 * 8.f * R6 * R * i8 * i8 + t10 * 10.f * R8 * R * i10 * i10);
+  const float dT_dp = -(6.f * p4 * p * i6 * i6 + t8 * 8.f * p6 * p * i8 * i8 + t10 * 10.f * p8 * p * i10 * i10);
+  const float dT_dig = 5.f * i8 + 61.25f * ig * i10;
+  const float dT_da17 = dT_dp * kp + dT_dig * 4.f * sg * dsg * fs;
+  const float da17_dh = a17 * rcp_fast(7.f * aij) * 0.5f;
+  float f = 1.f, df = 0.f;
+  if (P.has_cutoff && P.has_damping) switching_dev(r, P.disp_on, P.rc, f, df);
+  const float pre = -kHartree * c6;
+  e = pre * T * f;
+  de_dr = pre * (dT_dR * (1.f / kBohr) * f + T * df);
+  de_dhi = pre * f * (T * dlc6_dhi + dT_da17 * da17_dh * alf_i);
+  de_dhj = pre * f * (T * dlc6_dhj + dT_da17 * da17_dh * alf_j);
+}
+
+// The single-device long-range kernel with packed operands: per atom (x, y, z, q) and (h, alpha_free, c6_free, -) so that a pair costs two
+// 16-byte gathers, and a packed accumulator (Fx, Fy, Fz, dE/dq) so that the sender's share of a pair is one
+// vector reduction (red.global.add.v4.f32) and one scalar one (dE/dh) instead of five scalar atomics.
+__global__ void __launch_bounds__(256) pair_pack_kernel(int n, const float* __restrict__ R, const float* __restrict__ q,
+                                                        const float* __restrict__ h, const int* __restrict__ Z,
+                                                        float4* __restrict__ pq, float4* __restrict__ hz, float4* __restrict__ acc) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  pq[i] = make_float4(R[3 * (size_t)i], R[3 * (size_t)i + 1], R[3 * (size_t)i + 2], q[i]);
+  hz[i] = make_float4(h[i], alpha_free(Z[i]), c6_free(Z[i]), 0.f);
+  acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+__global__ void __launch_bounds__(256) pair_unpack_kernel(int n, const float4* __restrict__ acc, float* __restrict__ F, float* __restrict__ gq) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float4 a = acc[i];
+  F[3 * (size_t)i] += a.x; F[3 * (size_t)i + 1] += a.y; F[3 * (size_t)i + 2] += a.z;
+  gq[i] += a.w;
+}
+__device__ __forceinline__ void red_add_f4(float4* p, float x, float y, float z, float w) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+__global__ void __launch_bounds__(256) pair_lr_packed_kernel(LrParams P, Cell cell, int n, const int* __restrict__ row_ptr,
+                                                             const int* __restrict__ nbr_j, const float4* __restrict__ pq,
+                                                             const float4* __restrict__ hz, float4* __restrict__ acc,
+                                                             float* __restrict__ gh, float* __restrict__ e_coul,
+                                                             float* __restrict__ e_disp, float* __restrict__ virial) {
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (i >= n) return;
+  VirialAcc va;
+  const int e0 = row_ptr[i], e1 = row_ptr[i + 1];
+  if (e0 == e1) return;
+  const float4 pi = pq[i];
+  const float4 hzi = hz[i];
+  const float qi = pi.w, hi = hzi.x;
+  const float pf = P.pair_factor, kq = pf * kKe, rc2 = P.rc * P.rc;
+  float ec = 0.f, ed = 0.f, fx = 0.f, fy = 0.f, fz = 0.f, gqi = 0.f, ghi = 0.f;
+  for (int e = e0 + lane; e < e1; e += 32) {
+    const int j = nbr_j[e];
+    if (j < 0 || j >= n) continue;
+    const float4 pj = __ldg(pq + j);
+    float dx = pj.x - pi.x, dy = pj.y - pi.y, dz = pj.z - pi.z;
+    min_image(cell, dx, dy, dz);
+    const float r2 = dx * dx + dy * dy + dz * dz;
+    if (!(r2 > 0.f) || (P.has_cutoff && r2 >= rc2)) continue;
+    const float4 hzj = __ldg(hz + j);
+    const float rinv = rsqrtf(r2), r = r2 * rinv;
+    float chi, dchi;
+    coulomb_chi_dev(P, r, rinv, chi, dchi);
+    const float qj = pj.w;
+    float e_d, dd_dr, dd_dhi, dd_dhj;
+    dispersion_pair_dev(P, r, hzi.y, hzi.z, hi, hzj.y, hzj.z, hzj.x, e_d, dd_dr, dd_dhi, dd_dhj);
+    ec = fmaf(kq * qi * qj, chi, ec);
+    ed = fmaf(pf, e_d, ed);
+    gqi = fmaf(kq * qj, chi, gqi);
+    ghi = fmaf(pf, dd_dhi, ghi);
+    const float s = (kq * qi * qj * dchi + pf * dd_dr) * rinv;
+    const float gx = s * dx, gy = s * dy, gz = s * dz;   // dE/d(dR), dR = R_j - R_i
+    if (virial) va.add(1.f, dx, dy, dz, gx, gy, gz);
+    fx += gx; fy += gy; fz += gz;
+    red_add_f4(acc + j, -gx, -gy, -gz, kq * qi * chi);
+    atomicAdd(gh + j, pf * dd_dhj);
+  }
+  ec = warp_sum(ec); ed = warp_sum(ed); gqi = warp_sum(gqi); ghi = warp_sum(ghi);
+  fx = warp_sum(fx); fy = warp_sum(fy); fz = warp_sum(fz);
+  if (lane == 0) {
+    e_coul[i] += ec;     // only this warp writes the energies of row i
+    e_disp[i] += ed;
+    red_add_f4(acc + i, fx, fy, fz, gqi);
+    atomicAdd(gh + i, ghi);
+  }
+  if (virial) va.flush_warp(virial, (size_t)i, lane);
+}
+
 // owned rows of a full list: i-side derivatives only, no atomics
 __global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cell, int n_owned, int n, const int* __restrict__ row_ptr,
                                                             const int* __restrict__ nbr_j, const int* __restrict__ Z,
@@ -155,7 +299,7 @@ __global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cel
   if (i >= n_owned) return;
   const int e0 = row_ptr[i], e1 = row_ptr[i + 1];
   const float qi = q[i], hi = h[i];
-  const int Zi = Z[i];
+  const float alf_i = alpha_free(Z[i]), c6f_i = c6_free(Z[i]);
   const float xi = R[3 * (size_t)i], yi = R[3 * (size_t)i + 1], zi = R[3 * (size_t)i + 2];
   float ec = 0.f, ed = 0.f, fx = 0.f, fy = 0.f, fz = 0.f, gqi = 0.f, ghi = 0.f;
   VirialAcc va;
@@ -166,17 +310,18 @@ __global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cel
     min_image(cell, dx, dy, dz);
     const float r2 = dx * dx + dy * dy + dz * dz;
     if (!(r2 > 0.f) || (P.has_cutoff && r2 >= P.rc * P.rc)) continue;
-    const float r = sqrtf(r2);
+    const float rinv = rsqrtf(r2), r = r2 * rinv;
     float chi, dchi;
-    coulomb_chi(P, r, chi, dchi);
+    coulomb_chi_dev(P, r, rinv, chi, dchi);
     const float qj = q[j], hj = h[j];
+    const int Zj = Z[j];
     float e_d, dd_dr, dd_dhi, dd_dhj;
-    dispersion_pair_fast(P, r, Zi, Z[j], hi, hj, e_d, dd_dr, dd_dhi, dd_dhj);
+    dispersion_pair_dev(P, r, alf_i, c6f_i, hi, alpha_free(Zj), c6_free(Zj), hj, e_d, dd_dr, dd_dhi, dd_dhj);
     ec = fmaf(0.5f * kKe * qi * qj, chi, ec);
     ed += 0.5f * e_d;
     gqi = fmaf(kKe * qj, chi, gqi);
     ghi += dd_dhi;
-    const float s = (kKe * qi * qj * dchi + dd_dr) / r;   // dE_ij/d(dR), dR = R_j - R_i; F_i = +that
+    const float s = (kKe * qi * qj * dchi + dd_dr) * rinv;   // dE_ij/d(dR), dR = R_j - R_i; F_i = +that
     fx = fmaf(s, dx, fx); fy = fmaf(s, dy, fy); fz = fmaf(s, dz, fz);
     if (virial) va.add(0.5f * s, dx, dy, dz, dx, dy, dz);
   }
@@ -369,6 +514,19 @@ void launch_pair_lr(cudaStream_t s, const LrParams& P, const Cell& cell, int n, 
     { pair_lr_kernel<0><<<blocks, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, Z, R, q, h, dR_lr, g_dR_lr, e_atom, F, gq, gh, e_coul, e_disp, ge, virial); count_launch(); }
   else
     { pair_lr_kernel<1><<<blocks, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, Z, R, q, h, dR_lr, g_dR_lr, e_atom, F, gq, gh, e_coul, e_disp, ge, virial); count_launch(); }
+}
+
+void launch_pair_lr_packed(cudaStream_t s, const LrParams& P, const Cell& cell, int n, const int* row_ptr, const int* nbr_j, const int* Z,
+                           const float* R, const float* q, const float* h, float* pack /* 12 n floats */, float* F, float* gq, float* gh,
+                           float* e_coul, float* e_disp, float* virial) {
+  if (n <= 0) return;
+  float4* pq = reinterpret_cast<float4*>(pack);
+  float4* acc = pq + n;
+  float4* hz = acc + n;
+  pair_pack_kernel<<<(n + 255) / 256, 256, 0, s>>>(n, R, q, h, Z, pq, hz, acc);
+  pair_lr_packed_kernel<<<(n + 7) / 8, 256, 0, s>>>(P, cell, n, row_ptr, nbr_j, pq, hz, acc, gh, e_coul, e_disp, virial);
+  pair_unpack_kernel<<<(n + 255) / 256, 256, 0, s>>>(n, acc, F, gq);
+  count_launch(3);
 }
 
 void launch_pair_lr_owned(cudaStream_t s, const LrParams& P, const Cell& cell, int n_owned, int n, const int* row_ptr,
