@@ -150,28 +150,29 @@ class ClockSampler:
 
 # ---------------------------------------------------------------------------------------------------------------
 # algorithmic (unique-data) bytes per launch of each kernel group: every array the kernel must read or write is
-# counted once.  N atoms, E directed short-range list entries (skin included), P long-range list entries.
+# counted once.  N atoms, E short-range list entries inside the cutoff (the compacted list the tiled attention kernels walk:
+# receiver, sender and (dx, dy, dz, r) per entry = 24 bytes), P long-range list entries.
 # ---------------------------------------------------------------------------------------------------------------
 def algorithmic_bytes(group, N, E, P):
     f = 4
     if group == "attn_fwd":      # q1,q2 (256) + ev_i (24) + sender rows k1,v,k2 (384) + ev_j (24) + x_in (128); out xa, ev1 (152)
-        return N * f * (256 + 24 + 384 + 24 + 128 + 152) + E * (4 + 12) + (N + 1) * 4
-    if group == "attn_bwd":      # q1,q2, g_xa, gev1, ev (i and j once), sender rows; out g_qkv (640), gev_in (24); per edge idx, dR, g_dR rmw
-        return N * f * (256 + 128 + 24 + 24 + 384 + 640 + 24) + E * (4 + 12 + 24) + (N + 1) * 4
+        return N * f * (256 + 24 + 384 + 24 + 128 + 152) + E * 24 + (N + 1) * 4
+    if group == "attn_bwd":      # q1,q2, g_xa, gev1, ev (i and j once), sender rows; out g_qkv (640), gev_in (24), forces rmw (6)
+        return N * f * (256 + 128 + 24 + 24 + 384 + 640 + 24 + 6) + E * 24 + (N + 1) * 4
     if group == "pair_lr":       # per pair: index; per atom: R, q, h, Z in; F, gq, gh, e_coul, e_disp out
         return P * 4 + N * (12 + 4 + 4 + 4 + 12 + 4 + 4 + 4 + 4) + (N + 1) * 4
-    if group == "atom_post_fwd":
-        return N * f * (128 + 24 + 128 + 128 + 4 + 128 + 24)
-    if group == "atom_post_bwd":
-        return N * f * (128 + 24 + 128 + 128 + 4 + 128 + 24 + 128 + 24)
+    if group == "atom_post_fwd":  # xa, ev1 in; z1, x3, gate, x4, ev2 out (+ the next layer's q/k/v rows, 640, where one follows: 2 of 3 launches)
+        return N * f * (128 + 24 + 128 + 128 + 4 + 128 + 24 + 427)
+    if group == "atom_post_bwd":  # xa, ev1, z1, x3, gate, g4, gev2 in; g_xa, gev1 out (+ the upper layer's g_qkv rows, 640: 2 of 3 launches)
+        return N * f * (128 + 24 + 128 + 128 + 4 + 128 + 24 + 128 + 24 + 427)
     return None
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of each group's kernel from one ncu capture on the 98,304-atom water
-# box (attn_bwd_mma_kernel, attn_fwd_tc_kernel, pair_lr_kernel).  A full-size capture is not taken (ncu replays each launch
-# about 40 times); lists and per-atom arrays grow with the atom count at fixed density, so the figure is scaled by N / 98304
-# and the line says so in `traffic_source`.
-NCU_TRAFFIC_98K = {"attn_bwd": 865.3e6, "attn_fwd": 812.9e6, "pair_lr": 192.0e6}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of each group's kernel from ncu captures on the 98,304-atom water
+# box (attn_bwd_tc_kernel, attn_fwd_tc_kernel; atom_post_*_tc_kernel: the launch with the fused projections).  A full-size
+# capture is not taken (ncu replays each launch about 40 times); lists and per-atom arrays grow with the atom count at fixed
+# density, so the figure is scaled by N / 98304 and the line says so in `traffic_source`.
+NCU_TRAFFIC_98K = {"attn_bwd": 2248.9e6, "attn_fwd": 837.3e6, "atom_post_fwd": 430.1e6, "atom_post_bwd": 557.2e6}
 
 
 def ncu_traffic(group, n_atoms):
@@ -181,23 +182,29 @@ def ncu_traffic(group, n_atoms):
 
 TRAFFIC_SOURCE = "ncu capture of the same kernel on water_98k (98,304 atoms), scaled by the atom count"
 
+# FP16 MMA work of the tiled attention kernels per tile of 128 list entries (M = 128, K = 16 per instruction, 2 FLOPs per MAC):
+# forward 12 instructions with N = 256 and 12 with N = 128; reverse 36 with N = 128 and 48 with N = 96
+ATTN_TILE_FLOPS = {"attn_fwd": 2.0 * 128 * 16 * (12 * 256 + 12 * 128), "attn_bwd": 2.0 * 128 * 16 * (36 * 128 + 48 * 96)}
 
-def tensor_flops(group, N):
-    """FP16 tensor-core FLOPs one launch of a dense-block group issues: every FP32-accurate product is three FP16 MMAs (hi*hi, hi*lo, lo*hi)."""
-    mac = {"atom_post_fwd": 3 * 128 * 128 + 5 * 4 * 32 * 32, "atom_post_bwd": 2 * (3 * 128 * 128 + 5 * 4 * 32 * 32),
+
+def tensor_flops(group, N, E=0):
+    """FP16 tensor-core FLOPs one launch of a group issues: every FP32-accurate product is three FP16 MMAs (hi*hi, hi*lo, lo*hi)."""
+    if group in ATTN_TILE_FLOPS:
+        return ATTN_TILE_FLOPS[group] * ((E + 127) // 128) if E else None
+    mac = {"atom_post_fwd": 3 * 128 * 128 + 5 * 4 * 32 * 32, "atom_post_bwd": 3 * 128 * 128 + 5 * 4 * 32 * 32,
            "heads": 2 * 128 * 128 + 128 * 64 + 64 * 64}.get(group)
     return None if mac is None else 2.0 * 3.0 * mac * N
 
 
-def tensor_roofline(groups, N):
-    """Second roofline entry: the dense blocks against the measured tensor-core peak."""
-    cands = [g for g in groups if tensor_flops(g, N)]
+def tensor_roofline(groups, N, E=0):
+    """Second roofline entry: the kernel with the largest share of the step against the measured tensor-core peak."""
+    cands = [g for g in groups if tensor_flops(g, N, E)]
     if not cands:
         return None
     g = max(cands, key=lambda k: groups[k][0])
     t = groups[g][0] / groups[g][1]
     peak, kind = _tensor_peak()
-    ach = tensor_flops(g, N) / (t * 1e-3) / 1e12
+    ach = tensor_flops(g, N, E) / (t * 1e-3) / 1e12
     return {"kernel": g, "bound": "tensor", "achieved": round(ach, 2), "peak": peak, "peak_kind": f"of {kind} (sustained bf16)", "unit": "TFLOP/s",
             "frac": round(ach / peak, 4), "ms_per_launch": round(t, 4),
             "note": "issued FP16 MMA FLOPs (3 per FP32-accurate product) over the kernel's launch time"}
@@ -277,10 +284,11 @@ def run_b200(args, rank, world, local_rank):
     sysm.profile(False)
     st2 = sysm.stats()
     E_list, P_list = st2["edges"], st2["pairs"]
+    E_valid = sysm.valid_edges()
     groups = {k: v for k, v in prof.items() if v[1] > 0}
-    top = max((g for g in groups if algorithmic_bytes(g, N, E_list, P_list)), key=lambda g: groups[g][0])
+    top = max((g for g in groups if algorithmic_bytes(g, N, E_valid, P_list)), key=lambda g: groups[g][0])
     t_launch = groups[top][0] / groups[top][1]
-    ab = algorithmic_bytes(top, N, E_list, P_list)
+    ab = algorithmic_bytes(top, N, E_valid, P_list)
     peak, peak_kind = _peaks()
     achieved = ab / (t_launch * 1e-3) / 1e9
     roofline = {"kernel": top, "bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "peak_kind": f"of {peak_kind}",
@@ -290,7 +298,7 @@ def run_b200(args, rank, world, local_rank):
                 "algorithmic_bytes_per_launch": ab, "ms_per_launch": round(t_launch, 4),
                 "launches_per_step": round(groups[top][1] / args.steps, 2),
                 "groups_ms_per_step": {g: round(v[0] / args.steps, 4) for g, v in sorted(groups.items(), key=lambda kv: -kv[1][0])},
-                "tensor": tensor_roofline(groups, N)}
+                "tensor": tensor_roofline(groups, N, E_valid)}
 
     # end to end through the host-buffer call: positions from host memory, forces + energy back, every step
     Rh = Rd.cpu().numpy().copy()
@@ -328,7 +336,7 @@ def run_b200(args, rank, world, local_rank):
                                    + {"nvt": "NVT (Nose-Hoover chain 3) at 300 K, dt 0.5 fs",
                                       "npt": "NPT (MTK barostat, Nose-Hoover chains 3) at 300 K and 1 bar, dt 0.5 fs",
                                       "nve": "NVE dt 0.5 fs from 300 K"}[ensemble],
-                       "atoms": N, "sr_list_edges": E_list, "lr_list_pairs": P_list,
+                       "atoms": N, "sr_list_edges": E_list, "sr_edges_inside_cutoff": E_valid, "lr_list_pairs": P_list,
                        "list_rebuilds_in_timed_steps": st1["rebuilds"] - st0["rebuilds"],
                        "l2_policy": ("inputs larger than L2: a step streams about 18 kB per atom (q/k/v rows 2.5 kB per layer, "
                                      "activations, cotangents, both neighbor lists)" if N * 18e3 > 126e6

@@ -109,6 +109,9 @@ SO3LR_B200_API int so3lr_b200_system_aux(so3lr_b200_system* sys, const float** z
 /* Counters: number of list rebuilds, current short-range edges and long-range pairs, kernels launched so far. */
 SO3LR_B200_API int so3lr_b200_system_stats(so3lr_b200_system* sys, int64_t* n_rebuilds, int64_t* n_edges, int64_t* n_pairs,
                             int64_t* n_launches);
+/* Short-range list entries inside the 4.5 A cutoff at the latest evaluation (the compacted list the tiled attention kernels
+ * walk; the list of so3lr_b200_system_stats also holds the skin shell).  Waits for the device. */
+SO3LR_B200_API int so3lr_b200_system_valid_edges(so3lr_b200_system* sys, int64_t* n_valid);
 
 /* Copy the current neighbor lists out in jax-md layout: idx (2, capacity) int32 on the device, padded with n_atoms
  * (Sparse for the short-range list, OrderedSparse for the long-range one unless lr_both_directions).

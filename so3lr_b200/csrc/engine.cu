@@ -1073,6 +1073,18 @@ SO3LR_B200_API int so3lr_b200_system_stats(so3lr_b200_system* S, int64_t* n_rebu
   return kOk;
 }
 
+SO3LR_B200_API int so3lr_b200_system_valid_edges(so3lr_b200_system* S, int64_t* n_valid) {
+  if (!S || !n_valid) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  *n_valid = 0;
+  if (!S->ve.row_ptr || S->ve.n_rows <= 0) return kOk;
+  int v = 0;
+  SO3LR_CUDA_CHECK(cudaDeviceSynchronize());
+  SO3LR_CUDA_CHECK(cudaMemcpy(&v, S->ve.row_ptr + S->ve.n_rows, sizeof(int), cudaMemcpyDeviceToHost));
+  *n_valid = v;
+  return kOk;
+}
+
 SO3LR_B200_API int so3lr_b200_system_export_list(so3lr_b200_system* S, void* stream, const float* R, int which, int32_t* idx, int64_t capacity,
                                   int64_t* count_host, int* overflow_host) {
   if (!S || !R || !idx || capacity <= 0) return kInvalidArgument;

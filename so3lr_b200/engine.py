@@ -158,6 +158,12 @@ class System:
         check(lib.so3lr_b200_system_stats(self._h, *[C.byref(x) for x in v]), "stats")
         return dict(rebuilds=v[0].value, edges=v[1].value, pairs=v[2].value, launches=v[3].value)
 
+    def valid_edges(self):
+        """Short-range list entries inside the cutoff at the latest evaluation (synchronises the device)."""
+        v = C.c_int64()
+        check(lib.so3lr_b200_system_valid_edges(self._h, C.byref(v)), "valid_edges")
+        return v.value
+
     def profile(self, enable=True):
         check(lib.so3lr_b200_system_profile(self._h, 1 if enable else 0), "profile")
 
