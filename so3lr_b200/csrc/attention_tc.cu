@@ -784,12 +784,13 @@ __device__ __forceinline__ void reverse_edges4(const RevLoads& L, float* rec, co
 // 12-15 dA, 16-19 dB: cotangents of the equivariant logits of edge (i<-j) and (j<-i) | 20-23, 24-27 those logits x cutoff |
 // 28-30 unit vector | 31 1/r | 32 d/dr (cutoff part + even Chebyshev terms) | 33 r | 34 1 for a list entry, 0 for a padding row |
 // 35 d/dr (odd Chebyshev terms) | 36-39, 40-43 cotangents of the invariant logits of edge (i<-j) and (j<-i) |
-// 44-47 invariant logit of edge (j<-i) x cutoff
+// 44-47 invariant logit of edge (j<-i) x cutoff; after the value path has read it: 44-46 angular part of the force on the receiver
 //
 // 16 warps.  Per tile: (1) four threads per edge prepare records and the A operand; (2) MMA chain w = Phi C + hs K2 (both filters);
 // (3) per filter, in two halves of 64 rows: tensor memory -> shared tile, reverse edge loop (4 rows per warp, sender rows
 // prefetched across the barriers), dw into the A operand; (4) per filter: MMA chain [dPhi | dhs] = dw [C^T | K2^T], then per
-// edge the radial derivative and the spherical hidden layer; (5) angular part, force on the receiver, cotangent of ev.
+// edge the radial derivative and the spherical hidden layer (the angular part of the force is formed beneath the last chain);
+// (5) force on the receiver, cotangent of ev.
 __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsigned char* __restrict__ img_g, const float* __restrict__ sph1_k,
                                                                     const float* __restrict__ sph1_b, int n_recv,
                                                                     const int* __restrict__ vrow_ptr, const int* __restrict__ ve_i,
@@ -953,7 +954,36 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
         umma_commit(mbar);
       }
       __syncwarp();
-      if (f == 0) value_cotangent(rec, 8 * warp, lane, g_xa, g_qkv);      // while the tensor cores run
+      if (f == 0) {
+        value_cotangent(rec, 8 * warp, lane, g_xa, g_qkv);      // while the tensor cores run
+      } else if (tid < 128) {
+        // angular part of the force on the receiver (independent of the radial derivative that the running MMA yields); it
+        // takes the record fields 44..46, which the value path has released
+        float* rp = rec + tid * kBwRec;
+        if (rp[34] != 0.f) {
+          const int j = __float_as_int(rp[0]), i = __float_as_int(rp[1]);
+          const float4 aA = ld4(rp + 20), aB = ld4(rp + 24), uu = ld4(rp + 28);
+          const float* gevi = gev1 + (size_t)i * kMTot;
+          const float* gevj = gev1 + (size_t)j * kMTot;
+          const float aAv[4] = {aA.x, aA.y, aA.z, aA.w}, aBv[4] = {aB.x, aB.y, aB.z, aB.w};
+          float gY[kMTot];
+#pragma unroll
+          for (int c = 0; c < 6; ++c) {
+            const float4 a = ld4(gevi + 4 * c), b = ld4(gevj + 4 * c);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int m = 4 * c + q, l = degree_of(m);
+              const float sgn = (l == 0 || l == 2) ? -1.f : 1.f;
+              gY[m] = aAv[l] * av[q] + sgn * aBv[l] * bv[q];
+            }
+          }
+          float gux, guy, guz;
+          sph_harm_24_vjp(uu.x, uu.y, uu.z, gY, gux, guy, guz);
+          const float gd = gux * uu.x + guy * uu.y + guz * uu.z;
+          st4(rp + 44, make_float4((gux - gd * uu.x) * uu.w, (guy - gd * uu.y) * uu.w, (guz - gd * uu.z) * uu.w, 0.f));
+        }
+      }
       done = true;
       if (tid == 0) done = mbar_wait(mbar, parity);
       parity ^= 1;
@@ -1006,34 +1036,14 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
       BW_MARK(6);
     }
     if (failed) break;
-    // ---- angular part and the force on the receiver (threads 0..127); cotangent of ev (warps 8..15, 16 rows each) ----
+    // ---- force on the receiver (threads 0..127; the angular part was formed under the last MMA); cotangent of ev (8 rows per warp) ----
     if (tid < 128) {
       const float* rp = rec + tid * kBwRec;
       if (rp[34] != 0.f) {
-        const int j = __float_as_int(rp[0]), i = __float_as_int(rp[1]);
-        const float4 aA = ld4(rp + 20), aB = ld4(rp + 24), uu = ld4(rp + 28);
+        const int i = __float_as_int(rp[1]);
+        const float4 uu = ld4(rp + 28), ang = ld4(rp + 44);
         const float g_r = rp[32] + rp[35];
-        const float* gevi = gev1 + (size_t)i * kMTot;
-        const float* gevj = gev1 + (size_t)j * kMTot;
-        const float aAv[4] = {aA.x, aA.y, aA.z, aA.w}, aBv[4] = {aB.x, aB.y, aB.z, aB.w};
-        float gY[kMTot];
-#pragma unroll
-        for (int c = 0; c < 6; ++c) {
-          const float4 a = ld4(gevi + 4 * c), b = ld4(gevj + 4 * c);
-          const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int m = 4 * c + q, l = degree_of(m);
-            const float sgn = (l == 0 || l == 2) ? -1.f : 1.f;
-            gY[m] = aAv[l] * av[q] + sgn * aBv[l] * bv[q];
-          }
-        }
-        float gux, guy, guz;
-        sph_harm_24_vjp(uu.x, uu.y, uu.z, gY, gux, guy, guz);
-        const float gd = gux * uu.x + guy * uu.y + guz * uu.z;
-        const float fsx = g_r * uu.x + (gux - gd * uu.x) * uu.w;
-        const float fsy = g_r * uu.y + (guy - gd * uu.y) * uu.w;
-        const float fsz = g_r * uu.z + (guz - gd * uu.z) * uu.w;
+        const float fsx = fmaf(g_r, uu.x, ang.x), fsy = fmaf(g_r, uu.y, ang.y), fsz = fmaf(g_r, uu.z, ang.z);
         atomicAdd(F + 3 * (size_t)i, fsx); atomicAdd(F + 3 * (size_t)i + 1, fsy); atomicAdd(F + 3 * (size_t)i + 2, fsz);
         if (virial) {
           const float hr = 0.5f * rp[33];
@@ -1044,12 +1054,13 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
           atomicAdd(w + 5, 0.5f * (wx * fsy + wy * fsx));
         }
       }
-    } else if (warp >= 8) {
+    }
+    {
       int cur_i = -1;
       float acc = 0.f;
-      const int k0 = 16 * (warp - 8);
+      const int k0 = 8 * warp;
 #pragma unroll 4
-      for (int k = k0; k < k0 + 16; ++k) {
+      for (int k = k0; k < k0 + 8; ++k) {
         const float* rp = rec + k * kBwRec;
         const int j = __float_as_int(rp[0]), i = __float_as_int(rp[1]);
         if (i != cur_i) {
