@@ -256,6 +256,15 @@ SO3LR_B200_API int so3lr_b200_dd_layer_backward_attn(so3lr_b200_system* sys, voi
 SO3LR_B200_API int so3lr_b200_dd_forces(so3lr_b200_system* sys, void* stream, float* F_owned_dev);
 SO3LR_B200_API int so3lr_b200_dd_buffer(so3lr_b200_system* sys, int which, int layer, float** ptr, int* row_floats);
 
+/* Halo packing for the exchanges between ranks: gather rows idx[r] (r < n_rows; 64-bit indices on the device) of up to four
+ * row-major float arrays with `widths[t]` floats per row side by side into buf[n_rows][sum of widths], and the reverse
+ * (scatter the columns of buf back into rows idx[r] of the arrays).  One launch per call on the device of the current
+ * context; no counterpart in the reference (it has no multi-device path). */
+SO3LR_B200_API int so3lr_b200_pack_rows(void* stream, int n_arrays, const float* const* arrays_dev, const int* widths, const int64_t* idx_dev,
+                                        int64_t n_rows, float* buf_dev);
+SO3LR_B200_API int so3lr_b200_unpack_rows(void* stream, int n_arrays, float* const* arrays_dev, const int* widths, const int64_t* idx_dev,
+                                          int64_t n_rows, const float* buf_dev);
+
 /* Optional timing of kernel groups with CUDA events recorded on the launching stream.  `profile(sys, 1)` starts a
  * fresh recording; `profile_read` synchronises the device, returns the number of groups and fills, per group, the
  * summed device time in ms, the number of timed launches and a static name.  No counterpart in the reference

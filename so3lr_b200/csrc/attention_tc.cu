@@ -846,6 +846,7 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
 #define BW_MARK(k) do { } while (0)
 #endif
   for (long long tile = tile0; tile < tile1 && !failed; ++tile) {
+    float dev8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     // ---- per-edge preparation ----
     {
       const int row = tid & 127, role = tid >> 7;
@@ -954,6 +955,14 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
         umma_commit(mbar);
       }
       __syncwarp();
+      if (f == 1 && lane < kMTot) {      // ev differences of this warp's 8 rows of the final flush: requested now, used after the last MMA
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float* rp = rec + (8 * warp + k) * kBwRec;
+          const int j = __float_as_int(rp[0]), i = __float_as_int(rp[1]);
+          dev8[k] = ev_in[(size_t)j * kMTot + lane] - ev_in[(size_t)i * kMTot + lane];
+        }
+      }
       if (f == 0) {
         value_cotangent(rec, 8 * warp, lane, g_xa, g_qkv);      // while the tensor cores run
       } else if (tid < 128) {
@@ -1039,38 +1048,44 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
     // ---- force on the receiver (threads 0..127; the angular part was formed under the last MMA); cotangent of ev (8 rows per warp) ----
     if (tid < 128) {
       const float* rp = rec + tid * kBwRec;
-      if (rp[34] != 0.f) {
-        const int i = __float_as_int(rp[1]);
-        const float4 uu = ld4(rp + 28), ang = ld4(rp + 44);
-        const float g_r = rp[32] + rp[35];
-        const float fsx = fmaf(g_r, uu.x, ang.x), fsy = fmaf(g_r, uu.y, ang.y), fsz = fmaf(g_r, uu.z, ang.z);
+      const bool on = rp[34] != 0.f;
+      const int i = on ? __float_as_int(rp[1]) : -1;
+      const float4 uu = ld4(rp + 28), ang = ld4(rp + 44);
+      const float g_r = rp[32] + rp[35];
+      float fsx = on ? fmaf(g_r, uu.x, ang.x) : 0.f, fsy = on ? fmaf(g_r, uu.y, ang.y) : 0.f, fsz = on ? fmaf(g_r, uu.z, ang.z) : 0.f;
+      if (virial && on) {
+        const float hr = 0.5f * rp[33];
+        const float wx = hr * uu.x, wy = hr * uu.y, wz = hr * uu.z;
+        float* w = virial + 6 * (size_t)i;
+        atomicAdd(w, wx * fsx); atomicAdd(w + 1, wy * fsy); atomicAdd(w + 2, wz * fsz);
+        atomicAdd(w + 3, 0.5f * (wy * fsz + wz * fsy)); atomicAdd(w + 4, 0.5f * (wx * fsz + wz * fsx));
+        atomicAdd(w + 5, 0.5f * (wx * fsy + wy * fsx));
+      }
+      // the rows of a tile are sorted by receiver: sum each run of equal receivers inside the warp (segmented scan) and let its
+      // last lane add the total, instead of up to 32 additions to one address
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float tx = __shfl_up_sync(0xffffffffu, fsx, o), ty = __shfl_up_sync(0xffffffffu, fsy, o), tz = __shfl_up_sync(0xffffffffu, fsz, o);
+        const int ti = __shfl_up_sync(0xffffffffu, i, o);
+        if (lane >= o && ti == i) { fsx += tx; fsy += ty; fsz += tz; }
+      }
+      const int inext = __shfl_down_sync(0xffffffffu, i, 1);
+      if (on && (lane == 31 || inext != i)) {
         atomicAdd(F + 3 * (size_t)i, fsx); atomicAdd(F + 3 * (size_t)i + 1, fsy); atomicAdd(F + 3 * (size_t)i + 2, fsz);
-        if (virial) {
-          const float hr = 0.5f * rp[33];
-          const float wx = hr * uu.x, wy = hr * uu.y, wz = hr * uu.z;
-          float* w = virial + 6 * (size_t)i;
-          atomicAdd(w, wx * fsx); atomicAdd(w + 1, wy * fsy); atomicAdd(w + 2, wz * fsz);
-          atomicAdd(w + 3, 0.5f * (wy * fsz + wz * fsy)); atomicAdd(w + 4, 0.5f * (wx * fsz + wz * fsx));
-          atomicAdd(w + 5, 0.5f * (wx * fsy + wy * fsx));
-        }
       }
     }
     {
       int cur_i = -1;
       float acc = 0.f;
-      const int k0 = 8 * warp;
-#pragma unroll 4
-      for (int k = k0; k < k0 + 8; ++k) {
-        const float* rp = rec + k * kBwRec;
-        const int j = __float_as_int(rp[0]), i = __float_as_int(rp[1]);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float* rp = rec + (8 * warp + k) * kBwRec;
+        const int i = __float_as_int(rp[1]);
         if (i != cur_i) {
           if (cur_i >= 0 && lane < kMTot && acc != 0.f) atomicAdd(gev_in + (size_t)cur_i * kMTot + lane, acc);
           cur_i = i; acc = 0.f;
         }
-        if (lane < kMTot) {
-          const float dev = ev_in[(size_t)j * kMTot + lane] - ev_in[(size_t)i * kMTot + lane];
-          acc = fmaf(-2.f * invw(deg) * rp[8 + deg], dev, acc);
-        }
+        if (lane < kMTot) acc = fmaf(-2.f * invw(deg) * rp[8 + deg], dev8[k], acc);
       }
       if (cur_i >= 0 && lane < kMTot && acc != 0.f) atomicAdd(gev_in + (size_t)cur_i * kMTot + lane, acc);
     }

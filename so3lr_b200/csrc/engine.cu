@@ -1073,6 +1073,15 @@ SO3LR_B200_API int so3lr_b200_system_stats(so3lr_b200_system* S, int64_t* n_rebu
   return kOk;
 }
 
+SO3LR_B200_API int so3lr_b200_pack_rows(void* stream, int n_arrays, const float* const* arrays_dev, const int* widths, const int64_t* idx_dev,
+                                        int64_t n_rows, float* buf_dev) {
+  return so3lr::pack_rows(stream, n_arrays, const_cast<float* const*>(arrays_dev), widths, idx_dev, n_rows, buf_dev, false);
+}
+SO3LR_B200_API int so3lr_b200_unpack_rows(void* stream, int n_arrays, float* const* arrays_dev, const int* widths, const int64_t* idx_dev,
+                                          int64_t n_rows, const float* buf_dev) {
+  return so3lr::pack_rows(stream, n_arrays, arrays_dev, widths, idx_dev, n_rows, const_cast<float*>(buf_dev), true);
+}
+
 SO3LR_B200_API int so3lr_b200_system_valid_edges(so3lr_b200_system* S, int64_t* n_valid) {
   if (!S || !n_valid) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));

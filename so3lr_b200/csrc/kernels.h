@@ -43,6 +43,9 @@ void launch_atom_post_bwd_tc(cudaStream_t s, const LayerDev& L, int n, const flo
                              const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1, const unsigned char* projT_u,
                              const float* g_qkv_up, int* err);
 
+// ---- halo.cu: rows idx[r] of up to four row-major float arrays <-> one packed buffer [n_rows][sum of widths] ----
+int pack_rows(void* stream, int n_arrays, float* const* arrays, const int* widths, const int64_t* idx, int64_t n_rows, float* buf, bool unpack);
+
 // ---- attention.cu ----
 // Short-range edges are grouped by receiver: edges row_ptr[i] .. row_ptr[i+1]-1 belong to centre i and hold the
 // neighbour index nbr_j[e] and the displacement dR[e] (3 floats).  Edges with |dR| >= 4.5, |dR| == 0 or

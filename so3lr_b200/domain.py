@@ -356,6 +356,26 @@ class CudaBackend:
     def stats(self):
         return self.sys.stats()
 
+    # ---- halo packing: one launch gathers (scatters) the rows of all arrays of an exchange ----
+    def _rows_call(self, name, tensors, idx, buf):
+        from ._lib import check, lib
+        k = len(tensors)
+        ptrs = (C.c_void_p * k)(*[t.data_ptr() for t in tensors])
+        widths = (C.c_int * k)(*[int(t.shape[1]) for t in tensors])
+        check(getattr(lib, name)(self._stream(), k, ptrs, widths, C.c_void_p(idx.data_ptr()), C.c_int64(idx.numel()),
+                                 C.c_void_p(buf.data_ptr())), name)
+
+    def pack_rows(self, tensors, idx):
+        """buf[r] = the rows idx[r] of `tensors` ((n, w_t) float32, contiguous) side by side."""
+        buf = torch.empty((idx.numel(), sum(int(t.shape[1]) for t in tensors)), dtype=torch.float32, device=self.device)
+        if idx.numel():
+            self._rows_call("so3lr_b200_pack_rows", tensors, idx, buf)
+        return buf
+
+    def unpack_rows(self, tensors, idx, buf):
+        if idx.numel():
+            self._rows_call("so3lr_b200_unpack_rows", tensors, idx, buf)
+
 
 # ----------------------------------------------------------------------------------------------------------------
 # the driver of one rank
@@ -444,17 +464,30 @@ class DomainSystem:
             self._halo_events.append(ev)
         width = [t.shape[1] for t in tensors]
         me = self.rank
-        sends = {p: torch.cat([t[sl] for t in tensors], 1) for p, sl in send_slots.items() if p != me}
-        recvs = {p: torch.empty((sl.numel(), sum(width)), dtype=tensors[0].dtype, device=self.device)
-                 for p, sl in recv_slots.items() if p != me}
-        self.comm.exchange(sends, recvs)
-        for p, buf in recvs.items():
-            o = 0
-            for t, w in zip(tensors, width):
-                t[recv_slots[p]] = buf[:, o:o + w]
-                o += w
-        for t in tensors:                                   # own periodic images
-            t[recv_slots[me]] = t[send_slots[me]]
+        fused = (hasattr(self.backend, "pack_rows") and len(tensors) <= 4
+                 and all(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() for t in tensors))
+        if fused:       # one gather launch per peer into the send buffer, one scatter launch per peer out of the receive buffer
+            be = self.backend
+            sends = {p: be.pack_rows(tensors, sl) for p, sl in send_slots.items() if p != me}
+            recvs = {p: torch.empty((sl.numel(), sum(width)), dtype=torch.float32, device=self.device)
+                     for p, sl in recv_slots.items() if p != me}
+            self.comm.exchange(sends, recvs)
+            for p, buf in recvs.items():
+                be.unpack_rows(tensors, recv_slots[p], buf)
+            if recv_slots[me].numel():                      # own periodic images
+                be.unpack_rows(tensors, recv_slots[me], be.pack_rows(tensors, send_slots[me]))
+        else:
+            sends = {p: torch.cat([t[sl] for t in tensors], 1) for p, sl in send_slots.items() if p != me}
+            recvs = {p: torch.empty((sl.numel(), sum(width)), dtype=tensors[0].dtype, device=self.device)
+                     for p, sl in recv_slots.items() if p != me}
+            self.comm.exchange(sends, recvs)
+            for p, buf in recvs.items():
+                o = 0
+                for t, w in zip(tensors, width):
+                    t[recv_slots[p]] = buf[:, o:o + w]
+                    o += w
+            for t in tensors:                                   # own periodic images
+                t[recv_slots[me]] = t[send_slots[me]]
         if ev is not None:
             ev[1].record()
 
