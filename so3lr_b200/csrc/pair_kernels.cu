@@ -287,7 +287,10 @@ __global__ void __launch_bounds__(256) pair_lr_packed_kernel(LrParams P, Cell ce
   if (virial) va.flush_warp(virial, (size_t)i, lane);
 }
 
-// owned rows of a full list: i-side derivatives only, no atomics
+// Owned rows of a full list (decomposed runs).  A pair whose two ends are both owned is evaluated once, in the row that the
+// parity rule picks (balanced over the rows), and its share for the other end is scattered with atomics; a pair with a ghost
+// end is evaluated in the owned end's row only, which books half of the energy and its own derivatives (the ghost's owner does
+// the same from its side).  gq, gh and F_add must hold the values to add to (zeros for gq, gh) when the kernel starts.
 __global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cell, int n_owned, int n, const int* __restrict__ row_ptr,
                                                             const int* __restrict__ nbr_j, const int* __restrict__ Z,
                                                             const float* __restrict__ R, const float* __restrict__ q,
@@ -306,6 +309,8 @@ __global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cel
   for (int e = e0 + lane; e < e1; e += 32) {
     const int j = nbr_j[e];
     if (j < 0 || j >= n) continue;
+    const bool both = j < n_owned;
+    if (both && ((i < j) != (((i + j) & 1) == 0))) continue;      // the other end's row takes this pair
     float dx = R[3 * (size_t)j] - xi, dy = R[3 * (size_t)j + 1] - yi, dz = R[3 * (size_t)j + 2] - zi;
     min_image(cell, dx, dy, dz);
     const float r2 = dx * dx + dy * dy + dz * dz;
@@ -317,19 +322,27 @@ __global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cel
     const int Zj = Z[j];
     float e_d, dd_dr, dd_dhi, dd_dhj;
     dispersion_pair_dev(P, r, alf_i, c6f_i, hi, alpha_free(Zj), c6_free(Zj), hj, e_d, dd_dr, dd_dhi, dd_dhj);
-    ec = fmaf(0.5f * kKe * qi * qj, chi, ec);
-    ed += 0.5f * e_d;
+    const float w = both ? 1.f : 0.5f;                             // share of the pair energy booked on this row
+    ec = fmaf(w * kKe * qi * qj, chi, ec);
+    ed = fmaf(w, e_d, ed);
     gqi = fmaf(kKe * qj, chi, gqi);
     ghi += dd_dhi;
-    const float s = (kKe * qi * qj * dchi + dd_dr) * rinv;   // dE_ij/d(dR), dR = R_j - R_i; F_i = +that
-    fx = fmaf(s, dx, fx); fy = fmaf(s, dy, fy); fz = fmaf(s, dz, fz);
-    if (virial) va.add(0.5f * s, dx, dy, dz, dx, dy, dz);
+    const float s = (kKe * qi * qj * dchi + dd_dr) * rinv;   // dE_ij/d(dR), dR = R_j - R_i; F_i = +that, F_j = -that
+    const float gx = s * dx, gy = s * dy, gz = s * dz;
+    fx += gx; fy += gy; fz += gz;
+    if (virial) va.add(w * s, dx, dy, dz, dx, dy, dz);
+    if (both) {
+      atomicAdd(gq + j, kKe * qi * chi);
+      atomicAdd(gh + j, dd_dhj);
+      atomicAdd(F_add + 3 * (size_t)j, -gx); atomicAdd(F_add + 3 * (size_t)j + 1, -gy); atomicAdd(F_add + 3 * (size_t)j + 2, -gz);
+    }
   }
   ec = warp_sum(ec); ed = warp_sum(ed); gqi = warp_sum(gqi); ghi = warp_sum(ghi);
   fx = warp_sum(fx); fy = warp_sum(fy); fz = warp_sum(fz);
   if (lane == 0) {
-    e_coul[i] = ec; e_disp[i] = ed; gq[i] = gqi; gh[i] = ghi;
-    F_add[3 * (size_t)i] += fx; F_add[3 * (size_t)i + 1] += fy; F_add[3 * (size_t)i + 2] += fz;
+    e_coul[i] = ec; e_disp[i] = ed;      // only this warp writes the energies of row i
+    atomicAdd(gq + i, gqi); atomicAdd(gh + i, ghi);
+    atomicAdd(F_add + 3 * (size_t)i, fx); atomicAdd(F_add + 3 * (size_t)i + 1, fy); atomicAdd(F_add + 3 * (size_t)i + 2, fz);
   }
   if (virial) va.flush_warp(virial, (size_t)i, lane);
 }
@@ -533,6 +546,8 @@ void launch_pair_lr_owned(cudaStream_t s, const LrParams& P, const Cell& cell, i
                           const int* nbr_j, const int* Z, const float* R, const float* q, const float* h, float* F_add,
                           float* gq, float* gh, float* e_coul, float* e_disp, float* virial) {
   if (n_owned <= 0) return;
+  cudaMemsetAsync(gq, 0, (size_t)n_owned * sizeof(float), s);
+  cudaMemsetAsync(gh, 0, (size_t)n_owned * sizeof(float), s);
   { pair_lr_owned_kernel<<<(n_owned + 7) / 8, 256, 0, s>>>(P, cell, n_owned, n, row_ptr, nbr_j, Z, R, q, h, F_add, gq, gh, e_coul, e_disp, virial); count_launch(); }
 }
 
