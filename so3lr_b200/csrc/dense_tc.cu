@@ -945,6 +945,310 @@ __global__ void __launch_bounds__(NTHR, 1) atom_post_bwd_tc_kernel(LayerDev L, i
   T.finish(err);
 }
 
+
+// rows of 64 floats -> staging tile (two rows per warp instruction; rows beyond n read as zero)
+__device__ __forceinline__ void load_rows64(Tile& T, const float* __restrict__ src, int row0, int n) {
+  const int sub = T.lane >> 4, c = 4 * (T.lane & 15);
+#pragma unroll
+  for (int i = 0; i < TM / (2 * (NTHR / 32)); ++i) {
+    const int rr = 2 * (T.warp + (NTHR / 32) * i) + sub, a = row0 + rr;
+    const float4 v = a < n ? __ldg(reinterpret_cast<const float4*>(src + (size_t)a * 64 + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    st4(T.S + rr * SS + c, v);
+  }
+}
+__device__ __forceinline__ void flush_rows64(Tile& T, float* __restrict__ dst, int row0, int n) {
+  const int sub = T.lane >> 4, c = 4 * (T.lane & 15);
+#pragma unroll
+  for (int i = 0; i < TM / (2 * (NTHR / 32)); ++i) {
+    const int rr = 2 * (T.warp + (NTHR / 32) * i) + sub, a = row0 + rr;
+    if (a < n) st4(dst + (size_t)a * 64 + c, ld4(T.S + rr * SS + c));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// output heads, forward: per-atom NN energy, raw partial charge, signed Hirshfeld value.
+//   e = (fin_e . silu(x W_e + b_e) + c_e) scale[Z] + offset[Z];  q = fin_q . silu(x W_q + b_q) + c_q + embed_q[Z];
+//   hv = embed0[Z] + ((silu(x W_h1 + b_h1) W_h2 + b_h2) . embed1[Z]) / 8
+// saves the pre-activations ze, zq, zh for the reverse pass
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(NTHR, 1) heads_fwd_tc_kernel(ModelDev M, int n, const int* __restrict__ Z, const float* __restrict__ x,
+                                                               float* __restrict__ ze, float* __restrict__ zq, float* __restrict__ zh,
+                                                               float* __restrict__ e_nn, float* __restrict__ q_raw, float* __restrict__ hv,
+                                                               int* err) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  Tile T;
+  T.init(smem);
+  const int tid = T.tid, warp = T.warp, lane = T.lane, row = T.row, quarter = T.quarter, c0 = T.c0;
+  const uint32_t a_smem = smem_u32(T.A), w_smem = smem_u32(smem + kOffW);
+  float* S = T.S;
+  const int wr = 8 * warp + (lane & 7), ch = lane >> 3;
+  const int n_tiles = (n + TM - 1) / TM;
+
+  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const int row0 = tile * TM;
+    if (tid == 0) T.load_weights(M.e_reg_u, 65536);
+    {   // x -> A (warp-local)
+      const int aw = row0 + wr;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float v[8];
+        if (aw < n) ldg8(x + (size_t)aw * kF + 8 * (4 * i + ch), v);
+        else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) v[k] = 0.f;
+        }
+        a_store8(T.A, 4 * i + ch, wr, v);
+      }
+    }
+    T.operands_ready();
+    // energy and charge heads share the structure Dense(128) -> silu -> dot
+#pragma unroll 1
+    for (int head = 0; head < 2; ++head) {
+      if (tid == 0) {
+        T.wait_weights();
+        tc_fence_after();
+        issue_gemm(T.tmem, 0, a_smem, 0, w_smem, 32768, 128, 8, 0);
+        umma_commit(T.mbar);
+      }
+      if (head == 1) T.flush_rows(ze, kF, row0, n, kF);      // the first head's pre-activations leave beneath the second contraction
+      T.wait_mma();
+      if (tid == 0) {
+        if (head == 0) T.load_weights(M.q_reg_u, 65536);
+        else {      // both Hirshfeld kernels: [128 x 64] at the start of the buffer, [64 x 64] 32 KB above
+          mbar_expect_tx(T.wbar, 32768 + 16384);
+          bulk_load(w_smem, M.h_reg_u, 32768, T.wbar);
+          bulk_load(w_smem + 32768, M.h_fin_u, 16384, T.wbar);
+        }
+      }
+      __syncthreads();      // the staging tile has been flushed by every warp
+      {
+        const float* bias = head == 0 ? M.e_reg_b : M.q_reg_b;
+        const float* fin = head == 0 ? M.e_fin_k : M.q_fin_k;
+        float v[32];
+        tmem_acc32(T.tlane, c0, v);
+        float part = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float4 b = __ldg(reinterpret_cast<const float4*>(bias + c0) + k), f = __ldg(reinterpret_cast<const float4*>(fin + c0) + k);
+          v[4 * k] += b.x; v[4 * k + 1] += b.y; v[4 * k + 2] += b.z; v[4 * k + 3] += b.w;
+          st4(S + row * SS + c0 + 4 * k, make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]));
+          part = fmaf(silu_fast(v[4 * k]), f.x, fmaf(silu_fast(v[4 * k + 1]), f.y, fmaf(silu_fast(v[4 * k + 2]), f.z, fmaf(silu_fast(v[4 * k + 3]), f.w, part))));
+        }
+        T.redf[quarter * TM + row] = part;
+      }
+      tc_fence_before();
+      __syncthreads();
+      if (tid < TM) {
+        const int a = row0 + tid;
+        if (a < n) {
+          const float s = (T.redf[tid] + T.redf[TM + tid]) + (T.redf[2 * TM + tid] + T.redf[3 * TM + tid]);
+          int z = Z[a];
+          if (head == 0) {
+            z = z < 0 ? 0 : (z >= kZEmbed ? kZEmbed - 1 : z);
+            e_nn[a] = (s + M.e_fin_b) * M.e_scale[z] + M.e_offset[z];
+          } else {
+            z = z < 0 ? 0 : (z >= kZHead ? kZHead - 1 : z);
+            q_raw[a] = s + M.q_fin_b + M.q_embed[z];
+          }
+        }
+      }
+    }
+    // Hirshfeld: 128 -> 64 -> 64, then the dot product with the element's query
+    if (tid == 0) {
+      T.wait_weights();
+      tc_fence_after();
+      issue_gemm(T.tmem, 0, a_smem, 0, w_smem, 16384, 64, 8, 0);
+      umma_commit(T.mbar);
+    }
+    T.flush_rows(zq, kF, row0, n, kF);
+    T.wait_mma();
+    __syncthreads();
+    if (quarter < 2) {
+      float v[32];
+      tmem_acc32(T.tlane, c0, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float4 b = __ldg(reinterpret_cast<const float4*>(M.h_reg_b + c0) + k);
+        v[4 * k] += b.x; v[4 * k + 1] += b.y; v[4 * k + 2] += b.z; v[4 * k + 3] += b.w;
+        st4(S + row * SS + c0 + 4 * k, make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]));
+      }
+#pragma unroll
+      for (int k = 0; k < 32; ++k) v[k] = silu_fast(v[k]);
+      a_store32(T.A, c0, row, v);
+    }
+    T.operands_ready();
+    if (tid == 0) {
+      tc_fence_after();
+      issue_gemm(T.tmem, 0, a_smem, 0, w_smem + 32768, 8192, 64, 4, 0);
+      umma_commit(T.mbar);
+    }
+    flush_rows64(T, zh, row0, n);
+    T.wait_mma();
+    {
+      float part = 0.f;
+      if (quarter < 2) {
+        const int a = row0 + row;
+        int z = a < n ? Z[a] : 0;
+        z = z < 0 ? 0 : (z >= kZHead ? kZHead - 1 : z);
+        float v[32];
+        tmem_acc32(T.tlane, c0, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float4 b = __ldg(reinterpret_cast<const float4*>(M.h_fin_b + c0) + k);
+          const float4 e = __ldg(reinterpret_cast<const float4*>(M.h_embed1 + (size_t)z * 64 + c0) + k);
+          part = fmaf(v[4 * k] + b.x, e.x, fmaf(v[4 * k + 1] + b.y, e.y, fmaf(v[4 * k + 2] + b.z, e.z, fmaf(v[4 * k + 3] + b.w, e.w, part))));
+        }
+      }
+      T.redf[quarter * TM + row] = part;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid < TM) {
+      const int a = row0 + tid;
+      if (a < n) {
+        int z = Z[a];
+        z = z < 0 ? 0 : (z >= kZHead ? kZHead - 1 : z);
+        hv[a] = M.h_embed0[z] + (T.redf[tid] + T.redf[TM + tid]) * 0.125f;
+      }
+    }
+    __syncthreads();   // staging tile, operand buffer and reduction arrays are free for the next tile
+  }
+  T.finish(err);
+}
+
+// ------------------------------------------------------------------------------------------------
+// output heads, reverse: gx = dL/dx_final from the cotangents of e_nn (ge), of the raw charge (gq) and of the Hirshfeld ratio (gh)
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(NTHR, 1) heads_bwd_tc_kernel(ModelDev M, int n, const int* __restrict__ Z, const float* __restrict__ ze,
+                                                               const float* __restrict__ zq, const float* __restrict__ zh,
+                                                               const float* __restrict__ hv, const float* __restrict__ ge,
+                                                               const float* __restrict__ gq, const float* __restrict__ gh,
+                                                               float* __restrict__ gx, int* err) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  Tile T;
+  T.init(smem);
+  const int tid = T.tid, warp = T.warp, lane = T.lane, row = T.row, quarter = T.quarter, c0 = T.c0;
+  const uint32_t a_smem = smem_u32(T.A), w_smem = smem_u32(smem + kOffW);
+  unsigned char* A1 = smem + kOffS;   // second operand buffer inside the staging region
+  float* S = T.S;
+  const int wr = 8 * warp + (lane & 7), ch = lane >> 3;
+  const int n_tiles = (n + TM - 1) / TM;
+
+  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const int row0 = tile * TM;
+    const int aw = row0 + wr;
+    if (tid == 0) {      // h_fin^T [64 x 64] at the start of the buffer, h_reg^T [64 x 128] 16 KB above
+      mbar_expect_tx(T.wbar, 16384 + 32768);
+      bulk_load(w_smem, M.h_finT_u, 16384, T.wbar);
+      bulk_load(w_smem + 16384, M.h_regT_u, 32768, T.wbar);
+    }
+    // per-row coefficients (every lane of a row's quad computes them)
+    float c_e = 0.f, c_q = 0.f, c_h = 0.f;
+    int zz = 0;
+    if (aw < n) {
+      const int z = Z[aw];
+      const int ze_ = z < 0 ? 0 : (z >= kZEmbed ? kZEmbed - 1 : z);
+      zz = z < 0 ? 0 : (z >= kZHead ? kZHead - 1 : z);
+      c_e = ge[aw] * M.e_scale[ze_];
+      c_q = gq[aw];
+      c_h = gh[aw] * (hv[aw] < 0.f ? -0.125f : 0.125f);
+    }
+    // Hirshfeld branch: g_k = c_h embed1[Z] -> A (K = 64: chunks 0..7, two per lane); zh -> staging tile
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float v[8];
+      ldg8(M.h_embed1 + (size_t)zz * 64 + 8 * (4 * i + ch), v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] *= c_h;
+      a_store8(T.A, 4 * i + ch, wr, v);
+    }
+    load_rows64(T, zh, row0, n);
+    T.operands_ready();
+    if (tid == 0) {
+      T.wait_weights();
+      tc_fence_after();
+      issue_gemm(T.tmem, 128, a_smem, 0, w_smem, 8192, 64, 4, 0);      // g_sh = g_k H_fin^T into columns [128, 192)
+      umma_commit(T.mbar);
+    }
+    T.wait_mma();
+    if (quarter < 2) {      // g_zh = g_sh * silu'(zh) -> A
+      float v[32];
+      tmem_acc32(T.tlane, 128 + c0, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float4 z = ld4(S + row * SS + c0 + 4 * k);
+        v[4 * k] *= dsilu_fast(z.x); v[4 * k + 1] *= dsilu_fast(z.y); v[4 * k + 2] *= dsilu_fast(z.z); v[4 * k + 3] *= dsilu_fast(z.w);
+      }
+      a_store32(T.A, c0, row, v);
+    }
+    T.operands_ready();      // also: every thread is done with the staging tile, which now becomes the second operand buffer
+    if (tid == 0) {
+      tc_fence_after();
+      issue_gemm(T.tmem, 0, a_smem, 0, w_smem + 16384, 16384, 128, 4, 0);      // gx = g_zh H_reg^T
+      umma_commit(T.mbar);
+    }
+    // energy branch operand (warp-local): c_e fin_e silu'(ze) -> second buffer
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = 8 * (4 * i + ch);
+      float v[8], f[8];
+      if (aw < n) ldg8(ze + (size_t)aw * kF + c, v);
+      else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = 0.f;
+      }
+      ldg8(M.e_fin_k + c, f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = c_e * f[k] * dsilu_fast(v[k]);
+      a_store8(A1, 4 * i + ch, wr, v);
+    }
+    T.wait_mma();      // the Hirshfeld kernels have been read: their buffer takes the energy head's kernel
+    if (tid == 0) T.load_weights(M.e_regT_u, 65536);
+    // charge branch operand -> first buffer (its readers have completed)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = 8 * (4 * i + ch);
+      float v[8], f[8];
+      if (aw < n) ldg8(zq + (size_t)aw * kF + c, v);
+      else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = 0.f;
+      }
+      ldg8(M.q_fin_k + c, f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = c_q * f[k] * dsilu_fast(v[k]);
+      a_store8(T.A, 4 * i + ch, wr, v);
+    }
+    T.operands_ready();
+    if (tid == 0) {
+      T.wait_weights();
+      tc_fence_after();
+      issue_gemm(T.tmem, 0, smem_u32(A1), 0, w_smem, 32768, 128, 8, 1);      // gx += g_ze E_reg^T
+      umma_commit(T.mbar);
+    }
+    T.wait_mma();
+    if (tid == 0) {
+      T.load_weights(M.q_regT_u, 65536);
+      T.wait_weights();
+      tc_fence_after();
+      issue_gemm(T.tmem, 0, a_smem, 0, w_smem, 32768, 128, 8, 1);      // gx += g_zq Q_reg^T
+      umma_commit(T.mbar);
+    }
+    T.wait_mma();
+    {
+      float v[32];
+      tmem_acc32(T.tlane, c0, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) st4(S + row * SS + c0 + 4 * k, make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]));
+    }
+    tc_fence_before();
+    __syncthreads();
+    T.flush_rows(gx, kF, row0, n, kF);
+    __syncthreads();   // staging tile and operand buffers are free for the next tile
+  }
+  T.finish(err);
+}
+
 }  // namespace
 
 void dense_debug_print() {
@@ -964,6 +1268,8 @@ void dense_debug_print() {
 int configure_dense_tc_kernels() {
   SO3LR_CUDA_CHECK(cudaFuncSetAttribute(atom_post_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDense));
   SO3LR_CUDA_CHECK(cudaFuncSetAttribute(atom_post_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDense));
+  SO3LR_CUDA_CHECK(cudaFuncSetAttribute(heads_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDense));
+  SO3LR_CUDA_CHECK(cudaFuncSetAttribute(heads_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemDense));
   return kOk;
 }
 
@@ -981,6 +1287,21 @@ void launch_atom_post_bwd_tc(cudaStream_t s, const LayerDev& L, int n, const flo
   if (n <= 0) return;
   const int tiles = (n + TM - 1) / TM, grid = tiles < sm_count() ? tiles : sm_count();
   atom_post_bwd_tc_kernel<<<grid, NTHR, kSmemDense, s>>>(L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1, projT_u, g_qkv_up, err);
+  count_launch();
+}
+
+void launch_heads_fwd_tc(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* x, float* ze, float* zq, float* zh, float* e_nn,
+                         float* q_raw, float* hv, int* err) {
+  if (n <= 0) return;
+  const int tiles = (n + TM - 1) / TM, grid = tiles < sm_count() ? tiles : sm_count();
+  heads_fwd_tc_kernel<<<grid, NTHR, kSmemDense, s>>>(M, n, Z, x, ze, zq, zh, e_nn, q_raw, hv, err);
+  count_launch();
+}
+void launch_heads_bwd_tc(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* ze, const float* zq, const float* zh,
+                         const float* hv, const float* ge, const float* gq, const float* gh, float* gx, int* err) {
+  if (n <= 0) return;
+  const int tiles = (n + TM - 1) / TM, grid = tiles < sm_count() ? tiles : sm_count();
+  heads_bwd_tc_kernel<<<grid, NTHR, kSmemDense, s>>>(M, n, Z, ze, zq, zh, hv, ge, gq, gh, gx, err);
   count_launch();
 }
 

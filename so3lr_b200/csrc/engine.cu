@@ -478,7 +478,7 @@ bool use_mma_dense() {
   return v;
 }
 // The post-attention blocks run on the tcgen05 kernels of dense_tc.cu unless SO3LR_B200_DENSE names an earlier generation
-// ("mma": mma.sync kernels, "simt": FP32 shared-memory kernels); the output heads use the mma.sync kernels in both cases.
+// ("mma": mma.sync kernels, "simt": FP32 shared-memory kernels).
 bool use_tc_dense() {
   static const bool v = [] {
     const char* e = std::getenv("SO3LR_B200_DENSE");
@@ -503,13 +503,15 @@ void post_bwd_dispatch(cudaStream_t s, const LayerDev& L, int n, const float* xa
   else launch_atom_post_bwd(s, L, n, xa, ev1, z1, x3, gate, g4, gev2, g_xa, gev1);
 }
 void heads_fwd_dispatch(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* x, float* ze, float* zq, float* zh,
-                        float* e_nn, float* q_raw, float* hv) {
-  if (use_mma_dense()) launch_heads_fwd_mma(s, M, n, Z, x, ze, zq, zh, e_nn, q_raw, hv);
+                        float* e_nn, float* q_raw, float* hv, int* err) {
+  if (use_tc_dense()) launch_heads_fwd_tc(s, M, n, Z, x, ze, zq, zh, e_nn, q_raw, hv, err);
+  else if (use_mma_dense()) launch_heads_fwd_mma(s, M, n, Z, x, ze, zq, zh, e_nn, q_raw, hv);
   else launch_heads_fwd(s, M, n, Z, x, ze, zq, zh, e_nn, q_raw, hv);
 }
 void heads_bwd_dispatch(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* ze, const float* zq, const float* zh,
-                        const float* hv, const float* ge, const float* gq, const float* gh, float* gx) {
-  if (use_mma_dense()) launch_heads_bwd_mma(s, M, n, Z, ze, zq, zh, hv, ge, gq, gh, gx);
+                        const float* hv, const float* ge, const float* gq, const float* gh, float* gx, int* err) {
+  if (use_tc_dense()) launch_heads_bwd_tc(s, M, n, Z, ze, zq, zh, hv, ge, gq, gh, gx, err);
+  else if (use_mma_dense()) launch_heads_bwd_mma(s, M, n, Z, ze, zq, zh, hv, ge, gq, gh, gx);
   else launch_heads_bwd(s, M, n, Z, ze, zq, zh, hv, ge, gq, gh, gx);
 }
 void attn_fwd_dispatch(so3lr_b200_system* S, cudaStream_t st, const LayerDev& L, int n_recv, int n, const int* row_ptr, const int* nbr_j, const float* dR,
@@ -585,7 +587,7 @@ int fused_forward(so3lr_b200_system* S, cudaStream_t st, const float* R, const S
     S->prof.end(st);
   }
   S->prof.begin(kPHeads, st);
-  heads_fwd_dispatch(st, M, c.n0, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv);
+  heads_fwd_dispatch(st, M, c.n0, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv, S->d_flag + 1);
   S->prof.end(st);
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
@@ -598,7 +600,7 @@ int fused_backward(so3lr_b200_system* S, cudaStream_t st, const Shells& c, float
   const int npost[kNumLayers] = {c.n2, c.n1, c.n0};   // atoms whose layer-l outputs carry a cotangent
   const int nattn[kNumLayers] = {c.n3, c.n2, c.n1};   // atoms that receive a cotangent through layer l's attention
   S->prof.begin(kPHeads, st);
-  heads_bwd_dispatch(st, M, c.n0, S->d_Z, S->ze, S->zq, S->zh, S->hv, S->ones, S->gq_raw, S->gh, S->g4);
+  heads_bwd_dispatch(st, M, c.n0, S->d_Z, S->ze, S->zq, S->zh, S->hv, S->ones, S->gq_raw, S->gh, S->g4, S->d_flag + 1);
   S->prof.end(st);
   float* gev2 = S->gev_a;
   float* gev_in = S->gev_b;
@@ -1454,7 +1456,7 @@ SO3LR_B200_API int so3lr_b200_dd_heads(so3lr_b200_system* S, void* stream, float
   cudaStream_t st = (cudaStream_t)stream;
   const int n0 = S->shells[0];
   S->prof.begin(kPHeads, st);
-  heads_fwd_dispatch(st, S->mctx, n0, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv);
+  heads_fwd_dispatch(st, S->mctx, n0, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv, S->d_flag + 1);
   S->prof.end(st);
   SO3LR_CUDA_CHECK(cudaMemcpyAsync(q_raw_owned_dev, S->q_raw, (size_t)n0 * sizeof(float), cudaMemcpyDeviceToDevice, st));
   { abs_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->hv, h_owned_dev); count_launch(); }
@@ -1489,7 +1491,7 @@ SO3LR_B200_API int so3lr_b200_dd_heads_backward(so3lr_b200_system* S, void* stre
   { combine_energy_kernel<<<(n0 + 255) / 256, 256, 0, st>>>(n0, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
   if (energy_owned_dev) { sum_to_double_kernel<<<1, 1024, 0, st>>>(n0, S->e_atom, energy_owned_dev); count_launch(); }
   S->prof.begin(kPHeads, st);
-  heads_bwd_dispatch(st, S->mctx, n0, S->d_Z, S->ze, S->zq, S->zh, S->hv, S->ones, S->gq_raw, S->gh, S->g4);
+  heads_bwd_dispatch(st, S->mctx, n0, S->d_Z, S->ze, S->zq, S->zh, S->hv, S->ones, S->gq_raw, S->gh, S->g4, S->d_flag + 1);
   S->prof.end(st);
   S->dd_gev2 = S->gev_a; S->dd_gev_in = S->gev_b;
   fill(st, S->dd_gev2, (size_t)n0 * kMTot, 0.f);

@@ -43,6 +43,11 @@ void launch_atom_post_bwd_tc(cudaStream_t s, const LayerDev& L, int n, const flo
                              const float* gate, const float* g4, const float* gev2, float* g_xa, float* gev1, const unsigned char* projT_u,
                              const float* g_qkv_up, int* err);
 
+void launch_heads_fwd_tc(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* x, float* ze, float* zq, float* zh, float* e_nn,
+                         float* q_raw, float* hv, int* err);
+void launch_heads_bwd_tc(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* ze, const float* zq, const float* zh,
+                         const float* hv, const float* ge, const float* gq, const float* gh, float* gx, int* err);
+
 // ---- halo.cu: rows idx[r] of up to four row-major float arrays <-> one packed buffer [n_rows][sum of widths] ----
 int pack_rows(void* stream, int n_arrays, float* const* arrays, const int* widths, const int64_t* idx, int64_t n_rows, float* buf, bool unpack);
 

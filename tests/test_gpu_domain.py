@@ -115,3 +115,29 @@ def test_sharded_molecule_batch_matches_unsharded(oracle_params):
     np.testing.assert_allclose(np.concatenate([p["energy"] for p in parts]), whole["energy"], rtol=1e-6)
     np.testing.assert_allclose(np.concatenate([p["forces"] for p in parts]), whole["forces"], atol=2e-5)
     np.testing.assert_allclose(np.concatenate([p["dipole_vec"] for p in parts]), whole["dipole_vec"], atol=2e-5)
+
+
+def test_halo_pack_and_unpack_rows_match_indexing():
+    """The fused gather / scatter of the halo messages against plain tensor indexing: three arrays of different widths,
+    repeated and unsorted row indices on the way out, distinct rows on the way back, and the empty message."""
+    from so3lr_b200.domain import CudaBackend
+    be = CudaBackend.__new__(CudaBackend)          # the packing calls need the device only, no model
+    be.device = torch.device("cuda", 0)
+    g = torch.Generator(device="cpu").manual_seed(11)
+    n = 1000
+    tensors = [torch.randn(n, w, generator=g).cuda() for w in (128, 24, 2)]
+    idx = torch.randint(0, n, (313,), generator=g).cuda()
+    buf = be.pack_rows(tensors, idx)
+    assert torch.equal(buf, torch.cat([t[idx] for t in tensors], 1))
+    dst = [torch.zeros_like(t) for t in tensors]
+    rows = torch.randperm(n, generator=g)[:313].cuda()
+    be.unpack_rows(dst, rows, buf)
+    o = 0
+    for t, d in zip(tensors, dst):
+        want = torch.zeros_like(t)
+        want[rows] = buf[:, o:o + t.shape[1]]
+        assert torch.equal(d, want)
+        o += t.shape[1]
+    empty = torch.empty(0, dtype=torch.int64, device="cuda")
+    assert be.pack_rows(tensors, empty).shape == (0, 154)
+    be.unpack_rows(dst, empty, be.pack_rows(tensors, empty))

@@ -2,7 +2,7 @@
 the attention kernels, the dense blocks and the first layer gives the same energies and forces as the default build-up.
 
   SO3LR_B200_ATTENTION = tcf | mma | simt  (default: tiled tcgen05 kernels in both directions)
-  SO3LR_B200_DENSE     = mma | simt        (default: tcgen05 post-attention blocks, mma.sync heads)
+  SO3LR_B200_DENSE     = mma | simt        (default: tcgen05 post-attention blocks and heads)
   SO3LR_B200_LAYER0    = generic           (default: per-element-pair tables)
 """
 import os
