@@ -841,7 +841,7 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
 #ifdef SO3LR_TC_TIMING
   long long bph[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   long long bc0 = clock64();
-#define BW_MARK(k) do { if (dbg && tid == 32) { const long long c = clock64(); bph[k] += c - bc0; bc0 = c; } } while (0)
+#define BW_MARK(k) do { if (dbg && (tid & 31) == 0) { const long long c = clock64(); bph[k] += c - bc0; bc0 = c; } } while (0)
 #else
 #define BW_MARK(k) do { } while (0)
 #endif
@@ -999,7 +999,7 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
       if (!__syncthreads_and(done)) { failed = true; break; }
       tc_fence_after();
       BW_MARK(5);
-      // ---- per edge: radial derivative (even terms: threads 0..127, odd terms: 128..255), spherical hidden layer (256..383) ----
+      // ---- per edge: radial derivative (even terms: threads 0..127, odd terms: 128..255), spherical hidden layer (all four threads of a row) ----
       {
         const int row = tid & 127, role = tid >> 7;
         float* rp = rec + row * kBwRec;
@@ -1023,21 +1023,26 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
             up = uc; uc = un;
           }
           rp[role ? 35 : 32] += acc * dtdr;
-        } else if (role == 2) {
+        }
+        // spherical hidden layer, reverse: the four threads of a row take eight hidden units each and add their shares of the
+        // invariants' cotangents to the record
+        {
           float v[32];
           tmem_ld32_combined(lane_base + 64, v);
           const float4 s4 = ld4(rp + 4);
           float ds0 = 0.f, ds1 = 0.f, ds2 = 0.f, ds3 = 0.f;
 #pragma unroll
-          for (int c = 0; c < 32; ++c) {
+          for (int c8 = 0; c8 < 8; ++c8) {
+            const int c = 8 * role + c8;
             const float* p = sph + (f * 32 + c) * 8;
             const float4 k = ld4(p);
             const float z = fmaf(s4.x, k.x, fmaf(s4.y, k.y, fmaf(s4.z, k.z, fmaf(s4.w, k.w, p[4]))));
-            const float dz = v[c] * dsilu_f(z);
+            const float sg = __fdividef(1.f, 1.f + __expf(-z));
+            const float vc = role == 0 ? v[c8] : (role == 1 ? v[8 + c8] : (role == 2 ? v[16 + c8] : v[24 + c8]));
+            const float dz = vc * sg * (1.f + z * (1.f - sg));
             ds0 = fmaf(dz, k.x, ds0); ds1 = fmaf(dz, k.y, ds1); ds2 = fmaf(dz, k.z, ds2); ds3 = fmaf(dz, k.w, ds3);
           }
-          const float4 o = ld4(rp + 8);
-          st4(rp + 8, make_float4(o.x + ds0, o.y + ds1, o.z + ds2, o.w + ds3));
+          atomicAdd(rp + 8, ds0); atomicAdd(rp + 9, ds1); atomicAdd(rp + 10, ds2); atomicAdd(rp + 11, ds3);
         }
       }
       tc_fence_before();
@@ -1094,6 +1099,7 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
   }
 #ifdef SO3LR_TC_TIMING
   if (dbg && tid == 32 && blockIdx.x == 0) { for (int q = 0; q < 8; ++q) dbg[16 + q] = bph[q]; dbg[24] = tile1 - tile0; }
+  if (dbg && (tid & 31) == 0 && blockIdx.x == 0) { for (int q = 0; q < 8; ++q) dbg[32 + 8 * warp + q] = bph[q]; }
 #endif
   if (failed && tid == 0) atomicExch(err, 1);
   tc_fence_before();
@@ -1168,7 +1174,7 @@ static long long* tc_debug_buffer() {
   static long long* buf = [] {
     long long* p = nullptr;
     if (std::getenv("SO3LR_B200_TC_DEBUG")) {
-      cudaMalloc((void**)&p, 32 * sizeof(long long)); cudaMemset(p, 0, 32 * sizeof(long long));
+      cudaMalloc((void**)&p, 160 * sizeof(long long)); cudaMemset(p, 0, 160 * sizeof(long long));
     }
     return p;
   }();
@@ -1177,11 +1183,17 @@ static long long* tc_debug_buffer() {
 void tc_debug_print() {
   long long* d = tc_debug_buffer();
   if (!d) return;
-  long long h[32];
+  long long h[160];
   cudaDeviceSynchronize();
   cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost);
   if (h[24]) std::fprintf(stderr, "tc bwd phases (cycles per tile, %lld tiles): prep %lld | sync %lld | mma1 %lld | sync+tmem->tile %lld | edge loop %lld | sync+mma2 %lld | epilogue %lld | phase C %lld\n",
                h[24], h[16] / h[24], h[17] / h[24], h[18] / h[24], h[19] / h[24], h[20] / h[24], h[21] / h[24], h[22] / h[24], h[23] / h[24]);
+  if (h[24])
+    for (int w = 0; w < 16; ++w) {
+      std::fprintf(stderr, "  bwd warp %2d:", w);
+      for (int q = 0; q < 8; ++q) std::fprintf(stderr, " %6lld", h[32 + 8 * w + q] / h[24]);
+      std::fprintf(stderr, "\n");
+    }
   std::fprintf(stderr, "tc fwd mma issue %lld wait %lld cycles per tile\n", h[9] / (h[8] ? h[8] : 1), h[10] / (h[8] ? h[8] : 1));
   std::fprintf(stderr, "tc fwd phases (cycles per tile, %lld tiles): prep %lld | sync %lld | mma+wait %lld | tmem0 %lld | loop0 %lld | sync %lld | tmem1 %lld | loop1 %lld\n",
                h[8], h[0] / (h[8] ? h[8] : 1), h[1] / (h[8] ? h[8] : 1), h[2] / (h[8] ? h[8] : 1), h[3] / (h[8] ? h[8] : 1), h[4] / (h[8] ? h[8] : 1),
