@@ -272,11 +272,15 @@ __device__ __noinline__ void issue_forward_mma(uint32_t tmem, uint32_t a_hi, uin
   const uint64_t dc = desc_base(4096, 128) + (img >> 4), dcl = dc + (32768 >> 4);
   const uint64_t dk = desc_base(2048, 128) + ((img + 65536) >> 4), dkl = dk + (16384 >> 4);
   const uint32_t id256 = make_idesc(256, 0), id128 = make_idesc(128, 0);
+  // K steps 1 and 3 hold the Chebyshev terms of order 32..63 (even terms, then odd terms, 32 columns each).  Their coefficients
+  // are below 2^-12 of the filter scale (the expansion converges geometrically), so their hi * lo cross terms are below 2^-23 of
+  // it, like the lo * lo terms that are dropped everywhere: those steps issue the hi * hi product only.
 #pragma unroll
   for (int ks = 0; ks < 4; ++ks) {
     const uint64_t ah = da + ks * (2 * kLboA >> 4), al = dal + ks * (2 * kLboA >> 4);
     const uint64_t bh = dc + ks * (2 * 4096 >> 4), bl = dcl + ks * (2 * 4096 >> 4);
     umma(tmem, ah, bh, id256, ks > 0);
+    if (ks == 1 || ks == 3) continue;
     umma(tmem + 256, ah, bl, id256, ks > 0);
     umma(tmem + 256, al, bh, id256, 1);
   }
@@ -310,6 +314,7 @@ __device__ __noinline__ void issue_filter_mma(uint32_t tmem, uint32_t a_hi, uint
     const uint64_t ah = da + chunk * (kLboA >> 4), al = dal + chunk * (kLboA >> 4);
     const uint64_t bh = db + ks * (2 * 128 >> 4), bl = dbl + ks * (2 * 128 >> 4);
     umma(d_main, ah, bh, id128, ks > 0);
+    if (ks == 1 || ks == 3) continue;      // Chebyshev terms of order >= 32: no cross terms (see issue_forward_mma)
     umma(d_cross, ah, bl, id128, ks > 0);
     umma(d_cross, al, bh, id128, 1);
   }
@@ -458,7 +463,7 @@ __global__ void __launch_bounds__(kFwThreads, 1) attn_fwd_tc_kernel(const unsign
 #ifdef SO3LR_TC_TIMING
   long long tph[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   long long tc0 = clock64();
-#define TC_MARK(k) do { if (dbg && tid == 32) { const long long c = clock64(); tph[k] += c - tc0; tc0 = c; } } while (0)
+#define TC_MARK(k) do { if (dbg && (tid & 31) == 0) { const long long c = clock64(); tph[k] += c - tc0; tc0 = c; } } while (0)
 #else
 #define TC_MARK(k) do { } while (0)
 #endif
@@ -608,6 +613,7 @@ __global__ void __launch_bounds__(kFwThreads, 1) attn_fwd_tc_kernel(const unsign
   }
 #ifdef SO3LR_TC_TIMING
   if (dbg && tid == 32 && blockIdx.x == 0) { for (int q = 0; q < 8; ++q) dbg[q] = tph[q]; dbg[8] = tile1 - tile0; }
+  if (dbg && (tid & 31) == 0 && blockIdx.x == 0) { for (int q = 0; q < 8; ++q) dbg[160 + 8 * warp + q] = tph[q]; }
 #endif
   cp_async_wait_all();
   tc_fence_before();
@@ -1174,7 +1180,7 @@ static long long* tc_debug_buffer() {
   static long long* buf = [] {
     long long* p = nullptr;
     if (std::getenv("SO3LR_B200_TC_DEBUG")) {
-      cudaMalloc((void**)&p, 160 * sizeof(long long)); cudaMemset(p, 0, 160 * sizeof(long long));
+      cudaMalloc((void**)&p, 288 * sizeof(long long)); cudaMemset(p, 0, 288 * sizeof(long long));
     }
     return p;
   }();
@@ -1183,7 +1189,7 @@ static long long* tc_debug_buffer() {
 void tc_debug_print() {
   long long* d = tc_debug_buffer();
   if (!d) return;
-  long long h[160];
+  long long h[288];
   cudaDeviceSynchronize();
   cudaMemcpy(h, d, sizeof(h), cudaMemcpyDeviceToHost);
   if (h[24]) std::fprintf(stderr, "tc bwd phases (cycles per tile, %lld tiles): prep %lld | sync %lld | mma1 %lld | sync+tmem->tile %lld | edge loop %lld | sync+mma2 %lld | epilogue %lld | phase C %lld\n",
@@ -1192,6 +1198,12 @@ void tc_debug_print() {
     for (int w = 0; w < 16; ++w) {
       std::fprintf(stderr, "  bwd warp %2d:", w);
       for (int q = 0; q < 8; ++q) std::fprintf(stderr, " %6lld", h[32 + 8 * w + q] / h[24]);
+      std::fprintf(stderr, "\n");
+    }
+  if (h[8])
+    for (int w = 0; w < 16; ++w) {
+      std::fprintf(stderr, "  fwd warp %2d:", w);
+      for (int q = 0; q < 8; ++q) std::fprintf(stderr, " %6lld", h[160 + 8 * w + q] / h[8]);
       std::fprintf(stderr, "\n");
     }
   std::fprintf(stderr, "tc fwd mma issue %lld wait %lld cycles per tile\n", h[9] / (h[8] ? h[8] : 1), h[10] / (h[8] ? h[8] : 1));
