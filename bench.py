@@ -183,8 +183,8 @@ def ncu_traffic(group, n_atoms):
 TRAFFIC_SOURCE = "ncu capture of the same kernel on water_98k (98,304 atoms), scaled by the atom count"
 
 # FP16 MMA work of the tiled attention kernels per tile of 128 list entries (M = 128, K = 16 per instruction, 2 FLOPs per MAC):
-# forward 12 instructions with N = 256 and 12 with N = 128; reverse 36 with N = 128 and 48 with N = 96
-ATTN_TILE_FLOPS = {"attn_fwd": 2.0 * 128 * 16 * (12 * 256 + 12 * 128), "attn_bwd": 2.0 * 128 * 16 * (36 * 128 + 48 * 96)}
+# forward 8 instructions with N = 256 and 12 with N = 128; reverse 28 with N = 128 and 48 with N = 96
+ATTN_TILE_FLOPS = {"attn_fwd": 2.0 * 128 * 16 * (8 * 256 + 12 * 128), "attn_bwd": 2.0 * 128 * 16 * (28 * 128 + 48 * 96)}
 
 
 def tensor_flops(group, N, E=0):
