@@ -102,16 +102,6 @@ __device__ __forceinline__ void store_chunk(unsigned char* a_hi, int chunk, int 
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-// shared-memory matrix descriptor, no swizzle: lbo = bytes between core matrices along K, sbo = bytes between core matrices
-// along M / N (both majors), descriptor version 1
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
-  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
-  d |= (uint64_t)1 << 46;
-  return d;
-}
 // instruction descriptor, kind::f16: FP16 operands, FP32 accumulator, A K-major, B K-major or MN-major, M = 128
 __device__ __forceinline__ uint32_t make_idesc(int n, int b_mn_major) {
   return (1u << 4) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TE >> 4) << 24);
@@ -214,11 +204,6 @@ __device__ __forceinline__ void store_chebyshev_half(unsigned char* a_hi, int ro
     store_chunk(a_hi, 4 * odd + c, row, v);
   }
 }
-// all 64 terms by one thread
-__device__ __forceinline__ void store_chebyshev(unsigned char* a_hi, int row, float r, bool valid) {
-  store_chebyshev_half(a_hi, row, r, valid, 0);
-  store_chebyshev_half(a_hi, row, r, valid, 1);
-}
 // hidden layer of spherical filter f into chunks 8 + 4 f .. 11 + 4 f
 __device__ __forceinline__ void store_spherical_hidden_f(unsigned char* a_hi, int row, const float* s, const float* sph8, int f) {
   // sph8: per (filter, hidden unit) eight floats: the four first-layer weights, the bias, padding
@@ -235,24 +220,6 @@ __device__ __forceinline__ void store_spherical_hidden_f(unsigned char* a_hi, in
     store_chunk(a_hi, 8 + 4 * f + c8, row, v);
   }
 }
-// hidden layer of both spherical filters, hs_f = silu(s * k1w_f + b_f), into chunks 8..15; sph = k1w [2][4][32] | b [2][32]
-__device__ __forceinline__ void store_spherical_hidden(unsigned char* a_hi, int row, const float* s, const float* sph) {
-#pragma unroll
-  for (int f = 0; f < 2; ++f)
-#pragma unroll
-    for (int c8 = 0; c8 < 4; ++c8) {
-      float v[8];
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const int c = 8 * c8 + q;
-        float z = sph[256 + f * 32 + c];
-#pragma unroll
-        for (int l = 0; l < 4; ++l) z = fmaf(s[l], sph[f * 128 + l * 32 + c], z);
-        v[q] = silu_f(z);
-      }
-      store_chunk(a_hi, 8 + 4 * f + c8, row, v);
-    }
-}
 
 // Descriptors differ only in their start-address field (bits 0..13, in units of 16 bytes): desc(addr) = base + (addr >> 4).
 // The issuing thread keeps everything in registers -- shared-memory loads inside the issue loop wait behind the operand
@@ -260,7 +227,6 @@ __device__ __forceinline__ void store_spherical_hidden(unsigned char* a_hi, int 
 __device__ __forceinline__ uint64_t desc_base(uint32_t lbo, uint32_t sbo) {
   return ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) | ((uint64_t)1 << 46);
 }
-constexpr int kFilterOps = 18;     // per filter: 4 K-steps of Chebyshev terms + 2 of the spherical hidden layer, 3 MMAs each
 
 // Forward kernel, K-major weight image (rows = output features, 8 consecutive K entries per 16 bytes; the core matrices of
 // one K chunk are contiguous over the rows, the layout the tensor cores fetch fastest):
@@ -328,20 +294,6 @@ __device__ __forceinline__ void tmem_to_tile(uint32_t tmem, int f, int warp, int
   float* p = wt + (32 * q + lane) * kWStride + col;
 #pragma unroll
   for (int k = 0; k < 32; k += 4) st4(p + k, make_float4(v[k], v[k + 1], v[k + 2], v[k + 3]));
-}
-// filter f of the 32 rows of this warp's TMEM lane quadrant into the shared tile (tile row = edge - row0, 128 columns);
-// warps w and w + 4 share a quadrant and take 64 columns each
-__device__ __forceinline__ void tmem_to_tile(uint32_t tmem, int f, int warp, int lane, int row0, float* wt) {
-  const int q = warp & 3, ch = warp >> 2;
-#pragma unroll
-  for (int c0 = 0; c0 < 64; c0 += 32) {
-    float v[32];
-    const int col = ch * 64 + c0;
-    tmem_ld32_combined(tmem + ((uint32_t)(32 * q) << 16) + 128 * f + col, v);
-    float* p = wt + (32 * q + lane - row0) * kWStride + col;
-#pragma unroll
-    for (int k = 0; k < 32; k += 4) st4(p + k, make_float4(v[k], v[k + 1], v[k + 2], v[k + 3]));
-  }
 }
 
 // ------------------------------------------------------------------------------------------------------------------

@@ -50,10 +50,8 @@ constexpr float kLoScale = 2048.f, kLoInv = 1.f / 2048.f;
 constexpr int kTmemCols = 512;
 constexpr int kColCross = 256;         // cross accumulators
 constexpr int kColX = 128;             // residual stream slot (free while N <= 128)
-constexpr int kColY = 384;             // second slot
 constexpr int kWaitSpins = 1 << 22;
 constexpr int kProjBlockBytes = 16384; // [32 x 128] hi + lo, or four [32 x 32] hi + lo
-constexpr int kProjTBlockBytes = 4096; // [32 x 32] hi + lo
 
 __device__ __forceinline__ float inv_weight(int l) {
   return l == 0 ? 0.5773502691896258f : (l == 1 ? 0.4472135954999579f : (l == 2 ? 0.3779644730092272f : 0.3333333333333333f));
