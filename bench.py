@@ -227,6 +227,8 @@ def run_b200(args, rank, world, local_rank):
         return run_domain(args, rank, world, local_rank)
 
     Z, R, cell, what = make_workload(args.workload)
+    if args.entry == "graph_eval":
+        return run_graph_eval(args, Z, R, cell, what, local_rank)
     V, m = W.maxwell_boltzmann(Z, 300.0, seed + 1)
     N = len(Z)
     skin = args.skin
@@ -343,6 +345,89 @@ def run_b200(args, rank, world, local_rank):
                                      else "inputs smaller than L2; no flush"),
                        "ns_per_day": round(args.steps / (ms * 1e-3) * 0.0432, 3)},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu}
+    print(json.dumps(line), flush=True)
+
+
+def run_graph_eval(args, Z, R, cell, what, local_rank):
+    """One step = one energy + force evaluation through so3lr_b200_system_graph_eval: the lists (no skin) are built once, every
+    step forms the displacement vectors from the positions, calls the graph-level entry point and transposes the gathers
+    (forces from the per-entry cotangents), which is the work of jax.grad around potential(graph) in the reference."""
+    import torch
+    from so3lr_b200.engine import System
+    dev = torch.device("cuda", local_rank)
+    N = len(Z)
+    sysm = System(Z, cell, cutoff_lr=12.0, damping=2.0, lr_format="sparse", device=local_rank)
+    Rd = torch.tensor(R, dtype=torch.float32, device=dev)
+    cellt = torch.tensor(np.asarray(cell, dtype=np.float32), device=dev)
+    inv = torch.linalg.inv(cellt)
+
+    def lists(which):
+        _, cnt, _ = sysm.neighbor_list(Rd, which, 1)
+        idx, cnt, _ = sysm.neighbor_list(Rd, which, cnt)
+        return idx[0].contiguous(), idx[1].contiguous(), idx[0].long(), idx[1].long()
+
+    i32, j32, i, j = lists(0)
+    il32, jl32, il, jl = lists(1)
+
+    def step(Rt):
+        def disp(a, b):
+            d = Rt[b] - Rt[a]
+            f = d @ inv
+            return (f - torch.round(f)) @ cellt
+        o = sysm.graph_eval(i32, j32, disp(i, j), il32, jl32, disp(il, jl))
+        F = torch.zeros_like(Rt)
+        F.index_add_(0, i, o["g_edges"]); F.index_add_(0, j, -o["g_edges"])
+        F.index_add_(0, il, o["g_edges_lr"]); F.index_add_(0, jl, -o["g_edges_lr"])
+        return o["e_atom"].sum(dtype=torch.float64), F
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for _ in range(args.warmup):
+        step(Rd)
+    torch.cuda.synchronize()
+    st0 = sysm.stats()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    sampler.begin()
+    ev[0].record()
+    for _ in range(args.steps):
+        step(Rd)
+    ev[1].record()
+    torch.cuda.synchronize()
+    sampler.end()
+    clocks = sampler.stop()
+    ms = ev[0].elapsed_time(ev[1])
+    launches = sysm.stats()["launches"] - st0["launches"]
+    sysm.profile(True)
+    for _ in range(args.steps):
+        step(Rd)
+    prof = sysm.profile_read()
+    sysm.profile(False)
+    groups = {k: round(v[0] / args.steps, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1][0]) if v[1] > 0}
+    # end to end: positions from pinned host memory every step, forces and energy back
+    Rh = Rd.cpu().pin_memory()
+    Fh = torch.empty_like(Rh).pin_memory()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        E, F = step(Rh.to(dev, non_blocking=True))
+        Fh.copy_(F, non_blocking=True)
+        float(E)
+    torch.cuda.synchronize()
+    t_e2e = time.perf_counter() - t0
+    line = {"metric": METRIC, "value": round(N * args.steps / (ms * 1e-3), 1), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": f"{what}, cutoffs 4.5/12 A, no skin; a step = one energy + force evaluation through the graph-level call "
+                                   "(so3lr_b200_system_graph_eval) on prebuilt lists, displacement vectors and force scatter included",
+                       "entry": "graph_eval", "atoms": N, "sr_list_edges": int(i.numel()), "lr_list_pairs": int(il.numel()),
+                       "l2_policy": "inputs larger than L2" if N * 18e3 > 126e6 else "inputs smaller than L2; no flush"},
+            "e2e": {"value": round(N * args.steps / t_e2e, 1), "unit": UNIT, "h2d_bytes_per_step": N * 12, "d2h_bytes_per_step": N * 12 + 8,
+                    "ms_per_step": round(1e3 * t_e2e / args.steps, 3)},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "roofline": {"kernel": max(groups, key=groups.get), "bound": "hbm", "achieved": None, "peak": _peaks()[0], "unit": "GB/s", "frac": None,
+                         "traffic": None, "groups_ms_per_step": groups,
+                         "note": "kernel groups of the graph-level call; the roofline entries of the default run describe the same kernels"},
+            "cpu_baseline": None}
     print(json.dumps(line), flush=True)
 
 
@@ -641,6 +726,9 @@ def main():
     ap.add_argument("--ensemble", default=None, choices=["nve", "nvt", "npt"], help="step body (default: the one the workload is posed with)")
     ap.add_argument("--cpu-molecules", type=int, default=1024, help="molecules in the CPU-baseline sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--entry", default="md", choices=["md", "graph_eval"],
+                    help="md: MD steps through the fused positions -> forces call (default); graph_eval: energy + force evaluations "
+                         "through the graph-level call on prebuilt lists (the call a jax.ffi binding of potential(graph) uses), one GPU")
     ap.add_argument("--traffic", type=float, default=None, help="measured DRAM bytes per launch of the roofline kernel (overrides the built-in capture)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

@@ -164,7 +164,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_bwd_kernel(LayerDev L, int n,
                                                               const float* __restrict__ qkv, const float* __restrict__ ev_in,
                                                               const float* __restrict__ g_xa, const float* __restrict__ gev1,
                                                               float* __restrict__ g_qkv, float* __restrict__ gev_in,
-                                                              float* __restrict__ g_dR) {
+                                                              float* __restrict__ g_dR, const int* __restrict__ run_if_set) {
+  if (run_if_set && *run_if_set == 0) return;      // another kernel takes this launch's work
   extern __shared__ float sm[];
   float* K2 = sm;                     // [2][32][128]
   float* K2T = sm + 2 * 32 * 128;     // [2][128][32]
@@ -345,13 +346,13 @@ void launch_attn_fwd(cudaStream_t s, const LayerDev& L, int n, const int* row_pt
 
 void launch_attn_bwd(cudaStream_t s, const LayerDev& L, int n, const int* row_ptr, const int* nbr_j, const float* dR,
                      const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv,
-                     float* gev_in, float* g_dR, int first_layer) {
+                     float* gev_in, float* g_dR, int first_layer, const int* run_if_set) {
   if (n <= 0) return;
   int blocks = (n + WARPS - 1) / WARPS;
   if (first_layer)
-    { attn_bwd_kernel<true><<<blocks, WARPS * 32, 0, s>>>(L, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, g_dR); count_launch(); }
+    { attn_bwd_kernel<true><<<blocks, WARPS * 32, 0, s>>>(L, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, g_dR, nullptr); count_launch(); }
   else
-    { attn_bwd_kernel<false><<<blocks, WARPS * 32, kSmemBwd, s>>>(L, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, g_dR); count_launch(); }
+    { attn_bwd_kernel<false><<<blocks, WARPS * 32, kSmemBwd, s>>>(L, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, g_dR, run_if_set); count_launch(); }
 }
 
 }  // namespace so3lr

@@ -307,7 +307,7 @@ template <bool FILL>
 __global__ void __launch_bounds__(256) compact_rows_kernel(int n_rows, int n, const int* __restrict__ row_ptr, const int* __restrict__ nbr_j,
                                                            const float* __restrict__ dR, int* __restrict__ vcount,
                                                            const int* __restrict__ vrow_ptr, int* __restrict__ ve_i, int* __restrict__ ve_j,
-                                                           float4* __restrict__ ve_d) {
+                                                           float4* __restrict__ ve_d, int* __restrict__ ve_orig) {
   const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (i >= n_rows) return;
@@ -329,10 +329,30 @@ __global__ void __launch_bounds__(256) compact_rows_kernel(int n_rows, int n, co
       const int p = base + count + __popc(m & ((1u << lane) - 1u));
       ve_i[p] = i; ve_j[p] = j;
       ve_d[p] = make_float4(dx, dy, dz, sqrtf(r2));
+      if (ve_orig) ve_orig[p] = e;
     }
     count += __popc(m);
   }
   if (!FILL && lane == 0) vcount[i] = count;
+}
+// every compacted entry (i <- j, d) looks for (j <- i, -d) in row j; a miss sets *asym
+__global__ void __launch_bounds__(256) check_symmetric_kernel(int n_rows, const int* __restrict__ vrow_ptr, const int* __restrict__ ve_i,
+                                                              const int* __restrict__ ve_j, const float4* __restrict__ ve_d, int* asym) {
+  const long long n_entries = vrow_ptr[n_rows];
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < n_entries; e += (long long)gridDim.x * blockDim.x) {
+    const int i = ve_i[e], j = ve_j[e];
+    const float4 d = ve_d[e];
+    const float tol = 1e-5f * d.w + 1e-6f;
+    bool found = false;
+    if (j >= 0 && j < n_rows) {
+      for (int p = vrow_ptr[j]; p < vrow_ptr[j + 1] && !found; ++p) {
+        if (ve_j[p] != i) continue;
+        const float4 q = ve_d[p];
+        found = fabsf(q.x + d.x) <= tol && fabsf(q.y + d.y) <= tol && fabsf(q.z + d.z) <= tol;
+      }
+    }
+    if (!found) { atomicExch(asym, 1); return; }
+  }
 }
 __global__ void close_scan_kernel(int n_rows, const int* __restrict__ vcount, int* __restrict__ vrow_ptr) {
   if (threadIdx.x == 0 && blockIdx.x == 0) vrow_ptr[n_rows] = n_rows > 0 ? vrow_ptr[n_rows - 1] + vcount[n_rows - 1] : 0;
@@ -749,6 +769,9 @@ __device__ __forceinline__ void reverse_edges4(const RevLoads& L, float* rec, co
 // prefetched across the barriers), dw into the A operand; (4) per filter: MMA chain [dPhi | dhs] = dw [C^T | K2^T], then per
 // edge the radial derivative and the spherical hidden layer (the angular part of the force is formed beneath the last chain);
 // (5) force on the receiver, cotangent of ev.
+// PER_ENTRY (caller-supplied lists): `F` is the gradient with respect to the source list's displacement vectors (3 floats per
+// source entry, added to), `ve_orig` maps compacted entries to source entries, and the launch returns at once when *gate != 0.
+template <bool PER_ENTRY>
 __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsigned char* __restrict__ img_g, const float* __restrict__ sph1_k,
                                                                     const float* __restrict__ sph1_b, int n_recv,
                                                                     const int* __restrict__ vrow_ptr, const int* __restrict__ ve_i,
@@ -757,7 +780,9 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
                                                                     const float* __restrict__ g_xa, const float* __restrict__ gev1,
                                                                     float* __restrict__ g_qkv, float* __restrict__ gev_in,
                                                                     float* __restrict__ F, float* __restrict__ virial,
-                                                                    int* __restrict__ err, long long* __restrict__ dbg) {
+                                                                    int* __restrict__ err, long long* __restrict__ dbg,
+                                                                    const int* __restrict__ ve_orig, const int* __restrict__ gate) {
+  if (PER_ENTRY && gate && *gate != 0) return;
   extern __shared__ __align__(1024) unsigned char smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float* rec = reinterpret_cast<float*>(smem + kOffBwRec);
@@ -1024,6 +1049,15 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
         atomicAdd(w + 3, 0.5f * (wy * fsz + wz * fsy)); atomicAdd(w + 4, 0.5f * (wx * fsz + wz * fsx));
         atomicAdd(w + 5, 0.5f * (wx * fsy + wy * fsx));
       }
+      if (PER_ENTRY) {
+        // half of the pair's force on the receiver goes to this entry of the source list; the reversed entry, processed at the
+        // other atom, receives the other half with the opposite sign
+        if (on) {
+          const long long e = tile * TE + tid;
+          float* g = F + 3 * (size_t)ve_orig[e];
+          g[0] += 0.5f * fsx; g[1] += 0.5f * fsy; g[2] += 0.5f * fsz;
+        }
+      } else {
       // the rows of a tile are sorted by receiver: sum each run of equal receivers inside the warp (segmented scan) and let its
       // last lane add the total, instead of up to 32 additions to one address
 #pragma unroll
@@ -1035,6 +1069,7 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
       const int inext = __shfl_down_sync(0xffffffffu, i, 1);
       if (on && (lane == 31 || inext != i)) {
         atomicAdd(F + 3 * (size_t)i, fsx); atomicAdd(F + 3 * (size_t)i + 1, fsy); atomicAdd(F + 3 * (size_t)i + 2, fsz);
+      }
       }
     }
     {
@@ -1072,7 +1107,8 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
 // ------------------------------------------------------------------------------------------------------------------
 int configure_attention_tc_kernels() {
   SO3LR_CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemFwd));
-  SO3LR_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBwd));
+  SO3LR_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBwd));
+  SO3LR_CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBwd));
   return kOk;
 }
 
@@ -1108,20 +1144,26 @@ int valid_edges_reserve(ValidEdges* V, int n_rows, long long capacity) {
 }
 
 void valid_edges_free(ValidEdges* V) {
-  cudaFree(V->row_ptr); cudaFree(V->count); cudaFree(V->i); cudaFree(V->j); cudaFree(V->d); cudaFree(V->cub_tmp);
+  cudaFree(V->row_ptr); cudaFree(V->count); cudaFree(V->i); cudaFree(V->j); cudaFree(V->d); cudaFree(V->orig); cudaFree(V->cub_tmp);
   *V = ValidEdges{};
 }
 
-int valid_edges_build(ValidEdges* V, cudaStream_t s, int n_rows, int n, const int* row_ptr, const int* nbr_j, const float* dR) {
+int valid_edges_build(ValidEdges* V, cudaStream_t s, int n_rows, int n, const int* row_ptr, const int* nbr_j, const float* dR, bool want_orig) {
   if (n_rows <= 0) return kOk;
   if (n_rows + 1 > V->row_cap) return kInvalidArgument;
+  if (want_orig && V->orig_cap < V->capacity) {
+    if (V->orig) cudaFree(V->orig);
+    V->orig = nullptr;
+    SO3LR_CUDA_CHECK(cudaMalloc((void**)&V->orig, (size_t)V->capacity * sizeof(int)));
+    V->orig_cap = V->capacity;
+  }
   const int blocks = (n_rows + 7) / 8;
-  { compact_rows_kernel<false><<<blocks, 256, 0, s>>>(n_rows, n, row_ptr, nbr_j, dR, V->count, nullptr, nullptr, nullptr, nullptr); count_launch(); }
+  { compact_rows_kernel<false><<<blocks, 256, 0, s>>>(n_rows, n, row_ptr, nbr_j, dR, V->count, nullptr, nullptr, nullptr, nullptr, nullptr); count_launch(); }
   size_t tmp = V->cub_bytes;
   cub::DeviceScan::ExclusiveSum(V->cub_tmp, tmp, V->count, V->row_ptr, n_rows, s);
   count_launch(2);
   { close_scan_kernel<<<1, 32, 0, s>>>(n_rows, V->count, V->row_ptr); count_launch(); }
-  { compact_rows_kernel<true><<<blocks, 256, 0, s>>>(n_rows, n, row_ptr, nbr_j, dR, nullptr, V->row_ptr, V->i, V->j, V->d); count_launch(); }
+  { compact_rows_kernel<true><<<blocks, 256, 0, s>>>(n_rows, n, row_ptr, nbr_j, dR, nullptr, V->row_ptr, V->i, V->j, V->d, want_orig ? V->orig : nullptr); count_launch(); }
   SO3LR_CUDA_CHECK(cudaGetLastError());
   V->n_rows = n_rows;
   return kOk;
@@ -1181,9 +1223,23 @@ int launch_attn_bwd_tc(cudaStream_t s, const LayerDev& L, const ValidEdges& V, i
   // the kernel adds into the receivers' rows: cotangents of q/k/v start at zero, that of ev at the skip term
   SO3LR_CUDA_CHECK(cudaMemsetAsync(g_qkv, 0, (size_t)n_recv * kProj * sizeof(float), s));
   SO3LR_CUDA_CHECK(cudaMemcpyAsync(gev_in, gev1, (size_t)n_recv * kMTot * sizeof(float), cudaMemcpyDeviceToDevice, s));
-  { attn_bwd_tc_kernel<<<sm_count(), kBwThreads, kSmemBwd, s>>>(L.tc_img, L.sph1_k, L.sph1_b, n_recv, V.row_ptr, V.i, V.j, V.d, qkv, ev_in, g_xa, gev1, g_qkv,
-                                                       gev_in, F, virial, err, tc_debug_buffer()); count_launch(); }
+  { attn_bwd_tc_kernel<false><<<sm_count(), kBwThreads, kSmemBwd, s>>>(L.tc_img, L.sph1_k, L.sph1_b, n_recv, V.row_ptr, V.i, V.j, V.d, qkv, ev_in, g_xa, gev1,
+                                                              g_qkv, gev_in, F, virial, err, tc_debug_buffer(), nullptr, nullptr); count_launch(); }
   return kOk;
+}
+
+int launch_attn_bwd_tc_graph(cudaStream_t s, const LayerDev& L, const ValidEdges& V, int n_recv, const float* qkv, const float* ev_in,
+                             const float* g_xa, const float* gev1, float* g_qkv, float* gev_in, float* g_dR, int* err, const int* asym) {
+  if (n_recv <= 0) return kOk;
+  if (n_recv > V.n_rows || !V.orig) return kInvalidArgument;
+  { attn_bwd_tc_kernel<true><<<sm_count(), kBwThreads, kSmemBwd, s>>>(L.tc_img, L.sph1_k, L.sph1_b, n_recv, V.row_ptr, V.i, V.j, V.d, qkv, ev_in, g_xa, gev1,
+                                                             g_qkv, gev_in, g_dR, nullptr, err, nullptr, V.orig, asym); count_launch(); }
+  return kOk;
+}
+
+void valid_edges_check_symmetric(const ValidEdges& V, cudaStream_t s, int* asym) {
+  if (V.n_rows <= 0) return;
+  { check_symmetric_kernel<<<sm_count() * 8, 256, 0, s>>>(V.n_rows, V.row_ptr, V.i, V.j, V.d, asym); count_launch(); }
 }
 
 }  // namespace so3lr

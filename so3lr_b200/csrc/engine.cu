@@ -276,7 +276,8 @@ struct so3lr_b200_system {
   ValidEdges ve;                 // its entries inside the cutoff, compacted at every evaluation
   NlistWorkspace* nws = nullptr;
   float* d_Rref = nullptr;
-  int* d_flag = nullptr;   // [0] skin test of the current step, [1] sticky error word of the tensor-core kernels' bounded waits
+  int* d_flag = nullptr;   // [0] skin test of the current step, [1] sticky error word of the tensor-core kernels' bounded waits,
+                           // [2] graph-level call: the caller's list is not symmetric
   int* h_flag = nullptr;   // pinned copy of both
   // deferred skin test: the flags of step k are read by the host at step k + 1 (two pinned slots and an event each), so a
   // step never waits for the device; the trigger distance is lowered by `skin_margin` to cover the extra step
@@ -398,52 +399,6 @@ int rebuild_lists(so3lr_b200_system* S, cudaStream_t st, const float* R_user, bo
 
 // Graph-level evaluation (displacements and lists given by the caller, gradients per edge): scatter kernels with atomics,
 // valid for any list.
-int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, const int* nbr_j, const int* edge_i, long long n_edges,
-                   const int* row_ptr_lr, const int* nbr_j_lr, const float* dR_in, const float* dR_lr_in, float* g_dR,
-                   float* g_dR_lr_out, const float* ge) {
-  const ModelDev& M = S->mctx;
-  const int n = S->n;
-  float* dR = const_cast<float*>(dR_in);
-  fill(st, S->e_zbl, n, 0.f); fill(st, S->e_coul, n, 0.f); fill(st, S->e_disp, n, 0.f);
-  fill(st, S->gq, n, 0.f); fill(st, S->gh, n, 0.f);
-  S->prof.begin(kPGeom, st); launch_sr_geometry_zbl(st, M, S->cell, n, n_edges, edge_i, nbr_j, S->d_Z, nullptr, 1, dR, S->e_zbl, g_dR, ge, nullptr); S->prof.end(st);
-  { int rce = embed_atoms(S, st, n, S->x[0]); if (rce) return rce; }
-  for (int l = 0; l < kNumLayers; ++l) {
-    const LayerDev& L = M.layer[l];
-    S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], n, S->qkv[l]); S->prof.end(st);
-    S->prof.begin(kPAttnFwd, st); launch_attn_fwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]); S->prof.end(st);
-    S->prof.begin(kPPostFwd, st); launch_atom_post_fwd(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1]); S->prof.end(st);
-  }
-  S->prof.begin(kPHeads, st); launch_heads_fwd(st, M, n, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv); S->prof.end(st);
-  launch_charge_conserve(st, S->n_graphs, S->d_graph_start, S->q_raw, S->d_total_charge, S->hv, S->q, S->h, S->n, S->red_scratch);
-  S->prof.begin(kPPairLr, st);
-  launch_pair_lr(st, S->lr, S->cell, n, row_ptr_lr, nbr_j_lr, S->d_Z, nullptr, S->q, S->h, 1, dR_lr_in, g_dR_lr_out, nullptr, nullptr, S->gq,
-                 S->gh, S->e_coul, S->e_disp, ge);
-  S->prof.end(st);
-  { combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
-  launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw, S->n, S->red_scratch);
-  S->prof.begin(kPHeads, st); launch_heads_bwd(st, M, n, S->d_Z, S->ze, S->zq, S->zh, S->hv, ge ? ge : S->ones, S->gq_raw, S->gh, S->g4); S->prof.end(st);
-  float* gev2 = S->gev_a;
-  float* gev_in = S->gev_b;
-  fill(st, gev2, (size_t)n * kMTot, 0.f);
-  for (int l = kNumLayers - 1; l >= 0; --l) {
-    const LayerDev& L = M.layer[l];
-    S->prof.begin(kPPostBwd, st); launch_atom_post_bwd(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, gev2, S->g_xa, S->gev1); S->prof.end(st);
-    if (l > 0) {
-      SO3LR_CUDA_CHECK(cudaMemcpyAsync(gev_in, S->gev1, (size_t)n * kMTot * sizeof(float), cudaMemcpyDeviceToDevice, st));
-      fill(st, S->g_qkv, (size_t)n * kProj, 0.f);
-      S->prof.begin(kPAttnBwd, st); launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, g_dR, 0); S->prof.end(st);
-      // dL/dx_in = g_xa (skip connection) + projections^T
-      SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)n * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
-      S->prof.begin(kPProjBwd, st); launch_proj_bwd(st, L, S->g_qkv, n, S->g4, 1); S->prof.end(st);
-      float* t = gev2; gev2 = gev_in; gev_in = t;
-    } else {
-      S->prof.begin(kPAttnBwd, st); launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, nullptr, nullptr, g_dR, 1); S->prof.end(st);
-    }
-  }
-  SO3LR_CUDA_CHECK(cudaGetLastError());
-  return kOk;
-}
 
 // Attention kernels of the layers with a spherical filter.  Default: the tiled tcgen05 kernels in both directions.
 // SO3LR_B200_ATTENTION selects the earlier generations for comparison runs (all are covered by tests/test_gpu_modes.py):
@@ -528,6 +483,98 @@ void attn_bwd_dispatch(so3lr_b200_system* S, cudaStream_t st, const LayerDev& L,
   else if (!first_layer && L.has_spherical && use_mma_attention())
     launch_attn_bwd_mma(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F, virial);
   else launch_attn_bwd_sym(st, L, n_recv, n, row_ptr, nbr_j, dR, qkv, ev_in, g_xa, gev1, g_qkv, gev_in, F, first_layer, virial);
+}
+
+// SO3LR_B200_GRAPH=scatter keeps the graph-level call on the first-generation scatter kernels throughout (exact per-entry
+// gradients also for lists that are symmetric)
+bool graph_fast_path() {
+  static const bool v = [] {
+    const char* e = std::getenv("SO3LR_B200_GRAPH");
+    return !(e && std::strcmp(e, "scatter") == 0);
+  }();
+  return v;
+}
+
+// Evaluation on caller-supplied lists and displacement vectors (receiver-sorted).  The per-atom blocks and heads are the ones of
+// the fused path; the attention layers with a spherical filter run the tiled forward kernel on the entries inside the cutoff
+// (it needs the rows sorted by receiver, nothing else).  The tiled reverse kernel evaluates both directions of a pair at the
+// receiver, which presumes that every entry (i <- j, d) has its partner (j <- i, -d) in the list: a check kernel decides
+// that on the device, and of the two reverse kernels launched per layer (tiled, scatter) the one that does not apply
+// returns at once -- no host read, so the call stays enqueue-only.
+int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, const int* nbr_j, const int* edge_i, long long n_edges,
+                   const int* row_ptr_lr, const int* nbr_j_lr, const float* dR_in, const float* dR_lr_in, float* g_dR,
+                   float* g_dR_lr_out, const float* ge) {
+  const ModelDev& M = S->mctx;
+  const int n = S->n;
+  float* dR = const_cast<float*>(dR_in);
+  const bool tiled = graph_fast_path() && attention_mode() == kAttnTc && n_edges > 0;
+  int* asym = S->d_flag + 2;      // 1: some entry has no reversed partner (or the tiled path is off)
+  if (tiled) {
+    int rcv = valid_edges_reserve(&S->ve, S->n_cap, n_edges);
+    if (rcv) return rcv;
+    SO3LR_CUDA_CHECK(cudaMemsetAsync(asym, 0, sizeof(int), st));
+    rcv = valid_edges_build(&S->ve, st, n, n, row_ptr, nbr_j, dR, true);
+    if (rcv) return rcv;
+    valid_edges_check_symmetric(S->ve, st, asym);
+  }
+  fill(st, S->e_zbl, n, 0.f); fill(st, S->e_coul, n, 0.f); fill(st, S->e_disp, n, 0.f);
+  fill(st, S->gq, n, 0.f); fill(st, S->gh, n, 0.f);
+  S->prof.begin(kPGeom, st); launch_sr_geometry_zbl(st, M, S->cell, n, n_edges, edge_i, nbr_j, S->d_Z, nullptr, 1, dR, S->e_zbl, g_dR, ge, nullptr); S->prof.end(st);
+  { int rce = embed_atoms(S, st, n, S->x[0]); if (rce) return rce; }
+  for (int l = 0; l < kNumLayers; ++l) {
+    const LayerDev& L = M.layer[l];
+    S->prof.begin(kPProj, st); launch_proj_fwd(st, L, S->x[l], n, S->qkv[l]); S->prof.end(st);
+    S->prof.begin(kPAttnFwd, st);
+    if (tiled && L.has_spherical) launch_attn_fwd_tc(st, L, S->ve, n, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l], S->d_flag + 1);
+    else launch_attn_fwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->x[l], S->ev[l], S->xa[l], S->ev1[l]);
+    S->prof.end(st);
+    S->prof.begin(kPPostFwd, st);
+    post_fwd_dispatch(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->x[l + 1], S->ev[l + 1], nullptr, nullptr, S->d_flag + 1);
+    S->prof.end(st);
+  }
+  S->prof.begin(kPHeads, st);
+  heads_fwd_dispatch(st, M, n, S->d_Z, S->x[kNumLayers], S->ze, S->zq, S->zh, S->e_nn, S->q_raw, S->hv, S->d_flag + 1);
+  S->prof.end(st);
+  launch_charge_conserve(st, S->n_graphs, S->d_graph_start, S->q_raw, S->d_total_charge, S->hv, S->q, S->h, S->n, S->red_scratch);
+  S->prof.begin(kPPairLr, st);
+  launch_pair_lr(st, S->lr, S->cell, n, row_ptr_lr, nbr_j_lr, S->d_Z, nullptr, S->q, S->h, 1, dR_lr_in, g_dR_lr_out, nullptr, nullptr, S->gq,
+                 S->gh, S->e_coul, S->e_disp, ge);
+  S->prof.end(st);
+  { combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
+  launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw, S->n, S->red_scratch);
+  S->prof.begin(kPHeads, st);
+  heads_bwd_dispatch(st, M, n, S->d_Z, S->ze, S->zq, S->zh, S->hv, ge ? ge : S->ones, S->gq_raw, S->gh, S->g4, S->d_flag + 1);
+  S->prof.end(st);
+  float* gev2 = S->gev_a;
+  float* gev_in = S->gev_b;
+  fill(st, gev2, (size_t)n * kMTot, 0.f);
+  for (int l = kNumLayers - 1; l >= 0; --l) {
+    const LayerDev& L = M.layer[l];
+    S->prof.begin(kPPostBwd, st);
+    post_bwd_dispatch(st, L, n, S->xa[l], S->ev1[l], S->z1[l], S->x3[l], S->gate[l], S->g4, gev2, S->g_xa, S->gev1, nullptr, nullptr, S->d_flag + 1);
+    S->prof.end(st);
+    if (l > 0) {
+      SO3LR_CUDA_CHECK(cudaMemcpyAsync(gev_in, S->gev1, (size_t)n * kMTot * sizeof(float), cudaMemcpyDeviceToDevice, st));
+      fill(st, S->g_qkv, (size_t)n * kProj, 0.f);
+      S->prof.begin(kPAttnBwd, st);
+      if (tiled && L.has_spherical) {
+        int rcb = launch_attn_bwd_tc_graph(st, L, S->ve, n, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, g_dR, S->d_flag + 1, asym);
+        if (rcb) return rcb;
+        launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, g_dR, 0, asym);
+      } else {
+        launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, S->g_qkv, gev_in, g_dR, 0);
+      }
+      S->prof.end(st);
+      // dL/dx_in = g_xa (skip connection) + projections^T
+      SO3LR_CUDA_CHECK(cudaMemcpyAsync(S->g4, S->g_xa, (size_t)n * kF * sizeof(float), cudaMemcpyDeviceToDevice, st));
+      S->prof.begin(kPProjBwd, st); launch_proj_bwd(st, L, S->g_qkv, n, S->g4, 1); S->prof.end(st);
+      float* t = gev2; gev2 = gev_in; gev_in = t;
+    } else {
+      S->prof.begin(kPAttnBwd, st); launch_attn_bwd(st, L, n, row_ptr, nbr_j, dR, S->qkv[l], S->ev[l], S->g_xa, S->gev1, nullptr, nullptr, g_dR, 1); S->prof.end(st);
+    }
+  }
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
 }
 
 // ---- positions -> forces (gather-only kernels on the symmetric short-range list) ----
@@ -821,7 +868,7 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
   }
   std::vector<float> tq(n_graphs, 0.f);
   if (total_charge) for (int g = 0; g < n_graphs; ++g) tq[g] = total_charge[g];
-  S->d_Rref = A.get<float>((size_t)n * 3); S->d_flag = A.get<int>(2);
+  S->d_Rref = A.get<float>((size_t)n * 3); S->d_flag = A.get<int>(4);
   S->d_rowptr_g = A.get<int>((size_t)n + 1); S->d_rowptr_lr_g = A.get<int>((size_t)n + 1);
   for (int l = 0; l <= kNumLayers; ++l) { S->x[l] = A.get<float>((size_t)n * kF); S->ev[l] = A.get<float>((size_t)n * kMTot); }
   for (int l = 0; l < kNumLayers; ++l) {

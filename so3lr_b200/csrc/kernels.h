@@ -60,9 +60,10 @@ void launch_attn_fwd(cudaStream_t s, const LayerDev& L, int n, const int* row_pt
                      const float* qkv, const float* x_in, const float* ev_in, float* xa, float* ev1);
 // g_xa / gev1: cotangents of xa / ev1.  Adds into g_qkv (k,v parts by atomics; q parts stored), gev_in (atomics; the
 // caller pre-loads it with gev1 for the skip connection) and g_dR (+=).  `first_layer`: only g_dR is produced.
+// run_if_set (optional): the kernel of a layer with a spherical filter returns at once unless *run_if_set != 0
 void launch_attn_bwd(cudaStream_t s, const LayerDev& L, int n, const int* row_ptr, const int* nbr_j, const float* dR,
                      const float* qkv, const float* ev_in, const float* g_xa, const float* gev1, float* g_qkv,
-                     float* gev_in, float* g_dR, int first_layer);
+                     float* gev_in, float* g_dR, int first_layer, const int* run_if_set = nullptr);
 
 // ---- attention_sym.cu ----
 // Gather-only kernels of the fused positions -> forces path.  They need a symmetric list (j in row i <=> i in row j with
@@ -95,6 +96,8 @@ struct ValidEdges {
   int* i = nullptr;
   int* j = nullptr;
   float4* d = nullptr;
+  int* orig = nullptr;      // position of each entry in the list it was compacted from (only when asked for)
+  long long orig_cap = 0;
   void* cub_tmp = nullptr;
   size_t cub_bytes = 0;
   int row_cap = 0;
@@ -107,7 +110,16 @@ void tc_debug_print();
 int valid_edges_reserve(ValidEdges* V, int n_rows, long long capacity);
 void valid_edges_free(ValidEdges* V);
 // no host synchronisation: counts stay on the device
-int valid_edges_build(ValidEdges* V, cudaStream_t s, int n_rows, int n, const int* row_ptr, const int* nbr_j, const float* dR);
+int valid_edges_build(ValidEdges* V, cudaStream_t s, int n_rows, int n, const int* row_ptr, const int* nbr_j, const float* dR,
+                      bool want_orig = false);
+// *asym = 1 when some entry (i <- j, d) has no partner (j <- i, -d) in the compacted list (the word must be zero beforehand)
+void valid_edges_check_symmetric(const ValidEdges& V, cudaStream_t s, int* asym);
+// The reverse kernel for caller-supplied lists: runs only while *asym == 0 and, instead of summing forces, adds to every source
+// entry e (V.orig) half of the force that the pair exerts on its receiver, g[e] += (dE/d dR_e - dE/d dR_e') / 2 with e' the
+// reversed entry.  For any motion of atoms or cell (dR_e' = -dR_e) that is equivalent to the per-entry gradient.  The caller
+// zeroes g_qkv and presets gev_in.
+int launch_attn_bwd_tc_graph(cudaStream_t s, const LayerDev& L, const ValidEdges& V, int n_recv, const float* qkv, const float* ev_in,
+                             const float* g_xa, const float* gev1, float* g_qkv, float* gev_in, float* g_dR, int* err, const int* asym);
 // Same results as launch_attn_fwd_sym for rows [0, n_recv).  `err` (device int) is set to 1 when a bounded wait on the
 // tensor-core pipeline ran out; the outputs are then incomplete.
 int launch_attn_fwd_tc(cudaStream_t s, const LayerDev& L, const ValidEdges& V, int n_recv, const float* qkv, const float* x_in,

@@ -69,81 +69,7 @@ __global__ void force_scatter_kernel(int n, long long n_edges, const int* __rest
 }
 
 // one warp per row i; lanes stride over the row's pairs
-template <int MODE>
-__global__ void __launch_bounds__(256) pair_lr_kernel(LrParams P, Cell cell, int n, const int* __restrict__ row_ptr,
-                                                      const int* __restrict__ nbr_j, const int* __restrict__ Z,
-                                                      const float* __restrict__ R, const float* __restrict__ q,
-                                                      const float* __restrict__ h, const float* __restrict__ dR_lr,
-                                                      float* __restrict__ g_dR_lr, float* __restrict__ e_atom,
-                                                      float* __restrict__ F, float* __restrict__ gq, float* __restrict__ gh,
-                                                      float* __restrict__ e_coul, float* __restrict__ e_disp, const float* __restrict__ ge,
-                                                      float* __restrict__ virial) {
-  const int lane = threadIdx.x & 31;
-  const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (i >= n) return;
-  VirialAcc va;
-  const int e0 = row_ptr[i], e1 = row_ptr[i + 1];
-  if (e0 == e1) return;
-  const float qi = q[i], hi = h[i];
-  const int Zi = Z[i];
-  const float gei = ge ? ge[i] : 1.f;
-  float xi = 0.f, yi = 0.f, zi = 0.f;
-  if (MODE == 0) { xi = R[3 * (size_t)i]; yi = R[3 * (size_t)i + 1]; zi = R[3 * (size_t)i + 2]; }
-  float ec = 0.f, ed = 0.f, fx = 0.f, fy = 0.f, fz = 0.f, gqi = 0.f, ghi = 0.f;
-  for (int e = e0 + lane; e < e1; e += 32) {
-    const int j = nbr_j[e];
-    float gx = 0.f, gy = 0.f, gz = 0.f;
-    if (j >= 0 && j < n) {
-      float dx, dy, dz;
-      if (MODE == 0) {
-        dx = R[3 * (size_t)j] - xi; dy = R[3 * (size_t)j + 1] - yi; dz = R[3 * (size_t)j + 2] - zi;
-        min_image(cell, dx, dy, dz);
-      } else {
-        dx = dR_lr[3 * (size_t)e]; dy = dR_lr[3 * (size_t)e + 1]; dz = dR_lr[3 * (size_t)e + 2];
-      }
-      const float r2 = dx * dx + dy * dy + dz * dz;
-      if (r2 > 0.f && (!P.has_cutoff || r2 < P.rc * P.rc)) {
-        const float r = sqrtf(r2);
-        float chi, dchi;
-        coulomb_chi(P, r, chi, dchi);
-        const float qj = q[j], hj = h[j];
-        const float pf = P.pair_factor;
-        const float kq = pf * kKe;
-        const float e_c = kq * qi * qj * chi;
-        float e_d, dd_dr, dd_dhi, dd_dhj;
-        dispersion_pair_fast(P, r, Zi, Z[j], hi, hj, e_d, dd_dr, dd_dhi, dd_dhj);
-        e_d *= pf; dd_dr *= pf; dd_dhi *= pf; dd_dhj *= pf;
-        ec += e_c; ed += e_d;
-        gqi = fmaf(kq * qj, chi, gqi);
-        ghi += dd_dhi;
-        atomicAdd(gq + j, gei * kq * qi * chi);
-        atomicAdd(gh + j, gei * dd_dhj);
-        const float de_dr = gei * (kq * qi * qj * dchi + dd_dr);
-        const float s = de_dr / r;
-        gx = s * dx; gy = s * dy; gz = s * dz;   // dE/d(dR), dR = R_j - R_i
-        if (MODE == 0) {
-          if (virial) va.add(1.f, dx, dy, dz, gx, gy, gz);     // every listed pair carries its own share of the energy
-          fx += gx; fy += gy; fz += gz;
-          atomicAdd(F + 3 * (size_t)j, -gx); atomicAdd(F + 3 * (size_t)j + 1, -gy); atomicAdd(F + 3 * (size_t)j + 2, -gz);
-        }
-      }
-    }
-    if (MODE == 1) { g_dR_lr[3 * (size_t)e] = gx; g_dR_lr[3 * (size_t)e + 1] = gy; g_dR_lr[3 * (size_t)e + 2] = gz; }
-  }
-  ec = warp_sum(ec); ed = warp_sum(ed); gqi = warp_sum(gqi); ghi = warp_sum(ghi);
-  if (MODE == 0) { fx = warp_sum(fx); fy = warp_sum(fy); fz = warp_sum(fz); }
-  if (lane == 0) {
-    if (e_atom) atomicAdd(e_atom + i, ec + ed);
-    if (e_coul) atomicAdd(e_coul + i, ec);
-    if (e_disp) atomicAdd(e_disp + i, ed);
-    atomicAdd(gq + i, gei * gqi);
-    atomicAdd(gh + i, gei * ghi);
-    if (MODE == 0) { atomicAdd(F + 3 * (size_t)i, fx); atomicAdd(F + 3 * (size_t)i + 1, fy); atomicAdd(F + 3 * (size_t)i + 2, fz); }
-  }
-  if (MODE == 0 && virial) va.flush_warp(virial, (size_t)i, lane);
-}
-
-// Device forms of the pair terms for the packed kernel: the same functions as coulomb_chi / dispersion_pair_fast / switching
+// Device forms of the pair terms for the long-range kernels: the same functions as coulomb_chi / dispersion_pair_fast / switching
 // of pair_terms.cuh with approximate reciprocals and exponentials (rcp.approx, ex2.approx, lg2.approx: 1-2 ulp each) in place
 // of IEEE divisions and libm calls, and the switch written with one exponential:
 //   s(1-c) / (s(1-c) + s(c)),  s(a) = exp(-1/a)   ==   1 / (1 + E),  E = exp(1/(1-c) - 1/c)
@@ -210,6 +136,81 @@ __device__ __forceinline__ void dispersion_pair_dev(const LrParams& P, float r, 
   de_dr = pre * (dT_dR * (1.f / kBohr) * f + T * df);
   de_dhi = pre * f * (T * dlc6_dhi + dT_da17 * da17_dh * alf_i);
   de_dhj = pre * f * (T * dlc6_dhj + dT_da17 * da17_dh * alf_j);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(256) pair_lr_kernel(LrParams P, Cell cell, int n, const int* __restrict__ row_ptr,
+                                                      const int* __restrict__ nbr_j, const int* __restrict__ Z,
+                                                      const float* __restrict__ R, const float* __restrict__ q,
+                                                      const float* __restrict__ h, const float* __restrict__ dR_lr,
+                                                      float* __restrict__ g_dR_lr, float* __restrict__ e_atom,
+                                                      float* __restrict__ F, float* __restrict__ gq, float* __restrict__ gh,
+                                                      float* __restrict__ e_coul, float* __restrict__ e_disp, const float* __restrict__ ge,
+                                                      float* __restrict__ virial) {
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (i >= n) return;
+  VirialAcc va;
+  const int e0 = row_ptr[i], e1 = row_ptr[i + 1];
+  if (e0 == e1) return;
+  const float qi = q[i], hi = h[i];
+  const int Zi = Z[i];
+  const float gei = ge ? ge[i] : 1.f;
+  float xi = 0.f, yi = 0.f, zi = 0.f;
+  if (MODE == 0) { xi = R[3 * (size_t)i]; yi = R[3 * (size_t)i + 1]; zi = R[3 * (size_t)i + 2]; }
+  float ec = 0.f, ed = 0.f, fx = 0.f, fy = 0.f, fz = 0.f, gqi = 0.f, ghi = 0.f;
+  for (int e = e0 + lane; e < e1; e += 32) {
+    const int j = nbr_j[e];
+    float gx = 0.f, gy = 0.f, gz = 0.f;
+    if (j >= 0 && j < n) {
+      float dx, dy, dz;
+      if (MODE == 0) {
+        dx = R[3 * (size_t)j] - xi; dy = R[3 * (size_t)j + 1] - yi; dz = R[3 * (size_t)j + 2] - zi;
+        min_image(cell, dx, dy, dz);
+      } else {
+        dx = dR_lr[3 * (size_t)e]; dy = dR_lr[3 * (size_t)e + 1]; dz = dR_lr[3 * (size_t)e + 2];
+      }
+      const float r2 = dx * dx + dy * dy + dz * dz;
+      if (r2 > 0.f && (!P.has_cutoff || r2 < P.rc * P.rc)) {
+        const float rinv = rsqrtf(r2), r = r2 * rinv;
+        float chi, dchi;
+        coulomb_chi_dev(P, r, rinv, chi, dchi);
+        const float qj = q[j], hj = h[j];
+        const float pf = P.pair_factor;
+        const float kq = pf * kKe;
+        const float e_c = kq * qi * qj * chi;
+        float e_d, dd_dr, dd_dhi, dd_dhj;
+        const int Zj = Z[j];
+        dispersion_pair_dev(P, r, alpha_free(Zi), c6_free(Zi), hi, alpha_free(Zj), c6_free(Zj), hj, e_d, dd_dr, dd_dhi, dd_dhj);
+        e_d *= pf; dd_dr *= pf; dd_dhi *= pf; dd_dhj *= pf;
+        ec += e_c; ed += e_d;
+        gqi = fmaf(kq * qj, chi, gqi);
+        ghi += dd_dhi;
+        atomicAdd(gq + j, gei * kq * qi * chi);
+        atomicAdd(gh + j, gei * dd_dhj);
+        const float de_dr = gei * (kq * qi * qj * dchi + dd_dr);
+        const float s = de_dr * rinv;
+        gx = s * dx; gy = s * dy; gz = s * dz;   // dE/d(dR), dR = R_j - R_i
+        if (MODE == 0) {
+          if (virial) va.add(1.f, dx, dy, dz, gx, gy, gz);     // every listed pair carries its own share of the energy
+          fx += gx; fy += gy; fz += gz;
+          atomicAdd(F + 3 * (size_t)j, -gx); atomicAdd(F + 3 * (size_t)j + 1, -gy); atomicAdd(F + 3 * (size_t)j + 2, -gz);
+        }
+      }
+    }
+    if (MODE == 1) { g_dR_lr[3 * (size_t)e] = gx; g_dR_lr[3 * (size_t)e + 1] = gy; g_dR_lr[3 * (size_t)e + 2] = gz; }
+  }
+  ec = warp_sum(ec); ed = warp_sum(ed); gqi = warp_sum(gqi); ghi = warp_sum(ghi);
+  if (MODE == 0) { fx = warp_sum(fx); fy = warp_sum(fy); fz = warp_sum(fz); }
+  if (lane == 0) {
+    if (e_atom) atomicAdd(e_atom + i, ec + ed);
+    if (e_coul) atomicAdd(e_coul + i, ec);
+    if (e_disp) atomicAdd(e_disp + i, ed);
+    atomicAdd(gq + i, gei * gqi);
+    atomicAdd(gh + i, gei * ghi);
+    if (MODE == 0) { atomicAdd(F + 3 * (size_t)i, fx); atomicAdd(F + 3 * (size_t)i + 1, fy); atomicAdd(F + 3 * (size_t)i + 2, fz); }
+  }
+  if (MODE == 0 && virial) va.flush_warp(virial, (size_t)i, lane);
 }
 
 // The single-device long-range kernel with packed operands: per atom (x, y, z, q) and (h, alpha_free, c6_free, -) so that a pair costs two

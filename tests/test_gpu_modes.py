@@ -58,3 +58,66 @@ def test_kernel_variants_agree(tmp_path):
         for k in ("F_w", "F_m"):
             assert np.abs(got[k] - ref[k]).max() <= 5e-5, (name, k, np.abs(got[k] - ref[k]).max())
         assert np.abs(got["W_w"] - ref["W_w"]).max() <= 2e-4 * np.abs(ref["W_w"]).max(), name
+
+
+GRAPH_CHILD = r"""
+import sys, numpy as np, torch
+sys.path.insert(0, sys.argv[1])
+from so3lr_b200 import workloads as W
+from so3lr_b200.engine import System
+Z, R, cell = W.water_box(216, 18.7, 5)
+R = np.asarray(R, dtype=np.float32)
+cellt = torch.tensor(np.asarray(cell, dtype=np.float32), device="cuda")
+Rt = torch.tensor(R, device="cuda")
+s = System(Z, cell, cutoff_lr=9.0, damping=2.0, lr_format="sparse")
+def lists(which):
+    _, cnt, _ = s.neighbor_list(Rt, which, 1)
+    idx, cnt, _ = s.neighbor_list(Rt, which, cnt)
+    i, j = idx[0].long(), idx[1].long()
+    d = Rt[j] - Rt[i]
+    f = d @ torch.linalg.inv(cellt)
+    d = (f - torch.round(f)) @ cellt
+    return i, j, d
+i, j, d = lists(0)
+il, jl, dl = lists(1)
+out = {}
+def forces(o, i, j, il, jl):
+    F = torch.zeros_like(Rt)
+    F.index_add_(0, i, o["g_edges"]); F.index_add_(0, j, -o["g_edges"])
+    F.index_add_(0, il, o["g_edges_lr"]); F.index_add_(0, jl, -o["g_edges_lr"])
+    return F
+o = s.graph_eval(i, j, d, il, jl, dl)
+out["E_sym"], out["F_sym"] = o["e_atom"].cpu().numpy(), forces(o, i, j, il, jl).cpu().numpy()
+out["W_sym"] = (d[:, :, None] * o["g_edges"][:, None, :]).sum(0).cpu().numpy()
+# one entry removed: the list is no longer symmetric, the exact scatter kernels must take over inside the same call
+keep = torch.ones(i.numel(), dtype=torch.bool, device="cuda"); keep[i.numel() // 3] = False
+o = s.graph_eval(i[keep], j[keep], d[keep], il, jl, dl)
+out["E_asym"], out["G_asym"] = o["e_atom"].cpu().numpy(), o["g_edges"].cpu().numpy()
+ref = s.compute(Rt)
+out["E_ref"], out["F_ref"] = ref["energy"].cpu().numpy(), ref["forces"].cpu().numpy()
+np.savez(sys.argv[2], **out)
+"""
+
+
+def test_graph_level_call_fast_and_scatter_paths_agree(tmp_path):
+    """so3lr_b200_system_graph_eval on a symmetric list (tiled kernels, antisymmetrised per-entry cotangents) against the same
+    call kept on the scatter kernels (exact per-entry cotangents): same energies, same forces after the featurizer's transpose,
+    same strain derivative; both equal the fused positions -> forces call.  On a list with one entry removed both
+    processes must run the scatter kernels and agree entry by entry."""
+    def run(name, env):
+        out = str(tmp_path / f"{name}.npz")
+        e = dict(os.environ)
+        for k in ("SO3LR_B200_ATTENTION", "SO3LR_B200_DENSE", "SO3LR_B200_LAYER0", "SO3LR_B200_GRAPH"):
+            e.pop(k, None)
+        e.update(env)
+        subprocess.run([sys.executable, "-c", GRAPH_CHILD, ROOT, out], check=True, timeout=600, env=e)
+        return np.load(out)
+    fast, slow = run("fast", {}), run("scatter", {"SO3LR_B200_GRAPH": "scatter"})
+    for got in (fast, slow):
+        assert abs(float(got["E_sym"].sum()) - float(got["E_ref"].sum())) <= 2e-6 * abs(float(got["E_ref"].sum()))
+        assert np.abs(got["F_sym"] - got["F_ref"]).max() <= 5e-5
+    assert np.abs(fast["E_sym"] - slow["E_sym"]).max() <= 2e-5
+    assert np.abs(fast["F_sym"] - slow["F_sym"]).max() <= 5e-5
+    assert np.abs(fast["W_sym"] - slow["W_sym"]).max() <= 2e-4 * np.abs(slow["W_sym"]).max()
+    assert np.abs(fast["E_asym"] - slow["E_asym"]).max() <= 2e-5
+    assert np.abs(fast["G_asym"] - slow["G_asym"]).max() <= 5e-5
