@@ -125,6 +125,11 @@ SO3LR_B200_API int so3lr_b200_system_export_list(so3lr_b200_system* sys, void* s
  * inputs, the outputs are per-atom energies and the gradients of sum_i g_e_atom[i] * e_atom[i] with respect to the
  * displacements.  Lists must be grouped by centre index (idx_i non-decreasing); padding entries carry index
  * n_atoms.  All pointers are device pointers; g_e_atom may be NULL (= ones).
+ * When every short-range entry (i <- j, d) inside the cutoff has its partner (j <- i, -d) in the list (decided on the
+ * device, no host read), both entries of a pair receive the antisymmetrised cotangent (dE/dd_e - dE/dd_e') / 2, which
+ * contracts to the same forces and strain derivative for every motion of atoms or cell; otherwise, or with
+ * SO3LR_B200_GRAPH=scatter in the environment, each entry receives dE/dd_e itself.  The call only enqueues work; it
+ * allocates when the list is longer than any list the context has seen before.
  * Replaces: potential(graph) and its jax.grad w.r.t. graph.edges / graph.edges_lr
  *           (so3lr/jaxmd_utils.py:130-141, so3lr/graph.py:3-24). */
 SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* sys, void* stream, int64_t n_edges, const int32_t* idx_i,
