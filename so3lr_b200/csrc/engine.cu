@@ -1439,7 +1439,8 @@ SO3LR_B200_API int so3lr_b200_dd_begin(so3lr_b200_system* S, void* stream, const
     // rows of the owned atoms only: every kernel of the decomposed path gathers towards an owned atom
     int rc = nlist_build(S->nws, st, S->cell, S->n, R_local_dev, kCutoffSr + S->opt.skin, 0, nullptr, nullptr, &S->sr, 1, nullptr, n0);
     if (rc) return rc;
-    rc = nlist_build(S->nws, st, S->cell, S->n, R_local_dev, S->opt.cutoff_lr + S->opt.skin, 0, nullptr, nullptr, &S->lrl, 1, nullptr, n0);
+    // ordered: ghosts carry the larger indices, so an owned row holds every owned partner once and every ghost partner
+    rc = nlist_build(S->nws, st, S->cell, S->n, R_local_dev, S->opt.cutoff_lr + S->opt.skin, 1, nullptr, nullptr, &S->lrl, 1, nullptr, n0);
     if (rc) return rc;
     rc = ensure_edge_buffers(S, S->sr.count);
     if (rc) return rc;

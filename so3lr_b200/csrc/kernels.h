@@ -165,14 +165,15 @@ void launch_pair_lr(cudaStream_t s, const LrParams& P, const Cell& cell, int n, 
                     const int* Z, const float* R, const float* q, const float* h, int mode, const float* dR_lr,
                     float* g_dR_lr, float* e_atom, float* F, float* gq, float* gh, float* e_coul, float* e_disp,
                     const float* ge, float* virial = nullptr);
-// Domain-decomposed variant: rows 0 .. n_owned-1 of a full (both directions) list; every pair energy is booked half on
-// the row atom, and only the derivatives that land on the row atom are produced, at full weight: F[i], gq[i], gh[i],
-// e_coul[i], e_disp[i] are written (not accumulated) by the row's warp -- no atomics.
 // the single-device form with packed gathers and vector reductions (pack: scratch of 12 n floats, 16-byte aligned); adds to
 // F, gq, gh, e_coul, e_disp like launch_pair_lr in mode 0
 void launch_pair_lr_packed(cudaStream_t s, const LrParams& P, const Cell& cell, int n, const int* row_ptr, const int* nbr_j, const int* Z,
                            const float* R, const float* q, const float* h, float* pack, float* F, float* gq, float* gh, float* e_coul,
                            float* e_disp, float* virial);
+// Domain-decomposed variant: rows 0 .. n_owned-1 of an ordered list (j > i) over owned atoms and ghosts, ghosts carrying
+// the larger indices.  Pairs of two owned atoms are evaluated once and scatter the partner's derivatives (atomics); pairs
+// with a ghost end book half of the energy and the row atom's derivatives.  gq, gh are zeroed here and accumulated, F_add is
+// added to, e_coul[i], e_disp[i] are written by the row's warp.
 void launch_pair_lr_owned(cudaStream_t s, const LrParams& P, const Cell& cell, int n_owned, int n, const int* row_ptr,
                           const int* nbr_j, const int* Z, const float* R, const float* q, const float* h, float* F_add,
                           float* gq, float* gh, float* e_coul, float* e_disp, float* virial = nullptr);

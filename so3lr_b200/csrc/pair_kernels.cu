@@ -288,10 +288,11 @@ __global__ void __launch_bounds__(256) pair_lr_packed_kernel(LrParams P, Cell ce
   if (virial) va.flush_warp(virial, (size_t)i, lane);
 }
 
-// Owned rows of a full list (decomposed runs).  A pair whose two ends are both owned is evaluated once, in the row that the
-// parity rule picks (balanced over the rows), and its share for the other end is scattered with atomics; a pair with a ghost
-// end is evaluated in the owned end's row only, which books half of the energy and its own derivatives (the ghost's owner does
-// the same from its side).  gq, gh and F_add must hold the values to add to (zeros for gq, gh) when the kernel starts.
+// Owned rows of an ordered list over owned atoms and ghosts (decomposed runs; ghosts carry the larger indices, so the list
+// holds every pair of two owned atoms once and every owned-ghost pair in the owned atom's row).  A pair of two owned atoms
+// books its whole energy on the row atom and scatters the other end's derivatives with atomics; a pair with a ghost end books
+// half of the energy and the row atom's derivatives only (the ghost's owner does the same from its side).  gq, gh and F_add
+// must hold the values to add to (zeros for gq, gh) when the kernel starts.
 __global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cell, int n_owned, int n, const int* __restrict__ row_ptr,
                                                             const int* __restrict__ nbr_j, const int* __restrict__ Z,
                                                             const float* __restrict__ R, const float* __restrict__ q,
@@ -310,8 +311,6 @@ __global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cel
   for (int e = e0 + lane; e < e1; e += 32) {
     const int j = nbr_j[e];
     if (j < 0 || j >= n) continue;
-    const bool both = j < n_owned;
-    if (both && ((i < j) != (((i + j) & 1) == 0))) continue;      // the other end's row takes this pair
     float dx = R[3 * (size_t)j] - xi, dy = R[3 * (size_t)j + 1] - yi, dz = R[3 * (size_t)j + 2] - zi;
     min_image(cell, dx, dy, dz);
     const float r2 = dx * dx + dy * dy + dz * dz;
@@ -323,6 +322,7 @@ __global__ void __launch_bounds__(256) pair_lr_owned_kernel(LrParams P, Cell cel
     const int Zj = Z[j];
     float e_d, dd_dr, dd_dhi, dd_dhj;
     dispersion_pair_dev(P, r, alf_i, c6f_i, hi, alpha_free(Zj), c6_free(Zj), hj, e_d, dd_dr, dd_dhi, dd_dhj);
+    const bool both = j < n_owned;
     const float w = both ? 1.f : 0.5f;                             // share of the pair energy booked on this row
     ec = fmaf(w * kKe * qi * qj, chi, ec);
     ed = fmaf(w, e_d, ed);
