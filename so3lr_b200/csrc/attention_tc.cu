@@ -75,12 +75,23 @@ __device__ __forceinline__ float invw(int l) {
 }
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+// float4 arithmetic as two packed operations (fma.rn.f32x2 / mul.rn.f32x2) on the halves
+__device__ __forceinline__ float2 lo2(float4 v) { return make_float2(v.x, v.y); }
+__device__ __forceinline__ float2 hi2(float4 v) { return make_float2(v.z, v.w); }
 __device__ __forceinline__ float4 f4_fma(float a, float4 b, float4 c) {
-  return make_float4(fmaf(a, b.x, c.x), fmaf(a, b.y, c.y), fmaf(a, b.z, c.z), fmaf(a, b.w, c.w));
+  const float2 a2 = make_float2(a, a);
+  const float2 l = __ffma2_rn(a2, lo2(b), lo2(c)), h = __ffma2_rn(a2, hi2(b), hi2(c));
+  return make_float4(l.x, l.y, h.x, h.y);
 }
 __device__ __forceinline__ float4 f4_zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
-__device__ __forceinline__ float dot3(float4 a, float4 b, float4 c) { return a.x * b.x * c.x + a.y * b.y * c.y + a.z * b.z * c.z + a.w * b.w * c.w; }
-__device__ __forceinline__ float dot2(float4 a, float4 b) { return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w; }
+__device__ __forceinline__ float dot3(float4 a, float4 b, float4 c) {
+  const float2 s = __ffma2_rn(__fmul2_rn(hi2(a), hi2(b)), hi2(c), __fmul2_rn(__fmul2_rn(lo2(a), lo2(b)), lo2(c)));
+  return s.x + s.y;
+}
+__device__ __forceinline__ float dot2(float4 a, float4 b) {
+  const float2 s = __ffma2_rn(hi2(a), hi2(b), __fmul2_rn(lo2(a), lo2(b)));
+  return s.x + s.y;
+}
 __device__ __forceinline__ bool f4_nonzero(float4 a) { return a.x != 0.f || a.y != 0.f || a.z != 0.f || a.w != 0.f; }
 
 // (x, y) -> FP16 pair hi and FP16 pair of the residuals scaled by 2048
@@ -727,18 +738,31 @@ __device__ __forceinline__ void reverse_edges4(const RevLoads& L, float* rec, co
     }
     const float4 w = ld4(wt + (wrow0 + u) * kWStride + col);
     const float4 qj = L.qj[u], kj = L.kj[u];
-    const float DA = group8_sum(dot3(qa, w, kj));
-    const float DB = group8_sum(dot3(qj, w, ka));
+    // packed FP32 arithmetic (fma.rn.f32x2) on the two halves of every float4: the products q_i k_j and q_j k_i serve both the
+    // logits and dw
+    const float2 w01 = make_float2(w.x, w.y), w23 = make_float2(w.z, w.w);
+    const float2 pA01 = __fmul2_rn(make_float2(qa.x, qa.y), make_float2(kj.x, kj.y)), pA23 = __fmul2_rn(make_float2(qa.z, qa.w), make_float2(kj.z, kj.w));
+    const float2 pB01 = __fmul2_rn(make_float2(qj.x, qj.y), make_float2(ka.x, ka.y)), pB23 = __fmul2_rn(make_float2(qj.z, qj.w), make_float2(ka.z, ka.w));
+    const float2 sA = __ffma2_rn(w23, pA23, __fmul2_rn(w01, pA01)), sB = __ffma2_rn(w23, pB23, __fmul2_rn(w01, pB01));
+    const float DA = group8_sum(sA.x + sA.y);
+    const float DB = group8_sum(sB.x + sB.y);
     const float daA = rp[(F ? 12 : 36) + grp], daB = rp[(F ? 16 : 40) + grp];
     if (cg == 0) {
       if (F) { rp[20 + grp] = sc * DA; rp[24 + grp] = sc * DB; }
       else rp[44 + grp] = sc * DB;
     }
     const float dDA = sc * daA, dDB = sc * daB;
-    gq = make_float4(fmaf(dDA * w.x, kj.x, gq.x), fmaf(dDA * w.y, kj.y, gq.y), fmaf(dDA * w.z, kj.z, gq.z), fmaf(dDA * w.w, kj.w, gq.w));
-    gk = make_float4(fmaf(dDB * w.x, qj.x, gk.x), fmaf(dDB * w.y, qj.y, gk.y), fmaf(dDB * w.z, qj.z, gk.z), fmaf(dDB * w.w, qj.w, gk.w));
-    const float dw0 = fmaf(dDA * qa.x, kj.x, dDB * qj.x * ka.x), dw1 = fmaf(dDA * qa.y, kj.y, dDB * qj.y * ka.y);
-    const float dw2 = fmaf(dDA * qa.z, kj.z, dDB * qj.z * ka.z), dw3 = fmaf(dDA * qa.w, kj.w, dDB * qj.w * ka.w);
+    const float2 a2 = make_float2(dDA, dDA), b2 = make_float2(dDB, dDB);
+    {
+      const float2 g01 = __ffma2_rn(a2, __fmul2_rn(w01, make_float2(kj.x, kj.y)), make_float2(gq.x, gq.y));
+      const float2 g23 = __ffma2_rn(a2, __fmul2_rn(w23, make_float2(kj.z, kj.w)), make_float2(gq.z, gq.w));
+      gq = make_float4(g01.x, g01.y, g23.x, g23.y);
+      const float2 h01 = __ffma2_rn(b2, __fmul2_rn(w01, make_float2(qj.x, qj.y)), make_float2(gk.x, gk.y));
+      const float2 h23 = __ffma2_rn(b2, __fmul2_rn(w23, make_float2(qj.z, qj.w)), make_float2(gk.z, gk.w));
+      gk = make_float4(h01.x, h01.y, h23.x, h23.y);
+    }
+    const float2 d01 = __ffma2_rn(a2, pA01, __fmul2_rn(b2, pB01)), d23 = __ffma2_rn(a2, pA23, __fmul2_rn(b2, pB23));
+    const float dw0 = d01.x, dw1 = d01.y, dw2 = d23.x, dw3 = d23.y;
     // dw as A operand of the second MMA chain: row = edge, columns 4 lane .. 4 lane + 3 of the hi and the lo matrix
     {
       uint2 h, l;

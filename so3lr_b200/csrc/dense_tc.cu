@@ -63,7 +63,8 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 __device__ __forceinline__ void split2(float x, float y, unsigned& hi, unsigned& lo) {
   const __half2 h = __floats2half2_rn(x, y);
   const float2 hf = __half22float2(h);
-  const __half2 l = __floats2half2_rn((x - hf.x) * kLoScale, (y - hf.y) * kLoScale);
+  const float2 d = __fmul2_rn(__fadd2_rn(make_float2(x, y), make_float2(-hf.x, -hf.y)), make_float2(kLoScale, kLoScale));
+  const __half2 l = __float22half2_rn(d);
   hi = *reinterpret_cast<const unsigned*>(&h);
   lo = *reinterpret_cast<const unsigned*>(&l);
 }
