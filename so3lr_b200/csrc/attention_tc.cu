@@ -169,11 +169,22 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
 }
 // main + cross / 2048 of 32 columns (cross accumulators sit 256 columns above the main ones)
 __device__ __forceinline__ void tmem_ld32_combined(uint32_t taddr, float* v) {
-  float c[32];
-  tmem_ld32(taddr, v);
-  tmem_ld32(taddr + 256, c);
+  uint32_t a[32], b[32];      // both loads in flight before the one wait
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%64];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%65];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]), "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15]), "=r"(a[16]), "=r"(a[17]), "=r"(a[18]), "=r"(a[19]), "=r"(a[20]), "=r"(a[21]), "=r"(a[22]), "=r"(a[23]), "=r"(a[24]), "=r"(a[25]), "=r"(a[26]), "=r"(a[27]), "=r"(a[28]), "=r"(a[29]), "=r"(a[30]), "=r"(a[31]),
+        "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]), "=r"(b[4]), "=r"(b[5]), "=r"(b[6]), "=r"(b[7]), "=r"(b[8]), "=r"(b[9]), "=r"(b[10]), "=r"(b[11]), "=r"(b[12]), "=r"(b[13]), "=r"(b[14]), "=r"(b[15]), "=r"(b[16]), "=r"(b[17]), "=r"(b[18]), "=r"(b[19]), "=r"(b[20]), "=r"(b[21]), "=r"(b[22]), "=r"(b[23]), "=r"(b[24]), "=r"(b[25]), "=r"(b[26]), "=r"(b[27]), "=r"(b[28]), "=r"(b[29]), "=r"(b[30]), "=r"(b[31])
+      : "r"(taddr), "r"(taddr + 256)
+      : "memory");
+  const float2 s2 = make_float2(kLoInv, kLoInv);
 #pragma unroll
-  for (int k = 0; k < 32; ++k) v[k] = fmaf(c[k], kLoInv, v[k]);
+  for (int k = 0; k < 32; k += 2) {
+    const float2 r = __ffma2_rn(make_float2(__uint_as_float(b[k]), __uint_as_float(b[k + 1])), s2,
+                                make_float2(__uint_as_float(a[k]), __uint_as_float(a[k + 1])));
+    v[k] = r.x; v[k + 1] = r.y;
+  }
 }
 
 __device__ __forceinline__ void invariants(const float* __restrict__ evi, const float* __restrict__ evj, float* s) {
@@ -208,9 +219,9 @@ __device__ __forceinline__ void store_chebyshev_half(unsigned char* a_hi, int ro
     for (int q = 0; q < 8; q += 2) {
       v[q] = valid ? a_cur : 0.f;
       v[q + 1] = valid ? b_cur : 0.f;
-      const float an = fmaf(T4x2, a_cur, -a_prev), bn = fmaf(T4x2, b_cur, -b_prev);
-      a_prev = a_cur; a_cur = an;
-      b_prev = b_cur; b_cur = bn;
+      const float2 nx = __ffma2_rn(make_float2(T4x2, T4x2), make_float2(a_cur, b_cur), make_float2(-a_prev, -b_prev));
+      a_prev = a_cur; a_cur = nx.x;
+      b_prev = b_cur; b_cur = nx.y;
     }
     store_chunk(a_hi, 4 * odd + c, row, v);
   }
