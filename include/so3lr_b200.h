@@ -138,6 +138,31 @@ SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* sys, void* st
                                  float* e_atom_dev, float* g_edges_dev, float* g_edges_lr_dev, float* charges_dev,
                                  float* hirshfeld_dev);
 
+/* Reciprocal-space part of the electrostatic energy (one periodic structure with a long-range cutoff).  mode 1: Ewald sum over
+ * the k vectors of the FFT-frequency index grid of shape (n1, n2, n3) -- the shape of the reference's `k_grid` array -- with
+ * Gaussian smearing `smearing` (the reference's `k_smearing`, Angstrom); mode 0 switches it off again.  While it is on, every
+ * pair of the long-range list keeps only erf(r / sigma) / r - erf(r / (sqrt(2) smearing)) / r (shifted and blended towards the
+ * cutoff like the plain term), and so3lr_b200_system_compute / _compute_host / the MD step bodies add
+ *   ke / (2 V) sum_{k != 0} 4 pi / k^2 exp(-smearing^2 k^2 / 2) |S(k)|^2 - ke sum_i q_i^2 / (sqrt(2 pi) smearing) - ke pi smearing^2 Q^2 / V
+ * with its forces, its dE/dq (which continues into the charge head's reverse pass) and its strain derivative.  The cell may change
+ * afterwards (so3lr_b200_system_rescale_cell): the index grid stays, the k vectors follow the cell.  Allocates and waits for the
+ * device: call it between evaluations.  Not available in decomposed (so3lr_b200_dd_*) evaluations.  The mesh (PME) variant of
+ * the reference is not part of this library.
+ * Replaces: the `k_grid` / `k_smearing` arguments of the reference's energy function (so3lr/jaxmd_utils.py:39-47,70-71), the
+ *           grid set-up of so3lr/cli/so3lr_md.py:1392-1428 and `coulomb_kspace_do_ewald=True` of so3lr/potential.py:11-25. */
+SO3LR_B200_API int so3lr_b200_system_set_kspace(so3lr_b200_system* sys, int mode, float smearing, int n1, int n2, int n3);
+
+/* so3lr_b200_system_graph_eval for a context whose reciprocal-space part is on: `positions` (n_atoms, 3) are the Cartesian
+ * positions the displacements were formed from (Graph.positions), and g_positions_dev receives the gradient of the
+ * reciprocal-space energy with respect to them at fixed charges; the charges' own dependence on the geometry arrives through
+ * g_edges_dev as usual.  The upstream cotangent is one for every atom (the per-atom reciprocal energies are not separable).
+ * The strain derivative of the reciprocal part is available from the fused entry (so3lr_b200_system_virial) only. */
+SO3LR_B200_API int so3lr_b200_system_graph_eval_kspace(so3lr_b200_system* sys, void* stream, int64_t n_edges, const int32_t* idx_i,
+                                        const int32_t* idx_j, const float* edges, int64_t n_pairs, const int32_t* idx_i_lr,
+                                        const int32_t* idx_j_lr, const float* edges_lr, const float* positions,
+                                        float* e_atom_dev, float* g_edges_dev, float* g_edges_lr_dev, float* g_positions_dev,
+                                        float* charges_dev, float* hirshfeld_dev);
+
 /* A velocity-Verlet (NVE) step driven by the library: positions/velocities/forces stay on the device.
  * masses_dev in amu, dt in fs, velocities in Angstrom/fs.  Runs `n_steps` steps; forces_dev must hold the forces
  * of positions_dev on entry (call so3lr_b200_system_compute first) and holds the final forces on return.
@@ -310,6 +335,8 @@ SO3LR_B200_API void so3lr_b200_host_sph_harm_vjp(float x, float y, float z, cons
 SO3LR_B200_API void so3lr_b200_host_pair_terms(float r, int zi, int zj, float qi, float qj, float hi, float hj, float cutoff_lr,
                                 float damping, float* out8);
 /* out4 = dispersion energy, d/dr, d/dh_i, d/dh_j of one pair as the pair kernels evaluate it (hand-derived partials) */
+/* out2 = chi(r), d chi / d r of the Coulomb pair function; smearing > 0 takes the reciprocal-space part out of it */
+SO3LR_B200_API void so3lr_b200_host_coulomb_chi(float r, float cutoff_lr, float smearing, float* out2);
 SO3LR_B200_API void so3lr_b200_host_dispersion_fast(float r, int zi, int zj, float hi, float hj, float cutoff_lr, float damping,
                                                     float* out4);
 SO3LR_B200_API void so3lr_b200_host_zbl(const float* blob_host, float r, int zi, int zj, float* out2);

@@ -261,20 +261,28 @@ def zbl_energy(P, Zf, d, cut, idx_i, N):
     return a, c, p, dd
 
 
-def coulomb_pair(d, cutoff_lr):
+def coulomb_pair(d, cutoff_lr, k_smearing=None):
     """erf-damped Coulomb kernel chi(r) (without ke q_i q_j).  With a cutoff: potential-shifted below the
-    switch-on radius, blended smoothly into the force-shifted form towards the cutoff, zero beyond."""
+    switch-on radius, blended smoothly into the force-shifted form towards the cutoff, zero beyond.
+    With `k_smearing` s the part erf(r / (sqrt(2) s)) / r, which the reciprocal-space sum holds, is taken out of the
+    pair function before it is shifted and blended (the role of `coulomb_erf_shifted_force_smooth_pme`,
+    so3lr/cli/tune_ewald.py:612-614; its exact blending is in the absent mlff source, so this form is unpinned)."""
     sig = SIGMA_COULOMB
+    a = None if k_smearing is None else 1.0 / (math.sqrt(2.0) * float(k_smearing))
 
     def pot(r):
-        return torch.erf(r / sig) / r
+        v = torch.erf(r / sig) / r
+        return v if a is None else v - torch.erf(r * a) / r
 
     if cutoff_lr is None:
         return pot(d)
     rc = torch.tensor(float(cutoff_lr), dtype=d.dtype)
 
     def dpot(r):
-        return (2 * r * torch.exp(-(r / sig) ** 2) / (math.sqrt(math.pi) * sig) - torch.erf(r / sig)) / r ** 2
+        v = (2 * r * torch.exp(-(r / sig) ** 2) / (math.sqrt(math.pi) * sig) - torch.erf(r / sig)) / r ** 2
+        if a is not None:
+            v = v - (2 * r * a * torch.exp(-(r * a) ** 2) / math.sqrt(math.pi) - torch.erf(r * a)) / r ** 2
+        return v
 
     f = switching_fn(d, CUTON_FRACTION * cutoff_lr, cutoff_lr)
     shifted = pot(d) - pot(rc)
@@ -307,8 +315,11 @@ def dispersion_pair(d, Zi, Zj, hi, hj, cutoff_lr, damping):
 
 def energy_from_graph(P, Z, dR, idx_i, idx_j, dR_lr, idx_i_lr, idx_j_lr, *, lr_format="ordered_sparse",
                       cutoff_lr: Optional[float] = 12.0, damping: Optional[float] = 2.0,
-                      total_charge=None, num_unpaired=None, batch_segments=None, num_graphs=1, record=None):
+                      total_charge=None, num_unpaired=None, batch_segments=None, num_graphs=1, record=None, kspace=None):
     """Per-atom energies and auxiliary outputs from the Graph-level inputs of so3lr/graph.py:3-24.
+
+    `kspace` = dict(positions (N,3), cell (3,3), grid (n1,n2,n3), smearing) switches the Coulomb term to the
+    real-space + reciprocal-space split of oracle/kspace_oracle.py (Graph fields positions, cell, k_grid, k_smearing).
 
     dR (E,3) displacement of each short-range edge (idx_i = centre, idx_j = neighbour), dR_lr (P,3) of each
     long-range pair.  `lr_format`: 'ordered_sparse' (each pair once, so3lr/potential.py:22) or 'sparse'
@@ -375,12 +386,15 @@ def energy_from_graph(P, Z, dR, idx_i, idx_j, dR_lr, idx_i_lr, idx_j_lr, *, lr_f
     keep = (idx_i_lr < N) & (idx_j_lr < N) & (dl_all > 0)
     dl, il, jl = dl_all[keep], idx_i_lr[keep], idx_j_lr[keep]
     fac = 0.5 if lr_format == "sparse" else 1.0
-    e_c_pair = fac * KE * q[il] * q[jl] * coulomb_pair(dl, cutoff_lr)
+    e_c_pair = fac * KE * q[il] * q[jl] * coulomb_pair(dl, cutoff_lr, None if kspace is None else kspace["smearing"])
     e_d_pair = fac * dispersion_pair(dl, Z[il], Z[jl], hr[il], hr[jl], cutoff_lr, damping)
     if cutoff_lr is not None:
         e_d_pair = torch.where(dl < cutoff_lr, e_d_pair, torch.zeros_like(e_d_pair))
     e_c = torch.zeros(N, dtype=_dt()).index_add(0, il, e_c_pair)
     e_d = torch.zeros(N, dtype=_dt()).index_add(0, il, e_d_pair)
+    if kspace is not None:
+        from oracle.kspace_oracle import reciprocal_energy
+        e_c = e_c + reciprocal_energy(kspace["positions"], q, kspace["cell"], kspace["grid"], float(kspace["smearing"]))
 
     e_atom = e_nn + e_zbl + e_c + e_d
     aux = dict(partial_charges=q, hirshfeld_ratios=hr, zbl_repulsion=e_zbl, electrostatic_energy=e_c,
@@ -390,14 +404,16 @@ def energy_from_graph(P, Z, dR, idx_i, idx_j, dR_lr, idx_i_lr, idx_j_lr, *, lr_f
 
 def energy_forces(P, R, Z, cell=None, *, cutoff_lr: Optional[float] = 12.0, damping: Optional[float] = 2.0,
                   lr_format="ordered_sparse", lr_neighbor_cutoff: Optional[float] = None, total_charge=None,
-                  num_unpaired=None, batch_segments=None, num_graphs=1, record=None, lists=None):
+                  num_unpaired=None, batch_segments=None, num_graphs=1, record=None, lists=None, k_grid=None,
+                  k_smearing=None):
     """Positions -> total energy, forces and aux outputs, the composition used by
     so3lr/jaxmd_utils.py:130-141 + jax_md.quantity.force and by so3lr/base_calculator.py:95-122.
 
     R (N,3) Cartesian in Angstrom, cell None (free space) or 3x3 with lattice vectors as rows.
     Neighbor lists are built here (short range 4.5 A, long range `cutoff_lr`) unless `lists` provides
     (idx_i, idx_j, idx_i_lr, idx_j_lr).  For several graphs pass `batch_segments`; lists are then
-    restricted to pairs inside one graph.
+    restricted to pairs inside one graph.  `k_grid` (an index-grid shape or an array of that shape) and `k_smearing`
+    switch on the reciprocal-space Coulomb part (one periodic structure).
     """
     R = np.asarray(R, dtype=np.float64)
     N = len(R)
@@ -426,10 +442,15 @@ def energy_forces(P, R, Z, cell=None, *, cutoff_lr: Optional[float] = 12.0, damp
             dR = dR - torch.round(s) @ c
         return dR + dR @ eps.T
 
+    kspace = None
+    if k_grid is not None:
+        c0 = torch.tensor(np.asarray(cell, dtype=np.float64), dtype=_dt())
+        shape = tuple(int(v) for v in (k_grid.shape if hasattr(k_grid, "shape") else k_grid))
+        kspace = dict(positions=Rt + Rt @ eps.T, cell=c0 + c0 @ eps.T, grid=shape, smearing=float(np.asarray(k_smearing).reshape(-1)[0]))
     e_atom, aux = energy_from_graph(P, Z, disp(ii, jj), idx_i, idx_j, disp(il, jl), idx_i_lr, idx_j_lr,
                                     lr_format=lr_format, cutoff_lr=cutoff_lr, damping=damping,
                                     total_charge=total_charge, num_unpaired=num_unpaired,
-                                    batch_segments=batch_segments, num_graphs=num_graphs, record=record)
+                                    batch_segments=batch_segments, num_graphs=num_graphs, record=record, kspace=kspace)
     E = e_atom.sum()
     gR, gE = torch.autograd.grad(E, (Rt, eps))
     F = -gR

@@ -49,6 +49,8 @@ def _load():
         "so3lr_b200_unpack_rows": (i32, [p, i32, C.POINTER(p), C.POINTER(i32), p, i64, p]),
         "so3lr_b200_system_export_list": (i32, [p, p, p, i32, p, i64, C.POINTER(i64), C.POINTER(i32)]),
         "so3lr_b200_system_graph_eval": (i32, [p, p, i64, p, p, p, i64, p, p, p, p, p, p, p, p, p]),
+        "so3lr_b200_system_set_kspace": (i32, [p, i32, f32, i32, i32, i32]),
+        "so3lr_b200_system_graph_eval_kspace": (i32, [p, p, i64, p, p, p, i64, p, p, p, p, p, p, p, p, p, p]),
         "so3lr_b200_system_nve": (i32, [p, p, i32, f32, p, p, p, p, p]),
         "so3lr_b200_system_enable_virial": (i32, [p, i32]),
         "so3lr_b200_system_virial": (i32, [p, p, p]),
@@ -77,6 +79,7 @@ def _load():
         "so3lr_b200_host_sph_harm": (None, [f32, f32, f32, p]),
         "so3lr_b200_host_sph_harm_vjp": (None, [f32, f32, f32, p, p]),
         "so3lr_b200_host_pair_terms": (None, [f32, i32, i32, f32, f32, f32, f32, f32, f32, p]),
+        "so3lr_b200_host_coulomb_chi": (None, [f32, f32, f32, p]),
         "so3lr_b200_host_dispersion_fast": (None, [f32, i32, i32, f32, f32, f32, f32, p]),
         "so3lr_b200_host_zbl": (None, [p, f32, i32, i32, p]),
         "so3lr_b200_host_radial_filter": (None, [p, i32, C.c_double, p, p]),

@@ -54,24 +54,28 @@ class _GraphEnergy(torch.autograd.Function):
     reference takes, so3lr/jaxmd_utils.py:141); a non-uniform cotangent triggers one re-evaluation."""
 
     @staticmethod
-    def forward(ctx, edges, edges_lr, system, idx_i, idx_j, idx_i_lr, idx_j_lr, aux_out):
-        out = system.graph_eval(idx_i, idx_j, edges, idx_i_lr, idx_j_lr, edges_lr)
+    def forward(ctx, edges, edges_lr, system, idx_i, idx_j, idx_i_lr, idx_j_lr, aux_out, positions=None):
+        out = system.graph_eval(idx_i, idx_j, edges, idx_i_lr, idx_j_lr, edges_lr, positions=positions)
         ctx.system = system
         ctx.lists = (idx_i, idx_j, idx_i_lr, idx_j_lr)
-        ctx.save_for_backward(edges, edges_lr, out["g_edges"], out["g_edges_lr"])
+        ctx.has_positions = positions is not None
+        gp = out["g_positions"] if positions is not None else edges.new_zeros(0)
+        ctx.save_for_backward(edges, edges_lr, out["g_edges"], out["g_edges_lr"], gp)
         aux_out.update(partial_charges=out["partial_charges"], hirshfeld_ratios=out["hirshfeld_ratios"])
         return out["e_atom"]
 
     @staticmethod
     def backward(ctx, g):
-        edges, edges_lr, ge, gel = ctx.saved_tensors
+        edges, edges_lr, ge, gel, gp = ctx.saved_tensors
         g = g.contiguous()
         lo, hi = torch.aminmax(g)
         if bool(lo == hi):
             c = lo.to(ge.dtype)
-            return ge * c, gel * c, None, None, None, None, None, None
+            return ge * c, gel * c, None, None, None, None, None, None, (gp * c if ctx.has_positions else None)
+        if ctx.has_positions:
+            raise NotImplementedError("the reciprocal-space energy is differentiated for a uniform cotangent (its sum) only")
         out = ctx.system.graph_eval(ctx.lists[0], ctx.lists[1], edges, ctx.lists[2], ctx.lists[3], edges_lr, g_e_atom=g)
-        return out["g_edges"], out["g_edges_lr"], None, None, None, None, None, None
+        return out["g_edges"], out["g_edges_lr"], None, None, None, None, None, None, None
 
 
 class So3lrPotentialB200:
@@ -82,7 +86,7 @@ class So3lrPotentialB200:
     MAX_CACHED_SYSTEMS = 4      # evaluation contexts kept per potential (each holds every per-atom workspace of its system)
 
     def __init__(self, lr_cutoff=12.0, dispersion_energy_cutoff_lr_damping=2.0, neighborlist_format_lr="ordered_sparse",
-                 dtype=np.float32, device=None):
+                 dtype=np.float32, device=None, coulomb_kspace_do_ewald=False):
         """`dtype` is the dtype of the returned energies and gradients, as in the reference where it "determines the output
         dtype" of float32 parameters (tests/test_jaxmd.py:210-212): float32 or float64.  The kernels compute in float32 either
         way; with float64 the float32 results are widened, so they carry float32 accuracy (1e-7 relative on energies)."""
@@ -94,6 +98,9 @@ class So3lrPotentialB200:
         self.damping = dispersion_energy_cutoff_lr_damping
         self.neighborlist_format_lr = neighborlist_format_lr
         self.device = _dev(device)
+        # a graph that carries k_grid / k_smearing is evaluated with the Ewald sum when this is set; the reference's other choice,
+        # the mesh (PME) variant with `coulomb_kspace_interp_nodes` (so3lr/potential.py:11-12), is not part of this library
+        self.coulomb_kspace_do_ewald = bool(coulomb_kspace_do_ewald)
         self._systems = {}
 
     def system_for(self, species, cell=None, graph_start=None, total_charge=None, num_unpaired=None):
@@ -120,10 +127,24 @@ class So3lrPotentialB200:
         return s
 
     def __call__(self, graph: Graph, has_aux: bool = False):
-        for name in ("k_grid", "k_smearing"):
-            if getattr(graph, name) is not None:
-                raise NotImplementedError("k-space electrostatics (Ewald / PME) is not part of this library")
+        kspace = graph.k_grid is not None
+        if kspace:
+            if not self.coulomb_kspace_do_ewald:
+                raise NotImplementedError("the mesh (PME) variant of the k-space electrostatics is not part of this library; "
+                                          "create the potential with coulomb_kspace_do_ewald=True for the Ewald sum")
+            if graph.k_smearing is None or graph.positions is None or graph.cell is None:
+                raise ValueError("k-space electrostatics needs Graph.k_smearing, Graph.positions and Graph.cell")
         s = self.system_for(graph.nodes, total_charge=graph.total_charge, num_unpaired=graph.num_unpaired_electrons)
+        if kspace:
+            cell = np.asarray(graph.cell.detach().cpu(), dtype=np.float64).reshape(3, 3)
+            if s._cell is None or not np.array_equal(s._cell, cell):
+                s.set_cell(cell)
+            shape = tuple(int(v) for v in graph.k_grid.shape)
+            sm = float(np.asarray(torch.as_tensor(graph.k_smearing).detach().cpu(), dtype=np.float64).reshape(-1)[0])
+            if s.kspace != (shape, sm):
+                s.set_kspace(shape, sm)
+        elif s.kspace is not None:
+            s.set_kspace(None)
         edges, edges_lr = graph.edges, graph.edges_lr
         idx_i, idx_j, idx_i_lr, idx_j_lr = graph.centers, graph.others, graph.idx_i_lr, graph.idx_j_lr
         # the kernels want lists grouped by centre; jax-md style lists already are
@@ -136,7 +157,8 @@ class So3lrPotentialB200:
             idx_i_lr, idx_j_lr, edges_lr = idx_i_lr[perm_lr], idx_j_lr[perm_lr], edges_lr[perm_lr]
         aux = {}
         e = _GraphEnergy.apply(edges.to(self.device, torch.float32), edges_lr.to(self.device, torch.float32), s, idx_i, idx_j,
-                               idx_i_lr, idx_j_lr, aux).to(self.dtype)
+                               idx_i_lr, idx_j_lr, aux,
+                               graph.positions.to(self.device, torch.float32) if kspace else None).to(self.dtype)
         if not has_aux:
             return e
         aux.update(s.aux())
@@ -148,10 +170,24 @@ class So3lrPotentialB200:
 
 def make_potential_fn(lr_cutoff=12.0, dispersion_energy_cutoff_lr_damping=2.0, dtype=np.float32, coulomb_kspace_do_ewald=False,
                       coulomb_kspace_interp_nodes=4, **kwargs):
-    """so3lr/potential.py:7-29.  k-space options are accepted for signature compatibility and must stay off."""
-    if coulomb_kspace_do_ewald:
-        raise NotImplementedError("k-space electrostatics (Ewald / PME) is not part of this library")
-    return So3lrPotentialB200(lr_cutoff, dispersion_energy_cutoff_lr_damping, "ordered_sparse", dtype, kwargs.get("device"))
+    """so3lr/potential.py:7-29.  `coulomb_kspace_do_ewald=True` selects the Ewald sum for graphs that carry `k_grid` /
+    `k_smearing`; without it such graphs would take the mesh (PME) variant with `coulomb_kspace_interp_nodes`, which this library
+    does not have (the call then raises NotImplementedError)."""
+    return So3lrPotentialB200(lr_cutoff, dispersion_energy_cutoff_lr_damping, "ordered_sparse", dtype, kwargs.get("device"),
+                              coulomb_kspace_do_ewald=coulomb_kspace_do_ewald)
+
+
+def get_kgrid_ewald_shape(cell, lr_wavelength):
+    """Shape of the k-vector index grid for a resolution `lr_wavelength` (Angstrom): one index per `lr_wavelength` of each lattice
+    vector's length (argument convention of `jaxpme.kspace.get_kgrid_ewald` as called at so3lr/cli/so3lr_md.py:1421-1423)."""
+    c = np.asarray(cell.detach().cpu() if torch.is_tensor(cell) else cell, dtype=np.float64).reshape(3, 3)
+    lam = float(np.asarray(lr_wavelength.detach().cpu() if torch.is_tensor(lr_wavelength) else lr_wavelength).reshape(-1)[0])
+    return tuple(int(max(1, np.ceil(np.linalg.norm(c[d]) / lam - 1e-9))) for d in range(3))
+
+
+def get_kgrid_ewald(cell, lr_wavelength):
+    """An array whose SHAPE is the index grid (the only property of `k_grid` that the evaluation reads)."""
+    return torch.zeros(get_kgrid_ewald_shape(cell, lr_wavelength))
 
 
 # ------------------------------------------------------------------------------------------------------------
@@ -302,10 +338,12 @@ def neighbor_list_featurizer(displacement_fn, species, fractional_coordinates=Tr
                 cell_t = torch.eye(3, dtype=R.dtype, device=dev) * b.reshape(-1)[0]
             else:
                 raise ValueError(f"Invalid box shape {tuple(b.shape)}. Expected (3, 3), (3,), or (1,).")
-        for k in ("k_grid", "k_smearing"):
-            if kwargs.get(k) is not None:
-                raise NotImplementedError(f"`{k}` (k-space electrostatics) is not supported by this library")
+        k_grid, k_smearing = kwargs.get("k_grid"), kwargs.get("k_smearing")
         pert = kwargs.get("perturbation")
+        if k_grid is not None and pert is not None:
+            raise NotImplementedError("the strain derivative of the reciprocal-space energy is available from System.virial only")
+        if k_grid is not None and cell_t is None:
+            raise ValueError("k-space electrostatics needs `box`")
         Rc = _Transform.apply(R, cell_t) if (cell_t is not None and fractional_coordinates) else R
         neighbor, neighbor_lr = torch.as_tensor(neighbor, device=dev), torch.as_tensor(neighbor_lr, device=dev)
         idx_i, idx_j = neighbor[0].long(), neighbor[1].long()
@@ -323,7 +361,7 @@ def neighbor_list_featurizer(displacement_fn, species, fractional_coordinates=Tr
                 dR, dR_lr = dR @ p.T, dR_lr @ p.T
                 if cell_t is not None:
                     cell_t = cell_t @ p.T
-        return Graph(positions=None, nodes=species_t, edges=dR.float(), centers=neighbor[0], others=neighbor[1], mask=None,
+        return Graph(positions=Rc.float() if k_grid is not None else None, k_grid=k_grid, k_smearing=k_smearing, nodes=species_t, edges=dR.float(), centers=neighbor[0], others=neighbor[1], mask=None,
                      total_charge=torch.tensor([float(total_charge)]), num_unpaired_electrons=torch.zeros(1), edges_lr=dR_lr.float(),
                      idx_i_lr=neighbor_lr[0], idx_j_lr=neighbor_lr[1], cell=cell_t)
 

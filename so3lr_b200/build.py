@@ -8,7 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libso3lr_b200.so")
-SOURCES = ["model.cu", "atom_kernels.cu", "atom_kernels_mma.cu", "attention.cu", "attention_sym.cu", "attention_mma.cu", "attention_tc.cu", "dense_tc.cu", "halo.cu", "layer0_tab.cu", "pair_kernels.cu", "nlist.cu", "engine.cu", "noalloc.cu", "md.cu"]
+SOURCES = ["model.cu", "atom_kernels.cu", "atom_kernels_mma.cu", "attention.cu", "attention_sym.cu", "attention_mma.cu", "attention_tc.cu", "dense_tc.cu", "halo.cu", "kspace.cu", "layer0_tab.cu", "pair_kernels.cu", "nlist.cu", "engine.cu", "noalloc.cu", "md.cu"]
 FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "--expt-relaxed-constexpr",
          "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"] + os.environ.get("SO3LR_B200_NVCC_FLAGS", "").split()
 

@@ -259,6 +259,7 @@ struct so3lr_b200_system {
   so3lr_b200_options opt{};
   Cell cell{};
   LrParams lr{};
+  KSpaceDev ks{};                // reciprocal-space Coulomb part (off unless so3lr_b200_system_set_kspace switched it on)
   Pool pool;
   // static inputs.  d_Z is the array the kernels read: d_Z0 (caller order) or d_Zs (sorted order)
   int *d_Z = nullptr, *d_Z0 = nullptr, *d_Zs = nullptr, *d_seg = nullptr, *d_graph_start = nullptr;
@@ -503,9 +504,12 @@ bool graph_fast_path() {
 // returns at once -- no host read, so the call stays enqueue-only.
 int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, const int* nbr_j, const int* edge_i, long long n_edges,
                    const int* row_ptr_lr, const int* nbr_j_lr, const float* dR_in, const float* dR_lr_in, float* g_dR,
-                   float* g_dR_lr_out, const float* ge) {
+                   float* g_dR_lr_out, const float* ge, const float* positions = nullptr, float* g_positions = nullptr) {
   const ModelDev& M = S->mctx;
   const int n = S->n;
+  // the reciprocal-space part needs the positions and returns its own gradient; its per-atom energies are not separable, so a
+  // non-uniform upstream cotangent is not supported with it
+  if (S->ks.mode && (!positions || !g_positions || ge)) return kInvalidArgument;
   float* dR = const_cast<float*>(dR_in);
   const bool tiled = graph_fast_path() && attention_mode() == kAttnTc && n_edges > 0;
   int* asym = S->d_flag + 2;      // 1: some entry has no reversed partner (or the tiled path is off)
@@ -539,6 +543,11 @@ int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, co
   S->prof.begin(kPPairLr, st);
   launch_pair_lr(st, S->lr, S->cell, n, row_ptr_lr, nbr_j_lr, S->d_Z, nullptr, S->q, S->h, 1, dR_lr_in, g_dR_lr_out, nullptr, nullptr, S->gq,
                  S->gh, S->e_coul, S->e_disp, ge);
+  if (S->ks.mode) {
+    fill(st, g_positions, (size_t)n * 3, 0.f);
+    int rck = launch_ewald(st, S->ks, S->cell, n, positions, S->q, S->d_total_charge, S->e_coul, S->gq, g_positions, nullptr, -1.f);
+    if (rck) return rck;
+  }
   S->prof.end(st);
   { combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
   launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw, S->n, S->red_scratch);
@@ -582,6 +591,22 @@ int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, co
 // [n0, n1) atoms within one interaction shell of them, [n1, n2) within two, [n2, n3) within three.  Layer l of the
 // network is evaluated for the atoms that the owned atoms' energies can still see; a single-GPU evaluation has
 // n0 = n1 = n2 = n3 = n.
+// value and slope at the cutoff of the pair function the Coulomb term shifts: erf(r / sigma) / r, minus erf(r k_alpha) / r when the
+// reciprocal-space sum holds that part
+void set_coulomb_shift(LrParams& P) {
+  if (!P.has_cutoff) return;
+  const double rc = P.rc, sg = kSigmaCoulomb;
+  double pot = std::erf(rc / sg) / rc;
+  double dpot = (2.0 / std::sqrt(M_PI) / sg * std::exp(-(rc / sg) * (rc / sg)) - pot) / rc;
+  if (P.k_alpha > 0.f) {
+    const double a = P.k_alpha;
+    const double potk = std::erf(rc * a) / rc;
+    pot -= potk;
+    dpot -= (2.0 / std::sqrt(M_PI) * a * std::exp(-(rc * a) * (rc * a)) - potk) / rc;
+  }
+  P.v_rc = (float)pot; P.dv_rc = (float)dpot;
+}
+
 struct Shells { int n0, n1, n2, n3; };
 
 constexpr int kVirialBlocks = 1024;   // capacity of the block-partials buffer of the virial reduction
@@ -695,6 +720,10 @@ int evaluate_fused(so3lr_b200_system* S, cudaStream_t st, const float* R, float*
   S->prof.begin(kPPairLr, st);
   launch_pair_lr_packed(st, S->lr, S->cell, n, S->lrl.row_ptr, S->lrl.nbr_j, S->d_Z, R, S->q, S->h, S->pair_pack, F, S->gq, S->gh, S->e_coul,
                         S->e_disp, S->vir());
+  if (S->ks.mode) {
+    rc = launch_ewald(st, S->ks, S->cell, n, R, S->q, S->d_total_charge, S->e_coul, S->gq, F, S->vir(), 1.f);
+    if (rc) return rc;
+  }
   S->prof.end(st);
   { combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
   launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw, S->n, S->red_scratch);
@@ -844,12 +873,8 @@ SO3LR_B200_API int so3lr_b200_system_create(so3lr_b200_model* model, int n_atoms
   P.has_damping = options->damping > 0.f;
   P.disp_on = options->cutoff_lr - options->damping;
   P.pair_factor = options->lr_both_directions ? 0.5f : 1.f;
-  if (P.has_cutoff) {
-    double rcd = options->cutoff_lr, sg = kSigmaCoulomb;
-    double pot = std::erf(rcd / sg) / rcd;
-    double dpot = (2.0 / std::sqrt(M_PI) / sg * std::exp(-(rcd / sg) * (rcd / sg)) - pot) / rcd;
-    P.v_rc = (float)pot; P.dv_rc = (float)dpot;
-  }
+  P.k_alpha = 0.f;
+  set_coulomb_shift(P);
   const int n = n_atoms;
   Pool& A = S->pool;
   S->d_Z0 = A.get<int>(n); S->d_Zs = A.get<int>(n); S->d_Z = S->d_Z0; S->d_perm = A.get<int>(n);
@@ -950,6 +975,7 @@ SO3LR_B200_API int so3lr_b200_system_destroy(so3lr_b200_system* S) {
   tc_debug_print();
   dense_debug_print();
   S->pool.release();
+  kspace_free(&S->ks);
   species_tables_free(&S->sp);
   S->prof.destroy();
   nlist_workspace_destroy(S->nws);
@@ -977,6 +1003,26 @@ SO3LR_B200_API int so3lr_b200_system_set_cell(so3lr_b200_system* S, const float*
   if (rc) return rc;
   S->have_lists = false;
   S->virial_fresh = false;
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_set_kspace(so3lr_b200_system* S, int mode, float smearing, int n1, int n2, int n3) {
+  if (!S || (mode != 0 && mode != 1)) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  SO3LR_CUDA_CHECK(cudaDeviceSynchronize());
+  S->virial_fresh = false;
+  if (mode == 0) {
+    kspace_free(&S->ks);
+    S->lr.k_alpha = 0.f;
+    set_coulomb_shift(S->lr);
+    return kOk;
+  }
+  // one periodic structure whose pair sum is cut off: the split needs a short-ranged pair part
+  if (!S->cell.periodic || S->n_graphs != 1 || !S->lr.has_cutoff || !(smearing > 0.f)) return kInvalidArgument;
+  int rc = kspace_setup(&S->ks, S->n_cap, smearing, n1, n2, n3);
+  if (rc) return rc;
+  S->lr.k_alpha = (float)(1.0 / (std::sqrt(2.0) * (double)smearing));
+  set_coulomb_shift(S->lr);
   return kOk;
 }
 
@@ -1162,10 +1208,10 @@ SO3LR_B200_API int so3lr_b200_system_export_list(so3lr_b200_system* S, void* str
   return kOk;
 }
 
-SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* S, void* stream, int64_t n_edges, const int32_t* idx_i, const int32_t* idx_j,
-                                 const float* edges, int64_t n_pairs, const int32_t* idx_i_lr, const int32_t* idx_j_lr,
-                                 const float* edges_lr, const float* g_e_atom, float* e_atom, float* g_edges, float* g_edges_lr,
-                                 float* charges, float* hirshfeld) {
+static int graph_eval_impl(so3lr_b200_system* S, void* stream, int64_t n_edges, const int32_t* idx_i, const int32_t* idx_j,
+                           const float* edges, int64_t n_pairs, const int32_t* idx_i_lr, const int32_t* idx_j_lr,
+                           const float* edges_lr, const float* g_e_atom, float* e_atom, float* g_edges, float* g_edges_lr,
+                           float* charges, float* hirshfeld, const float* positions, float* g_positions) {
   if (!S || !idx_i || !idx_j || !edges || !g_edges || n_edges < 0 || n_pairs < 0) return kInvalidArgument;
   if (n_pairs > 0 && (!idx_i_lr || !idx_j_lr || !edges_lr || !g_edges_lr)) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
@@ -1178,12 +1224,29 @@ SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* S, void* stre
   { row_ptr_from_sorted_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(n, n_edges, idx_i, S->d_rowptr_g); count_launch(); }
   { row_ptr_from_sorted_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(n, n_pairs, idx_i_lr, S->d_rowptr_lr_g); count_launch(); }
   int rc = evaluate_graph(S, st, S->d_rowptr_g, idx_j, idx_i, n_edges, S->d_rowptr_lr_g, idx_j_lr, edges, edges_lr, g_edges, g_edges_lr,
-                          g_e_atom);
+                          g_e_atom, positions, g_positions);
   if (rc) return rc;
   if (e_atom) SO3LR_CUDA_CHECK(cudaMemcpyAsync(e_atom, S->e_atom, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
   if (charges) SO3LR_CUDA_CHECK(cudaMemcpyAsync(charges, S->q, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
   if (hirshfeld) SO3LR_CUDA_CHECK(cudaMemcpyAsync(hirshfeld, S->h, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
   return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* S, void* stream, int64_t n_edges, const int32_t* idx_i, const int32_t* idx_j,
+                                 const float* edges, int64_t n_pairs, const int32_t* idx_i_lr, const int32_t* idx_j_lr,
+                                 const float* edges_lr, const float* g_e_atom, float* e_atom, float* g_edges, float* g_edges_lr,
+                                 float* charges, float* hirshfeld) {
+  return graph_eval_impl(S, stream, n_edges, idx_i, idx_j, edges, n_pairs, idx_i_lr, idx_j_lr, edges_lr, g_e_atom, e_atom, g_edges, g_edges_lr,
+                         charges, hirshfeld, nullptr, nullptr);
+}
+
+SO3LR_B200_API int so3lr_b200_system_graph_eval_kspace(so3lr_b200_system* S, void* stream, int64_t n_edges, const int32_t* idx_i,
+                                        const int32_t* idx_j, const float* edges, int64_t n_pairs, const int32_t* idx_i_lr,
+                                        const int32_t* idx_j_lr, const float* edges_lr, const float* positions, float* e_atom,
+                                        float* g_edges, float* g_edges_lr, float* g_positions, float* charges, float* hirshfeld) {
+  if (!S || !S->ks.mode || !positions || !g_positions) return kInvalidArgument;
+  return graph_eval_impl(S, stream, n_edges, idx_i, idx_j, edges, n_pairs, idx_i_lr, idx_j_lr, edges_lr, nullptr, e_atom, g_edges, g_edges_lr,
+                         charges, hirshfeld, positions, g_positions);
 }
 
 SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* S, void* stream, int n_steps, float dt, const float* masses, float* R, float* V,
@@ -1394,6 +1457,10 @@ SO3LR_B200_API int so3lr_b200_dd_set_atoms(so3lr_b200_system* S, int n_local, co
                                            const float* cell9) {
   if (!S || !shells4 || !Z_local_dev || n_local <= 0) return kInvalidArgument;
   if (S->n_graphs != 1) return kInvalidArgument;
+  if (S->ks.mode) {
+    std::fprintf(stderr, "so3lr_b200: the reciprocal-space Coulomb sum is not available in a decomposed evaluation\n");
+    return kInvalidArgument;
+  }
   if (S->mctx.embed_z != S->model->M.embed_z) {
     std::fprintf(stderr, "so3lr_b200: a decomposed evaluation of a charged or open-shell structure is not supported (the charge embedding "
                          "needs the composition of the whole structure)\n");
@@ -1643,17 +1710,20 @@ SO3LR_B200_API void so3lr_b200_host_pair_terms(float r, int zi, int zj, float qi
   LrParams P{};
   P.has_cutoff = cutoff_lr > 0.f; P.rc = cutoff_lr; P.cuton = kCutonFraction * cutoff_lr; P.has_damping = damping > 0.f;
   P.disp_on = cutoff_lr - damping; P.pair_factor = 1.f;
-  if (P.has_cutoff) {
-    double rcd = cutoff_lr, sg = kSigmaCoulomb;
-    double pot = std::erf(rcd / sg) / rcd;
-    P.v_rc = (float)pot;
-    P.dv_rc = (float)((2.0 / std::sqrt(M_PI) / sg * std::exp(-(rcd / sg) * (rcd / sg)) - pot) / rcd);
-  }
+  set_coulomb_shift(P);
   float chi, dchi;
   coulomb_chi(P, r, chi, dchi);
   out8[0] = kKe * qi * qj * chi; out8[1] = kKe * qi * qj * dchi; out8[2] = kKe * qj * chi;
   dispersion_pair(P, r, zi, zj, hi, hj, out8[3], out8[4], out8[5], out8[6]);
   out8[7] = 0.f;
+}
+// chi(r) and its derivative of the Coulomb pair function with the reciprocal-space part taken out (smearing > 0) or not (0)
+SO3LR_B200_API void so3lr_b200_host_coulomb_chi(float r, float cutoff_lr, float smearing, float* out2) {
+  LrParams P{};
+  P.has_cutoff = cutoff_lr > 0.f; P.rc = cutoff_lr; P.cuton = kCutonFraction * cutoff_lr; P.pair_factor = 1.f;
+  P.k_alpha = smearing > 0.f ? (float)(1.0 / (std::sqrt(2.0) * (double)smearing)) : 0.f;
+  set_coulomb_shift(P);
+  coulomb_chi(P, r, out2[0], out2[1]);
 }
 SO3LR_B200_API void so3lr_b200_host_dispersion_fast(float r, int zi, int zj, float hi, float hj, float cutoff_lr, float damping, float* out4) {
   LrParams P{};

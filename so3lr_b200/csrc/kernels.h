@@ -48,6 +48,24 @@ void launch_heads_fwd_tc(cudaStream_t s, const ModelDev& M, int n, const int* Z,
 void launch_heads_bwd_tc(cudaStream_t s, const ModelDev& M, int n, const int* Z, const float* ze, const float* zq, const float* zh,
                          const float* hv, const float* ge, const float* gq, const float* gh, float* gx, int* err);
 
+// ---- kspace.cu: reciprocal-space (Ewald) part of the electrostatic energy of one periodic structure ----
+struct KSpaceDev {
+  int mode = 0;            // 0 off, 1 Ewald sum over the index grid
+  float smearing = 0.f;    // Gaussian width s of the split erf(r / (sqrt(2) s)) / r
+  int shape[3] = {0, 0, 0};
+  int n_tiles = 0;
+  int4* tiles = nullptr;   // (h1, first h2, first h3, -) of each 16 x 16 tile of kept indices
+  float* wgt = nullptr;    // [n_tiles][256] 2 / 1 / 0: member of a (k, -k) pair, unpaired index, not part of the sum
+  float2* Sk = nullptr;    // [n_tiles][256] structure factors
+  float* acc = nullptr;    // [n_atoms][4] potential and the three index-weighted force sums
+};
+int kspace_setup(KSpaceDev* K, int n_atoms, float smearing, int n1, int n2, int n3);   // allocates; call outside handlers
+void kspace_free(KSpaceDev* K);
+// adds to e_coul (per-atom energies), gq (dE/dq), F (force_sign = 1: forces at fixed charges; -1: the gradient) and, when given, the
+// six virial components of one row
+int launch_ewald(cudaStream_t st, const KSpaceDev& K, const Cell& cell, int n, const float* R, const float* q, const float* total_charge,
+                 float* e_coul, float* gq, float* F, float* virial_row, float force_sign);
+
 // ---- halo.cu: rows idx[r] of up to four row-major float arrays <-> one packed buffer [n_rows][sum of widths] ----
 int pack_rows(void* stream, int n_arrays, float* const* arrays, const int* widths, const int64_t* idx, int64_t n_rows, float* buf, bool unpack);
 

@@ -1,0 +1,303 @@
+// Reciprocal-space (Ewald) part of the electrostatic energy for one periodic structure: the path the reference takes when its
+// energy function is called with `k_grid` and `k_smearing` (so3lr/jaxmd_utils.py:39-47,70-71; grid from
+// jaxpme.kspace.get_kgrid_ewald, so3lr/cli/so3lr_md.py:1392-1428).  Published Ewald summation for Gaussian-smeared charges:
+//
+//   E_k = ke / (2 V) sum_{k != 0} (4 pi / k^2) exp(-s^2 k^2 / 2) |S(k)|^2 - ke sum_i q_i^2 / (sqrt(2 pi) s) - ke pi s^2 Q^2 / V,
+//   S(k) = sum_i q_i exp(i k r_i),   k = 2 pi (h1 b1 + h2 b2 + h3 b3) on the FFT-frequency index grid of shape (n1, n2, n3).
+//
+// S(-k) = conj S(k), so one vector of every pair (k, -k) is kept with weight 2 (an index -n/2 of an even grid has no partner and
+// keeps weight 1).  The kept indices are cut into tiles of 16 x 16 (h2, h3) values at one h1.  exp(i k r) factorises over the three
+// indices, so a tile needs 32 sines and cosines per atom instead of 256:
+//   ewald_structure_kernel  thread = k vector of a tile, loops over a slice of the atoms staged in shared memory (4 FMAs per pair)
+//   ewald_atom_kernel       thread = atom, loops over a slice of the tiles; potential phi_i and the three index-weighted sums that
+//                           give the force (8 FMAs per pair)
+//   ewald_finish_kernel     per atom: energy, dE/dq (it continues into the charge head's reverse pass), force
+//   ewald_virial_kernel     strain derivative, added to the first atom's virial row (the rows are only ever summed)
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace so3lr {
+
+namespace {
+
+constexpr int kTile = 16;
+constexpr int kTileK = kTile * kTile;
+constexpr int kStage = 64;                 // atoms per shared-memory stage of the structure-factor kernel
+constexpr float kTwoPi = 6.283185307179586f;
+
+// f * h modulo 1 in [-1/2, 1/2]: the product is formed exactly inside the FMA, so the result carries the rounding of f only
+__device__ __forceinline__ float phase_frac(float f, int h) {
+  const float hf = (float)h;
+  return fmaf(f, hf, -rintf(f * hf));
+}
+// exp(2 pi i x) for |x| <= 1
+__device__ __forceinline__ void unit_phase(float x, float& c, float& s) {
+  x -= rintf(x);
+  __sincosf(kTwoPi * x, &s, &c);
+}
+__device__ __forceinline__ void fractional(const Cell& c, const float* __restrict__ R, int a, float& f1, float& f2, float& f3) {
+  const float x = R[3 * (size_t)a], y = R[3 * (size_t)a + 1], z = R[3 * (size_t)a + 2];
+  f1 = x * c.hinv[0] + y * c.hinv[3] + z * c.hinv[6];
+  f2 = x * c.hinv[1] + y * c.hinv[4] + z * c.hinv[7];
+  f3 = x * c.hinv[2] + y * c.hinv[5] + z * c.hinv[8];
+  f1 -= floorf(f1); f2 -= floorf(f2); f3 -= floorf(f3);
+}
+// Cartesian k vector of an index triple: k_a = 2 pi sum_d hinv[a][d] h_d
+__device__ __forceinline__ void k_vector(const Cell& c, int h1, int h2, int h3, float& kx, float& ky, float& kz) {
+  kx = kTwoPi * (c.hinv[0] * h1 + c.hinv[1] * h2 + c.hinv[2] * h3);
+  ky = kTwoPi * (c.hinv[3] * h1 + c.hinv[4] * h2 + c.hinv[5] * h3);
+  kz = kTwoPi * (c.hinv[6] * h1 + c.hinv[7] * h2 + c.hinv[8] * h3);
+}
+// weight x ke / V x 4 pi exp(-s^2 k^2 / 2) / k^2
+__device__ __forceinline__ float k_weight(float w, float inv_vol, float smearing, float k2) {
+  return w * kKe * inv_vol * 12.566370614359172f * expf(-0.5f * smearing * smearing * k2) / k2;
+}
+
+__global__ void __launch_bounds__(kTileK) ewald_structure_kernel(Cell cell, int n, int atoms_per_split, const float* __restrict__ R,
+                                                                  const float* __restrict__ q, const int4* __restrict__ tiles,
+                                                                  float2* __restrict__ Sk) {
+  __shared__ float2 T[kStage][2 * kTile];    // per atom: q exp(2 pi i (f1 h1 + f2 h2)) for the tile's 16 h2, exp(2 pi i f3 h3) for its 16 h3
+  __shared__ float4 A[kStage];               // f1 f2 f3 q
+  const int4 t = tiles[blockIdx.x];
+  const int tid = threadIdx.x, t2 = tid >> 4, t3 = tid & 15;
+  const int a0 = blockIdx.y * atoms_per_split;
+  const int a1 = a0 + atoms_per_split < n ? a0 + atoms_per_split : n;
+  float sr = 0.f, si = 0.f;
+  for (int base = a0; base < a1; base += kStage) {
+    __syncthreads();
+    if (tid < kStage) {
+      const int a = base + tid;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (a < a1) {
+        fractional(cell, R, a, v.x, v.y, v.z);
+        v.w = q[a];
+      }
+      A[tid] = v;
+    }
+    __syncthreads();
+    for (int e = tid; e < kStage * 2 * kTile; e += kTileK) {
+      const int a = e >> 5, j = e & 31;
+      const float4 v = A[a];
+      float c, s;
+      if (j < kTile) {
+        unit_phase(phase_frac(v.x, t.x) + phase_frac(v.y, t.y + j), c, s);
+        T[a][j] = make_float2(v.w * c, v.w * s);
+      } else {
+        unit_phase(phase_frac(v.z, t.z + j - kTile), c, s);
+        T[a][j] = make_float2(c, s);
+      }
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int a = 0; a < kStage; ++a) {
+      const float2 u = T[a][t2], w = T[a][kTile + t3];
+      sr = fmaf(u.x, w.x, sr); sr = fmaf(-u.y, w.y, sr);
+      si = fmaf(u.x, w.y, si); si = fmaf(u.y, w.x, si);
+    }
+  }
+  float2* out = Sk + (size_t)blockIdx.x * kTileK + tid;
+  atomicAdd(&out->x, sr);
+  atomicAdd(&out->y, si);
+}
+
+// acc rows: phi_i, and sum_k G h_d Im[S(k) exp(-i k r_i)] for d = 1, 2, 3
+__global__ void __launch_bounds__(128) ewald_atom_kernel(Cell cell, float inv_vol, float smearing, int n, int n_tiles, int tiles_per_split,
+                                                         const float* __restrict__ R, const int4* __restrict__ tiles,
+                                                         const float* __restrict__ wgt, const float2* __restrict__ Sk,
+                                                         float* __restrict__ acc) {
+  __shared__ float2 A[kTileK];               // weight x S(k) of the current tile
+  const int tid = threadIdx.x;
+  const int a = blockIdx.x * 128 + tid;
+  float f1 = 0.f, f2 = 0.f, f3 = 0.f;
+  if (a < n) fractional(cell, R, a, f1, f2, f3);
+  float phi = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+  const int tile0 = blockIdx.y * tiles_per_split;
+  const int tile1 = tile0 + tiles_per_split < n_tiles ? tile0 + tiles_per_split : n_tiles;
+  for (int tile = tile0; tile < tile1; ++tile) {
+    const int4 t = tiles[tile];
+    __syncthreads();
+    for (int s = tid; s < kTileK; s += 128) {
+      const float w = wgt[(size_t)tile * kTileK + s];
+      float2 v = make_float2(0.f, 0.f);
+      if (w > 0.f) {
+        float kx, ky, kz;
+        k_vector(cell, t.x, t.y + (s >> 4), t.z + (s & 15), kx, ky, kz);
+        const float g = k_weight(w, inv_vol, smearing, kx * kx + ky * ky + kz * kz);
+        const float2 sk = Sk[(size_t)tile * kTileK + s];
+        v = make_float2(g * sk.x, g * sk.y);
+      }
+      A[s] = v;
+    }
+    __syncthreads();
+    float c3[kTile], s3[kTile];
+#pragma unroll
+    for (int j = 0; j < kTile; ++j) unit_phase(phase_frac(f3, t.z + j), c3[j], s3[j]);
+    const float x1 = phase_frac(f1, t.x);
+    const float h1f = (float)t.x;
+#pragma unroll 1
+    for (int i2 = 0; i2 < kTile; ++i2) {
+      float ur = 0.f, ui = 0.f, vr = 0.f, vi = 0.f;      // sum over h3 of A conj(T3), and of h3 A conj(T3)
+#pragma unroll
+      for (int j = 0; j < kTile; ++j) {
+        const float2 av = A[i2 * kTile + j];
+        const float pr = fmaf(av.x, c3[j], av.y * s3[j]);
+        const float pi = fmaf(av.y, c3[j], -av.x * s3[j]);
+        const float h3f = (float)(t.z + j);
+        ur += pr; ui += pi;
+        vr = fmaf(h3f, pr, vr); vi = fmaf(h3f, pi, vi);
+      }
+      float c, s;
+      unit_phase(x1 + phase_frac(f2, t.y + i2), c, s);
+      const float wr = fmaf(ur, c, ui * s);               // (u)(c - i s)
+      const float wi = fmaf(ui, c, -ur * s);
+      const float vim = fmaf(vi, c, -vr * s);
+      phi += wr;
+      d1 = fmaf(h1f, wi, d1);
+      d2 = fmaf((float)(t.y + i2), wi, d2);
+      d3 += vim;
+    }
+  }
+  if (a < n) {
+    float* o = acc + 4 * (size_t)a;
+    atomicAdd(o, phi); atomicAdd(o + 1, d1); atomicAdd(o + 2, d2); atomicAdd(o + 3, d3);
+  }
+}
+
+__global__ void __launch_bounds__(256) ewald_finish_kernel(Cell cell, float inv_vol, float smearing, int n, const float* __restrict__ q,
+                                                           const float* __restrict__ total_charge, const float* __restrict__ acc,
+                                                           float* __restrict__ e_coul, float* __restrict__ gq, float* __restrict__ F,
+                                                           float force_sign) {
+  const int a = blockIdx.x * blockDim.x + threadIdx.x;
+  if (a >= n) return;
+  const float4 v = *reinterpret_cast<const float4*>(acc + 4 * (size_t)a);
+  const float qa = q[a];
+  const float self = kKe * 0.7978845608028654f / smearing;                                  // ke sqrt(2 / pi) / s
+  const float bg = kKe * 3.141592653589793f * smearing * smearing * inv_vol * total_charge[0];
+  e_coul[a] += 0.5f * qa * v.x - 0.5f * self * qa * qa - bg * qa;
+  gq[a] += v.x - self * qa - 2.f * bg;
+  const float s = -kTwoPi * qa * force_sign;
+  float* f = F + 3 * (size_t)a;
+  f[0] += s * (cell.hinv[0] * v.y + cell.hinv[1] * v.z + cell.hinv[2] * v.w);
+  f[1] += s * (cell.hinv[3] * v.y + cell.hinv[4] * v.z + cell.hinv[5] * v.w);
+  f[2] += s * (cell.hinv[6] * v.y + cell.hinv[7] * v.z + cell.hinv[8] * v.w);
+}
+
+// dE_k / d eps_ab = sum_k G |S|^2 / 2 (-delta_ab + 2 k_a k_b (s^2 / 2 + 1 / k^2)) + delta_ab ke pi s^2 Q^2 / V
+__global__ void __launch_bounds__(kTileK) ewald_virial_kernel(Cell cell, float inv_vol, float smearing, const int4* __restrict__ tiles,
+                                                              const float* __restrict__ wgt, const float2* __restrict__ Sk,
+                                                              const float* __restrict__ total_charge, float* __restrict__ virial_row) {
+  __shared__ float part[8][6];
+  const int tid = threadIdx.x;
+  const int4 t = tiles[blockIdx.x];
+  const float w = wgt[(size_t)blockIdx.x * kTileK + tid];
+  float v[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (w > 0.f) {
+    float kx, ky, kz;
+    k_vector(cell, t.x, t.y + (tid >> 4), t.z + (tid & 15), kx, ky, kz);
+    const float k2 = kx * kx + ky * ky + kz * kz;
+    const float2 sk = Sk[(size_t)blockIdx.x * kTileK + tid];
+    const float e = 0.5f * k_weight(w, inv_vol, smearing, k2) * (sk.x * sk.x + sk.y * sk.y);
+    const float m = 2.f * (0.5f * smearing * smearing + 1.f / k2);
+    v[0] = e * (m * kx * kx - 1.f); v[1] = e * (m * ky * ky - 1.f); v[2] = e * (m * kz * kz - 1.f);
+    v[3] = e * m * ky * kz; v[4] = e * m * kx * kz; v[5] = e * m * kx * ky;
+  }
+  if (blockIdx.x == 0 && tid == 0) {
+    const float qt = total_charge[0];
+    const float b = kKe * 3.141592653589793f * smearing * smearing * inv_vol * qt * qt;
+    v[0] += b; v[1] += b; v[2] += b;
+  }
+#pragma unroll
+  for (int c = 0; c < 6; ++c) v[c] = warp_sum(v[c]);
+  if ((tid & 31) == 0)
+    for (int c = 0; c < 6; ++c) part[tid >> 5][c] = v[c];
+  __syncthreads();
+  if (tid < 6) {
+    float s = 0.f;
+    for (int wp = 0; wp < kTileK / 32; ++wp) s += part[wp][tid];
+    atomicAdd(virial_row + tid, s);
+  }
+}
+
+}  // namespace
+
+void kspace_free(KSpaceDev* K) {
+  cudaFree(K->tiles); cudaFree(K->wgt); cudaFree(K->Sk); cudaFree(K->acc);
+  *K = KSpaceDev{};
+}
+
+int kspace_setup(KSpaceDev* K, int n_atoms, float smearing, int n1, int n2, int n3) {
+  kspace_free(K);
+  if (!(smearing > 0.f) || n1 < 1 || n2 < 1 || n3 < 1 || n1 > 1024 || n2 > 1024 || n3 > 1024) return kInvalidArgument;
+  const int nn[3] = {n1, n2, n3};
+  int lo[3], hi[3];
+  for (int d = 0; d < 3; ++d) { lo[d] = -(nn[d] / 2); hi[d] = (nn[d] + 1) / 2 - 1; }
+  auto inside = [&](int a, int b, int c) { return a >= lo[0] && a <= hi[0] && b >= lo[1] && b <= hi[1] && c >= lo[2] && c <= hi[2]; };
+  // weight of an index triple: 2 for the kept member of a pair (k, -k), 0 for the other, 1 when -k is outside the grid
+  auto weight = [&](int a, int b, int c) -> float {
+    if (!inside(a, b, c) || (a == 0 && b == 0 && c == 0)) return 0.f;
+    if (!inside(-a, -b, -c)) return 1.f;
+    const bool positive = a > 0 || (a == 0 && (b > 0 || (b == 0 && c > 0)));
+    return positive ? 2.f : 0.f;
+  };
+  std::vector<int4> tiles;
+  std::vector<float> wgt;
+  for (int h1 = lo[0]; h1 <= hi[0]; ++h1)
+    for (int b0 = lo[1]; b0 <= hi[1]; b0 += kTile)
+      for (int c0 = lo[2]; c0 <= hi[2]; c0 += kTile) {
+        float w[kTileK];
+        bool any = false;
+        for (int s = 0; s < kTileK; ++s) { w[s] = weight(h1, b0 + (s >> 4), c0 + (s & 15)); any |= w[s] > 0.f; }
+        if (!any) continue;
+        tiles.push_back(make_int4(h1, b0, c0, 0));
+        wgt.insert(wgt.end(), w, w + kTileK);
+      }
+  if (tiles.empty() || tiles.size() > (size_t)(1 << 22)) return tiles.empty() ? kInvalidArgument : kTooLarge;
+  K->n_tiles = (int)tiles.size();
+  K->smearing = smearing;
+  K->shape[0] = n1; K->shape[1] = n2; K->shape[2] = n3;
+  SO3LR_CUDA_CHECK(cudaMalloc((void**)&K->tiles, tiles.size() * sizeof(int4)));
+  SO3LR_CUDA_CHECK(cudaMalloc((void**)&K->wgt, wgt.size() * sizeof(float)));
+  SO3LR_CUDA_CHECK(cudaMalloc((void**)&K->Sk, wgt.size() * sizeof(float2)));
+  SO3LR_CUDA_CHECK(cudaMalloc((void**)&K->acc, (size_t)n_atoms * 4 * sizeof(float)));
+  SO3LR_CUDA_CHECK(cudaMemcpy(K->tiles, tiles.data(), tiles.size() * sizeof(int4), cudaMemcpyHostToDevice));
+  SO3LR_CUDA_CHECK(cudaMemcpy(K->wgt, wgt.data(), wgt.size() * sizeof(float), cudaMemcpyHostToDevice));
+  K->mode = 1;
+  return kOk;
+}
+
+int launch_ewald(cudaStream_t st, const KSpaceDev& K, const Cell& cell, int n, const float* R, const float* q, const float* total_charge,
+                 float* e_coul, float* gq, float* F, float* virial_row, float force_sign) {
+  if (K.mode != 1 || !cell.periodic) return kInvalidArgument;
+  const float* h = cell.h;
+  const double det = (double)h[0] * ((double)h[4] * h[8] - (double)h[5] * h[7]) - (double)h[1] * ((double)h[3] * h[8] - (double)h[5] * h[6]) +
+                     (double)h[2] * ((double)h[3] * h[7] - (double)h[4] * h[6]);
+  const float inv_vol = (float)(1.0 / (det < 0 ? -det : det));
+  SO3LR_CUDA_CHECK(cudaMemsetAsync(K.Sk, 0, (size_t)K.n_tiles * kTileK * sizeof(float2), st));
+  SO3LR_CUDA_CHECK(cudaMemsetAsync(K.acc, 0, (size_t)n * 4 * sizeof(float), st));
+  const int target = 4 * sm_count();
+  // structure factors: tiles x atom slices
+  int splits = (target + K.n_tiles - 1) / K.n_tiles;
+  const int max_splits = (n + kStage - 1) / kStage;
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  int per = (n + splits - 1) / splits;
+  per = (per + kStage - 1) / kStage * kStage;
+  splits = (n + per - 1) / per;
+  { ewald_structure_kernel<<<dim3(K.n_tiles, splits), kTileK, 0, st>>>(cell, n, per, R, q, K.tiles, K.Sk); count_launch(); }
+  // per-atom sums: atom blocks x tile slices
+  const int blocks = (n + 127) / 128;
+  int ksplits = (target + blocks - 1) / blocks;
+  if (ksplits > K.n_tiles) ksplits = K.n_tiles;
+  if (ksplits < 1) ksplits = 1;
+  const int tper = (K.n_tiles + ksplits - 1) / ksplits;
+  ksplits = (K.n_tiles + tper - 1) / tper;
+  { ewald_atom_kernel<<<dim3(blocks, ksplits), 128, 0, st>>>(cell, inv_vol, K.smearing, n, K.n_tiles, tper, R, K.tiles, K.wgt, K.Sk, K.acc); count_launch(); }
+  { ewald_finish_kernel<<<(n + 255) / 256, 256, 0, st>>>(cell, inv_vol, K.smearing, n, q, total_charge, K.acc, e_coul, gq, F, force_sign); count_launch(); }
+  if (virial_row) { ewald_virial_kernel<<<K.n_tiles, kTileK, 0, st>>>(cell, inv_vol, K.smearing, K.tiles, K.wgt, K.Sk, total_charge, virial_row); count_launch(); }
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+}  // namespace so3lr

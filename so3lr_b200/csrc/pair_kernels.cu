@@ -92,8 +92,14 @@ __device__ __forceinline__ void switching_dev(float x, float on, float off, floa
 __device__ __forceinline__ void coulomb_chi_dev(const LrParams& p, float r, float rinv, float& chi, float& dchi) {
   const float inv_sig = 1.f / kSigmaCoulomb;
   const float x = r * inv_sig;
-  const float pot = erff(x) * rinv;
-  const float dpot = (1.1283791670955126f * inv_sig * __expf(-x * x) - pot) * rinv;
+  float pot = erff(x) * rinv;
+  float dpot = (1.1283791670955126f * inv_sig * __expf(-x * x) - pot) * rinv;
+  if (p.k_alpha > 0.f) {     // the reciprocal-space sum holds erf(r k_alpha) / r
+    const float y = r * p.k_alpha;
+    const float potk = erff(y) * rinv;
+    pot -= potk;
+    dpot -= (1.1283791670955126f * p.k_alpha * __expf(-y * y) - potk) * rinv;
+  }
   if (!p.has_cutoff) { chi = pot; dchi = dpot; return; }
   float f, df;
   switching_dev(r, p.cuton, p.rc, f, df);

@@ -53,6 +53,7 @@ struct LrParams {
   int has_damping;      // dispersion switched off between rc - damping and rc
   float disp_on;        // rc - damping
   float pair_factor;    // 1 for ordered lists, 0.5 for lists holding both directions
+  float k_alpha;        // 1 / (sqrt(2) s) when the reciprocal-space sum holds erf(r / (sqrt(2) s)) / r of every pair; 0: off
 };
 
 // erf-damped Coulomb kernel chi(r) (energy = ke q_i q_j chi) and d chi / d r
@@ -62,6 +63,12 @@ SO3LR_HD void coulomb_chi(const LrParams& p, float r, float& chi, float& dchi) {
   float er = erff(x);
   float pot = er / r;
   float dpot = (1.1283791670955126f * inv_sig * expf(-x * x) - pot) / r;
+  if (p.k_alpha > 0.f) {
+    const float y = r * p.k_alpha;
+    const float potk = erff(y) / r;
+    pot -= potk;
+    dpot -= (1.1283791670955126f * p.k_alpha * expf(-y * y) - potk) / r;
+  }
   if (!p.has_cutoff) { chi = pot; dchi = dpot; return; }
   if (r >= p.rc) { chi = 0.f; dchi = 0.f; return; }
   float f, df;

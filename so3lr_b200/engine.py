@@ -79,6 +79,7 @@ class System:
         self._h = h
         self._cell = None if cell is None else np.asarray(cell, dtype=np.float64).reshape(3, 3)
         self._virial = False
+        self.kspace = None
 
     def __del__(self):
         h = getattr(self, "_h", None)
@@ -183,7 +184,24 @@ class System:
                                                 C.byref(cnt), C.byref(ovf)), "export_list")
         return idx, cnt.value, bool(ovf.value)
 
-    def graph_eval(self, idx_i, idx_j, edges, idx_i_lr, idx_j_lr, edges_lr, g_e_atom=None):
+    def set_kspace(self, k_grid=None, k_smearing=None):
+        """Switch the reciprocal-space (Ewald) Coulomb part on: `k_grid` is the index-grid shape (n1, n2, n3) or an array of that
+        shape, `k_smearing` the Gaussian width in Angstrom (the `k_grid` / `k_smearing` arguments of the reference's energy function,
+        so3lr/jaxmd_utils.py:39-47).  `k_grid=None` switches it off.  One periodic structure with a long-range cutoff only."""
+        if k_grid is None:
+            check(lib.so3lr_b200_system_set_kspace(self._h, 0, 0.0, 0, 0, 0), "set_kspace")
+            self.kspace = None
+            return
+        shape = tuple(int(v) for v in (k_grid.shape if hasattr(k_grid, "shape") else k_grid))
+        if len(shape) != 3:
+            raise ValueError("k_grid must have three dimensions")
+        s = float(np.asarray(k_smearing.detach().cpu() if torch.is_tensor(k_smearing) else k_smearing, dtype=np.float64).reshape(-1)[0])
+        check(lib.so3lr_b200_system_set_kspace(self._h, 1, s, *shape), "set_kspace")
+        self.kspace = (shape, s)
+
+    def graph_eval(self, idx_i, idx_j, edges, idx_i_lr, idx_j_lr, edges_lr, g_e_atom=None, positions=None):
+        """`positions` (n, 3): required while the reciprocal-space part is on; the result then holds `g_positions`, the gradient
+        of that part with respect to the positions at fixed charges."""
         dev = self.device
         t = lambda a, dt: a.to(dev, dt).contiguous()
         idx_i, idx_j, idx_i_lr, idx_j_lr = (t(a, torch.int32) for a in (idx_i, idx_j, idx_i_lr, idx_j_lr))
@@ -193,6 +211,17 @@ class System:
         out = dict(e_atom=torch.empty(n, device=dev), g_edges=torch.zeros_like(edges), g_edges_lr=torch.zeros_like(edges_lr),
                    partial_charges=torch.empty(n, device=dev), hirshfeld_ratios=torch.empty(n, device=dev))
         s = torch.cuda.current_stream(dev)
+        if getattr(self, "kspace", None) is not None:
+            if positions is None or ge is not None:
+                raise ValueError("with the reciprocal-space part on, graph_eval needs `positions` and a uniform upstream cotangent")
+            R = t(positions, torch.float32)
+            out["g_positions"] = torch.empty(n, 3, device=dev)
+            check(lib.so3lr_b200_system_graph_eval_kspace(self._h, C.c_void_p(s.cuda_stream), edges.shape[0], _ptr(idx_i), _ptr(idx_j),
+                                                          _ptr(edges), edges_lr.shape[0], _ptr(idx_i_lr), _ptr(idx_j_lr), _ptr(edges_lr),
+                                                          _ptr(R), _ptr(out["e_atom"]), _ptr(out["g_edges"]), _ptr(out["g_edges_lr"]),
+                                                          _ptr(out["g_positions"]), _ptr(out["partial_charges"]),
+                                                          _ptr(out["hirshfeld_ratios"])), "graph_eval_kspace")
+            return out
         check(lib.so3lr_b200_system_graph_eval(self._h, C.c_void_p(s.cuda_stream), edges.shape[0], _ptr(idx_i), _ptr(idx_j), _ptr(edges),
                                                edges_lr.shape[0], _ptr(idx_i_lr), _ptr(idx_j_lr), _ptr(edges_lr), _ptr(ge),
                                                _ptr(out["e_atom"]), _ptr(out["g_edges"]), _ptr(out["g_edges_lr"]),

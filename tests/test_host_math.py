@@ -131,3 +131,17 @@ def test_radial_filter_chebyshev_expansion():
             worst_d = max(worst_d, np.abs(dw - dwc).max())
         assert worst < 1e-6, (layer, worst)
         assert worst_d < 5e-4, (layer, worst_d)
+
+
+@pytest.mark.parametrize("smearing", [0.0, 1.0, 2.4])
+def test_coulomb_pair_function_with_the_reciprocal_part_taken_out_matches_oracle(smearing):
+    """The pair function the long-range kernels evaluate when the Ewald sum is on (smearing > 0), value and slope."""
+    out = np.zeros(2, dtype=np.float32)
+    for cutoff in (6.0, 12.0):
+        for r in (0.9, 2.3, 4.0, 5.5, 5.99, 7.7, 11.2):
+            lib.so3lr_b200_host_coulomb_chi(r, cutoff, smearing, _p(out))
+            rt = torch.tensor([r], dtype=torch.float64, requires_grad=True)
+            chi = O.coulomb_pair(rt, cutoff, smearing if smearing > 0 else None)[0]
+            (dchi,) = torch.autograd.grad(chi, rt)
+            assert abs(out[0] - chi.item()) < 2e-7 + 2e-6 * abs(chi.item()), (cutoff, r, out[0], chi.item())
+            assert abs(out[1] - dchi.item()) < 2e-7 + 5e-6 * abs(dchi.item()), (cutoff, r, out[1], dchi.item())
