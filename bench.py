@@ -235,6 +235,19 @@ def run_b200(args, rank, world, local_rank):
     sysm = System(Z, cell, cutoff_lr=12.0, damping=2.0, skin=skin, device=local_rank)
     if skin > 0.1:
         sysm.defer_skin_test(True, 0.05)     # no host wait inside a step: the rebuild decision is taken one step late
+    kspace = None
+    if args.kspace != "off":
+        # reciprocal-space Coulomb sum, Gaussian smearing in Angstrom.  ewald: index grid with one index per `wavelength` of each
+        # cell edge (the reference's get_kgrid_ewald(cell, lr_wavelength)); pme: power-of-two mesh with at most `wavelength`
+        # between its points (get_kgrid_mesh(cell, mesh_spacing))
+        edge = [float(np.linalg.norm(np.asarray(cell, dtype=np.float64)[d])) for d in range(3)]
+        if args.kspace == "ewald":
+            shape = tuple(int(max(1, np.ceil(e / args.kspace_wavelength - 1e-9))) for e in edge)
+        else:
+            shape = tuple(int(2 ** max(2, int(np.ceil(np.log2(e / args.kspace_wavelength) - 1e-9)))) for e in edge)
+        sysm.set_kspace(shape, args.kspace_smearing, args.kspace)
+        kspace = {"method": args.kspace, "smearing_A": args.kspace_smearing, "lr_wavelength_A": args.kspace_wavelength,
+                  "k_grid_shape": list(shape), "k_vectors": sysm.kspace_vectors()}
     Rd = torch.tensor(R, dtype=torch.float32, device=dev)
     Vd = torch.tensor(V, dtype=torch.float32, device=dev)
     md = torch.tensor(m, dtype=torch.float32, device=dev)
@@ -330,6 +343,15 @@ def run_b200(args, rank, world, local_rank):
     e2e = {"value": round(N * args.steps / t_e2e, 1), "unit": UNIT, "h2d_bytes_per_step": N * 12, "d2h_bytes_per_step": N * 12 + 8,
            "ms_per_step": round(1e3 * t_e2e / args.steps, 3)}
 
+    if kspace is not None and "kspace" in groups and kspace["method"] == "pme":
+        kspace.update(ms_per_evaluation=round(groups["kspace"][0] / groups["kspace"][1], 4))
+    elif kspace is not None and "kspace" in groups:
+        # FP32 work of the two pair-like kernels: 4 FMAs (structure factors) + 8 FMAs (potential and force sums) per
+        # (atom, kept k vector), half of the vectors kept; against the nominal FP32 FMA rate 148 SMs x 128 lanes x 1.965 GHz
+        t_k = groups["kspace"][0] / groups["kspace"][1]
+        flops = 2.0 * 12.0 * N * (kspace["k_vectors"] / 2.0)
+        kspace.update(ms_per_evaluation=round(t_k, 4), fp32_tflops=round(flops / (t_k * 1e-3) / 1e12, 2),
+                      fp32_peak_tflops_nominal=74.4, fp32_frac=round(flops / (t_k * 1e-3) / 74.4e12, 4))
     cpu = cpu_baseline(args, sample_molecules=args.cpu_molecules, evals=1) if not args.no_cpu else None
     line = {"metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -345,6 +367,8 @@ def run_b200(args, rank, world, local_rank):
                                      else "inputs smaller than L2; no flush"),
                        "ns_per_day": round(args.steps / (ms * 1e-3) * 0.0432, 3)},
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu}
+    if kspace is not None:
+        line["config"]["kspace"] = kspace
     print(json.dumps(line), flush=True)
 
 
@@ -729,6 +753,10 @@ def main():
     ap.add_argument("--entry", default="md", choices=["md", "graph_eval"],
                     help="md: MD steps through the fused positions -> forces call (default); graph_eval: energy + force evaluations "
                          "through the graph-level call on prebuilt lists (the call a jax.ffi binding of potential(graph) uses), one GPU")
+    ap.add_argument("--kspace", default="off", choices=["off", "ewald", "pme"],
+                    help="reciprocal-space Coulomb sum beside the truncated pair sum (single-GPU md entry; off in the headline configuration)")
+    ap.add_argument("--kspace-smearing", type=float, default=2.4)
+    ap.add_argument("--kspace-wavelength", type=float, default=1.2)
     ap.add_argument("--traffic", type=float, default=None, help="measured DRAM bytes per launch of the roofline kernel (overrides the built-in capture)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup

@@ -138,18 +138,22 @@ SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* sys, void* st
                                  float* e_atom_dev, float* g_edges_dev, float* g_edges_lr_dev, float* charges_dev,
                                  float* hirshfeld_dev);
 
-/* Reciprocal-space part of the electrostatic energy (one periodic structure with a long-range cutoff).  mode 1: Ewald sum over
- * the k vectors of the FFT-frequency index grid of shape (n1, n2, n3) -- the shape of the reference's `k_grid` array -- with
- * Gaussian smearing `smearing` (the reference's `k_smearing`, Angstrom); mode 0 switches it off again.  While it is on, every
- * pair of the long-range list keeps only erf(r / sigma) / r - erf(r / (sqrt(2) smearing)) / r (shifted and blended towards the
- * cutoff like the plain term), and so3lr_b200_system_compute / _compute_host / the MD step bodies add
+/* Reciprocal-space part of the electrostatic energy (one periodic structure with a long-range cutoff).
+ *   mode 1: Ewald sum over the k vectors of the FFT-frequency index grid of shape (n1, n2, n3) -- the shape of the reference's
+ *           `k_grid` array as jaxpme.kspace.get_kgrid_ewald builds it;
+ *   mode 2: smooth particle-mesh Ewald on a mesh of shape (n1, n2, n3) (get_kgrid_mesh), cubic B-splines = four interpolation
+ *           nodes per axis (the reference's default `coulomb_kspace_interp_nodes=4`), each n >= 4; the two FFTs are cuFFT's,
+ *           loaded at run time (status "CUDA error" when libcufft.so.11 cannot be loaded);
+ *   mode 0: off again.
+ * `smearing` is the Gaussian width (the reference's `k_smearing`, Angstrom).  While it is on, every pair of the long-range list
+ * keeps only erf(r / sigma) / r - erf(r / (sqrt(2) smearing)) / r (shifted and blended towards the cutoff like the plain
+ * term), and so3lr_b200_system_compute / _compute_host / the MD step bodies add
  *   ke / (2 V) sum_{k != 0} 4 pi / k^2 exp(-smearing^2 k^2 / 2) |S(k)|^2 - ke sum_i q_i^2 / (sqrt(2 pi) smearing) - ke pi smearing^2 Q^2 / V
  * with its forces, its dE/dq (which continues into the charge head's reverse pass) and its strain derivative.  The cell may change
- * afterwards (so3lr_b200_system_rescale_cell): the index grid stays, the k vectors follow the cell.  Allocates and waits for the
- * device: call it between evaluations.  Not available in decomposed (so3lr_b200_dd_*) evaluations.  The mesh (PME) variant of
- * the reference is not part of this library.
+ * afterwards (so3lr_b200_system_rescale_cell): the grid shape stays, the k vectors follow the cell.  Allocates and waits for the
+ * device: call it between evaluations.  Not available in decomposed (so3lr_b200_dd_*) evaluations.
  * Replaces: the `k_grid` / `k_smearing` arguments of the reference's energy function (so3lr/jaxmd_utils.py:39-47,70-71), the
- *           grid set-up of so3lr/cli/so3lr_md.py:1392-1428 and `coulomb_kspace_do_ewald=True` of so3lr/potential.py:11-25. */
+ *           grid set-up of so3lr/cli/so3lr_md.py:1392-1428 and the `coulomb_kspace_*` options of so3lr/potential.py:11-25. */
 SO3LR_B200_API int so3lr_b200_system_set_kspace(so3lr_b200_system* sys, int mode, float smearing, int n1, int n2, int n3);
 
 /* so3lr_b200_system_graph_eval for a context whose reciprocal-space part is on: `positions` (n_atoms, 3) are the Cartesian

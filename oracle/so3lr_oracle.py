@@ -318,7 +318,7 @@ def energy_from_graph(P, Z, dR, idx_i, idx_j, dR_lr, idx_i_lr, idx_j_lr, *, lr_f
                       total_charge=None, num_unpaired=None, batch_segments=None, num_graphs=1, record=None, kspace=None):
     """Per-atom energies and auxiliary outputs from the Graph-level inputs of so3lr/graph.py:3-24.
 
-    `kspace` = dict(positions (N,3), cell (3,3), grid (n1,n2,n3), smearing) switches the Coulomb term to the
+    `kspace` = dict(positions (N,3), cell (3,3), grid (n1,n2,n3), smearing, method 'ewald' | 'pme') switches the Coulomb term to the
     real-space + reciprocal-space split of oracle/kspace_oracle.py (Graph fields positions, cell, k_grid, k_smearing).
 
     dR (E,3) displacement of each short-range edge (idx_i = centre, idx_j = neighbour), dR_lr (P,3) of each
@@ -393,8 +393,9 @@ def energy_from_graph(P, Z, dR, idx_i, idx_j, dR_lr, idx_i_lr, idx_j_lr, *, lr_f
     e_c = torch.zeros(N, dtype=_dt()).index_add(0, il, e_c_pair)
     e_d = torch.zeros(N, dtype=_dt()).index_add(0, il, e_d_pair)
     if kspace is not None:
-        from oracle.kspace_oracle import reciprocal_energy
-        e_c = e_c + reciprocal_energy(kspace["positions"], q, kspace["cell"], kspace["grid"], float(kspace["smearing"]))
+        from oracle.kspace_oracle import reciprocal_energy, reciprocal_energy_mesh
+        fn = reciprocal_energy_mesh if kspace.get("method", "ewald") == "pme" else reciprocal_energy
+        e_c = e_c + fn(kspace["positions"], q, kspace["cell"], kspace["grid"], float(kspace["smearing"]))
 
     e_atom = e_nn + e_zbl + e_c + e_d
     aux = dict(partial_charges=q, hirshfeld_ratios=hr, zbl_repulsion=e_zbl, electrostatic_energy=e_c,
@@ -405,7 +406,7 @@ def energy_from_graph(P, Z, dR, idx_i, idx_j, dR_lr, idx_i_lr, idx_j_lr, *, lr_f
 def energy_forces(P, R, Z, cell=None, *, cutoff_lr: Optional[float] = 12.0, damping: Optional[float] = 2.0,
                   lr_format="ordered_sparse", lr_neighbor_cutoff: Optional[float] = None, total_charge=None,
                   num_unpaired=None, batch_segments=None, num_graphs=1, record=None, lists=None, k_grid=None,
-                  k_smearing=None):
+                  k_smearing=None, k_method="ewald"):
     """Positions -> total energy, forces and aux outputs, the composition used by
     so3lr/jaxmd_utils.py:130-141 + jax_md.quantity.force and by so3lr/base_calculator.py:95-122.
 
@@ -413,7 +414,8 @@ def energy_forces(P, R, Z, cell=None, *, cutoff_lr: Optional[float] = 12.0, damp
     Neighbor lists are built here (short range 4.5 A, long range `cutoff_lr`) unless `lists` provides
     (idx_i, idx_j, idx_i_lr, idx_j_lr).  For several graphs pass `batch_segments`; lists are then
     restricted to pairs inside one graph.  `k_grid` (an index-grid shape or an array of that shape) and `k_smearing`
-    switch on the reciprocal-space Coulomb part (one periodic structure).
+    switch on the reciprocal-space Coulomb part (one periodic structure); `k_method` 'ewald' sums over the index grid,
+    'pme' interpolates on a mesh of that shape.
     """
     R = np.asarray(R, dtype=np.float64)
     N = len(R)
@@ -446,7 +448,8 @@ def energy_forces(P, R, Z, cell=None, *, cutoff_lr: Optional[float] = 12.0, damp
     if k_grid is not None:
         c0 = torch.tensor(np.asarray(cell, dtype=np.float64), dtype=_dt())
         shape = tuple(int(v) for v in (k_grid.shape if hasattr(k_grid, "shape") else k_grid))
-        kspace = dict(positions=Rt + Rt @ eps.T, cell=c0 + c0 @ eps.T, grid=shape, smearing=float(np.asarray(k_smearing).reshape(-1)[0]))
+        kspace = dict(positions=Rt + Rt @ eps.T, cell=c0 + c0 @ eps.T, grid=shape, smearing=float(np.asarray(k_smearing).reshape(-1)[0]),
+                      method=k_method)
     e_atom, aux = energy_from_graph(P, Z, disp(ii, jj), idx_i, idx_j, disp(il, jl), idx_i_lr, idx_j_lr,
                                     lr_format=lr_format, cutoff_lr=cutoff_lr, damping=damping,
                                     total_charge=total_charge, num_unpaired=num_unpaired,

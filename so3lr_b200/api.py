@@ -86,7 +86,7 @@ class So3lrPotentialB200:
     MAX_CACHED_SYSTEMS = 4      # evaluation contexts kept per potential (each holds every per-atom workspace of its system)
 
     def __init__(self, lr_cutoff=12.0, dispersion_energy_cutoff_lr_damping=2.0, neighborlist_format_lr="ordered_sparse",
-                 dtype=np.float32, device=None, coulomb_kspace_do_ewald=False):
+                 dtype=np.float32, device=None, coulomb_kspace_do_ewald=False, coulomb_kspace_interp_nodes=4):
         """`dtype` is the dtype of the returned energies and gradients, as in the reference where it "determines the output
         dtype" of float32 parameters (tests/test_jaxmd.py:210-212): float32 or float64.  The kernels compute in float32 either
         way; with float64 the float32 results are widened, so they carry float32 accuracy (1e-7 relative on energies)."""
@@ -98,8 +98,10 @@ class So3lrPotentialB200:
         self.damping = dispersion_energy_cutoff_lr_damping
         self.neighborlist_format_lr = neighborlist_format_lr
         self.device = _dev(device)
-        # a graph that carries k_grid / k_smearing is evaluated with the Ewald sum when this is set; the reference's other choice,
-        # the mesh (PME) variant with `coulomb_kspace_interp_nodes` (so3lr/potential.py:11-12), is not part of this library
+        # a graph that carries k_grid / k_smearing is evaluated with the Ewald sum over the index grid when this is set, else with
+        # particle-mesh Ewald on a mesh of that shape (so3lr/potential.py:11-12); the mesh variant has four interpolation nodes
+        if int(coulomb_kspace_interp_nodes) != 4:
+            raise NotImplementedError("the mesh variant interpolates with four nodes per axis (cubic B-splines) only")
         self.coulomb_kspace_do_ewald = bool(coulomb_kspace_do_ewald)
         self._systems = {}
 
@@ -129,9 +131,6 @@ class So3lrPotentialB200:
     def __call__(self, graph: Graph, has_aux: bool = False):
         kspace = graph.k_grid is not None
         if kspace:
-            if not self.coulomb_kspace_do_ewald:
-                raise NotImplementedError("the mesh (PME) variant of the k-space electrostatics is not part of this library; "
-                                          "create the potential with coulomb_kspace_do_ewald=True for the Ewald sum")
             if graph.k_smearing is None or graph.positions is None or graph.cell is None:
                 raise ValueError("k-space electrostatics needs Graph.k_smearing, Graph.positions and Graph.cell")
         s = self.system_for(graph.nodes, total_charge=graph.total_charge, num_unpaired=graph.num_unpaired_electrons)
@@ -141,8 +140,9 @@ class So3lrPotentialB200:
                 s.set_cell(cell)
             shape = tuple(int(v) for v in graph.k_grid.shape)
             sm = float(np.asarray(torch.as_tensor(graph.k_smearing).detach().cpu(), dtype=np.float64).reshape(-1)[0])
-            if s.kspace != (shape, sm):
-                s.set_kspace(shape, sm)
+            method = "ewald" if self.coulomb_kspace_do_ewald else "pme"
+            if s.kspace != (shape, sm, method):
+                s.set_kspace(shape, sm, method)
         elif s.kspace is not None:
             s.set_kspace(None)
         edges, edges_lr = graph.edges, graph.edges_lr
@@ -170,11 +170,10 @@ class So3lrPotentialB200:
 
 def make_potential_fn(lr_cutoff=12.0, dispersion_energy_cutoff_lr_damping=2.0, dtype=np.float32, coulomb_kspace_do_ewald=False,
                       coulomb_kspace_interp_nodes=4, **kwargs):
-    """so3lr/potential.py:7-29.  `coulomb_kspace_do_ewald=True` selects the Ewald sum for graphs that carry `k_grid` /
-    `k_smearing`; without it such graphs would take the mesh (PME) variant with `coulomb_kspace_interp_nodes`, which this library
-    does not have (the call then raises NotImplementedError)."""
+    """so3lr/potential.py:7-29.  For graphs that carry `k_grid` / `k_smearing`: `coulomb_kspace_do_ewald=True` selects the Ewald
+    sum over the index grid, the default the particle-mesh variant with `coulomb_kspace_interp_nodes` = 4 nodes per axis."""
     return So3lrPotentialB200(lr_cutoff, dispersion_energy_cutoff_lr_damping, "ordered_sparse", dtype, kwargs.get("device"),
-                              coulomb_kspace_do_ewald=coulomb_kspace_do_ewald)
+                              coulomb_kspace_do_ewald=coulomb_kspace_do_ewald, coulomb_kspace_interp_nodes=coulomb_kspace_interp_nodes)
 
 
 def get_kgrid_ewald_shape(cell, lr_wavelength):
@@ -188,6 +187,18 @@ def get_kgrid_ewald_shape(cell, lr_wavelength):
 def get_kgrid_ewald(cell, lr_wavelength):
     """An array whose SHAPE is the index grid (the only property of `k_grid` that the evaluation reads)."""
     return torch.zeros(get_kgrid_ewald_shape(cell, lr_wavelength))
+
+
+def get_kgrid_mesh_shape(cell, mesh_spacing):
+    """Mesh of the particle-mesh variant: the power of two per lattice vector that brings the distance between mesh points to
+    `mesh_spacing` (Angstrom) or below (argument convention of `jaxpme.kspace.get_kgrid_mesh`, so3lr/cli/so3lr_md.py:1424-1427)."""
+    c = np.asarray(cell.detach().cpu() if torch.is_tensor(cell) else cell, dtype=np.float64).reshape(3, 3)
+    h = float(np.asarray(mesh_spacing.detach().cpu() if torch.is_tensor(mesh_spacing) else mesh_spacing).reshape(-1)[0])
+    return tuple(int(2 ** max(2, int(np.ceil(np.log2(np.linalg.norm(c[d]) / h) - 1e-9)))) for d in range(3))
+
+
+def get_kgrid_mesh(cell, mesh_spacing):
+    return torch.zeros(get_kgrid_mesh_shape(cell, mesh_spacing))
 
 
 # ------------------------------------------------------------------------------------------------------------

@@ -211,10 +211,10 @@ int make_cell(const float* cell9, Cell* c) {
 // attn_fwd / attn_bwd: the kernels of the two layers with a spherical filter (one launch per layer); the first layer's
 // tabulated kernels have groups of their own, so that a group's time divided by its launches is one kernel's time
 enum ProfGroup { kPNlist = 0, kPGeom, kPProj, kPAttnFwd, kPPostFwd, kPHeads, kPPairLr, kPPostBwd, kPAttnBwd, kPProjBwd, kPScatter,
-                 kPMisc, kPMd, kPLayer0Fwd, kPLayer0Bwd, kPGroups };
+                 kPMisc, kPMd, kPLayer0Fwd, kPLayer0Bwd, kPKspace, kPGroups };
 static const char* kProfNames[kPGroups] = {"nlist", "sr_geometry_zbl", "proj_fwd", "attn_fwd", "atom_post_fwd", "heads", "pair_lr",
                                            "atom_post_bwd", "attn_bwd", "proj_bwd", "force_scatter", "misc", "md_step",
-                                           "layer0_fwd", "layer0_bwd"};
+                                           "layer0_fwd", "layer0_bwd", "kspace"};
 struct Profiler {
   bool on = false;
   std::vector<cudaEvent_t> a, b;
@@ -720,11 +720,13 @@ int evaluate_fused(so3lr_b200_system* S, cudaStream_t st, const float* R, float*
   S->prof.begin(kPPairLr, st);
   launch_pair_lr_packed(st, S->lr, S->cell, n, S->lrl.row_ptr, S->lrl.nbr_j, S->d_Z, R, S->q, S->h, S->pair_pack, F, S->gq, S->gh, S->e_coul,
                         S->e_disp, S->vir());
+  S->prof.end(st);
   if (S->ks.mode) {
+    S->prof.begin(kPKspace, st);
     rc = launch_ewald(st, S->ks, S->cell, n, R, S->q, S->d_total_charge, S->e_coul, S->gq, F, S->vir(), 1.f);
+    S->prof.end(st);
     if (rc) return rc;
   }
-  S->prof.end(st);
   { combine_energy_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->e_nn, S->e_zbl, S->e_coul, S->e_disp, S->e_atom); count_launch(); }
   launch_charge_conserve_bwd(st, S->n_graphs, S->d_graph_start, S->gq, S->gq_raw, S->n, S->red_scratch);
   return fused_backward(S, st, c, F);
@@ -1007,7 +1009,7 @@ SO3LR_B200_API int so3lr_b200_system_set_cell(so3lr_b200_system* S, const float*
 }
 
 SO3LR_B200_API int so3lr_b200_system_set_kspace(so3lr_b200_system* S, int mode, float smearing, int n1, int n2, int n3) {
-  if (!S || (mode != 0 && mode != 1)) return kInvalidArgument;
+  if (!S || mode < 0 || mode > 2) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
   SO3LR_CUDA_CHECK(cudaDeviceSynchronize());
   S->virial_fresh = false;
@@ -1019,7 +1021,7 @@ SO3LR_B200_API int so3lr_b200_system_set_kspace(so3lr_b200_system* S, int mode, 
   }
   // one periodic structure whose pair sum is cut off: the split needs a short-ranged pair part
   if (!S->cell.periodic || S->n_graphs != 1 || !S->lr.has_cutoff || !(smearing > 0.f)) return kInvalidArgument;
-  int rc = kspace_setup(&S->ks, S->n_cap, smearing, n1, n2, n3);
+  int rc = kspace_setup(&S->ks, S->n_cap, mode, smearing, n1, n2, n3);
   if (rc) return rc;
   S->lr.k_alpha = (float)(1.0 / (std::sqrt(2.0) * (double)smearing));
   set_coulomb_shift(S->lr);

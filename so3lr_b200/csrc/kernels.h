@@ -50,7 +50,7 @@ void launch_heads_bwd_tc(cudaStream_t s, const ModelDev& M, int n, const int* Z,
 
 // ---- kspace.cu: reciprocal-space (Ewald) part of the electrostatic energy of one periodic structure ----
 struct KSpaceDev {
-  int mode = 0;            // 0 off, 1 Ewald sum over the index grid
+  int mode = 0;            // 0 off, 1 Ewald sum over the index grid, 2 particle-mesh Ewald on a mesh of that shape
   float smearing = 0.f;    // Gaussian width s of the split erf(r / (sqrt(2) s)) / r
   int shape[3] = {0, 0, 0};
   int n_tiles = 0;
@@ -58,8 +58,12 @@ struct KSpaceDev {
   float* wgt = nullptr;    // [n_tiles][256] 2 / 1 / 0: member of a (k, -k) pair, unpaired index, not part of the sum
   float2* Sk = nullptr;    // [n_tiles][256] structure factors
   float* acc = nullptr;    // [n_atoms][4] potential and the three index-weighted force sums
+  float* mesh = nullptr;   // mode 2: [n1][n2][n3] charges, then the convolved potential
+  float2* fq = nullptr;    // mode 2: [n1][n2][n3 / 2 + 1] transform of the mesh
+  int plan_r2c = 0, plan_c2r = 0;   // cuFFT plans (handles)
+  bool plans = false;
 };
-int kspace_setup(KSpaceDev* K, int n_atoms, float smearing, int n1, int n2, int n3);   // allocates; call outside handlers
+int kspace_setup(KSpaceDev* K, int n_atoms, int mode, float smearing, int n1, int n2, int n3);   // allocates; call outside handlers
 void kspace_free(KSpaceDev* K);
 // adds to e_coul (per-atom energies), gq (dE/dq), F (force_sign = 1: forces at fixed charges; -1: the gradient) and, when given, the
 // six virial components of one row

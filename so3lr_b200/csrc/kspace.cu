@@ -13,6 +13,19 @@
 //                           give the force (8 FMAs per pair)
 //   ewald_finish_kernel     per atom: energy, dE/dq (it continues into the charge head's reverse pass), force
 //   ewald_virial_kernel     strain derivative, added to the first atom's virial row (the rows are only ever summed)
+//
+// Mesh variant (mode 2; the reference's default k-space method, `coulomb_kspace_interp_nodes=4`, so3lr/potential.py:11-12): smooth
+// particle-mesh Ewald (Essmann et al., J. Chem. Phys. 103, 8577 (1995)) with cubic B-splines, i.e. four mesh points per axis and atom.
+//   pme_spread_kernel     charges onto the mesh Q (64 atomic adds per atom, four threads per atom)
+//   cuFFT R2C             library FFT, loaded at run time (dlopen) so that the library itself has no link-time dependency on it
+//   pme_influence_kernel  F(Q)(m) *= ke / V x 4 pi exp(-s^2 k^2 / 2) / k^2 x prod_d 9 / (2 + cos(2 pi m_d / n_d))^2; strain derivative
+//   cuFFT C2R             the convolved potential on the mesh (unnormalised inverse transform)
+//   pme_gather_kernel     phi_i and its gradient from the 64 mesh points of atom i -> the same per-atom record as the direct sum
+//   ewald_finish_kernel   shared with the direct sum
+#include <cufft.h>
+#include <dlfcn.h>
+
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -220,16 +233,211 @@ __global__ void __launch_bounds__(kTileK) ewald_virial_kernel(Cell cell, float i
   }
 }
 
+
+// ---- mesh variant ----
+// weights M4(t + j) of the mesh points m0 - j (j = 0..3) around the scaled coordinate m0 + t, and their t-derivatives
+__device__ __forceinline__ void bspline4(float t, float* w, float* dw) {
+  const float t2 = t * t, t3 = t2 * t, o = 1.f - t;
+  w[0] = t3 * (1.f / 6.f);
+  w[1] = (-3.f * t3 + 3.f * t2 + 3.f * t + 1.f) * (1.f / 6.f);
+  w[2] = (3.f * t3 - 6.f * t2 + 4.f) * (1.f / 6.f);
+  w[3] = o * o * o * (1.f / 6.f);
+  dw[0] = 0.5f * t2;
+  dw[1] = 0.5f * (-3.f * t2 + 2.f * t + 1.f);
+  dw[2] = 0.5f * (3.f * t2 - 4.f * t);
+  dw[3] = -0.5f * o * o;
+}
+__device__ __forceinline__ int wrap_index(int k, int n) { return k < 0 ? k + n : (k >= n ? k - n : k); }
+// scaled coordinate of one axis: mesh point at or below it and the remainder in [0, 1)
+__device__ __forceinline__ void mesh_coordinate(float f, int n, int& m0, float& t) {
+  const float u = f * (float)n;
+  const float fl = floorf(u);
+  m0 = (int)fl;
+  t = u - fl;
+}
+// signed frequency of a mesh index, the convention of numpy's fftfreq (n / 2 of an even n counts as -n / 2)
+__device__ __forceinline__ int signed_frequency(int m, int n) { return m < (n + 1) / 2 ? m : m - n; }
+
+__global__ void __launch_bounds__(256) pme_spread_kernel(Cell cell, int n, int n1, int n2, int n3, const float* __restrict__ R,
+                                                         const float* __restrict__ q, float* __restrict__ mesh) {
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int a = (int)(gid >> 2), j1 = (int)(gid & 3);
+  if (a >= n) return;
+  float f1, f2, f3;
+  fractional(cell, R, a, f1, f2, f3);
+  int m1, m2, m3;
+  float t1, t2, t3, w1[4], w2[4], w3[4], dw[4];
+  mesh_coordinate(f1, n1, m1, t1); mesh_coordinate(f2, n2, m2, t2); mesh_coordinate(f3, n3, m3, t3);
+  bspline4(t1, w1, dw); bspline4(t2, w2, dw); bspline4(t3, w3, dw);
+  const float qa = q[a] * w1[j1];
+  const int k1 = wrap_index(wrap_index(m1 - j1, n1), n1);
+#pragma unroll
+  for (int j2 = 0; j2 < 4; ++j2) {
+    const int k2 = wrap_index(wrap_index(m2 - j2, n2), n2);
+    float* row = mesh + ((size_t)k1 * n2 + k2) * n3;
+#pragma unroll
+    for (int j3 = 0; j3 < 4; ++j3) atomicAdd(row + wrap_index(wrap_index(m3 - j3, n3), n3), qa * w2[j2] * w3[j3]);
+  }
+}
+
+__global__ void __launch_bounds__(256) pme_influence_kernel(Cell cell, float inv_vol, float smearing, int n1, int n2, int n3,
+                                                            float2* __restrict__ fq, const float* __restrict__ total_charge,
+                                                            float* __restrict__ virial_row) {
+  __shared__ float part[8][6];
+  const int nc = n3 / 2 + 1;
+  const long long total = (long long)n1 * n2 * nc;
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  float v[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (e < total) {
+    const int m3 = (int)(e % nc);
+    const int m2 = (int)((e / nc) % n2);
+    const int m1 = (int)(e / ((long long)nc * n2));
+    float2 f = fq[e];
+    float c = 0.f;
+    if (m1 | m2 | m3) {
+      float kx, ky, kz;
+      k_vector(cell, signed_frequency(m1, n1), signed_frequency(m2, n2), signed_frequency(m3, n3), kx, ky, kz);
+      const float k2 = kx * kx + ky * ky + kz * kz;
+      const float b1 = 2.f + cospif(2.f * (float)m1 / (float)n1), b2 = 2.f + cospif(2.f * (float)m2 / (float)n2),
+                  b3 = 2.f + cospif(2.f * (float)m3 / (float)n3);
+      const float bb = b1 * b2 * b3;
+      c = k_weight(1.f, inv_vol, smearing, k2) * 729.f / (bb * bb);
+      if (virial_row) {
+        // the stored half of the transform stands for its mirror image too, except on the planes that are their own mirror
+        const float wgt = (m3 == 0 || 2 * m3 == n3) ? 1.f : 2.f;
+        const float en = 0.5f * wgt * c * (f.x * f.x + f.y * f.y);
+        const float m = 2.f * (0.5f * smearing * smearing + 1.f / k2);
+        v[0] = en * (m * kx * kx - 1.f); v[1] = en * (m * ky * ky - 1.f); v[2] = en * (m * kz * kz - 1.f);
+        v[3] = en * m * ky * kz; v[4] = en * m * kx * kz; v[5] = en * m * kx * ky;
+      }
+    } else if (virial_row) {
+      const float qt = total_charge[0];
+      const float b = kKe * 3.141592653589793f * smearing * smearing * inv_vol * qt * qt;
+      v[0] = b; v[1] = b; v[2] = b;
+    }
+    fq[e] = make_float2(c * f.x, c * f.y);
+  }
+  if (!virial_row) return;
+  const int tid = threadIdx.x;
+#pragma unroll
+  for (int k = 0; k < 6; ++k) v[k] = warp_sum(v[k]);
+  if ((tid & 31) == 0)
+    for (int k = 0; k < 6; ++k) part[tid >> 5][k] = v[k];
+  __syncthreads();
+  if (tid < 6) {
+    float s = 0.f;
+    for (int wp = 0; wp < 8; ++wp) s += part[wp][tid];
+    if (s != 0.f) atomicAdd(virial_row + tid, s);
+  }
+}
+
+__global__ void __launch_bounds__(128) pme_gather_kernel(Cell cell, int n, int n1, int n2, int n3, const float* __restrict__ R,
+                                                         const float* __restrict__ mesh, float* __restrict__ acc) {
+  const int a = blockIdx.x * blockDim.x + threadIdx.x;
+  if (a >= n) return;
+  float f1, f2, f3;
+  fractional(cell, R, a, f1, f2, f3);
+  int m1, m2, m3;
+  float t1, t2, t3, w1[4], w2[4], w3[4], d1[4], d2[4], d3[4];
+  mesh_coordinate(f1, n1, m1, t1); mesh_coordinate(f2, n2, m2, t2); mesh_coordinate(f3, n3, m3, t3);
+  bspline4(t1, w1, d1); bspline4(t2, w2, d2); bspline4(t3, w3, d3);
+  int k3[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) k3[j] = wrap_index(wrap_index(m3 - j, n3), n3);
+  float phi = 0.f, g1 = 0.f, g2 = 0.f, g3 = 0.f;
+#pragma unroll
+  for (int j1 = 0; j1 < 4; ++j1) {
+    const int k1 = wrap_index(wrap_index(m1 - j1, n1), n1);
+#pragma unroll
+    for (int j2 = 0; j2 < 4; ++j2) {
+      const int k2 = wrap_index(wrap_index(m2 - j2, n2), n2);
+      const float* row = mesh + ((size_t)k1 * n2 + k2) * n3;
+      float s = 0.f, sd = 0.f;       // sums over the third axis with the weights and with their derivatives
+#pragma unroll
+      for (int j3 = 0; j3 < 4; ++j3) {
+        const float val = row[k3[j3]];
+        s = fmaf(w3[j3], val, s);
+        sd = fmaf(d3[j3], val, sd);
+      }
+      phi = fmaf(w1[j1] * w2[j2], s, phi);
+      g1 = fmaf(d1[j1] * w2[j2], s, g1);
+      g2 = fmaf(w1[j1] * d2[j2], s, g2);
+      g3 = fmaf(w1[j1] * w2[j2], sd, g3);
+    }
+  }
+  // the record of the direct sum: dE/dr_a = 2 pi q sum_d hinv[a][d] acc[1 + d]
+  const float inv2pi = 0.15915494309189535f;
+  *reinterpret_cast<float4*>(acc + 4 * (size_t)a) = make_float4(phi, g1 * (float)n1 * inv2pi, g2 * (float)n2 * inv2pi, g3 * (float)n3 * inv2pi);
+}
+
+// cuFFT entry points, resolved at run time
+struct CufftApi {
+  void* lib = nullptr;
+  cufftResult (*plan3d)(cufftHandle*, int, int, int, cufftType) = nullptr;
+  cufftResult (*set_stream)(cufftHandle, cudaStream_t) = nullptr;
+  cufftResult (*exec_r2c)(cufftHandle, cufftReal*, cufftComplex*) = nullptr;
+  cufftResult (*exec_c2r)(cufftHandle, cufftComplex*, cufftReal*) = nullptr;
+  cufftResult (*destroy)(cufftHandle) = nullptr;
+  bool ok = false;
+};
+CufftApi* cufft_api() {
+  static CufftApi api;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char* names[] = {"libcufft.so.11", "libcufft.so", "/usr/local/cuda/lib64/libcufft.so.11", "/usr/local/cuda/lib64/libcufft.so"};
+    for (const char* nm : names) {
+      api.lib = dlopen(nm, RTLD_NOW | RTLD_LOCAL);
+      if (api.lib) break;
+    }
+    if (!api.lib) {
+      std::fprintf(stderr, "so3lr_b200: the mesh variant of the reciprocal sum needs the cuFFT library (libcufft.so.11), which could not be loaded\n");
+      return;
+    }
+    api.plan3d = reinterpret_cast<decltype(api.plan3d)>(dlsym(api.lib, "cufftPlan3d"));
+    api.set_stream = reinterpret_cast<decltype(api.set_stream)>(dlsym(api.lib, "cufftSetStream"));
+    api.exec_r2c = reinterpret_cast<decltype(api.exec_r2c)>(dlsym(api.lib, "cufftExecR2C"));
+    api.exec_c2r = reinterpret_cast<decltype(api.exec_c2r)>(dlsym(api.lib, "cufftExecC2R"));
+    api.destroy = reinterpret_cast<decltype(api.destroy)>(dlsym(api.lib, "cufftDestroy"));
+    api.ok = api.plan3d && api.set_stream && api.exec_r2c && api.exec_c2r && api.destroy;
+  });
+  return api.ok ? &api : nullptr;
+}
+
 }  // namespace
 
 void kspace_free(KSpaceDev* K) {
-  cudaFree(K->tiles); cudaFree(K->wgt); cudaFree(K->Sk); cudaFree(K->acc);
+  if (K->plans) {
+    if (CufftApi* f = cufft_api()) { f->destroy(K->plan_r2c); f->destroy(K->plan_c2r); }
+  }
+  cudaFree(K->tiles); cudaFree(K->wgt); cudaFree(K->Sk); cudaFree(K->acc); cudaFree(K->mesh); cudaFree(K->fq);
   *K = KSpaceDev{};
 }
 
-int kspace_setup(KSpaceDev* K, int n_atoms, float smearing, int n1, int n2, int n3) {
+static int kspace_setup_mesh(KSpaceDev* K, int n_atoms, float smearing, int n1, int n2, int n3) {
+  if (n1 < 4 || n2 < 4 || n3 < 4 || (long long)n1 * n2 * n3 > (1LL << 30)) return n1 < 4 || n2 < 4 || n3 < 4 ? kInvalidArgument : kTooLarge;
+  CufftApi* f = cufft_api();
+  if (!f) return kCudaError;
+  K->smearing = smearing;
+  K->shape[0] = n1; K->shape[1] = n2; K->shape[2] = n3;
+  SO3LR_CUDA_CHECK(cudaMalloc((void**)&K->mesh, (size_t)n1 * n2 * n3 * sizeof(float)));
+  SO3LR_CUDA_CHECK(cudaMalloc((void**)&K->fq, (size_t)n1 * n2 * (n3 / 2 + 1) * sizeof(float2)));
+  SO3LR_CUDA_CHECK(cudaMalloc((void**)&K->acc, (size_t)n_atoms * 4 * sizeof(float)));
+  if (f->plan3d(&K->plan_r2c, n1, n2, n3, CUFFT_R2C) != CUFFT_SUCCESS) return kCudaError;
+  if (f->plan3d(&K->plan_c2r, n1, n2, n3, CUFFT_C2R) != CUFFT_SUCCESS) { f->destroy(K->plan_r2c); return kCudaError; }
+  K->plans = true;
+  K->mode = 2;
+  return kOk;
+}
+
+int kspace_setup(KSpaceDev* K, int n_atoms, int mode, float smearing, int n1, int n2, int n3) {
   kspace_free(K);
   if (!(smearing > 0.f) || n1 < 1 || n2 < 1 || n3 < 1 || n1 > 1024 || n2 > 1024 || n3 > 1024) return kInvalidArgument;
+  if (mode == 2) {
+    int rc = kspace_setup_mesh(K, n_atoms, smearing, n1, n2, n3);
+    if (rc) kspace_free(K);
+    return rc;
+  }
+  if (mode != 1) return kInvalidArgument;
   const int nn[3] = {n1, n2, n3};
   int lo[3], hi[3];
   for (int d = 0; d < 3; ++d) { lo[d] = -(nn[d] / 2); hi[d] = (nn[d] + 1) / 2 - 1; }
@@ -269,11 +477,27 @@ int kspace_setup(KSpaceDev* K, int n_atoms, float smearing, int n1, int n2, int 
 
 int launch_ewald(cudaStream_t st, const KSpaceDev& K, const Cell& cell, int n, const float* R, const float* q, const float* total_charge,
                  float* e_coul, float* gq, float* F, float* virial_row, float force_sign) {
-  if (K.mode != 1 || !cell.periodic) return kInvalidArgument;
+  if ((K.mode != 1 && K.mode != 2) || !cell.periodic) return kInvalidArgument;
   const float* h = cell.h;
   const double det = (double)h[0] * ((double)h[4] * h[8] - (double)h[5] * h[7]) - (double)h[1] * ((double)h[3] * h[8] - (double)h[5] * h[6]) +
                      (double)h[2] * ((double)h[3] * h[7] - (double)h[4] * h[6]);
   const float inv_vol = (float)(1.0 / (det < 0 ? -det : det));
+  if (K.mode == 2) {
+    CufftApi* f = cufft_api();
+    if (!f || !K.plans) return kCudaError;
+    const int n1 = K.shape[0], n2 = K.shape[1], n3 = K.shape[2];
+    SO3LR_CUDA_CHECK(cudaMemsetAsync(K.mesh, 0, (size_t)n1 * n2 * n3 * sizeof(float), st));
+    { pme_spread_kernel<<<(unsigned)(((long long)n * 4 + 255) / 256), 256, 0, st>>>(cell, n, n1, n2, n3, R, q, K.mesh); count_launch(); }
+    if (f->set_stream(K.plan_r2c, st) != CUFFT_SUCCESS || f->set_stream(K.plan_c2r, st) != CUFFT_SUCCESS) return kCudaError;
+    if (f->exec_r2c(K.plan_r2c, K.mesh, reinterpret_cast<cufftComplex*>(K.fq)) != CUFFT_SUCCESS) return kCudaError;
+    const long long total = (long long)n1 * n2 * (n3 / 2 + 1);
+    { pme_influence_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(cell, inv_vol, K.smearing, n1, n2, n3, K.fq, total_charge, virial_row); count_launch(); }
+    if (f->exec_c2r(K.plan_c2r, reinterpret_cast<cufftComplex*>(K.fq), K.mesh) != CUFFT_SUCCESS) return kCudaError;
+    { pme_gather_kernel<<<(n + 127) / 128, 128, 0, st>>>(cell, n, n1, n2, n3, R, K.mesh, K.acc); count_launch(); }
+    { ewald_finish_kernel<<<(n + 255) / 256, 256, 0, st>>>(cell, inv_vol, K.smearing, n, q, total_charge, K.acc, e_coul, gq, F, force_sign); count_launch(); }
+    SO3LR_CUDA_CHECK(cudaGetLastError());
+    return kOk;
+  }
   SO3LR_CUDA_CHECK(cudaMemsetAsync(K.Sk, 0, (size_t)K.n_tiles * kTileK * sizeof(float2), st));
   SO3LR_CUDA_CHECK(cudaMemsetAsync(K.acc, 0, (size_t)n * 4 * sizeof(float), st));
   const int target = 4 * sm_count();

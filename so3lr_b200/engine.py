@@ -154,6 +154,14 @@ class System:
             out[name] = _from_ptr(p.value, self.n, self.device).clone()
         return out
 
+    def kspace_vectors(self):
+        """Number of k vectors the reciprocal sum runs over (both members of every pair (k, -k) counted; mesh points of the
+        mesh variant) or None."""
+        if self.kspace is None:
+            return None
+        n1, n2, n3 = self.kspace[0]
+        return n1 * n2 * n3 - 1
+
     def stats(self):
         v = [C.c_int64() for _ in range(4)]
         check(lib.so3lr_b200_system_stats(self._h, *[C.byref(x) for x in v]), "stats")
@@ -184,10 +192,12 @@ class System:
                                                 C.byref(cnt), C.byref(ovf)), "export_list")
         return idx, cnt.value, bool(ovf.value)
 
-    def set_kspace(self, k_grid=None, k_smearing=None):
-        """Switch the reciprocal-space (Ewald) Coulomb part on: `k_grid` is the index-grid shape (n1, n2, n3) or an array of that
-        shape, `k_smearing` the Gaussian width in Angstrom (the `k_grid` / `k_smearing` arguments of the reference's energy function,
-        so3lr/jaxmd_utils.py:39-47).  `k_grid=None` switches it off.  One periodic structure with a long-range cutoff only."""
+    def set_kspace(self, k_grid=None, k_smearing=None, method="ewald"):
+        """Switch the reciprocal-space Coulomb part on: `k_grid` is the grid shape (n1, n2, n3) or an array of that shape,
+        `k_smearing` the Gaussian width in Angstrom (the `k_grid` / `k_smearing` arguments of the reference's energy function,
+        so3lr/jaxmd_utils.py:39-47); `method` 'ewald' sums over the k vectors of the index grid, 'pme' interpolates on a mesh of
+        that shape with cubic B-splines (so3lr/potential.py:11-12).  `k_grid=None` switches it off.  One periodic structure with
+        a long-range cutoff only."""
         if k_grid is None:
             check(lib.so3lr_b200_system_set_kspace(self._h, 0, 0.0, 0, 0, 0), "set_kspace")
             self.kspace = None
@@ -196,8 +206,10 @@ class System:
         if len(shape) != 3:
             raise ValueError("k_grid must have three dimensions")
         s = float(np.asarray(k_smearing.detach().cpu() if torch.is_tensor(k_smearing) else k_smearing, dtype=np.float64).reshape(-1)[0])
-        check(lib.so3lr_b200_system_set_kspace(self._h, 1, s, *shape), "set_kspace")
-        self.kspace = (shape, s)
+        if method not in ("ewald", "pme"):
+            raise ValueError("method must be 'ewald' or 'pme'")
+        check(lib.so3lr_b200_system_set_kspace(self._h, 1 if method == "ewald" else 2, s, *shape), "set_kspace")
+        self.kspace = (shape, s, method)
 
     def graph_eval(self, idx_i, idx_j, edges, idx_i_lr, idx_j_lr, edges_lr, g_e_atom=None, positions=None):
         """`positions` (n, 3): required while the reciprocal-space part is on; the result then holds `g_positions`, the gradient

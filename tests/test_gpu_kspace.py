@@ -126,11 +126,49 @@ def test_energy_function_with_k_grid_matches_the_fused_entry(oracle_params, refe
     kw2 = dict(neighbor=nbrs.idx, neighbor_lr=nbrs_lr.idx, box=box)
     plain = O.energy_forces(oracle_params, R.astype(np.float64), Z, cell, cutoff_lr=6.0, damping=2.0)
     assert abs(float(energy_fn(Rt, **kw2)) - plain["energy"]) < 1e-5 * abs(plain["energy"])
-    # the mesh variant is not part of the library: loud, not silent
+    # the reference's default k-space method is the mesh variant: same call, potential made without coulomb_kspace_do_ewald
     pot_pme = A.make_potential_fn(lr_cutoff=6.0)
     _, _, efn_pme = A.to_jax_md(potential=pot_pme, displacement_or_metric=None, box_size=box, species=Z)
+    mesh = A.get_kgrid_mesh_shape(cell, 0.4)
+    assert mesh == K.mesh_grid_shape(cell, 0.4) == (32, 32, 32)
+    kwm = dict(kw, k_grid=A.get_kgrid_mesh(cell, 0.4))
+    refm = O.energy_forces(oracle_params, R.astype(np.float64), Z, cell, cutoff_lr=6.0, damping=2.0, k_grid=mesh, k_smearing=smearing,
+                           k_method="pme")
+    Em, Fm = float(efn_pme(Rt, **kwm)), A.force(efn_pme)(Rt, **kwm).cpu().numpy()
+    assert abs(Em - refm["energy"]) < 1e-5 * abs(refm["energy"]), (Em, refm["energy"])
+    assert np.abs(Fm - refm["forces"]).max() < 1e-4
+    # and the mesh result is the direct sum up to the interpolation error of this mesh (0.39 A between points at a smearing
+    # of 1 A: 9e-3 eV and 1e-3 eV/A in the oracle)
+    assert abs(Em - E) < 2e-2 and np.abs(Fm - F).max() < 3e-3
     with pytest.raises(NotImplementedError):
-        efn_pme(Rt, **kw)
+        A.make_potential_fn(lr_cutoff=6.0, coulomb_kspace_interp_nodes=5)
+
+
+@pytest.mark.parametrize("case", ["water192", "water1536", "triclinic"])
+def test_mesh_variant_matches_oracle(oracle_params, reference_goldens, case):
+    from so3lr_b200 import workloads as Wl
+    from so3lr_b200.engine import System
+    g = reference_goldens
+    if case == "water192":
+        Z, R, cell = _water192(g)
+        rc, smearing, shape, skin = 6.0, 1.0, (32, 32, 32), 0.0
+    elif case == "water1536":
+        Z, R, cell = g["water_Z"], np.asarray(g["water_R"], dtype=np.float32), np.asarray(g["water_cell"], dtype=np.float64)
+        rc, smearing, shape, skin = 12.0, 2.4, (32, 30, 36), 0.8           # cuFFT takes any extents
+    else:
+        Z, R, cell = Wl.water_box(216, 18.7, 5, jitter=0.03)
+        shear = np.array([[1.0, 0.0, 0.0], [0.18, 1.0, 0.0], [-0.1, 0.12, 1.0]])
+        cell = np.asarray(cell, dtype=np.float64) @ shear
+        R = (np.asarray(R, dtype=np.float64) @ shear).astype(np.float32)
+        rc, smearing, shape, skin = 8.0, 1.5, (32, 32, 32), 0.0
+    ref = O.energy_forces(oracle_params, R.astype(np.float64), Z, cell, cutoff_lr=rc, damping=2.0, k_grid=shape, k_smearing=smearing,
+                          k_method="pme")
+    s = System(Z, cell, cutoff_lr=rc, damping=2.0, skin=skin)
+    s.enable_virial(True)
+    s.set_kspace(shape, smearing, "pme")
+    _check(s.compute(torch.tensor(R, device="cuda")), ref, R)
+    # a second evaluation reuses the plans and the mesh
+    _check(s.compute(torch.tensor(R, device="cuda")), ref, R)
 
 
 def test_invalid_kspace_requests_fail_loudly(reference_goldens):
@@ -143,3 +181,36 @@ def test_invalid_kspace_requests_fail_loudly(reference_goldens):
         System(Z, cell, cutoff_lr=None).set_kspace((8, 8, 8), 1.0)         # no cutoff: nothing short-ranged to keep in the pair sum
     with pytest.raises(So3lrB200Error):
         System(Z, cell, cutoff_lr=6.0).set_kspace((8, 8, 8), 0.0)          # smearing must be positive
+    with pytest.raises(So3lrB200Error):
+        System(Z, cell, cutoff_lr=6.0).set_kspace((8, 2, 8), 1.0, "pme")   # four mesh points per axis at least
+
+
+def test_nve_with_the_reciprocal_sum_conserves_energy_and_strained_cells_follow_the_virial():
+    """The forces are the derivative of the energy the context reports (a short NVE run keeps their sum), and after
+    rescale_cell the k vectors follow the cell: a finite strain changes the energy by trace(W eps)."""
+    from so3lr_b200 import md
+    from so3lr_b200 import workloads as W
+    from so3lr_b200.engine import System
+    Z, R, cell = W.water_box(512, 24.9, 7, jitter=0.02)
+    V, m = W.maxwell_boltzmann(Z, 300.0, 8)
+    cell = np.asarray(cell, dtype=np.float64)
+    s = System(Z, cell, cutoff_lr=10.0, damping=2.0, skin=0.5)
+    s.set_kspace(K.ewald_grid_shape(cell, 1.0), 2.0)
+    dof = 3.0 * len(Z)
+    init_fn, apply_fn = md.nve(s, 0.25)
+    state = init_fn(R, m, velocity=V)
+    E0 = float(state.energy.sum()) + md.kinetic_energy(state)
+    state = apply_fn(state, 120)
+    assert abs(float(state.energy.sum()) + md.kinetic_energy(state) - E0) < 2e-3 * dof * 300.0 * 8.617333262e-5
+    # strain
+    s.enable_virial(True)
+    Rf = np.asarray(R, dtype=np.float64)
+    Wv = s.compute(torch.tensor(Rf.astype(np.float32), device="cuda"))["virial"].cpu().numpy()
+    eps = 2e-4 * np.array([[1.0, 0.3, 0.0], [0.3, -0.5, 0.2], [0.0, 0.2, 0.7]])
+    Es = []
+    for sign in (+1, -1):
+        A = np.eye(3) + sign * eps
+        s.rescale_cell(cell @ A.T)
+        Es.append(float(s.compute(torch.tensor((Rf @ A.T).astype(np.float32), device="cuda"))["energy"].sum()))
+    dE = (Es[0] - Es[1]) / 2
+    assert abs(dE - float((Wv * eps).sum())) < 2e-3 + 2e-3 * abs(dE), (dE, float((Wv * eps).sum()))

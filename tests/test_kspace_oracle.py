@@ -72,3 +72,28 @@ def test_model_energy_and_forces_with_kspace_do_not_depend_on_the_smearing(oracl
     for k in ("dispersion_energy", "zbl_repulsion", "partial_charges", "hirshfeld_ratios"):
         np.testing.assert_allclose(plain[k], outs[0][k], atol=1e-12)
     assert np.abs(plain["electrostatic_energy"] - outs[0]["electrostatic_energy"]).max() > 1e-3
+
+
+def test_mesh_variant_converges_to_the_direct_sum_with_the_fourth_power_of_the_spacing():
+    rng = np.random.default_rng(3)
+    cell = np.array([[12.4, 0.0, 0.0], [1.0, 12.0, 0.0], [0.5, -0.7, 13.0]])
+    R = rng.random((60, 3)) @ cell
+    q = rng.normal(size=60); q -= q.mean()
+    qt, ct, s = torch.tensor(q), torch.tensor(cell), 1.2
+
+    def run(fn, shape):
+        Rt = torch.tensor(R, requires_grad=True)
+        eps = torch.zeros(3, 3, dtype=torch.float64, requires_grad=True)
+        e = fn(Rt + Rt @ eps.T, qt, ct + ct @ eps.T, shape, s).sum()
+        gR, gE = torch.autograd.grad(e, (Rt, eps))
+        return e.item(), gR.numpy(), gE.numpy()
+
+    e0, g0, v0 = run(K.reciprocal_energy, (40, 40, 40))
+    err = []
+    for n in (16, 32, 64):
+        e, g, v = run(K.reciprocal_energy_mesh, (n, n, n))
+        err.append((abs(e - e0), np.abs(g - g0).max(), np.abs(v - v0).max()))
+    for a, b in zip(err[:-1], err[1:]):
+        assert b[0] < a[0] / 10 and b[1] < a[1] / 8 and b[2] < a[2] / 8, err       # 16 per halving in the limit
+    assert err[-1][0] < 2e-3 and err[-1][1] < 2e-3
+    assert K.mesh_grid_shape(cell, 0.8) == (16, 16, 32) and K.mesh_grid_shape(np.eye(3) * 215.0, 1.0) == (256, 256, 256)
