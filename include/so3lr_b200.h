@@ -160,12 +160,15 @@ SO3LR_B200_API int so3lr_b200_system_set_kspace(so3lr_b200_system* sys, int mode
  * positions the displacements were formed from (Graph.positions), and g_positions_dev receives the gradient of the
  * reciprocal-space energy with respect to them at fixed charges; the charges' own dependence on the geometry arrives through
  * g_edges_dev as usual.  The upstream cotangent is one for every atom (the per-atom reciprocal energies are not separable).
- * The strain derivative of the reciprocal part is available from the fused entry (so3lr_b200_system_virial) only. */
+ * strain6_dev (may be NULL) receives the strain derivative of the reciprocal part at fixed fractional coordinates and fixed
+ * charges, six symmetric components xx yy zz yz xz xy; its share that belongs to the cell alone (what a caller needs who
+ * differentiates with respect to `positions` and `cell` separately, as the reference's `perturbation` does) is that minus
+ * sum_i positions_i (x) g_positions_i. */
 SO3LR_B200_API int so3lr_b200_system_graph_eval_kspace(so3lr_b200_system* sys, void* stream, int64_t n_edges, const int32_t* idx_i,
                                         const int32_t* idx_j, const float* edges, int64_t n_pairs, const int32_t* idx_i_lr,
                                         const int32_t* idx_j_lr, const float* edges_lr, const float* positions,
                                         float* e_atom_dev, float* g_edges_dev, float* g_edges_lr_dev, float* g_positions_dev,
-                                        float* charges_dev, float* hirshfeld_dev);
+                                        float* strain6_dev, float* charges_dev, float* hirshfeld_dev);
 
 /* A velocity-Verlet (NVE) step driven by the library: positions/velocities/forces stay on the device.
  * masses_dev in amu, dt in fs, velocities in Angstrom/fs.  Runs `n_steps` steps; forces_dev must hold the forces

@@ -50,7 +50,7 @@ def _load():
         "so3lr_b200_system_export_list": (i32, [p, p, p, i32, p, i64, C.POINTER(i64), C.POINTER(i32)]),
         "so3lr_b200_system_graph_eval": (i32, [p, p, i64, p, p, p, i64, p, p, p, p, p, p, p, p, p]),
         "so3lr_b200_system_set_kspace": (i32, [p, i32, f32, i32, i32, i32]),
-        "so3lr_b200_system_graph_eval_kspace": (i32, [p, p, i64, p, p, p, i64, p, p, p, p, p, p, p, p, p, p]),
+        "so3lr_b200_system_graph_eval_kspace": (i32, [p, p, i64, p, p, p, i64, p, p, p, p, p, p, p, p, p, p, p]),
         "so3lr_b200_system_nve": (i32, [p, p, i32, f32, p, p, p, p, p]),
         "so3lr_b200_system_enable_virial": (i32, [p, i32]),
         "so3lr_b200_system_virial": (i32, [p, p, p]),

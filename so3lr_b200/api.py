@@ -54,28 +54,37 @@ class _GraphEnergy(torch.autograd.Function):
     reference takes, so3lr/jaxmd_utils.py:141); a non-uniform cotangent triggers one re-evaluation."""
 
     @staticmethod
-    def forward(ctx, edges, edges_lr, system, idx_i, idx_j, idx_i_lr, idx_j_lr, aux_out, positions=None):
+    def forward(ctx, edges, edges_lr, system, idx_i, idx_j, idx_i_lr, idx_j_lr, aux_out, positions=None, cell=None):
         out = system.graph_eval(idx_i, idx_j, edges, idx_i_lr, idx_j_lr, edges_lr, positions=positions)
         ctx.system = system
         ctx.lists = (idx_i, idx_j, idx_i_lr, idx_j_lr)
         ctx.has_positions = positions is not None
         gp = out["g_positions"] if positions is not None else edges.new_zeros(0)
-        ctx.save_for_backward(edges, edges_lr, out["g_edges"], out["g_edges_lr"], gp)
+        gc = edges.new_zeros(0)
+        if positions is not None and cell is not None:
+            # reciprocal part E(positions X, cell C): its strain derivative at fixed fractional coordinates is
+            # W = g^T X + G^T C with g = dE/dX, G = dE/dC, so the cell's own cotangent is G = C^-T (W - g^T X)^T
+            w = out["kspace_strain"].double()
+            W = torch.stack([torch.stack([w[0], w[5], w[4]]), torch.stack([w[5], w[1], w[3]]), torch.stack([w[4], w[3], w[2]])])
+            X = positions.double()
+            gc = (torch.linalg.inv(cell.double().to(X.device)).T @ (W - gp.double().T @ X).T).to(cell.dtype)
+        ctx.save_for_backward(edges, edges_lr, out["g_edges"], out["g_edges_lr"], gp, gc)
         aux_out.update(partial_charges=out["partial_charges"], hirshfeld_ratios=out["hirshfeld_ratios"])
         return out["e_atom"]
 
     @staticmethod
     def backward(ctx, g):
-        edges, edges_lr, ge, gel, gp = ctx.saved_tensors
+        edges, edges_lr, ge, gel, gp, gc = ctx.saved_tensors
         g = g.contiguous()
         lo, hi = torch.aminmax(g)
         if bool(lo == hi):
             c = lo.to(ge.dtype)
-            return ge * c, gel * c, None, None, None, None, None, None, (gp * c if ctx.has_positions else None)
+            return (ge * c, gel * c, None, None, None, None, None, None, (gp * c if ctx.has_positions else None),
+                    (gc * c.to(gc.dtype) if gc.numel() else None))
         if ctx.has_positions:
             raise NotImplementedError("the reciprocal-space energy is differentiated for a uniform cotangent (its sum) only")
         out = ctx.system.graph_eval(ctx.lists[0], ctx.lists[1], edges, ctx.lists[2], ctx.lists[3], edges_lr, g_e_atom=g)
-        return out["g_edges"], out["g_edges_lr"], None, None, None, None, None, None, None
+        return out["g_edges"], out["g_edges_lr"], None, None, None, None, None, None, None, None
 
 
 class So3lrPotentialB200:
@@ -158,7 +167,8 @@ class So3lrPotentialB200:
         aux = {}
         e = _GraphEnergy.apply(edges.to(self.device, torch.float32), edges_lr.to(self.device, torch.float32), s, idx_i, idx_j,
                                idx_i_lr, idx_j_lr, aux,
-                               graph.positions.to(self.device, torch.float32) if kspace else None).to(self.dtype)
+                               graph.positions.to(self.device, torch.float32) if kspace else None,
+                               graph.cell.to(self.device) if kspace else None).to(self.dtype)
         if not has_aux:
             return e
         aux.update(s.aux())
@@ -351,8 +361,6 @@ def neighbor_list_featurizer(displacement_fn, species, fractional_coordinates=Tr
                 raise ValueError(f"Invalid box shape {tuple(b.shape)}. Expected (3, 3), (3,), or (1,).")
         k_grid, k_smearing = kwargs.get("k_grid"), kwargs.get("k_smearing")
         pert = kwargs.get("perturbation")
-        if k_grid is not None and pert is not None:
-            raise NotImplementedError("the strain derivative of the reciprocal-space energy is available from System.virial only")
         if k_grid is not None and cell_t is None:
             raise ValueError("k-space electrostatics needs `box`")
         Rc = _Transform.apply(R, cell_t) if (cell_t is not None and fractional_coordinates) else R
@@ -363,16 +371,21 @@ def neighbor_list_featurizer(displacement_fn, species, fractional_coordinates=Tr
         # the kernels take dR = R_j - R_i; the energy does not depend on the sign convention
         dR = _min_image(Rc[cl(idx_j)] - Rc[cl(idx_i)], cell_t)
         dR_lr = _min_image(Rc[cl(idx_j_lr)] - Rc[cl(idx_i_lr)], cell_t)
+        positions = Rc if k_grid is not None else None
         if pert is not None:
             p = pert if torch.is_tensor(pert) else torch.as_tensor(pert)
             p = p.to(device=dev, dtype=dR.dtype)
             if p.ndim == 0 or p.numel() == 1:
                 dR, dR_lr = dR * p.reshape(()), dR_lr * p.reshape(())
+                if positions is not None:     # positions and box are deformed with the displacements (jaxmd_utils.py:48-51)
+                    positions, cell_t = positions * p.reshape(()), cell_t * p.reshape(())
             else:
                 dR, dR_lr = dR @ p.T, dR_lr @ p.T
+                if positions is not None:
+                    positions = positions @ p.T
                 if cell_t is not None:
                     cell_t = cell_t @ p.T
-        return Graph(positions=Rc.float() if k_grid is not None else None, k_grid=k_grid, k_smearing=k_smearing, nodes=species_t, edges=dR.float(), centers=neighbor[0], others=neighbor[1], mask=None,
+        return Graph(positions=positions, k_grid=k_grid, k_smearing=k_smearing, nodes=species_t, edges=dR.float(), centers=neighbor[0], others=neighbor[1], mask=None,
                      total_charge=torch.tensor([float(total_charge)]), num_unpaired_electrons=torch.zeros(1), edges_lr=dR_lr.float(),
                      idx_i_lr=neighbor_lr[0], idx_j_lr=neighbor_lr[1], cell=cell_t)
 

@@ -504,7 +504,8 @@ bool graph_fast_path() {
 // returns at once -- no host read, so the call stays enqueue-only.
 int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, const int* nbr_j, const int* edge_i, long long n_edges,
                    const int* row_ptr_lr, const int* nbr_j_lr, const float* dR_in, const float* dR_lr_in, float* g_dR,
-                   float* g_dR_lr_out, const float* ge, const float* positions = nullptr, float* g_positions = nullptr) {
+                   float* g_dR_lr_out, const float* ge, const float* positions = nullptr, float* g_positions = nullptr,
+                   float* strain6 = nullptr) {
   const ModelDev& M = S->mctx;
   const int n = S->n;
   // the reciprocal-space part needs the positions and returns its own gradient; its per-atom energies are not separable, so a
@@ -545,7 +546,8 @@ int evaluate_graph(so3lr_b200_system* S, cudaStream_t st, const int* row_ptr, co
                  S->gh, S->e_coul, S->e_disp, ge);
   if (S->ks.mode) {
     fill(st, g_positions, (size_t)n * 3, 0.f);
-    int rck = launch_ewald(st, S->ks, S->cell, n, positions, S->q, S->d_total_charge, S->e_coul, S->gq, g_positions, nullptr, -1.f);
+    if (strain6) fill(st, strain6, 6, 0.f);
+    int rck = launch_ewald(st, S->ks, S->cell, n, positions, S->q, S->d_total_charge, S->e_coul, S->gq, g_positions, strain6, -1.f);
     if (rck) return rck;
   }
   S->prof.end(st);
@@ -1213,7 +1215,7 @@ SO3LR_B200_API int so3lr_b200_system_export_list(so3lr_b200_system* S, void* str
 static int graph_eval_impl(so3lr_b200_system* S, void* stream, int64_t n_edges, const int32_t* idx_i, const int32_t* idx_j,
                            const float* edges, int64_t n_pairs, const int32_t* idx_i_lr, const int32_t* idx_j_lr,
                            const float* edges_lr, const float* g_e_atom, float* e_atom, float* g_edges, float* g_edges_lr,
-                           float* charges, float* hirshfeld, const float* positions, float* g_positions) {
+                           float* charges, float* hirshfeld, const float* positions, float* g_positions, float* strain6) {
   if (!S || !idx_i || !idx_j || !edges || !g_edges || n_edges < 0 || n_pairs < 0) return kInvalidArgument;
   if (n_pairs > 0 && (!idx_i_lr || !idx_j_lr || !edges_lr || !g_edges_lr)) return kInvalidArgument;
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
@@ -1226,7 +1228,7 @@ static int graph_eval_impl(so3lr_b200_system* S, void* stream, int64_t n_edges, 
   { row_ptr_from_sorted_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(n, n_edges, idx_i, S->d_rowptr_g); count_launch(); }
   { row_ptr_from_sorted_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(n, n_pairs, idx_i_lr, S->d_rowptr_lr_g); count_launch(); }
   int rc = evaluate_graph(S, st, S->d_rowptr_g, idx_j, idx_i, n_edges, S->d_rowptr_lr_g, idx_j_lr, edges, edges_lr, g_edges, g_edges_lr,
-                          g_e_atom, positions, g_positions);
+                          g_e_atom, positions, g_positions, strain6);
   if (rc) return rc;
   if (e_atom) SO3LR_CUDA_CHECK(cudaMemcpyAsync(e_atom, S->e_atom, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
   if (charges) SO3LR_CUDA_CHECK(cudaMemcpyAsync(charges, S->q, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
@@ -1239,16 +1241,17 @@ SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* S, void* stre
                                  const float* edges_lr, const float* g_e_atom, float* e_atom, float* g_edges, float* g_edges_lr,
                                  float* charges, float* hirshfeld) {
   return graph_eval_impl(S, stream, n_edges, idx_i, idx_j, edges, n_pairs, idx_i_lr, idx_j_lr, edges_lr, g_e_atom, e_atom, g_edges, g_edges_lr,
-                         charges, hirshfeld, nullptr, nullptr);
+                         charges, hirshfeld, nullptr, nullptr, nullptr);
 }
 
 SO3LR_B200_API int so3lr_b200_system_graph_eval_kspace(so3lr_b200_system* S, void* stream, int64_t n_edges, const int32_t* idx_i,
                                         const int32_t* idx_j, const float* edges, int64_t n_pairs, const int32_t* idx_i_lr,
                                         const int32_t* idx_j_lr, const float* edges_lr, const float* positions, float* e_atom,
-                                        float* g_edges, float* g_edges_lr, float* g_positions, float* charges, float* hirshfeld) {
+                                        float* g_edges, float* g_edges_lr, float* g_positions, float* strain6, float* charges,
+                                        float* hirshfeld) {
   if (!S || !S->ks.mode || !positions || !g_positions) return kInvalidArgument;
   return graph_eval_impl(S, stream, n_edges, idx_i, idx_j, edges, n_pairs, idx_i_lr, idx_j_lr, edges_lr, nullptr, e_atom, g_edges, g_edges_lr,
-                         charges, hirshfeld, positions, g_positions);
+                         charges, hirshfeld, positions, g_positions, strain6);
 }
 
 SO3LR_B200_API int so3lr_b200_system_nve(so3lr_b200_system* S, void* stream, int n_steps, float dt, const float* masses, float* R, float* V,

@@ -213,7 +213,8 @@ class System:
 
     def graph_eval(self, idx_i, idx_j, edges, idx_i_lr, idx_j_lr, edges_lr, g_e_atom=None, positions=None):
         """`positions` (n, 3): required while the reciprocal-space part is on; the result then holds `g_positions`, the gradient
-        of that part with respect to the positions at fixed charges."""
+        of that part with respect to the positions at fixed charges, and `kspace_strain`, its strain derivative at fixed fractional
+        coordinates (xx yy zz yz xz xy)."""
         dev = self.device
         t = lambda a, dt: a.to(dev, dt).contiguous()
         idx_i, idx_j, idx_i_lr, idx_j_lr = (t(a, torch.int32) for a in (idx_i, idx_j, idx_i_lr, idx_j_lr))
@@ -228,10 +229,11 @@ class System:
                 raise ValueError("with the reciprocal-space part on, graph_eval needs `positions` and a uniform upstream cotangent")
             R = t(positions, torch.float32)
             out["g_positions"] = torch.empty(n, 3, device=dev)
+            out["kspace_strain"] = torch.empty(6, device=dev)
             check(lib.so3lr_b200_system_graph_eval_kspace(self._h, C.c_void_p(s.cuda_stream), edges.shape[0], _ptr(idx_i), _ptr(idx_j),
                                                           _ptr(edges), edges_lr.shape[0], _ptr(idx_i_lr), _ptr(idx_j_lr), _ptr(edges_lr),
                                                           _ptr(R), _ptr(out["e_atom"]), _ptr(out["g_edges"]), _ptr(out["g_edges_lr"]),
-                                                          _ptr(out["g_positions"]), _ptr(out["partial_charges"]),
+                                                          _ptr(out["g_positions"]), _ptr(out["kspace_strain"]), _ptr(out["partial_charges"]),
                                                           _ptr(out["hirshfeld_ratios"])), "graph_eval_kspace")
             return out
         check(lib.so3lr_b200_system_graph_eval(self._h, C.c_void_p(s.cuda_stream), edges.shape[0], _ptr(idx_i), _ptr(idx_j), _ptr(edges),

@@ -122,6 +122,12 @@ def test_energy_function_with_k_grid_matches_the_fused_entry(oracle_params, refe
     ref = O.energy_forces(oracle_params, R.astype(np.float64), Z, cell, cutoff_lr=6.0, damping=2.0, k_grid=shape, k_smearing=smearing)
     assert abs(E - ref["energy"]) < 1e-5 * abs(ref["energy"]), (E, ref["energy"])
     assert np.abs(F - ref["forces"]).max() < 1e-4
+    # the route of the reference's NPT: the strain derivative as the gradient with respect to `perturbation`, which deforms the
+    # displacements, the positions and the box (so3lr/jaxmd_utils.py:48-51)
+    P = torch.eye(3, dtype=torch.float64, requires_grad=True)
+    (gP,) = torch.autograd.grad(energy_fn(Rt, perturbation=P, **kw), P)
+    err = np.abs(gP.cpu().numpy() - ref["virial"]).max()
+    assert err <= 2 * _vir_tol(R, ref["forces"]), (err, _vir_tol(R, ref["forces"]))
     # the same potential without k_grid evaluates the truncated pair sum again
     kw2 = dict(neighbor=nbrs.idx, neighbor_lr=nbrs_lr.idx, box=box)
     plain = O.energy_forces(oracle_params, R.astype(np.float64), Z, cell, cutoff_lr=6.0, damping=2.0)
