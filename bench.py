@@ -210,6 +210,15 @@ def tensor_roofline(groups, N, E=0):
             "note": "issued FP16 MMA FLOPs (3 per FP32-accurate product) over the kernel's launch time"}
 
 
+def kspace_shape(args, cell):
+    """Grid of `--kspace`: ewald -> one index per `--kspace-wavelength` of each cell edge (the reference's
+    get_kgrid_ewald(cell, lr_wavelength)); pme -> power-of-two mesh with at most that much between points (get_kgrid_mesh)."""
+    edge = [float(np.linalg.norm(np.asarray(cell, dtype=np.float64)[d])) for d in range(3)]
+    if args.kspace == "ewald":
+        return tuple(int(max(1, np.ceil(e / args.kspace_wavelength - 1e-9))) for e in edge)
+    return tuple(int(2 ** max(2, int(np.ceil(np.log2(e / args.kspace_wavelength) - 1e-9)))) for e in edge)
+
+
 def run_b200(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -240,11 +249,7 @@ def run_b200(args, rank, world, local_rank):
         # reciprocal-space Coulomb sum, Gaussian smearing in Angstrom.  ewald: index grid with one index per `wavelength` of each
         # cell edge (the reference's get_kgrid_ewald(cell, lr_wavelength)); pme: power-of-two mesh with at most `wavelength`
         # between its points (get_kgrid_mesh(cell, mesh_spacing))
-        edge = [float(np.linalg.norm(np.asarray(cell, dtype=np.float64)[d])) for d in range(3)]
-        if args.kspace == "ewald":
-            shape = tuple(int(max(1, np.ceil(e / args.kspace_wavelength - 1e-9))) for e in edge)
-        else:
-            shape = tuple(int(2 ** max(2, int(np.ceil(np.log2(e / args.kspace_wavelength) - 1e-9)))) for e in edge)
+        shape = kspace_shape(args, cell)
         sysm.set_kspace(shape, args.kspace_smearing, args.kspace)
         kspace = {"method": args.kspace, "smearing_A": args.kspace_smearing, "lr_wavelength_A": args.kspace_wavelength,
                   "k_grid_shape": list(shape), "k_vectors": sysm.kspace_vectors()}
@@ -474,6 +479,12 @@ def run_domain(args, rank, world, local_rank):
     if ensemble == "npt":
         backend.enable_virial(True)
     dom.defer_skin_test(True, 0.05)      # no host read inside a step: the rebuild decision is taken one step late
+    kspace = None
+    if args.kspace != "off":
+        shape = kspace_shape(args, cell)
+        dom.set_kspace(shape, args.kspace_smearing, args.kspace)
+        kspace = {"method": args.kspace, "smearing_A": args.kspace_smearing, "lr_wavelength_A": args.kspace_wavelength,
+                  "k_grid_shape": list(shape), "exchange": "all-reduce of the charge mesh / structure factors over the ranks"}
     dom.compute(check_rebuild=False)
     # one clock sampler for all GPUs, on rank 0, started ahead of the warm-up (its start-up disturbs running CUDA work)
     sampler = ClockSampler(list(range(world))) if rank == 0 else None
@@ -597,6 +608,8 @@ def run_domain(args, rank, world, local_rank):
                 "e2e": {"value": round(N * args.steps / t_e2e, 1), "unit": UNIT, "h2d_bytes_per_step": N * 12 * world,
                         "d2h_bytes_per_step": (N * 12 + 8) * world, "ms_per_step": round(1e3 * t_e2e / args.steps, 3)},
                 "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": None}
+        if kspace is not None:
+            line["config"]["kspace"] = kspace
         print(json.dumps(line), flush=True)
     dist.barrier()
     dist.destroy_process_group()

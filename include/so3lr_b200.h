@@ -151,7 +151,7 @@ SO3LR_B200_API int so3lr_b200_system_graph_eval(so3lr_b200_system* sys, void* st
  *   ke / (2 V) sum_{k != 0} 4 pi / k^2 exp(-smearing^2 k^2 / 2) |S(k)|^2 - ke sum_i q_i^2 / (sqrt(2 pi) smearing) - ke pi smearing^2 Q^2 / V
  * with its forces, its dE/dq (which continues into the charge head's reverse pass) and its strain derivative.  The cell may change
  * afterwards (so3lr_b200_system_rescale_cell): the grid shape stays, the k vectors follow the cell.  Allocates and waits for the
- * device: call it between evaluations.  Not available in decomposed (so3lr_b200_dd_*) evaluations.
+ * device: call it between evaluations.  In decomposed evaluations it is driven through so3lr_b200_dd_kspace_*.
  * Replaces: the `k_grid` / `k_smearing` arguments of the reference's energy function (so3lr/jaxmd_utils.py:39-47,70-71), the
  *           grid set-up of so3lr/cli/so3lr_md.py:1392-1428 and the `coulomb_kspace_*` options of so3lr/potential.py:11-25. */
 SO3LR_B200_API int so3lr_b200_system_set_kspace(so3lr_b200_system* sys, int mode, float smearing, int n1, int n2, int n3);
@@ -286,6 +286,19 @@ SO3LR_B200_API int so3lr_b200_dd_layer_forward(so3lr_b200_system* sys, void* str
 SO3LR_B200_API int so3lr_b200_dd_heads(so3lr_b200_system* sys, void* stream, float* q_raw_owned_dev, float* h_owned_dev);
 SO3LR_B200_API int so3lr_b200_dd_pair(so3lr_b200_system* sys, void* stream, const float* R_local_dev, const float* q_local_dev,
                                       const float* h_local_dev, double* gq_sum_dev);
+/* Reciprocal-space part in a decomposed evaluation (so3lr_b200_system_set_kspace on every rank's context first, with the same
+ * arguments).  so3lr_b200_dd_kspace_cell gives the cell of the WHOLE structure (the context's own cell is the rank's local one)
+ * and its total charge; call it again when the cell is rescaled.  Between so3lr_b200_dd_pair and so3lr_b200_dd_heads_backward:
+ * _accumulate forms the owned atoms' share of the charge mesh (or of the structure factors) and names the buffer, the caller
+ * sums that buffer over the ranks in place (an all-reduce of *n_floats floats: the one exchange step of this part), and _finish
+ * transforms it and adds potential energies, dE/dq and forces of the owned atoms; gq_sum_dev then holds the sum of dE/dq over
+ * the owned atoms including the pair part (it replaces the value so3lr_b200_dd_pair returned).  The strain derivative of the whole
+ * reciprocal sum is added on the rank that passes add_strain != 0 (exactly one rank should). */
+SO3LR_B200_API int so3lr_b200_dd_kspace_cell(so3lr_b200_system* sys, const float* cell9_global, float total_charge);
+SO3LR_B200_API int so3lr_b200_dd_kspace_accumulate(so3lr_b200_system* sys, void* stream, const float* R_local_dev, const float* q_local_dev,
+                                                   float** buffer_dev, int64_t* n_floats);
+SO3LR_B200_API int so3lr_b200_dd_kspace_finish(so3lr_b200_system* sys, void* stream, const float* R_local_dev, const float* q_local_dev,
+                                               int add_strain, double* gq_sum_dev);
 SO3LR_B200_API int so3lr_b200_dd_heads_backward(so3lr_b200_system* sys, void* stream, const double* gq_sum_all_dev,
                                                 int64_t n_atoms_all, double* energy_owned_dev);
 SO3LR_B200_API int so3lr_b200_dd_layer_backward_post(so3lr_b200_system* sys, void* stream, int layer);

@@ -67,6 +67,9 @@ def _load():
         "so3lr_b200_dd_layer_forward": (i32, [p, p, i32]),
         "so3lr_b200_dd_heads": (i32, [p, p, p, p]),
         "so3lr_b200_dd_pair": (i32, [p, p, p, p, p, p]),
+        "so3lr_b200_dd_kspace_cell": (i32, [p, p, f32]),
+        "so3lr_b200_dd_kspace_accumulate": (i32, [p, p, p, p, C.POINTER(p), C.POINTER(i64)]),
+        "so3lr_b200_dd_kspace_finish": (i32, [p, p, p, p, i32, p]),
         "so3lr_b200_dd_heads_backward": (i32, [p, p, p, i64, p]),
         "so3lr_b200_dd_layer_backward_post": (i32, [p, p, i32]),
         "so3lr_b200_dd_layer_backward_attn": (i32, [p, p, i32]),

@@ -260,6 +260,8 @@ struct so3lr_b200_system {
   Cell cell{};
   LrParams lr{};
   KSpaceDev ks{};                // reciprocal-space Coulomb part (off unless so3lr_b200_system_set_kspace switched it on)
+  Cell ks_cell{};                // decomposed evaluation: the cell of the whole structure (`cell` is the rank's local one)
+  bool ks_cell_set = false;
   Pool pool;
   // static inputs.  d_Z is the array the kernels read: d_Z0 (caller order) or d_Zs (sorted order)
   int *d_Z = nullptr, *d_Z0 = nullptr, *d_Zs = nullptr, *d_seg = nullptr, *d_graph_start = nullptr;
@@ -1462,8 +1464,8 @@ SO3LR_B200_API int so3lr_b200_dd_set_atoms(so3lr_b200_system* S, int n_local, co
                                            const float* cell9) {
   if (!S || !shells4 || !Z_local_dev || n_local <= 0) return kInvalidArgument;
   if (S->n_graphs != 1) return kInvalidArgument;
-  if (S->ks.mode) {
-    std::fprintf(stderr, "so3lr_b200: the reciprocal-space Coulomb sum is not available in a decomposed evaluation\n");
+  if (S->ks.mode && !S->ks_cell_set) {
+    std::fprintf(stderr, "so3lr_b200: a decomposed evaluation with the reciprocal-space Coulomb sum needs so3lr_b200_dd_kspace_cell first\n");
     return kInvalidArgument;
   }
   if (S->mctx.embed_z != S->model->M.embed_z) {
@@ -1595,6 +1597,48 @@ SO3LR_B200_API int so3lr_b200_dd_pair(so3lr_b200_system* S, void* stream, const 
   launch_pair_lr_owned(st, S->lr, S->cell, n0, S->n, S->lrl.row_ptr, S->lrl.nbr_j, S->d_Z, R_local_dev, q_local_dev, h_local_dev, S->F_s,
                        S->gq, S->gh, S->e_coul, S->e_disp, S->vir());
   S->prof.end(st);
+  { sum_to_double_kernel<<<1, 1024, 0, st>>>(n0, S->gq, gq_sum_dev); count_launch(); }
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_dd_kspace_cell(so3lr_b200_system* S, const float* cell9_global, float total_charge) {
+  if (!S || !cell9_global) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  int rc = make_cell(cell9_global, &S->ks_cell);
+  if (rc) return rc;
+  if (!S->ks_cell.periodic) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaMemcpy(S->d_total_charge, &total_charge, sizeof(float), cudaMemcpyHostToDevice));
+  S->ks_cell_set = true;
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_dd_kspace_accumulate(so3lr_b200_system* S, void* stream, const float* R_local_dev, const float* q_local_dev,
+                                                   float** buffer_dev, int64_t* n_floats) {
+  if (!S || !R_local_dev || !q_local_dev || !buffer_dev || !n_floats || !S->ks.mode || !S->ks_cell_set || !S->have_lists) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
+  cudaStream_t st = (cudaStream_t)stream;
+  long long nf = 0;
+  S->prof.begin(kPKspace, st);
+  int rc = kspace_accumulate(st, S->ks, S->ks_cell, S->shells[0], R_local_dev, q_local_dev, buffer_dev, &nf);
+  S->prof.end(st);
+  *n_floats = nf;
+  return rc;
+}
+
+SO3LR_B200_API int so3lr_b200_dd_kspace_finish(so3lr_b200_system* S, void* stream, const float* R_local_dev, const float* q_local_dev,
+                                               int add_strain, double* gq_sum_dev) {
+  if (!S || !R_local_dev || !q_local_dev || !gq_sum_dev || !S->ks.mode || !S->ks_cell_set || !S->have_lists) return kInvalidArgument;
+  SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
+  tl_launch_counter = &S->n_launches;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int n0 = S->shells[0];
+  S->prof.begin(kPKspace, st);
+  int rc = kspace_finish(st, S->ks, S->ks_cell, n0, R_local_dev, q_local_dev, S->d_total_charge, S->e_coul, S->gq, S->F_s,
+                         add_strain ? S->vir() : nullptr, 1.f);
+  S->prof.end(st);
+  if (rc) return rc;
   { sum_to_double_kernel<<<1, 1024, 0, st>>>(n0, S->gq, gq_sum_dev); count_launch(); }
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;

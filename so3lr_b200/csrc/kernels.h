@@ -67,6 +67,11 @@ int kspace_setup(KSpaceDev* K, int n_atoms, int mode, float smearing, int n1, in
 void kspace_free(KSpaceDev* K);
 // adds to e_coul (per-atom energies), gq (dE/dq), F (force_sign = 1: forces at fixed charges; -1: the gradient) and, when given, the
 // six virial components of one row
+// the two halves of launch_ewald: what is additive over atoms (charge mesh or structure factors; `buffer` / `n_floats` name it), and the rest
+int kspace_accumulate(cudaStream_t st, const KSpaceDev& K, const Cell& cell, int n, const float* R, const float* q, float** buffer,
+                      long long* n_floats);
+int kspace_finish(cudaStream_t st, const KSpaceDev& K, const Cell& cell, int n, const float* R, const float* q, const float* total_charge,
+                  float* e_coul, float* gq, float* F, float* virial_row, float force_sign);
 int launch_ewald(cudaStream_t st, const KSpaceDev& K, const Cell& cell, int n, const float* R, const float* q, const float* total_charge,
                  float* e_coul, float* gq, float* F, float* virial_row, float force_sign);
 

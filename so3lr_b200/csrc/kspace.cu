@@ -475,53 +475,81 @@ int kspace_setup(KSpaceDev* K, int n_atoms, int mode, float smearing, int n1, in
   return kOk;
 }
 
-int launch_ewald(cudaStream_t st, const KSpaceDev& K, const Cell& cell, int n, const float* R, const float* q, const float* total_charge,
-                 float* e_coul, float* gq, float* F, float* virial_row, float force_sign) {
-  if ((K.mode != 1 && K.mode != 2) || !cell.periodic) return kInvalidArgument;
+namespace {
+float inverse_volume(const Cell& cell) {
   const float* h = cell.h;
   const double det = (double)h[0] * ((double)h[4] * h[8] - (double)h[5] * h[7]) - (double)h[1] * ((double)h[3] * h[8] - (double)h[5] * h[6]) +
                      (double)h[2] * ((double)h[3] * h[7] - (double)h[4] * h[6]);
-  const float inv_vol = (float)(1.0 / (det < 0 ? -det : det));
+  return (float)(1.0 / (det < 0 ? -det : det));
+}
+}  // namespace
+
+// first half: the quantity that is additive over atoms -- the charge mesh (mode 2) or the structure factors (mode 1) of atoms [0, n).
+// A decomposed evaluation sums it over the ranks before the second half.
+int kspace_accumulate(cudaStream_t st, const KSpaceDev& K, const Cell& cell, int n, const float* R, const float* q, float** buffer,
+                      long long* n_floats) {
+  if ((K.mode != 1 && K.mode != 2) || !cell.periodic) return kInvalidArgument;
+  if (K.mode == 2) {
+    const int n1 = K.shape[0], n2 = K.shape[1], n3 = K.shape[2];
+    SO3LR_CUDA_CHECK(cudaMemsetAsync(K.mesh, 0, (size_t)n1 * n2 * n3 * sizeof(float), st));
+    { pme_spread_kernel<<<(unsigned)(((long long)n * 4 + 255) / 256), 256, 0, st>>>(cell, n, n1, n2, n3, R, q, K.mesh); count_launch(); }
+    if (buffer) *buffer = K.mesh;
+    if (n_floats) *n_floats = (long long)n1 * n2 * n3;
+  } else {
+    SO3LR_CUDA_CHECK(cudaMemsetAsync(K.Sk, 0, (size_t)K.n_tiles * kTileK * sizeof(float2), st));
+    // tiles x atom slices
+    int splits = (4 * sm_count() + K.n_tiles - 1) / K.n_tiles;
+    const int max_splits = (n + kStage - 1) / kStage;
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    int per = (n + splits - 1) / splits;
+    per = (per + kStage - 1) / kStage * kStage;
+    splits = (n + per - 1) / per;
+    { ewald_structure_kernel<<<dim3(K.n_tiles, splits), kTileK, 0, st>>>(cell, n, per, R, q, K.tiles, K.Sk); count_launch(); }
+    if (buffer) *buffer = reinterpret_cast<float*>(K.Sk);
+    if (n_floats) *n_floats = 2LL * K.n_tiles * kTileK;
+  }
+  SO3LR_CUDA_CHECK(cudaGetLastError());
+  return kOk;
+}
+
+// second half, for atoms [0, n): potential, forces and (virial_row given) the strain derivative of the whole sum
+int kspace_finish(cudaStream_t st, const KSpaceDev& K, const Cell& cell, int n, const float* R, const float* q, const float* total_charge,
+                  float* e_coul, float* gq, float* F, float* virial_row, float force_sign) {
+  if ((K.mode != 1 && K.mode != 2) || !cell.periodic) return kInvalidArgument;
+  const float inv_vol = inverse_volume(cell);
   if (K.mode == 2) {
     CufftApi* f = cufft_api();
     if (!f || !K.plans) return kCudaError;
     const int n1 = K.shape[0], n2 = K.shape[1], n3 = K.shape[2];
-    SO3LR_CUDA_CHECK(cudaMemsetAsync(K.mesh, 0, (size_t)n1 * n2 * n3 * sizeof(float), st));
-    { pme_spread_kernel<<<(unsigned)(((long long)n * 4 + 255) / 256), 256, 0, st>>>(cell, n, n1, n2, n3, R, q, K.mesh); count_launch(); }
     if (f->set_stream(K.plan_r2c, st) != CUFFT_SUCCESS || f->set_stream(K.plan_c2r, st) != CUFFT_SUCCESS) return kCudaError;
     if (f->exec_r2c(K.plan_r2c, K.mesh, reinterpret_cast<cufftComplex*>(K.fq)) != CUFFT_SUCCESS) return kCudaError;
     const long long total = (long long)n1 * n2 * (n3 / 2 + 1);
     { pme_influence_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(cell, inv_vol, K.smearing, n1, n2, n3, K.fq, total_charge, virial_row); count_launch(); }
     if (f->exec_c2r(K.plan_c2r, reinterpret_cast<cufftComplex*>(K.fq), K.mesh) != CUFFT_SUCCESS) return kCudaError;
     { pme_gather_kernel<<<(n + 127) / 128, 128, 0, st>>>(cell, n, n1, n2, n3, R, K.mesh, K.acc); count_launch(); }
-    { ewald_finish_kernel<<<(n + 255) / 256, 256, 0, st>>>(cell, inv_vol, K.smearing, n, q, total_charge, K.acc, e_coul, gq, F, force_sign); count_launch(); }
-    SO3LR_CUDA_CHECK(cudaGetLastError());
-    return kOk;
+  } else {
+    SO3LR_CUDA_CHECK(cudaMemsetAsync(K.acc, 0, (size_t)n * 4 * sizeof(float), st));
+    // atom blocks x tile slices
+    const int blocks = (n + 127) / 128;
+    int ksplits = (4 * sm_count() + blocks - 1) / blocks;
+    if (ksplits > K.n_tiles) ksplits = K.n_tiles;
+    if (ksplits < 1) ksplits = 1;
+    const int tper = (K.n_tiles + ksplits - 1) / ksplits;
+    ksplits = (K.n_tiles + tper - 1) / tper;
+    { ewald_atom_kernel<<<dim3(blocks, ksplits), 128, 0, st>>>(cell, inv_vol, K.smearing, n, K.n_tiles, tper, R, K.tiles, K.wgt, K.Sk, K.acc); count_launch(); }
+    if (virial_row) { ewald_virial_kernel<<<K.n_tiles, kTileK, 0, st>>>(cell, inv_vol, K.smearing, K.tiles, K.wgt, K.Sk, total_charge, virial_row); count_launch(); }
   }
-  SO3LR_CUDA_CHECK(cudaMemsetAsync(K.Sk, 0, (size_t)K.n_tiles * kTileK * sizeof(float2), st));
-  SO3LR_CUDA_CHECK(cudaMemsetAsync(K.acc, 0, (size_t)n * 4 * sizeof(float), st));
-  const int target = 4 * sm_count();
-  // structure factors: tiles x atom slices
-  int splits = (target + K.n_tiles - 1) / K.n_tiles;
-  const int max_splits = (n + kStage - 1) / kStage;
-  if (splits > max_splits) splits = max_splits;
-  if (splits < 1) splits = 1;
-  int per = (n + splits - 1) / splits;
-  per = (per + kStage - 1) / kStage * kStage;
-  splits = (n + per - 1) / per;
-  { ewald_structure_kernel<<<dim3(K.n_tiles, splits), kTileK, 0, st>>>(cell, n, per, R, q, K.tiles, K.Sk); count_launch(); }
-  // per-atom sums: atom blocks x tile slices
-  const int blocks = (n + 127) / 128;
-  int ksplits = (target + blocks - 1) / blocks;
-  if (ksplits > K.n_tiles) ksplits = K.n_tiles;
-  if (ksplits < 1) ksplits = 1;
-  const int tper = (K.n_tiles + ksplits - 1) / ksplits;
-  ksplits = (K.n_tiles + tper - 1) / tper;
-  { ewald_atom_kernel<<<dim3(blocks, ksplits), 128, 0, st>>>(cell, inv_vol, K.smearing, n, K.n_tiles, tper, R, K.tiles, K.wgt, K.Sk, K.acc); count_launch(); }
   { ewald_finish_kernel<<<(n + 255) / 256, 256, 0, st>>>(cell, inv_vol, K.smearing, n, q, total_charge, K.acc, e_coul, gq, F, force_sign); count_launch(); }
-  if (virial_row) { ewald_virial_kernel<<<K.n_tiles, kTileK, 0, st>>>(cell, inv_vol, K.smearing, K.tiles, K.wgt, K.Sk, total_charge, virial_row); count_launch(); }
   SO3LR_CUDA_CHECK(cudaGetLastError());
   return kOk;
+}
+
+int launch_ewald(cudaStream_t st, const KSpaceDev& K, const Cell& cell, int n, const float* R, const float* q, const float* total_charge,
+                 float* e_coul, float* gq, float* F, float* virial_row, float force_sign) {
+  int rc = kspace_accumulate(st, K, cell, n, R, q, nullptr, nullptr);
+  if (rc) return rc;
+  return kspace_finish(st, K, cell, n, R, q, total_charge, e_coul, gq, F, virial_row, force_sign);
 }
 
 }  // namespace so3lr

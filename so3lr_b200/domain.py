@@ -243,6 +243,7 @@ class CudaBackend:
         self.sys = None
         self.capacity = 0
         self.want_virial = False
+        self.kspace = None          # (grid shape, smearing, method, cell of the whole structure, total charge)
 
     def _stream(self):
         return C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
@@ -268,6 +269,7 @@ class CudaBackend:
                               skin=self.skin, lr_format="sparse", model=self.model)
             if self.want_virial:
                 self.sys.enable_virial(True)
+            self._apply_kspace()
         self.n, self.counts = n, [int(v) for v in counts]
         sh = np.asarray([self.counts[0], self.counts[1], self.counts[1], n], dtype=np.int32)
         c9 = np.ascontiguousarray(np.asarray(cell_local, dtype=np.float32).reshape(9))
@@ -277,6 +279,41 @@ class CudaBackend:
         self._x = [self._buffer(0, l) for l in range(4)]
         self._ev = [self._buffer(1, l) for l in range(4)]
         self._g = [self._buffer(2, 0), self._buffer(3, 0)]
+
+    # ---- reciprocal-space Coulomb part: every rank holds the whole mesh (or all structure factors) ----
+    def set_kspace(self, k_grid, k_smearing, method, cell_global, total_charge):
+        self.kspace = None if k_grid is None else (k_grid, k_smearing, method, np.asarray(cell_global, dtype=np.float64).copy(),
+                                                   float(total_charge))
+        if self.sys is not None:
+            self._apply_kspace()
+
+    def _apply_kspace(self):
+        if self.kspace is None:
+            self.sys.set_kspace(None)
+            return
+        shape, smearing, method, cell, qtot = self.kspace
+        self.sys.set_kspace(shape, smearing, method)
+        self.kspace_cell(cell)
+
+    def kspace_cell(self, cell_global):
+        from .engine import _ptr
+        shape, smearing, method, _, qtot = self.kspace
+        self.kspace = (shape, smearing, method, np.asarray(cell_global, dtype=np.float64).copy(), qtot)
+        c9 = np.ascontiguousarray(np.asarray(cell_global, dtype=np.float32).reshape(9))
+        self._call("dd_kspace_cell", _ptr(c9), C.c_float(qtot))
+
+    def kspace_accumulate(self):
+        """The owned atoms' share of the charge mesh / structure factors: a flat float32 view to be summed over the ranks in place."""
+        from .engine import _from_ptr, _ptr
+        ptr, nf = C.c_void_p(), C.c_int64()
+        self._call("dd_kspace_accumulate", self._stream(), _ptr(self._R), _ptr(self._q), C.byref(ptr), C.byref(nf))
+        return _from_ptr(ptr.value, nf.value, self.device)
+
+    def kspace_finish(self, add_strain):
+        from .engine import _ptr
+        s = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self._call("dd_kspace_finish", self._stream(), _ptr(self._R), _ptr(self._q), 1 if add_strain else 0, _ptr(s))
+        return s
 
     def enable_virial(self, on=True):
         self.want_virial = bool(on)
@@ -403,7 +440,21 @@ class DomainSystem:
         R = torch.as_tensor(np.asarray(positions), dtype=torch.float32, device=self.device)
         V = None if velocities is None else torch.as_tensor(np.asarray(velocities), dtype=torch.float32, device=self.device)
         self.n_rebuilds = 0
+        self.kspace = None
         self._partition(R, V)
+
+    def set_kspace(self, k_grid=None, k_smearing=None, method="pme"):
+        """Reciprocal-space Coulomb part (System.set_kspace) for the decomposed structure; `k_grid=None` switches it off."""
+        if not hasattr(self.backend, "set_kspace"):
+            raise NotImplementedError("this backend has no reciprocal-space part")
+        if k_grid is None:
+            self.kspace = None
+            self.backend.set_kspace(None, None, None, self.geo.cell, self.total_charge)
+            return
+        shape = tuple(int(v) for v in (k_grid.shape if hasattr(k_grid, "shape") else k_grid))
+        s = float(np.asarray(k_smearing.detach().cpu() if torch.is_tensor(k_smearing) else k_smearing, dtype=np.float64).reshape(-1)[0])
+        self.kspace = (shape, s, method)
+        self.backend.set_kspace(shape, s, method, self.geo.cell, self.total_charge)
 
     # ---- partition / halo plans (all ranks hold identical R_all here) ----
     def _peers(self):
@@ -615,8 +666,18 @@ class DomainSystem:
         self._mark("heads_charge_sum")
         self._halo_fill([qh])
         self._mark("halo_charges")
-        gq_sum = self.comm.all_reduce_sum(be.pair(qh[:, 0].contiguous(), qh[:, 1].contiguous()))
+        gq_own = be.pair(qh[:, 0].contiguous(), qh[:, 1].contiguous())
         self._mark("pair_terms")
+        if self.kspace is not None:
+            # every rank spreads its own atoms, the meshes (or structure factors) are summed over the ranks, and every rank
+            # transforms the whole mesh and reads it at its own atoms
+            buf = be.kspace_accumulate()
+            tot = self.comm.all_reduce_sum(buf)
+            if tot.data_ptr() != buf.data_ptr():
+                buf.copy_(tot)
+            gq_own = be.kspace_finish(add_strain=self.rank == 0)
+            self._mark("kspace")
+        gq_sum = self.comm.all_reduce_sum(gq_own)
         E_own = be.heads_backward(gq_sum, self.n_all)
         self._mark("heads_backward")
         for l in reversed(range(L)):
@@ -704,6 +765,8 @@ class DomainSystem:
             a_vec = torch.tensor(self.geo.cell[self.geo.axis], dtype=torch.float32, device=self.device)
             self.shift_vec = self.shift[:, None].to(torch.float32) * a_vec
             self.backend.rescale_cell(self.geo.local_cell())
+            if self.kspace is not None:
+                self.backend.kspace_cell(self.geo.cell)
             self.compute()
             self._virial_all = self.virial().contiguous()
             acc = (ACC_UNIT / self.m)[:, None]              # ownership may have changed

@@ -66,6 +66,42 @@ def test_decomposed_water_matches_single_device(reference_goldens, world):
     np.testing.assert_allclose(res[0][1], g["water_forces_jaxmd"], atol=5e-4)
 
 
+@pytest.mark.parametrize("world,method", [(2, "pme"), (3, "pme"), (2, "ewald")])
+def test_decomposed_water_with_the_reciprocal_sum_matches_single_device(reference_goldens, world, method):
+    """The charge mesh (or the structure factors) is summed over the ranks; everything else is per rank."""
+    from so3lr_b200 import domain as D
+    from so3lr_b200.engine import System
+    g = reference_goldens
+    Z, R, cell = g["water_Z"], np.asarray(g["water_R"], dtype=np.float32), g["water_cell"]
+    skin, shape, smearing = 0.5, ((32, 30, 36) if method == "pme" else (21, 20, 19)), 2.4
+    single = System(Z, cell, cutoff_lr=12.0, damping=2.0, skin=skin)
+    single.enable_virial(True)
+    single.set_kspace(shape, smearing, method)
+    ref = single.compute(torch.tensor(R, device="cuda"))
+    E_ref, F_ref, W_ref = float(ref["energy"].sum()), ref["forces"].cpu().numpy(), ref["virial"].cpu().numpy()
+
+    def fn(comm, rank):
+        be = D.CudaBackend(cutoff_lr=12.0, damping=2.0, skin=skin, device=0)
+        be.enable_virial(True)
+        dom = D.DomainSystem(comm, be, Z, R, cell, skin=skin, cutoff_lr=12.0, device="cuda:0")
+        dom.set_kspace(shape, smearing, method)
+        E, _ = dom.compute(check_rebuild=False)
+        W = dom.virial().cpu().numpy()
+        F = dom.global_forces().cpu().numpy()
+        dom.set_kspace(None)
+        E_plain, _ = dom.compute(check_rebuild=False)
+        return float(E), F, W, float(E_plain)
+
+    res = _run_threads(world, fn)
+    single.set_kspace(None)
+    E_plain_ref = float(single.compute(torch.tensor(R, device="cuda"))["energy"].sum())
+    for E, F, W, E_plain in res:
+        assert abs(E - E_ref) <= 1e-5 * abs(E_ref), (E, E_ref)
+        assert np.abs(F - F_ref).max() <= 1e-4, np.abs(F - F_ref).max()
+        assert np.abs(W - W_ref).max() <= 2e-3 + 1e-5 * np.abs(W_ref).max(), np.abs(W - W_ref).max()
+        assert abs(E_plain - E_plain_ref) <= 1e-5 * abs(E_plain_ref)
+
+
 def test_decomposed_nve_tracks_single_device_and_migrates(reference_goldens):
     from so3lr_b200 import domain as D
     from so3lr_b200 import workloads as W
