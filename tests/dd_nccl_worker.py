@@ -26,8 +26,13 @@ def main(out):
     dom.nve(20, 0.5)
     R1 = dom.gather_global(dom.R[: dom.n0]).cpu().numpy()
     F1 = dom.global_forces().cpu().numpy()
+    E1 = float(dom.E)
+    # the same positions with the reciprocal-space sum on: the charge mesh is all-reduced over NCCL
+    dom.set_kspace((32, 32, 32), 2.0, "pme")
+    Ek, _ = dom.compute(check_rebuild=False)
+    Fk = dom.global_forces().cpu().numpy()
     if rank == 0:
-        np.savez(out, E0=float(E0), F0=F0, R1=R1, F1=F1, E1=float(dom.E), rebuilds=dom.n_rebuilds)
+        np.savez(out, E0=float(E0), F0=F0, R1=R1, F1=F1, E1=E1, rebuilds=dom.n_rebuilds, Ek=float(Ek), Fk=Fk)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -29,3 +29,7 @@ def test_two_gpu_nccl_run_matches_single_device(tmp_path):
     assert abs(float(r["E1"]) - float(b["energy"].sum())) <= 1e-5 * abs(float(r["E1"]))
     assert np.abs(r["F1"] - b["forces"].cpu().numpy()).max() <= 1e-4
     assert int(r["rebuilds"]) >= 1
+    s.set_kspace((32, 32, 32), 2.0, "pme")
+    c = s.compute(torch.tensor(r["R1"], device="cuda"))
+    assert abs(float(r["Ek"]) - float(c["energy"].sum())) <= 1e-5 * abs(float(r["Ek"]))
+    assert np.abs(r["Fk"] - c["forces"].cpu().numpy()).max() <= 1e-4
