@@ -56,9 +56,49 @@ class ToyBackend:
         return torch.where(r < RC_LR, -3 * (1 - r / RC_LR) ** 2 / RC_LR / (1 + r) - (1 - r / RC_LR) ** 3 / (1 + r) ** 2,
                            torch.zeros_like(r))
 
+    # reciprocal-space stand-in: E_k = 1/2 sum_k g(k) |S(k)|^2 over a few k vectors of the whole cell, S(k) = sum_i q_i exp(i k r_i)
+    kvec = None
+
+    @staticmethod
+    def k_vectors(shape, smearing, cell):
+        h = np.stack(np.meshgrid(*[np.arange(-(n // 2), (n + 1) // 2) for n in shape], indexing="ij"), -1).reshape(-1, 3)
+        h = h[(h != 0).any(1)]
+        k = 2 * np.pi * torch.tensor(h, dtype=torch.float64) @ torch.linalg.inv(torch.as_tensor(np.asarray(cell), dtype=torch.float64)).T
+        k2 = (k * k).sum(-1)
+        return k, torch.exp(-0.5 * smearing ** 2 * k2) / k2
+
+    def set_kspace(self, shape, smearing, method, cell_global, total_charge):
+        self.kset = None if shape is None else (shape, smearing)
+        self.kvec = None
+        if shape is not None:
+            self.kspace_cell(cell_global)
+
+    def kspace_cell(self, cell_global):
+        self.kvec, self.kg = self.k_vectors(self.kset[0], self.kset[1], cell_global)
+
+    def kspace_accumulate(self):
+        th = self.Rown @ self.kvec.T
+        q = self.q_all[: self.n0]
+        self.S = torch.cat([(q[:, None] * torch.cos(th)).sum(0), (q[:, None] * torch.sin(th)).sum(0)])
+        return self.S
+
+    def kspace_finish(self, add_strain):
+        K = len(self.kvec)
+        Sr, Si = self.S[:K], self.S[K:]
+        th = self.Rown @ self.kvec.T
+        c, s = torch.cos(th), torch.sin(th)
+        q = self.q_all[: self.n0]
+        phi = ((c * Sr[None, :] + s * Si[None, :]) * self.kg[None, :]).sum(1)
+        self.e_k_half = 0.5 * (q * phi).sum()
+        self.gq = self.gq + phi
+        self.F -= q[:, None] * (((c * Si[None, :] - s * Sr[None, :]) * self.kg[None, :]) @ self.kvec)
+        return self.gq.sum().reshape(1)
+
     def begin(self, R_local):
         n0 = self.n0
         R = R_local.detach().to(torch.float64)
+        self.Rown = R[:n0]
+        self.e_k_half = 0.0
         self.d = _min_image(R[None, :, :] - R[:n0, None, :], self.cell)          # (n0, n, 3): R_j - R_i
         r = self.d.norm(dim=-1)
         r[torch.arange(n0), torch.arange(n0)] = 1e3
@@ -82,6 +122,7 @@ class ToyBackend:
     def pair(self, q_local, h_local):
         n0 = self.n0
         q = q_local.detach().to(torch.float64)
+        self.q_all = q
         chi = self.chi(self.r)
         self.e_pair_half = 0.5 * (q[:n0, None] * q[None, :] * chi).sum()
         self.gq = (q[None, :] * chi).sum(1)                                        # dE/dq_i over all pairs of i
@@ -94,7 +135,7 @@ class ToyBackend:
         xL = self.x[-1][:n0, 0]
         gq_raw = self.gq - gq_sum_all / n_all
         self.g = 2 * xL + gq_raw * (1 - torch.tanh(xL) ** 2)                        # cotangent of x_L, owned atoms
-        return ((xL ** 2).sum() + self.e_pair_half).reshape(1)
+        return ((xL ** 2).sum() + self.e_pair_half + self.e_k_half).reshape(1)
 
     def layer_backward_post(self, l):
         self.G.zero_()
@@ -134,7 +175,7 @@ class ToyBackend:
         chain[10:10 + chain_length] = torch.from_numpy(c.p_xi)
 
 
-def _serial_reference(R, cell):
+def _serial_reference(R, cell, kspace=None):
     R = torch.tensor(R, dtype=torch.float64, requires_grad=True)
     c = torch.tensor(cell, dtype=torch.float64)
     d = _min_image(R[None] - R[:, None], c)
@@ -145,6 +186,10 @@ def _serial_reference(R, cell):
     q = torch.tanh(x)
     q = q - q.mean()
     E = (x ** 2).sum() + 0.5 * (q[:, None] * q[None, :] * ToyBackend.chi(r)).sum()
+    if kspace is not None:
+        k, g = ToyBackend.k_vectors(kspace[0], kspace[1], cell)
+        th = R @ k.T
+        E = E + 0.5 * (g * ((q[:, None] * torch.cos(th)).sum(0) ** 2 + (q[:, None] * torch.sin(th)).sum(0) ** 2)).sum()
     F = -torch.autograd.grad(E, R)[0]
     return E.item(), F.numpy()
 
@@ -157,6 +202,7 @@ def _problem(seed=3, n=160, box=(46.0, 19.0, 19.5)):
 
 
 NVT_STEPS, NVT_DT, NVT_KT, NVT_TAU = 6, 0.5, 0.5, 20.0
+KSPACE = ((5, 3, 4), 3.0)
 
 
 def _nvt_problem():
@@ -194,6 +240,13 @@ def _worker(rank, world, port, out):
     chain = dom.backend.nhc_state()
     dom.nvt(NVT_STEPS, NVT_DT, NVT_KT, NVT_TAU, chain)
     res.update(Rt=dom.gather_global(dom.R[: dom.n0]).numpy(), Vt=dom.gather_global(dom.V).numpy(), chain=chain.numpy().copy())
+    # reciprocal-space part: the ranks' shares of the structure factors are summed over the ranks (the one exchange of that part)
+    dom = D.DomainSystem(D.DistComm(), ToyBackend(), Z, R, cell, skin=1.0, cutoff_lr=RC_LR, velocities=V, masses=np.ones(len(R)))
+    dom.set_kspace(KSPACE[0], KSPACE[1], "ewald")
+    Ek, _ = dom.compute(check_rebuild=False)
+    res.update(Ek=float(Ek), Fk=dom.global_forces().numpy())
+    dom.set_kspace(None)
+    res.update(Ek_off=float(dom.compute(check_rebuild=False)[0]))
     if rank == 0:
         torch.save(res, out)
     dist.barrier()
@@ -223,6 +276,9 @@ def test_decomposed_toy_model_matches_single_domain(tmp_path, world):
     np.testing.assert_allclose(res["F2"], F0, atol=2e-5)
     np.testing.assert_allclose(res["F3"], F0, atol=1e-4)
     assert res["rebuilds_host"] == 3
+    Ek, Fk = _serial_reference(R, cell, KSPACE)
+    assert abs(Ek - E0) > 1e-3 and abs(res["Ek"] - Ek) < 1e-6 * max(1.0, abs(Ek)) and abs(res["Ek_off"] - E0) < 1e-6 * max(1.0, abs(E0))
+    np.testing.assert_allclose(res["Fk"], Fk, atol=2e-5)
     # thermostatted trajectory against the serial integrator of the oracle with the serial forces
     Rt, Vt, mt = _nvt_problem()
     force = lambda X: _serial_reference(X, cell)
