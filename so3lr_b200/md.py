@@ -169,3 +169,32 @@ def npt_nose_hoover_invariant(state: MDState, kT: float, pressure: float, tau_t:
         xi, p = c[off + 2:off + 2 + L], c[off + 10:off + 10 + L]
         H += float(np.sum(p * p / (2 * Q))) + dof * kT * xi[0] + kT * float(xi[1:].sum())
     return H
+
+
+OBSERVABLES = ("partial_charges", "hirshfeld_ratios", "dipole_vec", "electrostatic_energy", "dispersion_energy", "zbl_repulsion")
+
+
+def run_cycles(system: System, apply_fn, state: MDState, cycles: int, steps_per_cycle: int, sink=None, observables=(),
+               on_cycle=None):
+    """The outer loop of the reference's MD driver (so3lr/cli/so3lr_md.py:1815-1921): `cycles` times `steps_per_cycle` steps;
+    after every cycle the frame (positions, momenta, box) goes to `sink` (so3lr_b200.trajectory.FrameSink) together with the
+    requested observables, which -- as in the reference's obs_fn (so3lr/cli/so3lr_md.py:1345-1390) -- come from one more
+    evaluation of the energy function with its auxiliary outputs.  Nothing here waits for the device unless the sink's ring
+    of buffers is full; `on_cycle(cycle, state)` is called after each cycle (logging, restart files)."""
+    for name in observables:
+        if name not in OBSERVABLES:
+            raise ValueError(f"Observable '{name}' is not recognized")
+    for cycle in range(cycles):
+        state = apply_fn(state, steps_per_cycle)
+        if sink is not None:
+            obs = {}
+            if observables:
+                out = system.compute(state.position)
+                aux = system.aux() if any(k.endswith("_energy") or k == "zbl_repulsion" for k in observables) else {}
+                for k in observables:
+                    obs[k] = out[k][0] if k == "dipole_vec" else (out[k] if k in out else aux[k])
+            sink.append(state.position, state.momentum, state.box if state.box is not None else system._cell, obs,
+                        step=(cycle + 1) * steps_per_cycle)
+        if on_cycle is not None:
+            on_cycle(cycle, state)
+    return state

@@ -325,3 +325,51 @@ def test_deferred_skin_test_gives_the_same_trajectory():
     assert n0 >= 2 and n1 >= 2                       # both modes rebuild their lists on the way
     assert np.abs(R1 - R0).max() < 2e-3 and np.abs(F1 - F0).max() < 5e-2      # chaotic growth of float32 differences over 120 steps
     assert np.median(np.abs(R1 - R0)) < 2e-5
+
+
+def test_md_loop_writes_frames_and_observables_without_waiting_for_the_device(tmp_path):
+    """The outer loop of the reference's MD driver (cycles of steps, a frame and the observables after each cycle,
+    so3lr/cli/so3lr_md.py:1815-1921) with the asynchronous frame writer: what lands in the files is the state at the end of each
+    cycle, although the integrator goes on overwriting the positions in place while the copies are in flight."""
+    from so3lr_b200 import md
+    from so3lr_b200 import workloads as W
+    from so3lr_b200.engine import System
+    from so3lr_b200.trajectory import FrameSink, read_extxyz
+    Z, R, cell = W.water_box(216, 18.7, 5, jitter=0.03)
+    V, m = W.maxwell_boltzmann(Z, 300.0, 6)
+    s = System(Z, cell, cutoff_lr=8.0, damping=2.0, skin=0.5)
+    init_fn, apply_fn = md.nve(s, 0.5)
+    snaps = []
+    obs = ("partial_charges", "hirshfeld_ratios", "dipole_vec", "electrostatic_energy")
+    for fmt in ("extxyz", "npy"):
+        state = init_fn(R, m, velocity=V)
+        snaps.clear()
+        path = tmp_path / ("traj." + fmt)
+        with FrameSink(path, Z, fmt, observables=obs, slots=2) as sink:
+            md.run_cycles(s, apply_fn, state, cycles=5, steps_per_cycle=4, sink=sink, observables=obs,
+                          on_cycle=lambda c, st: snaps.append((st.position.clone(), st.momentum.clone())))
+        assert sink.frames_written == 5
+        want_R = np.stack([a.cpu().numpy() for a, _ in snaps])
+        want_P = np.stack([b.cpu().numpy() for _, b in snaps])
+        assert np.abs(want_R[1] - want_R[0]).max() > 1e-3            # the atoms did move between the frames
+        if fmt == "extxyz":
+            fr = read_extxyz(path)
+            got_R, got_P = np.stack([f["pos"] for f in fr]), np.stack([f["momenta"] for f in fr])
+            q, h = fr[-1]["charges"], fr[-1]["hirsh_ratios"]
+            dip = np.array([float(v) for v in fr[-1]["info"]["dipole_vec"].split()])
+            np.testing.assert_allclose(fr[0]["cell"], np.asarray(cell))
+            assert [int(f["info"]["step"]) for f in fr] == [4, 8, 12, 16, 20]
+            tol = 2e-7 * np.abs(want_R).max() + 1e-8                 # eight decimals in the text file
+        else:
+            got_R, got_P = np.load(path / "positions.npy"), np.load(path / "momenta.npy")
+            q, h, dip = np.load(path / "partial_charges.npy")[-1], np.load(path / "hirshfeld_ratios.npy")[-1], np.load(path / "dipole_vec.npy")[-1]
+            assert np.load(path / "electrostatic_energy.npy").shape == (5, len(Z)) and np.load(path / "box.npy").shape == (5, 3, 3)
+            tol = 0.0
+        np.testing.assert_allclose(got_R, want_R, atol=tol + 1e-7)
+        np.testing.assert_allclose(got_P, want_P, atol=1e-6)
+        ref = s.compute(snaps[-1][0])
+        np.testing.assert_allclose(q, ref["partial_charges"].cpu().numpy(), atol=1e-6)
+        np.testing.assert_allclose(h, ref["hirshfeld_ratios"].cpu().numpy(), atol=1e-6)
+        # sum_i q_i R_i over 648 atoms up to 18.7 A from the origin: a uniform charge offset of 1e-7 (float32 rounding of the charge
+        # conservation, which differs between two evaluations with different atom orderings) moves it by 6e-4
+        np.testing.assert_allclose(dip, ref["dipole_vec"][0].cpu().numpy(), atol=2e-3)
