@@ -41,6 +41,7 @@ constexpr int kAHalf = 16 * kLboA;            // one FP16 matrix of 128 rows x 1
 constexpr int kWStride = 132;                 // floats per row of the filter tile
 constexpr int kFwRec = 36;                    // floats per forward record: j | i | cutoff / nbar | - | Y[24] | padding (bank spread)
 constexpr int kFwThreads = 512;
+constexpr int kFwIssuer = 128;       // forward kernel: the thread that issues the MMAs (its own preparation is the shortest)
 constexpr int kBwRec = 52;                    // floats per reverse record (48 used; 52 spreads consecutive rows over the banks)
 constexpr int kBwThreads = 512;
 constexpr float kInvNbar = 1.0f / kAvgNumNeighbors;
@@ -255,7 +256,10 @@ __device__ __forceinline__ uint64_t desc_base(uint32_t lbo, uint32_t sbo) {
 //   CT hi | CT lo : [256 features][64 terms], core (n/8, k/8) at (k/8) * 4096 + (n/8) * 128           (2 x 32 KB)
 //   K2T_f hi | lo : [128 features][32 hidden], core (n/8, k/8) at (k/8) * 2048 + (n/8) * 128          (4 x 8 KB)
 // w = Phi * C + hs_f * K2_f: main accumulators in TMEM columns [0, 256), cross accumulators in [256, 512)
-__device__ __noinline__ void issue_forward_mma(uint32_t tmem, uint32_t a_hi, uint32_t img) {
+// The Chebyshev steps (part 0) read chunks 0..7 of A only, the steps of the spherical hidden layers (part 1) chunks 8..15: part 0 is
+// issued as soon as the two threads per entry that write the Chebyshev terms are through, while the other two still gather `ev`
+// rows and evaluate the hidden layers.
+__device__ __noinline__ void issue_forward_mma(uint32_t tmem, uint32_t a_hi, uint32_t img, int part) {
   const uint64_t da = desc_base(kLboA, 128) + (a_hi >> 4), dal = da + (kAHalf >> 4);
   const uint64_t dc = desc_base(4096, 128) + (img >> 4), dcl = dc + (32768 >> 4);
   const uint64_t dk = desc_base(2048, 128) + ((img + 65536) >> 4), dkl = dk + (16384 >> 4);
@@ -263,14 +267,17 @@ __device__ __noinline__ void issue_forward_mma(uint32_t tmem, uint32_t a_hi, uin
   // K steps 1 and 3 hold the Chebyshev terms of order 32..63 (even terms, then odd terms, 32 columns each).  Their coefficients
   // are below 2^-12 of the filter scale (the expansion converges geometrically), so their hi * lo cross terms are below 2^-23 of
   // it, like the lo * lo terms that are dropped everywhere: those steps issue the hi * hi product only.
+  if (part == 0) {
 #pragma unroll
-  for (int ks = 0; ks < 4; ++ks) {
-    const uint64_t ah = da + ks * (2 * kLboA >> 4), al = dal + ks * (2 * kLboA >> 4);
-    const uint64_t bh = dc + ks * (2 * 4096 >> 4), bl = dcl + ks * (2 * 4096 >> 4);
-    umma(tmem, ah, bh, id256, ks > 0);
-    if (ks == 1 || ks == 3) continue;
-    umma(tmem + 256, ah, bl, id256, ks > 0);
-    umma(tmem + 256, al, bh, id256, 1);
+    for (int ks = 0; ks < 4; ++ks) {
+      const uint64_t ah = da + ks * (2 * kLboA >> 4), al = dal + ks * (2 * kLboA >> 4);
+      const uint64_t bh = dc + ks * (2 * 4096 >> 4), bl = dcl + ks * (2 * 4096 >> 4);
+      umma(tmem, ah, bh, id256, ks > 0);
+      if (ks == 1 || ks == 3) continue;
+      umma(tmem + 256, ah, bl, id256, ks > 0);
+      umma(tmem + 256, al, bh, id256, 1);
+    }
+    return;
   }
 #pragma unroll
   for (int f = 0; f < 2; ++f)
@@ -291,13 +298,15 @@ __device__ __noinline__ void issue_forward_mma(uint32_t tmem, uint32_t a_hi, uin
 // Forward product (B read MN-major: N = features, K = rows): w_f = [Phi | hs_f] * [C_f ; K2_f], main accumulators in TMEM
 // columns [128 f, 128 f + 128), cross 256 columns above.
 constexpr int kRevImgFilter = 16 * 1536;
-__device__ __noinline__ void issue_filter_mma(uint32_t tmem, uint32_t a_hi, uint32_t img, int f) {
+// part 0: the four Chebyshev steps, part 1: the two steps of the filter's hidden layer (see issue_forward_mma)
+__device__ __noinline__ void issue_filter_mma(uint32_t tmem, uint32_t a_hi, uint32_t img, int f, int part) {
   const uint64_t da = desc_base(kLboA, 128) + (a_hi >> 4), dal = da + (kAHalf >> 4);
   const uint64_t db = desc_base(128, 1536) + ((img + f * kRevImgFilter) >> 4), dbl = db + (2 * kRevImgFilter >> 4);
   const uint32_t id128 = make_idesc(128, 1);
   const uint32_t d_main = tmem + 128 * f, d_cross = d_main + 256;
 #pragma unroll
   for (int ks = 0; ks < 6; ++ks) {      // K = 16 rows per step: Chebyshev chunks 0..7 of A, then the two chunks pairs of hs_f
+    if ((ks >= 4) != (part == 1)) continue;
     const int chunk = ks < 4 ? 2 * ks : 8 + 4 * f + 2 * (ks - 4);
     const uint64_t ah = da + chunk * (kLboA >> 4), al = dal + chunk * (kLboA >> 4);
     const uint64_t bh = db + ks * (2 * 128 >> 4), bl = dbl + ks * (2 * 128 >> 4);
@@ -469,6 +478,15 @@ __global__ void __launch_bounds__(kFwThreads, 1) attn_fwd_tc_kernel(const unsign
       if (role < 2) {
         const float4 d = st_d[row];
         const float r = d.w;
+        // the Chebyshev chunks first: once these 256 threads are through, their share of the MMA chain starts beneath the rest
+        // of the preparation
+        store_chebyshev_half(smem + kOffA, row, r, valid, role);
+        fence_async_smem();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (tid == kFwIssuer) {
+          tc_fence_after();
+          issue_forward_mma(tmem, a_hi, img, 0);
+        }
         if (role == 0) {
           const float ir = 1.f / r;
           float cut, dcut;
@@ -480,7 +498,6 @@ __global__ void __launch_bounds__(kFwThreads, 1) attn_fwd_tc_kernel(const unsign
 #pragma unroll
           for (int c = 0; c < 6; ++c) st4(rp + 4 + 4 * c, make_float4(Y[4 * c], Y[4 * c + 1], Y[4 * c + 2], Y[4 * c + 3]));
         }
-        store_chebyshev_half(smem + kOffA, row, r, valid, role);
       } else {
         float s[4];
         invariants(st_ev + row * (2 * kEvStride), st_ev + row * (2 * kEvStride) + kEvStride, s);
@@ -505,12 +522,12 @@ __global__ void __launch_bounds__(kFwThreads, 1) attn_fwd_tc_kernel(const unsign
     qf = ld4(qkv + (size_t)cur_i * kProj + col);
     stage_tile(tile + 1);
     bool done = true;
-    if (tid == 0) {
+    if (tid == kFwIssuer) {
       tc_fence_after();
 #ifdef SO3LR_TC_TIMING
       const long long q0 = clock64();
 #endif
-      issue_forward_mma(tmem, a_hi, img);
+      issue_forward_mma(tmem, a_hi, img, 1);
       umma_commit(mbar0);
 #ifdef SO3LR_TC_TIMING
       const long long q1 = clock64();
@@ -877,6 +894,16 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
         float4 d = make_float4(1.f, 0.f, 0.f, 1.f);
         if (valid) d = ve_d[e];
         const float r = d.w;
+        // the Chebyshev chunks first: once these 256 threads are through, the Chebyshev steps of both filters' MMA chains start
+        // beneath the rest of the preparation (the gathers of the other two threads of an entry above all)
+        store_chebyshev_half(a_ptr, row, r, valid, role);
+        fence_async_smem();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (tid == 0) {
+          tc_fence_after();
+          issue_filter_mma(tmem, a_hi, img, 0, 0);
+          issue_filter_mma(tmem, a_hi, img, 1, 0);
+        }
         const float ir = 1.f / r;
         const float ux = d.x * ir, uy = d.y * ir, uz = d.z * ir;
         if (role == 0) {
@@ -908,7 +935,6 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
           st4(rp + 12, make_float4(dA[0], dA[1], dA[2], dA[3]));
           st4(rp + 16, make_float4(dB[0], dB[1], dB[2], dB[3]));
         }
-        store_chebyshev_half(a_ptr, row, r, valid, role);
       } else {
         float s[4];
         invariants(ev_in + (size_t)i * kMTot, ev_in + (size_t)j * kMTot, s);
@@ -923,8 +949,8 @@ __global__ void __launch_bounds__(kBwThreads, 1) attn_bwd_tc_kernel(const unsign
     BW_MARK(1);
     if (tid == 0) {
       tc_fence_after();
-      issue_filter_mma(tmem, a_hi, img, 0);
-      issue_filter_mma(tmem, a_hi, img, 1);
+      issue_filter_mma(tmem, a_hi, img, 0, 1);
+      issue_filter_mma(tmem, a_hi, img, 1, 1);
       umma_commit(mbar);
     }
     __syncwarp();

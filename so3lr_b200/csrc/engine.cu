@@ -1026,7 +1026,11 @@ SO3LR_B200_API int so3lr_b200_system_set_kspace(so3lr_b200_system* S, int mode, 
   // one periodic structure whose pair sum is cut off: the split needs a short-ranged pair part
   if (!S->cell.periodic || S->n_graphs != 1 || !S->lr.has_cutoff || !(smearing > 0.f)) return kInvalidArgument;
   int rc = kspace_setup(&S->ks, S->n_cap, mode, smearing, n1, n2, n3);
-  if (rc) return rc;
+  if (rc) {      // the context falls back to the plain truncated pair sum, consistently
+    S->lr.k_alpha = 0.f;
+    set_coulomb_shift(S->lr);
+    return rc;
+  }
   S->lr.k_alpha = (float)(1.0 / (std::sqrt(2.0) * (double)smearing));
   set_coulomb_shift(S->lr);
   return kOk;
