@@ -505,21 +505,23 @@ __global__ void __launch_bounds__(kFwThreads, 1) attn_fwd_tc_kernel(const unsign
       }
     }
     TC_MARK(0);
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    TC_MARK(1);
-    // sender rows of filter 0 for this warp's edges and the first receiver's query row: in flight while the tensor cores run
+    // sender rows of filter 0 for this warp's edges and the first receiver's query row, requested before the barrier (the indices
+    // are in the staging buffer since the previous tile): the warps with the shorter preparation start their gathers while the
+    // others still work, and all of them are in flight while the tensor cores run
     float4 kf[8], vj[8], qf;
     int cur_i;
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
-      const float* kj = qkv + (size_t)__float_as_int(rec[(k0 + u) * kFwRec]) * kProj;
+      const float* kj = qkv + (size_t)st_ij[2 * (k0 + u) + 1] * kProj;
       kf[u] = ld4(kj + kF + col);
       vj[u] = ld4(kj + 2 * kF + col);
     }
-    cur_i = __float_as_int(rec[k0 * kFwRec + 1]);
+    cur_i = st_ij[2 * k0];
     qf = ld4(qkv + (size_t)cur_i * kProj + col);
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    TC_MARK(1);
     stage_tile(tile + 1);
     bool done = true;
     if (tid == kFwIssuer) {
