@@ -687,7 +687,7 @@ __device__ __forceinline__ void value_logit_cotangents(float* rec, int row0, int
   const int col = 4 * lane, grp = lane >> 3, cg = lane & 7;
   int cur_i = -1;
   float4 v_i = f4_zero(), gx_i = f4_zero();
-#pragma unroll 1
+#pragma unroll
   for (int k0 = 0; k0 < 8; k0 += 4) {
     float4 vj[4], gxj[4];
     int ii[4];
