@@ -54,7 +54,9 @@ struct KSpaceDev {
   float smearing = 0.f;    // Gaussian width s of the split erf(r / (sqrt(2) s)) / r
   int shape[3] = {0, 0, 0};
   int n_tiles = 0;
-  int4* tiles = nullptr;   // (h1, first h2, first h3, -) of each 16 x 16 tile of kept indices
+  int n_groups = 0;
+  int4* tiles = nullptr;   // (h1, first h2, first h3, mask of the h2 rows that hold a kept vector) of each 16 x 16 tile of kept indices
+  int2* groups = nullptr;  // (first tile, count <= 4): tiles that share (h1, first h2) and follow one another along h3
   float* wgt = nullptr;    // [n_tiles][256] 2 / 1 / 0: member of a (k, -k) pair, unpaired index, not part of the sum
   float2* Sk = nullptr;    // [n_tiles][256] structure factors
   float* acc = nullptr;    // [n_atoms][4] potential and the three index-weighted force sums

@@ -8,7 +8,8 @@
 // S(-k) = conj S(k), so one vector of every pair (k, -k) is kept with weight 2 (an index -n/2 of an even grid has no partner and
 // keeps weight 1).  The kept indices are cut into tiles of 16 x 16 (h2, h3) values at one h1.  exp(i k r) factorises over the three
 // indices, so a tile needs 32 sines and cosines per atom instead of 256:
-//   ewald_structure_kernel  thread = k vector of a tile, loops over a slice of the atoms staged in shared memory (4 FMAs per pair)
+//   ewald_structure_kernel  a CTA takes up to four tiles adjacent along h3 (80 table entries per atom for 1024 vectors), a thread eight
+//                           vectors, and loops over a slice of the atoms staged in shared memory (4 FMAs per pair)
 //   ewald_atom_kernel       thread = atom, loops over a slice of the tiles; potential phi_i and the three index-weighted sums that
 //                           give the force (8 FMAs per pair)
 //   ewald_finish_kernel     per atom: energy, dE/dq (it continues into the charge head's reverse pass), force
@@ -37,7 +38,6 @@ namespace {
 
 constexpr int kTile = 16;
 constexpr int kTileK = kTile * kTile;
-constexpr int kStage = 64;                 // atoms per shared-memory stage of the structure-factor kernel
 constexpr float kTwoPi = 6.283185307179586f;
 
 // f * h modulo 1 in [-1/2, 1/2]: the product is formed exactly inside the FMA, so the result carries the rounding of f only
@@ -68,19 +68,27 @@ __device__ __forceinline__ float k_weight(float w, float inv_vol, float smearing
   return w * kKe * inv_vol * 12.566370614359172f * expf(-0.5f * smearing * smearing * k2) / k2;
 }
 
-__global__ void __launch_bounds__(kTileK) ewald_structure_kernel(Cell cell, int n, int atoms_per_split, const float* __restrict__ R,
-                                                                  const float* __restrict__ q, const int4* __restrict__ tiles,
-                                                                  float2* __restrict__ Sk) {
-  __shared__ float2 T[kStage][2 * kTile];    // per atom: q exp(2 pi i (f1 h1 + f2 h2)) for the tile's 16 h2, exp(2 pi i f3 h3) for its 16 h3
-  __shared__ float4 A[kStage];               // f1 f2 f3 q
-  const int4 t = tiles[blockIdx.x];
-  const int tid = threadIdx.x, t2 = tid >> 4, t3 = tid & 15;
+// A group is up to four tiles that share (h1, first h2) and follow one another along h3: 16 x 64 index pairs whose phase factors need
+// 16 + 64 table entries per atom.  128 threads; thread (warp w, lane l) accumulates the eight vectors h2 = w, w + 4, w + 8, w + 12 times
+// h3 = l, l + 32: per atom four broadcast loads and two coalesced ones from shared memory feed 32 FMAs.
+constexpr int kGroupStage = 32;            // atoms per shared-memory stage
+__global__ void __launch_bounds__(128) ewald_structure_kernel(Cell cell, int n, int atoms_per_split, const float* __restrict__ R,
+                                                              const float* __restrict__ q, const int4* __restrict__ tiles,
+                                                              const int2* __restrict__ groups, float2* __restrict__ Sk) {
+  __shared__ float2 T2[kGroupStage][kTile];        // q exp(2 pi i (f1 h1 + f2 h2)) for the group's 16 h2
+  __shared__ float2 T3[kGroupStage][4 * kTile];    // exp(2 pi i f3 h3) for its 64 h3
+  __shared__ float4 A[kGroupStage];                // f1 f2 f3 q
+  const int2 g = groups[blockIdx.x];               // first tile, number of tiles
+  const int4 t = tiles[g.x];
+  const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
   const int a0 = blockIdx.y * atoms_per_split;
   const int a1 = a0 + atoms_per_split < n ? a0 + atoms_per_split : n;
-  float sr = 0.f, si = 0.f;
-  for (int base = a0; base < a1; base += kStage) {
+  float sr[8], si[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) { sr[k] = 0.f; si[k] = 0.f; }
+  for (int base = a0; base < a1; base += kGroupStage) {
     __syncthreads();
-    if (tid < kStage) {
+    if (tid < kGroupStage) {
       const int a = base + tid;
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if (a < a1) {
@@ -90,29 +98,43 @@ __global__ void __launch_bounds__(kTileK) ewald_structure_kernel(Cell cell, int 
       A[tid] = v;
     }
     __syncthreads();
-    for (int e = tid; e < kStage * 2 * kTile; e += kTileK) {
-      const int a = e >> 5, j = e & 31;
+    for (int e = tid; e < kGroupStage * 5 * kTile; e += 128) {
+      const int a = e / (5 * kTile), j = e - a * (5 * kTile);
       const float4 v = A[a];
       float c, s;
       if (j < kTile) {
         unit_phase(phase_frac(v.x, t.x) + phase_frac(v.y, t.y + j), c, s);
-        T[a][j] = make_float2(v.w * c, v.w * s);
+        T2[a][j] = make_float2(v.w * c, v.w * s);
       } else {
         unit_phase(phase_frac(v.z, t.z + j - kTile), c, s);
-        T[a][j] = make_float2(c, s);
+        T3[a][j - kTile] = make_float2(c, s);
       }
     }
     __syncthreads();
-#pragma unroll 8
-    for (int a = 0; a < kStage; ++a) {
-      const float2 u = T[a][t2], w = T[a][kTile + t3];
-      sr = fmaf(u.x, w.x, sr); sr = fmaf(-u.y, w.y, sr);
-      si = fmaf(u.x, w.y, si); si = fmaf(u.y, w.x, si);
+#pragma unroll 4
+    for (int a = 0; a < kGroupStage; ++a) {
+      const float2 w0 = T3[a][lane], w1 = T3[a][lane + 32];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 u = T2[a][w + 4 * k];
+        sr[2 * k] = fmaf(u.x, w0.x, sr[2 * k]); sr[2 * k] = fmaf(-u.y, w0.y, sr[2 * k]);
+        si[2 * k] = fmaf(u.x, w0.y, si[2 * k]); si[2 * k] = fmaf(u.y, w0.x, si[2 * k]);
+        sr[2 * k + 1] = fmaf(u.x, w1.x, sr[2 * k + 1]); sr[2 * k + 1] = fmaf(-u.y, w1.y, sr[2 * k + 1]);
+        si[2 * k + 1] = fmaf(u.x, w1.y, si[2 * k + 1]); si[2 * k + 1] = fmaf(u.y, w1.x, si[2 * k + 1]);
+      }
     }
   }
-  float2* out = Sk + (size_t)blockIdx.x * kTileK + tid;
-  atomicAdd(&out->x, sr);
-  atomicAdd(&out->y, si);
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int h3 = lane + 32 * hh, u = h3 >> 4;          // tile of the group, slot inside it
+      if (u < g.y) {
+        float2* out = Sk + (size_t)(g.x + u) * kTileK + (w + 4 * k) * kTile + (h3 & 15);
+        atomicAdd(&out->x, sr[2 * k + hh]);
+        atomicAdd(&out->y, si[2 * k + hh]);
+      }
+    }
 }
 
 // acc rows: phi_i, and sum_k G h_d Im[S(k) exp(-i k r_i)] for d = 1, 2, 3
@@ -151,6 +173,7 @@ __global__ void __launch_bounds__(128) ewald_atom_kernel(Cell cell, float inv_vo
     const float h1f = (float)t.x;
 #pragma unroll 1
     for (int i2 = 0; i2 < kTile; ++i2) {
+      if (!((t.w >> i2) & 1)) continue;                  // no kept vector in this row of the tile
       float ur = 0.f, ui = 0.f, vr = 0.f, vi = 0.f;      // sum over h3 of A conj(T3), and of h3 A conj(T3)
 #pragma unroll
       for (int j = 0; j < kTile; ++j) {
@@ -409,7 +432,7 @@ void kspace_free(KSpaceDev* K) {
   if (K->plans) {
     if (CufftApi* f = cufft_api()) { f->destroy(K->plan_r2c); f->destroy(K->plan_c2r); }
   }
-  cudaFree(K->tiles); cudaFree(K->wgt); cudaFree(K->Sk); cudaFree(K->acc); cudaFree(K->mesh); cudaFree(K->fq);
+  cudaFree(K->tiles); cudaFree(K->groups); cudaFree(K->wgt); cudaFree(K->Sk); cudaFree(K->acc); cudaFree(K->mesh); cudaFree(K->fq);
   *K = KSpaceDev{};
 }
 
@@ -458,17 +481,31 @@ int kspace_setup(KSpaceDev* K, int n_atoms, int mode, float smearing, int n1, in
         bool any = false;
         for (int s = 0; s < kTileK; ++s) { w[s] = weight(h1, b0 + (s >> 4), c0 + (s & 15)); any |= w[s] > 0.f; }
         if (!any) continue;
-        tiles.push_back(make_int4(h1, b0, c0, 0));
+        int mask = 0;                       // rows (h2) of the tile that hold a kept vector
+        for (int s = 0; s < kTileK; ++s) if (w[s] > 0.f) mask |= 1 << (s >> 4);
+        tiles.push_back(make_int4(h1, b0, c0, mask));
         wgt.insert(wgt.end(), w, w + kTileK);
       }
+  // groups of up to four tiles that share (h1, first h2) and are adjacent along h3, runs longer than four split evenly
+  std::vector<int2> groups;
+  for (size_t i = 0; i < tiles.size();) {
+    size_t j = i + 1;
+    while (j < tiles.size() && tiles[j].x == tiles[i].x && tiles[j].y == tiles[i].y && tiles[j].z == tiles[j - 1].z + kTile) ++j;
+    const int run = (int)(j - i), parts = (run + 3) / 4, size = (run + parts - 1) / parts;
+    for (int k = 0; k < run; k += size) groups.push_back(make_int2((int)i + k, run - k < size ? run - k : size));
+    i = j;
+  }
   if (tiles.empty() || tiles.size() > (size_t)(1 << 22)) return tiles.empty() ? kInvalidArgument : kTooLarge;
   K->n_tiles = (int)tiles.size();
+  K->n_groups = (int)groups.size();
   K->smearing = smearing;
   K->shape[0] = n1; K->shape[1] = n2; K->shape[2] = n3;
   SO3LR_CUDA_CHECK(cudaMalloc((void**)&K->tiles, tiles.size() * sizeof(int4)));
   SO3LR_CUDA_CHECK(cudaMalloc((void**)&K->wgt, wgt.size() * sizeof(float)));
   SO3LR_CUDA_CHECK(cudaMalloc((void**)&K->Sk, wgt.size() * sizeof(float2)));
   SO3LR_CUDA_CHECK(cudaMalloc((void**)&K->acc, (size_t)n_atoms * 4 * sizeof(float)));
+  SO3LR_CUDA_CHECK(cudaMalloc((void**)&K->groups, groups.size() * sizeof(int2)));
+  SO3LR_CUDA_CHECK(cudaMemcpy(K->groups, groups.data(), groups.size() * sizeof(int2), cudaMemcpyHostToDevice));
   SO3LR_CUDA_CHECK(cudaMemcpy(K->tiles, tiles.data(), tiles.size() * sizeof(int4), cudaMemcpyHostToDevice));
   SO3LR_CUDA_CHECK(cudaMemcpy(K->wgt, wgt.data(), wgt.size() * sizeof(float), cudaMemcpyHostToDevice));
   K->mode = 1;
@@ -497,15 +534,15 @@ int kspace_accumulate(cudaStream_t st, const KSpaceDev& K, const Cell& cell, int
     if (n_floats) *n_floats = (long long)n1 * n2 * n3;
   } else {
     SO3LR_CUDA_CHECK(cudaMemsetAsync(K.Sk, 0, (size_t)K.n_tiles * kTileK * sizeof(float2), st));
-    // tiles x atom slices
-    int splits = (4 * sm_count() + K.n_tiles - 1) / K.n_tiles;
-    const int max_splits = (n + kStage - 1) / kStage;
+    // groups of tiles x atom slices
+    int splits = (8 * sm_count() + K.n_groups - 1) / K.n_groups;
+    const int max_splits = (n + kGroupStage - 1) / kGroupStage;
     if (splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
     int per = (n + splits - 1) / splits;
-    per = (per + kStage - 1) / kStage * kStage;
+    per = (per + kGroupStage - 1) / kGroupStage * kGroupStage;
     splits = (n + per - 1) / per;
-    { ewald_structure_kernel<<<dim3(K.n_tiles, splits), kTileK, 0, st>>>(cell, n, per, R, q, K.tiles, K.Sk); count_launch(); }
+    { ewald_structure_kernel<<<dim3(K.n_groups, splits), 128, 0, st>>>(cell, n, per, R, q, K.tiles, K.groups, K.Sk); count_launch(); }
     if (buffer) *buffer = reinterpret_cast<float*>(K.Sk);
     if (n_floats) *n_floats = 2LL * K.n_tiles * kTileK;
   }
