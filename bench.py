@@ -172,7 +172,7 @@ def algorithmic_bytes(group, N, E, P):
 # box (attn_bwd_tc_kernel, attn_fwd_tc_kernel; atom_post_*_tc_kernel: the launch with the fused projections).  A full-size
 # capture is not taken (ncu replays each launch about 40 times); lists and per-atom arrays grow with the atom count at fixed
 # density, so the figure is scaled by N / 98304 and the line says so in `traffic_source`.
-NCU_TRAFFIC_98K = {"attn_bwd": 2248.9e6, "attn_fwd": 837.3e6, "atom_post_fwd": 430.1e6, "atom_post_bwd": 557.2e6}
+NCU_TRAFFIC_98K = {"attn_bwd": 2240.7e6, "attn_fwd": 838.8e6, "atom_post_fwd": 430.1e6, "atom_post_bwd": 557.2e6}
 
 
 def ncu_traffic(group, n_atoms):
