@@ -220,3 +220,22 @@ def test_nve_with_the_reciprocal_sum_conserves_energy_and_strained_cells_follow_
         Es.append(float(s.compute(torch.tensor((Rf @ A.T).astype(np.float32), device="cuda"))["energy"].sum()))
     dE = (Es[0] - Es[1]) / 2
     assert abs(dE - float((Wv * eps).sum())) < 2e-3 + 2e-3 * abs(dE), (dE, float((Wv * eps).sum()))
+
+
+@pytest.mark.parametrize("method", ["ewald", "pme"])
+def test_charged_cell_carries_the_background_term(oracle_params, reference_goldens, method):
+    """A net charge: the charge embedding changes the features, the charges sum to the total charge, and the reciprocal part
+    gains the neutralising-background term -ke pi s^2 Q^2 / V (energy and strain derivative)."""
+    from so3lr_b200.engine import System
+    Z, R, cell = _water192(reference_goldens)
+    shape, smearing = ((32, 32, 32) if method == "pme" else K.ewald_grid_shape(cell, 0.6)), 1.0
+    ref = O.energy_forces(oracle_params, R.astype(np.float64), Z, cell, cutoff_lr=6.0, damping=2.0, total_charge=[1.0],
+                          k_grid=shape, k_smearing=smearing, k_method=method)
+    s = System(Z, cell, cutoff_lr=6.0, damping=2.0, total_charge=[1.0])
+    s.enable_virial(True)
+    s.set_kspace(shape, smearing, method)
+    out = s.compute(torch.tensor(R, device="cuda"))
+    _check(out, ref, R)
+    assert abs(float(out["partial_charges"].sum()) - 1.0) < 1e-4
+    # the background term is far above the tolerance at this size (ke pi s^2 Q^2 / V = 0.024 eV), so a missing term would show
+    assert K.KE * np.pi * smearing ** 2 / abs(np.linalg.det(cell)) > 100 * 1e-5 * abs(ref["energy"]) / 10
