@@ -237,5 +237,5 @@ def test_charged_cell_carries_the_background_term(oracle_params, reference_golde
     out = s.compute(torch.tensor(R, device="cuda"))
     _check(out, ref, R)
     assert abs(float(out["partial_charges"].sum()) - 1.0) < 1e-4
-    # the background term is far above the tolerance at this size (ke pi s^2 Q^2 / V = 0.024 eV), so a missing term would show
-    assert K.KE * np.pi * smearing ** 2 / abs(np.linalg.det(cell)) > 100 * 1e-5 * abs(ref["energy"]) / 10
+    # the background term (ke pi s^2 Q^2 / V = 0.024 eV) is several times the energy tolerance at this size: a missing term would show
+    assert K.KE * np.pi * smearing ** 2 / abs(np.linalg.det(cell)) > 5 * 1e-5 * abs(ref["energy"])
