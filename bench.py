@@ -229,6 +229,10 @@ def run_b200(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    else:
+        # an ordinary (capturable) stream instead of the legacy default one: the library replays the force evaluation of small
+        # structures from a CUDA graph between list rebuilds, which the legacy stream does not allow
+        torch.cuda.set_stream(torch.cuda.Stream(device=dev))
     if args.workload in MOLECULE_BATCHES:
         return run_molecules(args, rank, world, local_rank)
     seed = WORKLOADS[args.workload][2]

@@ -101,6 +101,13 @@ SO3LR_B200_API int so3lr_b200_system_compute(so3lr_b200_system* sys, void* strea
 SO3LR_B200_API int so3lr_b200_system_compute_host(so3lr_b200_system* sys, const float* positions_host, float* forces_host,
                                    double* energy_host, float* charges_host, float* hirshfeld_host, float* dipole_host);
 
+/* Small structures are bound by the launch rate (about 40 launches per evaluation), so between two list rebuilds
+ * so3lr_b200_system_compute replays its launches from a CUDA graph: the graph is captured at the second consecutive call with the
+ * same positions / forces buffers on a stream that can be captured (not the legacy default stream) and dropped when the lists are
+ * rebuilt, the cell changes or the buffers differ.  At most 65,536 atoms, skin > 0, no reciprocal-space part; SO3LR_B200_CUDA_GRAPH=0
+ * in the environment keeps plain launches.  This counter tells how many evaluations were replays (tests, tuning). */
+SO3LR_B200_API int so3lr_b200_system_graph_replays(so3lr_b200_system* sys, int64_t* n_replays);
+
 /* Per-term energies of the last evaluation, per atom, device pointers valid until the next call (aux dictionary of
  * potential(graph, has_aux=True), so3lr/jaxmd_utils.py:138-139). */
 SO3LR_B200_API int so3lr_b200_system_aux(so3lr_b200_system* sys, const float** zbl_dev, const float** coulomb_dev,

@@ -44,6 +44,7 @@ def _load():
         "so3lr_b200_system_compute_host": (i32, [p, p, p, p, p, p, p]),
         "so3lr_b200_system_aux": (i32, [p, C.POINTER(p), C.POINTER(p), C.POINTER(p)]),
         "so3lr_b200_system_stats": (i32, [p, C.POINTER(i64), C.POINTER(i64), C.POINTER(i64), C.POINTER(i64)]),
+        "so3lr_b200_system_graph_replays": (i32, [p, C.POINTER(i64)]),
         "so3lr_b200_system_valid_edges": (i32, [p, C.POINTER(i64)]),
         "so3lr_b200_pack_rows": (i32, [p, i32, C.POINTER(p), C.POINTER(i32), p, i64, p]),
         "so3lr_b200_unpack_rows": (i32, [p, i32, C.POINTER(p), C.POINTER(i32), p, i64, p]),

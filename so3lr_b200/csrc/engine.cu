@@ -292,6 +292,15 @@ struct so3lr_b200_system {
   int flag_slot = 0;
   double* h_box = nullptr; // pinned: the box coordinate read back by the NPT step
   bool virial_fresh = false;   // virial_sum belongs to the latest evaluation
+  // CUDA graph of one force evaluation between two list rebuilds (small structures are bound by the launch rate): captured at the
+  // second consecutive call with the same position / force buffers, replayed until the lists are rebuilt or the buffers change
+  struct StepGraph {
+    cudaGraphExec_t exec = nullptr;
+    const float* R = nullptr; float* F = nullptr; int64_t stamp = -1; bool virial = false;
+    int64_t launches = 0, replays = 0;
+    const float* last_R = nullptr; float* last_F = nullptr; int64_t last_stamp = -1;
+    bool broken = false;        // a capture failed: the context stays on plain launches
+  } step_graph;
   bool have_lists = false;
   // graph-level row pointers
   int *d_rowptr_g = nullptr, *d_rowptr_lr_g = nullptr;
@@ -609,6 +618,25 @@ void set_coulomb_shift(LrParams& P) {
     dpot -= (2.0 / std::sqrt(M_PI) * a * std::exp(-(rc * a) * (rc * a)) - potk) / rc;
   }
   P.v_rc = (float)pot; P.dv_rc = (float)dpot;
+}
+
+// SO3LR_B200_CUDA_GRAPH=0 keeps every evaluation on plain launches
+bool step_graphs_enabled() {
+  static const bool v = [] {
+    const char* e = std::getenv("SO3LR_B200_CUDA_GRAPH");
+    return !(e && std::strcmp(e, "0") == 0);
+  }();
+  return v;
+}
+constexpr int kStepGraphMaxAtoms = 65536;   // above this a step is bound by its kernels, not by the launch rate
+// the captured launches hold the cell, the pair-term constants and the buffers by value: anything that changes them drops the graph
+void drop_step_graph(so3lr_b200_system* S) {
+  if (S->step_graph.exec) cudaGraphExecDestroy(S->step_graph.exec);
+  const bool broken = S->step_graph.broken;
+  const int64_t replays = S->step_graph.replays;
+  S->step_graph = so3lr_b200_system::StepGraph{};
+  S->step_graph.broken = broken;
+  S->step_graph.replays = replays;
 }
 
 struct Shells { int n0, n1, n2, n3; };
@@ -980,6 +1008,7 @@ SO3LR_B200_API int so3lr_b200_system_destroy(so3lr_b200_system* S) {
   cudaDeviceSynchronize();
   tc_debug_print();
   dense_debug_print();
+  drop_step_graph(S);
   S->pool.release();
   kspace_free(&S->ks);
   species_tables_free(&S->sp);
@@ -1009,6 +1038,7 @@ SO3LR_B200_API int so3lr_b200_system_set_cell(so3lr_b200_system* S, const float*
   if (rc) return rc;
   S->have_lists = false;
   S->virial_fresh = false;
+  drop_step_graph(S);
   return kOk;
 }
 
@@ -1017,6 +1047,7 @@ SO3LR_B200_API int so3lr_b200_system_set_kspace(so3lr_b200_system* S, int mode, 
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
   SO3LR_CUDA_CHECK(cudaDeviceSynchronize());
   S->virial_fresh = false;
+  drop_step_graph(S);
   if (mode == 0) {
     kspace_free(&S->ks);
     S->lr.k_alpha = 0.f;
@@ -1052,6 +1083,7 @@ SO3LR_B200_API int so3lr_b200_system_defer_skin_test(so3lr_b200_system* S, int e
 SO3LR_B200_API int so3lr_b200_system_rescale_cell(so3lr_b200_system* S, const float* cell9) {
   if (!S || !cell9 || !S->cell.periodic) return kInvalidArgument;
   S->virial_fresh = false;
+  drop_step_graph(S);
   return make_cell(cell9, &S->cell);
 }
 
@@ -1111,28 +1143,86 @@ SO3LR_B200_API int so3lr_b200_system_compute(so3lr_b200_system* S, void* stream,
   SO3LR_CUDA_CHECK(cudaSetDevice(S->model->device));
   tl_launch_counter = &S->n_launches;
   cudaStream_t st = (cudaStream_t)stream;
+  const int64_t rebuilds_before = S->n_rebuilds;
   int rc = prepare_lists(S, st, R);
   if (rc) return rc;
   float* Fout = F ? F : S->F_int;
   const int n = S->n;
-  const float* R_eval = R;
-  if (S->sorted) {
-    { gather_positions_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->d_perm, R, S->d_Rs); count_launch(); }
-    R_eval = S->d_Rs;
+  // everything between the list update and the copies of the optional outputs
+  auto evaluate = [&]() -> int {
+    const float* R_eval = R;
+    if (S->sorted) {
+      { gather_positions_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->d_perm, R, S->d_Rs); count_launch(); }
+      R_eval = S->d_Rs;
+    }
+    int rce = evaluate_fused(S, st, R_eval, S->sorted ? S->F_s : Fout);
+    if (rce) return rce;
+    launch_graph_reduce(st, S->n_graphs, S->d_graph_start, S->e_atom, S->q, R_eval, S->d_energy, S->d_dipole, S->n, S->red_scratch);
+    if (S->sorted) {
+      UnsortArgs A{{S->e_atom, S->q, S->h, S->e_zbl, S->e_coul, S->e_disp, nullptr},
+                   {S->u_e_atom, S->u_q, S->u_h, S->u_zbl, S->u_coul, S->u_disp, nullptr}};
+      { unsort_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->d_perm, S->F_s, Fout, A); count_launch(); }
+    }
+    return kOk;
+  };
+  so3lr_b200_system::StepGraph& G = S->step_graph;
+  // lists unchanged by this call, a stream that can be captured, nothing in the evaluation that allocates or reads back
+  const bool graph_ok = step_graphs_enabled() && !G.broken && n <= kStepGraphMaxAtoms && S->opt.skin > 0.f && !S->prof.on && !S->ks.mode &&
+                        S->n_rebuilds == rebuilds_before && st != nullptr && st != cudaStreamLegacy && st != cudaStreamPerThread;
+  if (graph_ok && G.exec && G.R == R && G.F == Fout && G.stamp == S->n_rebuilds && G.virial == S->want_virial) {
+    SO3LR_CUDA_CHECK(cudaGraphLaunch(G.exec, st));
+    S->n_launches += G.launches;
+    ++G.replays;
+    if (S->want_virial) S->virial_fresh = true;
+  } else if (graph_ok && G.last_R == R && G.last_F == Fout && G.last_stamp == S->n_rebuilds) {
+    if (G.exec) { cudaGraphExecDestroy(G.exec); G.exec = nullptr; }
+    if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+      cudaGetLastError();
+      G.broken = true;
+      rc = evaluate();
+      if (rc) return rc;
+    } else {
+      const int64_t l0 = S->n_launches;
+      rc = evaluate();
+      cudaGraph_t graph = nullptr;
+      const cudaError_t ce = cudaStreamEndCapture(st, &graph);
+      if (rc || ce != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        G.broken = true;
+        if (rc) return rc;
+        rc = evaluate();           // nothing ran during the failed capture
+        if (rc) return rc;
+      } else {
+        const cudaError_t ci = cudaGraphInstantiate(&G.exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (ci != cudaSuccess) {
+          cudaGetLastError();
+          G.exec = nullptr; G.broken = true;
+          rc = evaluate();
+          if (rc) return rc;
+        } else {
+          G.R = R; G.F = Fout; G.stamp = S->n_rebuilds; G.virial = S->want_virial; G.launches = S->n_launches - l0;
+          SO3LR_CUDA_CHECK(cudaGraphLaunch(G.exec, st));
+        }
+      }
+    }
+  } else {
+    rc = evaluate();
+    if (rc) return rc;
   }
-  rc = evaluate_fused(S, st, R_eval, S->sorted ? S->F_s : Fout);
-  if (rc) return rc;
-  launch_graph_reduce(st, S->n_graphs, S->d_graph_start, S->e_atom, S->q, R_eval, S->d_energy, S->d_dipole, S->n, S->red_scratch);
-  if (S->sorted) {
-    UnsortArgs A{{S->e_atom, S->q, S->h, S->e_zbl, S->e_coul, S->e_disp, nullptr},
-                 {S->u_e_atom, S->u_q, S->u_h, S->u_zbl, S->u_coul, S->u_disp, nullptr}};
-    { unsort_kernel<<<(n + 255) / 256, 256, 0, st>>>(n, S->d_perm, S->F_s, Fout, A); count_launch(); }
-  }
+  G.last_R = R; G.last_F = Fout; G.last_stamp = S->n_rebuilds;
   if (e_atom) SO3LR_CUDA_CHECK(cudaMemcpyAsync(e_atom, S->o_e_atom, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
   if (energy) SO3LR_CUDA_CHECK(cudaMemcpyAsync(energy, S->d_energy, (size_t)S->n_graphs * sizeof(double), cudaMemcpyDeviceToDevice, st));
   if (charges) SO3LR_CUDA_CHECK(cudaMemcpyAsync(charges, S->o_q, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
   if (hirshfeld) SO3LR_CUDA_CHECK(cudaMemcpyAsync(hirshfeld, S->o_h, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, st));
   if (dipole) SO3LR_CUDA_CHECK(cudaMemcpyAsync(dipole, S->d_dipole, (size_t)S->n_graphs * 3 * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  return kOk;
+}
+
+SO3LR_B200_API int so3lr_b200_system_graph_replays(so3lr_b200_system* S, int64_t* n_replays) {
+  if (!S || !n_replays) return kInvalidArgument;
+  *n_replays = S->step_graph.replays;
   return kOk;
 }
 
@@ -1292,6 +1382,7 @@ SO3LR_B200_API int so3lr_b200_system_enable_virial(so3lr_b200_system* S, int ena
   }
   S->want_virial = enable != 0;
   S->virial_fresh = false;
+  drop_step_graph(S);
   return kOk;
 }
 
@@ -1468,6 +1559,7 @@ SO3LR_B200_API int so3lr_b200_dd_set_atoms(so3lr_b200_system* S, int n_local, co
                                            const float* cell9) {
   if (!S || !shells4 || !Z_local_dev || n_local <= 0) return kInvalidArgument;
   if (S->n_graphs != 1) return kInvalidArgument;
+  drop_step_graph(S);
   if (S->ks.mode && !S->ks_cell_set) {
     std::fprintf(stderr, "so3lr_b200: a decomposed evaluation with the reciprocal-space Coulomb sum needs so3lr_b200_dd_kspace_cell first\n");
     return kInvalidArgument;

@@ -167,6 +167,12 @@ class System:
         check(lib.so3lr_b200_system_stats(self._h, *[C.byref(x) for x in v]), "stats")
         return dict(rebuilds=v[0].value, edges=v[1].value, pairs=v[2].value, launches=v[3].value)
 
+    def graph_replays(self):
+        """Evaluations that were replayed from a CUDA graph so far (see so3lr_b200_system_graph_replays)."""
+        v = C.c_int64()
+        check(lib.so3lr_b200_system_graph_replays(self._h, C.byref(v)), "graph_replays")
+        return v.value
+
     def valid_edges(self):
         """Short-range list entries inside the cutoff at the latest evaluation (synchronises the device)."""
         v = C.c_int64()

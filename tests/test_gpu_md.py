@@ -373,3 +373,32 @@ def test_md_loop_writes_frames_and_observables_without_waiting_for_the_device(tm
         # sum_i q_i R_i over 648 atoms up to 18.7 A from the origin: a uniform charge offset of 1e-7 (float32 rounding of the charge
         # conservation, which differs between two evaluations with different atom orderings) moves it by 6e-4
         np.testing.assert_allclose(dip, ref["dipole_vec"][0].cpu().numpy(), atol=2e-3)
+
+
+def test_md_steps_replayed_from_a_cuda_graph_match_plain_launches():
+    """Between two list rebuilds the force evaluation of a small structure is replayed from a CUDA graph when the caller's stream
+    can be captured; on the legacy default stream the same steps run as plain launches.  Same trajectory either way."""
+    from so3lr_b200 import workloads as W
+    from so3lr_b200.engine import System
+    Z, R, cell = W.water_box(216, 18.7, 5, jitter=0.03)
+    V, m = W.maxwell_boltzmann(Z, 300.0, 6)
+
+    def run(stream, steps=14):
+        s = System(Z, cell, cutoff_lr=8.0, damping=2.0, skin=0.6)
+        s.defer_skin_test(True, 0.05)
+        with torch.cuda.stream(stream):
+            Rd = torch.tensor(np.asarray(R, dtype=np.float32), device="cuda")
+            Vd = torch.tensor(np.asarray(V, dtype=np.float32), device="cuda")
+            md_ = torch.tensor(np.asarray(m, dtype=np.float32), device="cuda")
+            Fd = s.compute(Rd)["forces"].clone()
+            E = s.nve(steps, 0.5, md_, Rd, Vd, Fd)
+        stream.synchronize()
+        return Rd.cpu().numpy(), Fd.cpu().numpy(), float(E.sum()), s.stats(), s.graph_replays()
+
+    Ra, Fa, Ea, sa, ra = run(torch.cuda.Stream())
+    Rb, Fb, Eb, sb, rb = run(torch.cuda.default_stream())
+    assert rb == 0 and ra >= 8, (ra, rb)                 # replays on the side stream (the first two steps capture), none on the default one
+    assert sa["launches"] == sb["launches"] and sa["rebuilds"] == sb["rebuilds"]
+    np.testing.assert_allclose(Ra, Rb, atol=2e-5)        # atomics reorder sums: float32 roundoff over 14 steps
+    np.testing.assert_allclose(Fa, Fb, atol=2e-4)
+    assert abs(Ea - Eb) < 1e-5 * abs(Eb)
