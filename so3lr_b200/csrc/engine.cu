@@ -1176,7 +1176,14 @@ SO3LR_B200_API int so3lr_b200_system_compute(so3lr_b200_system* S, void* stream,
     if (S->want_virial) S->virial_fresh = true;
   } else if (graph_ok && G.last_R == R && G.last_F == Fout && G.last_stamp == S->n_rebuilds) {
     if (G.exec) { cudaGraphExecDestroy(G.exec); G.exec = nullptr; }
-    if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+    // a stream that its owner is capturing already (a runtime that records its own graphs around the call) takes plain launches
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+      cudaGetLastError();
+      G.broken = true;
+      rc = evaluate();
+      if (rc) return rc;
+    } else if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
       cudaGetLastError();
       G.broken = true;
       rc = evaluate();
