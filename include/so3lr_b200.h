@@ -362,6 +362,9 @@ SO3LR_B200_API void so3lr_b200_host_sph_harm_vjp(float x, float y, float z, cons
 SO3LR_B200_API void so3lr_b200_host_pair_terms(float r, int zi, int zj, float qi, float qj, float hi, float hj, float cutoff_lr,
                                 float damping, float* out8);
 /* out4 = dispersion energy, d/dr, d/dh_i, d/dh_j of one pair as the pair kernels evaluate it (hand-derived partials) */
+/* Host-only check of the direct Ewald sum's tile decomposition for an index grid: counts4 = number of tiles, of groups, largest
+ * group, inconsistencies found; weight_sum = sum of the slot weights (n1 n2 n3 - 1 when every non-zero index is counted once). */
+SO3LR_B200_API int so3lr_b200_host_kspace_tiles(int n1, int n2, int n3, int64_t* counts4, double* weight_sum);
 /* out2 = chi(r), d chi / d r of the Coulomb pair function; smearing > 0 takes the reciprocal-space part out of it */
 SO3LR_B200_API void so3lr_b200_host_coulomb_chi(float r, float cutoff_lr, float smearing, float* out2);
 SO3LR_B200_API void so3lr_b200_host_dispersion_fast(float r, int zi, int zj, float hi, float hj, float cutoff_lr, float damping,

@@ -83,6 +83,7 @@ def _load():
         "so3lr_b200_host_sph_harm": (None, [f32, f32, f32, p]),
         "so3lr_b200_host_sph_harm_vjp": (None, [f32, f32, f32, p, p]),
         "so3lr_b200_host_pair_terms": (None, [f32, i32, i32, f32, f32, f32, f32, f32, f32, p]),
+        "so3lr_b200_host_kspace_tiles": (i32, [i32, i32, i32, p, C.POINTER(f64)]),
         "so3lr_b200_host_coulomb_chi": (None, [f32, f32, f32, p]),
         "so3lr_b200_host_dispersion_fast": (None, [f32, i32, i32, f32, f32, f32, f32, p]),
         "so3lr_b200_host_zbl": (None, [p, f32, i32, i32, p]),

@@ -1869,6 +1869,39 @@ SO3LR_B200_API void so3lr_b200_host_pair_terms(float r, int zi, int zj, float qi
   dispersion_pair(P, r, zi, zj, hi, hj, out8[3], out8[4], out8[5], out8[6]);
   out8[7] = 0.f;
 }
+// Tile decomposition of the direct Ewald sum for an index grid (n1, n2, n3), host only.  counts4 = tiles, groups, largest group,
+// groups that are not runs of adjacent tiles; weight_sum = sum of the slot weights (every non-zero index triple of the grid must be
+// counted once: 2 for the kept member of a pair (k, -k), 1 for an index whose mirror image is outside the grid)
+SO3LR_B200_API int so3lr_b200_host_kspace_tiles(int n1, int n2, int n3, int64_t* counts4, double* weight_sum) {
+  if (!counts4 || !weight_sum || n1 < 1 || n2 < 1 || n3 < 1 || n1 > 1024 || n2 > 1024 || n3 > 1024) return kInvalidArgument;
+  std::vector<int4> tiles; std::vector<float> wgt; std::vector<int2> groups;
+  kspace_build_tiles(n1, n2, n3, tiles, wgt, groups);
+  double sum = 0.0;
+  for (float w : wgt) sum += w;
+  int64_t largest = 0, bad = 0, covered = 0;
+  std::vector<char> seen(tiles.size(), 0);
+  for (const int2& g : groups) {
+    if (g.y > largest) largest = g.y;
+    for (int u = 0; u < g.y; ++u) {
+      const size_t t = (size_t)g.x + u;
+      if (t >= tiles.size() || seen[t]) { ++bad; continue; }
+      seen[t] = 1; ++covered;
+      if (u > 0 && (tiles[t].x != tiles[g.x].x || tiles[t].y != tiles[g.x].y || tiles[t].z != tiles[t - 1].z + 16)) ++bad;
+    }
+  }
+  if (covered != (int64_t)tiles.size()) ++bad;
+  // row masks agree with the weights
+  for (size_t t = 0; t < tiles.size(); ++t)
+    for (int r = 0; r < 16; ++r) {
+      bool any = false;
+      for (int c = 0; c < 16; ++c) any |= wgt[t * 256 + r * 16 + c] > 0.f;
+      if (any != (((tiles[t].w >> r) & 1) != 0)) ++bad;
+    }
+  counts4[0] = (int64_t)tiles.size(); counts4[1] = (int64_t)groups.size(); counts4[2] = largest; counts4[3] = bad;
+  *weight_sum = sum;
+  return kOk;
+}
+
 // chi(r) and its derivative of the Coulomb pair function with the reciprocal-space part taken out (smearing > 0) or not (0)
 SO3LR_B200_API void so3lr_b200_host_coulomb_chi(float r, float cutoff_lr, float smearing, float* out2) {
   LrParams P{};

@@ -65,6 +65,8 @@ struct KSpaceDev {
   int plan_r2c = 0, plan_c2r = 0;   // cuFFT plans (handles)
   bool plans = false;
 };
+// host side of the direct sum's set-up: tiles (h1, first h2, first h3, row mask), 256 slot weights per tile, groups (first tile, count)
+void kspace_build_tiles(int n1, int n2, int n3, std::vector<int4>& tiles, std::vector<float>& wgt, std::vector<int2>& groups);
 int kspace_setup(KSpaceDev* K, int n_atoms, int mode, float smearing, int n1, int n2, int n3);   // allocates; call outside handlers
 void kspace_free(KSpaceDev* K);
 // adds to e_coul (per-atom energies), gq (dE/dq), F (force_sign = 1: forces at fixed charges; -1: the gradient) and, when given, the

@@ -452,15 +452,8 @@ static int kspace_setup_mesh(KSpaceDev* K, int n_atoms, float smearing, int n1, 
   return kOk;
 }
 
-int kspace_setup(KSpaceDev* K, int n_atoms, int mode, float smearing, int n1, int n2, int n3) {
-  kspace_free(K);
-  if (!(smearing > 0.f) || n1 < 1 || n2 < 1 || n3 < 1 || n1 > 1024 || n2 > 1024 || n3 > 1024) return kInvalidArgument;
-  if (mode == 2) {
-    int rc = kspace_setup_mesh(K, n_atoms, smearing, n1, n2, n3);
-    if (rc) kspace_free(K);
-    return rc;
-  }
-  if (mode != 1) return kInvalidArgument;
+// Tiles of the kept half of the index grid, their slot weights and the groups of the structure-factor kernel (host side)
+void kspace_build_tiles(int n1, int n2, int n3, std::vector<int4>& tiles, std::vector<float>& wgt, std::vector<int2>& groups) {
   const int nn[3] = {n1, n2, n3};
   int lo[3], hi[3];
   for (int d = 0; d < 3; ++d) { lo[d] = -(nn[d] / 2); hi[d] = (nn[d] + 1) / 2 - 1; }
@@ -472,8 +465,6 @@ int kspace_setup(KSpaceDev* K, int n_atoms, int mode, float smearing, int n1, in
     const bool positive = a > 0 || (a == 0 && (b > 0 || (b == 0 && c > 0)));
     return positive ? 2.f : 0.f;
   };
-  std::vector<int4> tiles;
-  std::vector<float> wgt;
   for (int h1 = lo[0]; h1 <= hi[0]; ++h1)
     for (int b0 = lo[1]; b0 <= hi[1]; b0 += kTile)
       for (int c0 = lo[2]; c0 <= hi[2]; c0 += kTile) {
@@ -487,7 +478,6 @@ int kspace_setup(KSpaceDev* K, int n_atoms, int mode, float smearing, int n1, in
         wgt.insert(wgt.end(), w, w + kTileK);
       }
   // groups of up to four tiles that share (h1, first h2) and are adjacent along h3, runs longer than four split evenly
-  std::vector<int2> groups;
   for (size_t i = 0; i < tiles.size();) {
     size_t j = i + 1;
     while (j < tiles.size() && tiles[j].x == tiles[i].x && tiles[j].y == tiles[i].y && tiles[j].z == tiles[j - 1].z + kTile) ++j;
@@ -495,6 +485,21 @@ int kspace_setup(KSpaceDev* K, int n_atoms, int mode, float smearing, int n1, in
     for (int k = 0; k < run; k += size) groups.push_back(make_int2((int)i + k, run - k < size ? run - k : size));
     i = j;
   }
+}
+
+int kspace_setup(KSpaceDev* K, int n_atoms, int mode, float smearing, int n1, int n2, int n3) {
+  kspace_free(K);
+  if (!(smearing > 0.f) || n1 < 1 || n2 < 1 || n3 < 1 || n1 > 1024 || n2 > 1024 || n3 > 1024) return kInvalidArgument;
+  if (mode == 2) {
+    int rc = kspace_setup_mesh(K, n_atoms, smearing, n1, n2, n3);
+    if (rc) kspace_free(K);
+    return rc;
+  }
+  if (mode != 1) return kInvalidArgument;
+  std::vector<int4> tiles;
+  std::vector<float> wgt;
+  std::vector<int2> groups;
+  kspace_build_tiles(n1, n2, n3, tiles, wgt, groups);
   if (tiles.empty() || tiles.size() > (size_t)(1 << 22)) return tiles.empty() ? kInvalidArgument : kTooLarge;
   K->n_tiles = (int)tiles.size();
   K->n_groups = (int)groups.size();

@@ -145,3 +145,17 @@ def test_coulomb_pair_function_with_the_reciprocal_part_taken_out_matches_oracle
             (dchi,) = torch.autograd.grad(chi, rt)
             assert abs(out[0] - chi.item()) < 2e-7 + 2e-6 * abs(chi.item()), (cutoff, r, out[0], chi.item())
             assert abs(out[1] - dchi.item()) < 2e-7 + 5e-6 * abs(dchi.item()), (cutoff, r, out[1], dchi.item())
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 2), (4, 5, 1), (16, 16, 16), (17, 33, 64), (21, 20, 19), (52, 52, 52), (83, 83, 83), (3, 130, 7)])
+def test_ewald_tiles_count_every_index_once(shape):
+    """Half of the index grid is kept (one member of every pair (k, -k) with weight 2, unpaired indices of even extents with
+    weight 1): the weights must add up to the number of non-zero index triples, the groups of the structure-factor kernel must
+    cover every tile exactly once with runs of at most four adjacent tiles, and the row masks must agree with the weights."""
+    counts = np.zeros(4, dtype=np.int64)
+    wsum = C.c_double()
+    assert lib.so3lr_b200_host_kspace_tiles(*shape, _p(counts), C.byref(wsum)) == 0
+    n1, n2, n3 = shape
+    assert wsum.value == n1 * n2 * n3 - 1
+    assert counts[3] == 0 and 1 <= counts[2] <= 4 and counts[1] <= counts[0]
+    assert counts[0] * 256 >= (n1 * n2 * n3 - 1) / 2
