@@ -211,6 +211,8 @@ class System:
         shape = tuple(int(v) for v in (k_grid.shape if hasattr(k_grid, "shape") else k_grid))
         if len(shape) != 3:
             raise ValueError("k_grid must have three dimensions")
+        if k_smearing is None:
+            raise ValueError("k_smearing is needed with k_grid")
         s = float(np.asarray(k_smearing.detach().cpu() if torch.is_tensor(k_smearing) else k_smearing, dtype=np.float64).reshape(-1)[0])
         if method not in ("ewald", "pme"):
             raise ValueError("method must be 'ewald' or 'pme'")

@@ -107,6 +107,8 @@ class FrameSink:
     def append(self, positions, momenta=None, box=None, observables: Optional[Dict[str, torch.Tensor]] = None, step: Optional[int] = None):
         """Queue one frame.  Tensors may live on the device (copied asynchronously, ordered after the work already enqueued on the
         current stream) or on the host.  box: None, (3,), or (3, 3) with lattice vectors as rows."""
+        if getattr(self, "_closed", False):
+            raise RuntimeError("the sink is closed")
         if self._error is not None:
             raise RuntimeError("trajectory writer failed") from self._error
         rec = {"positions": positions}
@@ -151,7 +153,10 @@ class FrameSink:
         self._todo.put((slot, event, list(rec.keys()), cell, step))
 
     def close(self):
-        """Write what is in flight and close the files."""
+        """Write what is in flight and close the files (a second call does nothing)."""
+        if getattr(self, "_closed", False):
+            return
+        self._closed = True
         self._todo.put(None)
         self._thread.join()
         if self.fmt == "npy":

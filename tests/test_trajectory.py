@@ -73,5 +73,8 @@ def test_existing_output_and_missing_observables_fail_loudly(tmp_path):
     with pytest.raises(KeyError):
         sink.append(torch.zeros(3, 3), torch.zeros(3, 3), None, {})
     sink.close()
+    sink.close()                                   # idempotent
+    with pytest.raises(RuntimeError, match="closed"):
+        sink.append(torch.zeros(3, 3), torch.zeros(3, 3), None, dict(partial_charges=torch.zeros(3)))
     with pytest.raises(ValueError):
         FrameSink(tmp_path / "b", Z, fmt="hdf5")
