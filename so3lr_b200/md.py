@@ -198,3 +198,44 @@ def run_cycles(system: System, apply_fn, state: MDState, cycles: int, steps_per_
         if on_cycle is not None:
             on_cycle(cycle, state)
     return state
+
+
+def save_state(state: MDState, box, cycle: int, path_to_save, ensemble: str = "nvt"):
+    """Restart file of an MD run, one .npz (so3lr/cli/so3lr_md.py:2286-2345): position, momentum, force, mass, box, the cycle
+    number and the ensemble's extra state -- the thermostat chain for 'nvt', the barostat / chains record for 'npt' (both are the
+    flat device records of so3lr_b200.engine.nhc_state / npt_state).  Waits for the device."""
+    ens = ensemble.lower()
+    if ens not in ("nve", "nvt", "npt"):
+        raise ValueError("ensemble must be 'nve', 'nvt' or 'npt'")
+    cpu = lambda t: np.asarray(t.detach().cpu())
+    d = dict(position=cpu(state.position), momentum=cpu(state.momentum), force=cpu(state.force), mass=cpu(state.mass),
+             box=np.zeros(3) if box is None else np.asarray(box, dtype=np.float64), step=int(cycle), ensemble=ens)
+    if ens in ("nvt", "npt"):
+        if state.chain is None:
+            raise ValueError(f"an '{ens}' state carries its thermostat record in state.chain")
+        d["chain"] = cpu(state.chain)
+    if ens == "npt" and state.reference_box is not None:
+        d["reference_box"] = np.asarray(state.reference_box, dtype=np.float64)
+    np.savez(path_to_save, **d)
+
+
+class RestartInNewEnsembleError(RuntimeError):
+    """The restart file was written by another ensemble (so3lr/cli/so3lr_md.py:2369-2372 raises an error of this name)."""
+
+
+def load_state(path_to_load, ensemble: str = "nvt", device="cuda"):
+    """(state, box, cycle) from a file written by save_state; raises RestartInNewEnsembleError when the file belongs to another
+    ensemble (so3lr/cli/so3lr_md.py:2348-2440)."""
+    z = np.load(path_to_load, allow_pickle=False)
+    ens = ensemble.lower()
+    if str(z["ensemble"]) != ens:
+        raise RestartInNewEnsembleError(f"restart file holds an '{z['ensemble']}' state, asked for '{ens}'")
+    dev = torch.device(device)
+    t = lambda a, dt=torch.float32: torch.as_tensor(np.asarray(a)).to(dev, dt).contiguous()
+    mass = t(z["mass"])
+    chain = t(z["chain"], torch.float64) if "chain" in z.files else None
+    box = np.asarray(z["box"], dtype=np.float64)
+    state = MDState(t(z["position"]), (t(z["momentum"]) / mass[:, None]).contiguous(), t(z["force"]), mass, chain, None,
+                    box if box.shape == (3, 3) else None,
+                    np.asarray(z["reference_box"], dtype=np.float64) if "reference_box" in z.files else None)
+    return state, (None if not box.any() else box), int(z["step"])
