@@ -433,9 +433,12 @@ __global__ void __launch_bounds__(kFwThreads, 1) attn_fwd_tc_kernel(const unsign
     st_ij[2 * row] = i; st_ij[2 * row + 1] = j;
     const float* gi = ev_in + (size_t)i * kMTot;
     const float* gj = ev_in + (size_t)j * kMTot;
-    float* d = st_ev + row * (2 * kEvStride);
+    // receivers' rows in the first half of the buffer, senders' rows in the second: consecutive entries are 112 bytes apart in
+    // either half, which spreads the 16-byte accesses of eight threads over all banks (interleaved, 224 bytes apart, they collide
+    // in pairs)
+    float* d = st_ev + row * kEvStride;
 #pragma unroll
-    for (int c = 0; c < 6; ++c) { cp_async16(d + 4 * c, gi + 4 * c); cp_async16(d + kEvStride + 4 * c, gj + 4 * c); }
+    for (int c = 0; c < 6; ++c) { cp_async16(d + 4 * c, gi + 4 * c); cp_async16(d + TE * kEvStride + 4 * c, gj + 4 * c); }
   };
   for (int k = tid; k < kTcImageBytes / 16; k += kFwThreads) reinterpret_cast<uint4*>(smem + kOffImg)[k] = reinterpret_cast<const uint4*>(img_g)[k];
   for (int k = tid; k < 512; k += kFwThreads) {      // [filter][hidden unit][w0 w1 w2 w3 b - - -]
@@ -500,7 +503,7 @@ __global__ void __launch_bounds__(kFwThreads, 1) attn_fwd_tc_kernel(const unsign
         }
       } else {
         float s[4];
-        invariants(st_ev + row * (2 * kEvStride), st_ev + row * (2 * kEvStride) + kEvStride, s);
+        invariants(st_ev + row * kEvStride, st_ev + (TE + row) * kEvStride, s);
         store_spherical_hidden_f(smem + kOffA, row, s, sph, role - 2);
       }
     }
